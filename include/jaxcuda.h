@@ -1,0 +1,140 @@
+/*
+ * C ABI of libjaxcuda.so: the B200 `cuda` device backend for jax-js.
+ *
+ * Each entry point stands behind one method of the reference's `Backend` interface
+ * (src/backend.ts:158-211); the TypeScript class that implements that interface calls
+ * these through a Node addon.  Plain pointers and sizes only.
+ *
+ * Every call returns a jaxcuda_status; on failure jaxcuda_last_error(ctx) holds a
+ * message (NVRTC logs and the generated source included for compile errors, as the
+ * reference surfaces shader compile errors, src/backend/webgpu.ts:778-792).
+ *
+ * Threading: one host thread drives a context at a time (the reference's backends are
+ * driven from the single JS thread).  All device work of a context is ordered on one
+ * stream: dispatch order is execution order (src/backend.ts:203-210).
+ */
+#ifndef JAXCUDA_H
+#define JAXCUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#include "jaxcuda_ir.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  JAXCUDA_OK = 0,
+  JAXCUDA_ESLOT = 1,        /* SlotError: slot invalid or already freed (src/backend.ts:222-226) */
+  JAXCUDA_EUNSUPPORTED = 2, /* UnsupportedOpError / UnsupportedRoutineError (src/backend.ts:228-240) */
+  JAXCUDA_EINVAL = 3,       /* plain Error: size mismatch, bad image, bad range (src/backend/cpu.ts:21-24) */
+  JAXCUDA_ECOMPILE = 4,     /* NVRTC rejected generated source */
+  JAXCUDA_ECUDA = 5,        /* a CUDA or NCCL call failed */
+  JAXCUDA_ENOMEM = 6
+} jaxcuda_status;
+
+typedef struct jaxcuda_ctx jaxcuda_ctx;
+typedef struct jaxcuda_exe jaxcuda_exe;
+typedef uint32_t jaxcuda_slot; /* `Slot`, src/backend.ts:155 */
+
+/* createBackend("cuda") arm (src/backend.ts:72-142): binds a context to one GPU and creates
+ * its stream.  Fails with JAXCUDA_ECUDA when no usable GPU or driver is present: there is no
+ * CPU fallback. */
+int jaxcuda_create(int device, jaxcuda_ctx** out);
+int jaxcuda_destroy(jaxcuda_ctx* ctx);
+const char* jaxcuda_last_error(jaxcuda_ctx* ctx); /* ctx may be NULL: error of the last failed create */
+
+/* Backend.maxArgs (src/backend.ts:163; the Wasm backend's value, src/backend/wasm.ts:38). */
+int jaxcuda_max_args(void);
+
+/* Backend.malloc (src/backend.ts:166-171): new slot with reference count 1.  `init` may be NULL;
+ * otherwise `init_bytes` must equal `bytes` (JAXCUDA_EINVAL, as src/backend/cpu.ts:21-24).
+ * bytes == 0 is legal (src/backend/webgpu.ts:84-86). */
+int jaxcuda_malloc(jaxcuda_ctx* ctx, size_t bytes, const void* init, size_t init_bytes, jaxcuda_slot* out);
+/* Backend.incRef / decRef (src/backend.ts:173-180).  decRef of a dead slot is JAXCUDA_ESLOT. */
+int jaxcuda_incref(jaxcuda_ctx* ctx, jaxcuda_slot slot);
+int jaxcuda_decref(jaxcuda_ctx* ctx, jaxcuda_slot slot);
+/* Backend.read / readSync (src/backend.ts:182-190): copies bytes [start, start+count) to dst after
+ * all dispatched work has finished.  count == SIZE_MAX means "to the end"; count == 0 is a pure
+ * barrier (src/frontend/array.ts:827). */
+int jaxcuda_read(jaxcuda_ctx* ctx, jaxcuda_slot slot, size_t start, size_t count, void* dst);
+/* Upload into an existing slot (the H2D half of malloc(initialData), for callers that reuse
+ * slots between steps instead of reallocating; the Wasm backend writes through its memory view,
+ * src/backend/wasm.ts:57-75). */
+int jaxcuda_write(jaxcuda_ctx* ctx, jaxcuda_slot slot, size_t start, size_t count, const void* src);
+int jaxcuda_slot_size(jaxcuda_ctx* ctx, jaxcuda_slot slot, size_t* bytes);
+
+/* Backend.prepareKernel[Sync] (src/backend.ts:192-196).  `ir` is the lowered Kernel image of
+ * jaxcuda_ir.h; `hash` is the caller's cache key (FpHash of the Kernel, src/backend/wasm.ts:126),
+ * 0 to let the library hash the image.  Compiles with NVRTC on a cache miss. */
+int jaxcuda_prepare_kernel(jaxcuda_ctx* ctx, const uint8_t* ir, size_t len, uint64_t hash, jaxcuda_exe** out);
+
+/* Diagnostic that needs no GPU: parse, choose the skeleton and (compile != 0) run NVRTC for
+ * sm_100a.  Writes the plan description to `describe`; `message` receives the error text, or,
+ * when compile == 0, the generated CUDA C.  force_skeleton < 0 lets the planner choose.
+ * Used by CPU-side tests of the code generator; no counterpart in the reference. */
+int jaxcuda_check_kernel(const uint8_t* ir, size_t len, int sm_count, int force_skeleton, int compile,
+                         char* describe, size_t describe_len, char* message, size_t message_len);
+
+/* `RoutineType` (src/routine.ts:112-123) flattened: shapes are concatenated, ranks give the split. */
+typedef struct {
+  int n_inputs, n_outputs;
+  const int32_t* input_dtypes;  /* jaxcuda_dtype per input */
+  const int32_t* input_ranks;
+  const int64_t* input_shapes;  /* all input shapes, concatenated */
+  const int32_t* output_dtypes;
+  const int32_t* output_ranks;
+  const int64_t* output_shapes;
+} jaxcuda_routine_type;
+
+/* Backend.prepareRoutine[Sync] (src/backend.ts:198-202).  name is a `Routines` member
+ * (src/routine.ts:32-102): "Sort" and "Argsort" are implemented; others return
+ * JAXCUDA_EUNSUPPORTED (UnsupportedRoutineError). */
+int jaxcuda_prepare_routine(jaxcuda_ctx* ctx, const char* name, const jaxcuda_routine_type* type,
+                            const char* params_json, jaxcuda_exe** out);
+
+/* Backend.dispatch (src/backend.ts:204-211): enqueue only; runs in dispatch order. */
+int jaxcuda_dispatch(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const jaxcuda_slot* inputs, int n_inputs,
+                     const jaxcuda_slot* outputs, int n_outputs);
+/* Executables are owned by the context's cache; release drops the caller's handle. */
+int jaxcuda_exe_release(jaxcuda_exe* exe);
+
+/* What the backend decided for an executable (setDebug(4) prints the same for WebGPU tuning,
+ * src/tuner.ts:250): skeleton name and launch shape, generated CUDA C, algorithmic bytes/flops. */
+const char* jaxcuda_exe_describe(jaxcuda_exe* exe);
+const char* jaxcuda_exe_source(jaxcuda_exe* exe);
+int jaxcuda_exe_cost(jaxcuda_exe* exe, double* algo_bytes, double* algo_flops, int* n_launches);
+
+/* Pinned host staging memory for callers that time host<->device transfers. */
+int jaxcuda_host_alloc(jaxcuda_ctx* ctx, size_t bytes, void** out);
+int jaxcuda_host_free(jaxcuda_ctx* ctx, void* ptr);
+
+/* Barrier: wait for everything dispatched so far (read(slot, 0, 0) without a slot). */
+int jaxcuda_sync(jaxcuda_ctx* ctx);
+
+/* Device timing of a dispatch sequence on the context's stream (the cuda counterpart of the
+ * WebGPU timestamp queries, src/backend/webgpu/tracing.ts:11-164): records an event now. */
+int jaxcuda_event_record(jaxcuda_ctx* ctx, int index); /* index in [0, 65536) */
+int jaxcuda_event_elapsed_ms(jaxcuda_ctx* ctx, int start_index, int stop_index, float* ms);
+/* Number of kernels this context has launched so far (its own kernels only). */
+uint64_t jaxcuda_launch_count(jaxcuda_ctx* ctx);
+
+/* Interop for host code that shares the CUDA primary context (torch): raw pointer of a slot and
+ * the stream handle (cudaStream_t) as integers.  No counterpart in the reference. */
+int jaxcuda_slot_ptr(jaxcuda_ctx* ctx, jaxcuda_slot slot, uint64_t* device_ptr);
+uint64_t jaxcuda_stream(jaxcuda_ctx* ctx);
+
+/* Data-parallel gradient sum.  No counterpart in the reference, which has no multi-device
+ * support: one context per GPU and process, an NCCL communicator over them, and an in-place
+ * f32 sum over the listed slots on the context's stream, ordered after prior dispatches. */
+int jaxcuda_comm_unique_id(void* id128); /* fills 128 bytes (ncclUniqueId) on rank 0 */
+int jaxcuda_comm_init(jaxcuda_ctx* ctx, int rank, int nranks, const void* id128);
+int jaxcuda_allreduce_sum_f32(jaxcuda_ctx* ctx, const jaxcuda_slot* slots, int n);
+int jaxcuda_comm_destroy(jaxcuda_ctx* ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* JAXCUDA_H */

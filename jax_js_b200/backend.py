@@ -1,0 +1,327 @@
+"""`CudaBackend`: the reference's `Backend` interface (src/backend.ts:158-211) over
+libjaxcuda.so.
+
+Method names, argument meaning and error behaviour follow the TypeScript interface
+(malloc / incRef / decRef / read / readSync / prepareKernel[Sync] / prepareRoutine[Sync] /
+dispatch), spelled in snake_case; `Executable`, `SlotError`, `UnsupportedOpError` and
+`UnsupportedRoutineError` mirror src/backend.ts:213-240.  There is no CPU fallback: without
+the shared library or without a B200 the constructor raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+from typing import Sequence
+
+import numpy as np
+
+from .alu import DType, Kernel
+from .routine import Routine
+
+_HERE = Path(__file__).resolve().parent
+_LIB_PATH = _HERE / "libjaxcuda.so"
+_lib = None
+
+OK, ESLOT, EUNSUPPORTED, EINVAL, ECOMPILE, ECUDA, ENOMEM = range(7)
+SIZE_MAX = ctypes.c_size_t(-1).value
+
+
+class SlotError(RuntimeError):
+    """src/backend.ts:222-226."""
+
+
+class UnsupportedOpError(RuntimeError):
+    """src/backend.ts:228-234."""
+
+
+class UnsupportedRoutineError(RuntimeError):
+    """src/backend.ts:236-240."""
+
+
+class CompileError(RuntimeError):
+    """NVRTC rejected generated source; the message carries the log and the source."""
+
+
+class CudaError(RuntimeError):
+    pass
+
+
+class _RoutineType(ctypes.Structure):
+    _fields_ = [("n_inputs", ctypes.c_int), ("n_outputs", ctypes.c_int),
+                ("input_dtypes", ctypes.POINTER(ctypes.c_int32)), ("input_ranks", ctypes.POINTER(ctypes.c_int32)),
+                ("input_shapes", ctypes.POINTER(ctypes.c_int64)),
+                ("output_dtypes", ctypes.POINTER(ctypes.c_int32)), ("output_ranks", ctypes.POINTER(ctypes.c_int32)),
+                ("output_shapes", ctypes.POINTER(ctypes.c_int64))]
+
+
+#: Every symbol include/jaxcuda.h declares, with its ctypes signature (restype, argtypes).
+_P, _U32, _U64, _SZ, _I = ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_size_t, ctypes.c_int
+SYMBOLS = {
+    "jaxcuda_create": (_I, [_I, ctypes.POINTER(_P)]),
+    "jaxcuda_destroy": (_I, [_P]),
+    "jaxcuda_last_error": (ctypes.c_char_p, [_P]),
+    "jaxcuda_max_args": (_I, []),
+    "jaxcuda_malloc": (_I, [_P, _SZ, _P, _SZ, ctypes.POINTER(_U32)]),
+    "jaxcuda_incref": (_I, [_P, _U32]),
+    "jaxcuda_decref": (_I, [_P, _U32]),
+    "jaxcuda_read": (_I, [_P, _U32, _SZ, _SZ, _P]),
+    "jaxcuda_write": (_I, [_P, _U32, _SZ, _SZ, _P]),
+    "jaxcuda_slot_size": (_I, [_P, _U32, ctypes.POINTER(_SZ)]),
+    "jaxcuda_prepare_kernel": (_I, [_P, ctypes.c_char_p, _SZ, _U64, ctypes.POINTER(_P)]),
+    "jaxcuda_check_kernel": (_I, [ctypes.c_char_p, _SZ, _I, _I, _I, ctypes.c_char_p, _SZ, ctypes.c_char_p, _SZ]),
+    "jaxcuda_prepare_routine": (_I, [_P, ctypes.c_char_p, ctypes.POINTER(_RoutineType), ctypes.c_char_p, ctypes.POINTER(_P)]),
+    "jaxcuda_dispatch": (_I, [_P, _P, ctypes.POINTER(_U32), _I, ctypes.POINTER(_U32), _I]),
+    "jaxcuda_exe_release": (_I, [_P]),
+    "jaxcuda_exe_describe": (ctypes.c_char_p, [_P]),
+    "jaxcuda_exe_source": (ctypes.c_char_p, [_P]),
+    "jaxcuda_exe_cost": (_I, [_P, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double), ctypes.POINTER(_I)]),
+    "jaxcuda_host_alloc": (_I, [_P, _SZ, ctypes.POINTER(_P)]),
+    "jaxcuda_host_free": (_I, [_P, _P]),
+    "jaxcuda_sync": (_I, [_P]),
+    "jaxcuda_event_record": (_I, [_P, _I]),
+    "jaxcuda_event_elapsed_ms": (_I, [_P, _I, _I, ctypes.POINTER(ctypes.c_float)]),
+    "jaxcuda_launch_count": (_U64, [_P]),
+    "jaxcuda_slot_ptr": (_I, [_P, _U32, ctypes.POINTER(_U64)]),
+    "jaxcuda_stream": (_U64, [_P]),
+    "jaxcuda_comm_unique_id": (_I, [_P]),
+    "jaxcuda_comm_init": (_I, [_P, _I, _I, _P]),
+    "jaxcuda_allreduce_sum_f32": (_I, [_P, ctypes.POINTER(_U32), _I]),
+    "jaxcuda_comm_destroy": (_I, [_P]),
+}
+
+
+def load_library():
+    """dlopen libjaxcuda.so (built by `python -m jax_js_b200.build`) and bind its C ABI."""
+    global _lib
+    if _lib is None:
+        if not _LIB_PATH.exists():
+            raise CudaError(f"{_LIB_PATH} is missing: run `python -m jax_js_b200.build` "
+                            "(the cuda backend has no CPU fallback)")
+        lib = ctypes.CDLL(str(_LIB_PATH))
+        for name, (restype, argtypes) in SYMBOLS.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = restype, argtypes
+        _lib = lib
+    return _lib
+
+
+def check_kernel(kernel: Kernel, *, sm_count: int = 148, force_skeleton: int = -1, compile: bool = True):
+    """Plan (and NVRTC-compile) a kernel without a GPU.  Returns (describe, source)."""
+    lib = load_library()
+    image = kernel.serialize()
+    desc = ctypes.create_string_buffer(512)
+    msg = ctypes.create_string_buffer(1 << 20)
+    rc = lib.jaxcuda_check_kernel(image, len(image), sm_count, force_skeleton, 0, desc, len(desc), msg, len(msg))
+    source = msg.value.decode()
+    if rc == OK and compile:
+        rc = lib.jaxcuda_check_kernel(image, len(image), sm_count, force_skeleton, 1, desc, len(desc), msg, len(msg))
+    if rc != OK:
+        _raise(rc, msg.value.decode())
+    return desc.value.decode(), source
+
+
+def _raise(status: int, message: str):
+    if status == ESLOT:
+        raise SlotError(message)
+    if status == EUNSUPPORTED:
+        raise (UnsupportedRoutineError if message.startswith("routine ") else UnsupportedOpError)(message)
+    if status == EINVAL:
+        raise ValueError(message)
+    if status == ECOMPILE:
+        raise CompileError(message)
+    if status == ENOMEM:
+        raise MemoryError(message)
+    raise CudaError(message)
+
+
+class Executable:
+    """src/backend.ts:213-220: the prepared Kernel or Routine plus backend data."""
+
+    def __init__(self, source, handle: int, backend: "CudaBackend"):
+        self.source = source
+        self.data = handle
+        self._backend = backend
+
+    @property
+    def describe(self) -> str:
+        return load_library().jaxcuda_exe_describe(self.data).decode()
+
+    @property
+    def cuda_source(self) -> str:
+        return load_library().jaxcuda_exe_source(self.data).decode()
+
+    def cost(self):
+        """(algorithmic bytes, algorithmic flops, kernel launches per dispatch)."""
+        b, f, n = ctypes.c_double(), ctypes.c_double(), ctypes.c_int()
+        load_library().jaxcuda_exe_cost(self.data, ctypes.byref(b), ctypes.byref(f), ctypes.byref(n))
+        return b.value, f.value, n.value
+
+
+class CudaBackend:
+    """`Backend` for device "cuda" (src/backend.ts:158-211)."""
+
+    type = "cuda"
+
+    def __init__(self, device: int = 0):
+        self._lib = load_library()
+        ctx = ctypes.c_void_p()
+        rc = self._lib.jaxcuda_create(device, ctypes.byref(ctx))
+        if rc != OK:
+            _raise(rc, self._lib.jaxcuda_last_error(None).decode())
+        self._ctx = ctx
+        self.device = device
+        self.max_args = self._lib.jaxcuda_max_args()
+
+    # -- helpers ---------------------------------------------------------------------
+    def _check(self, rc: int):
+        if rc != OK:
+            _raise(rc, self._lib.jaxcuda_last_error(self._ctx).decode())
+
+    def close(self):
+        if self._ctx:
+            self._lib.jaxcuda_destroy(self._ctx)
+            self._ctx = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- memory (src/backend.ts:166-190) ----------------------------------------------
+    def malloc(self, size: int, initial_data=None) -> int:
+        slot = ctypes.c_uint32()
+        if initial_data is None:
+            self._check(self._lib.jaxcuda_malloc(self._ctx, size, None, 0, ctypes.byref(slot)))
+        else:
+            buf = np.ascontiguousarray(np.frombuffer(initial_data, dtype=np.uint8) if not isinstance(initial_data, np.ndarray)
+                                       else initial_data)
+            self._check(self._lib.jaxcuda_malloc(self._ctx, size, buf.ctypes.data, buf.nbytes, ctypes.byref(slot)))
+        return slot.value
+
+    def inc_ref(self, slot: int) -> None:
+        self._check(self._lib.jaxcuda_incref(self._ctx, slot))
+
+    def dec_ref(self, slot: int) -> None:
+        self._check(self._lib.jaxcuda_decref(self._ctx, slot))
+
+    def read_sync(self, slot: int, start: int | None = None, count: int | None = None) -> np.ndarray:
+        """Bytes [start, start+count) of the slot as a uint8 array, after all pending work."""
+        size = ctypes.c_size_t()
+        self._check(self._lib.jaxcuda_slot_size(self._ctx, slot, ctypes.byref(size)))
+        start = 0 if start is None else start
+        count = size.value - start if count is None else count
+        out = np.empty(max(count, 0), dtype=np.uint8)
+        self._check(self._lib.jaxcuda_read(self._ctx, slot, start, count, out.ctypes.data))
+        return out
+
+    read = read_sync  # the async variant exists so that JS does not block its event loop
+
+    def read_into(self, slot: int, dst: np.ndarray, start: int = 0) -> None:
+        self._check(self._lib.jaxcuda_read(self._ctx, slot, start, dst.nbytes, dst.ctypes.data))
+
+    def write(self, slot: int, src: np.ndarray, start: int = 0) -> None:
+        self._check(self._lib.jaxcuda_write(self._ctx, slot, start, src.nbytes, src.ctypes.data))
+
+    def write_ptr(self, slot: int, ptr: int, nbytes: int, start: int = 0) -> None:
+        self._check(self._lib.jaxcuda_write(self._ctx, slot, start, nbytes, ptr))
+
+    def read_ptr(self, slot: int, ptr: int, nbytes: int, start: int = 0) -> None:
+        self._check(self._lib.jaxcuda_read(self._ctx, slot, start, nbytes, ptr))
+
+    # -- compile (src/backend.ts:192-202) ----------------------------------------------
+    def prepare_kernel_sync(self, kernel: Kernel) -> Executable:
+        image = kernel.serialize()
+        exe = ctypes.c_void_p()
+        self._check(self._lib.jaxcuda_prepare_kernel(self._ctx, image, len(image), 0, ctypes.byref(exe)))
+        return Executable(kernel, exe.value, self)
+
+    prepare_kernel = prepare_kernel_sync
+
+    def prepare_routine_sync(self, routine: Routine) -> Executable:
+        t = routine.type
+        flat = lambda shapes: [d for s in shapes for d in s]
+        ins, outs = flat(t.input_shapes), flat(t.output_shapes)
+        keep = [(ctypes.c_int32 * max(1, len(t.input_dtypes)))(*[int(d) for d in t.input_dtypes]),
+                (ctypes.c_int32 * max(1, len(t.input_shapes)))(*[len(s) for s in t.input_shapes]),
+                (ctypes.c_int64 * max(1, len(ins)))(*ins),
+                (ctypes.c_int32 * max(1, len(t.output_dtypes)))(*[int(d) for d in t.output_dtypes]),
+                (ctypes.c_int32 * max(1, len(t.output_shapes)))(*[len(s) for s in t.output_shapes]),
+                (ctypes.c_int64 * max(1, len(outs)))(*outs)]
+        rt = _RoutineType(len(t.input_shapes), len(t.output_shapes), *keep)
+        exe = ctypes.c_void_p()
+        self._check(self._lib.jaxcuda_prepare_routine(self._ctx, routine.name.encode(), ctypes.byref(rt), b"{}",
+                                                      ctypes.byref(exe)))
+        return Executable(routine, exe.value, self)
+
+    prepare_routine = prepare_routine_sync
+
+    # -- run (src/backend.ts:204-211) --------------------------------------------------
+    def dispatch(self, exe: Executable, inputs: Sequence[int], outputs: Sequence[int]) -> None:
+        ins = (ctypes.c_uint32 * max(1, len(inputs)))(*inputs)
+        outs = (ctypes.c_uint32 * max(1, len(outputs)))(*outputs)
+        self._check(self._lib.jaxcuda_dispatch(self._ctx, exe.data, ins, len(inputs), outs, len(outputs)))
+
+    # -- extras outside the Backend interface -------------------------------------------
+    def sync(self) -> None:
+        self._check(self._lib.jaxcuda_sync(self._ctx))
+
+    def event_record(self, index: int) -> None:
+        self._check(self._lib.jaxcuda_event_record(self._ctx, index))
+
+    def event_elapsed_ms(self, a: int, b: int) -> float:
+        ms = ctypes.c_float()
+        self._check(self._lib.jaxcuda_event_elapsed_ms(self._ctx, a, b, ctypes.byref(ms)))
+        return ms.value
+
+    def launch_count(self) -> int:
+        return int(self._lib.jaxcuda_launch_count(self._ctx))
+
+    def host_alloc(self, nbytes: int) -> np.ndarray:
+        """Pinned host memory as a uint8 array (freed with host_free)."""
+        p = ctypes.c_void_p()
+        self._check(self._lib.jaxcuda_host_alloc(self._ctx, nbytes, ctypes.byref(p)))
+        arr = np.ctypeslib.as_array((ctypes.c_uint8 * max(1, nbytes)).from_address(p.value))[:nbytes]
+        arr.flags.writeable = True
+        self._pinned = getattr(self, "_pinned", {})
+        self._pinned[arr.ctypes.data] = p.value
+        return arr
+
+    def host_free(self, arr: np.ndarray) -> None:
+        p = self._pinned.pop(arr.ctypes.data, None)
+        if p:
+            self._check(self._lib.jaxcuda_host_free(self._ctx, p))
+
+    def slot_ptr(self, slot: int) -> int:
+        p = ctypes.c_uint64()
+        self._check(self._lib.jaxcuda_slot_ptr(self._ctx, slot, ctypes.byref(p)))
+        return p.value
+
+    def stream(self) -> int:
+        return int(self._lib.jaxcuda_stream(self._ctx))
+
+    def comm_init(self, rank: int, nranks: int, unique_id: bytes) -> None:
+        buf = ctypes.create_string_buffer(unique_id, 128)
+        self._check(self._lib.jaxcuda_comm_init(self._ctx, rank, nranks, buf))
+
+    @staticmethod
+    def comm_unique_id() -> bytes:
+        buf = ctypes.create_string_buffer(128)
+        if load_library().jaxcuda_comm_unique_id(buf) != OK:
+            raise CudaError("ncclGetUniqueId failed (is libnccl.so.2 loadable?)")
+        return buf.raw
+
+    def allreduce_sum_f32(self, slots: Sequence[int]) -> None:
+        arr = (ctypes.c_uint32 * max(1, len(slots)))(*slots)
+        self._check(self._lib.jaxcuda_allreduce_sum_f32(self._ctx, arr, len(slots)))
+
+    # -- conveniences for tests and programs -------------------------------------------
+    def put(self, array: np.ndarray) -> int:
+        a = np.ascontiguousarray(array)
+        return self.malloc(a.nbytes, a.view(np.uint8).reshape(-1))
+
+    def get(self, slot: int, dtype: DType | str, shape=None) -> np.ndarray:
+        from .alu import np_dtype
+        name = np_dtype(dtype) if isinstance(dtype, DType) else dtype
+        out = self.read_sync(slot).view(name)
+        return out.reshape(shape) if shape is not None else out

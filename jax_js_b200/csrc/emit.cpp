@@ -1,0 +1,849 @@
+#include "emit.hpp"
+
+#include <algorithm>
+#include <cstring>
+#include <map>
+#include <sstream>
+#include <stdexcept>
+
+#include "prelude.hpp"
+
+namespace jaxcuda {
+
+namespace {
+
+// ---- small helpers ------------------------------------------------------------------
+
+std::string S(int64_t v) { return std::to_string(v); }
+
+const char* ctype(uint32_t dt) {  // type a value of this dtype has in registers
+  switch (dt) {
+    case JAXCUDA_F32: case JAXCUDA_F16: return "float";  // f16 values are carried as f32, rounded on Cast/store
+    case JAXCUDA_F64: return "double";
+    case JAXCUDA_U32: return "u32";
+    default: return "int";
+  }
+}
+const char* ptype(uint32_t dt) {  // element type in memory
+  switch (dt) {
+    case JAXCUDA_F32: return "float";
+    case JAXCUDA_F16: return "jx_half";
+    case JAXCUDA_F64: return "double";
+    case JAXCUDA_U32: return "u32";
+    default: return "int";
+  }
+}
+
+[[noreturn]] void unsupported(uint32_t op, uint32_t dtype, const std::string& extra = "") {
+  // wording of UnsupportedOpError, src/backend.ts:228-234
+  throw std::runtime_error(std::string(op_name(op)) + "<" + dtype_name(dtype) + "> not supported in cuda backend" +
+                           (extra.empty() ? "" : " with arg " + extra));
+}
+
+std::string hex32(uint32_t v) { char b[16]; snprintf(b, sizeof b, "0x%08xu", v); return b; }
+
+std::string literal(const Node& nd) {
+  if (nd.dtype == JAXCUDA_F32 || nd.dtype == JAXCUDA_F16) {
+    double d; memcpy(&d, &nd.arg0, 8);
+    float f = (float)d; uint32_t bits; memcpy(&bits, &f, 4);
+    return "__uint_as_float(" + hex32(bits) + ")";
+  }
+  if (nd.dtype == JAXCUDA_F64) {
+    char b[48]; snprintf(b, sizeof b, "__longlong_as_double(0x%016llxLL)", (unsigned long long)nd.arg0);
+    return b;
+  }
+  if (nd.dtype == JAXCUDA_U32) return hex32((uint32_t)nd.arg0);
+  if (nd.dtype == JAXCUDA_BOOL) return (nd.arg0 & 0xffffffffu) ? "1" : "0";
+  return "((int)" + hex32((uint32_t)nd.arg0) + ")";
+}
+
+struct Env {
+  std::string prefix = "t";
+  std::string gidx = "gidx", ridx = "ridx", acc = "acc";
+  const std::map<size_t, std::string>* load_override = nullptr;  // node -> expression of the loaded value
+};
+
+bool in_range(const std::optional<Affine>& a, uint32_t len) { return a && a->lo >= 0 && a->hi < (int64_t)len; }
+
+std::string load_value(const Node& nd, const std::string& ix, bool proven) {
+  const uint32_t len = nd.arg1;
+  if (len == 0) return nd.dtype == JAXCUDA_F64 ? "0.0" : (nd.dtype == JAXCUDA_F32 || nd.dtype == JAXCUDA_F16) ? "0.0f" : "0";
+  // An index outside the buffer reads element 0, as the Wasm emitter does (translation.ts:221-228).
+  std::string at = proven ? ix : "((u32)(" + ix + ") < " + S(len) + "u ? (" + ix + ") : 0)";
+  std::string p = std::string("((const ") + ptype(nd.dtype) + "*)p" + S((int64_t)nd.arg0) + ")[" + at + "]";
+  return nd.dtype == JAXCUDA_F16 ? "jx_h2f(" + p + ")" : p;
+}
+
+std::string binary_expr(uint32_t op, uint32_t dt, const std::string& a, const std::string& b, uint64_t arg0,
+                        const Node* bnode) {
+  const bool f = dt == JAXCUDA_F32 || dt == JAXCUDA_F16, d = dt == JAXCUDA_F64, bo = dt == JAXCUDA_BOOL,
+             i = dt == JAXCUDA_I32, u = dt == JAXCUDA_U32;
+  auto wrap = [&](const char* sym) {  // integer arithmetic wraps modulo 2^32 (translation.ts:38-45)
+    if (i) return "(int)((u32)" + a + " " + sym + " (u32)" + b + ")";
+    return "(" + a + " " + sym + " " + b + ")";
+  };
+  switch (op) {
+    case JAXCUDA_OP_ADD: return bo ? "(" + a + " | " + b + ")" : wrap("+");
+    case JAXCUDA_OP_SUB: if (bo) unsupported(op, dt); return wrap("-");
+    case JAXCUDA_OP_MUL: return bo ? "(" + a + " & " + b + ")" : wrap("*");
+    case JAXCUDA_OP_IDIV: {
+      if (f) return "jx_fidiv(" + a + ", " + b + ")";
+      if (d) return "jx_didiv(" + a + ", " + b + ")";
+      const bool safe_const = bnode && bnode->op == JAXCUDA_OP_CONST && (uint32_t)bnode->arg0 != 0 &&
+                              (uint32_t)bnode->arg0 != 0xffffffffu;
+      if (i) return safe_const ? "(" + a + " / " + b + ")" : "jx_idiv(" + a + ", " + b + ")";
+      if (u) return safe_const ? "(" + a + " / " + b + ")" : "jx_udiv(" + a + ", " + b + ")";
+      unsupported(op, dt);
+    }
+    case JAXCUDA_OP_MOD: {
+      if (f) return "jx_fmod(" + a + ", " + b + ")";
+      if (d) return "jx_dmod(" + a + ", " + b + ")";
+      const bool safe_const = bnode && bnode->op == JAXCUDA_OP_CONST && (uint32_t)bnode->arg0 != 0 &&
+                              (uint32_t)bnode->arg0 != 0xffffffffu;
+      if (i) return safe_const ? "(" + a + " % " + b + ")" : "jx_imod(" + a + ", " + b + ")";
+      if (u) return safe_const ? "(" + a + " % " + b + ")" : "jx_umod(" + a + ", " + b + ")";
+      unsupported(op, dt);
+    }
+    case JAXCUDA_OP_MIN:
+      if (bo) return "(" + a + " & " + b + ")";
+      return std::string(f ? "jx_fmin(" : d ? "jx_dmin(" : i ? "jx_imin(" : "jx_umin(") + a + ", " + b + ")";
+    case JAXCUDA_OP_MAX:
+      if (bo) return "(" + a + " | " + b + ")";
+      return std::string(f ? "jx_fmax(" : d ? "jx_dmax(" : i ? "jx_imax(" : "jx_umax(") + a + ", " + b + ")";
+    case JAXCUDA_OP_BITCOMBINE: {
+      if (f || d) unsupported(op, dt);
+      const char* sym = arg0 == 0 ? "&" : arg0 == 1 ? "|" : "^";
+      return "(" + a + " " + sym + " " + b + ")";
+    }
+    case JAXCUDA_OP_BITSHIFT: {  // count masked to 5 bits; shr is logical for every dtype (translation.ts:101-103)
+      if (f || d || bo) unsupported(op, dt);
+      const char* sym = arg0 == 0 ? "<<" : ">>";
+      return std::string("(") + ctype(dt) + ")((u32)" + a + " " + sym + " ((u32)" + b + " & 31u))";
+    }
+    default: unsupported(op, dt);
+  }
+}
+
+std::string unary_math(uint32_t op, uint32_t dt, const std::string& a) {
+  const char* fn = nullptr;
+  switch (op) {
+    case JAXCUDA_OP_SIN: fn = "jx_sin"; break;
+    case JAXCUDA_OP_COS: fn = "jx_cos"; break;
+    case JAXCUDA_OP_ASIN: fn = "jx_asin"; break;
+    case JAXCUDA_OP_ATAN: fn = "jx_atan"; break;
+    case JAXCUDA_OP_EXP: fn = "jx_exp"; break;
+    case JAXCUDA_OP_LOG: fn = "jx_log"; break;
+    case JAXCUDA_OP_ERF: fn = "jx_erf"; break;
+    case JAXCUDA_OP_ERFC: fn = "jx_erfc"; break;
+    default: break;
+  }
+  if (!dtype_is_float(dt)) unsupported(op, dt);
+  if (fn) {  // f32 routines; f64 is demoted and promoted as in translation.ts:115-122
+    if (dt == JAXCUDA_F64) return std::string("(double)") + fn + "((float)" + a + ")";
+    return std::string(fn) + "(" + a + ")";
+  }
+  const bool d = dt == JAXCUDA_F64;
+  switch (op) {
+    case JAXCUDA_OP_SQRT: return (d ? "sqrt(" : "sqrtf(") + a + ")";
+    case JAXCUDA_OP_FLOOR: return (d ? "floor(" : "floorf(") + a + ")";
+    case JAXCUDA_OP_CEIL: return (d ? "ceil(" : "ceilf(") + a + ")";
+    case JAXCUDA_OP_RECIPROCAL: return (d ? "(1.0 / " : "(1.0f / ") + a + ")";  // true division (translation.ts:132-134)
+    default: unsupported(op, dt);
+  }
+}
+
+std::string cast_expr(uint32_t to, uint32_t from, const std::string& a) {  // translation.ts:139-173
+  const bool from_f = from == JAXCUDA_F32 || from == JAXCUDA_F16, from_d = from == JAXCUDA_F64;
+  switch (to) {
+    case JAXCUDA_BOOL:
+      return from == JAXCUDA_BOOL ? a : "(int)(" + a + (from_f ? " != 0.0f)" : from_d ? " != 0.0)" : " != 0)");
+    case JAXCUDA_I32:
+      if (from_f) return "__float2int_rz(" + a + ")";      // trunc_sat: saturates, NaN -> 0
+      if (from_d) return "__double2int_rz(" + a + ")";
+      return "(int)" + a;
+    case JAXCUDA_U32:
+      if (from_f) return "__float2uint_rz(" + a + ")";
+      if (from_d) return "__double2uint_rz(" + a + ")";
+      return "(u32)" + a;
+    case JAXCUDA_F32:
+      if (from == JAXCUDA_F32 || from == JAXCUDA_F16) return a;
+      return "(float)" + a;  // signed convert for int32 and Bool, unsigned for uint32
+    case JAXCUDA_F16:
+      if (from == JAXCUDA_F16) return a;
+      if (from_f) return "jx_round_h(" + a + ")";
+      return "jx_round_h((float)" + a + ")";
+    case JAXCUDA_F64:
+      return from_d ? a : "(double)" + a;
+    default: unsupported(JAXCUDA_OP_CAST, to);
+  }
+}
+
+std::string bitcast_expr(uint32_t to, uint32_t from, const std::string& a) {  // translation.ts:175-189
+  auto is_i = [](uint32_t t) { return t == JAXCUDA_I32 || t == JAXCUDA_U32; };
+  if (to == from) return a;
+  if (is_i(to) && from == JAXCUDA_F32) return to == JAXCUDA_I32 ? "__float_as_int(" + a + ")" : "__float_as_uint(" + a + ")";
+  if (is_i(to) && is_i(from)) return std::string("(") + ctype(to) + ")" + a;
+  if (to == JAXCUDA_F32 && from == JAXCUDA_I32) return "__int_as_float(" + a + ")";
+  if (to == JAXCUDA_F32 && from == JAXCUDA_U32) return "__uint_as_float(" + a + ")";
+  unsupported(JAXCUDA_OP_BITCAST, to, dtype_name(from));
+}
+
+// Emit `const T name = expr;` for every wanted node that has no name yet.
+void emit_nodes(std::ostream& os, const std::vector<Node>& nodes, const Analysis& an,
+                std::vector<std::string>& names, const std::vector<char>& want, const Env& env,
+                const std::string& indent) {
+  for (size_t i = 0; i < nodes.size(); i++) {
+    if (!want[i] || !names[i].empty()) continue;
+    const Node& nd = nodes[i];
+    auto a = [&](int s) -> const std::string& { return names[nd.src[s]]; };
+    std::string expr;
+    switch (nd.op) {
+      case JAXCUDA_OP_CONST: names[i] = literal(nd); continue;
+      case JAXCUDA_OP_SPECIAL: names[i] = nd.arg0 == 0 ? env.gidx : env.ridx; continue;
+      case JAXCUDA_OP_VARIABLE: names[i] = env.acc; continue;
+      case JAXCUDA_OP_GLOBALINDEX: {
+        if (env.load_override) {
+          auto it = env.load_override->find(i);
+          if (it != env.load_override->end()) { expr = it->second; break; }
+        }
+        expr = load_value(nd, a(0), in_range(an.affine[nd.src[0]], nd.arg1));
+        break;
+      }
+      case JAXCUDA_OP_CAST: expr = cast_expr(nd.dtype, nodes[nd.src[0]].dtype, a(0)); break;
+      case JAXCUDA_OP_BITCAST: expr = bitcast_expr(nd.dtype, nodes[nd.src[0]].dtype, a(0)); break;
+      case JAXCUDA_OP_BITINVERT:
+        if (dtype_is_float(nd.dtype)) unsupported(nd.op, nd.dtype);
+        expr = nd.dtype == JAXCUDA_BOOL ? "(" + a(0) + " ^ 1)" : "(~" + a(0) + ")";
+        break;
+      case JAXCUDA_OP_CMPLT: expr = "(int)(" + a(0) + " < " + a(1) + ")"; break;
+      case JAXCUDA_OP_CMPNE: expr = "(int)(" + a(0) + " != " + a(1) + ")"; break;
+      case JAXCUDA_OP_WHERE: expr = "(" + a(0) + " ? " + a(1) + " : " + a(2) + ")"; break;
+      case JAXCUDA_OP_THREEFRY2X32:
+        if (nd.arg0 > 2) unsupported(nd.op, nd.dtype, S((int64_t)nd.arg0));
+        expr = "jx_threefry(" + a(0) + ", " + a(1) + ", " + a(2) + ", " + a(3) + ", " + S((int64_t)nd.arg0) + ")";
+        break;
+      default:
+        if (nd.nsrc == 2) expr = binary_expr(nd.op, nd.dtype, a(0), a(1), nd.arg0, &nodes[nd.src[1]]);
+        else expr = unary_math(nd.op, nd.dtype, a(0));
+    }
+    names[i] = env.prefix + S((int64_t)i);
+    os << indent << "const " << ctype(nd.dtype) << " " << names[i] << " = " << expr << ";\n";
+  }
+}
+
+std::vector<char> closure(const std::vector<Node>& nodes, size_t root) {
+  std::vector<char> m(nodes.size(), 0);
+  m[root] = 1;
+  for (size_t i = root + 1; i-- > 0;)
+    if (m[i]) for (uint32_t s = 0; s < nodes[i].nsrc; s++) m[nodes[i].src[s]] = 1;
+  return m;
+}
+
+std::string to_storage(uint32_t dt, const std::string& v) { return dt == JAXCUDA_F16 ? "jx_f2h(" + v + ")" : v; }
+std::string from_storage(uint32_t dt, const std::string& v) { return dt == JAXCUDA_F16 ? "jx_h2f(" + v + ")" : v; }
+
+std::string identity_literal(uint32_t op, uint32_t dt) {  // src/alu.ts:1584-1604
+  if (dt == JAXCUDA_BOOL) return (op == JAXCUDA_OP_ADD || op == JAXCUDA_OP_MAX) ? "0" : "1";
+  if (dt == JAXCUDA_I32) return op == JAXCUDA_OP_ADD ? "0" : op == JAXCUDA_OP_MUL ? "1" : op == JAXCUDA_OP_MIN ? "2147483647" : "(-2147483647 - 1)";
+  if (dt == JAXCUDA_U32) return op == JAXCUDA_OP_ADD ? "0u" : op == JAXCUDA_OP_MUL ? "1u" : op == JAXCUDA_OP_MIN ? "0xffffffffu" : "0u";
+  if (dt == JAXCUDA_F64) return op == JAXCUDA_OP_ADD ? "0.0" : op == JAXCUDA_OP_MUL ? "1.0" : op == JAXCUDA_OP_MIN ? "(double)JX_INF" : "(double)(-JX_INF)";
+  return op == JAXCUDA_OP_ADD ? "0.0f" : op == JAXCUDA_OP_MUL ? "1.0f" : op == JAXCUDA_OP_MIN ? "JX_INF" : "(-JX_INF)";
+}
+
+// How a load behaves over an aligned run of V consecutive values of `var`.
+enum LoadKind { LK_GATHER, LK_BROADCAST, LK_VECTOR };
+
+LoadKind classify_load(const Node& nd, const std::optional<Affine>& ix, int var, int V) {
+  if (!ix || !in_range(ix, nd.arg1)) return LK_GATHER;
+  int64_t cv = 0;
+  for (const Term& t : ix->terms) {
+    if (t.var != var) continue;
+    if (t.div == 1) {
+      if (t.mod && t.mod % V) return LK_GATHER;
+      cv = t.coef;
+    } else if (t.div % V) {
+      return LK_GATHER;
+    }
+  }
+  if (cv == 0) return LK_BROADCAST;
+  if (cv != 1 || ix->c0 % V) return LK_GATHER;
+  for (const Term& t : ix->terms)
+    if (!(t.var == var && t.div == 1) && t.coef % V) return LK_GATHER;
+  return LK_VECTOR;
+}
+
+struct Builder {
+  const KernelIR& k;
+  const Options& opt;
+  Analysis an_exp, an_epi;
+  uint32_t out_dt;
+
+  Builder(const KernelIR& k_, const Options& o) : k(k_), opt(o) {
+    an_exp = analyze(k.exp, k.size, k.has_red ? k.red_size : 0);
+    if (k.has_red) an_epi = analyze(k.epi, k.size, 0);
+    out_dt = k.out_dtype();
+  }
+
+  std::string params() const {
+    std::ostringstream os;
+    for (uint32_t i = 0; i < k.nargs; i++) os << "const void* __restrict__ p" << i << ", ";
+    os << ptype(out_dt) << "* __restrict__ out, void* __restrict__ scratch";
+    return os.str();
+  }
+
+  std::string red(const std::string& a, const std::string& b) const {
+    return binary_expr(k.red_op, k.red_dtype, a, b, 0, nullptr);
+  }
+
+  void account(Plan& p) const {
+    std::map<uint32_t, double> bytes;
+    auto scan = [&](const std::vector<Node>& nodes) {
+      for (const Node& nd : nodes)
+        if (nd.op == JAXCUDA_OP_GLOBALINDEX)
+          bytes[(uint32_t)nd.arg0] = std::max(bytes[(uint32_t)nd.arg0], (double)nd.arg1 * dtype_bytes(nd.dtype));
+    };
+    scan(k.exp);
+    scan(k.epi);
+    p.algo_bytes = (double)k.size * dtype_bytes(out_dt);
+    for (auto& kv : bytes) p.algo_bytes += kv.second;
+    p.algo_flops = (double)k.size * (k.has_red ? 2.0 * k.red_size : 1.0);
+  }
+
+  // Loads of `nodes` that can be fetched once per run of V values of `var` starting at an
+  // aligned position: emits the index closure at the run start (prefix b) and the fetch,
+  // and records the per-lane expression (pack element or broadcast scalar) as an override.
+  // `slot` is an optional array suffix for ILP copies, e.g. "[j]".
+  void preload(std::ostream& decl, std::ostream& fetch, const std::vector<Node>& nodes, const Analysis& an,
+               const std::vector<char>& live, int var, int V, const Env& base_env, const std::string& run_start,
+               const std::string& slot_decl, const std::string& slot_use, const std::string& lane,
+               std::map<size_t, std::string>& override_, std::vector<std::string>& bnames,
+               const std::string& indent) const {
+    Env env = base_env;
+    env.prefix = "b";
+    if (var == 0) env.gidx = run_start; else env.ridx = run_start;
+    for (size_t i = 0; i < nodes.size(); i++) {
+      const Node& nd = nodes[i];
+      if (!live[i] || nd.op != JAXCUDA_OP_GLOBALINDEX || nd.arg1 == 0) continue;
+      LoadKind lk = classify_load(nd, an.affine[nd.src[0]], var, V);
+      if (lk == LK_GATHER) continue;
+      if (lk == LK_BROADCAST && !(var == 0 ? an.dep_g[i] : an.dep_r[i])) continue;  // invariant anyway
+      std::vector<char> need = closure(nodes, nd.src[0]);
+      emit_nodes(fetch, nodes, an, bnames, need, env, indent);
+      const std::string ix = bnames[nd.src[0]];
+      const std::string ptr = std::string("((const ") + ptype(nd.dtype) + "*)p" + S((int64_t)nd.arg0) + ")";
+      if (lk == LK_VECTOR) {
+        decl << indent << "jx_pack<" << ptype(nd.dtype) << ", " << V << "> pk" << i << slot_decl << ";\n";
+        fetch << indent << "jx_load(pk" << i << slot_use << ", " << ptr << " + " << ix << ");\n";
+        override_[i] = from_storage(nd.dtype, "pk" + S((int64_t)i) + slot_use + ".e[" + lane + "]");
+      } else {
+        decl << indent << ptype(nd.dtype) << " bc" << i << slot_decl << ";\n";
+        fetch << indent << "bc" << i << slot_use << " = " << ptr << "[" << ix << "];\n";
+        override_[i] = from_storage(nd.dtype, "bc" + S((int64_t)i) + slot_use);
+      }
+    }
+  }
+
+  // ---- elementwise -----------------------------------------------------------------
+  Plan elementwise() const {
+    Plan p;
+    p.skeleton = SK_ELEMENTWISE;
+    account(p);
+    const int T = 256;
+    int V = std::max(1, 16 / dtype_bytes(out_dt));
+    if (k.size < (uint64_t)V * 64) V = 1;
+    const int64_t nvec = (int64_t)(k.size / V);
+    const int64_t tail = (int64_t)(k.size - nvec * V);
+    int ILP = V > 1 ? std::max(1, opt.ew_ilp) : 1;
+    while (ILP > 1 && nvec < (int64_t)T * ILP * opt.sm_count) ILP >>= 1;
+    const bool exact = nvec % ((int64_t)T * ILP) == 0;
+    std::vector<char> all(k.exp.size(), 1);
+    const size_t root = k.exp.size() - 1;
+
+    std::ostringstream os;
+    os << kPrelude;
+    os << "extern \"C\" __global__ void __launch_bounds__(" << T << ") jx_kernel(" << params() << ") {\n";
+    if (nvec > 0) {
+      std::map<size_t, std::string> ov;
+      std::ostringstream decl, fetch;
+      std::vector<std::string> bnames(k.exp.size());
+      Env env;
+      if (V > 1)
+        preload(decl, fetch, k.exp, an_exp, all, 0, V, env, "g0", "[" + S(ILP) + "]", "[j]", "u", ov, bnames, "        ");
+      os << "  for (int base = blockIdx.x * " << T * ILP << "; base < " << nvec << "; base += gridDim.x * " << T * ILP << ") {\n";
+      os << decl.str();
+      os << "    #pragma unroll\n    for (int j = 0; j < " << ILP << "; j++) {\n";
+      os << "      const int vi = base + j * " << T << " + threadIdx.x;\n";
+      os << (exact ? "      {\n" : "      if (vi < " + S(nvec) + ") {\n");
+      os << "        const int g0 = vi * " << V << ";\n";
+      os << fetch.str();
+      os << "      }\n    }\n";
+      os << "    #pragma unroll\n    for (int j = 0; j < " << ILP << "; j++) {\n";
+      os << "      const int vi = base + j * " << T << " + threadIdx.x;\n";
+      os << (exact ? "      {\n" : "      if (vi < " + S(nvec) + ") {\n");
+      os << "        const int g0 = vi * " << V << ";\n";
+      os << "        jx_pack<" << ptype(out_dt) << ", " << V << "> res;\n";
+      os << "        #pragma unroll\n        for (int u = 0; u < " << V << "; u++) {\n";
+      os << "          const int gidx = g0 + u;\n";
+      std::vector<std::string> names(k.exp.size());
+      env.load_override = &ov;
+      emit_nodes(os, k.exp, an_exp, names, all, env, "          ");
+      os << "          res.e[u] = " << to_storage(out_dt, names[root]) << ";\n";
+      os << "        }\n";
+      os << "        jx_store(out + g0, res);\n";
+      os << "      }\n    }\n  }\n";
+    }
+    if (tail > 0) {
+      os << "  if (blockIdx.x == 0) {\n";
+      os << "    for (int gidx = " << nvec * V << " + threadIdx.x; gidx < " << k.size << "; gidx += " << T << ") {\n";
+      std::vector<std::string> names(k.exp.size());
+      Env env;
+      emit_nodes(os, k.exp, an_exp, names, all, env, "      ");
+      os << "      out[gidx] = " << to_storage(out_dt, names[root]) << ";\n";
+      os << "    }\n  }\n";
+    }
+    os << "}\n";
+    p.source = os.str();
+    Stage st;
+    st.entry = "jx_kernel";
+    int64_t blocks = nvec > 0 ? (nvec + (int64_t)T * ILP - 1) / ((int64_t)T * ILP) : 1;
+    blocks = std::min<int64_t>(blocks, (int64_t)opt.sm_count * opt.ew_blocks_per_sm);
+    st.grid[0] = (unsigned)std::max<int64_t>(1, blocks);
+    st.block[0] = T;
+    p.stages.push_back(st);
+    p.describe = "elementwise V=" + S(V) + " ILP=" + S(ILP) + " grid=" + S(st.grid[0]) + "x" + S(T);
+    return p;
+  }
+
+  // ---- reductions --------------------------------------------------------------------
+  void emit_epilogue_store(std::ostream& os, const std::string& indent, const std::string& dst) const {
+    std::vector<std::string> names(k.epi.size());
+    std::vector<char> all(k.epi.size(), 1);
+    Env env;
+    env.prefix = "e";
+    emit_nodes(os, k.epi, an_epi, names, all, env, indent);
+    os << indent << dst << " = " << to_storage(out_dt, names.back()) << ";\n";
+  }
+
+  void emit_finish_kernel(std::ostream& os, int splits) const {
+    const char* AT = ctype(k.red_dtype);
+    os << "extern \"C\" __global__ void __launch_bounds__(256) jx_finish(" << params() << ") {\n";
+    os << "  const int gidx = blockIdx.x * 256 + threadIdx.x;\n  if (gidx >= " << k.size << ") return;\n";
+    os << "  const " << AT << "* part = (const " << AT << "*)scratch;\n";
+    os << "  " << AT << " acc = " << identity_literal(k.red_op, k.red_dtype) << ";\n";
+    os << "  for (int s = 0; s < " << splits << "; s++) { const " << AT << " v = part[(size_t)s * " << k.size
+       << " + gidx]; acc = " << red("acc", "v") << "; }\n";
+    emit_epilogue_store(os, "  ", "out[gidx]");
+    os << "}\n";
+  }
+
+  bool has_load(int var_contig) const {  // some in-range load whose index moves by 1 with var (div 1)
+    for (size_t i = 0; i < k.exp.size(); i++) {
+      const Node& nd = k.exp[i];
+      if (nd.op != JAXCUDA_OP_GLOBALINDEX || !an_exp.dep_r[i]) continue;  // loads hoisted out of the loop do not count
+      const auto& ix = an_exp.affine[nd.src[0]];
+      if (ix && ix->coef_of(var_contig, 1) == 1) return true;
+    }
+    return false;
+  }
+
+  int min_load_bytes(int var, int Vmax) const {  // narrowest element among loads that vectorise over var
+    int b = 0;
+    for (size_t i = 0; i < k.exp.size(); i++) {
+      const Node& nd = k.exp[i];
+      if (nd.op != JAXCUDA_OP_GLOBALINDEX) continue;
+      if (classify_load(nd, an_exp.affine[nd.src[0]], var, Vmax) == LK_VECTOR)
+        b = b ? std::min(b, dtype_bytes(nd.dtype)) : dtype_bytes(nd.dtype);
+    }
+    return b;
+  }
+
+  Plan reduce_row() const {
+    Plan p;
+    p.skeleton = SK_REDUCE_ROW;
+    account(p);
+    const int64_t K = k.red_size;
+    const int T = 256;
+    int TPR = K >= 1024 ? 256 : K >= 128 ? 32 : 8;
+    // vector width over ridx
+    int V = 1;
+    for (int cand : {8, 4, 2}) {
+      if (K % cand) continue;
+      int eb = min_load_bytes(1, cand);
+      if (eb && eb * cand <= 16) { V = cand; break; }
+    }
+    const int RPC = T / TPR;
+    int64_t row_blocks = ((int64_t)k.size + RPC - 1) / RPC;
+    // few outputs and a long axis: split ridx across CTAs, finish in a second pass
+    int splits = 1;
+    if (row_blocks < opt.sm_count && K >= 16384) {
+      int64_t want = (2 * opt.sm_count + row_blocks - 1) / row_blocks;
+      int64_t max_splits = K / ((int64_t)TPR * V * 4);
+      splits = (int)std::max<int64_t>(1, std::min(want, max_splits));
+    }
+    int64_t rchunk = (K + splits - 1) / splits;
+    rchunk = (rchunk + V - 1) / V * V;
+    splits = (int)((K + rchunk - 1) / rchunk);
+    const char* AT = ctype(k.red_dtype);
+    const size_t root = k.exp.size() - 1;
+
+    std::vector<char> hoist(k.exp.size(), 0), inner(k.exp.size(), 0);
+    for (size_t i = 0; i < k.exp.size(); i++) (an_exp.dep_r[i] ? inner : hoist)[i] = 1;
+
+    std::ostringstream os;
+    os << kPrelude;
+    os << "extern \"C\" __global__ void __launch_bounds__(" << T << ") jx_kernel(" << params() << ") {\n";
+    os << "  const int lane = threadIdx.x % " << TPR << ", rowc = threadIdx.x / " << TPR << ";\n";
+    os << "  const long long gl = (long long)blockIdx.x * " << RPC << " + rowc;\n";
+    os << "  const bool active = gl < " << k.size << "LL;\n";
+    os << "  const int gidx = active ? (int)gl : 0;\n";
+    if (splits > 1) {
+      os << "  const int rbeg = blockIdx.y * " << rchunk << ";\n";
+      os << "  const int rend = min(" << K << ", rbeg + " << rchunk << ");\n";
+    } else {
+      os << "  const int rbeg = 0, rend = " << K << ";\n";
+    }
+    std::vector<std::string> names(k.exp.size());
+    Env env;
+    emit_nodes(os, k.exp, an_exp, names, hoist, env, "  ");
+    os << "  " << AT << " acc = " << identity_literal(k.red_op, k.red_dtype) << ";\n";
+    std::map<size_t, std::string> ov;
+    std::ostringstream decl, fetch;
+    std::vector<std::string> bnames = names;  // hoisted values stay visible to the index closures
+    if (V > 1) preload(decl, fetch, k.exp, an_exp, inner, 1, V, env, "r0", "", "", "u", ov, bnames, "    ");
+    os << "  #pragma unroll 4\n";
+    os << "  for (int r0 = rbeg + lane * " << V << "; r0 < rend; r0 += " << TPR * V << ") {\n";
+    os << decl.str() << fetch.str();
+    os << "    #pragma unroll\n    for (int u = 0; u < " << V << "; u++) {\n";
+    os << "      const int ridx = r0 + u;\n";
+    env.load_override = &ov;
+    std::vector<std::string> inames = names;
+    emit_nodes(os, k.exp, an_exp, inames, inner, env, "      ");
+    os << "      acc = " << red("acc", inames[root]) << ";\n";
+    os << "    }\n  }\n";
+    const int W = std::min(TPR, 32);
+    os << "  #pragma unroll\n  for (int o = " << W / 2 << "; o > 0; o >>= 1) { const " << AT
+       << " v = jx_shfl_down(acc, o, " << W << "); acc = " << red("acc", "v") << "; }\n";
+    if (TPR > 32) {
+      os << "  __shared__ " << AT << " sm[" << T / 32 << "];\n";
+      os << "  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = acc;\n  __syncthreads();\n";
+      os << "  if (threadIdx.x < 32) {\n";
+      os << "    acc = threadIdx.x < " << T / 32 << " ? sm[threadIdx.x] : " << identity_literal(k.red_op, k.red_dtype) << ";\n";
+      os << "    #pragma unroll\n    for (int o = " << T / 64 << "; o > 0; o >>= 1) { const " << AT
+         << " v = jx_shfl_down(acc, o, 32); acc = " << red("acc", "v") << "; }\n  }\n";
+    }
+    os << "  if (lane == 0 && active) {\n";
+    if (splits > 1) {
+      os << "    ((" << AT << "*)scratch)[(size_t)blockIdx.y * " << k.size << " + gidx] = acc;\n";
+    } else {
+      emit_epilogue_store(os, "    ", "out[gidx]");
+    }
+    os << "  }\n}\n";
+    if (splits > 1) emit_finish_kernel(os, splits);
+    p.source = os.str();
+    Stage st;
+    st.entry = "jx_kernel";
+    st.grid[0] = (unsigned)row_blocks;
+    st.grid[1] = (unsigned)splits;
+    st.block[0] = T;
+    p.stages.push_back(st);
+    if (splits > 1) {
+      Stage fin;
+      fin.entry = "jx_finish";
+      fin.grid[0] = (unsigned)((k.size + 255) / 256);
+      fin.block[0] = 256;
+      p.stages.push_back(fin);
+      p.scratch_bytes = (size_t)splits * k.size * dtype_bytes(k.red_dtype == JAXCUDA_F16 ? JAXCUDA_F32 : k.red_dtype);
+    }
+    p.describe = "reduce-row TPR=" + S(TPR) + " V=" + S(V) + " splits=" + S(splits) + " grid=" + S(row_blocks);
+    return p;
+  }
+
+  Plan reduce_col() const {
+    Plan p;
+    p.skeleton = SK_REDUCE_COL;
+    account(p);
+    const int64_t K = k.red_size;
+    int V = 1;
+    for (int cand : {8, 4, 2}) {
+      if (k.size % cand) continue;
+      int eb = min_load_bytes(0, cand);
+      if (eb && eb * cand <= 16 && (int64_t)k.size / cand >= 256) { V = cand; break; }
+    }
+    const int T = 128;
+    const int64_t nvec = ((int64_t)k.size + V - 1) / V;
+    const int64_t gblocks = (nvec + T - 1) / T;
+    int splits = 1;
+    if (gblocks < 4 * opt.sm_count && K >= 64) {
+      int64_t want = (4 * opt.sm_count + gblocks - 1) / gblocks;
+      splits = (int)std::max<int64_t>(1, std::min<int64_t>(want, K / 16));
+    }
+    int64_t rchunk = (K + splits - 1) / splits;
+    splits = (int)((K + rchunk - 1) / std::max<int64_t>(1, rchunk));
+    if (K == 0) { splits = 1; rchunk = 0; }
+    const char* AT = ctype(k.red_dtype);
+    const size_t root = k.exp.size() - 1;
+    std::vector<char> all(k.exp.size(), 1);
+
+    std::ostringstream os;
+    os << kPrelude;
+    os << "extern \"C\" __global__ void __launch_bounds__(" << T << ") jx_kernel(" << params() << ") {\n";
+    os << "  const int gv = blockIdx.x * " << T << " + threadIdx.x;\n  if (gv >= " << nvec << ") return;\n";
+    os << "  const int g0 = gv * " << V << ";\n";
+    if (splits > 1) {
+      os << "  const int rbeg = blockIdx.y * " << rchunk << ";\n  const int rend = min(" << K << ", rbeg + " << rchunk << ");\n";
+    } else {
+      os << "  const int rbeg = 0, rend = " << K << ";\n";
+    }
+    os << "  " << AT << " acc[" << V << "];\n  #pragma unroll\n  for (int u = 0; u < " << V << "; u++) acc[u] = "
+       << identity_literal(k.red_op, k.red_dtype) << ";\n";
+    std::map<size_t, std::string> ov;
+    std::ostringstream decl, fetch;
+    std::vector<std::string> bnames(k.exp.size());
+    Env env;
+    if (V > 1) preload(decl, fetch, k.exp, an_exp, all, 0, V, env, "g0", "", "", "u", ov, bnames, "    ");
+    os << "  #pragma unroll 4\n  for (int ridx = rbeg; ridx < rend; ridx++) {\n";
+    os << decl.str() << fetch.str();
+    os << "    #pragma unroll\n    for (int u = 0; u < " << V << "; u++) {\n      const int gidx = g0 + u;\n";
+    env.load_override = &ov;
+    std::vector<std::string> names(k.exp.size());
+    emit_nodes(os, k.exp, an_exp, names, all, env, "      ");
+    os << "      acc[u] = " << red("acc[u]", names[root]) << ";\n    }\n  }\n";
+    if (splits > 1) {
+      os << "  " << AT << "* part = (" << AT << "*)scratch + (size_t)blockIdx.y * " << k.size << " + g0;\n";
+      os << "  #pragma unroll\n  for (int u = 0; u < " << V << "; u++) part[u] = acc[u];\n";
+    } else {
+      os << "  #pragma unroll\n  for (int u = 0; u < " << V << "; u++) {\n    const int gidx = g0 + u;\n    const " << AT << " acc_u = acc[u];\n";
+      std::vector<std::string> en(k.epi.size());
+      std::vector<char> eall(k.epi.size(), 1);
+      Env ee;
+      ee.prefix = "e";
+      ee.acc = "acc_u";
+      emit_nodes(os, k.epi, an_epi, en, eall, ee, "    ");
+      os << "    out[gidx] = " << to_storage(out_dt, en.back()) << ";\n  }\n";
+    }
+    os << "}\n";
+    if (splits > 1) emit_finish_kernel(os, splits);
+    p.source = os.str();
+    Stage st;
+    st.entry = "jx_kernel";
+    st.grid[0] = (unsigned)std::max<int64_t>(1, gblocks);
+    st.grid[1] = (unsigned)splits;
+    st.block[0] = T;
+    p.stages.push_back(st);
+    if (splits > 1) {
+      Stage fin;
+      fin.entry = "jx_finish";
+      fin.grid[0] = (unsigned)((k.size + 255) / 256);
+      fin.block[0] = 256;
+      p.stages.push_back(fin);
+      p.scratch_bytes = (size_t)splits * k.size * (k.red_dtype == JAXCUDA_F64 ? 8 : 4);
+    }
+    p.describe = "reduce-col V=" + S(V) + " splits=" + S(splits) + " grid=" + S(gblocks) + "x" + S(T);
+    return p;
+  }
+
+  // ---- GEMM recognition ----------------------------------------------------------------
+  // Body = [Cast<f32>] Mul(load, load) under an f32 Add reduction, both indices affine with
+  // ridx plain: the form `jitRules[Dot]` builds (src/frontend/jit.ts:639-648).
+  GemmDesc match_gemm() const {
+    GemmDesc g;
+    if (!k.has_red || k.red_op != JAXCUDA_OP_ADD || k.red_dtype != JAXCUDA_F32 || k.red_size < 1) return g;
+    size_t r = k.exp.size() - 1;
+    const Node* mul = &k.exp[r];
+    if (mul->op == JAXCUDA_OP_CAST && mul->dtype == JAXCUDA_F32 && k.exp[mul->src[0]].dtype == JAXCUDA_F16) {
+      mul = &k.exp[mul->src[0]];
+      g.round_product_f16 = true;
+    }
+    if (mul->op != JAXCUDA_OP_MUL) return g;
+    auto operand = [&](uint32_t idx) -> const Node* {
+      const Node* nd = &k.exp[idx];
+      if (nd->op == JAXCUDA_OP_CAST && nd->dtype == JAXCUDA_F32) nd = &k.exp[nd->src[0]];
+      if (nd->op != JAXCUDA_OP_GLOBALINDEX) return nullptr;
+      if (nd->dtype != JAXCUDA_F32 && nd->dtype != JAXCUDA_F16) return nullptr;
+      return nd;
+    };
+    const Node* L[2] = {operand(mul->src[0]), operand(mul->src[1])};
+    if (!L[0] || !L[1]) return g;
+    const std::optional<Affine>* ix[2] = {&an_exp.affine[L[0]->src[0]], &an_exp.affine[L[1]->src[0]]};
+    for (int s = 0; s < 2; s++) {
+      if (!*ix[s] || !in_range(*ix[s], L[s]->arg1)) return g;
+      if (!(*ix[s])->only_plain(1) || (*ix[s])->coef_of(1, 1) == 0) return g;
+    }
+    for (int swap = 0; swap < 2; swap++) {
+      const Affine& A = **ix[swap];
+      const Affine& Bx = **ix[1 - swap];
+      // N: modulus of B's unit digit of gidx
+      int64_t N = 0, sBn = 0;
+      for (const Term& t : Bx.terms) if (t.var == 0 && t.div == 1) { N = t.mod; sBn = t.coef; }
+      if (N <= 1 || (int64_t)k.size % N) continue;
+      int64_t M = 0, sAm = 0;
+      for (const Term& t : A.terms) if (t.var == 0 && t.div == N) { M = t.mod ? t.mod : (int64_t)k.size / N; sAm = t.coef; }
+      if (M <= 0 || ((int64_t)k.size / N) % M) continue;
+      const int64_t batch = (int64_t)k.size / (M * N);
+      bool ok = true;
+      int64_t sAb = 0, sBb = 0;
+      for (const Term& t : A.terms) {
+        if (t.var != 0) continue;
+        if (t.div == N && (t.mod == 0 || t.mod == M)) continue;
+        if (t.div == M * N && t.mod == 0 && batch > 1) { sAb = t.coef; continue; }
+        ok = false;
+      }
+      for (const Term& t : Bx.terms) {
+        if (t.var != 0) continue;
+        if (t.div == 1 && t.mod == N) continue;
+        if (t.div == M * N && t.mod == 0 && batch > 1) { sBb = t.coef; continue; }
+        ok = false;
+      }
+      if (!ok) continue;
+      g.valid = true;
+      g.gidA = (uint32_t)L[swap]->arg0; g.gidB = (uint32_t)L[1 - swap]->arg0;
+      g.dtA = L[swap]->dtype; g.dtB = L[1 - swap]->dtype;
+      g.lenA = L[swap]->arg1; g.lenB = L[1 - swap]->arg1;
+      g.M = M; g.N = N; g.K = k.red_size; g.batch = batch;
+      g.offA = A.c0; g.sAm = sAm; g.sAk = A.coef_of(1, 1); g.sAb = sAb;
+      g.offB = Bx.c0; g.sBn = sBn; g.sBk = Bx.coef_of(1, 1); g.sBb = sBb;
+      return g;
+    }
+    return g;
+  }
+
+  // Epilogue statements for one output: expects `acc` (float) and `gidx` (int) in scope and
+  // assigns the storage-typed result to `dst`.
+  std::string epilogue_body(const std::string& indent, const std::string& dst) const {
+    std::ostringstream os;
+    emit_epilogue_store(os, indent, dst);
+    return os.str();
+  }
+
+  Plan gemm_ffma(const GemmDesc& g) const {
+    Plan p;
+    p.skeleton = SK_GEMM_FFMA;
+    p.gemm = g;
+    account(p);
+    p.algo_flops = 2.0 * g.M * g.N * g.K * g.batch;
+    const int BM = 128, BN = 128, BK = 16, T = 256;
+    std::ostringstream os;
+    os << kPrelude;
+    os << "#define BM " << BM << "\n#define BN " << BN << "\n#define BK " << BK << "\n";
+    os << "#define GM " << g.M << "\n#define GN " << g.N << "\n#define GK " << g.K << "\n";
+    os << "#define OFFA " << g.offA << "LL\n#define SAM " << g.sAm << "LL\n#define SAK " << g.sAk << "LL\n#define SAB " << g.sAb << "LL\n";
+    os << "#define OFFB " << g.offB << "LL\n#define SBN " << g.sBn << "LL\n#define SBK " << g.sBk << "LL\n#define SBB " << g.sBb << "LL\n";
+    os << "typedef " << ptype(g.dtA) << " TA;\ntypedef " << ptype(g.dtB) << " TB;\n";
+    os << "__device__ __forceinline__ float jx_ldA(const TA* p) { return " << from_storage(g.dtA, "*p") << "; }\n";
+    os << "__device__ __forceinline__ float jx_ldB(const TB* p) { return " << from_storage(g.dtB, "*p") << "; }\n";
+    // thread -> tile element mapping for the global loads: adjacent threads walk the contiguous axis
+    const bool a_kcontig = std::llabs(g.sAk) <= std::llabs(g.sAm);
+    const bool b_kcontig = std::llabs(g.sBk) <= std::llabs(g.sBn);
+    os << "extern \"C\" __global__ void __launch_bounds__(" << T << ") jx_kernel(" << params() << ") {\n";
+    os << R"(  __shared__ __align__(16) float As[2][BK][BM + 4];
+  __shared__ __align__(16) float Bs[2][BK][BN + 4];
+  const int t = threadIdx.x;
+  const int bz = blockIdx.z, bm = blockIdx.y * BM, bn = blockIdx.x * BN;
+)";
+    os << "  const TA* A = (const TA*)p" << g.gidA << " + OFFA + (i64)bz * SAB;\n";
+    os << "  const TB* B = (const TB*)p" << g.gidB << " + OFFB + (i64)bz * SBB;\n";
+    os << "  const int tx = t % 16, ty = t / 16;\n";
+    os << "  float c[8][8];\n  #pragma unroll\n  for (int i = 0; i < 8; i++)\n    #pragma unroll\n    for (int j = 0; j < 8; j++) c[i][j] = 0.0f;\n";
+    os << "  float ra[8], rb[8];\n";
+    // element e (0..7) of this thread within the A tile: (m, k)
+    if (a_kcontig) os << "  #define A_K(e) (t % BK)\n  #define A_M(e) (t / BK + (e) * " << T / BK << ")\n";
+    else os << "  #define A_M(e) (t % BM)\n  #define A_K(e) (t / BM + (e) * " << T / BM << ")\n";
+    if (b_kcontig) os << "  #define B_K(e) (t % BK)\n  #define B_N(e) (t / BK + (e) * " << T / BK << ")\n";
+    else os << "  #define B_N(e) (t % BN)\n  #define B_K(e) (t / BN + (e) * " << T / BN << ")\n";
+    os << R"(  auto fetch = [&](int k0) {
+    #pragma unroll
+    for (int e = 0; e < 8; e++) {
+      const int m = bm + A_M(e), ka = k0 + A_K(e);
+      ra[e] = (m < GM && ka < GK) ? jx_ldA(A + (i64)m * SAM + (i64)ka * SAK) : 0.0f;
+      const int n = bn + B_N(e), kb = k0 + B_K(e);
+      rb[e] = (n < GN && kb < GK) ? jx_ldB(B + (i64)n * SBN + (i64)kb * SBK) : 0.0f;
+    }
+  };
+  auto stash = [&](int buf) {
+    #pragma unroll
+    for (int e = 0; e < 8; e++) {
+      As[buf][A_K(e)][A_M(e)] = ra[e];
+      Bs[buf][B_K(e)][B_N(e)] = rb[e];
+    }
+  };
+  fetch(0);
+  stash(0);
+  __syncthreads();
+  int buf = 0;
+  for (int k0 = 0; k0 < GK; k0 += BK) {
+    const bool more = k0 + BK < GK;
+    if (more) fetch(k0 + BK);
+    #pragma unroll
+    for (int kk = 0; kk < BK; kk++) {
+      float a[8], b[8];
+      *(float4*)&a[0] = *(const float4*)&As[buf][kk][ty * 4];
+      *(float4*)&a[4] = *(const float4*)&As[buf][kk][ty * 4 + 64];
+      *(float4*)&b[0] = *(const float4*)&Bs[buf][kk][tx * 4];
+      *(float4*)&b[4] = *(const float4*)&Bs[buf][kk][tx * 4 + 64];
+      #pragma unroll
+      for (int i = 0; i < 8; i++)
+        #pragma unroll
+        for (int j = 0; j < 8; j++) c[i][j] = fmaf(a[i], b[j], c[i][j]);
+    }
+    if (more) { stash(buf ^ 1); __syncthreads(); buf ^= 1; }
+  }
+  #pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const int m = bm + ty * 4 + (i & 3) + (i >> 2) * 64;
+    if (m >= GM) continue;
+    #pragma unroll
+    for (int j = 0; j < 8; j++) {
+      const int n = bn + tx * 4 + (j & 3) + (j >> 2) * 64;
+      if (n >= GN) continue;
+      const int gidx = (int)(((i64)bz * GM + m) * GN + n);
+      const float acc = c[i][j];
+)";
+    os << epilogue_body("      ", "out[gidx]");
+    os << "    }\n  }\n}\n";
+    p.source = os.str();
+    Stage st;
+    st.entry = "jx_kernel";
+    st.grid[0] = (unsigned)((g.N + BN - 1) / BN);
+    st.grid[1] = (unsigned)((g.M + BM - 1) / BM);
+    st.grid[2] = (unsigned)g.batch;
+    st.block[0] = T;
+    p.stages.push_back(st);
+    p.describe = "gemm-ffma " + S(g.batch) + "x" + S(g.M) + "x" + S(g.N) + "x" + S(g.K) + " tile 128x128x16";
+    return p;
+  }
+
+  Plan build() const {
+    if (!k.has_red) return elementwise();
+    if (opt.force_skeleton == SK_REDUCE_ROW) return reduce_row();
+    if (opt.force_skeleton == SK_REDUCE_COL) return reduce_col();
+    GemmDesc g = match_gemm();
+    if (g.valid && g.batch <= 65535 &&
+        ((g.M >= opt.gemm_min_dim && g.N >= opt.gemm_min_dim && g.K >= 8) || opt.force_skeleton == SK_GEMM_FFMA)) {
+      if (opt.allow_tc && opt.force_skeleton != SK_GEMM_FFMA) {
+        Plan p;
+        p.gemm = g;
+        account(p);
+        p.algo_flops = 2.0 * g.M * g.N * g.K * g.batch;
+        if (plan_gemm_tc(k, g, opt, p, epilogue_body("      ", "JX_DST"), params())) return p;
+      }
+      return gemm_ffma(g);
+    }
+    const int64_t K = k.red_size;
+    const bool r_contig = has_load(1), g_contig = has_load(0);
+    bool row;
+    if (r_contig && !g_contig) row = K >= 16;
+    else if (g_contig && !r_contig) row = false;
+    else if (r_contig && g_contig) row = k.size < 4096 && K >= 128;
+    else row = k.size < 2048 && K >= 128;
+    return row ? reduce_row() : reduce_col();
+  }
+};
+
+}  // namespace
+
+Plan make_plan(const KernelIR& k, const Options& opt) {
+  Builder b(k, opt);
+  return b.build();
+}
+
+}  // namespace jaxcuda

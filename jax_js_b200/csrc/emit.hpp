@@ -1,0 +1,74 @@
+// Skeleton choice and CUDA C generation for one lowered Kernel.
+//
+// A Kernel (src/alu.ts:1479) reaches the backend as an untagged expression DAG; this file
+// decides which hand-written sm_100a skeleton it runs in and splices the DAG into it.
+// It takes the place of `tuneWebgpu` + `pipelineSource` (src/tuner.ts:243-478,
+// src/backend/webgpu.ts:285-530) and of the Wasm tile planner
+// (src/backend/wasm/tilePlan.ts:278-334), re-derived for Blackwell.
+#pragma once
+
+#include <string>
+#include <vector>
+
+#include "ir.hpp"
+
+namespace jaxcuda {
+
+enum Skeleton {
+  SK_ELEMENTWISE = 0,  // 128-bit vectorised streaming kernel
+  SK_REDUCE_ROW = 1,   // lanes of a warp/CTA stride over ridx, shuffle + shared-memory tree
+  SK_REDUCE_COL = 2,   // one thread per (vector of) outputs loops over ridx; optional split over ridx
+  SK_GEMM_FFMA = 3,    // shared-memory tiled FFMA GEMM with spliced epilogue (any strides)
+  SK_GEMM_TC = 4,      // TMA + tcgen05/TMEM GEMM (f16 operands, or f32 as 3xTF32)
+};
+
+// Strides are in elements.  C[b, m, n] = sum_k A[offA + b*sAb + m*sAm + k*sAk] * B[offB + b*sBb + n*sBn + k*sBk]
+struct GemmDesc {
+  bool valid = false;
+  uint32_t gidA = 0, gidB = 0, dtA = 0, dtB = 0;
+  uint64_t lenA = 0, lenB = 0;
+  int64_t M = 0, N = 0, K = 0, batch = 1;
+  int64_t offA = 0, sAm = 0, sAk = 0, sAb = 0;
+  int64_t offB = 0, sBn = 0, sBk = 0, sBb = 0;
+  bool round_product_f16 = false;  // body is Cast<f32>(Mul<f16>(a, b))
+};
+
+struct Stage {
+  std::string entry;
+  unsigned grid[3] = {1, 1, 1};
+  unsigned block[3] = {1, 1, 1};
+  unsigned smem = 0;
+};
+
+struct Plan {
+  int skeleton = SK_ELEMENTWISE;
+  std::string source;        // complete CUDA C translation unit for NVRTC
+  std::vector<Stage> stages;  // launched in order on the backend's stream
+  size_t scratch_bytes = 0;   // global scratch shared by the stages (split reductions, TF32 planes)
+  std::string describe;       // one line: skeleton and launch shape
+  GemmDesc gemm;
+  double algo_bytes = 0;      // distinct input bytes addressed + output bytes
+  double algo_flops = 0;      // 2*M*N*K for GEMM-shaped kernels, else size * K
+  // tensor-core GEMM launch parameters (SK_GEMM_TC), filled by gemm_tc.cpp
+  int tc_kind = 0;            // 1 f16, 2 3xTF32
+  int tc_bm = 0, tc_bn = 0, tc_bk = 0, tc_stages = 0;
+};
+
+struct Options {
+  int sm_count = 148;
+  int ew_ilp = 4;             // independent 128-bit accesses in flight per thread (elementwise)
+  int ew_blocks_per_sm = 16;  // grid cap for the grid-stride elementwise loop
+  int gemm_min_dim = 32;      // below this M or N a GEMM-shaped kernel stays on the reduce skeletons
+  bool allow_tc = true;       // tcgen05 path allowed (JAXCUDA_NO_TC=1 clears it)
+  int force_skeleton = -1;    // tests: force SK_REDUCE_ROW / SK_REDUCE_COL / SK_GEMM_FFMA
+};
+
+// Throws std::runtime_error with the reference's UnsupportedOpError wording
+// ("Op<dtype> not supported in cuda backend") for combinations that cannot be emitted.
+Plan make_plan(const KernelIR& k, const Options& opt);
+
+// Implemented in gemm_tc.cpp: rewrites `plan` to the tcgen05 skeleton when `g` qualifies.
+bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan& plan,
+                  const std::string& epilogue_body, const std::string& params_decl);
+
+}  // namespace jaxcuda

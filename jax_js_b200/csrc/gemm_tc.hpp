@@ -1,0 +1,20 @@
+// TMA + tcgen05/TMEM GEMM skeleton: planning (source generation) and launch.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <string>
+#include <vector>
+
+#include "emit.hpp"
+
+namespace jaxcuda {
+
+// Launches the stages of a SK_GEMM_TC plan.  Returns the number of kernels launched, or -1
+// with `err` set.  `encode_fn` is cuTensorMapEncodeTiled, `launch_fn` cuLaunchKernel.
+int launch_gemm_tc(void* encode_fn, void* launch_fn, const Plan& plan, const std::vector<CUfunction>& fns,
+                   const std::vector<void*>& inputs, void* out, void* scratch, cudaStream_t stream,
+                   std::string& err);
+
+}  // namespace jaxcuda

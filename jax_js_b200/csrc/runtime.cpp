@@ -1,0 +1,704 @@
+// libjaxcuda.so runtime: contexts, ref-counted slots over a caching device allocator, the
+// NVRTC kernel cache, dispatch, readback, event timing and the NCCL gradient sum.
+//
+// Shape of the reference it stands behind: the slot map and allocator of the Wasm backend
+// (src/backend/wasm.ts:57-123, src/backend/wasm/allocator.ts:73-90), the buffer pool and
+// pipeline cache of the WebGPU backend (src/backend/webgpu.ts:224-247, :655-760), and the
+// dispatch-order guarantee of the interface (src/backend.ts:203-210) -- here one CUDA stream.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+#include <nvrtc.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <stdexcept>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/jaxcuda.h"
+#include "emit.hpp"
+#include "gemm_tc.hpp"
+#include "ir.hpp"
+
+extern "C" size_t jaxcuda_sort_work_bytes(int argsort, int64_t batch, int64_t n);
+extern "C" int jaxcuda_sort_launch(void* stream, int argsort, const void* x, void* y, int32_t* yi, int dtype,
+                                   int64_t batch, int64_t n, void* work, int* launches);
+
+using namespace jaxcuda;
+
+namespace jaxcuda_rt {
+
+std::string g_create_error;
+
+struct Driver {
+  CUresult (*ModuleLoadData)(CUmodule*, const void*) = nullptr;
+  CUresult (*ModuleUnload)(CUmodule) = nullptr;
+  CUresult (*ModuleGetFunction)(CUfunction*, CUmodule, const char*) = nullptr;
+  CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned,
+                           CUstream, void**, void**) = nullptr;
+  CUresult (*FuncSetAttribute)(CUfunction, CUfunction_attribute, int) = nullptr;
+  CUresult (*GetErrorString)(CUresult, const char**) = nullptr;
+  void* TensorMapEncodeTiled = nullptr;
+  bool loaded = false;
+};
+
+bool load_driver(Driver& d, std::string& err) {
+  auto get = [&](const char* name, void** fn) {
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint(name, fn, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !*fn) {
+      err = std::string("driver entry point ") + name + " unavailable";
+      return false;
+    }
+    return true;
+  };
+  if (!get("cuModuleLoadData", (void**)&d.ModuleLoadData)) return false;
+  if (!get("cuModuleUnload", (void**)&d.ModuleUnload)) return false;
+  if (!get("cuModuleGetFunction", (void**)&d.ModuleGetFunction)) return false;
+  if (!get("cuLaunchKernel", (void**)&d.LaunchKernel)) return false;
+  if (!get("cuFuncSetAttribute", (void**)&d.FuncSetAttribute)) return false;
+  if (!get("cuGetErrorString", (void**)&d.GetErrorString)) return false;
+  if (!get("cuTensorMapEncodeTiled", &d.TensorMapEncodeTiled)) return false;
+  d.loaded = true;
+  return true;
+}
+
+// Size-class caching allocator.  Everything a context does is ordered on one stream, so a
+// block returned to the free list may be handed out again at once: any kernel that still
+// reads it was enqueued before whatever the next owner enqueues.
+struct Allocator {
+  std::map<size_t, std::vector<void*>> free_lists;
+  size_t reserved = 0, in_use = 0;
+
+  static size_t round_size(size_t n) {
+    if (n <= 512) return 512;
+    size_t p = 512;
+    while (p < n) p <<= 1;
+    const size_t step = p >> 3;  // eight classes per octave: at most 12.5 % slack
+    return (n + step - 1) / step * step;
+  }
+  cudaError_t get(size_t n, void** out) {
+    const size_t cls = round_size(n);
+    auto it = free_lists.find(cls);
+    if (it != free_lists.end() && !it->second.empty()) {
+      *out = it->second.back();
+      it->second.pop_back();
+      in_use += cls;
+      return cudaSuccess;
+    }
+    cudaError_t e = cudaMalloc(out, cls);
+    if (e != cudaSuccess) {  // give cached blocks back to the driver and retry once
+      cudaGetLastError();
+      release_cached();
+      e = cudaMalloc(out, cls);
+    }
+    if (e == cudaSuccess) { reserved += cls; in_use += cls; }
+    return e;
+  }
+  void put(void* p, size_t n) {
+    const size_t cls = round_size(n);
+    free_lists[cls].push_back(p);
+    in_use -= cls;
+  }
+  void release_cached() {
+    for (auto& kv : free_lists) {
+      for (void* p : kv.second) { cudaFree(p); reserved -= kv.first; }
+      kv.second.clear();
+    }
+  }
+};
+
+struct SlotRec {
+  void* ptr = nullptr;
+  size_t bytes = 0;
+  int refs = 0;
+};
+
+}  // namespace jaxcuda_rt
+using namespace jaxcuda_rt;
+
+struct jaxcuda_exe {
+  jaxcuda_ctx* ctx = nullptr;
+  int kind = 0;  // 0 kernel, 1 Sort, 2 Argsort
+  int handles = 0;
+  uint64_t hash = 0;
+  KernelIR ir;
+  Plan plan;
+  CUmodule module = nullptr;
+  std::vector<CUfunction> fns;
+  // routine
+  int rt_dtype = 0;
+  int64_t rt_batch = 0, rt_n = 0;
+  std::string describe;
+};
+
+struct jaxcuda_ctx {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  Driver drv;
+  Allocator alloc;
+  std::unordered_map<uint32_t, SlotRec> slots;
+  uint32_t next_slot = 1;
+  std::unordered_map<uint64_t, std::unique_ptr<jaxcuda_exe>> kernels;
+  std::vector<std::unique_ptr<jaxcuda_exe>> routines;
+  std::string last_error;
+  Options opt;
+  std::vector<cudaEvent_t> events;  // created on first use of an index
+  uint64_t launches = 0;
+  int debug = 0;
+  // NCCL (resolved with dlopen so that the library loads where NCCL is absent)
+  void* nccl_lib = nullptr;
+  void* comm = nullptr;
+  int nranks = 1;
+};
+
+namespace {
+
+int fail(jaxcuda_ctx* ctx, int status, const char* fmt, ...) {
+  char buf[2048];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  if (ctx) ctx->last_error = buf; else g_create_error = buf;
+  return status;
+}
+
+#define CUDA_TRY(ctx, call)                                                                        \
+  do {                                                                                             \
+    cudaError_t e__ = (call);                                                                      \
+    if (e__ != cudaSuccess) return fail(ctx, JAXCUDA_ECUDA, "%s: %s", #call, cudaGetErrorString(e__)); \
+  } while (0)
+
+int drv_fail(jaxcuda_ctx* ctx, const char* what, CUresult r) {
+  const char* s = nullptr;
+  if (ctx->drv.GetErrorString) ctx->drv.GetErrorString(r, &s);
+  return fail(ctx, JAXCUDA_ECUDA, "%s: %s", what, s ? s : "unknown driver error");
+}
+
+SlotRec* find_slot(jaxcuda_ctx* ctx, jaxcuda_slot s) {
+  auto it = ctx->slots.find(s);
+  return it == ctx->slots.end() ? nullptr : &it->second;
+}
+
+int slot_error(jaxcuda_ctx* ctx, jaxcuda_slot s) {
+  // wording of SlotError, src/backend.ts:222-226
+  return fail(ctx, JAXCUDA_ESLOT, "Used a buffer that is invalid or already freed: %u", s);
+}
+
+uint64_t fnv1a(const uint8_t* p, size_t n) {
+  uint64_t h = 0xcbf29ce484222325ull;
+  for (size_t i = 0; i < n; i++) h = (h ^ p[i]) * 0x100000001b3ull;
+  return h;
+}
+
+// NVRTC: CUDA C -> sm_100a cubin.  Needs no GPU.
+bool nvrtc_compile(const std::string& src, std::vector<char>& cubin, std::string& err) {
+  nvrtcProgram prog;
+  if (nvrtcCreateProgram(&prog, src.c_str(), "jaxcuda_kernel.cu", 0, nullptr, nullptr) != NVRTC_SUCCESS) {
+    err = "nvrtcCreateProgram failed";
+    return false;
+  }
+  const char* opts[] = {"--gpu-architecture=sm_100a", "-std=c++17", "-lineinfo", "--fmad=true"};
+  nvrtcResult r = nvrtcCompileProgram(prog, 4, opts);
+  if (r != NVRTC_SUCCESS) {
+    size_t n = 0;
+    nvrtcGetProgramLogSize(prog, &n);
+    std::string log(n, '\0');
+    nvrtcGetProgramLog(prog, &log[0]);
+    nvrtcDestroyProgram(&prog);
+    err = "NVRTC: " + log + "\n---- generated source ----\n" + src;
+    return false;
+  }
+  size_t n = 0;
+  nvrtcGetCUBINSize(prog, &n);
+  cubin.resize(n);
+  nvrtcGetCUBIN(prog, cubin.data());
+  nvrtcDestroyProgram(&prog);
+  return true;
+}
+
+int compile_plan(jaxcuda_ctx* ctx, jaxcuda_exe* exe) {
+  std::vector<char> cubin;
+  if (!nvrtc_compile(exe->plan.source, cubin, ctx->last_error)) return JAXCUDA_ECOMPILE;
+  CUresult cr = ctx->drv.ModuleLoadData(&exe->module, cubin.data());
+  if (cr != CUDA_SUCCESS) return drv_fail(ctx, "cuModuleLoadData", cr);
+  for (const Stage& st : exe->plan.stages) {
+    CUfunction fn;
+    cr = ctx->drv.ModuleGetFunction(&fn, exe->module, st.entry.c_str());
+    if (cr != CUDA_SUCCESS) return drv_fail(ctx, "cuModuleGetFunction", cr);
+    if (st.smem > 48 * 1024) {
+      cr = ctx->drv.FuncSetAttribute(fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)st.smem);
+      if (cr != CUDA_SUCCESS) return drv_fail(ctx, "cuFuncSetAttribute", cr);
+    }
+    exe->fns.push_back(fn);
+  }
+  return JAXCUDA_OK;
+}
+
+void free_exe(jaxcuda_ctx* ctx, jaxcuda_exe* exe) {
+  if (exe->module && ctx->drv.ModuleUnload) ctx->drv.ModuleUnload(exe->module);
+  exe->module = nullptr;
+}
+
+int env_int(const char* name, int dflt) {
+  const char* v = getenv(name);
+  return v && *v ? atoi(v) : dflt;
+}
+
+}  // namespace
+
+extern "C" {
+
+int jaxcuda_max_args(void) { return 64; }
+
+const char* jaxcuda_last_error(jaxcuda_ctx* ctx) { return ctx ? ctx->last_error.c_str() : g_create_error.c_str(); }
+
+int jaxcuda_create(int device, jaxcuda_ctx** out) {
+  if (!out) return fail(nullptr, JAXCUDA_EINVAL, "null out pointer");
+  *out = nullptr;
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0)
+    return fail(nullptr, JAXCUDA_ECUDA, "no CUDA device available (%s); the cuda backend has no CPU fallback",
+                e != cudaSuccess ? cudaGetErrorString(e) : "device count is 0");
+  if (device < 0) device = env_int("JAXCUDA_DEVICE", 0);
+  if (device >= count) return fail(nullptr, JAXCUDA_EINVAL, "device %d out of range (%d devices)", device, count);
+  std::unique_ptr<jaxcuda_ctx> ctx(new jaxcuda_ctx);
+  ctx->device = device;
+  if ((e = cudaSetDevice(device)) != cudaSuccess || (e = cudaFree(0)) != cudaSuccess)
+    return fail(nullptr, JAXCUDA_ECUDA, "cudaSetDevice(%d): %s", device, cudaGetErrorString(e));
+  cudaDeviceProp prop;
+  if ((e = cudaGetDeviceProperties(&prop, device)) != cudaSuccess)
+    return fail(nullptr, JAXCUDA_ECUDA, "cudaGetDeviceProperties: %s", cudaGetErrorString(e));
+  if (prop.major != 10)
+    return fail(nullptr, JAXCUDA_ECUDA, "device %d is sm_%d%d; this backend is built for sm_100a only", device,
+                prop.major, prop.minor);
+  std::string err;
+  if (!load_driver(ctx->drv, err)) return fail(nullptr, JAXCUDA_ECUDA, "%s", err.c_str());
+  if ((e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking)) != cudaSuccess)
+    return fail(nullptr, JAXCUDA_ECUDA, "cudaStreamCreate: %s", cudaGetErrorString(e));
+  ctx->opt.sm_count = prop.multiProcessorCount;
+  ctx->opt.ew_ilp = env_int("JAXCUDA_EW_ILP", ctx->opt.ew_ilp);
+  ctx->opt.ew_blocks_per_sm = env_int("JAXCUDA_EW_BLOCKS_PER_SM", ctx->opt.ew_blocks_per_sm);
+  ctx->opt.allow_tc = env_int("JAXCUDA_NO_TC", 0) == 0;
+  ctx->opt.force_skeleton = env_int("JAXCUDA_FORCE_SKELETON", -1);
+  ctx->debug = env_int("JAXCUDA_DEBUG", 0);
+  *out = ctx.release();
+  return JAXCUDA_OK;
+}
+
+int jaxcuda_destroy(jaxcuda_ctx* ctx) {
+  if (!ctx) return JAXCUDA_OK;
+  cudaSetDevice(ctx->device);
+  cudaStreamSynchronize(ctx->stream);
+  jaxcuda_comm_destroy(ctx);
+  for (auto& kv : ctx->kernels) free_exe(ctx, kv.second.get());
+  for (auto& ev : ctx->events) if (ev) cudaEventDestroy(ev);
+  for (auto& kv : ctx->slots) if (kv.second.ptr) ctx->alloc.put(kv.second.ptr, kv.second.bytes);
+  ctx->alloc.release_cached();
+  cudaStreamDestroy(ctx->stream);
+  delete ctx;
+  return JAXCUDA_OK;
+}
+
+int jaxcuda_malloc(jaxcuda_ctx* ctx, size_t bytes, const void* init, size_t init_bytes, jaxcuda_slot* out) {
+  if (!ctx || !out) return JAXCUDA_EINVAL;
+  if (init && init_bytes != bytes)
+    return fail(ctx, JAXCUDA_EINVAL, "initialData size %zu does not match buffer size %zu", init_bytes, bytes);
+  cudaSetDevice(ctx->device);
+  SlotRec rec;
+  rec.bytes = bytes;
+  rec.refs = 1;
+  if (bytes) {
+    cudaError_t e = ctx->alloc.get(bytes, &rec.ptr);
+    if (e != cudaSuccess) return fail(ctx, JAXCUDA_ENOMEM, "device allocation of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
+    if (init) {
+      e = cudaMemcpyAsync(rec.ptr, init, bytes, cudaMemcpyHostToDevice, ctx->stream);
+      // The caller may reuse `init` as soon as malloc returns (it is a JS typed array).
+      if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+      if (e != cudaSuccess) {
+        ctx->alloc.put(rec.ptr, bytes);
+        return fail(ctx, JAXCUDA_ECUDA, "upload failed: %s", cudaGetErrorString(e));
+      }
+    }
+  }
+  const jaxcuda_slot id = ctx->next_slot++;
+  ctx->slots[id] = rec;
+  *out = id;
+  return JAXCUDA_OK;
+}
+
+int jaxcuda_incref(jaxcuda_ctx* ctx, jaxcuda_slot slot) {
+  SlotRec* s = find_slot(ctx, slot);
+  if (!s) return slot_error(ctx, slot);
+  s->refs++;
+  return JAXCUDA_OK;
+}
+
+int jaxcuda_decref(jaxcuda_ctx* ctx, jaxcuda_slot slot) {
+  SlotRec* s = find_slot(ctx, slot);
+  if (!s) return slot_error(ctx, slot);
+  if (--s->refs == 0) {
+    if (s->ptr) ctx->alloc.put(s->ptr, s->bytes);
+    ctx->slots.erase(slot);
+  }
+  return JAXCUDA_OK;
+}
+
+int jaxcuda_slot_size(jaxcuda_ctx* ctx, jaxcuda_slot slot, size_t* bytes) {
+  SlotRec* s = find_slot(ctx, slot);
+  if (!s) return slot_error(ctx, slot);
+  *bytes = s->bytes;
+  return JAXCUDA_OK;
+}
+
+int jaxcuda_read(jaxcuda_ctx* ctx, jaxcuda_slot slot, size_t start, size_t count, void* dst) {
+  SlotRec* s = find_slot(ctx, slot);
+  if (!s) return slot_error(ctx, slot);
+  if (start > s->bytes) return fail(ctx, JAXCUDA_EINVAL, "read start %zu beyond buffer of %zu bytes", start, s->bytes);
+  if (count == SIZE_MAX) count = s->bytes - start;
+  if (count > s->bytes - start) return fail(ctx, JAXCUDA_EINVAL, "read of %zu bytes at %zu beyond buffer of %zu bytes", count, start, s->bytes);
+  cudaSetDevice(ctx->device);
+  if (count) {
+    if (!dst) return fail(ctx, JAXCUDA_EINVAL, "null destination");
+    CUDA_TRY(ctx, cudaMemcpyAsync(dst, (const char*)s->ptr + start, count, cudaMemcpyDeviceToHost, ctx->stream));
+  }
+  CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+  return JAXCUDA_OK;
+}
+
+int jaxcuda_write(jaxcuda_ctx* ctx, jaxcuda_slot slot, size_t start, size_t count, const void* src) {
+  SlotRec* s = find_slot(ctx, slot);
+  if (!s) return slot_error(ctx, slot);
+  if (start > s->bytes || count > s->bytes - start)
+    return fail(ctx, JAXCUDA_EINVAL, "write of %zu bytes at %zu beyond buffer of %zu bytes", count, start, s->bytes);
+  cudaSetDevice(ctx->device);
+  if (count) CUDA_TRY(ctx, cudaMemcpyAsync((char*)s->ptr + start, src, count, cudaMemcpyHostToDevice, ctx->stream));
+  return JAXCUDA_OK;
+}
+
+int jaxcuda_prepare_kernel(jaxcuda_ctx* ctx, const uint8_t* ir, size_t len, uint64_t hash, jaxcuda_exe** out) {
+  if (!ctx || !out) return JAXCUDA_EINVAL;
+  *out = nullptr;
+  if (!ir) return fail(ctx, JAXCUDA_EINVAL, "null kernel image");
+  if (hash == 0) hash = fnv1a(ir, len);
+  auto it = ctx->kernels.find(hash);
+  if (it != ctx->kernels.end()) {
+    it->second->handles++;
+    *out = it->second.get();
+    return JAXCUDA_OK;
+  }
+  std::unique_ptr<jaxcuda_exe> exe(new jaxcuda_exe);
+  exe->ctx = ctx;
+  exe->hash = hash;
+  std::string err = parse_kernel(ir, len, exe->ir);
+  if (!err.empty()) return fail(ctx, JAXCUDA_EINVAL, "%s", err.c_str());
+  if (exe->ir.nargs > (uint32_t)jaxcuda_max_args())
+    return fail(ctx, JAXCUDA_EINVAL, "kernel takes %u arguments, at most %d are supported", exe->ir.nargs, jaxcuda_max_args());
+  try {
+    exe->plan = make_plan(exe->ir, ctx->opt);
+  } catch (const std::exception& e) {
+    return fail(ctx, JAXCUDA_EUNSUPPORTED, "%s", e.what());
+  }
+  exe->describe = exe->plan.describe;
+  if (ctx->debug >= 4) fprintf(stderr, "[jaxcuda] %016llx %s\n", (unsigned long long)hash, exe->describe.c_str());
+  if (ctx->debug >= 2) fprintf(stderr, "%s\n", exe->plan.source.c_str());
+  cudaSetDevice(ctx->device);
+  int rc = compile_plan(ctx, exe.get());
+  if (rc != JAXCUDA_OK) { free_exe(ctx, exe.get()); return rc; }
+  exe->handles = 1;
+  *out = exe.get();
+  ctx->kernels[hash] = std::move(exe);
+  return JAXCUDA_OK;
+}
+
+int jaxcuda_check_kernel(const uint8_t* ir, size_t len, int sm_count, int force_skeleton, int compile,
+                         char* describe, size_t describe_len, char* message, size_t message_len) {
+  auto put = [](char* dst, size_t n, const std::string& s) {
+    if (dst && n) { snprintf(dst, n, "%s", s.c_str()); }
+  };
+  KernelIR k;
+  std::string err = parse_kernel(ir, len, k);
+  if (!err.empty()) { put(message, message_len, err); return JAXCUDA_EINVAL; }
+  Options opt;
+  if (sm_count > 0) opt.sm_count = sm_count;
+  opt.force_skeleton = force_skeleton;
+  opt.allow_tc = env_int("JAXCUDA_NO_TC", 0) == 0;
+  Plan plan;
+  try {
+    plan = make_plan(k, opt);
+  } catch (const std::exception& e) {
+    put(message, message_len, e.what());
+    return JAXCUDA_EUNSUPPORTED;
+  }
+  put(describe, describe_len, plan.describe);
+  if (compile) {
+    std::vector<char> cubin;
+    if (!nvrtc_compile(plan.source, cubin, err)) { put(message, message_len, err); return JAXCUDA_ECOMPILE; }
+  } else {
+    put(message, message_len, plan.source);
+  }
+  return JAXCUDA_OK;
+}
+
+int jaxcuda_prepare_routine(jaxcuda_ctx* ctx, const char* name, const jaxcuda_routine_type* type,
+                            const char* params_json, jaxcuda_exe** out) {
+  (void)params_json;
+  if (!ctx || !out || !name || !type) return JAXCUDA_EINVAL;
+  *out = nullptr;
+  const bool is_sort = !strcmp(name, "Sort"), is_argsort = !strcmp(name, "Argsort");
+  if (!is_sort && !is_argsort)  // wording of UnsupportedRoutineError, src/backend.ts:236-240
+    return fail(ctx, JAXCUDA_EUNSUPPORTED, "routine '%s' is not supported in cuda backend", name);
+  if (type->n_inputs != 1 || type->n_outputs != (is_argsort ? 2 : 1))
+    return fail(ctx, JAXCUDA_EINVAL, "%s: wrong number of inputs or outputs", name);
+  const int rank = type->input_ranks[0];
+  if (rank == 0) return fail(ctx, JAXCUDA_EINVAL, "%s: cannot sort a scalar", is_sort ? "sort" : "argsort");  // routine.ts:187, :197
+  const int dt = type->input_dtypes[0];
+  if (dt == JAXCUDA_F64) return fail(ctx, JAXCUDA_EUNSUPPORTED, "%s<float64> not supported in cuda backend", name);
+  std::unique_ptr<jaxcuda_exe> exe(new jaxcuda_exe);
+  exe->ctx = ctx;
+  exe->kind = is_sort ? 1 : 2;
+  exe->rt_dtype = dt;
+  exe->rt_n = type->input_shapes[rank - 1];
+  exe->rt_batch = 1;
+  for (int i = 0; i < rank - 1; i++) exe->rt_batch *= type->input_shapes[i];
+  if (exe->rt_n >= (1ll << 31)) return fail(ctx, JAXCUDA_EINVAL, "%s: axis too long", name);
+  exe->describe = std::string(name) + " batch=" + std::to_string(exe->rt_batch) + " n=" + std::to_string(exe->rt_n);
+  exe->plan.describe = exe->describe;
+  exe->plan.algo_bytes = 2.0 * exe->rt_batch * exe->rt_n * dtype_bytes(dt) + (is_argsort ? 4.0 * exe->rt_batch * exe->rt_n : 0);
+  exe->handles = 1;
+  *out = exe.get();
+  ctx->routines.push_back(std::move(exe));
+  return JAXCUDA_OK;
+}
+
+int jaxcuda_dispatch(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const jaxcuda_slot* inputs, int n_inputs,
+                     const jaxcuda_slot* outputs, int n_outputs) {
+  if (!ctx || !exe || exe->ctx != ctx) return JAXCUDA_EINVAL;
+  cudaSetDevice(ctx->device);
+  std::vector<SlotRec*> in(n_inputs), outv(n_outputs);
+  for (int i = 0; i < n_inputs; i++) if (!(in[i] = find_slot(ctx, inputs[i]))) return slot_error(ctx, inputs[i]);
+  for (int i = 0; i < n_outputs; i++) if (!(outv[i] = find_slot(ctx, outputs[i]))) return slot_error(ctx, outputs[i]);
+
+  if (exe->kind != 0) {  // Sort / Argsort
+    const bool arg = exe->kind == 2;
+    if (n_inputs != 1 || n_outputs != (arg ? 2 : 1)) return fail(ctx, JAXCUDA_EINVAL, "routine called with wrong slot counts");
+    const size_t need = (size_t)exe->rt_batch * exe->rt_n * dtype_bytes(exe->rt_dtype);
+    if (in[0]->bytes < need || outv[0]->bytes < need || (arg && outv[1]->bytes < (size_t)exe->rt_batch * exe->rt_n * 4))
+      return fail(ctx, JAXCUDA_EINVAL, "routine buffers are smaller than its declared shapes");
+    const size_t wb = jaxcuda_sort_work_bytes(arg, exe->rt_batch, exe->rt_n);
+    void* work = nullptr;
+    if (wb) {
+      cudaError_t e = ctx->alloc.get(wb, &work);
+      if (e != cudaSuccess) return fail(ctx, JAXCUDA_ENOMEM, "sort work space of %zu bytes: %s", wb, cudaGetErrorString(e));
+    }
+    int launches = 0;
+    int rc = jaxcuda_sort_launch(ctx->stream, arg, in[0]->ptr, outv[0]->ptr, arg ? (int32_t*)outv[1]->ptr : nullptr,
+                                 exe->rt_dtype, exe->rt_batch, exe->rt_n, work, &launches);
+    ctx->launches += launches;
+    if (work) ctx->alloc.put(work, wb);  // stream order keeps it alive for the launches above
+    if (rc) return fail(ctx, JAXCUDA_ECUDA, "sort launch: %s", cudaGetErrorString((cudaError_t)rc));
+    return JAXCUDA_OK;
+  }
+
+  const KernelIR& k = exe->ir;
+  if ((uint32_t)n_inputs != k.nargs || n_outputs != 1)
+    return fail(ctx, JAXCUDA_EINVAL, "kernel takes %u inputs and 1 output, got %d and %d", k.nargs, n_inputs, n_outputs);
+  const size_t out_bytes = (size_t)k.size * dtype_bytes(k.out_dtype());
+  if (outv[0]->bytes < out_bytes)
+    return fail(ctx, JAXCUDA_EINVAL, "output buffer of %zu bytes is smaller than the kernel's %zu", outv[0]->bytes, out_bytes);
+  auto check_len = [&](const std::vector<Node>& nodes) -> int {
+    for (const Node& nd : nodes)
+      if (nd.op == JAXCUDA_OP_GLOBALINDEX && in[nd.arg0]->bytes < (size_t)nd.arg1 * dtype_bytes(nd.dtype))
+        return fail(ctx, JAXCUDA_EINVAL, "input %llu holds %zu bytes, the kernel addresses %zu", (unsigned long long)nd.arg0,
+                    in[nd.arg0]->bytes, (size_t)nd.arg1 * dtype_bytes(nd.dtype));
+    return JAXCUDA_OK;
+  };
+  if (int rc = check_len(k.exp)) return rc;
+  if (int rc = check_len(k.epi)) return rc;
+  for (int i = 0; i < n_inputs; i++)
+    if (in[i]->ptr && in[i]->ptr == outv[0]->ptr)
+      return fail(ctx, JAXCUDA_EINVAL, "output slot %u is also input %d; kernels read inputs through the read-only path", outputs[0], i);
+  if (k.size == 0) return JAXCUDA_OK;
+
+  void* scratch = nullptr;
+  if (exe->plan.scratch_bytes) {
+    cudaError_t e = ctx->alloc.get(exe->plan.scratch_bytes, &scratch);
+    if (e != cudaSuccess) return fail(ctx, JAXCUDA_ENOMEM, "scratch of %zu bytes: %s", exe->plan.scratch_bytes, cudaGetErrorString(e));
+  }
+  int rc = JAXCUDA_OK;
+  if (exe->plan.skeleton == SK_GEMM_TC) {
+    std::vector<void*> inptr(n_inputs);
+    for (int i = 0; i < n_inputs; i++) inptr[i] = in[i]->ptr;
+    std::string err;
+    int nl = launch_gemm_tc(ctx->drv.TensorMapEncodeTiled, (void*)ctx->drv.LaunchKernel, exe->plan, exe->fns, inptr,
+                            outv[0]->ptr, scratch, ctx->stream, err);
+    if (nl < 0) rc = fail(ctx, JAXCUDA_ECUDA, "%s", err.c_str());
+    else ctx->launches += nl;
+  } else {
+    std::vector<void*> ptrs(n_inputs + 2);
+    std::vector<void*> args(n_inputs + 2);
+    for (int i = 0; i < n_inputs; i++) ptrs[i] = in[i]->ptr;
+    ptrs[n_inputs] = outv[0]->ptr;
+    ptrs[n_inputs + 1] = scratch;
+    for (size_t i = 0; i < ptrs.size(); i++) args[i] = &ptrs[i];
+    for (size_t s = 0; s < exe->plan.stages.size() && rc == JAXCUDA_OK; s++) {
+      const Stage& st = exe->plan.stages[s];
+      CUresult cr = ctx->drv.LaunchKernel(exe->fns[s], st.grid[0], st.grid[1], st.grid[2], st.block[0], st.block[1],
+                                          st.block[2], st.smem, (CUstream)ctx->stream, args.data(), nullptr);
+      if (cr != CUDA_SUCCESS) rc = drv_fail(ctx, "cuLaunchKernel", cr);
+      else ctx->launches++;
+    }
+  }
+  if (scratch) ctx->alloc.put(scratch, exe->plan.scratch_bytes);
+  return rc;
+}
+
+int jaxcuda_exe_release(jaxcuda_exe* exe) {
+  if (exe && exe->handles > 0) exe->handles--;
+  return JAXCUDA_OK;
+}
+
+const char* jaxcuda_exe_describe(jaxcuda_exe* exe) { return exe ? exe->describe.c_str() : ""; }
+const char* jaxcuda_exe_source(jaxcuda_exe* exe) { return exe ? exe->plan.source.c_str() : ""; }
+int jaxcuda_exe_cost(jaxcuda_exe* exe, double* algo_bytes, double* algo_flops, int* n_launches) {
+  if (!exe) return JAXCUDA_EINVAL;
+  if (algo_bytes) *algo_bytes = exe->plan.algo_bytes;
+  if (algo_flops) *algo_flops = exe->plan.algo_flops;
+  if (n_launches) *n_launches = exe->kind ? 1 : (int)exe->plan.stages.size();
+  return JAXCUDA_OK;
+}
+
+int jaxcuda_host_alloc(jaxcuda_ctx* ctx, size_t bytes, void** out) {
+  if (!ctx || !out) return JAXCUDA_EINVAL;
+  cudaSetDevice(ctx->device);
+  CUDA_TRY(ctx, cudaHostAlloc(out, bytes ? bytes : 1, cudaHostAllocDefault));
+  return JAXCUDA_OK;
+}
+int jaxcuda_host_free(jaxcuda_ctx* ctx, void* ptr) {
+  if (!ctx) return JAXCUDA_EINVAL;
+  if (ptr) CUDA_TRY(ctx, cudaFreeHost(ptr));
+  return JAXCUDA_OK;
+}
+
+int jaxcuda_sync(jaxcuda_ctx* ctx) {
+  if (!ctx) return JAXCUDA_EINVAL;
+  cudaSetDevice(ctx->device);
+  CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+  return JAXCUDA_OK;
+}
+
+int jaxcuda_event_record(jaxcuda_ctx* ctx, int index) {
+  if (!ctx || index < 0 || index >= 65536) return JAXCUDA_EINVAL;
+  cudaSetDevice(ctx->device);
+  if ((size_t)index >= ctx->events.size()) ctx->events.resize(index + 1, nullptr);
+  if (!ctx->events[index]) CUDA_TRY(ctx, cudaEventCreate(&ctx->events[index]));
+  CUDA_TRY(ctx, cudaEventRecord(ctx->events[index], ctx->stream));
+  return JAXCUDA_OK;
+}
+int jaxcuda_event_elapsed_ms(jaxcuda_ctx* ctx, int a, int b, float* ms) {
+  const int n = ctx ? (int)ctx->events.size() : 0;
+  if (!ctx || a < 0 || a >= n || b < 0 || b >= n || !ctx->events[a] || !ctx->events[b] || !ms) return JAXCUDA_EINVAL;
+  CUDA_TRY(ctx, cudaEventSynchronize(ctx->events[b]));
+  CUDA_TRY(ctx, cudaEventElapsedTime(ms, ctx->events[a], ctx->events[b]));
+  return JAXCUDA_OK;
+}
+uint64_t jaxcuda_launch_count(jaxcuda_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+int jaxcuda_slot_ptr(jaxcuda_ctx* ctx, jaxcuda_slot slot, uint64_t* device_ptr) {
+  SlotRec* s = find_slot(ctx, slot);
+  if (!s) return slot_error(ctx, slot);
+  *device_ptr = (uint64_t)(uintptr_t)s->ptr;
+  return JAXCUDA_OK;
+}
+uint64_t jaxcuda_stream(jaxcuda_ctx* ctx) { return ctx ? (uint64_t)(uintptr_t)ctx->stream : 0; }
+
+// ---- NCCL ------------------------------------------------------------------------------
+// Minimal prototypes of the NCCL C API (nccl.h), bound at run time.
+typedef struct { char internal[128]; } jx_nccl_uid;
+typedef int (*nccl_get_uid_t)(jx_nccl_uid*);
+typedef int (*nccl_init_rank_t)(void**, int, jx_nccl_uid, int);
+typedef int (*nccl_allreduce_t)(const void*, void*, size_t, int, int, void*, cudaStream_t);
+typedef int (*nccl_destroy_t)(void*);
+typedef int (*nccl_group_t)(void);
+typedef const char* (*nccl_errstr_t)(int);
+
+static void* nccl_handle(jaxcuda_ctx* ctx) {
+  static void* h = nullptr;
+  if (!h) {
+    const char* override_ = getenv("JAXCUDA_NCCL_LIB");
+    if (override_) h = dlopen(override_, RTLD_NOW | RTLD_GLOBAL);
+    if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+  }
+  if (!h && ctx) ctx->last_error = std::string("NCCL library not found: ") + dlerror();
+  return h;
+}
+
+int jaxcuda_comm_unique_id(void* id128) {
+  void* h = nccl_handle(nullptr);
+  if (!h || !id128) return JAXCUDA_ECUDA;
+  auto fn = (nccl_get_uid_t)dlsym(h, "ncclGetUniqueId");
+  if (!fn) return JAXCUDA_ECUDA;
+  return fn((jx_nccl_uid*)id128) == 0 ? JAXCUDA_OK : JAXCUDA_ECUDA;
+}
+
+int jaxcuda_comm_init(jaxcuda_ctx* ctx, int rank, int nranks, const void* id128) {
+  if (!ctx || !id128 || nranks < 1 || rank < 0 || rank >= nranks) return JAXCUDA_EINVAL;
+  void* h = nccl_handle(ctx);
+  if (!h) return JAXCUDA_ECUDA;
+  auto init = (nccl_init_rank_t)dlsym(h, "ncclCommInitRank");
+  auto errstr = (nccl_errstr_t)dlsym(h, "ncclGetErrorString");
+  if (!init) return fail(ctx, JAXCUDA_ECUDA, "ncclCommInitRank not found");
+  cudaSetDevice(ctx->device);
+  jx_nccl_uid uid;
+  memcpy(&uid, id128, sizeof uid);
+  int r = init(&ctx->comm, nranks, uid, rank);
+  if (r != 0) return fail(ctx, JAXCUDA_ECUDA, "ncclCommInitRank: %s", errstr ? errstr(r) : "error");
+  ctx->nccl_lib = h;
+  ctx->nranks = nranks;
+  return JAXCUDA_OK;
+}
+
+int jaxcuda_allreduce_sum_f32(jaxcuda_ctx* ctx, const jaxcuda_slot* slots, int n) {
+  if (!ctx || (n > 0 && !slots)) return JAXCUDA_EINVAL;
+  if (!ctx->comm) {
+    if (ctx->nranks == 1) return JAXCUDA_OK;  // a single rank: the sum is the input
+    return fail(ctx, JAXCUDA_EINVAL, "communicator not initialised");
+  }
+  auto allreduce = (nccl_allreduce_t)dlsym(ctx->nccl_lib, "ncclAllReduce");
+  auto gstart = (nccl_group_t)dlsym(ctx->nccl_lib, "ncclGroupStart");
+  auto gend = (nccl_group_t)dlsym(ctx->nccl_lib, "ncclGroupEnd");
+  auto errstr = (nccl_errstr_t)dlsym(ctx->nccl_lib, "ncclGetErrorString");
+  if (!allreduce || !gstart || !gend) return fail(ctx, JAXCUDA_ECUDA, "NCCL symbols missing");
+  cudaSetDevice(ctx->device);
+  for (int i = 0; i < n; i++) if (!find_slot(ctx, slots[i])) return slot_error(ctx, slots[i]);
+  gstart();
+  int r = 0;
+  for (int i = 0; i < n && r == 0; i++) {
+    SlotRec* s = find_slot(ctx, slots[i]);
+    if (s->bytes) r = allreduce(s->ptr, s->ptr, s->bytes / 4, /*ncclFloat32*/ 7, /*ncclSum*/ 0, ctx->comm, ctx->stream);
+  }
+  int r2 = gend();
+  if (r == 0) r = r2;
+  if (r != 0) return fail(ctx, JAXCUDA_ECUDA, "ncclAllReduce: %s", errstr ? errstr(r) : "error");
+  return JAXCUDA_OK;
+}
+
+int jaxcuda_comm_destroy(jaxcuda_ctx* ctx) {
+  if (!ctx || !ctx->comm) return JAXCUDA_OK;
+  auto destroy = (nccl_destroy_t)dlsym(ctx->nccl_lib, "ncclCommDestroy");
+  if (destroy) destroy(ctx->comm);
+  ctx->comm = nullptr;
+  return JAXCUDA_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,225 @@
+"""Kernel sequences that `jit` hands to a backend for the benchmarked programs.
+
+The reference's tracing frontend is device-independent and stays in TypeScript; what the
+backend sees per program is a static list of malloc / execute / free steps
+(`JitProgram`, src/frontend/jit.ts:111-162).  This module builds those lists directly,
+kernel by kernel, in the form the frontend's rules produce them:
+
+  * `np.dot` / `lax.dot`: Mul of two loads under an Add reduction
+    (`jitRules[Dot]`, src/frontend/jit.ts:639-648; operand views of src/library/lax.ts:87-128);
+  * `nn.softmax` = max, exp(x - max) materialised, sum, mul by reciprocal: four kernels,
+    because the keepdims reshape blocks epilogue fusion and exp has two consumers
+    (src/library/nn.ts:291-301; src/frontend/jit.ts:833-885, :1015-1028);
+  * `nn.logsumexp` (nn.ts:332-345) and `np.argmax` (src/library/numpy.ts:533-556).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Sequence
+
+import numpy as np
+
+from .alu import AluExp, AluOp, AluVar, DType, Kernel, Reduction, byte_width, np_dtype
+
+F32, I32, F16 = DType.Float32, DType.Int32, DType.Float16
+_g, _r = AluVar.gidx, AluVar.ridx
+
+
+def _i(v: int) -> AluExp:
+    return AluExp.i32(v)
+
+
+# ---- single kernels ---------------------------------------------------------------------
+
+def row_reduce_kernel(rows: int, cols: int, op: AluOp, dtype: DType = F32) -> Kernel:
+    """K1 / K3: reduce the last axis of a contiguous [rows, cols] array."""
+    x = AluExp.global_index(dtype, 0, rows * cols, AluExp.add(AluExp.mul(_g, _i(cols)), _r))
+    return Kernel(1, rows, x, Reduction(dtype, op, cols))
+
+
+def softmax_exp_kernel(rows: int, cols: int) -> Kernel:
+    """K2: exp(x + (0 - max[row])), materialised."""
+    x = AluExp.global_index(F32, 0, rows * cols, _g)
+    m = AluExp.global_index(F32, 1, rows, AluExp.idiv(_g, _i(cols)))
+    return Kernel(2, rows * cols, AluExp.exp(AluExp.add(x, AluExp.sub(AluExp.f32(0), m))))
+
+
+def softmax_scale_kernel(rows: int, cols: int) -> Kernel:
+    """K4: u * (1 / sum[row])."""
+    u = AluExp.global_index(F32, 0, rows * cols, _g)
+    s = AluExp.global_index(F32, 1, rows, AluExp.idiv(_g, _i(cols)))
+    return Kernel(2, rows * cols, AluExp.mul(u, AluExp.reciprocal(s)))
+
+
+def lse_sum_kernel(rows: int, cols: int) -> Kernel:
+    """K2': row sum of exp(x - max) with the exponential fused as the reduction body."""
+    x = AluExp.global_index(F32, 0, rows * cols, AluExp.add(AluExp.mul(_g, _i(cols)), _r))
+    m = AluExp.global_index(F32, 1, rows, _g)
+    return Kernel(2, rows, AluExp.exp(AluExp.add(x, AluExp.sub(AluExp.f32(0), m))), Reduction(F32, AluOp.Add, cols))
+
+
+def lse_finish_kernel(rows: int) -> Kernel:
+    """K3': max + log(sum)."""
+    s = AluExp.global_index(F32, 0, rows, _g)
+    m = AluExp.global_index(F32, 1, rows, _g)
+    return Kernel(2, rows, AluExp.add(m, AluExp.log(s)))
+
+
+def argmax_index_kernel(rows: int, cols: int) -> Kernel:
+    """K5: int32 row max of cast(x == max) * (n - ridx) with epilogue n - acc.
+
+    `G_2` is the closed-over constant arange(n, 0, -1) (numpy.ts:533-556); ties resolve to
+    the first index because the largest weight wins.
+    """
+    x = AluExp.global_index(F32, 0, rows * cols, AluExp.add(AluExp.mul(_g, _i(cols)), _r))
+    m = AluExp.global_index(F32, 1, rows, _g)
+    w = AluExp.global_index(I32, 2, cols, _r)
+    eq = AluExp.cmpne(x, m).not_()
+    body = AluExp.mul(AluExp.cast(I32, eq), w)
+    epilogue = AluExp.add(_i(cols), AluExp.sub(_i(0), AluVar.acc(I32)))
+    return Kernel(3, rows, body, Reduction(I32, AluOp.Max, cols, epilogue))
+
+
+def dot_kernel(M: int, N: int, K: int, dtype: DType = F32, *, a_layout: str = "mk", b_layout: str = "kn",
+               batch: int = 1, bias: bool = False, relu: bool = False, swap: bool = False) -> Kernel:
+    """C[b, m, n] = sum_k A[b, m, k] * B[b, k, n], optionally + bias[n] and relu, as one Kernel.
+
+    Layouts name the memory order of each operand: "mk" is row-major A, "km" its transpose;
+    "kn" is row-major B (the `np.dot` case: read with stride N along k), "nk" its transpose.
+    `swap` writes the product as B*A (operand order of src/backend/backend.test.ts:447-458).
+    """
+    m = AluExp.mod(AluExp.idiv(_g, _i(N)), _i(M))
+    n = AluExp.mod(_g, _i(N))
+    b = AluExp.idiv(_g, _i(M * N))
+    a_ix = AluExp.add(AluExp.mul(m, _i(K)), _r) if a_layout == "mk" else AluExp.add(m, AluExp.mul(_r, _i(M)))
+    b_ix = AluExp.add(n, AluExp.mul(_r, _i(N))) if b_layout == "kn" else AluExp.add(AluExp.mul(n, _i(K)), _r)
+    if batch > 1:
+        a_ix = AluExp.add(AluExp.mul(b, _i(M * K)), a_ix)
+        b_ix = AluExp.add(AluExp.mul(b, _i(K * N)), b_ix)
+    la = AluExp.global_index(dtype, 0, batch * M * K, a_ix)
+    lb = AluExp.global_index(dtype, 1, batch * K * N, b_ix)
+    body = AluExp.mul(lb, la) if swap else AluExp.mul(la, lb)
+    red = Reduction(dtype, AluOp.Add, K)
+    nargs = 2
+    if bias or relu:
+        acc = red.epilogue  # already Cast<f16>(acc:f32) for float16
+        if bias:
+            acc = AluExp.add(acc, AluExp.global_index(dtype, 2, N, AluExp.mod(_g, _i(N))))
+            nargs = 3
+        if relu:
+            acc = AluExp.max(acc, AluExp.const(dtype, 0))
+        red.epilogue = acc
+    return Kernel(nargs, batch * M * N, body, red)
+
+
+def matvec_kernel(rows: int, cols: int, dtype: DType = F16, *, orientation: str = "xW") -> Kernel:
+    """"xW": y[n] = sum_k x[k] W[k, n] for W[rows=K, cols=N] (`np.dot(x, W)`);
+    "Wx": y[m] = sum_k W[m, k] x[k] for W[rows=M, cols=K] (`np.dot(W, x)`)."""
+    if orientation == "xW":
+        x = AluExp.global_index(dtype, 0, rows, _r)
+        w = AluExp.global_index(dtype, 1, rows * cols, AluExp.add(_g, AluExp.mul(_r, _i(cols))))
+        return Kernel(2, cols, AluExp.mul(x, w), Reduction(dtype, AluOp.Add, rows))
+    w = AluExp.global_index(dtype, 0, rows * cols, AluExp.add(AluExp.mul(_g, _i(cols)), _r))
+    x = AluExp.global_index(dtype, 1, cols, _r)
+    return Kernel(2, rows, AluExp.mul(w, x), Reduction(dtype, AluOp.Add, cols))
+
+
+# ---- step lists ---------------------------------------------------------------------------
+
+@dataclass
+class Step:
+    kind: str                       # "malloc" | "execute" | "free"
+    name: str = ""                  # malloc/free: buffer name; execute: output buffer name
+    nbytes: int = 0
+    kernel: Kernel | None = None
+    inputs: Sequence[str] = ()
+
+
+@dataclass
+class JitProgram:
+    """Static step list replayed per call (src/frontend/jit.ts:111-162)."""
+    inputs: Sequence[str]
+    outputs: Sequence[str]
+    steps: list = field(default_factory=list)
+    _exes: dict = field(default_factory=dict, repr=False)
+
+    def malloc(self, name: str, nbytes: int) -> None:
+        self.steps.append(Step("malloc", name, nbytes))
+
+    def run(self, out: str, kernel: Kernel, inputs: Sequence[str]) -> None:
+        self.steps.append(Step("malloc", out, kernel.bytes))
+        self.steps.append(Step("execute", out, 0, kernel, tuple(inputs)))
+
+    def free(self, name: str) -> None:
+        self.steps.append(Step("free", name))
+
+    def kernels(self):
+        return [s.kernel for s in self.steps if s.kind == "execute"]
+
+    def prepare(self, backend) -> None:
+        for s in self.steps:
+            if s.kind == "execute" and id(s) not in self._exes:
+                self._exes[id(s)] = backend.prepare_kernel_sync(s.kernel)
+
+    def execute(self, backend, slots: Sequence[int]) -> list:
+        """Replays the steps; `slots` are the input slots (not consumed).  Returns output slots
+        with reference count 1, owned by the caller."""
+        self.prepare(backend)
+        env = dict(zip(self.inputs, slots))
+        owned = set()
+        for s in self.steps:
+            if s.kind == "malloc":
+                env[s.name] = backend.malloc(s.nbytes)
+                owned.add(s.name)
+            elif s.kind == "execute":
+                backend.dispatch(self._exes[id(s)], [env[n] for n in s.inputs], [env[s.name]])
+            elif s.kind == "free" and s.name in owned:
+                backend.dec_ref(env.pop(s.name))
+                owned.discard(s.name)
+        outs = [env[n] for n in self.outputs]
+        for n in owned - set(self.outputs):
+            backend.dec_ref(env[n])
+        return outs
+
+    def cost(self, backend):
+        """Sum of algorithmic bytes, flops and launches over the execute steps."""
+        self.prepare(backend)
+        tot = [0.0, 0.0, 0]
+        for s in self.steps:
+            if s.kind == "execute":
+                b, f, n = self._exes[id(s)].cost()
+                tot[0] += b
+                tot[1] += f
+                tot[2] += n
+        return tuple(tot)
+
+
+def softmax_lse_argmax_program(rows: int, cols: int) -> JitProgram:
+    """One jit computing softmax, logsumexp and argmax of x[rows, cols] over the last axis.
+
+    `Jaxpr.simplify` does no common-subexpression elimination (src/frontend/jaxpr.ts:252-257),
+    so the row max is computed three times, once per consumer; inputs: x and the constant
+    arange(cols, 0, -1); outputs: softmax f32[rows, cols], lse f32[rows], argmax i32[rows].
+    """
+    p = JitProgram(inputs=["x", "iota"], outputs=["softmax", "lse", "argmax"])
+    k1 = row_reduce_kernel(rows, cols, AluOp.Max)
+    p.run("m1", k1, ["x"])
+    p.run("u", softmax_exp_kernel(rows, cols), ["x", "m1"])
+    p.free("m1")
+    p.run("s", row_reduce_kernel(rows, cols, AluOp.Add), ["u"])
+    p.run("softmax", softmax_scale_kernel(rows, cols), ["u", "s"])
+    p.free("u")
+    p.free("s")
+    p.run("m2", k1, ["x"])
+    p.run("s2", lse_sum_kernel(rows, cols), ["x", "m2"])
+    p.run("lse", lse_finish_kernel(rows), ["s2", "m2"])
+    p.free("s2")
+    p.free("m2")
+    p.run("m3", k1, ["x"])
+    p.run("argmax", argmax_index_kernel(rows, cols), ["x", "m3", "iota"])
+    p.free("m3")
+    return p
+
+
+def argmax_iota(cols: int) -> np.ndarray:
+    return np.arange(cols, 0, -1, dtype=np.int32)

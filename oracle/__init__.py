@@ -1,0 +1,115 @@
+"""ctypes binding of the CPU oracle (oracle/oracle.cpp).  TEST INFRASTRUCTURE ONLY.
+
+Imported by tests/, by the smoke check and by the bench's CPU-baseline legs; never
+by the product package.  `build()` compiles oracle.cpp with g++ into
+oracle/liboracle.so (kept out of git, shipped with the tree).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+_HERE = Path(__file__).resolve().parent
+_SRC = _HERE / "oracle.cpp"
+_LIB = _HERE / "liboracle.so"
+_lib = None
+
+MODE_AUTO, MODE_WASM, MODE_CPU = 0, 1, 2
+
+
+def build(force: bool = False) -> Path:
+    """g++ -O3 -ffp-contract=off: each f32 operation rounds on its own, as Wasm's do."""
+    deps = [_SRC, _HERE.parent / "include" / "jaxcuda_ir.h"]
+    if not force and _LIB.exists() and all(_LIB.stat().st_mtime >= d.stat().st_mtime for d in deps if d.exists()):
+        return _LIB
+    cmd = ["g++", "-O3", "-march=x86-64-v3", "-ffp-contract=off", "-fno-fast-math", "-fopenmp",
+           "-std=c++17", "-shared", "-fPIC", "-o", str(_LIB), str(_SRC)]
+    subprocess.run(cmd, check=True)
+    return _LIB
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        build()
+        L = ctypes.CDLL(str(_LIB))
+        L.oracle_last_error.restype = ctypes.c_char_p
+        L.oracle_kernel.argtypes = [ctypes.c_char_p, ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p),
+                                    ctypes.c_void_p, ctypes.c_uint64, ctypes.c_uint64,
+                                    ctypes.c_int, ctypes.c_int, ctypes.c_int]
+        L.oracle_sort.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint64, ctypes.c_uint64]
+        L.oracle_argsort.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                     ctypes.c_uint64, ctypes.c_uint64]
+        L.oracle_wasm_unary.argtypes = [ctypes.c_int, ctypes.c_float]
+        L.oracle_wasm_unary.restype = ctypes.c_float
+        L.oracle_threefry2x32.argtypes = [ctypes.c_uint32] * 4 + [ctypes.POINTER(ctypes.c_uint32)]
+        L.oracle_double_to_half.argtypes = [ctypes.c_double]
+        L.oracle_double_to_half.restype = ctypes.c_uint16
+        L.oracle_half_to_double.argtypes = [ctypes.c_uint16]
+        L.oracle_half_to_double.restype = ctypes.c_double
+        _lib = L
+    return _lib
+
+
+def default_threads() -> int:
+    return max(1, len(os.sched_getaffinity(0)))
+
+
+def run_kernel(kernel, args, *, begin: int = 0, end: int | None = None, mode: int = MODE_AUTO,
+               fma: bool = False, threads: int | None = None, out: np.ndarray | None = None) -> np.ndarray:
+    """Evaluate `kernel` (a jax_js_b200.alu.Kernel) over outputs [begin, end).
+
+    `args` are numpy arrays, one per kernel argument.  Returns the whole output
+    array (elements outside [begin, end) are zero unless `out` is passed in).
+    """
+    from jax_js_b200.alu import np_dtype  # the IR definition is shared; no device code is touched
+
+    L = lib()
+    image = kernel.serialize()
+    arrays = [np.ascontiguousarray(a) for a in args]
+    if len(arrays) != kernel.nargs:
+        raise ValueError(f"kernel takes {kernel.nargs} arguments, got {len(arrays)}")
+    ptrs = (ctypes.c_void_p * max(1, len(arrays)))(*[a.ctypes.data for a in arrays])
+    if out is None:
+        out = np.zeros(kernel.size, dtype=np_dtype(kernel.dtype))
+    end = kernel.size if end is None else end
+    rc = L.oracle_kernel(image, len(image), ptrs, out.ctypes.data, begin, end, mode, int(fma),
+                         threads if threads is not None else default_threads())
+    if rc:
+        raise RuntimeError(L.oracle_last_error().decode())
+    return out
+
+
+def sort(x: np.ndarray, dtype_code: int) -> np.ndarray:
+    x = np.ascontiguousarray(x)
+    n = x.shape[-1] if x.ndim else 0
+    y = np.empty_like(x)
+    if x.size:
+        if lib().oracle_sort(dtype_code, x.ctypes.data, y.ctypes.data, x.size // n, n):
+            raise RuntimeError(lib().oracle_last_error().decode())
+    return y
+
+
+def argsort(x: np.ndarray, dtype_code: int):
+    x = np.ascontiguousarray(x)
+    n = x.shape[-1] if x.ndim else 0
+    y = np.empty_like(x)
+    yi = np.empty(x.shape, dtype=np.int32)
+    if x.size:
+        if lib().oracle_argsort(dtype_code, x.ctypes.data, y.ctypes.data, yi.ctypes.data, x.size // n, n):
+            raise RuntimeError(lib().oracle_last_error().decode())
+    return y, yi
+
+
+def wasm_unary(op: int, x: float) -> float:
+    return float(lib().oracle_wasm_unary(int(op), float(x)))
+
+
+def threefry2x32(k0, k1, c0, c1):
+    out = (ctypes.c_uint32 * 2)()
+    lib().oracle_threefry2x32(k0, k1, c0, c1, out)
+    return int(out[0]), int(out[1])

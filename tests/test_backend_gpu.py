@@ -1,0 +1,186 @@
+"""The reference's backend contract tests (src/backend/backend.test.ts), run against the cuda
+backend through the C ABI.  Expected arrays are the ones that file asserts."""
+import numpy as np
+import pytest
+
+from jax_js_b200 import (AluExp, AluOp, AluVar, DType, Kernel, Reduction, ShapeTracker, accessor_global,
+                         global_view, unravel_alu)
+from jax_js_b200.backend import SlotError, UnsupportedRoutineError
+from jax_js_b200.routine import Routine, Routines, RoutineType
+
+pytestmark = pytest.mark.gpu
+F32, U32 = DType.Float32, DType.Uint32
+g, r = AluVar.gidx, AluVar.ridx
+
+
+def f32(*v):
+    return np.array(v, dtype=np.float32)
+
+
+def test_can_run_simple_operations(backend):
+    # backend.test.ts:37-85
+    shape = ShapeTracker.from_shape([3])
+    a, b, c = backend.put(f32(1, 2, 3)), backend.put(f32(4, 5, 6)), backend.malloc(12)
+    try:
+        arg1 = accessor_global(F32, 0, shape, [g])
+        arg2 = accessor_global(F32, 1, shape.flip([True]), [g])
+        backend.dispatch(backend.prepare_kernel(Kernel(2, 3, AluExp.mul(arg1, arg2))), [a, b], [c])
+        assert backend.get(c, F32).tolist() == [6, 10, 12]
+        backend.dispatch(backend.prepare_kernel(Kernel(2, 3, AluExp.add(arg1, arg2))), [a, b], [c])
+        assert backend.get(c, F32).tolist() == [7, 7, 7]
+    finally:
+        for s in (a, b, c):
+            backend.dec_ref(s)
+
+
+def test_can_create_array_from_index(backend):
+    # backend.test.ts:190-203
+    a = backend.malloc(200 * 4)
+    try:
+        backend.dispatch(backend.prepare_kernel(Kernel(0, 200, AluExp.cast(F32, g))), [], [a])
+        assert backend.get(a, F32).tolist() == list(range(200))
+    finally:
+        backend.dec_ref(a)
+
+
+def test_reads_a_buffer_with_byte_ranges(backend):
+    # backend.test.ts:219-246
+    arr = f32(1, 1, 2, 3, 5, 7)
+    a = backend.put(arr)
+    try:
+        assert backend.read_sync(a).view(np.float32).tolist() == arr.tolist()
+        assert backend.read_sync(a, 3 * 4, 2 * 4).view(np.float32).tolist() == [3, 5]
+        assert backend.read_sync(a, 0, 0).size == 0  # the barrier form, src/frontend/array.ts:827
+    finally:
+        backend.dec_ref(a)
+
+
+def test_performs_reduction_with_fused_epilogue(backend):
+    # backend.test.ts:248-286
+    a, out = backend.put(f32(1, 1, 2, 3, 5, 7)), backend.malloc(12)
+    try:
+        exp = global_view(F32, 0, ShapeTracker.from_shape([3, 2]), [g, r])
+        backend.dispatch(backend.prepare_kernel_sync(Kernel(1, 3, exp, Reduction(F32, AluOp.Add, 2))), [a], [out])
+        assert backend.get(out, F32).tolist() == [2, 5, 12]
+        red = Reduction(F32, AluOp.Add, 2, AluExp.add(AluVar.acc(F32), AluExp.f32(1)))
+        backend.dispatch(backend.prepare_kernel_sync(Kernel(1, 3, exp, red)), [a], [out])
+        assert backend.get(out, F32).tolist() == [3, 6, 13]
+    finally:
+        backend.dec_ref(a)
+        backend.dec_ref(out)
+
+
+def test_bitwise_operations(backend):
+    # backend.test.ts:288-373
+    shape = ShapeTracker.from_shape([4])
+    a = backend.put(np.array([0xFF00FF00, 0x0F0F0F0F, 0xAAAAAAAA, 7], np.uint32))
+    b = backend.put(np.array([0x00FF00FF, 0xF0F0F0F0, 0x55555555, 3], np.uint32))
+    sa, sb = backend.put(np.ones(4, np.uint32)), backend.put(np.array([0, 1, 8, 16], np.uint32))
+    ra = backend.put(np.array([256, 65536, 0xFFFF0000, 8], np.uint32))
+    c = backend.malloc(16)
+    x, y = accessor_global(U32, 0, shape, [g]), accessor_global(U32, 1, shape, [g])
+    try:
+        def run(e, ins):
+            backend.dispatch(backend.prepare_kernel(Kernel(2, 4, e)), ins, [c])
+            return backend.get(c, U32).tolist()
+        assert run(AluExp.bit_combine(x, y, "and"), [a, b]) == [0, 0, 0, 3]
+        assert run(AluExp.bit_combine(x, y, "or"), [a, b]) == [0xFFFFFFFF] * 3 + [7]
+        assert run(AluExp.bit_combine(x, y, "xor"), [a, b]) == [0xFFFFFFFF] * 3 + [4]
+        assert run(AluExp.bit_shift(x, y, "shl"), [sa, sb]) == [1, 2, 256, 65536]
+        assert run(AluExp.bit_shift(x, y, "shr"), [ra, sb]) == [256, 32768, 0x00FFFF00, 0]
+    finally:
+        for s in (a, b, sa, sb, ra, c):
+            backend.dec_ref(s)
+
+
+def _matmul_kernel(M, N, K, gid_b, swapped=False):
+    stA = ShapeTracker.from_shape([M, K]).reshape([M, 1, K]).expand([M, N, K])
+    stB = ShapeTracker.from_shape([K, N]).permute([1, 0]).reshape([1, N, K]).expand([M, N, K])
+    idx = [*unravel_alu([M, N], g), r]
+    la, lb = global_view(F32, 0, stA, idx), global_view(F32, gid_b, stB, idx)
+    return Kernel(gid_b + 1, M * N, AluExp.mul(lb, la) if swapped else AluExp.mul(la, lb), Reduction(F32, AluOp.Add, K))
+
+
+def test_performs_64x64_matmul(backend):
+    # backend.test.ts:375-409: the same slot feeds both operands
+    n = 64
+    a, b = backend.put(np.ones(n * n, np.float32)), backend.malloc(n * n * 4)
+    try:
+        backend.dispatch(backend.prepare_kernel(_matmul_kernel(n, n, n, 0)), [a], [b])
+        np.testing.assert_allclose(backend.get(b, F32), n)
+    finally:
+        backend.dec_ref(a)
+        backend.dec_ref(b)
+
+
+def test_performs_non_square_matmul_both_operand_orders(backend):
+    # backend.test.ts:411-464
+    M, N, K = 16, 48, 24
+    a, b, c = backend.put(np.ones(M * K, np.float32)), backend.put(np.ones(K * N, np.float32)), backend.malloc(M * N * 4)
+    try:
+        for swapped in (False, True):
+            backend.dispatch(backend.prepare_kernel(_matmul_kernel(M, N, K, 1, swapped)), [a, b], [c])
+            np.testing.assert_allclose(backend.get(c, F32), K)
+    finally:
+        for s in (a, b, c):
+            backend.dec_ref(s)
+
+
+def test_keeps_row_dependent_contiguous_reduction_loads_distinct(backend):
+    # backend.test.ts:466-507
+    M, N, K = 32, 128, 5
+    x = np.fromfunction(lambda m, k, n: m * 1000 + k * 10 + n, (M, K, N)).astype(np.float32)
+    a, out = backend.put(x), backend.malloc(M * N * 4)
+    try:
+        mm, nn = unravel_alu([M, N], g)
+        exp = global_view(F32, 0, ShapeTracker.from_shape([M, K, N]), [mm, r, nn])
+        backend.dispatch(backend.prepare_kernel(Kernel(1, M * N, exp, Reduction(F32, AluOp.Add, K))), [a], [out])
+        want = K * (np.arange(M)[:, None] * 1000 + np.arange(N)[None, :]) + 10 * K * (K - 1) / 2
+        np.testing.assert_allclose(backend.get(out, F32, (M, N)), want, rtol=1e-6)
+    finally:
+        backend.dec_ref(a)
+        backend.dec_ref(out)
+
+
+def test_slot_lifetime_errors(backend):
+    # src/backend.ts:176-180: decRef of a freed slot throws SlotError; refcounts keep a slot alive
+    s = backend.malloc(16)
+    backend.inc_ref(s)
+    backend.dec_ref(s)
+    assert backend.read_sync(s).size == 16
+    backend.dec_ref(s)
+    with pytest.raises(SlotError):
+        backend.dec_ref(s)
+    with pytest.raises(SlotError):
+        backend.read_sync(s)
+
+
+def test_malloc_edge_cases(backend):
+    # size 0 is legal (src/backend/webgpu.ts:84-86); initialData must match (src/backend/cpu.ts:21-24)
+    z = backend.malloc(0)
+    assert backend.read_sync(z).size == 0
+    backend.dec_ref(z)
+    with pytest.raises(ValueError):
+        backend.malloc(8, np.zeros(3, np.uint8))
+
+
+def test_unsupported_routine_raises(backend):
+    # src/backend.ts:236-240
+    rt = Routine(Routines.Cholesky, RoutineType([[2, 2]], [F32], [[2, 2]], [F32]))
+    with pytest.raises(UnsupportedRoutineError, match="routine 'Cholesky' is not supported in cuda backend"):
+        backend.prepare_routine(rt)
+
+
+def test_dispatch_order_is_execution_order(backend):
+    # src/backend.ts:203-210: a chain of dependent kernels on one slot, read once at the end
+    n = 1 << 16
+    a, b = backend.put(np.zeros(n, np.float32)), backend.malloc(n * 4)
+    inc = backend.prepare_kernel(Kernel(1, n, AluExp.add(AluExp.global_index(F32, 0, n, g), AluExp.f32(1))))
+    try:
+        for _ in range(25):
+            backend.dispatch(inc, [a], [b])
+            backend.dispatch(inc, [b], [a])
+        assert (backend.get(a, F32) == 50).all()
+    finally:
+        backend.dec_ref(a)
+        backend.dec_ref(b)

@@ -1,0 +1,125 @@
+"""CPU-side checks of the host logic: the wire format, the planner's skeleton choice, NVRTC
+compilation of every skeleton for sm_100a (no GPU needed), and the C ABI's exported symbols."""
+import ctypes
+import re
+import struct
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from jax_js_b200 import AluExp, AluOp, AluVar, DType, Kernel, Reduction, ShapeTracker, accessor_global
+from jax_js_b200 import programs as P
+from jax_js_b200.alu import NODE_WORDS, WIRE_MAGIC
+from jax_js_b200.backend import (SYMBOLS, CudaBackend, CudaError, UnsupportedOpError, check_kernel)
+
+ROOT = Path(__file__).resolve().parent.parent
+F32, I32, F16 = DType.Float32, DType.Int32, DType.Float16
+g, r = AluVar.gidx, AluVar.ridx
+
+
+def test_every_declared_symbol_is_exported(lib):
+    header = (ROOT / "include" / "jaxcuda.h").read_text()
+    declared = set(re.findall(r"\b(jaxcuda_[a-z0-9_]+)\s*\(", header))
+    declared -= {"jaxcuda_status"}
+    assert declared == set(SYMBOLS), declared ^ set(SYMBOLS)
+    for name in declared:
+        assert getattr(lib, name) is not None
+
+
+def test_create_fails_loudly_without_a_gpu(lib):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    with pytest.raises(CudaError, match="no CPU fallback"):
+        CudaBackend(0)
+
+
+def test_wire_image_layout():
+    k = P.row_reduce_kernel(3, 2, AluOp.Add)
+    img = k.serialize()
+    head = struct.unpack("<10I", img[:40])
+    assert head[0] == WIRE_MAGIC and head[1] == 1 and head[2] == 3 and head[4] == 1
+    assert head[5] == int(F32) and head[6] == int(AluOp.Add) and head[7] == 2
+    assert len(img) == 40 + (head[8] + head[9]) * NODE_WORDS * 4
+    assert k.fingerprint() == P.row_reduce_kernel(3, 2, AluOp.Add).fingerprint()
+    assert k.fingerprint() != P.row_reduce_kernel(3, 2, AluOp.Max).fingerprint()
+
+
+def test_f16_add_reduction_accumulates_in_f32():
+    # src/alu.ts:1560-1568
+    red = Reduction(F16, AluOp.Add, 8)
+    assert red.dtype == F32 and red.epilogue.op == AluOp.Cast and red.epilogue.dtype == F16
+    assert Reduction(F16, AluOp.Max, 8).dtype == F16
+
+
+def test_bad_images_are_rejected(lib):
+    def check(img):
+        msg = ctypes.create_string_buffer(4096)
+        return lib.jaxcuda_check_kernel(img, len(img), 148, -1, 0, None, 0, msg, len(msg)), msg.value.decode()
+    good = P.lse_finish_kernel(16).serialize()
+    assert check(good)[0] == 0
+    assert check(good[:-4])[0] == 3
+    assert check(b"\0\0\0\0" + good[4:])[0] == 3
+    words = list(struct.unpack(f"<{len(good) // 4}I", good))
+    words[10 + 3] = 99  # first node: operand index beyond itself
+    words[10 + 2] = 1
+    assert check(struct.pack(f"<{len(words)}I", *words))[0] == 3
+
+
+CASES = {
+    "k1 row max": (P.row_reduce_kernel(8192, 4096, AluOp.Max), "reduce-row TPR=256 V=4"),
+    "k2 exp": (P.softmax_exp_kernel(8192, 4096), "elementwise V=4"),
+    "k4 scale": (P.softmax_scale_kernel(8192, 4096), "elementwise V=4"),
+    "k2' fused sum": (P.lse_sum_kernel(8192, 4096), "reduce-row TPR=256 V=4"),
+    "k3' tiny": (P.lse_finish_kernel(8192), "elementwise"),
+    "k5 argmax": (P.argmax_index_kernel(8192, 4096), "reduce-row TPR=256 V=4"),
+    "matvec xW": (P.matvec_kernel(4096, 11008, F16, orientation="xW"), "reduce-col V=8"),
+    "matvec Wx": (P.matvec_kernel(11008, 4096, F16, orientation="Wx"), "reduce-row TPR=256 V=8"),
+    "dot f32": (P.dot_kernel(1024, 1024, 1024), "gemm"),
+    "dot f16": (P.dot_kernel(4096, 4096, 4096, F16), "gemm"),
+    "dot TN": (P.dot_kernel(784, 2048, 8192, a_layout="km"), "gemm"),
+    "dot NT": (P.dot_kernel(8192, 784, 2048, b_layout="nk"), "gemm"),
+    "dot bias relu": (P.dot_kernel(256, 1024, 784, bias=True, relu=True), "gemm"),
+    "dot batched": (P.dot_kernel(64, 48, 32, batch=5), "gemm-ffma 5x64x48x32"),
+    "dot tiny": (P.dot_kernel(16, 48, 24), "reduce-"),
+    "short rows": (P.row_reduce_kernel(65536, 10, AluOp.Max), "reduce-col V=1"),
+    "mid rows": (P.row_reduce_kernel(4096, 200, AluOp.Add), "reduce-row TPR=32"),
+    "scalar sum": (P.row_reduce_kernel(1, 1 << 24, AluOp.Add), "splits="),
+}
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_planner_choice_and_nvrtc_compile(lib, name):
+    kernel, expect = CASES[name]
+    describe, source = check_kernel(kernel, compile=True)
+    assert expect in describe, describe
+    assert "jx_kernel" in source
+
+
+def test_vector_loads_only_where_provably_aligned(lib):
+    n = 4096
+    aligned = Kernel(1, n, AluExp.global_index(F32, 0, n, g))
+    shifted = Kernel(1, n, AluExp.global_index(F32, 0, n + 1, AluExp.add(g, AluExp.i32(1))))
+    flipped = Kernel(1, n, accessor_global(F32, 0, ShapeTracker.from_shape([n]).flip([True]), [g]))
+    assert "jx_load(pk" in check_kernel(aligned, compile=False)[1]
+    assert "jx_load(pk" not in check_kernel(shifted, compile=False)[1]
+    assert "jx_load(pk" not in check_kernel(flipped, compile=False)[1]
+    bcast = check_kernel(P.softmax_scale_kernel(64, 256), compile=False)[1]
+    assert "bc" in bcast  # the per-row scalar is fetched once per 128-bit run
+
+
+def test_unsupported_combination_uses_reference_wording(lib):
+    bad = Kernel(0, 4, AluExp(AluOp.Sub, DType.Bool, [AluExp.bool(True), AluExp.bool(False)]))
+    with pytest.raises(UnsupportedOpError, match=r"Sub<bool> not supported in cuda backend"):
+        check_kernel(bad)
+
+
+def test_shape_tracker_views_lower_to_expected_indices():
+    st = ShapeTracker.from_shape([4, 6]).permute([1, 0])
+    ix, valid = st.to_alu_exp([AluExp.i32(5), AluExp.i32(3)])
+    assert ix.arg == 3 * 6 + 5 and valid.arg == 1
+    padded = ShapeTracker.from_shape([3]).pad([(1, 2)])
+    assert padded.shape == (6,) and padded.data_range() == (0, 3)
+    e = accessor_global(F32, 0, padded, [g])
+    assert e.op == AluOp.Where

@@ -1,0 +1,310 @@
+"""Parity of the CUDA skeletons with the CPU oracle on seeded inputs, through the C ABI.
+
+Bars (BASELINE north_star): bit-exact for integer, comparison, argmax and sort outputs;
+within 1e-5 relative for f32 elementwise and reduce kernels; f32 GEMM within 1e-4 and f16
+GEMM/matvec within 2e-3 per element after normalising by K.  Where a result can cancel to
+nearly zero (sums, dot products) "relative" is taken against the sum of absolute terms.
+"""
+import numpy as np
+import pytest
+
+import oracle
+from jax_js_b200 import AluExp, AluOp, AluVar, DType, Kernel, Reduction, np_dtype
+from jax_js_b200 import programs as P
+from jax_js_b200.backend import UnsupportedOpError
+
+from util import assert_close, assert_same_bits, run_cuda
+
+pytestmark = pytest.mark.gpu
+F32, I32, U32, BOOL, F16, F64 = (DType.Float32, DType.Int32, DType.Uint32, DType.Bool, DType.Float16, DType.Float64)
+g, r = AluVar.gidx, AluVar.ridx
+SPECIAL = np.array([0.0, -0.0, 1.0, -1.0, np.inf, -np.inf, np.nan, 1e-40, -1e-40, 3.4e38, 88.8, -104.0, 0.5, 2.0,
+                    1.9999999, 1e-3], np.float32)
+
+
+def _inputs(n, seed, lo=-4.0, hi=4.0, special=True):
+    rng = np.random.default_rng(seed)
+    x = rng.uniform(lo, hi, n).astype(np.float32)
+    if special:
+        x[: len(SPECIAL)] = SPECIAL
+    return x
+
+
+N = 4099  # odd on purpose: exercises the scalar tail after the 128-bit body
+
+
+@pytest.mark.parametrize("op,lo,hi,rtol,scale", [
+    (AluOp.Exp, -100, 90, 1e-5, 0), (AluOp.Log, 0, 50, 1e-5, 1e-3), (AluOp.Sin, -30, 30, 1e-5, 1.0),
+    (AluOp.Cos, -30, 30, 1e-5, 1.0), (AluOp.Asin, -1, 1, 1e-5, 1e-3), (AluOp.Atan, -50, 50, 1e-5, 1e-3),
+    (AluOp.Erf, -4, 4, 1e-5, 1e-3), (AluOp.Erfc, -4, 4, 1e-5, 1.0), (AluOp.Sqrt, 0, 100, 0, 0),
+    (AluOp.Floor, -9, 9, 0, 0), (AluOp.Ceil, -9, 9, 0, 0), (AluOp.Reciprocal, -9, 9, 0, 0)])
+def test_unary_float_ops_match_wasm_semantics(backend, op, lo, hi, rtol, scale):
+    x = _inputs(N, int(op), lo, hi)
+    k = Kernel(1, N, AluExp(op, F32, [AluExp.global_index(F32, 0, N, g)]))
+    got, want = run_cuda(backend, k, [x]), oracle.run_kernel(k, [x])
+    if rtol == 0:
+        assert_same_bits(got, want, op.name)   # IEEE operations: identical on both sides
+    else:
+        assert_close(got, want, rtol, scale or None, op.name)
+
+
+@pytest.mark.parametrize("op", [AluOp.Add, AluOp.Sub, AluOp.Mul, AluOp.Idiv, AluOp.Mod, AluOp.Min, AluOp.Max])
+@pytest.mark.parametrize("dtype", [F32, I32, U32])
+def test_binary_ops(backend, op, dtype):
+    rng = np.random.default_rng(int(op) * 7 + int(dtype))
+    if dtype == F32:
+        a, b = _inputs(N, 1), np.roll(_inputs(N, 2), 3)
+    else:
+        a = rng.integers(-2**31, 2**31, N).astype(np.int64).astype(np_dtype(dtype))
+        b = rng.integers(-50, 50, N).astype(np.int64).astype(np_dtype(dtype))
+        a[:4] = np.array([2**31 - 1, -2**31, 0, -1]).astype(np_dtype(dtype))
+        b[:4] = np.array([-1, -1, 0, 0]).astype(np_dtype(dtype))
+    k = Kernel(2, N, AluExp(op, dtype, [AluExp.global_index(dtype, 0, N, g), AluExp.global_index(dtype, 1, N, g)]))
+    got, want = run_cuda(backend, k, [a, b]), oracle.run_kernel(k, [a, b])
+    if dtype == F32 and op == AluOp.Mod:
+        # a - trunc(a/b)*b: the GPU may fuse the multiply-subtract; bounded by one rounding of |a|
+        assert_close(got, want, 1e-6, np.abs(a), "f32 Mod")
+    else:
+        assert_same_bits(got, want, f"{op.name}<{dtype.name}>")
+
+
+def test_compare_where_cast_bitcast_bool_logic(backend):
+    a, b = _inputs(N, 5), np.roll(_inputs(N, 6), 1)
+    x, y = AluExp.global_index(F32, 0, N, g), AluExp.global_index(F32, 1, N, g)
+    lt, ne = AluExp.cmplt(x, y), AluExp.cmpne(x, y)
+    cases = {
+        "cmplt": lt, "cmpne": ne, "and": AluExp.mul(lt, ne), "or": AluExp.add(lt, ne.not_()),
+        "where": AluExp.where(lt, x, y), "cast_i32": AluExp.cast(I32, AluExp.mul(x, AluExp.f32(1e9))),
+        "cast_u32": AluExp.cast(U32, AluExp.mul(x, AluExp.f32(1e9))), "cast_bool": AluExp.cast(BOOL, x),
+        "bool_to_f32": AluExp.cast(F32, lt), "bitcast": AluExp.bitcast(U32, x),
+        "u32_to_f32": AluExp.cast(F32, AluExp.bitcast(U32, x)), "i32_to_f32": AluExp.cast(F32, AluExp.bitcast(I32, x)),
+        "bit_invert": AluExp.bit_invert(AluExp.bitcast(I32, x)),
+        "shr_int32_is_logical": AluExp.bit_shift(AluExp.bitcast(I32, x), AluExp.i32(35), "shr"),
+    }
+    for name, e in cases.items():
+        k = Kernel(2, N, e)
+        assert_same_bits(run_cuda(backend, k, [a, b]), oracle.run_kernel(k, [a, b]), name)
+
+
+def test_threefry_bits_are_exact(backend):
+    n = 10007
+    key = np.array([0, 42], np.uint32)
+    k0, k1 = AluExp.global_index(U32, 0, 2, AluExp.i32(0)), AluExp.global_index(U32, 0, 2, AluExp.i32(1))
+    c = AluExp.cast(U32, g)
+    for mode in ("xor", 0, 1):
+        k = Kernel(1, n, AluExp.threefry2x32(k0, k1, AluExp.u32(0), c, mode))
+        assert_same_bits(run_cuda(backend, k, [key]), oracle.run_kernel(k, [key]), f"threefry {mode}")
+    k = Kernel(0, 1, AluExp.threefry2x32(AluExp.u32(0), AluExp.u32(0), AluExp.u32(0), AluExp.u32(0), 0))
+    assert int(run_cuda(backend, k, [])[0]) == 1797259609   # src/alu.test.ts:202-209
+
+
+def test_out_of_range_and_guarded_loads(backend):
+    # a padded view: Where(valid, load, 0) with the load clamped to element 0 when invalid
+    from jax_js_b200 import ShapeTracker, accessor_global
+    n = 1000
+    x = _inputs(n, 9, special=False)
+    st = ShapeTracker.from_shape([n]).pad([(3, 5)])
+    k = Kernel(1, n + 8, accessor_global(F32, 0, st, [g]))
+    got = run_cuda(backend, k, [x])
+    assert_same_bits(got, oracle.run_kernel(k, [x]))
+    assert (got[:3] == 0).all() and (got[-5:] == 0).all() and (got[3:-5] == x).all()
+    k = Kernel(1, 3, AluExp.global_index(F32, 0, 3, AluExp.add(g, AluExp.i32(2))))
+    assert run_cuda(backend, k, [np.array([5, 6, 7], np.float32)]).tolist() == [7, 5, 5]
+
+
+def test_float64_and_float16_elementwise(backend):
+    rng = np.random.default_rng(3)
+    d = rng.standard_normal(N)
+    x = AluExp.global_index(F64, 0, N, g)
+    k = Kernel(1, N, AluExp.add(AluExp.mul(x, x), AluExp.f64(0.25)))
+    assert_close(run_cuda(backend, k, [d]), oracle.run_kernel(k, [d], mode=oracle.MODE_WASM), 1e-15, 1.0)
+    h = (rng.standard_normal(N) * 3).astype(np.float16)
+    hx = AluExp.global_index(F16, 0, N, g)
+    k = Kernel(1, N, AluExp.exp(AluExp.mul(hx, AluExp.f16(0.5))))
+    assert_close(run_cuda(backend, k, [h]), oracle.run_kernel(k, [h]), 2e-3, 1e-4, "f16 exp")
+
+
+def test_unsupported_op_is_reported_not_emulated(backend):
+    # UnsupportedOpError wording of src/backend.ts:228-234; nothing falls back to the host
+    bad = Kernel(0, 4, AluExp(AluOp.Sub, BOOL, [AluExp.bool(True), AluExp.bool(False)]))
+    with pytest.raises(UnsupportedOpError, match=r"Sub<bool> not supported in cuda backend"):
+        backend.prepare_kernel(bad)
+
+
+# ---- reductions ---------------------------------------------------------------------------
+
+def _row_kernel(rows, cols, dtype, op, body=None, epilogue=None):
+    x = AluExp.global_index(dtype, 0, rows * cols, AluExp.add(AluExp.mul(g, AluExp.i32(cols)), r))
+    return Kernel(1, rows, body(x) if body else x, Reduction(dtype, op, cols, epilogue))
+
+
+def _col_kernel(rows, cols, dtype, op):
+    x = AluExp.global_index(dtype, 0, rows * cols, AluExp.add(g, AluExp.mul(r, AluExp.i32(cols))))
+    return Kernel(1, cols, x, Reduction(dtype, op, rows))
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 7), (5, 33), (37, 130), (64, 1000), (19, 4096), (3, 70001), (1, 300000)])
+@pytest.mark.parametrize("op", [AluOp.Add, AluOp.Max, AluOp.Min, AluOp.Mul])
+def test_row_reductions_f32(backend, rows, cols, op):
+    rng = np.random.default_rng(rows * 131 + cols)
+    x = rng.standard_normal((rows, cols)).astype(np.float32)
+    if op == AluOp.Mul:
+        x = (1 + x * 1e-3).astype(np.float32)
+    if op in (AluOp.Max, AluOp.Min) and cols > 8:
+        x[0, 5] = np.nan   # NaN propagates through f32.max/min
+    k = _row_kernel(rows, cols, F32, op)
+    got, want = run_cuda(backend, k, [x]), oracle.run_kernel(k, [x])
+    if op in (AluOp.Max, AluOp.Min):
+        assert_same_bits(got, want, f"{op.name} {rows}x{cols}")
+    else:
+        scale = np.abs(x).sum(1) if op == AluOp.Add else None
+        assert_close(got, want, 1e-5, scale, f"{op.name} {rows}x{cols}")
+
+
+@pytest.mark.parametrize("rows,cols", [(7, 1), (33, 5), (1000, 64), (4096, 19), (70001, 6), (65536, 2048)])
+def test_column_reductions_f32(backend, rows, cols):
+    rng = np.random.default_rng(rows + cols)
+    x = rng.standard_normal((rows, cols)).astype(np.float32)
+    k = _col_kernel(rows, cols, F32, AluOp.Add)
+    assert_close(run_cuda(backend, k, [x]), oracle.run_kernel(k, [x]), 1e-5, np.abs(x).sum(0))
+
+
+@pytest.mark.parametrize("dtype", [I32, U32, BOOL])
+@pytest.mark.parametrize("op", [AluOp.Add, AluOp.Mul, AluOp.Min, AluOp.Max])
+@pytest.mark.parametrize("shape", [(9, 513), (513, 9), (2, 40000)])
+def test_integer_and_bool_reductions_are_exact(backend, dtype, op, shape):
+    rows, cols = shape
+    rng = np.random.default_rng(int(dtype) * 100 + int(op))
+    if dtype == BOOL:
+        x = (rng.random((rows, cols)) < (0.999 if op in (AluOp.Mul, AluOp.Min) else 0.001)).astype(np.int32)
+    else:
+        x = rng.integers(-2**31, 2**31, (rows, cols)).astype(np.int64).astype(np_dtype(dtype))
+        if op == AluOp.Mul:
+            x |= 1
+    for k in (_row_kernel(rows, cols, dtype, op), _col_kernel(rows, cols, dtype, op)):
+        assert_same_bits(run_cuda(backend, k, [x]), oracle.run_kernel(k, [x]), f"{op.name}<{dtype.name}> {shape}")
+
+
+def test_forced_skeletons_agree(backend, monkeypatch):
+    # the same kernel through both reduce skeletons (and odd sizes that defeat vector loads)
+    from jax_js_b200.backend import CudaBackend
+    rows, cols = 257, 1031
+    x = np.random.default_rng(0).standard_normal((rows, cols)).astype(np.float32)
+    k = _row_kernel(rows, cols, F32, AluOp.Add, epilogue=AluExp.mul(AluVar.acc(F32), AluExp.f32(0.5)))
+    want = oracle.run_kernel(k, [x])
+    for sk in ("1", "2"):
+        monkeypatch.setenv("JAXCUDA_FORCE_SKELETON", sk)
+        be = CudaBackend(backend.device)
+        try:
+            got, exe = run_cuda(be, k, [x], keep=True)
+            assert ("reduce-row" if sk == "1" else "reduce-col") in exe.describe
+            assert_close(got, want, 1e-5, 0.5 * np.abs(x).sum(1), f"skeleton {sk}")
+        finally:
+            be.close()
+
+
+# ---- config 2: softmax, log-sum-exp, argmax over f32[8192, 4096] ------------------------
+
+@pytest.mark.parametrize("rows,cols", [(64, 1000), (8192, 4096)])
+def test_softmax_lse_argmax_kernels(backend, rows, cols):
+    x = np.random.default_rng(0).standard_normal((rows, cols)).astype(np.float32)
+    x[1, 7] = x[1, 3] = x[1].max() + 1      # a tie: argmax takes the first index
+    iota = P.argmax_iota(cols)
+    prog = P.softmax_lse_argmax_program(rows, cols)
+    sx, si = backend.put(x), backend.put(iota)
+    outs = prog.execute(backend, [sx, si])
+    sm, lse, am = backend.get(outs[0], F32, (rows, cols)), backend.get(outs[1], F32), backend.get(outs[2], I32)
+    for s in outs + [sx, si]:
+        backend.dec_ref(s)
+    # the oracle replays the same kernels in the same order
+    m = oracle.run_kernel(P.row_reduce_kernel(rows, cols, AluOp.Max), [x])
+    u = oracle.run_kernel(P.softmax_exp_kernel(rows, cols), [x, m])
+    s = oracle.run_kernel(P.row_reduce_kernel(rows, cols, AluOp.Add), [u])
+    want_sm = oracle.run_kernel(P.softmax_scale_kernel(rows, cols), [u, s]).reshape(rows, cols)
+    s2 = oracle.run_kernel(P.lse_sum_kernel(rows, cols), [x, m])
+    want_lse = oracle.run_kernel(P.lse_finish_kernel(rows), [s2, m])
+    want_am = oracle.run_kernel(P.argmax_index_kernel(rows, cols), [x, m, iota])
+    assert_close(sm, want_sm, 1e-5, None, "softmax")
+    assert_close(lse, want_lse, 1e-5, None, "logsumexp")
+    assert_same_bits(am, want_am, "argmax")
+    assert am[1] == 3 and (am == x.argmax(1)).all()
+    np.testing.assert_allclose(sm.sum(1), 1.0, rtol=1e-5)           # size-independent properties
+    assert (sm[np.arange(rows), am] == sm.max(1)).all()
+
+
+# ---- config 3a: f16 matvec ---------------------------------------------------------------------
+
+@pytest.mark.parametrize("K,Nout,orientation", [(4096, 11008, "xW"), (4096, 11008, "Wx"), (300, 70, "xW"), (70, 300, "Wx")])
+def test_matvec_f16(backend, K, Nout, orientation):
+    rng = np.random.default_rng(0)
+    if orientation == "xW":
+        W, x = (rng.standard_normal((K, Nout)) * 0.02).astype(np.float16), (rng.standard_normal(K) * 0.02).astype(np.float16)
+        k, args = P.matvec_kernel(K, Nout, F16, orientation="xW"), [x, W]
+        scale = np.abs(x.astype(np.float64)) @ np.abs(W.astype(np.float64))
+    else:
+        W, x = (rng.standard_normal((Nout, K)) * 0.02).astype(np.float16), (rng.standard_normal(K) * 0.02).astype(np.float16)
+        k, args = P.matvec_kernel(Nout, K, F16, orientation="Wx"), [W, x]
+        scale = np.abs(W.astype(np.float64)) @ np.abs(x.astype(np.float64))
+    got, want = run_cuda(backend, k, args), oracle.run_kernel(k, args)
+    # 2e-3 relative per element after normalising by K; the f16 store itself rounds by 2^-11 of the value
+    assert_close(got.astype(np.float64) / K, want.astype(np.float64) / K, 2e-3, scale / K, "matvec f16")
+
+
+# ---- GEMM-shaped kernels -------------------------------------------------------------------------
+
+def _gemm_case(backend, kernel, args, K, tol, dtype, rows=None):
+    got = run_cuda(backend, kernel, args).astype(np.float64)
+    if rows is None:
+        want = oracle.run_kernel(kernel, args, fma=True).astype(np.float64)
+        sel = slice(None)
+    else:  # full-size case: the oracle evaluates a sample of output ranges
+        want = np.zeros(kernel.size, np_dtype(kernel.dtype))
+        for b, e in rows:
+            oracle.run_kernel(kernel, args, begin=b, end=e, fma=True, out=want)
+        sel = np.concatenate([np.arange(b, e) for b, e in rows])
+        want = want.astype(np.float64)
+    a, b = args[0].astype(np.float64), args[1].astype(np.float64)
+    bound = np.abs(a).max() * np.abs(b).max()
+    assert_close(got[sel] / K, want[sel] / K, tol, bound, "gemm")
+    return got
+
+
+@pytest.mark.parametrize("M,N,K,al,bl", [(1024, 1024, 1024, "mk", "kn"), (100, 130, 70, "mk", "kn"),
+                                         (256, 192, 520, "km", "kn"), (192, 256, 136, "mk", "nk"), (130, 100, 64, "km", "nk")])
+def test_gemm_f32(backend, M, N, K, al, bl):
+    rng = np.random.default_rng(0)
+    A = rng.uniform(-1, 1, (M, K) if al == "mk" else (K, M)).astype(np.float32)
+    B = rng.uniform(-1, 1, (K, N) if bl == "kn" else (N, K)).astype(np.float32)
+    k = P.dot_kernel(M, N, K, F32, a_layout=al, b_layout=bl)
+    got = _gemm_case(backend, k, [A, B], K, 1e-4, F32).reshape(M, N)
+    Am = A if al == "mk" else A.T
+    Bm = B if bl == "kn" else B.T
+    ref = Am.astype(np.float64) @ Bm.astype(np.float64)
+    # tighter than the bar: against float64, relative to the sum of absolute products
+    assert_close(got, ref, 2e-6, np.abs(Am).astype(np.float64) @ np.abs(Bm).astype(np.float64), "gemm f32 vs f64")
+
+
+def test_gemm_f32_bias_relu_batched_and_swapped(backend):
+    rng = np.random.default_rng(1)
+    M, N, K = 96, 160, 200
+    A, B, bias = (rng.standard_normal(s).astype(np.float32) for s in ((M, K), (K, N), (N,)))
+    for kw in (dict(bias=True, relu=True), dict(swap=True), dict(bias=True)):
+        k = P.dot_kernel(M, N, K, F32, **kw)
+        _gemm_case(backend, k, [A, B, bias][: k.nargs], K, 1e-4, F32)
+    Ab, Bb = rng.standard_normal((5, 64, 40)).astype(np.float32), rng.standard_normal((5, 40, 48)).astype(np.float32)
+    k = P.dot_kernel(64, 48, 40, F32, batch=5)
+    got = _gemm_case(backend, k, [Ab, Bb], 40, 1e-4, F32).reshape(5, 64, 48)
+    np.testing.assert_allclose(got, np.einsum("bmk,bkn->bmn", Ab, Bb), rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("n", [256, 4096])
+def test_gemm_f16(backend, n):
+    rng = np.random.default_rng(0)
+    A = (rng.standard_normal((n, n)) * 0.02).astype(np.float16)
+    B = (rng.standard_normal((n, n)) * 0.02).astype(np.float16)
+    k = P.dot_kernel(n, n, n, F16)
+    rows = None if n <= 256 else [(0, 2 * n), (n * n // 2 + 17, n * n // 2 + 17 + n), (n * n - 3 * n, n * n)]
+    got = _gemm_case(backend, k, [A, B], n, 2e-3, F16, rows).reshape(n, n)
+    # linearity (size independent): (2A)B == 2(AB) exactly in binary floating point
+    got2 = run_cuda(backend, k, [(A * np.float16(2)), B]).astype(np.float64).reshape(n, n)
+    np.testing.assert_array_equal(got2, 2 * got)
