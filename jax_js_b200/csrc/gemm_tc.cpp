@@ -1,15 +1,458 @@
+// TMA-fed tcgen05 / TMEM GEMM skeleton for sm_100a.
+//
+// A GEMM-shaped Kernel (Mul of two loads under an f32 Add reduction, the form the reference's
+// `jitRules[Dot]` builds, src/frontend/jit.ts:639-648) runs here when its operands can be
+// described by TMA tensor maps.  The reference tiles the same kernel for WebGPU with 4x4
+// register tiles and no shared memory (src/tuner.ts:284-383) and for Wasm with a 128x128x64
+// plan (src/backend/wasm/tilePlan.ts:38-45); on Blackwell the tile lives in tensor memory:
+//
+//   warp 0      TMA producer: 128-byte-swizzled tiles of A and B into a ring of shared-memory
+//               stages (cp.async.bulk.tensor, one CTA, no multicast), mbarrier expect_tx
+//   warp 1      MMA issuer: tcgen05.mma (cta_group::1, M=128, N=BN) from shared-memory
+//               descriptors into one of two TMEM accumulators; tcgen05.commit frees the stage
+//   warps 2-5   epilogue: tcgen05.ld the finished accumulator, apply the Kernel's spliced
+//               epilogue (Cast, bias, ReLU ...) and store, while warp 1 fills the other one
+//
+// The kernel is persistent (one CTA per SM, static tile schedule).  float16 operands use
+// kind::f16 with f32 accumulation.  float32 operands use kind::tf32 three times per k-step on
+// planes split into a TF32-exact high part and the remainder (3xTF32: lo*hi + hi*lo + hi*hi),
+// which keeps f32 accuracy; plain TF32 is never used.  Every mbarrier wait is bounded: on a
+// time-out the kernel records a code in `status` and winds down instead of hanging the GPU.
 #include "gemm_tc.hpp"
+
+#include <cstring>
+#include <sstream>
+
+#include "prelude.hpp"
 
 namespace jaxcuda {
 
-bool plan_gemm_tc(const KernelIR&, const GemmDesc&, const Options&, Plan&, const std::string&, const std::string&) {
+namespace {
+
+const char* const kTcSource = R"TCGEMM(
+struct __align__(64) CUtensorMap { unsigned long long opaque[16]; };
+
+#define SPIN_LIMIT 20000000
+
+__device__ __forceinline__ u32 smem_u32(const void* p) { return (u32)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(u32 bar, u32 count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(u32 bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(u32 bar, u32 bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait: polls without blocking (test_wait), backs off with nanosleep, and gives up after
+// SPIN_LIMIT polls (about a second) or as soon as another role has reported a failure.
+__device__ __forceinline__ bool mbar_wait(u32 bar, u32 parity, volatile int* status) {
+  for (int spin = 0; spin < SPIN_LIMIT; spin++) {
+    u32 done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    if (done) return true;
+    if (spin > 64) __nanosleep(40);
+    if ((spin & 1023) == 1023 && *status != 0) return false;
+  }
   return false;
 }
+__device__ __forceinline__ void tma_load_3d(u32 dst, const CUtensorMap* map, u32 bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void umma(u32 d_tmem, u64 adesc, u64 bdesc, u32 idesc, u32 accumulate) {
+#if KIND == 1
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+#else
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+#endif
+}
+__device__ __forceinline__ void umma_commit(u32 bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(u32 taddr, u32* v) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                 "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+               : "r"(taddr));
+}
 
-int launch_gemm_tc(void*, void*, const Plan&, const std::vector<CUfunction>&, const std::vector<void*>&, void*, void*,
-                   cudaStream_t, std::string& err) {
-  err = "tensor-core GEMM skeleton is not built";
-  return -1;
+// Shared-memory matrix descriptor (sm_100): start address, leading / stride byte offsets in
+// 16-byte units, descriptor version 1, 128-byte swizzle.
+// layout: 2 = 128-byte swizzle in 16-byte units; 1 = 128-byte swizzle in 32-byte units, the only
+// layout tensor cores accept for MN-major 32-bit (TF32) operands.
+__device__ __forceinline__ u64 make_desc(u32 addr, u32 lbo_bytes, u32 sbo_bytes, u32 layout) {
+  return (u64)((addr >> 4) & 0x3fff) | ((u64)((lbo_bytes >> 4) & 0x3fff) << 16) |
+         ((u64)((sbo_bytes >> 4) & 0x3fff) << 32) | (1ull << 46) | ((u64)layout << 61);
+}
+
+// Per k-step (32 bytes of K) descriptor of an operand tile that starts at `base`.
+//   K-major : rows of 128 bytes, 8-row swizzle atoms 1024 bytes apart; advance 32 bytes per step
+//   MN-major: boxes of [BK rows of k][128 bytes of m/n], BOX_BYTES apart; a step covers KROWS k-rows
+#define KROWS (32 / ELEM)             /* k elements per MMA: 16 (f16) or 8 (tf32) */
+#define BK (128 / ELEM)               /* k elements per stage */
+#define BOX_BYTES (BK * 128)
+//             (4-byte elements: swizzle atoms are 4 k-rows = 512 bytes, in 32-byte units)
+__device__ __forceinline__ u64 operand_desc(u32 base, int kk, int mn_major) {
+  if (!mn_major) return make_desc(base + kk * 32, 16, 1024, 2);
+  return ELEM == 4 ? make_desc(base + kk * KROWS * 128, BOX_BYTES, 512, 1)
+                   : make_desc(base + kk * KROWS * 128, BOX_BYTES, 1024, 2);
+}
+
+#define A_BYTES (BM * 128)
+#define B_BYTES (BN * 128)
+#define NPLANES (KIND == 2 ? 2 : 1)
+#define STAGE_BYTES (NPLANES * (A_BYTES + B_BYTES))
+#define TILES_M ((GM + BM - 1) / BM)
+#define TILES_N ((GN + BN - 1) / BN)
+#define NUM_TILES (TILES_M * TILES_N * GBATCH)
+#define K_BLOCKS ((GK + BK - 1) / BK)
+#define TMEM_COLS (2 * BN)
+#define IDESC ((1u << 4) | ((KIND == 2 ? 2u : 0u) << 7) | ((KIND == 2 ? 2u : 0u) << 10) | ((u32)A_MN << 15) | \
+               ((u32)B_MN << 16) | ((u32)(BN >> 3) << 17) | ((u32)(BM >> 4) << 24))
+
+__device__ __forceinline__ void tile_coords(int t, int& b, int& m_blk, int& n_blk) {
+  const int per_batch = TILES_M * TILES_N;
+  b = t / per_batch;
+  const int rem = t - b * per_batch;
+  const int GROUP = 8;                       // M-tiles sharing a sweep over N: keeps B tiles hot in L2
+  const int span = GROUP * TILES_N;
+  const int first_m = (rem / span) * GROUP;
+  const int gsz = (TILES_M - first_m) < GROUP ? (TILES_M - first_m) : GROUP;
+  const int in = rem % span;
+  m_blk = first_m + in % gsz;
+  n_blk = in / gsz;
+}
+
+extern "C" __global__ void __launch_bounds__(192, 1)
+jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA2,
+        const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmB2,
+        JX_PARAMS, int* status_ptr) {
+  extern __shared__ unsigned char smem_raw[];
+  volatile int* status = status_ptr;
+  const u32 smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;     // swizzle atoms are 1024-byte aligned
+  const u32 bars = smem_base + STAGES * STAGE_BYTES;                // full[STAGES], empty[STAGES], tfull[2], tempty[2]
+  const u32 tmem_slot = bars + (2 * STAGES + 4) * 8;
+  auto full = [&](int s) { return bars + s * 8; };
+  auto empty = [&](int s) { return bars + (STAGES + s) * 8; };
+  auto tfull = [&](int a) { return bars + (2 * STAGES + a) * 8; };
+  auto tempty = [&](int a) { return bars + (2 * STAGES + 2 + a) * 8; };
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) { mbar_init(full(s), 1); mbar_init(empty(s), 1); }
+    for (int a = 0; a < 2; a++) { mbar_init(tfull(a), 1); mbar_init(tempty(a), 4); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"((u32)TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  u32 tmem_base;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+
+  bool failed = false;
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      int it = 0;
+      for (int t = blockIdx.x; t < NUM_TILES && !failed; t += gridDim.x) {
+        int b, m_blk, n_blk;
+        tile_coords(t, b, m_blk, n_blk);
+        for (int kb = 0; kb < K_BLOCKS; kb++, it++) {
+          const int s = it % STAGES;
+          if (it >= STAGES && !mbar_wait(empty(s), ((it / STAGES) + 1) & 1, status)) { atomicCAS((int*)status_ptr, 0, 1); failed = true; break; }
+          mbar_expect_tx(full(s), STAGE_BYTES);
+          const u32 sa = smem_base + s * STAGE_BYTES, sb = sa + NPLANES * A_BYTES;
+          const int k0 = kb * BK;
+#if A_MN
+          for (int j = 0; j < BM / BK; j++) {
+            tma_load_3d(sa + j * BOX_BYTES, &tmA, full(s), m_blk * BM + j * BK, k0, b);
+            if (KIND == 2) tma_load_3d(sa + A_BYTES + j * BOX_BYTES, &tmA2, full(s), m_blk * BM + j * BK, k0, b);
+          }
+#else
+          tma_load_3d(sa, &tmA, full(s), k0, m_blk * BM, b);
+          if (KIND == 2) tma_load_3d(sa + A_BYTES, &tmA2, full(s), k0, m_blk * BM, b);
+#endif
+#if B_MN
+          for (int j = 0; j < BN / BK; j++) {
+            tma_load_3d(sb + j * BOX_BYTES, &tmB, full(s), n_blk * BN + j * BK, k0, b);
+            if (KIND == 2) tma_load_3d(sb + B_BYTES + j * BOX_BYTES, &tmB2, full(s), n_blk * BN + j * BK, k0, b);
+          }
+#else
+          tma_load_3d(sb, &tmB, full(s), k0, n_blk * BN, b);
+          if (KIND == 2) tma_load_3d(sb + B_BYTES, &tmB2, full(s), k0, n_blk * BN, b);
+#endif
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      int it = 0, tile_i = 0;
+      for (int t = blockIdx.x; t < NUM_TILES && !failed; t += gridDim.x, tile_i++) {
+        const int acc = tile_i & 1;
+        if (tile_i >= 2 && !mbar_wait(tempty(acc), ((tile_i >> 1) + 1) & 1, status)) { atomicCAS((int*)status_ptr, 0, 2); failed = true; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const u32 d = tmem_base + acc * BN;
+        for (int kb = 0; kb < K_BLOCKS; kb++, it++) {
+          const int s = it % STAGES;
+          if (!mbar_wait(full(s), (it / STAGES) & 1, status)) { atomicCAS((int*)status_ptr, 0, 3); failed = true; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const u32 sa = smem_base + s * STAGE_BYTES, sb = sa + NPLANES * A_BYTES;
+          #pragma unroll
+          for (int kk = 0; kk < 4; kk++) {
+            const u32 first = (kb | kk) ? 1u : 0u;
+#if KIND == 1
+            umma(d, operand_desc(sa, kk, A_MN), operand_desc(sb, kk, B_MN), IDESC, first);
+#else
+            // 3xTF32: small cross terms first, then the main product
+            umma(d, operand_desc(sa + A_BYTES, kk, A_MN), operand_desc(sb, kk, B_MN), IDESC, first);
+            umma(d, operand_desc(sa, kk, A_MN), operand_desc(sb + B_BYTES, kk, B_MN), IDESC, 1u);
+            umma(d, operand_desc(sa, kk, A_MN), operand_desc(sb, kk, B_MN), IDESC, 1u);
+#endif
+          }
+          umma_commit(empty(s));            // the stage is free once these MMAs have read it
+        }
+        if (!failed) umma_commit(tfull(acc));  // accumulator complete
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue warps 2..5
+    const int q = warp & 3;                 // TMEM lane quarter this warp may access
+    int tile_i = 0;
+    for (int t = blockIdx.x; t < NUM_TILES && !failed; t += gridDim.x, tile_i++) {
+      const int acc_i = tile_i & 1;
+      int b, m_blk, n_blk;
+      tile_coords(t, b, m_blk, n_blk);
+      if (!mbar_wait(tfull(acc_i), (tile_i >> 1) & 1, status)) { atomicCAS((int*)status_ptr, 0, 4); failed = true; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int m = m_blk * BM + q * 32 + lane;
+      const u32 trow = tmem_base + ((u32)(q * 32) << 16) + acc_i * BN;
+      #pragma unroll 1
+      for (int c = 0; c < BN / 16; c++) {
+        u32 v[16];
+        tmem_ld16(trow + c * 16, v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const int n0 = n_blk * BN + c * 16;
+        if (m < GM && n0 < GN) {
+          __align__(16) JX_OUT_T res[16];
+          #pragma unroll
+          for (int j = 0; j < 16; j++) {
+            const int n = n0 + j;
+            const int gidx = (int)(((i64)b * GM + m) * GN + (n < GN ? n : GN - 1));
+            const float acc = __uint_as_float(v[j]);
+#define JX_DST res[j]
+JX_EPILOGUE
+#undef JX_DST
+          }
+          JX_OUT_T* dst = out + (((i64)b * GM + m) * GN + n0);
+          if (n0 + 16 <= GN && (GN * sizeof(JX_OUT_T)) % 16 == 0) {
+            #pragma unroll
+            for (int j = 0; j < 16; j += 16 / sizeof(JX_OUT_T))
+              *reinterpret_cast<jx_vec<16>*>(dst + j) = *reinterpret_cast<const jx_vec<16>*>(&res[j]);
+          } else {
+            for (int j = 0; j < 16 && n0 + j < GN; j++) dst[j] = res[j];
+          }
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty(acc_i));
+    }
+  }
+  if (*status != 0) {
+    // Wind-down after a time-out: give copies that are still in flight time to land before the
+    // shared memory and the tensor memory of this CTA are released.
+    for (int i = 0; i < 2000; i++) __nanosleep(1000);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((u32)TMEM_COLS) : "memory");
+  }
+}
+
+#if KIND == 2
+// Splits f32 operands into a TF32-exact high part (low 13 mantissa bits cleared) and the exact
+// remainder; planes keep the operand's own indexing.
+extern "C" __global__ void __launch_bounds__(256) jx_split(const float* __restrict__ a, const float* __restrict__ b,
+                                                          float* __restrict__ planes) {
+  const i64 total = (i64)LEN_A + (i64)LEN_B;
+  for (i64 i = (i64)blockIdx.x * 256 + threadIdx.x; i < total; i += (i64)gridDim.x * 256) {
+    const bool is_a = i < LEN_A;
+    const i64 j = is_a ? i : i - LEN_A;
+    const float v = is_a ? a[j] : b[j];
+    const float hi = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
+    float* dst = planes + (is_a ? 0 : 2 * (i64)LEN_A_PAD);
+    const i64 pad = is_a ? LEN_A_PAD : LEN_B_PAD;
+    dst[j] = hi;
+    dst[pad + j] = v - hi;
+  }
+}
+#endif
+)TCGEMM";
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+typedef CUresult (*LaunchFn)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream,
+                             void**, void**);
+
+int64_t pad64(int64_t n) { return (n + 63) / 64 * 64; }  // planes start on 256-byte boundaries
+
+}  // namespace
+
+bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan& plan,
+                  const std::string& epilogue_body, const std::string& params_decl) {
+  if (g.dtA != g.dtB) return false;
+  const int kind = g.dtA == JAXCUDA_F16 ? 1 : g.dtA == JAXCUDA_F32 ? 2 : 0;
+  if (!kind) return false;
+  const int e = kind == 1 ? 2 : 4;
+  const bool a_mn = g.sAm == 1 && g.sAk != 1, b_mn = g.sBn == 1 && g.sBk != 1;
+  if (!a_mn && g.sAk != 1) return false;
+  if (!b_mn && g.sBk != 1) return false;
+  const int64_t a_outer = a_mn ? g.sAk : g.sAm, b_outer = b_mn ? g.sBk : g.sBn;
+  auto ok16 = [&](int64_t elems) { return elems > 0 && (elems * e) % 16 == 0; };
+  if (!ok16(a_outer) || !ok16(b_outer)) return false;
+  if ((g.offA * e) % 16 || (g.offB * e) % 16 || g.offA < 0 || g.offB < 0) return false;
+  if (g.batch > 1 && (!ok16(g.sAb == 0 ? 16 : g.sAb) || !ok16(g.sBb == 0 ? 16 : g.sBb) || g.sAb < 0 || g.sBb < 0)) return false;
+  if (g.M < 64 || g.N < 64 || g.K < 32) return false;
+  if ((uint64_t)g.lenA >= (1ull << 31) || (uint64_t)g.lenB >= (1ull << 31)) return false;
+
+  const int BM = 128;
+  const int bk = 128 / e;
+  int BN = 64;
+  for (int cand : {256, 128, 64}) {
+    if (kind == 2 && cand == 256) continue;  // two planes per operand: 256 columns would leave two stages
+    const int64_t tiles = ((g.M + BM - 1) / BM) * ((g.N + cand - 1) / cand) * g.batch;
+    if (cand <= g.N && (tiles >= (int64_t)opt.sm_count * 3 / 4 || cand == 64)) { BN = cand; break; }
+  }
+  if (BN > g.N) BN = 64;
+  const int planes = kind == 2 ? 2 : 1;
+  const int stage_bytes = planes * (BM + BN) * 128;
+  int stages = (227 * 1024 - 2048) / stage_bytes;
+  stages = std::max(2, std::min(stages, 6));
+  const int64_t tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN) * g.batch;
+
+  std::ostringstream os;
+  os << kPrelude;
+  os << "#define KIND " << kind << "\n#define ELEM " << e << "\n#define BM " << BM << "\n#define BN " << BN << "\n";
+  os << "#define STAGES " << stages << "\n#define A_MN " << (a_mn ? 1 : 0) << "\n#define B_MN " << (b_mn ? 1 : 0) << "\n";
+  os << "#define GM " << g.M << "\n#define GN " << g.N << "\n#define GK " << g.K << "\n#define GBATCH " << g.batch << "\n";
+  os << "#define LEN_A " << g.lenA << "LL\n#define LEN_B " << g.lenB << "LL\n";
+  os << "#define LEN_A_PAD " << pad64(g.lenA) << "LL\n#define LEN_B_PAD " << pad64(g.lenB) << "LL\n";
+  const char* out_t = k.out_dtype() == JAXCUDA_F16 ? "jx_half" : k.out_dtype() == JAXCUDA_F64 ? "double"
+                      : k.out_dtype() == JAXCUDA_U32 ? "u32" : k.out_dtype() == JAXCUDA_F32 ? "float" : "int";
+  os << "#define JX_OUT_T " << out_t << "\n";
+  os << "#define JX_PARAMS " << params_decl << "\n";
+  std::string body = epilogue_body;  // newlines inside a macro need continuation
+  std::string escaped;
+  for (char c : body) { if (c == '\n') escaped += " \\\n"; else escaped += c; }
+  os << "#define JX_EPILOGUE " << escaped << "\n";
+  os << kTcSource;
+  plan.source = os.str();
+  plan.skeleton = SK_GEMM_TC;
+  plan.tc_kind = kind;
+  plan.tc_bm = BM; plan.tc_bn = BN; plan.tc_bk = bk; plan.tc_stages = stages;
+  plan.stages.clear();
+  if (kind == 2) {
+    Stage sp;
+    sp.entry = "jx_split";
+    sp.grid[0] = (unsigned)std::min<int64_t>((g.lenA + g.lenB + 255) / 256, (int64_t)opt.sm_count * 16);
+    sp.block[0] = 256;
+    plan.stages.push_back(sp);
+    plan.scratch_bytes = (size_t)(2 * pad64(g.lenA) + 2 * pad64(g.lenB)) * 4;
+  }
+  Stage st;
+  st.entry = "jx_gemm";
+  st.grid[0] = (unsigned)std::min<int64_t>(tiles, opt.sm_count);
+  st.block[0] = 192;
+  st.smem = (unsigned)(stages * stage_bytes + 1024 + (2 * stages + 4) * 8 + 16);
+  plan.stages.push_back(st);
+  plan.describe = std::string("gemm-tcgen05 ") + (kind == 1 ? "f16" : "3xtf32") + " " + std::to_string(g.batch) + "x" +
+                  std::to_string(g.M) + "x" + std::to_string(g.N) + "x" + std::to_string(g.K) + " tile 128x" +
+                  std::to_string(BN) + "x" + std::to_string(bk) + " stages=" + std::to_string(stages) + " A:" +
+                  (a_mn ? "MN" : "K") + " B:" + (b_mn ? "MN" : "K") + " ctas=" + std::to_string(st.grid[0]);
+  return true;
+}
+
+int launch_gemm_tc(void* encode_fn, void* launch_fn, const Plan& plan, const std::vector<CUfunction>& fns,
+                   const std::vector<void*>& inputs, void* out, void* scratch, cudaStream_t stream,
+                   int* status_dev, std::string& err) {
+  auto encode = (EncodeTiledFn)encode_fn;
+  auto launch = (LaunchFn)launch_fn;
+  const GemmDesc& g = plan.gemm;
+  const int kind = plan.tc_kind;
+  const int e = kind == 1 ? 2 : 4;
+  const bool a_mn = g.sAm == 1 && g.sAk != 1, b_mn = g.sBn == 1 && g.sBk != 1;
+  int launches = 0;
+  const char* baseA = (const char*)inputs[g.gidA];
+  const char* baseB = (const char*)inputs[g.gidB];
+  const char* baseA2 = baseA;
+  const char* baseB2 = baseB;
+  if (kind == 2) {
+    float* planes = (float*)scratch;
+    void* args[] = {(void*)&baseA, (void*)&baseB, (void*)&planes};
+    const Stage& sp = plan.stages[0];
+    CUresult r = launch(fns[0], sp.grid[0], 1, 1, sp.block[0], 1, 1, 0, (CUstream)stream, args, nullptr);
+    if (r != CUDA_SUCCESS) { err = "launch of the TF32 split kernel failed"; return -1; }
+    launches++;
+    baseA = (const char*)planes;
+    baseA2 = (const char*)(planes + pad64(g.lenA));
+    baseB = (const char*)(planes + 2 * pad64(g.lenA));
+    baseB2 = (const char*)(planes + 2 * pad64(g.lenA) + pad64(g.lenB));
+  }
+  const CUtensorMapDataType dt = kind == 1 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  const cuuint32_t inner_box = 128 / e;
+  auto make_map = [&](CUtensorMap* m, const char* base, int64_t off, bool mn, int64_t mn_extent, int64_t k_extent,
+                      int64_t outer_stride, int64_t batch_stride, int rows_box) -> bool {
+    // dim 0 is the contiguous one: k for a K-major operand, m/n for an MN-major one
+    cuuint64_t dims[3] = {(cuuint64_t)(mn ? mn_extent : k_extent), (cuuint64_t)(mn ? k_extent : mn_extent), (cuuint64_t)g.batch};
+    cuuint64_t bs = batch_stride > 0 ? (cuuint64_t)batch_stride * e : dims[1] * (cuuint64_t)outer_stride * e;
+    cuuint64_t strides[2] = {(cuuint64_t)outer_stride * e, bs};
+    cuuint32_t box[3] = {inner_box, (cuuint32_t)rows_box, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    // MN-major 32-bit operands must sit in shared memory in the 128-byte swizzle with 32-byte atoms
+    const CUtensorMapSwizzle sw = (mn && e == 4) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B;
+    CUresult r = encode(m, dt, 3, (void*)(base + off * e), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+  };
+  alignas(64) CUtensorMap tmA, tmA2, tmB, tmB2;
+  const int bk = plan.tc_bk;
+  const int64_t a_outer = a_mn ? g.sAk : g.sAm, b_outer = b_mn ? g.sBk : g.sBn;
+  bool ok = make_map(&tmA, baseA, g.offA, a_mn, g.M, g.K, a_outer, g.sAb, a_mn ? bk : plan.tc_bm) &&
+            make_map(&tmA2, baseA2, g.offA, a_mn, g.M, g.K, a_outer, g.sAb, a_mn ? bk : plan.tc_bm) &&
+            make_map(&tmB, baseB, g.offB, b_mn, g.N, g.K, b_outer, g.sBb, b_mn ? bk : plan.tc_bn) &&
+            make_map(&tmB2, baseB2, g.offB, b_mn, g.N, g.K, b_outer, g.sBb, b_mn ? bk : plan.tc_bn);
+  if (!ok) { err = "cuTensorMapEncodeTiled rejected a GEMM operand"; return -1; }
+  std::vector<void*> ptrs(inputs.begin(), inputs.end());
+  ptrs.push_back(out);
+  ptrs.push_back(scratch);
+  std::vector<void*> args;
+  args.push_back(&tmA); args.push_back(&tmA2); args.push_back(&tmB); args.push_back(&tmB2);
+  for (auto& p : ptrs) args.push_back(&p);
+  args.push_back(&status_dev);
+  const Stage& st = plan.stages.back();
+  CUresult r = launch(fns.back(), st.grid[0], 1, 1, st.block[0], 1, 1, st.smem, (CUstream)stream, args.data(), nullptr);
+  if (r != CUDA_SUCCESS) { err = "launch of the tcgen05 GEMM kernel failed"; return -1; }
+  launches++;
+  return launches;
 }
 
 }  // namespace jaxcuda

@@ -12,9 +12,10 @@
 namespace jaxcuda {
 
 // Launches the stages of a SK_GEMM_TC plan.  Returns the number of kernels launched, or -1
-// with `err` set.  `encode_fn` is cuTensorMapEncodeTiled, `launch_fn` cuLaunchKernel.
+// with `err` set.  `status_dev` is a device-visible word the kernel writes a code to when a
+// pipeline wait times out (0 = healthy).  `encode_fn` is cuTensorMapEncodeTiled, `launch_fn` cuLaunchKernel.
 int launch_gemm_tc(void* encode_fn, void* launch_fn, const Plan& plan, const std::vector<CUfunction>& fns,
                    const std::vector<void*>& inputs, void* out, void* scratch, cudaStream_t stream,
-                   std::string& err);
+                   int* status_dev, std::string& err);
 
 }  // namespace jaxcuda

@@ -73,7 +73,7 @@ __device__ __forceinline__ double jx_dmod(double a, double b) { return a - trunc
 __device__ __forceinline__ float jx_exp(float x) {
   float kf = rintf(x * 1.44269504088896341f);
   int k = __float2int_rz(kf);
-  float r = x - kf * 0.69314718055994531f;
+  float r = x - __fmul_rn(kf, 0.69314718055994531f);  // unfused, as Wasm rounds the product
   float p = 1.0f / 720.0f;
   p = p * r + 1.0f / 120.0f;
   p = p * r + 1.0f / 24.0f;
@@ -106,10 +106,11 @@ __device__ __forceinline__ float jx_log(float x) {
 
 // sin / cos: reduce by the nearest multiple of 2pi, then of pi/2 (builtins.ts:203-310).
 __device__ __forceinline__ void jx_sincos(float x, int& q, float& sz, float& cz) {
-  float y = x - rintf(x * 0.15915494309189535f) * 6.283185307179586f;
+  float y = x - __fmul_rn(rintf(x * 0.15915494309189535f), 6.283185307179586f);  // unfused: the
+  // reduction's rounding error is part of the reference's result for large arguments
   float qf = rintf(y * 0.63661977236758138f);
   q = __float2int_rz(qf);
-  float z = y - qf * 1.5707963267948966f;
+  float z = y - __fmul_rn(qf, 1.5707963267948966f);
   float z2 = z * z;
   float s = -1.0f / 5040.0f;
   s = s * z2 + 1.0f / 120.0f;

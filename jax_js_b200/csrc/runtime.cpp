@@ -153,6 +153,11 @@ struct jaxcuda_ctx {
   std::vector<cudaEvent_t> events;  // created on first use of an index
   uint64_t launches = 0;
   int debug = 0;
+  // Kernels whose bounded waits give up write a code to `status_dev` (device memory: every CTA
+  // polls it, which must not cross PCIe); it is copied to the pinned `status_host` before a sync.
+  int* status_host = nullptr;
+  int* status_dev = nullptr;
+  bool tc_dispatched = false;
   // NCCL (resolved with dlopen so that the library loads where NCCL is absent)
   void* nccl_lib = nullptr;
   void* comm = nullptr;
@@ -191,6 +196,18 @@ SlotRec* find_slot(jaxcuda_ctx* ctx, jaxcuda_slot s) {
 int slot_error(jaxcuda_ctx* ctx, jaxcuda_slot s) {
   // wording of SlotError, src/backend.ts:222-226
   return fail(ctx, JAXCUDA_ESLOT, "Used a buffer that is invalid or already freed: %u", s);
+}
+
+// After a stream sync: has a kernel abandoned a bounded wait?
+int check_device_status(jaxcuda_ctx* ctx) {
+  if (ctx->status_host && *ctx->status_host != 0) {
+    const int code = *ctx->status_host;
+    *ctx->status_host = 0;
+    cudaMemsetAsync(ctx->status_dev, 0, sizeof(int), ctx->stream);
+    return fail(ctx, JAXCUDA_ECUDA, "tcgen05 GEMM pipeline wait timed out (role %d: 1 producer, 2/3 mma, 4 epilogue); "
+                "results of that dispatch are invalid", code);
+  }
+  return JAXCUDA_OK;
 }
 
 uint64_t fnv1a(const uint8_t* p, size_t n) {
@@ -285,6 +302,11 @@ int jaxcuda_create(int device, jaxcuda_ctx** out) {
   if (!load_driver(ctx->drv, err)) return fail(nullptr, JAXCUDA_ECUDA, "%s", err.c_str());
   if ((e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking)) != cudaSuccess)
     return fail(nullptr, JAXCUDA_ECUDA, "cudaStreamCreate: %s", cudaGetErrorString(e));
+  if ((e = cudaHostAlloc((void**)&ctx->status_host, sizeof(int), cudaHostAllocDefault)) != cudaSuccess ||
+      (e = cudaMalloc((void**)&ctx->status_dev, sizeof(int))) != cudaSuccess ||
+      (e = cudaMemset(ctx->status_dev, 0, sizeof(int))) != cudaSuccess)
+    return fail(nullptr, JAXCUDA_ECUDA, "status word: %s", cudaGetErrorString(e));
+  *ctx->status_host = 0;
   ctx->opt.sm_count = prop.multiProcessorCount;
   ctx->opt.ew_ilp = env_int("JAXCUDA_EW_ILP", ctx->opt.ew_ilp);
   ctx->opt.ew_blocks_per_sm = env_int("JAXCUDA_EW_BLOCKS_PER_SM", ctx->opt.ew_blocks_per_sm);
@@ -304,6 +326,8 @@ int jaxcuda_destroy(jaxcuda_ctx* ctx) {
   for (auto& ev : ctx->events) if (ev) cudaEventDestroy(ev);
   for (auto& kv : ctx->slots) if (kv.second.ptr) ctx->alloc.put(kv.second.ptr, kv.second.bytes);
   ctx->alloc.release_cached();
+  if (ctx->status_host) cudaFreeHost(ctx->status_host);
+  if (ctx->status_dev) cudaFree(ctx->status_dev);
   cudaStreamDestroy(ctx->stream);
   delete ctx;
   return JAXCUDA_OK;
@@ -371,8 +395,12 @@ int jaxcuda_read(jaxcuda_ctx* ctx, jaxcuda_slot slot, size_t start, size_t count
     if (!dst) return fail(ctx, JAXCUDA_EINVAL, "null destination");
     CUDA_TRY(ctx, cudaMemcpyAsync(dst, (const char*)s->ptr + start, count, cudaMemcpyDeviceToHost, ctx->stream));
   }
+  if (ctx->tc_dispatched) {  // only contexts that ran the tensor-core skeleton have anything to report
+    CUDA_TRY(ctx, cudaMemcpyAsync(ctx->status_host, ctx->status_dev, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    ctx->tc_dispatched = false;
+  }
   CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-  return JAXCUDA_OK;
+  return check_device_status(ctx);
 }
 
 int jaxcuda_write(jaxcuda_ctx* ctx, jaxcuda_slot slot, size_t start, size_t count, const void* src) {
@@ -540,9 +568,9 @@ int jaxcuda_dispatch(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const jaxcuda_slot* inp
     for (int i = 0; i < n_inputs; i++) inptr[i] = in[i]->ptr;
     std::string err;
     int nl = launch_gemm_tc(ctx->drv.TensorMapEncodeTiled, (void*)ctx->drv.LaunchKernel, exe->plan, exe->fns, inptr,
-                            outv[0]->ptr, scratch, ctx->stream, err);
+                            outv[0]->ptr, scratch, ctx->stream, ctx->status_dev, err);
     if (nl < 0) rc = fail(ctx, JAXCUDA_ECUDA, "%s", err.c_str());
-    else ctx->launches += nl;
+    else { ctx->launches += nl; ctx->tc_dispatched = true; }
   } else {
     std::vector<void*> ptrs(n_inputs + 2);
     std::vector<void*> args(n_inputs + 2);
@@ -592,8 +620,12 @@ int jaxcuda_host_free(jaxcuda_ctx* ctx, void* ptr) {
 int jaxcuda_sync(jaxcuda_ctx* ctx) {
   if (!ctx) return JAXCUDA_EINVAL;
   cudaSetDevice(ctx->device);
+  if (ctx->tc_dispatched) {  // only contexts that ran the tensor-core skeleton have anything to report
+    CUDA_TRY(ctx, cudaMemcpyAsync(ctx->status_host, ctx->status_dev, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    ctx->tc_dispatched = false;
+  }
   CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-  return JAXCUDA_OK;
+  return check_device_status(ctx);
 }
 
 int jaxcuda_event_record(jaxcuda_ctx* ctx, int index) {

@@ -94,7 +94,7 @@ def test_planner_choice_and_nvrtc_compile(lib, name):
     kernel, expect = CASES[name]
     describe, source = check_kernel(kernel, compile=True)
     assert expect in describe, describe
-    assert "jx_kernel" in source
+    assert 'extern "C" __global__' in source
 
 
 def test_vector_loads_only_where_provably_aligned(lib):
