@@ -463,7 +463,13 @@ struct Builder {
     account(p);
     const int64_t K = k.red_size;
     const int T = 256;
-    int TPR = K >= 1024 ? 256 : K >= 128 ? 32 : 8;
+    // A body with transcendentals does more work per load: half-size row groups keep more rows
+    // (and their loads) in flight per SM while the special-function unit is busy.
+    bool heavy = false;
+    for (const Node& nd : k.exp) heavy = heavy || (nd.op >= JAXCUDA_OP_SIN && nd.op <= JAXCUDA_OP_ERFC);
+    int TPR = K >= 1024 ? (heavy ? 128 : 256) : K >= 128 ? 32 : 8;
+    if (opt.row_tpr == 8 || opt.row_tpr == 32 || opt.row_tpr == 64 || opt.row_tpr == 128 || opt.row_tpr == 256)
+      TPR = opt.row_tpr;
     // vector width over ridx
     int V = 1;
     for (int cand : {8, 4, 2}) {
@@ -510,7 +516,8 @@ struct Builder {
     std::ostringstream decl, fetch;
     std::vector<std::string> bnames = names;  // hoisted values stay visible to the index closures
     if (V > 1) preload(decl, fetch, k.exp, an_exp, inner, 1, V, env, "r0", "", "", "u", ov, bnames, "    ");
-    os << "  #pragma unroll 4\n";
+    const int64_t iters = std::max<int64_t>(1, (rchunk + (int64_t)TPR * V - 1) / ((int64_t)TPR * V));
+    os << "  #pragma unroll " << (opt.row_unroll > 0 ? opt.row_unroll : (int)std::min<int64_t>(iters, 4)) << "\n";
     os << "  for (int r0 = rbeg + lane * " << V << "; r0 < rend; r0 += " << TPR * V << ") {\n";
     os << decl.str() << fetch.str();
     os << "    #pragma unroll\n    for (int u = 0; u < " << V << "; u++) {\n";
@@ -524,11 +531,13 @@ struct Builder {
     os << "  #pragma unroll\n  for (int o = " << W / 2 << "; o > 0; o >>= 1) { const " << AT
        << " v = jx_shfl_down(acc, o, " << W << "); acc = " << red("acc", "v") << "; }\n";
     if (TPR > 32) {
+      // one partial per warp; the first warp of each row folds its row's TPR/32 partials
+      const int WPR = TPR / 32;
       os << "  __shared__ " << AT << " sm[" << T / 32 << "];\n";
       os << "  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = acc;\n  __syncthreads();\n";
-      os << "  if (threadIdx.x < 32) {\n";
-      os << "    acc = threadIdx.x < " << T / 32 << " ? sm[threadIdx.x] : " << identity_literal(k.red_op, k.red_dtype) << ";\n";
-      os << "    #pragma unroll\n    for (int o = " << T / 64 << "; o > 0; o >>= 1) { const " << AT
+      os << "  if (lane < 32) {\n";
+      os << "    acc = lane < " << WPR << " ? sm[rowc * " << WPR << " + lane] : " << identity_literal(k.red_op, k.red_dtype) << ";\n";
+      os << "    #pragma unroll\n    for (int o = " << WPR / 2 << "; o > 0; o >>= 1) { const " << AT
          << " v = jx_shfl_down(acc, o, 32); acc = " << red("acc", "v") << "; }\n  }\n";
     }
     os << "  if (lane == 0 && active) {\n";
@@ -558,6 +567,9 @@ struct Builder {
     return p;
   }
 
+  // One thread per vector of V adjacent outputs walks ridx; TY such threads share a vector and
+  // take interleaved ridx values (folded through shared memory in a fixed order), and `splits`
+  // CTAs along grid.y take contiguous ridx chunks whose partials a second kernel folds.
   Plan reduce_col() const {
     Plan p;
     p.skeleton = SK_REDUCE_COL;
@@ -569,15 +581,19 @@ struct Builder {
       int eb = min_load_bytes(0, cand);
       if (eb && eb * cand <= 16 && (int64_t)k.size / cand >= 256) { V = cand; break; }
     }
-    const int T = 128;
     const int64_t nvec = ((int64_t)k.size + V - 1) / V;
-    const int64_t gblocks = (nvec + T - 1) / T;
-    int splits = 1;
-    if (gblocks < 4 * opt.sm_count && K >= 64) {
-      int64_t want = (4 * opt.sm_count + gblocks - 1) / gblocks;
-      splits = (int)std::max<int64_t>(1, std::min<int64_t>(want, K / 16));
-    }
+    // r-parallelism wanted so that the grid fills the machine: col_ctas_per_sm CTAs of 256 threads per SM
+    const int64_t target_threads = (int64_t)opt.sm_count * opt.col_ctas_per_sm * 256;
+    int64_t par = std::max<int64_t>(1, std::min<int64_t>((target_threads + nvec - 1) / nvec, K / 8));
+    int TY = 1;
+    while (TY < 8 && TY < par) TY <<= 1;
+    if (opt.col_ty > 0) TY = opt.col_ty;
+    const int T = TY == 1 ? std::max(32, opt.col_threads) : 256;
+    const int TX = T / TY;
+    const int64_t gblocks = (nvec + TX - 1) / TX;
+    int splits = (int)std::max<int64_t>(1, (par + TY - 1) / TY);
     int64_t rchunk = (K + splits - 1) / splits;
+    rchunk = (rchunk + TY - 1) / TY * TY;
     splits = (int)((K + rchunk - 1) / std::max<int64_t>(1, rchunk));
     if (K == 0) { splits = 1; rchunk = 0; }
     const char* AT = ctype(k.red_dtype);
@@ -587,8 +603,9 @@ struct Builder {
     std::ostringstream os;
     os << kPrelude;
     os << "extern \"C\" __global__ void __launch_bounds__(" << T << ") jx_kernel(" << params() << ") {\n";
-    os << "  const int gv = blockIdx.x * " << T << " + threadIdx.x;\n  if (gv >= " << nvec << ") return;\n";
-    os << "  const int g0 = gv * " << V << ";\n";
+    os << "  const int tx = threadIdx.x % " << TX << ", ty = threadIdx.x / " << TX << ";\n";
+    os << "  const int gv = blockIdx.x * " << TX << " + tx;\n  const bool active = gv < " << nvec << ";\n";
+    os << "  const int g0 = active ? gv * " << V << " : 0;\n";
     if (splits > 1) {
       os << "  const int rbeg = blockIdx.y * " << rchunk << ";\n  const int rend = min(" << K << ", rbeg + " << rchunk << ");\n";
     } else {
@@ -601,17 +618,50 @@ struct Builder {
     std::vector<std::string> bnames(k.exp.size());
     Env env;
     if (V > 1) preload(decl, fetch, k.exp, an_exp, all, 0, V, env, "g0", "", "", "u", ov, bnames, "    ");
-    os << "  #pragma unroll 4\n  for (int ridx = rbeg; ridx < rend; ridx++) {\n";
+    os << "  #pragma unroll " << std::max(1, opt.col_unroll) << "\n  for (int ridx = rbeg + ty; ridx < rend; ridx += " << TY << ") {\n";
     os << decl.str() << fetch.str();
     os << "    #pragma unroll\n    for (int u = 0; u < " << V << "; u++) {\n      const int gidx = g0 + u;\n";
     env.load_override = &ov;
     std::vector<std::string> names(k.exp.size());
     emit_nodes(os, k.exp, an_exp, names, all, env, "      ");
     os << "      acc[u] = " << red("acc[u]", names[root]) << ";\n    }\n  }\n";
+    if (TY > 1) {
+      os << "  __shared__ " << AT << " sm[" << TY * V * TX << "];\n";
+      os << "  #pragma unroll\n  for (int u = 0; u < " << V << "; u++) sm[(ty * " << V << " + u) * " << TX << " + tx] = acc[u];\n";
+      os << "  __syncthreads();\n";
+      os << "  if (ty == 0) {\n    #pragma unroll\n    for (int u = 0; u < " << V << "; u++)\n      for (int y = 1; y < " << TY
+         << "; y++) { const " << AT << " v = sm[(y * " << V << " + u) * " << TX << " + tx]; acc[u] = " << red("acc[u]", "v") << "; }\n  }\n";
+    }
+    const int64_t counter_bytes = 1024 + gblocks * 4;  // per-column-block arrival counters ahead of the partials
+    const int64_t counter_pad = (counter_bytes + 255) / 256 * 256;
     if (splits > 1) {
-      os << "  " << AT << "* part = (" << AT << "*)scratch + (size_t)blockIdx.y * " << k.size << " + g0;\n";
-      os << "  #pragma unroll\n  for (int u = 0; u < " << V << "; u++) part[u] = acc[u];\n";
+      // Every CTA stores its partial; the CTA that arrives last at its column block's counter folds
+      // all partials in split order (so the result does not depend on arrival order), applies the
+      // epilogue and re-arms the counter.  The counters live at the head of a scratch area that is
+      // zeroed once when the executable is prepared.
+      os << "  " << AT << "* parts = (" << AT << "*)((char*)scratch + " << counter_pad << ");\n";
+      os << "  if (ty == 0 && active) {\n    " << AT << "* part = parts + (size_t)blockIdx.y * " << k.size << " + g0;\n";
+      os << "    #pragma unroll\n    for (int u = 0; u < " << V << "; u++) part[u] = acc[u];\n  }\n";
+      os << "  __shared__ int last;\n  __threadfence();\n  __syncthreads();\n";
+      os << "  if (threadIdx.x == 0) last = atomicAdd((int*)scratch + blockIdx.x, 1) == " << splits - 1 << ";\n";
+      os << "  __syncthreads();\n  if (!last) return;\n  __threadfence();\n";
+      os << "  for (int o = threadIdx.x; o < " << TX * V << "; o += " << T << ") {\n";
+      os << "    const long long gl = (long long)blockIdx.x * " << TX * V << " + o;\n    if (gl >= " << k.size << "LL) break;\n";
+      os << "    const int gidx = (int)gl;\n    " << AT << " acc_u = " << identity_literal(k.red_op, k.red_dtype) << ";\n";
+      os << "    for (int s = 0; s < " << splits << "; s++) { const " << AT << " v = __ldcg(parts + (size_t)s * " << k.size
+         << " + gidx); acc_u = " << red("acc_u", "v") << "; }\n";
+      {
+        std::vector<std::string> en(k.epi.size());
+        std::vector<char> eall(k.epi.size(), 1);
+        Env ee;
+        ee.prefix = "e";
+        ee.acc = "acc_u";
+        emit_nodes(os, k.epi, an_epi, en, eall, ee, "    ");
+        os << "    out[gidx] = " << to_storage(out_dt, en.back()) << ";\n  }\n";
+      }
+      os << "  if (threadIdx.x == 0) ((int*)scratch)[blockIdx.x] = 0;\n";
     } else {
+      os << "  if (ty != 0 || !active) return;\n";
       os << "  #pragma unroll\n  for (int u = 0; u < " << V << "; u++) {\n    const int gidx = g0 + u;\n    const " << AT << " acc_u = acc[u];\n";
       std::vector<std::string> en(k.epi.size());
       std::vector<char> eall(k.epi.size(), 1);
@@ -622,7 +672,6 @@ struct Builder {
       os << "    out[gidx] = " << to_storage(out_dt, en.back()) << ";\n  }\n";
     }
     os << "}\n";
-    if (splits > 1) emit_finish_kernel(os, splits);
     p.source = os.str();
     Stage st;
     st.entry = "jx_kernel";
@@ -631,14 +680,10 @@ struct Builder {
     st.block[0] = T;
     p.stages.push_back(st);
     if (splits > 1) {
-      Stage fin;
-      fin.entry = "jx_finish";
-      fin.grid[0] = (unsigned)((k.size + 255) / 256);
-      fin.block[0] = 256;
-      p.stages.push_back(fin);
-      p.scratch_bytes = (size_t)splits * k.size * (k.red_dtype == JAXCUDA_F64 ? 8 : 4);
+      p.scratch_bytes = (size_t)counter_pad + (size_t)splits * k.size * (k.red_dtype == JAXCUDA_F64 ? 8 : 4);
+      p.scratch_persistent = true;
     }
-    p.describe = "reduce-col V=" + S(V) + " splits=" + S(splits) + " grid=" + S(gblocks) + "x" + S(T);
+    p.describe = "reduce-col V=" + S(V) + " TY=" + S(TY) + " splits=" + S(splits) + " grid=" + S(gblocks) + "x" + S(T);
     return p;
   }
 

@@ -45,6 +45,7 @@ struct Plan {
   std::string source;        // complete CUDA C translation unit for NVRTC
   std::vector<Stage> stages;  // launched in order on the backend's stream
   size_t scratch_bytes = 0;   // global scratch shared by the stages (split reductions, TF32 planes)
+  bool scratch_persistent = false;  // scratch belongs to the executable and starts zeroed (arrival counters)
   std::string describe;       // one line: skeleton and launch shape
   GemmDesc gemm;
   double algo_bytes = 0;      // distinct input bytes addressed + output bytes
@@ -56,11 +57,17 @@ struct Plan {
 
 struct Options {
   int sm_count = 148;
-  int ew_ilp = 4;             // independent 128-bit accesses in flight per thread (elementwise)
-  int ew_blocks_per_sm = 16;  // grid cap for the grid-stride elementwise loop
+  int ew_ilp = 2;             // independent 128-bit accesses in flight per thread (elementwise)
+  int ew_blocks_per_sm = 4096;  // grid cap; at the default the grid covers the array in one pass
   int gemm_min_dim = 32;      // below this M or N a GEMM-shaped kernel stays on the reduce skeletons
   bool allow_tc = true;       // tcgen05 path allowed (JAXCUDA_NO_TC=1 clears it)
   int force_skeleton = -1;    // tests: force SK_REDUCE_ROW / SK_REDUCE_COL / SK_GEMM_FFMA
+  int row_tpr = 0;            // threads per output row in the row-reduce skeleton (0: chosen from K)
+  int row_unroll = 0;         // vector loads in flight per thread in the row-reduce loop (0: trip count, at most 4)
+  int col_threads = 128;      // CTA size of the column-reduce skeleton
+  int col_ctas_per_sm = 8;    // spread ridx over threads and CTAs until the grid holds this many 256-thread CTAs per SM
+  int col_ty = 0;             // threads sharing one output vector inside a CTA (0: chosen)
+  int col_unroll = 8;         // independent loads in flight per thread in the column-reduce loop
 };
 
 // Throws std::runtime_error with the reference's UnsupportedOpError wording

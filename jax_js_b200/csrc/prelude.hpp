@@ -69,22 +69,22 @@ __device__ __forceinline__ float jx_fmod(float a, float b) { return a - truncf(a
 __device__ __forceinline__ double jx_didiv(double a, double b) { return trunc(a / b); }
 __device__ __forceinline__ double jx_dmod(double a, double b) { return a - trunc(a / b) * b; }
 
-// e^x: k = nearest(x / ln2), r = x - k ln2, degree-6 Taylor, scale by 2^k (builtins.ts:25-90).
+// e^x.  The reference computes k = nearest(x / ln2), a degree-6 Taylor polynomial in x - k ln2 and
+// a scale by 2^k, returning +Inf for k > 127 and 0 for k < -126 (builtins.ts:25-90; relative
+// error below 2e-7).  Here the same function is 2^(x log2 e) on the special-function unit:
+// t = rn(x log2 e), the rounding residual e of that product recovered exactly with two FMAs,
+// ex2.approx(t) (relative error 2^-22) and a first-order correction 2^e = 1 + e ln2, with the
+// reference's overflow and underflow thresholds kept (t > 127.5 and t < -126.5).  Ten issue
+// slots instead of about twenty, which is what keeps exp-fused kernels memory-bound.
 __device__ __forceinline__ float jx_exp(float x) {
-  float kf = rintf(x * 1.44269504088896341f);
-  int k = __float2int_rz(kf);
-  float r = x - __fmul_rn(kf, 0.69314718055994531f);  // unfused, as Wasm rounds the product
-  float p = 1.0f / 720.0f;
-  p = p * r + 1.0f / 120.0f;
-  p = p * r + 1.0f / 24.0f;
-  p = p * r + 1.0f / 6.0f;
-  p = p * r + 0.5f;
-  p = p * r + 1.0f;
-  p = p * r + 1.0f;
-  float res = p * __int_as_float((k + 127) << 23);
-  res = (k > 127) ? JX_INF : res;
-  res = (k < -126) ? 0.0f : res;
-  return (x != x) ? x : res;
+  const float t = x * 1.4426950408889634f;
+  float e = fmaf(x, 1.4426950408889634f, -t);
+  e = fmaf(x, 1.925963033500978e-8f, e);        // log2 e - float(log2 e)
+  float p;
+  asm("ex2.approx.f32 %0, %1;" : "=f"(p) : "f"(t));
+  float res = fmaf(p, e * 0.6931471805599453f, p);
+  res = (t > 127.5f) ? JX_INF : res;
+  return (t < -126.5f) ? 0.0f : res;
 }
 
 // ln x: exponent extraction plus the atanh series in t = (m-1)/(m+1) (builtins.ts:99-193).

@@ -137,6 +137,7 @@ struct jaxcuda_exe {
   int rt_dtype = 0;
   int64_t rt_batch = 0, rt_n = 0;
   std::string describe;
+  void* persistent_scratch = nullptr;  // zero-initialised once; reused by every dispatch (stream-ordered)
 };
 
 struct jaxcuda_ctx {
@@ -261,6 +262,8 @@ int compile_plan(jaxcuda_ctx* ctx, jaxcuda_exe* exe) {
 }
 
 void free_exe(jaxcuda_ctx* ctx, jaxcuda_exe* exe) {
+  if (exe->persistent_scratch) ctx->alloc.put(exe->persistent_scratch, exe->plan.scratch_bytes);
+  exe->persistent_scratch = nullptr;
   if (exe->module && ctx->drv.ModuleUnload) ctx->drv.ModuleUnload(exe->module);
   exe->module = nullptr;
 }
@@ -312,6 +315,12 @@ int jaxcuda_create(int device, jaxcuda_ctx** out) {
   ctx->opt.ew_blocks_per_sm = env_int("JAXCUDA_EW_BLOCKS_PER_SM", ctx->opt.ew_blocks_per_sm);
   ctx->opt.allow_tc = env_int("JAXCUDA_NO_TC", 0) == 0;
   ctx->opt.force_skeleton = env_int("JAXCUDA_FORCE_SKELETON", -1);
+  ctx->opt.row_tpr = env_int("JAXCUDA_ROW_TPR", ctx->opt.row_tpr);
+  ctx->opt.row_unroll = env_int("JAXCUDA_ROW_UNROLL", ctx->opt.row_unroll);
+  ctx->opt.col_threads = env_int("JAXCUDA_COL_THREADS", ctx->opt.col_threads);
+  ctx->opt.col_ctas_per_sm = env_int("JAXCUDA_COL_CTAS_PER_SM", ctx->opt.col_ctas_per_sm);
+  ctx->opt.col_ty = env_int("JAXCUDA_COL_TY", ctx->opt.col_ty);
+  ctx->opt.col_unroll = env_int("JAXCUDA_COL_UNROLL", ctx->opt.col_unroll);
   ctx->debug = env_int("JAXCUDA_DEBUG", 0);
   *out = ctx.release();
   return JAXCUDA_OK;
@@ -558,7 +567,14 @@ int jaxcuda_dispatch(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const jaxcuda_slot* inp
   if (k.size == 0) return JAXCUDA_OK;
 
   void* scratch = nullptr;
-  if (exe->plan.scratch_bytes) {
+  if (exe->plan.scratch_bytes && exe->plan.scratch_persistent) {
+    if (!exe->persistent_scratch) {
+      cudaError_t e = ctx->alloc.get(exe->plan.scratch_bytes, &exe->persistent_scratch);
+      if (e == cudaSuccess) e = cudaMemsetAsync(exe->persistent_scratch, 0, exe->plan.scratch_bytes, ctx->stream);
+      if (e != cudaSuccess) return fail(ctx, JAXCUDA_ENOMEM, "scratch of %zu bytes: %s", exe->plan.scratch_bytes, cudaGetErrorString(e));
+    }
+    scratch = exe->persistent_scratch;
+  } else if (exe->plan.scratch_bytes) {
     cudaError_t e = ctx->alloc.get(exe->plan.scratch_bytes, &scratch);
     if (e != cudaSuccess) return fail(ctx, JAXCUDA_ENOMEM, "scratch of %zu bytes: %s", exe->plan.scratch_bytes, cudaGetErrorString(e));
   }
@@ -586,7 +602,7 @@ int jaxcuda_dispatch(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const jaxcuda_slot* inp
       else ctx->launches++;
     }
   }
-  if (scratch) ctx->alloc.put(scratch, exe->plan.scratch_bytes);
+  if (scratch && !exe->plan.scratch_persistent) ctx->alloc.put(scratch, exe->plan.scratch_bytes);
   return rc;
 }
 

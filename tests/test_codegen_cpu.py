@@ -71,7 +71,7 @@ CASES = {
     "k1 row max": (P.row_reduce_kernel(8192, 4096, AluOp.Max), "reduce-row TPR=256 V=4"),
     "k2 exp": (P.softmax_exp_kernel(8192, 4096), "elementwise V=4"),
     "k4 scale": (P.softmax_scale_kernel(8192, 4096), "elementwise V=4"),
-    "k2' fused sum": (P.lse_sum_kernel(8192, 4096), "reduce-row TPR=256 V=4"),
+    "k2' fused sum": (P.lse_sum_kernel(8192, 4096), "reduce-row TPR=128 V=4"),
     "k3' tiny": (P.lse_finish_kernel(8192), "elementwise"),
     "k5 argmax": (P.argmax_index_kernel(8192, 4096), "reduce-row TPR=256 V=4"),
     "matvec xW": (P.matvec_kernel(4096, 11008, F16, orientation="xW"), "reduce-col V=8"),
