@@ -137,6 +137,54 @@ def other_configs(be, peaks):
     return out
 
 
+def mlp_train(be, rank, world, dist, steps=8, warmup=2):
+    """Config 5: data-parallel Adam step of the 784-2048-2048-10 MLP, global batch 65536 split over
+    the ranks, gradients summed with NCCL on the backend's stream.  Returns steps/s (strong scaling)."""
+    import torch
+    from jax_js_b200 import mlp
+    from jax_js_b200.backend import CudaBackend
+    dims, GB = [784, 2048, 2048, 10], 65536
+    local = GB // world
+    if world > 1:
+        uid = [CudaBackend.comm_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(uid, src=0)
+        be.comm_init(rank, world, uid[0])
+    rng = np.random.default_rng(100 + rank)
+    sx = be.put(rng.uniform(0, 1, (local, dims[0])).astype(np.float32))
+    sy = be.put(rng.integers(0, 10, local).astype(np.int32))
+    tr = mlp.MlpTrainer(be, dims, local, GB)
+    losses = []
+    for _ in range(warmup):
+        be.dec_ref(tr.step(sx, sy, world))
+    be.sync()
+    if dist:
+        dist.barrier()
+    l0 = be.launch_count()
+    be.event_record(0)
+    for _ in range(steps):
+        s = tr.step(sx, sy, world)
+        losses.append(s)
+    be.event_record(1)
+    be.sync()
+    ms = be.event_elapsed_ms(0, 1)
+    launches = be.launch_count() - l0
+    vals = [float(be.get(s, "float32")[0]) for s in losses]
+    for s in losses:
+        be.dec_ref(s)
+    t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+    if dist:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    flops = 2.0 * GB * (784 * 2048 + 2048 * 2048 + 2048 * 10) * 3 - 2.0 * GB * 784 * 2048
+    tr.close()
+    be.dec_ref(sx)
+    be.dec_ref(sy)
+    return {"steps_per_s": steps / ms * 1e3, "ms_per_step": ms / steps, "global_batch": GB, "local_batch": local,
+            "tflops_algorithmic": flops * steps / ms / 1e9, "scaling": "strong", "launches_per_step": launches / steps,
+            "allreduce_bytes": 4 * sum(mlp.leaf_sizes(dims)), "loss_first": vals[0], "loss_last": vals[-1],
+            "gemm": "3xTF32 on tcgen05 (f32 accuracy), f32 accumulate"}
+
+
 def cpu_baseline(prog_factory, budget_s=10.0, threads=1):
     """The oracle (port of the reference's Wasm backend arithmetic) on a bounded sample of rows."""
     import oracle
@@ -344,6 +392,10 @@ def main():
         if world == 1 and not args.skip_extras:
             line["configs"] = other_configs(be, peaks)
             line["cpu_baseline"] = cpu_baseline(None, budget_s=10.0, threads=1)
+    if not args.skip_extras:
+        train = mlp_train(be, rank, world, dist)
+        if line:
+            line["mlp_train"] = train
     for s in (sx, si):
         be.dec_ref(s)
     be.host_free(x_host)

@@ -275,6 +275,15 @@ LoadKind classify_load(const Node& nd, const std::optional<Affine>& ix, int var,
 struct Builder {
   const KernelIR& k;
   const Options& opt;
+
+  // Source header: the prelude, with the bit-faithful transcendentals selected for kernels small
+  // enough to be latency-bound (and for all kernels when asked).
+  std::string header() const {
+    const double work = (double)k.size * (k.has_red ? (double)k.red_size : 1.0);
+    const bool exact = opt.exact_math == 1 || (opt.exact_math < 0 && work < opt.exact_math_work);
+    return std::string(exact ? "#define JX_EXACT_TRANSCENDENTALS 1\n" : "") + kPrelude;
+  }
+
   Analysis an_exp, an_epi;
   uint32_t out_dt;
 
@@ -360,7 +369,7 @@ struct Builder {
     const size_t root = k.exp.size() - 1;
 
     std::ostringstream os;
-    os << kPrelude;
+    os << header();
     os << "extern \"C\" __global__ void __launch_bounds__(" << T << ") jx_kernel(" << params() << ") {\n";
     if (nvec > 0) {
       std::map<size_t, std::string> ov;
@@ -496,7 +505,7 @@ struct Builder {
     for (size_t i = 0; i < k.exp.size(); i++) (an_exp.dep_r[i] ? inner : hoist)[i] = 1;
 
     std::ostringstream os;
-    os << kPrelude;
+    os << header();
     os << "extern \"C\" __global__ void __launch_bounds__(" << T << ") jx_kernel(" << params() << ") {\n";
     os << "  const int lane = threadIdx.x % " << TPR << ", rowc = threadIdx.x / " << TPR << ";\n";
     os << "  const long long gl = (long long)blockIdx.x * " << RPC << " + rowc;\n";
@@ -601,7 +610,7 @@ struct Builder {
     std::vector<char> all(k.exp.size(), 1);
 
     std::ostringstream os;
-    os << kPrelude;
+    os << header();
     os << "extern \"C\" __global__ void __launch_bounds__(" << T << ") jx_kernel(" << params() << ") {\n";
     os << "  const int tx = threadIdx.x % " << TX << ", ty = threadIdx.x / " << TX << ";\n";
     os << "  const int gv = blockIdx.x * " << TX << " + tx;\n  const bool active = gv < " << nvec << ";\n";
@@ -768,7 +777,7 @@ struct Builder {
     p.algo_flops = 2.0 * g.M * g.N * g.K * g.batch;
     const int BM = 128, BN = 128, BK = 16, T = 256;
     std::ostringstream os;
-    os << kPrelude;
+    os << header();
     os << "#define BM " << BM << "\n#define BN " << BN << "\n#define BK " << BK << "\n";
     os << "#define GM " << g.M << "\n#define GN " << g.N << "\n#define GK " << g.K << "\n";
     os << "#define OFFA " << g.offA << "LL\n#define SAM " << g.sAm << "LL\n#define SAK " << g.sAk << "LL\n#define SAB " << g.sAb << "LL\n";

@@ -62,6 +62,8 @@ struct Options {
   int gemm_min_dim = 32;      // below this M or N a GEMM-shaped kernel stays on the reduce skeletons
   bool allow_tc = true;       // tcgen05 path allowed (JAXCUDA_NO_TC=1 clears it)
   int force_skeleton = -1;    // tests: force SK_REDUCE_ROW / SK_REDUCE_COL / SK_GEMM_FFMA
+  int exact_math = -1;        // 1: bit-faithful exp everywhere, 0: fast everywhere, -1: exact below exact_math_work
+  double exact_math_work = 1 << 20;  // element evaluations (size x K) under which a kernel is latency-bound anyway
   int row_tpr = 0;            // threads per output row in the row-reduce skeleton (0: chosen from K)
   int row_unroll = 0;         // vector loads in flight per thread in the row-reduce loop (0: trip count, at most 4)
   int col_threads = 128;      // CTA size of the column-reduce skeleton

@@ -118,6 +118,7 @@ __device__ __forceinline__ u64 operand_desc(u32 base, int kk, int mn_major) {
 #define NUM_TILES (TILES_M * TILES_N * GBATCH)
 #define K_BLOCKS ((GK + BK - 1) / BK)
 #define TMEM_COLS (2 * BN)
+#define NCHUNK ((K_BLOCKS + CHUNK_KB - 1) / CHUNK_KB)
 #define IDESC ((1u << 4) | ((KIND == 2 ? 2u : 0u) << 7) | ((KIND == 2 ? 2u : 0u) << 10) | ((u32)A_MN << 15) | \
                ((u32)B_MN << 16) | ((u32)(BN >> 3) << 17) | ((u32)(BM >> 4) << 24))
 
@@ -202,48 +203,82 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
+    // A tile's K loop is cut into NCHUNK chunks of CHUNK_KB k-blocks; every chunk starts a fresh
+    // accumulator (alternating between the two TMEM buffers) that the epilogue warps fold into
+    // registers.  Tensor cores add into the accumulator with truncation, a bias that grows with the
+    // length of the chain; short chains joined by round-to-nearest f32 adds keep f32 accuracy.
     if (lane == 0) {
-      int it = 0, tile_i = 0;
-      for (int t = blockIdx.x; t < NUM_TILES && !failed; t += gridDim.x, tile_i++) {
-        const int acc = tile_i & 1;
-        if (tile_i >= 2 && !mbar_wait(tempty(acc), ((tile_i >> 1) + 1) & 1, status)) { atomicCAS((int*)status_ptr, 0, 2); failed = true; break; }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const u32 d = tmem_base + acc * BN;
-        for (int kb = 0; kb < K_BLOCKS; kb++, it++) {
-          const int s = it % STAGES;
-          if (!mbar_wait(full(s), (it / STAGES) & 1, status)) { atomicCAS((int*)status_ptr, 0, 3); failed = true; break; }
+      int it = 0, cc = 0;
+      for (int t = blockIdx.x; t < NUM_TILES && !failed; t += gridDim.x) {
+        for (int ch = 0; ch < NCHUNK && !failed; ch++, cc++) {
+          const int acc = cc & 1;
+          if (cc >= 2 && !mbar_wait(tempty(acc), ((cc >> 1) + 1) & 1, status)) { atomicCAS((int*)status_ptr, 0, 2); failed = true; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const u32 sa = smem_base + s * STAGE_BYTES, sb = sa + NPLANES * A_BYTES;
-          #pragma unroll
-          for (int kk = 0; kk < 4; kk++) {
-            const u32 first = (kb | kk) ? 1u : 0u;
+          const u32 d = tmem_base + acc * BN;
+          const int kb_end = (ch + 1) * CHUNK_KB < K_BLOCKS ? (ch + 1) * CHUNK_KB : K_BLOCKS;
+          for (int kb = ch * CHUNK_KB; kb < kb_end; kb++, it++) {
+            const int s = it % STAGES;
+            if (!mbar_wait(full(s), (it / STAGES) & 1, status)) { atomicCAS((int*)status_ptr, 0, 3); failed = true; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const u32 sa = smem_base + s * STAGE_BYTES, sb = sa + NPLANES * A_BYTES;
+            #pragma unroll
+            for (int kk = 0; kk < 4; kk++) {
+              const u32 first = (kb != ch * CHUNK_KB || kk) ? 1u : 0u;
 #if KIND == 1
-            umma(d, operand_desc(sa, kk, A_MN), operand_desc(sb, kk, B_MN), IDESC, first);
+              umma(d, operand_desc(sa, kk, A_MN), operand_desc(sb, kk, B_MN), IDESC, first);
 #else
-            // 3xTF32: small cross terms first, then the main product
-            umma(d, operand_desc(sa + A_BYTES, kk, A_MN), operand_desc(sb, kk, B_MN), IDESC, first);
-            umma(d, operand_desc(sa, kk, A_MN), operand_desc(sb + B_BYTES, kk, B_MN), IDESC, 1u);
-            umma(d, operand_desc(sa, kk, A_MN), operand_desc(sb, kk, B_MN), IDESC, 1u);
+              // 3xTF32: small cross terms first, then the main product
+              umma(d, operand_desc(sa + A_BYTES, kk, A_MN), operand_desc(sb, kk, B_MN), IDESC, first);
+              umma(d, operand_desc(sa, kk, A_MN), operand_desc(sb + B_BYTES, kk, B_MN), IDESC, 1u);
+              umma(d, operand_desc(sa, kk, A_MN), operand_desc(sb, kk, B_MN), IDESC, 1u);
 #endif
+            }
+            umma_commit(empty(s));            // the stage is free once these MMAs have read it
           }
-          umma_commit(empty(s));            // the stage is free once these MMAs have read it
+          if (!failed) umma_commit(tfull(acc));  // this chunk's accumulator is complete
         }
-        if (!failed) umma_commit(tfull(acc));  // accumulator complete
       }
     }
   } else {
     // ---------------------------------------------------------------- epilogue warps 2..5
     const int q = warp & 3;                 // TMEM lane quarter this warp may access
-    int tile_i = 0;
-    for (int t = blockIdx.x; t < NUM_TILES && !failed; t += gridDim.x, tile_i++) {
-      const int acc_i = tile_i & 1;
+    int cc = 0;
+    for (int t = blockIdx.x; t < NUM_TILES && !failed; t += gridDim.x) {
       int b, m_blk, n_blk;
       tile_coords(t, b, m_blk, n_blk);
-      if (!mbar_wait(tfull(acc_i), (tile_i >> 1) & 1, status)) { atomicCAS((int*)status_ptr, 0, 4); failed = true; break; }
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int m = m_blk * BM + q * 32 + lane;
+#if NCHUNK > 1
+      float sum[BN];
+      #pragma unroll
+      for (int j = 0; j < BN; j++) sum[j] = 0.0f;
+      for (int ch = 0; ch < NCHUNK - 1 && !failed; ch++, cc++) {
+        const int acc_i = cc & 1;
+        if (!mbar_wait(tfull(acc_i), (cc >> 1) & 1, status)) { atomicCAS((int*)status_ptr, 0, 4); failed = true; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const u32 trow = tmem_base + ((u32)(q * 32) << 16) + acc_i * BN;
+        #pragma unroll
+        for (int c = 0; c < BN / 16; c++) {
+          u32 v[16];
+          tmem_ld16(trow + c * 16, v);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          #pragma unroll
+          for (int j = 0; j < 16; j++) sum[c * 16 + j] += __uint_as_float(v[j]);
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty(acc_i));
+      }
+      if (failed) break;
+#endif
+      const int acc_i = cc & 1;
+      if (!mbar_wait(tfull(acc_i), (cc >> 1) & 1, status)) { atomicCAS((int*)status_ptr, 0, 4); failed = true; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const u32 trow = tmem_base + ((u32)(q * 32) << 16) + acc_i * BN;
+#if NCHUNK > 1
+      #pragma unroll
+#else
       #pragma unroll 1
+#endif
       for (int c = 0; c < BN / 16; c++) {
         u32 v[16];
         tmem_ld16(trow + c * 16, v);
@@ -255,7 +290,11 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
           for (int j = 0; j < 16; j++) {
             const int n = n0 + j;
             const int gidx = (int)(((i64)b * GM + m) * GN + (n < GN ? n : GN - 1));
+#if NCHUNK > 1
+            const float acc = sum[c * 16 + j] + __uint_as_float(v[j]);
+#else
             const float acc = __uint_as_float(v[j]);
+#endif
 #define JX_DST res[j]
 JX_EPILOGUE
 #undef JX_DST
@@ -273,6 +312,7 @@ JX_EPILOGUE
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty(acc_i));
+      cc++;
     }
   }
   if (*status != 0) {
@@ -354,6 +394,10 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
   os << "#define KIND " << kind << "\n#define ELEM " << e << "\n#define BM " << BM << "\n#define BN " << BN << "\n";
   os << "#define STAGES " << stages << "\n#define A_MN " << (a_mn ? 1 : 0) << "\n#define B_MN " << (b_mn ? 1 : 0) << "\n";
   os << "#define GM " << g.M << "\n#define GN " << g.N << "\n#define GK " << g.K << "\n#define GBATCH " << g.batch << "\n";
+  // k-blocks accumulated in tensor memory before the partial sum is folded into registers with a
+  // rounded f32 add: 256 elements of K for 3xTF32; the whole K for f16 (its f16 result absorbs the bias)
+  const int64_t k_blocks = (g.K + bk - 1) / bk;
+  os << "#define CHUNK_KB " << (kind == 2 ? 8 : k_blocks) << "\n";
   os << "#define LEN_A " << g.lenA << "LL\n#define LEN_B " << g.lenB << "LL\n";
   os << "#define LEN_A_PAD " << pad64(g.lenA) << "LL\n#define LEN_B_PAD " << pad64(g.lenB) << "LL\n";
   const char* out_t = k.out_dtype() == JAXCUDA_F16 ? "jx_half" : k.out_dtype() == JAXCUDA_F64 ? "double"

@@ -69,14 +69,34 @@ __device__ __forceinline__ float jx_fmod(float a, float b) { return a - truncf(a
 __device__ __forceinline__ double jx_didiv(double a, double b) { return trunc(a / b); }
 __device__ __forceinline__ double jx_dmod(double a, double b) { return a - trunc(a / b) * b; }
 
-// e^x.  The reference computes k = nearest(x / ln2), a degree-6 Taylor polynomial in x - k ln2 and
-// a scale by 2^k, returning +Inf for k > 127 and 0 for k < -126 (builtins.ts:25-90; relative
-// error below 2e-7).  Here the same function is 2^(x log2 e) on the special-function unit:
-// t = rn(x log2 e), the rounding residual e of that product recovered exactly with two FMAs,
-// ex2.approx(t) (relative error 2^-22) and a first-order correction 2^e = 1 + e ln2, with the
-// reference's overflow and underflow thresholds kept (t > 127.5 and t < -126.5).  Ten issue
-// slots instead of about twenty, which is what keeps exp-fused kernels memory-bound.
-__device__ __forceinline__ float jx_exp(float x) {
+// e^x, two versions.  The reference computes k = nearest(x / ln2), r = x - k ln2, a degree-6
+// Taylor polynomial in r (Horner, every step rounded) and a scale by 2^k, with +Inf for k > 127
+// and 0 for k < -126 (builtins.ts:25-90).
+//
+// jx_exp_exact repeats those operations one by one with no fused multiply-add, so it returns the
+// reference's bits.  It matters where a result is fed to a cancellation -- Adam's 1 - b^t turns a
+// single ulp of exp into 1e-4 of the bias correction.
+__device__ __forceinline__ float jx_exp_exact(float x) {
+  const float kf = rintf(__fmul_rn(x, 1.4426950408889634f));
+  const int k = __float2int_rz(kf);
+  const float r = __fsub_rn(x, __fmul_rn(kf, 0.6931471805599453f));
+  float p = 1.0f / 720.0f;
+  p = __fadd_rn(__fmul_rn(p, r), 1.0f / 120.0f);
+  p = __fadd_rn(__fmul_rn(p, r), 1.0f / 24.0f);
+  p = __fadd_rn(__fmul_rn(p, r), 1.0f / 6.0f);
+  p = __fadd_rn(__fmul_rn(p, r), 0.5f);
+  p = __fadd_rn(__fmul_rn(p, r), 1.0f);
+  p = __fadd_rn(__fmul_rn(p, r), 1.0f);
+  float res = __fmul_rn(p, __int_as_float((k + 127) << 23));
+  res = (k > 127) ? JX_INF : res;
+  return (k < -126) ? 0.0f : res;   // NaN: k = 0 and r = NaN, so res is NaN
+}
+// jx_exp_fast is the same function as 2^(x log2 e) on the special-function unit: t = rn(x log2 e),
+// the rounding residual of that product recovered exactly with two FMAs, ex2.approx(t) and the
+// first-order correction 2^e = 1 + e ln2, with the reference's overflow and underflow thresholds
+// (t > 127.5, t < -126.5).  Within 5e-7 relative of the exact version in ten issue slots instead
+// of about twenty-five, which is what keeps exp-fused streaming kernels memory-bound.
+__device__ __forceinline__ float jx_exp_fast(float x) {
   const float t = x * 1.4426950408889634f;
   float e = fmaf(x, 1.4426950408889634f, -t);
   e = fmaf(x, 1.925963033500978e-8f, e);        // log2 e - float(log2 e)
@@ -86,6 +106,11 @@ __device__ __forceinline__ float jx_exp(float x) {
   res = (t > 127.5f) ? JX_INF : res;
   return (t < -126.5f) ? 0.0f : res;
 }
+#ifdef JX_EXACT_TRANSCENDENTALS
+#define jx_exp jx_exp_exact
+#else
+#define jx_exp jx_exp_fast
+#endif
 
 // ln x: exponent extraction plus the atanh series in t = (m-1)/(m+1) (builtins.ts:99-193).
 __device__ __forceinline__ float jx_log(float x) {

@@ -1,0 +1,118 @@
+"""MLP programs on the GPU through the C ABI: per-example gradients under vmap (config 4) and the
+Adam training step (config 5), checked against the oracle replaying the same kernel lists, and at
+full shard size against a float64 model evaluated with torch on the same GPU."""
+import numpy as np
+import pytest
+
+from jax_js_b200 import DType, mlp
+
+from oracle_backend import OracleBackend
+from util import assert_close
+
+pytestmark = pytest.mark.gpu
+F32 = DType.Float32
+
+
+def _data(batch, n_in, classes, seed=0):
+    rng = np.random.default_rng(seed)
+    return rng.uniform(0, 1, (batch, n_in)).astype(np.float32), rng.integers(0, classes, batch).astype(np.int32)
+
+
+def test_adam_training_matches_oracle_after_1_and_10_steps(backend):
+    dims, B = [784, 256, 256, 10], 512
+    x, y = _data(B, dims[0], dims[-1])
+    # two oracles: the Wasm backend without and with relaxed_madd (src/backend/wasm/codegen.ts:318-322);
+    # both are the reference, and their distance after n Adam steps is the reference's own noise floor
+    trainers = []
+    for be in (backend, OracleBackend(), OracleBackend(fma=True)):
+        tr = mlp.MlpTrainer(be, dims, B, B)
+        trainers.append((be, tr, be.put(x), be.put(y)))
+    for step in range(1, 11):
+        losses = []
+        for be, tr, sx, sy in trainers:
+            s = tr.step(sx, sy)
+            losses.append(float(be.get(s, "float32")[0]))
+            be.dec_ref(s)
+        # f32, GEMM-dominated: 1e-4 relative (BASELINE north_star).  Adam divides by sqrt(nu), which
+        # amplifies last-bit differences where gradients are of the order of eps, so trajectories of
+        # the reference's own two accumulation modes drift apart; the bar never goes below that drift.
+        floor = 3 * abs(losses[2] - losses[1])
+        assert abs(losses[0] - losses[1]) <= max(1e-4 * abs(losses[1]), floor), (step, losses)
+        if step == 1:
+            assert abs(losses[0] - losses[1]) <= 1e-5 * abs(losses[1]), losses
+        if step in (1, 10):
+            (b0, t0, _, _), (b1, t1, _, _), (b2, t2, _, _) = trainers
+            for s0, s1, s2 in zip(t0.params, t1.params, t2.params):
+                want, got = b1.get(s1, "float32").astype(np.float64), b0.get(s0, "float32").astype(np.float64)
+                alt = b2.get(s2, "float32").astype(np.float64)
+                tol = 1e-4 * np.abs(want).max()
+                err, ref_err = np.abs(got - want), np.abs(alt - want)
+                # After one step: all but a sliver within 1e-4 of the leaf's scale.  Later a second
+                # mechanism appears that no implementation can avoid: a hidden unit whose
+                # pre-activation lies within rounding of zero switches its ReLU differently under a
+                # different summation order (about 1e-6 of the units per step here), which changes one
+                # whole column of dW by a few per cent of an update.  So after ten steps the bar is:
+                # the typical element still far inside 1e-4 of the scale, at most 5 % of a leaf beyond
+                # it, and nothing off by more than one full update per step.
+                frac = (err > tol).mean()
+                assert frac <= (1e-4 if step == 1 else 0.05) + 2 * (ref_err > tol).mean(), (step, frac)
+                assert np.median(err) <= 0.1 * tol, (step, np.median(err))
+                assert err.max() <= step * 1e-3 * 1.01, f"params after step {step}"
+    for be, tr, sx, sy in trainers:
+        tr.close()
+        be.dec_ref(sx)
+        be.dec_ref(sy)
+
+
+def test_per_example_gradients_config4(backend):
+    dims, B = [784, 1024, 10], 64
+    x, y = _data(B, dims[0], dims[-1], 1)
+    params = mlp.init_params(dims, 0)
+    params[1] = params[1] + 0.05   # non-zero biases so that bias handling is exercised
+    prog = mlp.mlp_grad_program(B, dims, per_example=True)
+    outs = []
+    for be in (backend, OracleBackend()):
+        slots = [be.put(x), be.put(y), be.put(np.eye(10, dtype=np.float32))] + [be.put(p) for p in params]
+        res = prog.execute(be, slots)
+        outs.append([be.get(s, "float32") for s in res])
+        for s in slots + res:
+            be.dec_ref(s)
+    names = ["loss", "dW1", "db1", "dW2", "db2"]
+    for name, got, want in zip(names, outs[0], outs[1]):
+        # the gradients are products of GEMM-like intermediates: 1e-4 of the leaf's scale
+        assert_close(got, want, 1e-4, np.abs(want).max() if name != "loss" else None, name)
+    assert outs[0][1].size == 784 * 1024 * 64
+
+
+def test_config5_shard_gradients_against_float64(backend):
+    import torch
+    dims, B, GB = [784, 2048, 2048, 10], 8192, 65536
+    x, y = _data(B, dims[0], dims[-1], 2)
+    params = mlp.init_params(dims, 0)
+    prog = mlp.mlp_grad_program(B, dims, global_batch=GB)
+    slots = [backend.put(x), backend.put(y), backend.put(np.eye(10, dtype=np.float32))] + [backend.put(p) for p in params]
+    res = prog.execute(backend, slots)
+    got = [backend.get(s, "float32") for s in res]
+    for s in slots + res:
+        backend.dec_ref(s)
+    dev = torch.device("cuda", backend.device)
+    tp = [torch.tensor(p, dtype=torch.float64, device=dev, requires_grad=True) for p in params]
+    h = torch.tensor(x, dtype=torch.float64, device=dev)
+    for l in range(3):
+        h = h @ tp[2 * l] + tp[2 * l + 1]
+        if l < 2:
+            h = torch.relu(h)
+    loss = torch.nn.functional.cross_entropy(h, torch.tensor(y, dtype=torch.long, device=dev), reduction="sum") / GB
+    loss.backward()
+    assert abs(got[0][0] - loss.item()) <= 1e-4 * abs(loss.item())
+    for name, g, t in zip(mlp.param_order(3), got[1:], tp):
+        want = t.grad.detach().cpu().numpy().reshape(-1)
+        # A float64 forward pass switches a few ReLUs (pre-activations within rounding of zero)
+        # differently from any f32 pass; each such unit changes one column of dW by up to ~1e-3 of
+        # the leaf's scale.  Bar: 1e-4 of the scale for 95 % of every leaf, 1e-2 for all of it, and
+        # the mean error far inside the bar.
+        err = np.abs(g.astype(np.float64) - want)
+        scale = np.abs(want).max()
+        assert (err <= 1e-4 * scale).mean() >= 0.95, f"d{name}"
+        assert err.max() <= 1e-2 * scale, f"d{name}"
+        assert err.mean() <= 3e-5 * scale, f"d{name}"
