@@ -370,7 +370,7 @@ struct Builder {
 
     std::ostringstream os;
     os << header();
-    os << "extern \"C\" __global__ void __launch_bounds__(" << T << ") jx_kernel(" << params() << ") {\n";
+    os << "extern \"C\" __global__ void __launch_bounds__(" << T << ") jx_elementwise(" << params() << ") {\n";
     if (nvec > 0) {
       std::map<size_t, std::string> ov;
       std::ostringstream decl, fetch;
@@ -413,7 +413,7 @@ struct Builder {
     os << "}\n";
     p.source = os.str();
     Stage st;
-    st.entry = "jx_kernel";
+    st.entry = "jx_elementwise";
     int64_t blocks = nvec > 0 ? (nvec + (int64_t)T * ILP - 1) / ((int64_t)T * ILP) : 1;
     blocks = std::min<int64_t>(blocks, (int64_t)opt.sm_count * opt.ew_blocks_per_sm);
     st.grid[0] = (unsigned)std::max<int64_t>(1, blocks);
@@ -506,7 +506,7 @@ struct Builder {
 
     std::ostringstream os;
     os << header();
-    os << "extern \"C\" __global__ void __launch_bounds__(" << T << ") jx_kernel(" << params() << ") {\n";
+    os << "extern \"C\" __global__ void __launch_bounds__(" << T << ") jx_reduce_row(" << params() << ") {\n";
     os << "  const int lane = threadIdx.x % " << TPR << ", rowc = threadIdx.x / " << TPR << ";\n";
     os << "  const long long gl = (long long)blockIdx.x * " << RPC << " + rowc;\n";
     os << "  const bool active = gl < " << k.size << "LL;\n";
@@ -559,7 +559,7 @@ struct Builder {
     if (splits > 1) emit_finish_kernel(os, splits);
     p.source = os.str();
     Stage st;
-    st.entry = "jx_kernel";
+    st.entry = "jx_reduce_row";
     st.grid[0] = (unsigned)row_blocks;
     st.grid[1] = (unsigned)splits;
     st.block[0] = T;
@@ -611,7 +611,7 @@ struct Builder {
 
     std::ostringstream os;
     os << header();
-    os << "extern \"C\" __global__ void __launch_bounds__(" << T << ") jx_kernel(" << params() << ") {\n";
+    os << "extern \"C\" __global__ void __launch_bounds__(" << T << ") jx_reduce_col(" << params() << ") {\n";
     os << "  const int tx = threadIdx.x % " << TX << ", ty = threadIdx.x / " << TX << ";\n";
     os << "  const int gv = blockIdx.x * " << TX << " + tx;\n  const bool active = gv < " << nvec << ";\n";
     os << "  const int g0 = active ? gv * " << V << " : 0;\n";
@@ -683,7 +683,7 @@ struct Builder {
     os << "}\n";
     p.source = os.str();
     Stage st;
-    st.entry = "jx_kernel";
+    st.entry = "jx_reduce_col";
     st.grid[0] = (unsigned)std::max<int64_t>(1, gblocks);
     st.grid[1] = (unsigned)splits;
     st.block[0] = T;
@@ -788,7 +788,7 @@ struct Builder {
     // thread -> tile element mapping for the global loads: adjacent threads walk the contiguous axis
     const bool a_kcontig = std::llabs(g.sAk) <= std::llabs(g.sAm);
     const bool b_kcontig = std::llabs(g.sBk) <= std::llabs(g.sBn);
-    os << "extern \"C\" __global__ void __launch_bounds__(" << T << ") jx_kernel(" << params() << ") {\n";
+    os << "extern \"C\" __global__ void __launch_bounds__(" << T << ") jx_gemm_ffma(" << params() << ") {\n";
     os << R"(  __shared__ __align__(16) float As[2][BK][BM + 4];
   __shared__ __align__(16) float Bs[2][BK][BN + 4];
   const int t = threadIdx.x;
@@ -856,7 +856,7 @@ struct Builder {
     os << "    }\n  }\n}\n";
     p.source = os.str();
     Stage st;
-    st.entry = "jx_kernel";
+    st.entry = "jx_gemm_ffma";
     st.grid[0] = (unsigned)((g.N + BN - 1) / BN);
     st.grid[1] = (unsigned)((g.M + BM - 1) / BM);
     st.grid[2] = (unsigned)g.batch;
