@@ -41,6 +41,9 @@ ROWS, COLS = 8192, 4096
 WORKLOAD = f"softmax_lse_argmax_f32_{ROWS}x{COLS}"
 METRIC = "fused-kernel algorithmic HBM throughput (softmax + logsumexp + argmax program)"
 UNIT = "GB/s"
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the longest kernel (K2, exp(x - max)) from
+# the committed ncu capture of this same workload (profiles/softmax_lse_argmax_f32_8192x4096.md)
+NCU_TRAFFIC_K2_BYTES = 215.2e6
 
 
 def measured_peaks():
@@ -414,7 +417,7 @@ def _run():
                     "steps": e2e_steps, "ms_per_step": float(e2e_t.item()) / e2e_steps * 1e3},
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "achieved": top["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": top["gbs"] / peaks["hbm_gbs"], "traffic": None, "kernel": top["kernel"],
+                         "frac": top["gbs"] / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_K2_BYTES, "kernel": top["kernel"],
                          "kernel_output": top["out"], "ms": top["ms"], "algorithmic_bytes": top["bytes"],
                          "peak_source": peaks["source"]},
             "kernels": [{k: (round(v, 5) if isinstance(v, float) else v) for k, v in pk.items()} for pk in per_kernel],

@@ -1,0 +1,127 @@
+// Node-API addon: forwards the calls of jax_js_b200/ts/cuda.ts to libjaxcuda.so (include/jaxcuda.h).
+// Build where Node headers exist:
+//   g++ -std=c++17 -shared -fPIC -I$(node -p "require('node-addon-api').include_dir") -I<node>/include/node \
+//       -Iinclude addon.cc -Ljax_js_b200 -ljaxcuda -Wl,-rpath,'$ORIGIN' -o jaxcuda_addon.node
+// Not compiled in this repository: the build image has neither Node nor node_api.h.
+#include <napi.h>
+
+#include <vector>
+
+#include "jaxcuda.h"
+
+namespace {
+
+jaxcuda_ctx* Ctx(const Napi::Value& v) {
+  bool lossless;
+  return reinterpret_cast<jaxcuda_ctx*>(v.As<Napi::BigInt>().Uint64Value(&lossless));
+}
+jaxcuda_exe* Exe(const Napi::Value& v) {
+  bool lossless;
+  return reinterpret_cast<jaxcuda_exe*>(v.As<Napi::BigInt>().Uint64Value(&lossless));
+}
+Napi::Value Handle(Napi::Env env, void* p) { return Napi::BigInt::New(env, (uint64_t)(uintptr_t)p); }
+
+void Throw(Napi::Env env, jaxcuda_ctx* ctx) { throw Napi::Error::New(env, jaxcuda_last_error(ctx)); }
+
+Napi::Value Create(const Napi::CallbackInfo& info) {
+  jaxcuda_ctx* ctx = nullptr;
+  if (jaxcuda_create(info[0].As<Napi::Number>().Int32Value(), &ctx) != JAXCUDA_OK) Throw(info.Env(), nullptr);
+  return Handle(info.Env(), ctx);
+}
+void Destroy(const Napi::CallbackInfo& info) { jaxcuda_destroy(Ctx(info[0])); }
+Napi::Value LastError(const Napi::CallbackInfo& info) { return Napi::String::New(info.Env(), jaxcuda_last_error(Ctx(info[0]))); }
+
+Napi::Value Malloc(const Napi::CallbackInfo& info) {
+  jaxcuda_ctx* ctx = Ctx(info[0]);
+  const size_t bytes = (size_t)info[1].As<Napi::Number>().Int64Value();
+  const void* init = nullptr;
+  size_t init_bytes = 0;
+  if (info.Length() > 2 && info[2].IsTypedArray()) {
+    auto a = info[2].As<Napi::Uint8Array>();
+    init = a.Data();
+    init_bytes = a.ByteLength();
+  }
+  jaxcuda_slot slot = 0;
+  if (jaxcuda_malloc(ctx, bytes, init, init_bytes, &slot) != JAXCUDA_OK) Throw(info.Env(), ctx);
+  return Napi::Number::New(info.Env(), slot);
+}
+Napi::Value IncRef(const Napi::CallbackInfo& info) {
+  return Napi::Number::New(info.Env(), jaxcuda_incref(Ctx(info[0]), info[1].As<Napi::Number>().Uint32Value()));
+}
+Napi::Value DecRef(const Napi::CallbackInfo& info) {
+  return Napi::Number::New(info.Env(), jaxcuda_decref(Ctx(info[0]), info[1].As<Napi::Number>().Uint32Value()));
+}
+Napi::Value Read(const Napi::CallbackInfo& info) {
+  jaxcuda_ctx* ctx = Ctx(info[0]);
+  const jaxcuda_slot slot = info[1].As<Napi::Number>().Uint32Value();
+  const size_t start = (size_t)info[2].As<Napi::Number>().Int64Value();
+  int64_t count = info[3].As<Napi::Number>().Int64Value();
+  size_t size = 0;
+  if (jaxcuda_slot_size(ctx, slot, &size) != JAXCUDA_OK) Throw(info.Env(), ctx);
+  if (count < 0) count = (int64_t)(size - start);
+  auto out = Napi::Uint8Array::New(info.Env(), (size_t)count);
+  if (jaxcuda_read(ctx, slot, start, (size_t)count, out.Data()) != JAXCUDA_OK) Throw(info.Env(), ctx);
+  return out;
+}
+Napi::Value PrepareKernel(const Napi::CallbackInfo& info) {
+  jaxcuda_ctx* ctx = Ctx(info[0]);
+  auto image = info[1].As<Napi::Uint8Array>();
+  bool lossless;
+  const uint64_t hash = info[2].As<Napi::BigInt>().Uint64Value(&lossless);
+  jaxcuda_exe* exe = nullptr;
+  if (jaxcuda_prepare_kernel(ctx, image.Data(), image.ByteLength(), hash, &exe) != JAXCUDA_OK) Throw(info.Env(), ctx);
+  return Handle(info.Env(), exe);
+}
+Napi::Value PrepareRoutine(const Napi::CallbackInfo& info) {
+  jaxcuda_ctx* ctx = Ctx(info[0]);
+  const std::string name = info[1].As<Napi::String>();
+  auto type = info[2].As<Napi::Object>();
+  static const char* kDtypes[] = {"float32", "int32", "uint32", "bool", "float16", "float64"};
+  auto dtypes = [&](const char* key, std::vector<int32_t>& out) {
+    auto arr = type.Get(key).As<Napi::Array>();
+    for (uint32_t i = 0; i < arr.Length(); i++) {
+      const std::string s = arr.Get(i).As<Napi::String>();
+      for (int d = 0; d < 6; d++) if (s == kDtypes[d]) out.push_back(d);
+    }
+  };
+  auto shapes = [&](const char* key, std::vector<int32_t>& ranks, std::vector<int64_t>& flat) {
+    auto arr = type.Get(key).As<Napi::Array>();
+    for (uint32_t i = 0; i < arr.Length(); i++) {
+      auto shape = arr.Get(i).As<Napi::Array>();
+      ranks.push_back((int32_t)shape.Length());
+      for (uint32_t j = 0; j < shape.Length(); j++) flat.push_back(shape.Get(j).As<Napi::Number>().Int64Value());
+    }
+  };
+  std::vector<int32_t> idt, odt, irk, ork;
+  std::vector<int64_t> ish, osh;
+  dtypes("inputDtypes", idt); dtypes("outputDtypes", odt);
+  shapes("inputShapes", irk, ish); shapes("outputShapes", ork, osh);
+  jaxcuda_routine_type rt{(int)irk.size(), (int)ork.size(), idt.data(), irk.data(), ish.data(), odt.data(), ork.data(), osh.data()};
+  const std::string params = info[3].As<Napi::String>();
+  jaxcuda_exe* exe = nullptr;
+  if (jaxcuda_prepare_routine(ctx, name.c_str(), &rt, params.c_str(), &exe) != JAXCUDA_OK) Throw(info.Env(), ctx);
+  return Handle(info.Env(), exe);
+}
+Napi::Value Dispatch(const Napi::CallbackInfo& info) {
+  auto in = info[2].As<Napi::Uint32Array>(), out = info[3].As<Napi::Uint32Array>();
+  return Napi::Number::New(info.Env(), jaxcuda_dispatch(Ctx(info[0]), Exe(info[1]), in.Data(), (int)in.ElementLength(),
+                                                        out.Data(), (int)out.ElementLength()));
+}
+
+Napi::Object Init(Napi::Env env, Napi::Object exports) {
+  exports.Set("create", Napi::Function::New(env, Create));
+  exports.Set("destroy", Napi::Function::New(env, Destroy));
+  exports.Set("lastError", Napi::Function::New(env, LastError));
+  exports.Set("malloc", Napi::Function::New(env, Malloc));
+  exports.Set("incref", Napi::Function::New(env, IncRef));
+  exports.Set("decref", Napi::Function::New(env, DecRef));
+  exports.Set("read", Napi::Function::New(env, Read));
+  exports.Set("prepareKernel", Napi::Function::New(env, PrepareKernel));
+  exports.Set("prepareRoutine", Napi::Function::New(env, PrepareRoutine));
+  exports.Set("dispatch", Napi::Function::New(env, Dispatch));
+  return exports;
+}
+
+}  // namespace
+
+NODE_API_MODULE(jaxcuda_addon, Init)
