@@ -45,7 +45,9 @@ def test_adam_training_matches_oracle_after_1_and_10_steps(backend):
             for s0, s1, s2 in zip(t0.params, t1.params, t2.params):
                 want, got = b1.get(s1, "float32").astype(np.float64), b0.get(s0, "float32").astype(np.float64)
                 alt = b2.get(s2, "float32").astype(np.float64)
-                tol = 1e-4 * np.abs(want).max()
+                # 1e-4 of the leaf's scale, but not finer than 2 % of one Adam update (lr = 1e-3): the
+                # bias leaves start at zero and are themselves only a few updates large
+                tol = max(1e-4 * np.abs(want).max(), 2e-5)
                 err, ref_err = np.abs(got - want), np.abs(alt - want)
                 # After one step: all but a sliver within 1e-4 of the leaf's scale.  Later a second
                 # mechanism appears that no implementation can avoid: a hidden unit whose
