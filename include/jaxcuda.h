@@ -134,6 +134,19 @@ int jaxcuda_comm_init(jaxcuda_ctx* ctx, int rank, int nranks, const void* id128)
 int jaxcuda_allreduce_sum_f32(jaxcuda_ctx* ctx, const jaxcuda_slot* slots, int n);
 int jaxcuda_comm_destroy(jaxcuda_ctx* ctx);
 
+/* Sort along the last axis of a contiguous [batch, n] device array without allocating anything.
+ * No counterpart in the reference.  It is for embedders that cannot let the library call
+ * cudaMalloc (all device memory already belongs to their own pool, or the device-wide
+ * synchronisation of an allocation is unacceptable inside a serving loop): the work buffer that
+ * jaxcuda_dispatch would take from the allocator is a fixed 16 MiB array inside the library image.
+ * x and y are device pointers (jaxcuda_slot_ptr), stream a cudaStream_t (jaxcuda_stream); the owning
+ * device must be current.  Limit: batch * next_pow2(n) <= 4 Mi keys (rows up to 32768 keys never
+ * touch the buffer); beyond it JAXCUDA_EINVAL with the reason in err.  The first call on a device
+ * looks the buffer up and belongs outside any stream capture; all calls share the buffer, so calls
+ * that overlap on the GPU race. */
+int jaxcuda_sort_no_alloc(void* stream, int dtype, const void* x, void* y, int64_t batch, int64_t n,
+                          char* err, size_t err_len);
+
 #ifdef __cplusplus
 }
 #endif

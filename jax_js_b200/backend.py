@@ -87,6 +87,7 @@ SYMBOLS = {
     "jaxcuda_comm_init": (_I, [_P, _I, _I, _P]),
     "jaxcuda_allreduce_sum_f32": (_I, [_P, ctypes.POINTER(_U32), _I]),
     "jaxcuda_comm_destroy": (_I, [_P]),
+    "jaxcuda_sort_no_alloc": (_I, [_P, _I, _P, _P, ctypes.c_int64, ctypes.c_int64, ctypes.c_char_p, _SZ]),
 }
 
 
@@ -314,6 +315,15 @@ class CudaBackend:
     def allreduce_sum_f32(self, slots: Sequence[int]) -> None:
         arr = (ctypes.c_uint32 * max(1, len(slots)))(*slots)
         self._check(self._lib.jaxcuda_allreduce_sum_f32(self._ctx, arr, len(slots)))
+
+    def sort_no_alloc(self, dtype: DType, x_slot: int, y_slot: int, batch: int, n: int) -> None:
+        """Sort rows of x_slot into y_slot through the entry point that allocates nothing (its
+        work buffer is a fixed array inside the library; see include/jaxcuda.h for the limit)."""
+        err = ctypes.create_string_buffer(256)
+        rc = self._lib.jaxcuda_sort_no_alloc(self.stream(), int(dtype), self.slot_ptr(x_slot), self.slot_ptr(y_slot),
+                                             batch, n, err, len(err))
+        if rc != OK:
+            _raise(rc, err.value.decode())
 
     # -- conveniences for tests and programs -------------------------------------------
     def put(self, array: np.ndarray) -> int:

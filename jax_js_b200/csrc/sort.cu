@@ -14,6 +14,7 @@
 // which makes the network's result the stable order.
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdio.h>
 
 #include "../../include/jaxcuda_ir.h"
 
@@ -221,4 +222,67 @@ extern "C" int jaxcuda_sort_launch(void* stream, int argsort, const void* x, voi
   if (batch == 0 || n == 0) return 0;
   return (int)(argsort ? jaxcuda_sort::run<true>(st, x, y, yi, dtype, batch, n, work, launches)
                        : jaxcuda_sort::run<false>(st, x, y, yi, dtype, batch, n, work, launches));
+}
+
+// ---- Sort without any allocation --------------------------------------------------------------
+//
+// jaxcuda_dispatch takes the work buffer of a large-row sort from the context's allocator, which
+// may call cudaMalloc.  Some embedders cannot afford that call: a process that has handed all of
+// the GPU's memory to its own pool (cudaMalloc then fails, or eats into a reserve), and serving
+// loops in which the implicit device-wide synchronisation of cudaMalloc is a latency spike.  For
+// them the same sort is offered over a work buffer that is part of the library image itself: a
+// fixed array in device global memory.  Every GPU that loads the library holds these 16 MiB until
+// the process exits, whether or not the entry point is ever called.
+#define JX_SORT_STATIC_ITEMS (4 * 1024 * 1024) /* padded keys: batch * next_pow2(n) may not exceed this */
+static __device__ __align__(256) uint32_t jx_sort_static_work[JX_SORT_STATIC_ITEMS];
+
+// In host code the array's name is only a handle for the runtime, not an address a kernel could
+// use; the device address is looked up once per device and cached here.
+static void* g_static_work_addr[64] = {};
+
+// Sorts each row of a contiguous [batch, n] array along the last axis (same order as the Sort
+// routine: numeric, -0 before +0, NaN last) from device pointer x to device pointer y, on `stream`,
+// without allocating host or device memory.  The device that owns x, y and the stream must be
+// current.  dtype is a jaxcuda_dtype other than float64.
+//
+// Limits and rules:
+//   * batch * P <= 4 Mi keys, P = n rounded up to a power of two (rows of up to 32768 keys are
+//     sorted in shared memory and do not touch the static buffer at all); larger inputs are
+//     rejected with JAXCUDA_EINVAL and a message in `err`.
+//   * The first call on a device resolves the buffer's device address (cudaGetSymbolAddress); make
+//     that first call outside any stream capture.
+//   * All calls share the one buffer and it keeps whatever the previous call left there.  Nothing in
+//     it has to start at zero: each call overwrites every key slot it later reads.  Two calls that
+//     overlap on the GPU (different streams) race on it; keep them on one stream or order them.
+extern "C" int jaxcuda_sort_no_alloc(void* stream, int dtype, const void* x, void* y, int64_t batch, int64_t n,
+                                     char* err, size_t err_len) {
+  auto fail = [&](int status, const char* msg) {
+    if (err && err_len) snprintf(err, err_len, "%s", msg);
+    return status;
+  };
+  if (err && err_len) err[0] = '\0';
+  if (batch < 0 || n < 0 || (batch > 0 && n > 0 && (!x || !y))) return fail(3, "sort_no_alloc: null buffer or negative size");
+  if (dtype < 0 || dtype > JAXCUDA_F16) return fail(2, "sort_no_alloc: dtype not supported (float64 has no 32-bit key)");
+  if (batch == 0 || n == 0) return 0;
+  if (n >= ((int64_t)1 << 31)) return fail(3, "sort_no_alloc: axis too long");
+  int64_t P = 2;
+  while (P < n) P <<= 1;
+  if (P > 32768 && (batch > JX_SORT_STATIC_ITEMS / P)) {
+    char msg[200];
+    snprintf(msg, sizeof msg, "sort_no_alloc: %lld rows of %lld keys pad to %lld keys, the static work buffer holds %d",
+             (long long)batch, (long long)n, (long long)(batch * P), JX_SORT_STATIC_ITEMS);
+    return fail(3, msg);
+  }
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(5, "sort_no_alloc: no current CUDA device");
+  if (!g_static_work_addr[dev]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, jx_sort_static_work);
+    if (e != cudaSuccess || !p) return fail(5, cudaGetErrorString(e));
+    g_static_work_addr[dev] = p;
+  }
+  int launches = 0;
+  cudaError_t e = jaxcuda_sort::run<false>((cudaStream_t)stream, x, y, nullptr, dtype, batch, n, g_static_work_addr[dev], &launches);
+  if (e != cudaSuccess) return fail(5, cudaGetErrorString(e));
+  return 0;
 }
