@@ -197,6 +197,45 @@ def mlp_train(be, rank, world, dist, steps=8, warmup=2):
             "gemm": "3xTF32 on tcgen05 (f32 accuracy), f32 accumulate"}
 
 
+def vmap_grad(be, rank, world, dist, steps=30, warmup=3):
+    """Config 4: per-example value-and-gradient of the 784-1024-10 MLP under vmap, batch 64 split in
+    contiguous chunks over the ranks (independent units, no collective).  Returns steps/s."""
+    import torch
+    from jax_js_b200 import mlp
+    dims, GB = [784, 1024, 10], 64
+    local = GB // world
+    rng = np.random.default_rng(7)
+    x = rng.uniform(0, 1, (GB, dims[0])).astype(np.float32)[rank * local:(rank + 1) * local]
+    y = rng.integers(0, 10, GB).astype(np.int32)[rank * local:(rank + 1) * local]
+    prog = mlp.mlp_grad_program(local, dims, per_example=True)
+    prog.prepare(be)
+    slots = [be.put(x), be.put(y), be.put(np.eye(10, dtype=np.float32))] + [be.put(p) for p in mlp.init_params(dims)]
+    nbytes = prog.cost(be)[0]
+
+    def step():
+        for s in prog.execute(be, slots):
+            be.dec_ref(s)
+    for _ in range(warmup):
+        step()
+    be.sync()
+    if dist:
+        dist.barrier()
+    be.event_record(0)
+    for _ in range(steps):
+        step()
+    be.event_record(1)
+    be.sync()
+    t = torch.tensor([be.event_elapsed_ms(0, 1)], dtype=torch.float64, device="cuda")
+    if dist:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    for s in slots:
+        be.dec_ref(s)
+    return {"steps_per_s": steps / ms * 1e3, "ms_per_step": ms / steps, "batch": GB, "local_batch": local,
+            "algorithmic_gbs": nbytes * world * steps / ms / 1e6, "scaling": "strong",
+            "note": "per-example dW1 is f32[784,1024,batch]: the step is a streaming write"}
+
+
 def cpu_baseline(prog_factory, budget_s=10.0, threads=1):
     """The oracle (port of the reference's Wasm backend arithmetic) on a bounded sample of rows."""
     import oracle
@@ -428,8 +467,10 @@ def _run():
             line["cpu_baseline"] = cpu_baseline(None, budget_s=10.0, threads=1)
     if not args.skip_extras:
         train = mlp_train(be, rank, world, dist)
+        vg = vmap_grad(be, rank, world, dist)
         if line:
             line["mlp_train"] = train
+            line["vmap_grad"] = vg
     for s in (sx, si):
         be.dec_ref(s)
     be.host_free(x_host)

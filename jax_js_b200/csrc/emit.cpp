@@ -281,7 +281,7 @@ struct Builder {
   std::string header() const {
     const double work = (double)k.size * (k.has_red ? (double)k.red_size : 1.0);
     const bool exact = opt.exact_math == 1 || (opt.exact_math < 0 && work < opt.exact_math_work);
-    return std::string(exact ? "#define JX_EXACT_TRANSCENDENTALS 1\n" : "") + kPrelude;
+    return std::string(exact ? "#define JX_EXACT_TRANSCENDENTALS 1\n" : "") + "#define JX_LD_HINT " + S(opt.ld_hint) + "\n" + kPrelude;
   }
 
   Analysis an_exp, an_epi;
@@ -579,7 +579,9 @@ struct Builder {
   // One thread per vector of V adjacent outputs walks ridx; TY such threads share a vector and
   // take interleaved ridx values (folded through shared memory in a fixed order), and `splits`
   // CTAs along grid.y take contiguous ridx chunks whose partials a second kernel folds.
-  Plan reduce_col() const {
+  // group > 0: every thread owns `group` adjacent outputs (a run of gidx that shares its other
+  // operand, e.g. the N = 10 columns of one row of a skinny dot) instead of a 128-bit vector.
+  Plan reduce_col(int group = 0) const {
     Plan p;
     p.skeleton = SK_REDUCE_COL;
     account(p);
@@ -590,6 +592,8 @@ struct Builder {
       int eb = min_load_bytes(0, cand);
       if (eb && eb * cand <= 16 && (int64_t)k.size / cand >= 256) { V = cand; break; }
     }
+    const bool grouped = group > 1 && k.size % group == 0;
+    if (grouped) V = group;
     const int64_t nvec = ((int64_t)k.size + V - 1) / V;
     // r-parallelism wanted so that the grid fills the machine: col_ctas_per_sm CTAs of 256 threads per SM
     const int64_t target_threads = (int64_t)opt.sm_count * opt.col_ctas_per_sm * 256;
@@ -626,14 +630,30 @@ struct Builder {
     std::ostringstream decl, fetch;
     std::vector<std::string> bnames(k.exp.size());
     Env env;
-    if (V > 1) preload(decl, fetch, k.exp, an_exp, all, 0, V, env, "g0", "", "", "u", ov, bnames, "    ");
-    os << "  #pragma unroll " << std::max(1, opt.col_unroll) << "\n  for (int ridx = rbeg + ty; ridx < rend; ridx += " << TY << ") {\n";
-    os << decl.str() << fetch.str();
-    os << "    #pragma unroll\n    for (int u = 0; u < " << V << "; u++) {\n      const int gidx = g0 + u;\n";
-    env.load_override = &ov;
-    std::vector<std::string> names(k.exp.size());
-    emit_nodes(os, k.exp, an_exp, names, all, env, "      ");
-    os << "      acc[u] = " << red("acc[u]", names[root]) << ";\n    }\n  }\n";
+    // The ridx loop runs in batches of U steps: first every 128-bit load of the batch is issued,
+    // then the batch is consumed, so that U loads per thread are in flight whatever the compiler
+    // makes of the accumulator dependences.
+    const int U = (V > 1 && !grouped) ? std::max(1, opt.col_unroll) : 1;
+    if (V > 1 && !grouped) preload(decl, fetch, k.exp, an_exp, all, 0, V, env, "g0", "[" + S(U) + "]", "[j]", "u", ov, bnames, "        ");
+    if (U > 1) {
+      os << "  for (int rb = rbeg + ty; rb < rend; rb += " << TY * U << ") {\n";
+      os << decl.str();
+      os << "    #pragma unroll\n    for (int j = 0; j < " << U << "; j++) {\n      const int ridx = rb + j * " << TY << ";\n";
+      os << "      if (ridx < rend) {\n" << fetch.str() << "      }\n    }\n";
+      os << "    #pragma unroll\n    for (int j = 0; j < " << U << "; j++) {\n      const int ridx = rb + j * " << TY << ";\n";
+      os << "      if (ridx < rend) {\n";
+      os << "        #pragma unroll\n        for (int u = 0; u < " << V << "; u++) {\n          const int gidx = g0 + u;\n";
+      env.load_override = &ov;
+      std::vector<std::string> names(k.exp.size());
+      emit_nodes(os, k.exp, an_exp, names, all, env, "          ");
+      os << "          acc[u] = " << red("acc[u]", names[root]) << ";\n        }\n      }\n    }\n  }\n";
+    } else {
+      os << "  #pragma unroll 4\n  for (int ridx = rbeg + ty; ridx < rend; ridx += " << TY << ") {\n";
+      os << "    #pragma unroll\n    for (int u = 0; u < " << V << "; u++) {\n      const int gidx = g0 + u;\n";
+      std::vector<std::string> names(k.exp.size());
+      emit_nodes(os, k.exp, an_exp, names, all, env, "      ");
+      os << "      acc[u] = " << red("acc[u]", names[root]) << ";\n    }\n  }\n";
+    }
     if (TY > 1) {
       os << "  __shared__ " << AT << " sm[" << TY * V * TX << "];\n";
       os << "  #pragma unroll\n  for (int u = 0; u < " << V << "; u++) sm[(ty * " << V << " + u) * " << TX << " + tx] = acc[u];\n";
@@ -866,11 +886,90 @@ struct Builder {
     return p;
   }
 
+  // Skinny dot with a k-contiguous big operand: C[m, n] = sum_k A[m, k] B[n, k], N <= 16.
+  // A warp owns four rows of A and walks k with 128-bit loads; B is staged once per CTA in shared
+  // memory as [n][k] (f32), so that a lane's four (or eight) k values of every column are one
+  // conflict-free 128-bit shared load shared by its four rows; the N x 4 partial sums per lane are
+  // folded with warp shuffles.  CTAs are persistent over blocks of 32 rows, so A is read from HBM
+  // exactly once and B from L2 once per CTA.
+  bool dot_skinny(const GemmDesc& g, Plan& p) const {
+    const int e = dtype_bytes(g.dtA);
+    const int VX = 16 / e;                                   // k elements per 128-bit load
+    if (g.K % VX || (g.sAm * e) % 16 || (g.offA * e) % 16 || g.sAm <= 0) return false;
+    const int64_t smem = g.N * g.K * 4;
+    if (smem > 160 * 1024) return false;
+    p.skeleton = SK_REDUCE_ROW;
+    p.gemm = g;
+    account(p);
+    p.algo_flops = 2.0 * g.M * g.N * g.K;
+    const int R = 4, T = 256, ROWS = (T / 32) * R;
+    const int64_t blocks = (g.M + ROWS - 1) / ROWS;
+    std::ostringstream os;
+    os << header();
+    os << "#define GM " << g.M << "\n#define GN " << g.N << "\n#define GK " << g.K << "\n#define VX " << VX << "\n";
+    os << "#define OFFA " << g.offA << "LL\n#define SAM " << g.sAm << "LL\n";
+    os << "#define OFFB " << g.offB << "LL\n#define SBN " << g.sBn << "LL\n#define SBK " << g.sBk << "LL\n";
+    os << "typedef " << ptype(g.dtA) << " TA;\ntypedef " << ptype(g.dtB) << " TB;\n";
+    os << "extern \"C\" __global__ void __launch_bounds__(" << T << ") jx_dot_skinny(" << params() << ") {\n";
+    os << "  extern __shared__ __align__(16) float Bs[];   // [GN][GK]\n";
+    os << "  const TA* A = (const TA*)p" << g.gidA << " + OFFA;\n  const TB* B = (const TB*)p" << g.gidB << " + OFFB;\n";
+    os << "  for (int i = threadIdx.x; i < GN * GK; i += " << T << ") {\n    const int n = i / GK, kk = i - n * GK;\n";
+    os << "    Bs[i] = " << from_storage(g.dtB, "B[(i64)n * SBN + (i64)kk * SBK]") << ";\n  }\n  __syncthreads();\n";
+    os << "  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;\n";
+    os << "  for (int blk = blockIdx.x; blk < " << blocks << "; blk += gridDim.x) {\n";
+    os << "    const int m0 = blk * " << ROWS << " + warp * " << R << ";\n";
+    os << "    float acc[" << R << "][GN];\n    #pragma unroll\n    for (int r = 0; r < " << R << "; r++)\n      #pragma unroll\n      for (int n = 0; n < GN; n++) acc[r][n] = 0.0f;\n";
+    os << "    #pragma unroll 2\n    for (int k0 = lane * VX; k0 < GK; k0 += 32 * VX) {\n";
+    os << "      jx_pack<TA, VX> x[" << R << "];\n      #pragma unroll\n      for (int r = 0; r < " << R << "; r++) {\n";
+    os << "        const int m = (m0 + r < GM) ? m0 + r : GM - 1;\n        jx_load(x[r], A + (i64)m * SAM + k0);\n      }\n";
+    os << "      #pragma unroll\n      for (int n = 0; n < GN; n++) {\n        #pragma unroll\n        for (int v = 0; v < VX; v += 4) {\n";
+    os << "          const float4 y = *reinterpret_cast<const float4*>(&Bs[n * GK + k0 + v]);\n";
+    os << "          #pragma unroll\n          for (int r = 0; r < " << R << "; r++) {\n";
+    os << "            acc[r][n] = fmaf(" << from_storage(g.dtA, "x[r].e[v]") << ", y.x, acc[r][n]);\n";
+    os << "            acc[r][n] = fmaf(" << from_storage(g.dtA, "x[r].e[v + 1]") << ", y.y, acc[r][n]);\n";
+    os << "            acc[r][n] = fmaf(" << from_storage(g.dtA, "x[r].e[v + 2]") << ", y.z, acc[r][n]);\n";
+    os << "            acc[r][n] = fmaf(" << from_storage(g.dtA, "x[r].e[v + 3]") << ", y.w, acc[r][n]);\n";
+    os << "          }\n        }\n      }\n    }\n";
+    os << "    #pragma unroll\n    for (int r = 0; r < " << R << "; r++)\n      #pragma unroll\n      for (int n = 0; n < GN; n++)\n";
+    os << "        #pragma unroll\n        for (int o = 16; o > 0; o >>= 1) acc[r][n] += __shfl_xor_sync(0xffffffffu, acc[r][n], o);\n";
+    os << "    // every lane now holds all sums; lane j finishes output j of the warp's R x GN block\n";
+    os << "    #pragma unroll\n    for (int r = 0; r < " << R << "; r++) {\n      #pragma unroll\n      for (int n = 0; n < GN; n++) {\n";
+    os << "        if (lane == ((r * GN + n) & 31) && m0 + r < GM) {\n";
+    os << "          const int gidx = (m0 + r) * GN + n;\n          const float acc_v = acc[r][n];\n";
+    {
+      std::vector<std::string> en(k.epi.size());
+      std::vector<char> eall(k.epi.size(), 1);
+      Env ee;
+      ee.prefix = "e";
+      ee.acc = "acc_v";
+      emit_nodes(os, k.epi, an_epi, en, eall, ee, "          ");
+      os << "          out[gidx] = " << to_storage(out_dt, en.back()) << ";\n";
+    }
+    os << "        }\n      }\n    }\n  }\n}\n";
+    p.source = os.str();
+    Stage st;
+    st.entry = "jx_dot_skinny";
+    st.grid[0] = (unsigned)std::min<int64_t>(blocks, (int64_t)opt.sm_count * (smem > 100 * 1024 ? 1 : 2));
+    st.block[0] = T;
+    st.smem = (unsigned)smem;
+    p.stages.push_back(st);
+    p.describe = "dot-skinny " + S(g.M) + "x" + S(g.N) + "x" + S(g.K) + " rows/warp=4 grid=" + S(st.grid[0]) + "x" + S(T);
+    return true;
+  }
+
   Plan build() const {
     if (!k.has_red) return elementwise();
     if (opt.force_skeleton == SK_REDUCE_ROW) return reduce_row();
     if (opt.force_skeleton == SK_REDUCE_COL) return reduce_col();
     GemmDesc g = match_gemm();
+    if (g.valid && g.batch == 1 && opt.force_skeleton < 0) {
+      // Skinny dots (a class-count sized N): the big operand is streamed once and every thread or
+      // warp keeps all N partial sums of its rows.
+      if (g.N <= 16 && g.M >= 256 && g.K >= 64) {
+        if (g.sAk == 1) { Plan p; if (dot_skinny(g, p)) return p; }
+        if (g.sAm == 1 && g.K >= 256) return reduce_col((int)g.N);
+      }
+    }
     if (g.valid && g.batch <= 65535 &&
         ((g.M >= opt.gemm_min_dim && g.N >= opt.gemm_min_dim && g.K >= 8) || opt.force_skeleton == SK_GEMM_FFMA)) {
       if (opt.allow_tc && opt.force_skeleton != SK_GEMM_FFMA) {

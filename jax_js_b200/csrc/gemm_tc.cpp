@@ -15,11 +15,13 @@
 //
 // The kernel is persistent (one CTA per SM, static tile schedule).  float16 operands use
 // kind::f16 with f32 accumulation.  float32 operands use kind::tf32 three times per k-step on
-// planes split into a TF32-exact high part and the remainder (3xTF32: lo*hi + hi*lo + hi*hi),
+// the operand (whose low 13 mantissa bits the tensor core ignores) and a remainder plane
+// lo = x - tf32(x) (3xTF32: lo*hi + hi*lo + hi*hi),
 // which keeps f32 accuracy; plain TF32 is never used.  Every mbarrier wait is bounded: on a
 // time-out the kernel records a code in `status` and winds down instead of hanging the GPU.
 #include "gemm_tc.hpp"
 
+#include <cstdlib>
 #include <cstring>
 #include <sstream>
 
@@ -328,20 +330,33 @@ JX_EPILOGUE
 }
 
 #if KIND == 2
-// Splits f32 operands into a TF32-exact high part (low 13 mantissa bits cleared) and the exact
-// remainder; planes keep the operand's own indexing.
+// Remainder planes of the f32 operands: lo = x - hi, hi = x with the low 13 mantissa bits cleared.
+// The hi planes themselves are never materialised: a kind::tf32 MMA reads f32 words and ignores
+// those 13 bits (verified on B200: results are bit-identical with explicit hi planes), so the
+// original operand serves as hi.  Planes keep the operand's own indexing.
 extern "C" __global__ void __launch_bounds__(256) jx_split(const float* __restrict__ a, const float* __restrict__ b,
                                                           float* __restrict__ planes) {
-  const i64 total = (i64)LEN_A + (i64)LEN_B;
-  for (i64 i = (i64)blockIdx.x * 256 + threadIdx.x; i < total; i += (i64)gridDim.x * 256) {
-    const bool is_a = i < LEN_A;
-    const i64 j = is_a ? i : i - LEN_A;
-    const float v = is_a ? a[j] : b[j];
-    const float hi = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
-    float* dst = planes + (is_a ? 0 : 2 * (i64)LEN_A_PAD);
-    const i64 pad = is_a ? LEN_A_PAD : LEN_B_PAD;
-    dst[j] = hi;
-    dst[pad + j] = v - hi;
+  const i64 na4 = (i64)LEN_A / 4, nb4 = (i64)LEN_B / 4;
+  const i64 total4 = na4 + nb4;
+  for (i64 i = (i64)blockIdx.x * 256 + threadIdx.x; i < total4; i += (i64)gridDim.x * 256) {
+    const bool is_a = i < na4;
+    const i64 j = is_a ? i : i - na4;
+    const float4 v = reinterpret_cast<const float4*>(is_a ? a : b)[j];
+    float4 lo;
+    lo.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xffffe000u);
+    lo.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xffffe000u);
+    lo.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xffffe000u);
+    lo.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xffffe000u);
+    reinterpret_cast<float4*>(planes + (is_a ? 0 : (i64)LEN_A_PAD))[j] = lo;
+  }
+  if (blockIdx.x == 0 && threadIdx.x < 8) {     // the up to three trailing elements of each operand
+    const bool is_a = threadIdx.x < 4;
+    const i64 len = is_a ? (i64)LEN_A : (i64)LEN_B;
+    const i64 j = (len / 4) * 4 + (threadIdx.x & 3);
+    if (j < len) {
+      const float v = (is_a ? a : b)[j];
+      (planes + (is_a ? 0 : (i64)LEN_A_PAD))[j] = v - __uint_as_float(__float_as_uint(v) & 0xffffe000u);
+    }
   }
 }
 #endif
@@ -417,10 +432,10 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
   if (kind == 2) {
     Stage sp;
     sp.entry = "jx_split";
-    sp.grid[0] = (unsigned)std::min<int64_t>((g.lenA + g.lenB + 255) / 256, (int64_t)opt.sm_count * 16);
+    sp.grid[0] = (unsigned)std::max<int64_t>(1, std::min<int64_t>(((int64_t)(g.lenA + g.lenB) / 4 + 255) / 256, (int64_t)opt.sm_count * 32));
     sp.block[0] = 256;
     plan.stages.push_back(sp);
-    plan.scratch_bytes = (size_t)(2 * pad64(g.lenA) + 2 * pad64(g.lenB)) * 4;
+    plan.scratch_bytes = (size_t)(pad64(g.lenA) + pad64(g.lenB)) * 4;
   }
   Stage st;
   st.entry = "jx_gemm";
@@ -456,10 +471,8 @@ int launch_gemm_tc(void* encode_fn, void* launch_fn, const Plan& plan, const std
     CUresult r = launch(fns[0], sp.grid[0], 1, 1, sp.block[0], 1, 1, 0, (CUstream)stream, args, nullptr);
     if (r != CUDA_SUCCESS) { err = "launch of the TF32 split kernel failed"; return -1; }
     launches++;
-    baseA = (const char*)planes;
-    baseA2 = (const char*)(planes + pad64(g.lenA));
-    baseB = (const char*)(planes + 2 * pad64(g.lenA));
-    baseB2 = (const char*)(planes + 2 * pad64(g.lenA) + pad64(g.lenB));
+    baseA2 = (const char*)planes;                     // lo planes; the operands themselves are the hi terms
+    baseB2 = (const char*)(planes + pad64(g.lenA));
   }
   const CUtensorMapDataType dt = kind == 1 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
   const cuuint32_t inner_box = 128 / e;

@@ -221,6 +221,18 @@ template <class T, int N> struct jx_pack {
 };
 template <class T, int N>
 __device__ __forceinline__ void jx_load(jx_pack<T, N>& p, const T* src) {
+#if defined(JX_LD_HINT) && JX_LD_HINT > 0
+  // Streaming reads: 128-bit non-coherent loads that do not allocate in L1 and ask L2 to fetch
+  // 256-byte lines, which keeps DRAM bursts long when a warp only touches 512 bytes of a row.
+  if constexpr (sizeof(T) * N == 16) {
+    u32 w0, w1, w2, w3;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::256B.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3) : "l"(src));
+    u32* w = reinterpret_cast<u32*>(&p.raw);
+    w[0] = w0; w[1] = w1; w[2] = w2; w[3] = w3;
+    return;
+  }
+#endif
   p.raw = *reinterpret_cast<const jx_vec<sizeof(T) * N>*>(src);
 }
 template <class T, int N>

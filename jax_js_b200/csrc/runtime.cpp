@@ -316,6 +316,7 @@ int jaxcuda_create(int device, jaxcuda_ctx** out) {
   ctx->opt.allow_tc = env_int("JAXCUDA_NO_TC", 0) == 0;
   ctx->opt.force_skeleton = env_int("JAXCUDA_FORCE_SKELETON", -1);
   ctx->opt.exact_math = env_int("JAXCUDA_EXACT_MATH", ctx->opt.exact_math);
+  ctx->opt.ld_hint = env_int("JAXCUDA_LD_HINT", ctx->opt.ld_hint);
   ctx->opt.row_tpr = env_int("JAXCUDA_ROW_TPR", ctx->opt.row_tpr);
   ctx->opt.row_unroll = env_int("JAXCUDA_ROW_UNROLL", ctx->opt.row_unroll);
   ctx->opt.col_threads = env_int("JAXCUDA_COL_THREADS", ctx->opt.col_threads);
