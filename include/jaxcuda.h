@@ -37,6 +37,7 @@ typedef enum {
 
 typedef struct jaxcuda_ctx jaxcuda_ctx;
 typedef struct jaxcuda_exe jaxcuda_exe;
+typedef struct jaxcuda_graph jaxcuda_graph;
 typedef uint32_t jaxcuda_slot; /* `Slot`, src/backend.ts:155 */
 
 /* createBackend("cuda") arm (src/backend.ts:72-142): binds a context to one GPU and creates
@@ -120,6 +121,21 @@ int jaxcuda_event_record(jaxcuda_ctx* ctx, int index); /* index in [0, 65536) */
 int jaxcuda_event_elapsed_ms(jaxcuda_ctx* ctx, int start_index, int stop_index, float* ms);
 /* Number of kernels this context has launched so far (its own kernels only). */
 uint64_t jaxcuda_launch_count(jaxcuda_ctx* ctx);
+
+/* Replay of a static step list as one CUDA graph: the counterpart of `JitProgram.execute`
+ * (src/frontend/jit.ts:111-162), which replays the same malloc / execute / free steps on every call.
+ * Between capture_begin and capture_end the usual calls (malloc without initialData, dispatch,
+ * incref/decref, copy, allreduce) are recorded instead of run; every buffer touched in between
+ * belongs to the graph until it is destroyed, so slots that are still alive at capture_end (the
+ * step's outputs) keep their addresses and are rewritten in place by every launch.  Dispatch each
+ * program eagerly at least once before capturing it.  read / sync / event_record are refused
+ * inside a capture. */
+int jaxcuda_capture_begin(jaxcuda_ctx* ctx);
+int jaxcuda_capture_end(jaxcuda_ctx* ctx, jaxcuda_graph** out);
+int jaxcuda_graph_launch(jaxcuda_ctx* ctx, jaxcuda_graph* graph);
+int jaxcuda_graph_destroy(jaxcuda_ctx* ctx, jaxcuda_graph* graph);
+/* Device-to-device copy between two slots of equal size, in stream order (capturable). */
+int jaxcuda_copy(jaxcuda_ctx* ctx, jaxcuda_slot dst, jaxcuda_slot src);
 
 /* Interop for host code that shares the CUDA primary context (torch): raw pointer of a slot and
  * the stream handle (cudaStream_t) as integers.  No counterpart in the reference. */

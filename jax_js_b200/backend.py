@@ -87,6 +87,11 @@ SYMBOLS = {
     "jaxcuda_comm_init": (_I, [_P, _I, _I, _P]),
     "jaxcuda_allreduce_sum_f32": (_I, [_P, ctypes.POINTER(_U32), _I]),
     "jaxcuda_comm_destroy": (_I, [_P]),
+    "jaxcuda_capture_begin": (_I, [_P]),
+    "jaxcuda_capture_end": (_I, [_P, ctypes.POINTER(_P)]),
+    "jaxcuda_graph_launch": (_I, [_P, _P]),
+    "jaxcuda_graph_destroy": (_I, [_P, _P]),
+    "jaxcuda_copy": (_I, [_P, _U32, _U32]),
     "jaxcuda_sort_no_alloc": (_I, [_P, _I, _P, _P, ctypes.c_int64, ctypes.c_int64, ctypes.c_char_p, _SZ]),
 }
 
@@ -315,6 +320,24 @@ class CudaBackend:
     def allreduce_sum_f32(self, slots: Sequence[int]) -> None:
         arr = (ctypes.c_uint32 * max(1, len(slots)))(*slots)
         self._check(self._lib.jaxcuda_allreduce_sum_f32(self._ctx, arr, len(slots)))
+
+    # -- captured step lists ---------------------------------------------------------------
+    def capture_begin(self) -> None:
+        self._check(self._lib.jaxcuda_capture_begin(self._ctx))
+
+    def capture_end(self) -> int:
+        g = ctypes.c_void_p()
+        self._check(self._lib.jaxcuda_capture_end(self._ctx, ctypes.byref(g)))
+        return g.value
+
+    def graph_launch(self, graph: int) -> None:
+        self._check(self._lib.jaxcuda_graph_launch(self._ctx, graph))
+
+    def graph_destroy(self, graph: int) -> None:
+        self._check(self._lib.jaxcuda_graph_destroy(self._ctx, graph))
+
+    def copy(self, dst: int, src: int) -> None:
+        self._check(self._lib.jaxcuda_copy(self._ctx, dst, src))
 
     def sort_no_alloc(self, dtype: DType, x_slot: int, y_slot: int, batch: int, n: int) -> None:
         """Sort rows of x_slot into y_slot through the entry point that allocates nothing (its

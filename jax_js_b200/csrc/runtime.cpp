@@ -76,6 +76,13 @@ bool load_driver(Driver& d, std::string& err) {
 struct Allocator {
   std::map<size_t, std::vector<void*>> free_lists;
   size_t reserved = 0, in_use = 0;
+  // Blocks that a captured graph has baked into its kernel parameters belong to that graph until
+  // it is destroyed: `owner` maps such a block to its graph, `idle` holds the owned blocks that no
+  // slot is using at the moment.  While `capturing` is non-zero every block that is handed out or
+  // handed back is adopted by the graph being captured, and reuse happens among adopted blocks only.
+  std::unordered_map<void*, int> owner;
+  std::unordered_map<int, std::map<size_t, std::vector<void*>>> idle;
+  int capturing = 0;
 
   static size_t round_size(size_t n) {
     if (n <= 512) return 512;
@@ -86,11 +93,21 @@ struct Allocator {
   }
   cudaError_t get(size_t n, void** out) {
     const size_t cls = round_size(n);
+    if (capturing) {
+      auto& mine = idle[capturing][cls];
+      if (!mine.empty()) {
+        *out = mine.back();
+        mine.pop_back();
+        in_use += cls;
+        return cudaSuccess;
+      }
+    }
     auto it = free_lists.find(cls);
     if (it != free_lists.end() && !it->second.empty()) {
       *out = it->second.back();
       it->second.pop_back();
       in_use += cls;
+      if (capturing) owner[*out] = capturing;
       return cudaSuccess;
     }
     cudaError_t e = cudaMalloc(out, cls);
@@ -99,13 +116,28 @@ struct Allocator {
       release_cached();
       e = cudaMalloc(out, cls);
     }
-    if (e == cudaSuccess) { reserved += cls; in_use += cls; }
+    if (e == cudaSuccess) {
+      reserved += cls;
+      in_use += cls;
+      if (capturing) owner[*out] = capturing;
+    }
     return e;
   }
   void put(void* p, size_t n) {
     const size_t cls = round_size(n);
-    free_lists[cls].push_back(p);
     in_use -= cls;
+    if (capturing) owner[p] = capturing;  // a block released inside a capture may be reused by it: adopt it
+    auto it = owner.find(p);
+    if (it != owner.end()) idle[it->second][cls].push_back(p);
+    else free_lists[cls].push_back(p);
+  }
+  // The graph is gone: its idle blocks return to the pool, its blocks still behind live slots
+  // become ordinary blocks.
+  void release_graph(int id) {
+    for (auto& kv : idle[id])
+      for (void* p : kv.second) free_lists[kv.first].push_back(p);
+    idle.erase(id);
+    for (auto it = owner.begin(); it != owner.end();) it = (it->second == id) ? owner.erase(it) : std::next(it);
   }
   void release_cached() {
     for (auto& kv : free_lists) {
@@ -140,8 +172,18 @@ struct jaxcuda_exe {
   void* persistent_scratch = nullptr;  // zero-initialised once; reused by every dispatch (stream-ordered)
 };
 
+struct jaxcuda_graph {
+  jaxcuda_ctx* ctx = nullptr;
+  int id = 0;
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  uint64_t kernels = 0;  // kernel launches recorded in the graph
+};
+
 struct jaxcuda_ctx {
   int device = 0;
+  int next_graph_id = 1;
+  uint64_t capture_launches0 = 0;
   cudaStream_t stream = nullptr;
   Driver drv;
   Allocator alloc;
@@ -348,6 +390,8 @@ int jaxcuda_malloc(jaxcuda_ctx* ctx, size_t bytes, const void* init, size_t init
   if (!ctx || !out) return JAXCUDA_EINVAL;
   if (init && init_bytes != bytes)
     return fail(ctx, JAXCUDA_EINVAL, "initialData size %zu does not match buffer size %zu", init_bytes, bytes);
+  if (init && ctx->alloc.capturing)
+    return fail(ctx, JAXCUDA_EINVAL, "malloc with initialData inside a capture: upload before jaxcuda_capture_begin");
   cudaSetDevice(ctx->device);
   SlotRec rec;
   rec.bytes = bytes;
@@ -398,6 +442,7 @@ int jaxcuda_slot_size(jaxcuda_ctx* ctx, jaxcuda_slot slot, size_t* bytes) {
 int jaxcuda_read(jaxcuda_ctx* ctx, jaxcuda_slot slot, size_t start, size_t count, void* dst) {
   SlotRec* s = find_slot(ctx, slot);
   if (!s) return slot_error(ctx, slot);
+  if (ctx->alloc.capturing) return fail(ctx, JAXCUDA_EINVAL, "read inside a capture: reads synchronise the stream");
   if (start > s->bytes) return fail(ctx, JAXCUDA_EINVAL, "read start %zu beyond buffer of %zu bytes", start, s->bytes);
   if (count == SIZE_MAX) count = s->bytes - start;
   if (count > s->bytes - start) return fail(ctx, JAXCUDA_EINVAL, "read of %zu bytes at %zu beyond buffer of %zu bytes", count, start, s->bytes);
@@ -570,6 +615,8 @@ int jaxcuda_dispatch(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const jaxcuda_slot* inp
 
   void* scratch = nullptr;
   if (exe->plan.scratch_bytes && exe->plan.scratch_persistent) {
+    if (!exe->persistent_scratch && ctx->alloc.capturing)
+      return fail(ctx, JAXCUDA_EINVAL, "dispatch the program once before capturing it: a kernel still has to set up its arrival counters");
     if (!exe->persistent_scratch) {
       cudaError_t e = ctx->alloc.get(exe->plan.scratch_bytes, &exe->persistent_scratch);
       if (e == cudaSuccess) e = cudaMemsetAsync(exe->persistent_scratch, 0, exe->plan.scratch_bytes, ctx->stream);
@@ -637,6 +684,7 @@ int jaxcuda_host_free(jaxcuda_ctx* ctx, void* ptr) {
 
 int jaxcuda_sync(jaxcuda_ctx* ctx) {
   if (!ctx) return JAXCUDA_EINVAL;
+  if (ctx->alloc.capturing) return fail(ctx, JAXCUDA_EINVAL, "sync inside a capture");
   cudaSetDevice(ctx->device);
   if (ctx->tc_dispatched) {  // only contexts that ran the tensor-core skeleton have anything to report
     CUDA_TRY(ctx, cudaMemcpyAsync(ctx->status_host, ctx->status_dev, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
@@ -648,6 +696,7 @@ int jaxcuda_sync(jaxcuda_ctx* ctx) {
 
 int jaxcuda_event_record(jaxcuda_ctx* ctx, int index) {
   if (!ctx || index < 0 || index >= 65536) return JAXCUDA_EINVAL;
+  if (ctx->alloc.capturing) return fail(ctx, JAXCUDA_EINVAL, "event_record inside a capture");
   cudaSetDevice(ctx->device);
   if ((size_t)index >= ctx->events.size()) ctx->events.resize(index + 1, nullptr);
   if (!ctx->events[index]) CUDA_TRY(ctx, cudaEventCreate(&ctx->events[index]));
@@ -662,6 +711,79 @@ int jaxcuda_event_elapsed_ms(jaxcuda_ctx* ctx, int a, int b, float* ms) {
   return JAXCUDA_OK;
 }
 uint64_t jaxcuda_launch_count(jaxcuda_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+// ---- captured step lists ------------------------------------------------------------------
+int jaxcuda_copy(jaxcuda_ctx* ctx, jaxcuda_slot dst, jaxcuda_slot src) {
+  SlotRec* d = find_slot(ctx, dst);
+  if (!d) return slot_error(ctx, dst);
+  SlotRec* s = find_slot(ctx, src);
+  if (!s) return slot_error(ctx, src);
+  if (d->bytes != s->bytes) return fail(ctx, JAXCUDA_EINVAL, "copy between slots of %zu and %zu bytes", s->bytes, d->bytes);
+  cudaSetDevice(ctx->device);
+  if (d->bytes && d->ptr != s->ptr)
+    CUDA_TRY(ctx, cudaMemcpyAsync(d->ptr, s->ptr, d->bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+  return JAXCUDA_OK;
+}
+
+int jaxcuda_capture_begin(jaxcuda_ctx* ctx) {
+  if (!ctx) return JAXCUDA_EINVAL;
+  if (ctx->alloc.capturing) return fail(ctx, JAXCUDA_EINVAL, "a capture is already open");
+  cudaSetDevice(ctx->device);
+  CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+  // relaxed mode: the allocator may still call cudaMalloc for a size it has never seen
+  CUDA_TRY(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeRelaxed));
+  ctx->alloc.capturing = ctx->next_graph_id++;
+  ctx->capture_launches0 = ctx->launches;
+  return JAXCUDA_OK;
+}
+
+int jaxcuda_capture_end(jaxcuda_ctx* ctx, jaxcuda_graph** out) {
+  if (!ctx || !out) return JAXCUDA_EINVAL;
+  *out = nullptr;
+  if (!ctx->alloc.capturing) return fail(ctx, JAXCUDA_EINVAL, "no capture is open");
+  const int id = ctx->alloc.capturing;
+  ctx->alloc.capturing = 0;
+  cudaGraph_t graph = nullptr;
+  cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+  if (e != cudaSuccess || !graph) {
+    ctx->alloc.release_graph(id);
+    return fail(ctx, JAXCUDA_ECUDA, "cudaStreamEndCapture: %s", cudaGetErrorString(e));
+  }
+  cudaGraphExec_t exec = nullptr;
+  e = cudaGraphInstantiate(&exec, graph, 0);
+  if (e != cudaSuccess) {
+    cudaGraphDestroy(graph);
+    ctx->alloc.release_graph(id);
+    return fail(ctx, JAXCUDA_ECUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(e));
+  }
+  jaxcuda_graph* g = new jaxcuda_graph;
+  g->ctx = ctx; g->id = id; g->graph = graph; g->exec = exec;
+  g->kernels = ctx->launches - ctx->capture_launches0;
+  ctx->launches = ctx->capture_launches0;  // nothing has run yet: launches count when the graph does
+  *out = g;
+  return JAXCUDA_OK;
+}
+
+int jaxcuda_graph_launch(jaxcuda_ctx* ctx, jaxcuda_graph* g) {
+  if (!ctx || !g || g->ctx != ctx) return JAXCUDA_EINVAL;
+  if (ctx->alloc.capturing) return fail(ctx, JAXCUDA_EINVAL, "graph launch inside a capture");
+  cudaSetDevice(ctx->device);
+  CUDA_TRY(ctx, cudaGraphLaunch(g->exec, ctx->stream));
+  ctx->launches += g->kernels;
+  ctx->tc_dispatched = true;
+  return JAXCUDA_OK;
+}
+
+int jaxcuda_graph_destroy(jaxcuda_ctx* ctx, jaxcuda_graph* g) {
+  if (!ctx || !g || g->ctx != ctx) return JAXCUDA_EINVAL;
+  cudaSetDevice(ctx->device);
+  cudaStreamSynchronize(ctx->stream);
+  if (g->exec) cudaGraphExecDestroy(g->exec);
+  if (g->graph) cudaGraphDestroy(g->graph);
+  ctx->alloc.release_graph(g->id);
+  delete g;
+  return JAXCUDA_OK;
+}
 
 int jaxcuda_slot_ptr(jaxcuda_ctx* ctx, jaxcuda_slot slot, uint64_t* device_ptr) {
   SlotRec* s = find_slot(ctx, slot);

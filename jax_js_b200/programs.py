@@ -181,6 +181,21 @@ class JitProgram:
             backend.dec_ref(env[n])
         return outs
 
+    def capture(self, backend, slots: Sequence[int]):
+        """Record the step list as one CUDA graph (jaxcuda_capture_begin/end).  Returns
+        (graph, output slots): every `backend.graph_launch(graph)` recomputes the outputs in place
+        from whatever the input slots hold then.  The program is dispatched eagerly once first, so
+        that every kernel has set up its scratch."""
+        for s in self.execute(backend, slots):
+            backend.dec_ref(s)
+        backend.capture_begin()
+        try:
+            outs = self.execute(backend, slots)
+        except Exception:
+            backend.graph_destroy(backend.capture_end())
+            raise
+        return backend.capture_end(), outs
+
     def cost(self, backend):
         """Sum of algorithmic bytes, flops and launches over the execute steps."""
         self.prepare(backend)
