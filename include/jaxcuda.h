@@ -91,8 +91,9 @@ typedef struct {
 } jaxcuda_routine_type;
 
 /* Backend.prepareRoutine[Sync] (src/backend.ts:198-202).  name is a `Routines` member
- * (src/routine.ts:32-102): "Sort" and "Argsort" are implemented; others return
- * JAXCUDA_EUNSUPPORTED (UnsupportedRoutineError). */
+ * (src/routine.ts:32-102): "Sort", "Argsort" and "Scatter" are implemented; others return
+ * JAXCUDA_EUNSUPPORTED (UnsupportedRoutineError).  params_json is the routine's `params` object as
+ * JSON (for Scatter: `ScatterParams`, src/routine.ts:104-110). */
 int jaxcuda_prepare_routine(jaxcuda_ctx* ctx, const char* name, const jaxcuda_routine_type* type,
                             const char* params_json, jaxcuda_exe** out);
 

@@ -256,7 +256,9 @@ class CudaBackend:
                 (ctypes.c_int64 * max(1, len(outs)))(*outs)]
         rt = _RoutineType(len(t.input_shapes), len(t.output_shapes), *keep)
         exe = ctypes.c_void_p()
-        self._check(self._lib.jaxcuda_prepare_routine(self._ctx, routine.name.encode(), ctypes.byref(rt), b"{}",
+        import json
+        params = json.dumps(routine.params if routine.params is not None else {}).encode()
+        self._check(self._lib.jaxcuda_prepare_routine(self._ctx, routine.name.encode(), ctypes.byref(rt), params,
                                                       ctypes.byref(exe)))
         return Executable(routine, exe.value, self)
 

@@ -26,6 +26,7 @@
 #include "emit.hpp"
 #include "gemm_tc.hpp"
 #include "ir.hpp"
+#include "scatter.hpp"
 
 extern "C" size_t jaxcuda_sort_work_bytes(int argsort, int64_t batch, int64_t n);
 extern "C" int jaxcuda_sort_launch(void* stream, int argsort, const void* x, void* y, int32_t* yi, int dtype,
@@ -158,7 +159,8 @@ using namespace jaxcuda_rt;
 
 struct jaxcuda_exe {
   jaxcuda_ctx* ctx = nullptr;
-  int kind = 0;  // 0 kernel, 1 Sort, 2 Argsort
+  int kind = 0;  // 0 kernel, 1 Sort, 2 Argsort, 3 Scatter
+  jaxcuda_scatter_desc scatter = {};
   int handles = 0;
   uint64_t hash = 0;
   KernelIR ir;
@@ -533,11 +535,97 @@ int jaxcuda_check_kernel(const uint8_t* ir, size_t len, int sm_count, int force_
   return JAXCUDA_OK;
 }
 
+// Minimal reader for the flat JSON object of `ScatterParams` (src/routine.ts:104-110).
+static const char* json_value(const char* json, const char* key) {
+  if (!json) return nullptr;
+  std::string pat = std::string("\"") + key + "\"";
+  const char* p = strstr(json, pat.c_str());
+  if (!p) return nullptr;
+  p = strchr(p + pat.size(), ':');
+  if (!p) return nullptr;
+  p++;
+  while (*p == ' ' || *p == '\t' || *p == '\n') p++;
+  return p;
+}
+static bool json_ints(const char* json, const char* key, std::vector<long long>& out) {
+  const char* p = json_value(json, key);
+  if (!p || *p != '[') return false;
+  p++;
+  while (*p && *p != ']') {
+    char* end;
+    long long v = strtoll(p, &end, 10);
+    if (end == p) { p++; continue; }
+    out.push_back(v);
+    p = end;
+  }
+  return *p == ']';
+}
+
+static int prepare_scatter(jaxcuda_ctx* ctx, const jaxcuda_routine_type* type, const char* params, jaxcuda_exe** out) {
+  std::vector<long long> shape, axis;
+  const char* op = json_value(params, "op");
+  const char* od = json_value(params, "outDim");
+  const char* uq = json_value(params, "uniqueIndices");
+  if (!op || !od || !json_ints(params, "shape", shape) || !json_ints(params, "axis", axis))
+    return fail(ctx, JAXCUDA_EINVAL, "Scatter: params need op, shape, axis, outDim and uniqueIndices");
+  if (type->n_inputs < 1 || type->n_inputs != 1 + (int)axis.size() || type->n_outputs != 1 || axis.size() > 8 || shape.size() > 8)
+    return fail(ctx, JAXCUDA_EINVAL, "Scatter: one updates input plus one index input per indexed axis (at most 8 axes)");
+  jaxcuda_scatter_desc d = {};
+  d.dtype = type->input_dtypes[0];
+  const bool add = !strncmp(op, "\"add\"", 5);
+  d.unique = uq && !strncmp(uq, "true", 4);
+  d.mode = (add && !d.unique) ? (d.dtype == JAXCUDA_BOOL ? 2 : 1) : 0;   // routine.ts:241
+  d.out_dim = atoi(od);
+  d.out_rank = (int)shape.size();
+  d.out_size = 1;
+  for (int i = d.out_rank - 1; i >= 0; i--) { d.out_shape[i] = shape[i]; d.out_stride[i] = d.out_size; d.out_size *= shape[i]; }
+  // shapes: inputs are concatenated in type->input_shapes
+  const int64_t* sh = type->input_shapes;
+  d.upd_rank = type->input_ranks[0];
+  if (d.upd_rank > 8) return fail(ctx, JAXCUDA_EINVAL, "Scatter: rank above 8");
+  d.n_updates = 1;
+  for (int i = d.upd_rank - 1; i >= 0; i--) { d.upd_shape[i] = sh[i]; d.upd_stride[i] = d.n_updates; d.n_updates *= sh[i]; }
+  sh += d.upd_rank;
+  d.n_index = (int)axis.size();
+  d.index_rank = 0;
+  for (int k = 0; k < d.n_index; k++) {
+    const int r = type->input_ranks[1 + k];
+    if (r > 8) return fail(ctx, JAXCUDA_EINVAL, "Scatter: rank above 8");
+    if (type->input_dtypes[1 + k] != JAXCUDA_I32 && type->input_dtypes[1 + k] != JAXCUDA_U32)
+      return fail(ctx, JAXCUDA_EINVAL, "Scatter: index inputs must be 32-bit integers");
+    d.idx_rank[k] = r;
+    long long st = 1;
+    for (int j = r - 1; j >= 0; j--) { d.idx_shape[k][j] = sh[j]; d.idx_stride[k][j] = st; st *= sh[j]; }
+    sh += r;
+    d.index_rank = std::max(d.index_rank, r);
+  }
+  for (int ax = 0; ax < d.out_rank; ax++) {
+    d.axis_to_index[ax] = -1;
+    for (int k = 0; k < d.n_index; k++) if (axis[k] == ax) d.axis_to_index[ax] = k;
+  }
+  int nf = 0;
+  for (int i = 0; i < d.upd_rank; i++)
+    if (i < d.out_dim || i >= d.out_dim + d.index_rank) d.free_dims[nf++] = i;
+  if (d.n_updates >= (1ll << 31) || d.out_size >= (1ll << 31)) return fail(ctx, JAXCUDA_EINVAL, "Scatter: array too large");
+  std::unique_ptr<jaxcuda_exe> exe(new jaxcuda_exe);
+  exe->ctx = ctx;
+  exe->kind = 3;
+  exe->scatter = d;
+  exe->describe = std::string("Scatter ") + (d.mode == 0 ? (d.unique ? "update" : "update (last wins)") : d.mode == 1 ? "add" : "or") +
+                  " updates=" + std::to_string(d.n_updates) + " out=" + std::to_string(d.out_size);
+  exe->plan.describe = exe->describe;
+  exe->plan.algo_bytes = (double)(d.n_updates + d.out_size) * dtype_bytes(d.dtype) + 4.0 * d.n_updates * d.n_index;
+  exe->handles = 1;
+  *out = exe.get();
+  ctx->routines.push_back(std::move(exe));
+  return JAXCUDA_OK;
+}
+
 int jaxcuda_prepare_routine(jaxcuda_ctx* ctx, const char* name, const jaxcuda_routine_type* type,
                             const char* params_json, jaxcuda_exe** out) {
-  (void)params_json;
   if (!ctx || !out || !name || !type) return JAXCUDA_EINVAL;
   *out = nullptr;
+  if (!strcmp(name, "Scatter")) return prepare_scatter(ctx, type, params_json, out);
   const bool is_sort = !strcmp(name, "Sort"), is_argsort = !strcmp(name, "Argsort");
   if (!is_sort && !is_argsort)  // wording of UnsupportedRoutineError, src/backend.ts:236-240
     return fail(ctx, JAXCUDA_EUNSUPPORTED, "routine '%s' is not supported in cuda backend", name);
@@ -572,6 +660,27 @@ int jaxcuda_dispatch(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const jaxcuda_slot* inp
   for (int i = 0; i < n_inputs; i++) if (!(in[i] = find_slot(ctx, inputs[i]))) return slot_error(ctx, inputs[i]);
   for (int i = 0; i < n_outputs; i++) if (!(outv[i] = find_slot(ctx, outputs[i]))) return slot_error(ctx, outputs[i]);
 
+  if (exe->kind == 3) {  // Scatter
+    const jaxcuda_scatter_desc& d = exe->scatter;
+    if (n_inputs != 1 + d.n_index || n_outputs != 1) return fail(ctx, JAXCUDA_EINVAL, "Scatter called with wrong slot counts");
+    const size_t eb = dtype_bytes(d.dtype);
+    if (in[0]->bytes < (size_t)d.n_updates * eb || outv[0]->bytes < (size_t)d.out_size * eb)
+      return fail(ctx, JAXCUDA_EINVAL, "Scatter buffers are smaller than its declared shapes");
+    const void* idx[8] = {};
+    for (int k = 0; k < d.n_index; k++) idx[k] = in[1 + k]->ptr;
+    const size_t wb = jaxcuda_scatter_work_bytes(&d);
+    void* work = nullptr;
+    if (wb) {
+      cudaError_t e = ctx->alloc.get(wb, &work);
+      if (e != cudaSuccess) return fail(ctx, JAXCUDA_ENOMEM, "scatter work space of %zu bytes: %s", wb, cudaGetErrorString(e));
+    }
+    int launches = 0;
+    int rc = jaxcuda_scatter_launch(ctx->stream, &d, in[0]->ptr, idx, outv[0]->ptr, work, &launches);
+    ctx->launches += launches;
+    if (work) ctx->alloc.put(work, wb);
+    if (rc) return fail(ctx, JAXCUDA_ECUDA, "scatter launch: %s", cudaGetErrorString((cudaError_t)rc));
+    return JAXCUDA_OK;
+  }
   if (exe->kind != 0) {  // Sort / Argsort
     const bool arg = exe->kind == 2;
     if (n_inputs != 1 || n_outputs != (arg ? 2 : 1)) return fail(ctx, JAXCUDA_EINVAL, "routine called with wrong slot counts");

@@ -105,6 +105,24 @@ def argsort(x: np.ndarray, dtype_code: int):
     return y, yi
 
 
+def scatter(updates: np.ndarray, indices, params: dict, dtype_code: int) -> np.ndarray:
+    """`runScatter` (src/routine.ts:226-296): updates and one int32 index array per indexed axis."""
+    L = lib()
+    updates = np.ascontiguousarray(updates)
+    indices = [np.ascontiguousarray(i, dtype=np.int32) for i in indices]
+    out = np.zeros(params["shape"], dtype=updates.dtype)
+    i64 = lambda v: (ctypes.c_int64 * max(1, len(v)))(*v)
+    i32 = lambda v: (ctypes.c_int32 * max(1, len(v)))(*v)
+    ptrs = (ctypes.c_void_p * max(1, len(indices)))(*[i.ctypes.data for i in indices])
+    flat = [d for i in indices for d in i.shape]
+    L.oracle_scatter.argtypes = [ctypes.c_int] * 5 + [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int] + [ctypes.c_void_p] * 6
+    L.oracle_scatter(dtype_code, int(params["op"] == "add"), int(bool(params["uniqueIndices"])), params["outDim"],
+                     len(params["shape"]), i64(params["shape"]), updates.ndim, i64(updates.shape), len(indices),
+                     i32(params["axis"]), i32([i.ndim for i in indices]), i64(flat), updates.ctypes.data, ptrs,
+                     out.ctypes.data)
+    return out
+
+
 def wasm_unary(op: int, x: float) -> float:
     return float(lib().oracle_wasm_unary(int(op), float(x)))
 

@@ -697,6 +697,69 @@ int oracle_argsort(int dtype, const void* x, void* y, int32_t* yi, uint64_t batc
   return 0;
 }
 
+// Scatter (src/routine.ts:226-296): zero-fill, then for every update element translate its
+// coordinate to a destination and store / add / or.  Shapes are passed flat; `axis[k]` is the output
+// axis that index input k addresses.  Elements are 4 bytes (f32 / i32 / u32 / Bool) or f64 / f16.
+int oracle_scatter(int dtype, int add, int unique, int out_dim, int out_rank, const int64_t* out_shape,
+                   int upd_rank, const int64_t* upd_shape, int n_index, const int32_t* axis,
+                   const int32_t* idx_ranks, const int64_t* idx_shapes, const void* updates,
+                   const int32_t* const* indices, void* output) {
+  int64_t out_stride[16], upd_stride[16], out_size = 1, n_upd = 1;
+  for (int i = out_rank - 1; i >= 0; i--) { out_stride[i] = out_size; out_size *= out_shape[i]; }
+  for (int i = upd_rank - 1; i >= 0; i--) { upd_stride[i] = n_upd; n_upd *= upd_shape[i]; }
+  const int eb = dtype == JAXCUDA_F16 ? 2 : dtype == JAXCUDA_F64 ? 8 : 4;
+  memset(output, 0, (size_t)out_size * eb);
+  const bool accumulate = add && !unique;
+  int index_rank = 0;
+  std::vector<std::vector<int64_t>> ishape(n_index), istride(n_index);
+  const int64_t* sh = idx_shapes;
+  for (int k = 0; k < n_index; k++) {
+    ishape[k].assign(sh, sh + idx_ranks[k]);
+    istride[k].assign(idx_ranks[k], 1);
+    for (int j = idx_ranks[k] - 2; j >= 0; j--) istride[k][j] = istride[k][j + 1] * ishape[k][j + 1];
+    sh += idx_ranks[k];
+    index_rank = std::max(index_rank, idx_ranks[k]);
+  }
+  std::vector<int> free_dims;
+  for (int i = 0; i < upd_rank; i++) if (i < out_dim || i >= out_dim + index_rank) free_dims.push_back(i);
+  for (int64_t i = 0; i < n_upd; i++) {
+    int64_t at = 0;
+    bool valid = true;
+    size_t fd = 0;
+    for (int ax = 0; ax < out_rank && valid; ax++) {
+      int which = -1;
+      for (int k = 0; k < n_index; k++) if (axis[k] == ax) which = k;
+      int64_t coord;
+      if (which < 0) {
+        const int ud = free_dims[fd++];
+        coord = (i / upd_stride[ud]) % upd_shape[ud];
+      } else {
+        const int first = out_dim + index_rank - idx_ranks[which];
+        int64_t off = 0;
+        for (int j = 0; j < idx_ranks[which]; j++) {
+          if (ishape[which][j] == 1) continue;
+          const int ud = first + j;
+          off += ((i / upd_stride[ud]) % upd_shape[ud]) * istride[which][j];
+        }
+        coord = indices[which][off];
+      }
+      if (coord < 0 || coord >= out_shape[ax]) valid = false;
+      else at += coord * out_stride[ax];
+    }
+    if (!valid) continue;
+    if (dtype == JAXCUDA_F32) { float* o = (float*)output; const float v = ((const float*)updates)[i]; if (accumulate) o[at] += v; else o[at] = v; }
+    else if (dtype == JAXCUDA_F64) { double* o = (double*)output; const double v = ((const double*)updates)[i]; if (accumulate) o[at] += v; else o[at] = v; }
+    else if (dtype == JAXCUDA_F16) {
+      uint16_t* o = (uint16_t*)output; const uint16_t v = ((const uint16_t*)updates)[i];
+      o[at] = accumulate ? double_to_half(half_to_double(o[at]) + half_to_double(v)) : v;
+    } else {
+      uint32_t* o = (uint32_t*)output; const uint32_t v = ((const uint32_t*)updates)[i];
+      if (accumulate && dtype == JAXCUDA_BOOL) o[at] |= v; else if (accumulate) o[at] += v; else o[at] = v;
+    }
+  }
+  return 0;
+}
+
 // Scalar entry points for the known-answer tests of the software transcendentals.
 float oracle_wasm_unary(int op, float x) {
   switch (op) {
