@@ -164,7 +164,7 @@ def mlp_train(be, rank, world, dist, steps=8, warmup=2):
     off = rank * local - (rank * local // chunk) * chunk
     sx = be.put(np.concatenate(xs)[off:off + local])
     sy = be.put(np.concatenate(ys)[off:off + local])
-    tr = mlp.MlpTrainer(be, dims, local, GB)
+    tr = mlp.MlpTrainer(be, dims, local, GB, overlap=os.environ.get("BENCH_MLP_OVERLAP", "1") != "0")
     losses = []
     for _ in range(warmup):
         be.dec_ref(tr.step(sx, sy, world))
@@ -206,6 +206,7 @@ def mlp_train(be, rank, world, dist, steps=8, warmup=2):
             "tflops_algorithmic": flops * steps / ms / 1e9, "scaling": "strong", "launches_per_step": launches / steps,
             "allreduce_bytes": 4 * sum(mlp.leaf_sizes(dims)), "loss_last": vals[-1],
             "replay": "one CUDA graph per step (gradient program + NCCL sum + Adam program)",
+            "gradient_sum": "per layer on a second stream, under back-propagation" if tr.overlap and world > 1 else "after the gradient program",
             "eager_ms_per_step": eager_ms,
             "gemm": "3xTF32 on tcgen05 (f32 accuracy), f32 accumulate"}
 
@@ -337,6 +338,7 @@ def _run():
     ap.add_argument("--skip-extras", action="store_true", help="only the headline program (used under ncu)")
     ap.add_argument("--only-configs", action="store_true",
                     help="run each remaining config kernel a few times and print their figures (used under ncu)")
+    ap.add_argument("--only-mlp", action="store_true", help="only the data-parallel MLP training step")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -363,6 +365,13 @@ def _run():
     from jax_js_b200.backend import CudaBackend
     be = CudaBackend(local)           # raises when the library or the GPU is missing: no fallback
     peaks = measured_peaks()
+    if args.only_mlp:
+        train = mlp_train(be, rank, world, dist, steps=args.steps or 50)
+        be.close()
+        if dist:
+            dist.barrier()
+            dist.destroy_process_group()
+        return {"n_gpus": world, "mlp_train": train} if rank == 0 else None
 
     rng = np.random.default_rng(rank)
     x_host = be.host_alloc(ROWS * COLS * 4)

@@ -149,6 +149,12 @@ uint64_t jaxcuda_stream(jaxcuda_ctx* ctx);
 int jaxcuda_comm_unique_id(void* id128); /* fills 128 bytes (ncclUniqueId) on rank 0 */
 int jaxcuda_comm_init(jaxcuda_ctx* ctx, int rank, int nranks, const void* id128);
 int jaxcuda_allreduce_sum_f32(jaxcuda_ctx* ctx, const jaxcuda_slot* slots, int n);
+/* The same sum on a second stream: it starts after everything dispatched so far and runs under
+ * what is dispatched next.  jaxcuda_comm_join makes later dispatches wait for every sum begun
+ * this way; read, sync, event_record and capture_end join by themselves.  The slots must not be
+ * read, written or released between the two calls. */
+int jaxcuda_allreduce_sum_f32_async(jaxcuda_ctx* ctx, const jaxcuda_slot* slots, int n);
+int jaxcuda_comm_join(jaxcuda_ctx* ctx);
 int jaxcuda_comm_destroy(jaxcuda_ctx* ctx);
 
 /* Sort along the last axis of a contiguous [batch, n] device array without allocating anything.

@@ -86,6 +86,8 @@ SYMBOLS = {
     "jaxcuda_comm_unique_id": (_I, [_P]),
     "jaxcuda_comm_init": (_I, [_P, _I, _I, _P]),
     "jaxcuda_allreduce_sum_f32": (_I, [_P, ctypes.POINTER(_U32), _I]),
+    "jaxcuda_allreduce_sum_f32_async": (_I, [_P, ctypes.POINTER(_U32), _I]),
+    "jaxcuda_comm_join": (_I, [_P]),
     "jaxcuda_comm_destroy": (_I, [_P]),
     "jaxcuda_capture_begin": (_I, [_P]),
     "jaxcuda_capture_end": (_I, [_P, ctypes.POINTER(_P)]),
@@ -322,6 +324,15 @@ class CudaBackend:
     def allreduce_sum_f32(self, slots: Sequence[int]) -> None:
         arr = (ctypes.c_uint32 * max(1, len(slots)))(*slots)
         self._check(self._lib.jaxcuda_allreduce_sum_f32(self._ctx, arr, len(slots)))
+
+    def allreduce_sum_f32_async(self, slots: Sequence[int]) -> None:
+        """The sum on a second stream, under the kernels dispatched next; `comm_join` before the
+        first use of the summed slots."""
+        arr = (ctypes.c_uint32 * max(1, len(slots)))(*slots)
+        self._check(self._lib.jaxcuda_allreduce_sum_f32_async(self._ctx, arr, len(slots)))
+
+    def comm_join(self) -> None:
+        self._check(self._lib.jaxcuda_comm_join(self._ctx))
 
     # -- captured step lists ---------------------------------------------------------------
     def capture_begin(self) -> None:

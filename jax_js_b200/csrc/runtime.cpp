@@ -207,6 +207,10 @@ struct jaxcuda_ctx {
   void* nccl_lib = nullptr;
   void* comm = nullptr;
   int nranks = 1;
+  // second stream for sums that run under later kernels (jaxcuda_allreduce_sum_f32_async)
+  cudaStream_t comm_stream = nullptr;
+  cudaEvent_t comm_fork = nullptr, comm_done = nullptr;
+  bool comm_pending = false;
 };
 
 namespace {
@@ -376,6 +380,12 @@ int jaxcuda_destroy(jaxcuda_ctx* ctx) {
   if (!ctx) return JAXCUDA_OK;
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->stream);
+  if (ctx->comm_stream) {
+    cudaStreamSynchronize(ctx->comm_stream);
+    cudaEventDestroy(ctx->comm_fork);
+    cudaEventDestroy(ctx->comm_done);
+    cudaStreamDestroy(ctx->comm_stream);
+  }
   jaxcuda_comm_destroy(ctx);
   for (auto& kv : ctx->kernels) free_exe(ctx, kv.second.get());
   for (auto& ev : ctx->events) if (ev) cudaEventDestroy(ev);
@@ -449,6 +459,7 @@ int jaxcuda_read(jaxcuda_ctx* ctx, jaxcuda_slot slot, size_t start, size_t count
   if (count == SIZE_MAX) count = s->bytes - start;
   if (count > s->bytes - start) return fail(ctx, JAXCUDA_EINVAL, "read of %zu bytes at %zu beyond buffer of %zu bytes", count, start, s->bytes);
   cudaSetDevice(ctx->device);
+  if (int rc = jaxcuda_comm_join(ctx)) return rc;
   if (count) {
     if (!dst) return fail(ctx, JAXCUDA_EINVAL, "null destination");
     CUDA_TRY(ctx, cudaMemcpyAsync(dst, (const char*)s->ptr + start, count, cudaMemcpyDeviceToHost, ctx->stream));
@@ -795,6 +806,7 @@ int jaxcuda_sync(jaxcuda_ctx* ctx) {
   if (!ctx) return JAXCUDA_EINVAL;
   if (ctx->alloc.capturing) return fail(ctx, JAXCUDA_EINVAL, "sync inside a capture");
   cudaSetDevice(ctx->device);
+  if (int rc = jaxcuda_comm_join(ctx)) return rc;
   if (ctx->tc_dispatched) {  // only contexts that ran the tensor-core skeleton have anything to report
     CUDA_TRY(ctx, cudaMemcpyAsync(ctx->status_host, ctx->status_dev, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
     ctx->tc_dispatched = false;
@@ -809,6 +821,7 @@ int jaxcuda_event_record(jaxcuda_ctx* ctx, int index) {
   cudaSetDevice(ctx->device);
   if ((size_t)index >= ctx->events.size()) ctx->events.resize(index + 1, nullptr);
   if (!ctx->events[index]) CUDA_TRY(ctx, cudaEventCreate(&ctx->events[index]));
+  if (int rc = jaxcuda_comm_join(ctx)) return rc;  // an interval covers the sums begun inside it
   CUDA_TRY(ctx, cudaEventRecord(ctx->events[index], ctx->stream));
   return JAXCUDA_OK;
 }
@@ -850,6 +863,7 @@ int jaxcuda_capture_end(jaxcuda_ctx* ctx, jaxcuda_graph** out) {
   if (!ctx || !out) return JAXCUDA_EINVAL;
   *out = nullptr;
   if (!ctx->alloc.capturing) return fail(ctx, JAXCUDA_EINVAL, "no capture is open");
+  jaxcuda_comm_join(ctx);  // a forked stream must rejoin before the capture closes
   const int id = ctx->alloc.capturing;
   ctx->alloc.capturing = 0;
   cudaGraph_t graph = nullptr;
@@ -949,12 +963,52 @@ int jaxcuda_comm_init(jaxcuda_ctx* ctx, int rank, int nranks, const void* id128)
   return JAXCUDA_OK;
 }
 
+static int allreduce_on(jaxcuda_ctx* ctx, const jaxcuda_slot* slots, int n, cudaStream_t stream);
+
 int jaxcuda_allreduce_sum_f32(jaxcuda_ctx* ctx, const jaxcuda_slot* slots, int n) {
   if (!ctx || (n > 0 && !slots)) return JAXCUDA_EINVAL;
   if (!ctx->comm) {
     if (ctx->nranks == 1) return JAXCUDA_OK;  // a single rank: the sum is the input
     return fail(ctx, JAXCUDA_EINVAL, "communicator not initialised");
   }
+  if (int rc = jaxcuda_comm_join(ctx)) return rc;  // keep NCCL calls of this rank in one order
+  return allreduce_on(ctx, slots, n, ctx->stream);
+}
+
+// The same sum issued on a second stream, so that it runs under the kernels dispatched after it
+// (a gradient leaf is summed while the layers below it are still being differentiated).  The sum
+// starts after everything dispatched so far; nothing dispatched later waits for it until
+// jaxcuda_comm_join, which the caller issues before the first use of the summed slots.  The slots
+// must stay alive until then.
+int jaxcuda_allreduce_sum_f32_async(jaxcuda_ctx* ctx, const jaxcuda_slot* slots, int n) {
+  if (!ctx || (n > 0 && !slots)) return JAXCUDA_EINVAL;
+  if (!ctx->comm) {
+    if (ctx->nranks == 1) return JAXCUDA_OK;
+    return fail(ctx, JAXCUDA_EINVAL, "communicator not initialised");
+  }
+  cudaSetDevice(ctx->device);
+  if (!ctx->comm_stream) {
+    CUDA_TRY(ctx, cudaStreamCreateWithFlags(&ctx->comm_stream, cudaStreamNonBlocking));
+    CUDA_TRY(ctx, cudaEventCreateWithFlags(&ctx->comm_fork, cudaEventDisableTiming));
+    CUDA_TRY(ctx, cudaEventCreateWithFlags(&ctx->comm_done, cudaEventDisableTiming));
+  }
+  CUDA_TRY(ctx, cudaEventRecord(ctx->comm_fork, ctx->stream));
+  CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->comm_stream, ctx->comm_fork, 0));
+  ctx->comm_pending = true;
+  return allreduce_on(ctx, slots, n, ctx->comm_stream);
+}
+
+int jaxcuda_comm_join(jaxcuda_ctx* ctx) {
+  if (!ctx) return JAXCUDA_EINVAL;
+  if (!ctx->comm_pending) return JAXCUDA_OK;
+  cudaSetDevice(ctx->device);
+  CUDA_TRY(ctx, cudaEventRecord(ctx->comm_done, ctx->comm_stream));
+  CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->stream, ctx->comm_done, 0));
+  ctx->comm_pending = false;
+  return JAXCUDA_OK;
+}
+
+static int allreduce_on(jaxcuda_ctx* ctx, const jaxcuda_slot* slots, int n, cudaStream_t stream) {
   auto allreduce = (nccl_allreduce_t)dlsym(ctx->nccl_lib, "ncclAllReduce");
   auto gstart = (nccl_group_t)dlsym(ctx->nccl_lib, "ncclGroupStart");
   auto gend = (nccl_group_t)dlsym(ctx->nccl_lib, "ncclGroupEnd");
@@ -966,7 +1020,7 @@ int jaxcuda_allreduce_sum_f32(jaxcuda_ctx* ctx, const jaxcuda_slot* slots, int n
   int r = 0;
   for (int i = 0; i < n && r == 0; i++) {
     SlotRec* s = find_slot(ctx, slots[i]);
-    if (s->bytes) r = allreduce(s->ptr, s->ptr, s->bytes / 4, /*ncclFloat32*/ 7, /*ncclSum*/ 0, ctx->comm, ctx->stream);
+    if (s->bytes) r = allreduce(s->ptr, s->ptr, s->bytes / 4, /*ncclFloat32*/ 7, /*ncclSum*/ 0, ctx->comm, stream);
   }
   int r2 = gend();
   if (r == 0) r = r2;

@@ -229,7 +229,7 @@ class MlpTrainer:
     program -- identical on every rank, so parameters stay replicated."""
 
     def __init__(self, backend, dims: Sequence[int], local_batch: int, global_batch: int, lr: float = 1e-3,
-                 seed: int = 0, allreduce=None):
+                 seed: int = 0, allreduce=None, overlap: bool = True):
         self.be, self.dims = backend, list(dims)
         self.names = param_order(len(dims) - 1)
         self.sizes = leaf_sizes(dims)
@@ -238,11 +238,38 @@ class MlpTrainer:
         self.grad.prepare(backend)
         self.adam.prepare(backend)
         self.allreduce = allreduce if allreduce is not None else backend.allreduce_sum_f32
+        # With the backend's own sum, each layer's gradient leaves are summed on a second stream as
+        # soon as they exist, under the back-propagation of the layers below.
+        self.overlap = overlap and allreduce is None and hasattr(backend, "allreduce_sum_f32_async")
         self.params = [backend.put(a) for a in init_params(dims, seed)]
         self.mu = [backend.put(np.zeros(n, np.float32)) for n in self.sizes]
         self.nu = [backend.put(np.zeros(n, np.float32)) for n in self.sizes]
         self.count = backend.put(np.zeros(1, np.uint32))
         self.eye = backend.put(np.eye(dims[-1], dtype=np.float32))
+
+    def _grads(self, x_slot: int, y_slot: int, world: int):
+        """Gradient program followed by the sum over ranks; returns (loss slot, gradient slots)."""
+        be = self.be
+        ins = [x_slot, y_slot, self.eye] + self.params
+        if world <= 1:
+            outs = self.grad.execute(be, ins)
+        elif not self.overlap:
+            outs = self.grad.execute(be, ins)
+            self.allreduce(list(outs[1:]) + [outs[0]])
+        else:
+            ready = []
+
+            def on_output(name, slot):
+                ready.append(slot)
+                if name.startswith("db"):        # a layer's last leaf: dW and db go out together
+                    be.allreduce_sum_f32_async(ready)
+                    ready.clear()
+
+            outs = self.grad.execute(be, ins, on_output)
+            if ready:
+                be.allreduce_sum_f32_async(ready)
+            be.comm_join()
+        return outs[0], list(outs[1:])
 
     def capture(self, x_slot: int, y_slot: int, world: int = 1) -> None:
         """Record one whole step (gradient program, gradient sum, Adam program) as a CUDA graph and
@@ -255,10 +282,7 @@ class MlpTrainer:
         be = self.be
         be.capture_begin()
         try:
-            outs = self.grad.execute(be, [x_slot, y_slot, self.eye] + self.params)
-            loss, grads = outs[0], outs[1:]
-            if world > 1:
-                self.allreduce(grads + [loss])
+            loss, grads = self._grads(x_slot, y_slot, world)
             ins = [self.count]
             for i in range(len(self.names)):
                 ins += [self.params[i], grads[i], self.mu[i], self.nu[i]]
@@ -287,10 +311,7 @@ class MlpTrainer:
             be.graph_launch(self.graph)
             be.inc_ref(self.graph_loss)      # the caller releases the loss slot like an eager one
             return self.graph_loss
-        outs = self.grad.execute(be, [x_slot, y_slot, self.eye] + self.params)
-        loss, grads = outs[0], outs[1:]
-        if world > 1:
-            self.allreduce(grads + [loss])
+        loss, grads = self._grads(x_slot, y_slot, world)
         ins = [self.count]
         for i in range(len(self.names)):
             ins += [self.params[i], grads[i], self.mu[i], self.nu[i]]

@@ -161,9 +161,10 @@ class JitProgram:
             if s.kind == "execute" and id(s) not in self._exes:
                 self._exes[id(s)] = backend.prepare_kernel_sync(s.kernel)
 
-    def execute(self, backend, slots: Sequence[int]) -> list:
+    def execute(self, backend, slots: Sequence[int], on_output=None) -> list:
         """Replays the steps; `slots` are the input slots (not consumed).  Returns output slots
-        with reference count 1, owned by the caller."""
+        with reference count 1, owned by the caller.  `on_output(name, slot)` is called right after
+        the kernel that produces a program output has been dispatched."""
         self.prepare(backend)
         env = dict(zip(self.inputs, slots))
         owned = set()
@@ -173,6 +174,8 @@ class JitProgram:
                 owned.add(s.name)
             elif s.kind == "execute":
                 backend.dispatch(self._exes[id(s)], [env[n] for n in s.inputs], [env[s.name]])
+                if on_output is not None and s.name in self.outputs:
+                    on_output(s.name, env[s.name])
             elif s.kind == "free" and s.name in owned:
                 backend.dec_ref(env.pop(s.name))
                 owned.discard(s.name)

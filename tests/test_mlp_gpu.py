@@ -33,7 +33,7 @@ def test_adam_training_matches_oracle_after_1_and_10_steps(backend):
             s = tr.step(sx, sy)
             losses.append(float(be.get(s, "float32")[0]))
             be.dec_ref(s)
-        # f32, GEMM-dominated: 1e-4 relative (BASELINE north_star).  Adam divides by sqrt(nu), which
+        # f32, GEMM-dominated: 1e-4 relative (the GEMM bar).  Adam divides by sqrt(nu), which
         # amplifies last-bit differences where gradients are of the order of eps, so trajectories of
         # the reference's own two accumulation modes drift apart; the bar never goes below that drift.
         # From the fourth step on, ReLU units that sit within rounding of zero start to switch
@@ -44,7 +44,7 @@ def test_adam_training_matches_oracle_after_1_and_10_steps(backend):
         assert abs(losses[0] - losses[1]) <= max(bar * abs(losses[1]), floor), (step, losses)
         if step == 1:
             assert abs(losses[0] - losses[1]) <= 1e-5 * abs(losses[1]), losses
-        if step in (1, 10):
+        if step in (1, 5, 10):
             (b0, t0, _, _), (b1, t1, _, _), (b2, t2, _, _) = trainers
             for s0, s1, s2 in zip(t0.params, t1.params, t2.params):
                 want, got = b1.get(s1, "float32").astype(np.float64), b0.get(s0, "float32").astype(np.float64)
@@ -53,22 +53,91 @@ def test_adam_training_matches_oracle_after_1_and_10_steps(backend):
                 # bias leaves start at zero and are themselves only a few updates large
                 tol = max(1e-4 * np.abs(want).max(), 2e-5)
                 err, ref_err = np.abs(got - want), np.abs(alt - want)
-                # After one step: all but a sliver within 1e-4 of the leaf's scale.  Later a second
-                # mechanism appears that no implementation can avoid: a hidden unit whose
-                # pre-activation lies within rounding of zero switches its ReLU differently under a
-                # different summation order (about 1e-6 of the units per step here), which changes one
-                # whole column of dW by a few per cent of an update (a handful of the 256 columns of a
-                # leaf in ten steps).  So after ten steps the bar is: the typical element still far
-                # inside 1e-4 of the scale, at most a quarter of a leaf beyond it, and nothing off by
-                # more than one full update per step.
+                # After one step: all but a sliver within 1e-4 of the leaf's scale.  After that the two
+                # free-running trajectories separate geometrically (about 1.75x per step here): Adam
+                # divides by sqrt(nu), so a last-bit difference in a gradient moves the next update by
+                # the same relative amount, and that moves the next gradient.  Independently, a hidden
+                # unit whose pre-activation lies within rounding of zero switches its ReLU differently
+                # under a different summation order, which changes one whole column of dW by a few per
+                # cent of an update.  So the free-running bars are: after five steps the typical element
+                # within a tenth of the tolerance and at most 5 % of a leaf beyond it; after ten steps the
+                # typical element still inside 1e-4 of the scale and at most half of a (bias) leaf beyond
+                # it; never anything off by more than one full update per step.  The step-by-step parity of the two programs
+                # from identical state, which has no such amplification, is checked by
+                # test_each_step_from_the_oracle_state below.
                 frac = (err > tol).mean()
-                assert frac <= (1e-4 if step == 1 else 0.25) + 2 * (ref_err > tol).mean(), (step, frac)
-                assert np.median(err) <= 0.1 * tol, (step, np.median(err))
+                assert frac <= {1: 1e-4, 5: 0.05, 10: 0.5}[step] + 2 * (ref_err > tol).mean(), (step, frac)
+                assert np.median(err) <= (1.0 if step == 10 else 0.1) * tol, (step, np.median(err), np.median(ref_err))
                 assert err.max() <= step * 1e-3 * 1.01, f"params after step {step}"
     for be, tr, sx, sy in trainers:
         tr.close()
         be.dec_ref(sx)
         be.dec_ref(sy)
+
+
+def test_each_step_from_the_oracle_state(backend):
+    """Ten Adam steps along the oracle's trajectory; at every step the GPU runs the gradient program
+    and the Adam program from the ORACLE's state of that step, so each comparison is of one program
+    on identical inputs (no accumulated drift)."""
+    dims, B = [784, 256, 256, 10], 512
+    x, y = _data(B, dims[0], dims[-1])
+    ob = OracleBackend()
+    tg, to = mlp.MlpTrainer(backend, dims, B, B), mlp.MlpTrainer(ob, dims, B, B)
+    gx, gy, ox, oy = backend.put(x), backend.put(y), ob.put(x), ob.put(y)
+    up = lambda slot, dt="float32": backend.put(ob.get(slot, dt))
+    strict = 0
+    for step in range(1, 11):
+        ps = [up(s) for s in to.params]
+        outs_g = tg.grad.execute(backend, [gx, gy, tg.eye] + ps)
+        outs_o = to.grad.execute(ob, [ox, oy, to.eye] + to.params)
+        # A hidden unit whose pre-activation is within f32 summation error of zero for some example
+        # ("on the edge") may have its ReLU gate taken either way, depending on summation order; that
+        # example's share (1/B) of the gradient then differs: in one column of that layer's dW, one
+        # element of db, and through dz in every leaf below.  Both outcomes are correct roundings of
+        # the same program.  Edge units are found here in float64 from the state itself (margin
+        # 2e-6: five standard deviations of the summation error of a 784-term f32 dot of these
+        # magnitudes); steps without any get the strict bar, steps with one the loose bar.
+        h, edge = x.astype(np.float64), 0
+        for l in range(len(dims) - 2):
+            z = h @ ob.get(to.params[2 * l], "float32").astype(np.float64).reshape(dims[l], dims[l + 1]) \
+                + ob.get(to.params[2 * l + 1], "float32").astype(np.float64)
+            edge += int((np.abs(z) < 2e-6).sum())
+            h = np.maximum(z, 0)
+        strict += edge == 0
+        for name, a, b in zip(["loss"] + tg.names, outs_g, outs_o):
+            got, want = backend.get(a, "float32").astype(np.float64), ob.get(b, "float32").astype(np.float64)
+            scale = np.abs(want).max()
+            err = np.abs(got - want)
+            # f32, GEMM-dominated: every element within 1e-4 of the leaf's scale, the typical one 10x
+            # closer; with a unit on the edge, one example's share of the gradient: 1e-2 of the scale
+            assert err.max() <= (1e-4 if edge == 0 else 1e-2) * scale, (step, name, edge, err.max(), scale)
+            assert np.median(err) <= 1e-5 * scale, (step, name, np.median(err), scale)
+        cnt = up(to.count, "uint32")
+        ins_g, ins_o, tmp = [cnt], [to.count], [cnt]
+        for i in range(len(tg.names)):
+            gi, mi, ni = up(outs_o[1 + i]), up(to.mu[i]), up(to.nu[i])
+            tmp += [gi, mi, ni]
+            ins_g += [ps[i], gi, mi, ni]
+            ins_o += [to.params[i], outs_o[1 + i], to.mu[i], to.nu[i]]
+        new_g, new_o = tg.adam.execute(backend, ins_g), to.adam.execute(ob, ins_o)
+        assert backend.get(new_g[0], "uint32")[0] == ob.get(new_o[0], "uint32")[0] == step
+        for a, b in zip(new_g[1:], new_o[1:]):
+            got, want = backend.get(a, "float32").astype(np.float64), ob.get(b, "float32").astype(np.float64)
+            # elementwise f32 with one reciprocal, one sqrt and the bias corrections: 1e-5 relative
+            # (the elementwise bar), measured against the element or, where
+            # the element is below one update, against the update size
+            assert (np.abs(got - want) <= 1e-5 * np.maximum(np.abs(want), 1e-3)).all(), step
+        for s in list(outs_g) + ps + tmp + list(new_g):
+            backend.dec_ref(s)
+        for s in list(outs_o) + list(new_o):
+            ob.dec_ref(s)
+        ob.dec_ref(to.step(ox, oy))
+    assert strict >= 3, f"only {strict} of 10 steps were free of edge units: the strict bar was hardly exercised"
+    tg.close()
+    to.close()
+    for be, a, b in ((backend, gx, gy), (ob, ox, oy)):
+        be.dec_ref(a)
+        be.dec_ref(b)
 
 
 def test_per_example_gradients_config4(backend):
