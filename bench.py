@@ -205,7 +205,7 @@ def mlp_train(be, rank, world, dist, steps=8, warmup=2):
     return {"steps_per_s": steps / ms * 1e3, "ms_per_step": ms / steps, "global_batch": GB, "local_batch": local,
             "tflops_algorithmic": flops * steps / ms / 1e9, "scaling": "strong", "launches_per_step": launches / steps,
             "allreduce_bytes": 4 * sum(mlp.leaf_sizes(dims)), "loss_last": vals[-1],
-            "replay": "one CUDA graph per step (gradient program + NCCL sum + Adam program)",
+            "replay": "one CUDA graph launch per step (gradient program + NCCL sum + Adam program; two graphs alternate between two state buffers)",
             "gradient_sum": "per layer on a second stream, under back-propagation" if tr.overlap and world > 1 else "after the gradient program",
             "eager_ms_per_step": eager_ms,
             "gemm": "3xTF32 on tcgen05 (f32 accuracy), f32 accumulate"}

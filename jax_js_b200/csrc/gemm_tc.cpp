@@ -452,7 +452,7 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
 
 int launch_gemm_tc(void* encode_fn, void* launch_fn, const Plan& plan, const std::vector<CUfunction>& fns,
                    const std::vector<void*>& inputs, void* out, void* scratch, cudaStream_t stream,
-                   int* status_dev, std::string& err) {
+                   int* status_dev, std::string& err, int max_ctas) {
   auto encode = (EncodeTiledFn)encode_fn;
   auto launch = (LaunchFn)launch_fn;
   const GemmDesc& g = plan.gemm;
@@ -506,7 +506,8 @@ int launch_gemm_tc(void* encode_fn, void* launch_fn, const Plan& plan, const std
   for (auto& p : ptrs) args.push_back(&p);
   args.push_back(&status_dev);
   const Stage& st = plan.stages.back();
-  CUresult r = launch(fns.back(), st.grid[0], 1, 1, st.block[0], 1, 1, st.smem, (CUstream)stream, args.data(), nullptr);
+  const unsigned grid = max_ctas > 0 ? std::min<unsigned>(st.grid[0], (unsigned)max_ctas) : st.grid[0];
+  CUresult r = launch(fns.back(), grid, 1, 1, st.block[0], 1, 1, st.smem, (CUstream)stream, args.data(), nullptr);
   if (r != CUDA_SUCCESS) { err = "launch of the tcgen05 GEMM kernel failed"; return -1; }
   launches++;
   return launches;

@@ -211,6 +211,9 @@ struct jaxcuda_ctx {
   cudaStream_t comm_stream = nullptr;
   cudaEvent_t comm_fork = nullptr, comm_done = nullptr;
   bool comm_pending = false;
+  // SMs a persistent GEMM leaves free while such a sum is in flight (JAXCUDA_COMM_SMS).  Off by default:
+  // on 8 GPUs 8 SMs changed nothing and 24 or 32 cost more GEMM time than the sum took.
+  int comm_sms = 0;
 };
 
 namespace {
@@ -371,6 +374,7 @@ int jaxcuda_create(int device, jaxcuda_ctx** out) {
   ctx->opt.col_ctas_per_sm = env_int("JAXCUDA_COL_CTAS_PER_SM", ctx->opt.col_ctas_per_sm);
   ctx->opt.col_ty = env_int("JAXCUDA_COL_TY", ctx->opt.col_ty);
   ctx->opt.col_unroll = env_int("JAXCUDA_COL_UNROLL", ctx->opt.col_unroll);
+  ctx->comm_sms = env_int("JAXCUDA_COMM_SMS", ctx->comm_sms);
   ctx->debug = env_int("JAXCUDA_DEBUG", 0);
   *out = ctx.release();
   return JAXCUDA_OK;
@@ -753,7 +757,10 @@ int jaxcuda_dispatch(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const jaxcuda_slot* inp
     for (int i = 0; i < n_inputs; i++) inptr[i] = in[i]->ptr;
     std::string err;
     int nl = launch_gemm_tc(ctx->drv.TensorMapEncodeTiled, (void*)ctx->drv.LaunchKernel, exe->plan, exe->fns, inptr,
-                            outv[0]->ptr, scratch, ctx->stream, ctx->status_dev, err);
+                            outv[0]->ptr, scratch, ctx->stream, ctx->status_dev, err,
+                            // a persistent GEMM that holds every SM would keep a sum begun on the second
+                            // stream waiting until it ends; leave that sum a few SMs while one is in flight
+                            ctx->comm_pending && ctx->comm_sms > 0 ? std::max(1, ctx->opt.sm_count - ctx->comm_sms) : 0);
     if (nl < 0) rc = fail(ctx, JAXCUDA_ECUDA, "%s", err.c_str());
     else { ctx->launches += nl; ctx->tc_dispatched = true; }
   } else {
@@ -988,7 +995,10 @@ int jaxcuda_allreduce_sum_f32_async(jaxcuda_ctx* ctx, const jaxcuda_slot* slots,
   }
   cudaSetDevice(ctx->device);
   if (!ctx->comm_stream) {
-    CUDA_TRY(ctx, cudaStreamCreateWithFlags(&ctx->comm_stream, cudaStreamNonBlocking));
+    int least = 0, greatest = 0;  // the sum's CTAs go first when SMs free up: it is the longer pole
+    CUDA_TRY(ctx, cudaDeviceGetStreamPriorityRange(&least, &greatest));
+    CUDA_TRY(ctx, cudaStreamCreateWithPriority(&ctx->comm_stream, cudaStreamNonBlocking,
+                                               env_int("JAXCUDA_COMM_PRIORITY", 1) ? greatest : least));
     CUDA_TRY(ctx, cudaEventCreateWithFlags(&ctx->comm_fork, cudaEventDisableTiming));
     CUDA_TRY(ctx, cudaEventCreateWithFlags(&ctx->comm_done, cudaEventDisableTiming));
   }

@@ -247,10 +247,10 @@ class MlpTrainer:
         self.count = backend.put(np.zeros(1, np.uint32))
         self.eye = backend.put(np.eye(dims[-1], dtype=np.float32))
 
-    def _grads(self, x_slot: int, y_slot: int, world: int):
+    def _grads(self, x_slot: int, y_slot: int, world: int, params=None):
         """Gradient program followed by the sum over ranks; returns (loss slot, gradient slots)."""
         be = self.be
-        ins = [x_slot, y_slot, self.eye] + self.params
+        ins = [x_slot, y_slot, self.eye] + list(self.params if params is None else params)
         if world <= 1:
             outs = self.grad.execute(be, ins)
         elif not self.overlap:
@@ -271,46 +271,59 @@ class MlpTrainer:
             be.comm_join()
         return outs[0], list(outs[1:])
 
-    def capture(self, x_slot: int, y_slot: int, world: int = 1) -> None:
-        """Record one whole step (gradient program, gradient sum, Adam program) as a CUDA graph and
-        replay it from then on: `step` becomes a single graph launch instead of ~44 dispatches.
+    def _state(self):
+        return [self.count] + [s for i in range(len(self.names)) for s in (self.params[i], self.mu[i], self.nu[i])]
 
-        The graph reads and writes fixed addresses, so the step is closed over the state in place:
-        after the Adam program the new count, parameters and moments are copied over the old ones.
+    def _set_state(self, flat):
+        self.count = flat[0]
+        self.params, self.mu, self.nu = list(flat[1::3]), list(flat[2::3]), list(flat[3::3])
+
+    def capture(self, x_slot: int, y_slot: int, world: int = 1) -> None:
+        """Record one whole step (gradient program, gradient sum, Adam program) as CUDA graphs and
+        replay them from then on: `step` becomes a single graph launch instead of ~44 dispatches.
+
+        A graph reads and writes fixed addresses, so the state (count, parameters, moments) lives in
+        two sets of buffers and two graphs are recorded: one steps from set 0 into set 1, the other
+        from set 1 into set 0, and `step` alternates between them; nothing is copied back.
         x_slot and y_slot are baked in; refresh a batch by writing into them.  Run at least one eager
         step first (kernels set up their scratch on first dispatch)."""
         be = self.be
-        be.capture_begin()
-        try:
-            loss, grads = self._grads(x_slot, y_slot, world)
-            ins = [self.count]
-            for i in range(len(self.names)):
-                ins += [self.params[i], grads[i], self.mu[i], self.nu[i]]
-            new = self.adam.execute(be, ins)
-            be.copy(self.count, new[0])
-            for i in range(len(self.names)):
-                be.copy(self.params[i], new[1 + 3 * i])
-                be.copy(self.mu[i], new[2 + 3 * i])
-                be.copy(self.nu[i], new[3 + 3 * i])
-            for s in list(new) + list(grads):
-                be.dec_ref(s)
-        except Exception:
+        cur = self._state()
+        other = [be.malloc(4)] + [be.malloc(4 * n) for n in self.sizes for _ in range(3)]
+        out_names = self.adam.outputs
+        self.graphs, self.graph_loss = [], []
+        for src, dst in ((cur, other), (other, cur)):
+            be.capture_begin()
             try:
-                be.graph_destroy(be.capture_end())
+                loss, grads = self._grads(x_slot, y_slot, world, params=src[1::3])
+                ins = [src[0]]
+                for i in range(len(self.names)):
+                    ins += [src[1 + 3 * i], grads[i], src[2 + 3 * i], src[3 + 3 * i]]
+                self.adam.execute(be, ins, out_slots=dict(zip(out_names, dst)))
+                for s in grads:
+                    be.dec_ref(s)
             except Exception:
-                pass
-            raise
-        self.graph, self.graph_loss, self.graph_io = be.capture_end(), loss, (x_slot, y_slot, world)
+                try:
+                    be.graph_destroy(be.capture_end())
+                except Exception:
+                    pass
+                raise
+            self.graphs.append(be.capture_end())
+            self.graph_loss.append(loss)
+        self.graph_sets, self.graph_next, self.graph_io = (cur, other), 0, (x_slot, y_slot, world)
 
     def step(self, x_slot: int, y_slot: int, world: int = 1) -> int:
         """One training step on resident inputs; returns the slot of the (global) loss."""
         be = self.be
-        if getattr(self, "graph", None) is not None:
+        if getattr(self, "graphs", None):
             if (x_slot, y_slot, world) != self.graph_io:
                 raise ValueError("the captured step is bound to the slots it was captured with")
-            be.graph_launch(self.graph)
-            be.inc_ref(self.graph_loss)      # the caller releases the loss slot like an eager one
-            return self.graph_loss
+            k = self.graph_next
+            be.graph_launch(self.graphs[k])
+            self.graph_next = 1 - k
+            self._set_state(self.graph_sets[1 - k])
+            be.inc_ref(self.graph_loss[k])   # the caller releases the loss slot like an eager one
+            return self.graph_loss[k]
         loss, grads = self._grads(x_slot, y_slot, world)
         ins = [self.count]
         for i in range(len(self.names)):
@@ -323,9 +336,13 @@ class MlpTrainer:
         return loss
 
     def close(self):
-        if getattr(self, "graph", None) is not None:
-            self.be.dec_ref(self.graph_loss)
-            self.be.graph_destroy(self.graph)
-            self.graph = None
+        if getattr(self, "graphs", None):
+            for g, l in zip(self.graphs, self.graph_loss):
+                self.be.dec_ref(l)
+                self.be.graph_destroy(g)
+            # the current state is graph_sets[graph_next]; the other set holds the previous step
+            for s in self.graph_sets[1 - self.graph_next]:
+                self.be.dec_ref(s)
+            self.graphs = None
         for s in [self.count, self.eye] + self.params + self.mu + self.nu:
             self.be.dec_ref(s)

@@ -161,15 +161,20 @@ class JitProgram:
             if s.kind == "execute" and id(s) not in self._exes:
                 self._exes[id(s)] = backend.prepare_kernel_sync(s.kernel)
 
-    def execute(self, backend, slots: Sequence[int], on_output=None) -> list:
+    def execute(self, backend, slots: Sequence[int], on_output=None, out_slots=None) -> list:
         """Replays the steps; `slots` are the input slots (not consumed).  Returns output slots
         with reference count 1, owned by the caller.  `on_output(name, slot)` is called right after
-        the kernel that produces a program output has been dispatched."""
+        the kernel that produces a program output has been dispatched.  `out_slots` maps names of
+        program outputs to slots the caller already owns: those outputs are written there instead of
+        into fresh slots (they must not alias an input of the kernel that writes them)."""
         self.prepare(backend)
         env = dict(zip(self.inputs, slots))
         owned = set()
         for s in self.steps:
             if s.kind == "malloc":
+                if out_slots and s.name in out_slots:
+                    env[s.name] = out_slots[s.name]
+                    continue
                 env[s.name] = backend.malloc(s.nbytes)
                 owned.add(s.name)
             elif s.kind == "execute":
