@@ -100,6 +100,49 @@ def test_threefry_bits_are_exact(backend):
     assert int(run_cuda(backend, k, [])[0]) == 1797259609   # src/alu.test.ts:202-209
 
 
+def test_gather_kernels_are_exact(backend):
+    """`jitRules[Gather]` (src/frontend/jit.ts:716-763): the data index is built from loaded int32
+    indices.  Rows of a table (an embedding lookup), elements along an axis (takeAlongAxis), and
+    indices outside the table, which read element 0 (src/backend/wasm/translation.ts:221-228)."""
+    rng = np.random.default_rng(5)
+    V, D, B = 1000, 96, 777
+    table = rng.standard_normal((V, D)).astype(np.float32)
+    idx = rng.integers(0, V, B).astype(np.int32)
+    idx[:4] = [0, V - 1, V + 5, -3]                      # the last two are out of range
+    row = AluExp.global_index(I32, 1, B, AluExp.idiv(g, AluExp.i32(D)))
+    k = Kernel(2, B * D, AluExp.global_index(F32, 0, V * D, AluExp.add(AluExp.mul(row, AluExp.i32(D)), AluExp.mod(g, AluExp.i32(D)))))
+    got, want = run_cuda(backend, k, [table, idx]), oracle.run_kernel(k, [table, idx])
+    assert_same_bits(got, want, "row gather")
+    assert np.array_equal(got.reshape(B, D)[4:], table[idx[4:]])
+    assert (got.reshape(B, D)[2:4, 1:] == table[0, 0]).all()   # out of range: element 0 of the table
+    R, C, T = 513, 300, 7
+    x = rng.standard_normal((R, C)).astype(np.float32)
+    along = rng.integers(0, C, (R, T)).astype(np.int32)
+    i = AluExp.idiv(g, AluExp.i32(T))
+    k = Kernel(2, R * T, AluExp.global_index(F32, 0, R * C, AluExp.add(AluExp.mul(i, AluExp.i32(C)), AluExp.global_index(I32, 1, R * T, g))))
+    got = run_cuda(backend, k, [x, along])
+    assert_same_bits(got, oracle.run_kernel(k, [x, along]), "take along axis")
+    assert np.array_equal(got.reshape(R, T), np.take_along_axis(x, along, 1))
+    # gathered rows under a reduction: sum_j table[idx[g], j]
+    k = Kernel(2, B, AluExp.global_index(F32, 0, V * D, AluExp.add(AluExp.mul(AluExp.global_index(I32, 1, B, g), AluExp.i32(D)), r)),
+               Reduction(F32, AluOp.Add, D))
+    assert_close(run_cuda(backend, k, [table, idx]), oracle.run_kernel(k, [table, idx]), 1e-5, np.abs(table).sum(1).max(), "gathered row sums")
+
+
+def test_random_bits_kernel_is_exact(backend):
+    """`jitRules[RandomBits]` (src/frontend/jit.ts:698-714): keys broadcast over the trailing shape,
+    counter = gidx mod the trailing size; 5 keys x 1001 draws, every mode."""
+    keys = np.random.default_rng(6).integers(0, 2**32, (5, 2), dtype=np.uint64).astype(np.uint32)
+    k0s, k1s = np.ascontiguousarray(keys[:, 0]), np.ascontiguousarray(keys[:, 1])
+    n = 1001
+    which = AluExp.idiv(g, AluExp.i32(n))
+    c1 = AluExp.mod(AluExp.cast(U32, g), AluExp.u32(n))
+    for mode in ("xor", 0, 1):
+        k = Kernel(2, 5 * n, AluExp.threefry2x32(AluExp.global_index(U32, 0, 5, which), AluExp.global_index(U32, 1, 5, which),
+                                                 AluExp.u32(0), c1, mode))
+        assert_same_bits(run_cuda(backend, k, [k0s, k1s]), oracle.run_kernel(k, [k0s, k1s]), f"random bits {mode}")
+
+
 def test_out_of_range_and_guarded_loads(backend):
     # a padded view: Where(valid, load, 0) with the load clamped to element 0 when invalid
     from jax_js_b200 import ShapeTracker, accessor_global
