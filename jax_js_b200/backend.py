@@ -10,6 +10,7 @@ the shared library or without a B200 the constructor raises.
 from __future__ import annotations
 
 import ctypes
+import os
 from pathlib import Path
 from typing import Sequence
 
@@ -165,6 +166,24 @@ class Executable:
         return b.value, f.value, n.value
 
 
+def _prefer_packaged_nccl() -> None:
+    """A process holds one libnccl.so.2.  If the `nvidia.nccl` wheel is installed (the copy torch
+    links against), point the library at that file, so that a later `import torch` in the same
+    process finds the NCCL it was built for instead of an older system one."""
+    if os.environ.get("JAXCUDA_NCCL_LIB"):
+        return
+    import importlib.util
+    try:
+        spec = importlib.util.find_spec("nvidia.nccl")
+    except (ImportError, ValueError):
+        spec = None
+    for root in (spec.submodule_search_locations if spec and spec.submodule_search_locations else []):
+        cand = os.path.join(root, "lib", "libnccl.so.2")
+        if os.path.exists(cand):
+            os.environ["JAXCUDA_NCCL_LIB"] = cand
+            return
+
+
 class CudaBackend:
     """`Backend` for device "cuda" (src/backend.ts:158-211)."""
 
@@ -311,11 +330,13 @@ class CudaBackend:
         return int(self._lib.jaxcuda_stream(self._ctx))
 
     def comm_init(self, rank: int, nranks: int, unique_id: bytes) -> None:
+        _prefer_packaged_nccl()
         buf = ctypes.create_string_buffer(unique_id, 128)
         self._check(self._lib.jaxcuda_comm_init(self._ctx, rank, nranks, buf))
 
     @staticmethod
     def comm_unique_id() -> bytes:
+        _prefer_packaged_nccl()
         buf = ctypes.create_string_buffer(128)
         if load_library().jaxcuda_comm_unique_id(buf) != OK:
             raise CudaError("ncclGetUniqueId failed (is libnccl.so.2 loadable?)")

@@ -957,6 +957,198 @@ struct Builder {
     return true;
   }
 
+  // Split-reduction tail shared by the skeletons that keep `[counters | splits x size partials]`
+  // in a persistent scratch area: the CTA that arrives last at its column block's counter folds the
+  // partials in split order (so the result does not depend on arrival order), applies the epilogue
+  // and re-arms the counter.  `outs` = outputs per column block, T = threads per CTA.
+  void emit_split_tail(std::ostream& os, int splits, int64_t outs, int T) const {
+    const char* AT = ctype(k.red_dtype);
+    os << "  __shared__ int last;\n  __threadfence();\n  __syncthreads();\n";
+    os << "  if (threadIdx.x == 0) last = atomicAdd((int*)scratch + blockIdx.x, 1) == " << splits - 1 << ";\n";
+    os << "  __syncthreads();\n  if (!last) return;\n  __threadfence();\n";
+    os << "  for (int o = threadIdx.x; o < " << outs << "; o += " << T << ") {\n";
+    os << "    const long long gl = (long long)blockIdx.x * " << outs << " + o;\n    if (gl >= " << k.size << "LL) break;\n";
+    os << "    const int gidx = (int)gl;\n    " << AT << " acc_u = " << identity_literal(k.red_op, k.red_dtype) << ";\n";
+    os << "    for (int s = 0; s < " << splits << "; s++) { const " << AT << " v = __ldcg(parts + (size_t)s * " << k.size
+       << " + gidx); acc_u = " << red("acc_u", "v") << "; }\n";
+    std::vector<std::string> en(k.epi.size());
+    std::vector<char> eall(k.epi.size(), 1);
+    Env ee;
+    ee.prefix = "e";
+    ee.acc = "acc_u";
+    emit_nodes(os, k.epi, an_epi, en, eall, ee, "    ");
+    os << "    out[gidx] = " << to_storage(out_dt, en.back()) << ";\n  }\n";
+    os << "  if (threadIdx.x == 0) ((int*)scratch)[blockIdx.x] = 0;\n";
+  }
+
+  // Skinny dot with an m-contiguous big operand: C[m, n] = sum_k A[k, m] B[k, n], N <= 16 (the
+  // weight gradient of a class-count sized layer: K is the batch).  A thread owns four consecutive
+  // m (one 128-bit load of A per k) and all N columns, 4N accumulators; TY thread rows interleave k
+  // and keep four loads in flight each; the CTA's slice of B sits in shared memory, rows padded to
+  // a multiple of four floats, so that a warp reads it with broadcast 128-bit loads.  K is split
+  // over grid.y; partials are folded by the last CTA to arrive (deterministic order).
+  bool dot_skinny_t(const GemmDesc& g, Plan& p) const {
+    const int e = dtype_bytes(g.dtA);
+    if (g.sAm != 1 || g.M % 4 || (g.offA * e) % (4 * e) || (g.sAk * e) % (4 * e) || g.N > 16) return false;
+    const int T = 256, U = 4;
+    const int TX = g.M / 4 >= 64 ? 64 : 32, TY = T / TX;
+    const int NP = (int)((g.N + 3) / 4 * 4);
+    const int64_t gx = (g.M / 4 + TX - 1) / TX;
+    int64_t splits = std::max<int64_t>(1, ((int64_t)opt.sm_count * 2 + gx - 1) / gx);
+    splits = std::min<int64_t>(splits, std::max<int64_t>(1, g.K / (TY * U)));
+    splits = std::max<int64_t>(splits, (g.K * NP * 4 + 48 * 1024 - 1) / (48 * 1024));
+    int64_t rchunk = (g.K + splits - 1) / splits;
+    rchunk = (rchunk + TY - 1) / TY * TY;
+    splits = (g.K + rchunk - 1) / rchunk;
+    const int64_t outs = (int64_t)TX * 4 * g.N;
+    const int64_t counter_pad = (1024 + gx * 4 + 255) / 256 * 256;
+    p.skeleton = SK_REDUCE_COL;
+    p.gemm = g;
+    account(p);
+    p.algo_flops = 2.0 * g.M * g.N * g.K;
+    std::ostringstream os;
+    os << header();
+    os << "#define GM " << g.M << "\n#define GN " << g.N << "\n#define GK " << g.K << "\n#define NP " << NP << "\n";
+    os << "#define TX " << TX << "\n#define TY " << TY << "\n#define RCHUNK " << rchunk << "\n";
+    os << "#define OFFA " << g.offA << "LL\n#define SAK " << g.sAk << "LL\n";
+    os << "#define OFFB " << g.offB << "LL\n#define SBN " << g.sBn << "LL\n#define SBK " << g.sBk << "LL\n";
+    os << "typedef " << ptype(g.dtA) << " TA;\ntypedef " << ptype(g.dtB) << " TB;\n";
+    os << "extern \"C\" __global__ void __launch_bounds__(" << T << ") jx_dot_skinny_t(" << params() << ") {\n";
+    os << "  extern __shared__ __align__(16) float smem[];\n  float* Bs = smem;                  // [RCHUNK][NP]\n";
+    os << "  float* fold = smem + RCHUNK * NP;   // [4 * GN][TX]\n";
+    os << "  const TA* A = (const TA*)p" << g.gidA << " + OFFA;\n  const TB* B = (const TB*)p" << g.gidB << " + OFFB;\n";
+    os << "  const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;\n";
+    os << "  const int m0 = (blockIdx.x * TX + tx) * 4;\n  const bool active = m0 < GM;\n";
+    os << "  const int k0 = blockIdx.y * RCHUNK;\n  const int kn = min(GK - k0, RCHUNK);\n";
+    os << "  for (int i = threadIdx.x; i < kn * NP; i += " << T << ") {\n    const int kk = i / NP, n = i - kk * NP;\n";
+    os << "    Bs[i] = n < GN ? " << from_storage(g.dtB, "B[(i64)n * SBN + (i64)(k0 + kk) * SBK]") << " : 0.0f;\n  }\n  __syncthreads();\n";
+    os << "  float acc[4 * GN];\n  #pragma unroll\n  for (int q = 0; q < 4 * GN; q++) acc[q] = 0.0f;\n";
+    os << "  const TA* Ap = A + (i64)k0 * SAK + (active ? m0 : 0);\n";
+    os << "  for (int kb = ty; kb < kn; kb += TY * " << U << ") {\n    jx_pack<TA, 4> x[" << U << "];\n";
+    os << "    #pragma unroll\n    for (int j = 0; j < " << U << "; j++) {\n      const int kk = kb + j * TY;\n";
+    os << "      if (kk < kn) jx_load(x[j], Ap + (i64)kk * SAK);\n    }\n";
+    os << "    #pragma unroll\n    for (int j = 0; j < " << U << "; j++) {\n      const int kk = kb + j * TY;\n      if (kk < kn) {\n";
+    os << "        float bv[NP];\n        #pragma unroll\n        for (int q = 0; q < NP; q += 4) *reinterpret_cast<float4*>(&bv[q]) = *reinterpret_cast<const float4*>(&Bs[kk * NP + q]);\n";
+    os << "        #pragma unroll\n        for (int v = 0; v < 4; v++) {\n          const float a = " << from_storage(g.dtA, "x[j].e[v]") << ";\n";
+    os << "          #pragma unroll\n          for (int n = 0; n < GN; n++) acc[v * GN + n] = fmaf(a, bv[n], acc[v * GN + n]);\n        }\n      }\n    }\n  }\n";
+    os << "  for (int y = 1; y < TY; y++) {\n    if (ty == y) {\n      #pragma unroll\n      for (int q = 0; q < 4 * GN; q++) fold[q * TX + tx] = acc[q];\n    }\n    __syncthreads();\n";
+    os << "    if (ty == 0) {\n      #pragma unroll\n      for (int q = 0; q < 4 * GN; q++) acc[q] += fold[q * TX + tx];\n    }\n    __syncthreads();\n  }\n";
+    if (splits > 1) {
+      os << "  float* parts = (float*)((char*)scratch + " << counter_pad << ");\n";
+      os << "  if (ty == 0 && active) {\n    float* part = parts + (size_t)blockIdx.y * " << k.size << " + (size_t)m0 * GN;\n";
+      os << "    #pragma unroll\n    for (int q = 0; q < 4 * GN; q += 4) *reinterpret_cast<float4*>(part + q) = make_float4(acc[q], acc[q + 1], acc[q + 2], acc[q + 3]);\n  }\n";
+      emit_split_tail(os, (int)splits, outs, T);
+    } else {
+      os << "  if (ty != 0 || !active) return;\n  #pragma unroll\n  for (int q = 0; q < 4 * GN; q++) {\n";
+      os << "    const int gidx = m0 * GN + q;\n    const float acc_u = acc[q];\n";
+      std::vector<std::string> en(k.epi.size());
+      std::vector<char> eall(k.epi.size(), 1);
+      Env ee;
+      ee.prefix = "e";
+      ee.acc = "acc_u";
+      emit_nodes(os, k.epi, an_epi, en, eall, ee, "    ");
+      os << "    out[gidx] = " << to_storage(out_dt, en.back()) << ";\n  }\n";
+    }
+    os << "}\n";
+    p.source = os.str();
+    Stage st;
+    st.entry = "jx_dot_skinny_t";
+    st.grid[0] = (unsigned)gx;
+    st.grid[1] = (unsigned)splits;
+    st.block[0] = T;
+    st.smem = (unsigned)((rchunk * NP + outs) * 4);
+    p.stages.push_back(st);
+    if (splits > 1) {
+      p.scratch_bytes = (size_t)counter_pad + (size_t)splits * k.size * 4;
+      p.scratch_persistent = true;
+    }
+    p.describe = "dot-skinny-t " + S(g.M) + "x" + S(g.N) + "x" + S(g.K) + " TY=" + S(TY) + " splits=" + S(splits) + " grid=" + S(gx) + "x" + S(T);
+    return true;
+  }
+
+  // Dot with a tiny contraction (K <= 16, e.g. back-propagation through a class-count sized layer):
+  // C[m, n] = epilogue(sum_k A[m, k] B[n, k]).  The kernel is bound by writing C (and by whatever the
+  // epilogue reads per element), so it is laid out like the elementwise skeleton: a thread owns four
+  // consecutive n, keeps its 4 x K slice of B in registers for its whole life, and walks the CTA's
+  // rows two at a time; the rows of A sit in shared memory and are read with broadcast loads; loads
+  // of the epilogue that are contiguous in gidx are fetched as 128-bit vectors ahead of the math.
+  bool dot_small_k(const GemmDesc& g, Plan& p) const {
+    if (g.K > 16 || g.N % 4 || g.N < 128 || g.M < 64) return false;
+    const int T = 256, NB = T * 4, NBP = NB + 4, ILP = 2;
+    const int KA = (int)((g.K + 3) / 4 * 4);
+    const int64_t gx = (g.N + NB - 1) / NB;
+    const int64_t want_y = std::max<int64_t>(1, (int64_t)opt.sm_count * 4 / gx);
+    int64_t rc = std::min<int64_t>(256, std::max<int64_t>(ILP, (g.M + want_y - 1) / want_y));
+    rc = (rc + ILP - 1) / ILP * ILP;
+    const int64_t gy = (g.M + rc - 1) / rc;
+    if (gy > 65535) return false;
+    p.skeleton = SK_GEMM_FFMA;
+    p.gemm = g;
+    account(p);
+    p.algo_flops = 2.0 * g.M * g.N * g.K;
+    const bool b_kcontig = std::llabs(g.sBk) <= std::llabs(g.sBn);
+    std::ostringstream os;
+    os << header();
+    os << "#define GM " << g.M << "\n#define GN " << g.N << "\n#define GK " << g.K << "\n#define KA " << KA << "\n";
+    os << "#define NB " << NB << "\n#define NBP " << NBP << "\n#define RC " << rc << "\n";
+    os << "#define OFFA " << g.offA << "LL\n#define SAM " << g.sAm << "LL\n#define SAK " << g.sAk << "LL\n";
+    os << "#define OFFB " << g.offB << "LL\n#define SBN " << g.sBn << "LL\n#define SBK " << g.sBk << "LL\n";
+    os << "typedef " << ptype(g.dtA) << " TA;\ntypedef " << ptype(g.dtB) << " TB;\n";
+    os << "extern \"C\" __global__ void __launch_bounds__(" << T << ") jx_dot_small_k(" << params() << ") {\n";
+    os << "  extern __shared__ __align__(16) float smem[];\n  float* Bs = smem;              // [GK][NBP]\n  float* As = smem + GK * NBP;   // [RC][KA]\n";
+    os << "  const TA* A = (const TA*)p" << g.gidA << " + OFFA;\n  const TB* B = (const TB*)p" << g.gidB << " + OFFB;\n";
+    os << "  const int nb = blockIdx.x * NB, n0 = nb + threadIdx.x * 4;\n  const bool active = n0 < GN;\n";
+    os << "  const int r0 = blockIdx.y * RC;\n  const int rn = min(GM - r0, RC);\n";
+    os << "  for (int i = threadIdx.x; i < NB * GK; i += " << T << ") {\n";
+    if (b_kcontig) os << "    const int n = i / GK, kk = i - n * GK;\n";
+    else os << "    const int kk = i / NB, n = i - kk * NB;\n";
+    os << "    Bs[kk * NBP + n] = nb + n < GN ? " << from_storage(g.dtB, "B[(i64)(nb + n) * SBN + (i64)kk * SBK]") << " : 0.0f;\n  }\n";
+    os << "  for (int i = threadIdx.x; i < RC * KA; i += " << T << ") {\n    const int r = i / KA, kk = i - r * KA;\n";
+    os << "    As[i] = (r < rn && kk < GK) ? " << from_storage(g.dtA, "A[(i64)(r0 + r) * SAM + (i64)kk * SAK]") << " : 0.0f;\n  }\n  __syncthreads();\n";
+    os << "  if (!active) return;\n";
+    os << "  float w[4][GK];\n  #pragma unroll\n  for (int kk = 0; kk < GK; kk++) {\n    const float4 t = *reinterpret_cast<const float4*>(&Bs[kk * NBP + threadIdx.x * 4]);\n";
+    os << "    w[0][kk] = t.x; w[1][kk] = t.y; w[2][kk] = t.z; w[3][kk] = t.w;\n  }\n";
+    std::map<size_t, std::string> ov;
+    std::ostringstream decl, fetch;
+    std::vector<std::string> bnames(k.epi.size());
+    std::vector<char> eall(k.epi.size(), 1);
+    Env env;
+    env.prefix = "e";
+    preload(decl, fetch, k.epi, an_epi, eall, 0, 4, env, "g0", "[" + S(ILP) + "]", "[j]", "u", ov, bnames, "        ");
+    os << "  for (int rb = 0; rb < rn; rb += " << ILP << ") {\n";
+    os << decl.str();
+    os << "    #pragma unroll\n    for (int j = 0; j < " << ILP << "; j++) {\n      if (rb + j < rn) {\n";
+    os << "        const int g0 = (r0 + rb + j) * GN + n0;\n";
+    os << fetch.str();
+    os << "      }\n    }\n";
+    os << "    #pragma unroll\n    for (int j = 0; j < " << ILP << "; j++) {\n      if (rb + j < rn) {\n";
+    os << "        const int g0 = (r0 + rb + j) * GN + n0;\n";
+    os << "        float a[KA];\n        #pragma unroll\n        for (int q = 0; q < KA; q += 4) *reinterpret_cast<float4*>(&a[q]) = *reinterpret_cast<const float4*>(&As[(rb + j) * KA + q]);\n";
+    os << "        jx_pack<" << ptype(out_dt) << ", 4> res;\n";
+    os << "        #pragma unroll\n        for (int u = 0; u < 4; u++) {\n          const int gidx = g0 + u;\n";
+    os << "          float acc_u = 0.0f;\n          #pragma unroll\n          for (int kk = 0; kk < GK; kk++) acc_u = fmaf(a[kk], w[u][kk], acc_u);\n";
+    {
+      std::vector<std::string> en(k.epi.size());
+      Env ee;
+      ee.prefix = "e";
+      ee.acc = "acc_u";
+      ee.load_override = &ov;
+      emit_nodes(os, k.epi, an_epi, en, eall, ee, "          ");
+      os << "          res.e[u] = " << to_storage(out_dt, en.back()) << ";\n";
+    }
+    os << "        }\n        jx_store(out + g0, res);\n      }\n    }\n  }\n}\n";
+    p.source = os.str();
+    Stage st;
+    st.entry = "jx_dot_small_k";
+    st.grid[0] = (unsigned)gx;
+    st.grid[1] = (unsigned)gy;
+    st.block[0] = T;
+    st.smem = (unsigned)((g.K * NBP + rc * KA) * 4);
+    p.stages.push_back(st);
+    p.describe = "dot-small-k " + S(g.M) + "x" + S(g.N) + "x" + S(g.K) + " rows/cta=" + S(rc) + " grid=" + S(gx) + "x" + S(gy) + "x" + S(T);
+    return true;
+  }
+
   Plan build() const {
     if (!k.has_red) return elementwise();
     if (opt.force_skeleton == SK_REDUCE_ROW) return reduce_row();
@@ -967,8 +1159,13 @@ struct Builder {
       // warp keeps all N partial sums of its rows.
       if (g.N <= 16 && g.M >= 256 && g.K >= 64) {
         if (g.sAk == 1) { Plan p; if (dot_skinny(g, p)) return p; }
-        if (g.sAm == 1 && g.K >= 256) return reduce_col((int)g.N);
+        if (g.sAm == 1 && g.K >= 256) {
+          Plan p;
+          if (dot_skinny_t(g, p)) return p;
+          return reduce_col((int)g.N);
+        }
       }
+      if (g.K <= 16) { Plan p; if (dot_small_k(g, p)) return p; }
     }
     if (g.valid && g.batch <= 65535 &&
         ((g.M >= opt.gemm_min_dim && g.N >= opt.gemm_min_dim && g.K >= 8) || opt.force_skeleton == SK_GEMM_FFMA)) {

@@ -344,6 +344,51 @@ def test_gemm_f32_bias_relu_batched_and_swapped(backend):
     np.testing.assert_allclose(got, np.einsum("bmk,bkn->bmn", Ab, Bb), rtol=1e-4, atol=1e-4)
 
 
+@pytest.mark.parametrize("M,N,K,al,bl,kw", [
+    (2048, 10, 8192, "km", "kn", {}),                      # weight gradient of a 10-class layer: dot-skinny-t
+    (1000, 16, 777, "km", "kn", {}),                       # ragged K and M, widest N
+    (512, 3, 4100, "km", "kn", dict(bias=True)),           # epilogue after the split fold
+    (260, 8, 300, "km", "kn", dict(relu=True)),
+    (8192, 2048, 10, "mk", "nk", dict(bias=True, relu=True)),   # K = 10: dot-small-k, both operands k-contiguous
+    (300, 512, 7, "mk", "kn", dict(bias=True)),            # B read [K, N]
+    (65, 1028, 16, "km", "nk", {}),                        # odd row count, last column block ragged
+])
+def test_skinny_and_small_k_dots(backend, M, N, K, al, bl, kw):
+    rng = np.random.default_rng(7)
+    A = rng.uniform(-1, 1, (M, K) if al == "mk" else (K, M)).astype(np.float32)
+    B = rng.uniform(-1, 1, (K, N) if bl == "kn" else (N, K)).astype(np.float32)
+    bias = rng.uniform(-1, 1, N).astype(np.float32)
+    k = P.dot_kernel(M, N, K, F32, a_layout=al, b_layout=bl, **kw)
+    exe = backend.prepare_kernel(k)
+    assert exe.describe.startswith("dot-skinny-t" if N <= 16 else "dot-small-k"), exe.describe
+    got = _gemm_case(backend, k, [A, B, bias][: k.nargs], K, 1e-4, F32).reshape(M, N)
+    Am, Bm = (A if al == "mk" else A.T), (B if bl == "kn" else B.T)
+    ref = Am.astype(np.float64) @ Bm.astype(np.float64)
+    if kw.get("bias"):
+        ref = ref + bias.astype(np.float64)
+    if kw.get("relu"):
+        ref = np.maximum(ref, 0)
+    assert_close(got, ref, 2e-6, np.abs(Am).astype(np.float64) @ np.abs(Bm).astype(np.float64) + 1, "dot vs f64")
+    # a second dispatch re-uses the persistent scratch (arrival counters re-armed by the first)
+    assert np.array_equal(run_cuda(backend, k, [A, B, bias][: k.nargs]), got.reshape(-1).astype(np.float32))
+
+
+def test_mlp_backward_dot_through_relu_gate(backend):
+    """dz[b, j] = (sum_k dz_next[b, k] W[j, k]) gated by the activation a[b, j] > 0: the K = 10 kernel of
+    the MLP's backward pass, whose epilogue reads a third array contiguously in gidx."""
+    from jax_js_b200 import mlp
+    B, H, C = 515, 2048, 10
+    rng = np.random.default_rng(8)
+    dz, W = rng.standard_normal((B, C)).astype(np.float32), rng.standard_normal((H, C)).astype(np.float32)
+    a = np.maximum(rng.standard_normal((B, H)), 0).astype(np.float32)
+    k = mlp.backprop_dot_kernel(B, H, C)
+    assert backend.prepare_kernel(k).describe.startswith("dot-small-k")
+    got = run_cuda(backend, k, [dz, W, a]).reshape(B, H)
+    want = oracle.run_kernel(k, [dz, W, a], fma=True).reshape(B, H)
+    assert np.array_equal(got == 0, want == 0)
+    assert_close(got, want, 1e-5, np.abs(dz).astype(np.float64) @ np.abs(W.T).astype(np.float64), "gated dot")
+
+
 @pytest.mark.parametrize("n", [256, 4096])
 def test_gemm_f16(backend, n):
     rng = np.random.default_rng(0)
