@@ -300,6 +300,9 @@ struct Builder {
     return os.str();
   }
 
+  std::string params_rev() const { return params() + ", int jx_rev"; }
+  static const char* rev_block() { return "  const unsigned jx_bx = jx_rev ? gridDim.x - 1 - blockIdx.x : blockIdx.x;\n"; }
+
   std::string red(const std::string& a, const std::string& b) const {
     return binary_expr(k.red_op, k.red_dtype, a, b, 0, nullptr);
   }
@@ -370,7 +373,9 @@ struct Builder {
 
     std::ostringstream os;
     os << header();
-    os << "extern \"C\" __global__ void __launch_bounds__(" << T << ") jx_elementwise(" << params() << ") {\n";
+    os << "extern \"C\" __global__ void __launch_bounds__(" << T << ") jx_elementwise(" << params_rev() << ") {\n";
+    p.takes_rev = true;
+    os << rev_block();
     if (nvec > 0) {
       std::map<size_t, std::string> ov;
       std::ostringstream decl, fetch;
@@ -378,7 +383,7 @@ struct Builder {
       Env env;
       if (V > 1)
         preload(decl, fetch, k.exp, an_exp, all, 0, V, env, "g0", "[" + S(ILP) + "]", "[j]", "u", ov, bnames, "        ");
-      os << "  for (int base = blockIdx.x * " << T * ILP << "; base < " << nvec << "; base += gridDim.x * " << T * ILP << ") {\n";
+      os << "  for (int base = jx_bx * " << T * ILP << "; base < " << nvec << "; base += gridDim.x * " << T * ILP << ") {\n";
       os << decl.str();
       os << "    #pragma unroll\n    for (int j = 0; j < " << ILP << "; j++) {\n";
       os << "      const int vi = base + j * " << T << " + threadIdx.x;\n";
@@ -506,9 +511,11 @@ struct Builder {
 
     std::ostringstream os;
     os << header();
-    os << "extern \"C\" __global__ void __launch_bounds__(" << T << ") jx_reduce_row(" << params() << ") {\n";
+    os << "extern \"C\" __global__ void __launch_bounds__(" << T << ") jx_reduce_row(" << params_rev() << ") {\n";
+    p.takes_rev = true;
+    os << rev_block();
     os << "  const int lane = threadIdx.x % " << TPR << ", rowc = threadIdx.x / " << TPR << ";\n";
-    os << "  const long long gl = (long long)blockIdx.x * " << RPC << " + rowc;\n";
+    os << "  const long long gl = (long long)jx_bx * " << RPC << " + rowc;\n";
     os << "  const bool active = gl < " << k.size << "LL;\n";
     os << "  const int gidx = active ? (int)gl : 0;\n";
     if (splits > 1) {

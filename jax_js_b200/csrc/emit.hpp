@@ -45,6 +45,10 @@ struct Plan {
   std::string source;        // complete CUDA C translation unit for NVRTC
   std::vector<Stage> stages;  // launched in order on the backend's stream
   size_t scratch_bytes = 0;   // global scratch shared by the stages (split reductions, TF32 planes)
+  // The kernel takes a trailing `int jx_rev`: non-zero walks the grid from the last block to the
+  // first.  Consecutive streaming kernels alternate, so that each starts on the part of the
+  // previous kernel's data that is still in L2.
+  bool takes_rev = false;
   bool scratch_persistent = false;  // scratch belongs to the executable and starts zeroed (arrival counters)
   std::string describe;       // one line: skeleton and launch shape
   GemmDesc gemm;

@@ -211,6 +211,9 @@ struct jaxcuda_ctx {
   cudaStream_t comm_stream = nullptr;
   cudaEvent_t comm_fork = nullptr, comm_done = nullptr;
   bool comm_pending = false;
+  // direction of the next streaming kernel's walk over its grid (JAXCUDA_SWEEP=0: always forward)
+  int sweep = 0;
+  bool sweep_alternate = true;
   // SMs a persistent GEMM leaves free while such a sum is in flight (JAXCUDA_COMM_SMS).  Off by default:
   // on 8 GPUs 8 SMs changed nothing and 24 or 32 cost more GEMM time than the sum took.
   int comm_sms = 0;
@@ -375,6 +378,7 @@ int jaxcuda_create(int device, jaxcuda_ctx** out) {
   ctx->opt.col_ty = env_int("JAXCUDA_COL_TY", ctx->opt.col_ty);
   ctx->opt.col_unroll = env_int("JAXCUDA_COL_UNROLL", ctx->opt.col_unroll);
   ctx->comm_sms = env_int("JAXCUDA_COMM_SMS", ctx->comm_sms);
+  ctx->sweep_alternate = env_int("JAXCUDA_SWEEP", 1) != 0;
   ctx->debug = env_int("JAXCUDA_DEBUG", 0);
   *out = ctx.release();
   return JAXCUDA_OK;
@@ -765,7 +769,14 @@ int jaxcuda_dispatch(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const jaxcuda_slot* inp
     else { ctx->launches += nl; ctx->tc_dispatched = true; }
   } else {
     std::vector<void*> ptrs(n_inputs + 2);
-    std::vector<void*> args(n_inputs + 2);
+    std::vector<void*> args(n_inputs + 3);
+    int rev = 0;
+    if (exe->plan.takes_rev) {
+      rev = ctx->sweep_alternate ? ctx->sweep : 0;
+      // only a kernel that streams more than a fraction of L2 changes what the cache holds
+      if (exe->plan.algo_bytes >= 16.0 * 1024 * 1024) ctx->sweep ^= 1;
+    }
+    args[n_inputs + 2] = &rev;
     for (int i = 0; i < n_inputs; i++) ptrs[i] = in[i]->ptr;
     ptrs[n_inputs] = outv[0]->ptr;
     ptrs[n_inputs + 1] = scratch;
