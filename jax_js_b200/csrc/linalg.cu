@@ -1,0 +1,236 @@
+// TriangularSolve, Cholesky and LU routines (CPU reference: src/routine.ts:298-432).
+//
+// The reference runs these on typed arrays with JavaScript numbers: every intermediate is a double
+// and a value is rounded to the array's element type only when it is stored.  The kernels keep
+// that arithmetic (double accumulators and quotients, one rounding per store), so float32 results
+// agree with the reference to the last bit except where a sum's order of addition (here: split
+// over the lanes of a warp) changes a double's last bit exactly at a float32 rounding boundary.
+//
+// Parallelism: independent matrices (and right-hand sides) go to different CTAs (warps); inside a
+// matrix the algorithms are the reference's, column by column, with the work of one column spread
+// over the CTA.  A matrix stays in L2/L1 while its CTA works on it.  Large single matrices would
+// want a blocked, multi-CTA factorisation on top of the GEMM skeleton; that is not built.
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/jaxcuda_ir.h"
+#include "linalg.hpp"
+
+namespace {
+
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// ---- Cholesky-Banachiewicz, one CTA per matrix -------------------------------------------------
+// Column j: the diagonal first (warp 0), then L[i, j] for i > j, one warp per row, lanes over k.
+template <class T>
+__global__ void __launch_bounds__(1024) cholesky_kernel(const T* __restrict__ x, T* __restrict__ y, int n) {
+  extern __shared__ double rowj[];  // row j of L, columns < j; rowj[n] = the stored diagonal
+  const T* A = x + (size_t)blockIdx.x * n * n;
+  T* L = y + (size_t)blockIdx.x * n * n;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (size_t i = threadIdx.x; i < (size_t)n * n; i += blockDim.x) L[i] = (T)0;
+  __syncthreads();
+  for (int j = 0; j < n; j++) {
+    for (int k = threadIdx.x; k < j; k += blockDim.x) rowj[k] = (double)L[(size_t)j * n + k];
+    __syncthreads();
+    if (warp == 0) {
+      double s = 0.0;
+      for (int k = lane; k < j; k += 32) s = fma(rowj[k], rowj[k], s);
+      s = warp_sum(s);
+      if (lane == 0) {
+        const T d = (T)sqrt((double)A[(size_t)j * n + j] - s);
+        L[(size_t)j * n + j] = d;
+        rowj[n] = (double)d;
+      }
+    }
+    __syncthreads();
+    const double d = rowj[n];
+    for (int i = j + 1 + warp; i < n; i += nw) {
+      const T* Li = L + (size_t)i * n;
+      double s = 0.0;
+      for (int k = lane; k < j; k += 32) s = fma((double)Li[k], rowj[k], s);
+      s = warp_sum(s);
+      if (lane == 0) L[(size_t)i * n + j] = (T)(((double)A[(size_t)i * n + j] - s) / d);
+    }
+    __syncthreads();
+  }
+}
+
+// ---- back substitution, one warp per right-hand side ----------------------------------------------
+template <class T>
+__global__ void __launch_bounds__(256) trisolve_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ x,
+                                                       int n, long long rows, long long total, int unit) {
+  extern __shared__ double xs_all[];  // [warps][n]: the solved entries, as stored
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const long long rhs = (long long)blockIdx.x * nw + warp;
+  if (rhs >= total) return;
+  const T* A = a + (size_t)(rhs / rows) * n * n;
+  const T* bv = b + (size_t)rhs * n;
+  T* xv = x + (size_t)rhs * n;
+  double* xs = xs_all + (size_t)warp * n;
+  for (int i = n - 1; i >= 0; i--) {
+    const T* Ai = A + (size_t)i * n;
+    double s = 0.0;
+    for (int j = i + 1 + lane; j < n; j += 32) s = fma((double)Ai[j], xs[j], s);
+    s = warp_sum(s);
+    if (lane == 0) {
+      double v = (double)bv[i] - s;
+      if (!unit) v = v / (double)Ai[i];
+      const T r = (T)v;
+      xv[i] = r;
+      xs[i] = (double)r;
+    }
+    __syncwarp();
+  }
+}
+
+// ---- LU with partial pivoting, one CTA per matrix ---------------------------------------------------
+template <class T>
+__global__ void __launch_bounds__(1024) lu_kernel(const T* __restrict__ a, T* __restrict__ lu_all, int32_t* __restrict__ pivots,
+                                                  int32_t* __restrict__ perm_all, int m, int n) {
+  __shared__ double best_v[32];
+  __shared__ int best_r[32];
+  __shared__ int pivot_row;
+  const int r = m < n ? m : n;
+  const T* A = a + (size_t)blockIdx.x * m * n;
+  T* lu = lu_all + (size_t)blockIdx.x * m * n;
+  int32_t* piv = pivots + (size_t)blockIdx.x * r;
+  int32_t* perm = perm_all + (size_t)blockIdx.x * m;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
+  for (size_t i = tid; i < (size_t)m * n; i += blockDim.x) lu[i] = A[i];
+  for (int i = tid; i < m; i += blockDim.x) perm[i] = i;
+  __syncthreads();
+  for (int j = 0; j < r; j++) {
+    // Pivot: the reference scans rows j+1.. and moves on a strictly greater |value| (a NaN never
+    // compares greater; a NaN in row j stays the pivot): the first row attaining the maximum.
+    double bv = -1.0;
+    int br = 0x7fffffff;
+    for (int i = j + 1 + tid; i < m; i += blockDim.x) {
+      const double v = fabs((double)lu[(size_t)i * n + j]);
+      if (v > bv) { bv = v; br = i; }      // ascending i per thread: keeps the first of equals
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const double ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int orow = __shfl_xor_sync(0xffffffffu, br, o);
+      if (ov > bv || (ov == bv && orow < br)) { bv = ov; br = orow; }
+    }
+    if (lane == 0) { best_v[warp] = bv; best_r[warp] = br; }
+    __syncthreads();
+    if (warp == 0) {
+      bv = lane < nw ? best_v[lane] : -1.0;
+      br = lane < nw ? best_r[lane] : 0x7fffffff;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const double ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int orow = __shfl_xor_sync(0xffffffffu, br, o);
+        if (ov > bv || (ov == bv && orow < br)) { bv = ov; br = orow; }
+      }
+      if (lane == 0) {
+        const double own = fabs((double)lu[(size_t)j * n + j]);
+        const int row = (bv > own) ? br : j;   // own = NaN: every comparison is false, row j stays
+        pivot_row = row;
+        piv[j] = row;
+        if (row != j) { const int t = perm[j]; perm[j] = perm[row]; perm[row] = t; }
+      }
+    }
+    __syncthreads();
+    const int row = pivot_row;
+    if (row != j) {
+      for (int c = tid; c < n; c += blockDim.x) {
+        const T t = lu[(size_t)j * n + c];
+        lu[(size_t)j * n + c] = lu[(size_t)row * n + c];
+        lu[(size_t)row * n + c] = t;
+      }
+      __syncthreads();
+    }
+    const double diag = (double)lu[(size_t)j * n + j];
+    if (diag != 0.0) {
+      // trailing update with the unrounded factor, as the reference keeps it in a local
+      for (int i = j + 1 + warp; i < m; i += nw) {
+        const double f = (double)lu[(size_t)i * n + j] / diag;
+        T* row_i = lu + (size_t)i * n;
+        const T* row_j = lu + (size_t)j * n;
+        for (int c = j + 1 + lane; c < n; c += 32)
+          row_i[c] = (T)__dsub_rn((double)row_i[c], __dmul_rn(f, (double)row_j[c]));
+      }
+      __syncthreads();
+      for (int i = j + 1 + tid; i < m; i += blockDim.x)
+        lu[(size_t)i * n + j] = (T)((double)lu[(size_t)i * n + j] / diag);
+    }
+    __syncthreads();
+  }
+}
+
+template <class K>
+cudaError_t allow_smem(K kernel, size_t bytes) {
+  if (bytes <= 48 * 1024) return cudaSuccess;
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+}
+
+}  // namespace
+
+extern "C" {
+
+int jaxcuda_cholesky_launch(cudaStream_t stream, int dtype, const void* x, void* y, int64_t batch, int64_t n, int* launches) {
+  if (launches) *launches = 0;
+  if (batch <= 0 || n <= 0) return cudaSuccess;
+  const size_t smem = (size_t)(n + 1) * sizeof(double);
+  if (smem > 200 * 1024 || batch > 0x7fffffff) return cudaErrorInvalidValue;
+  const int threads = n >= 256 ? 1024 : n >= 64 ? 256 : 64;
+  cudaError_t e;
+  if (dtype == JAXCUDA_F32) {
+    if ((e = allow_smem(cholesky_kernel<float>, smem)) != cudaSuccess) return e;
+    cholesky_kernel<float><<<(unsigned)batch, threads, smem, stream>>>((const float*)x, (float*)y, (int)n);
+  } else {
+    if ((e = allow_smem(cholesky_kernel<double>, smem)) != cudaSuccess) return e;
+    cholesky_kernel<double><<<(unsigned)batch, threads, smem, stream>>>((const double*)x, (double*)y, (int)n);
+  }
+  if (launches) *launches = 1;
+  return cudaGetLastError();
+}
+
+int jaxcuda_triangular_solve_launch(cudaStream_t stream, int dtype, const void* a, const void* b, void* x, int64_t mats,
+                                    int64_t rows, int64_t n, int unit_diagonal, int* launches) {
+  if (launches) *launches = 0;
+  const int64_t total = mats * rows;
+  if (total <= 0 || n <= 0) return cudaSuccess;
+  int warps = 8;
+  while (warps > 1 && (size_t)warps * n * sizeof(double) > 160 * 1024) warps >>= 1;
+  const size_t smem = (size_t)warps * n * sizeof(double);
+  if (smem > 200 * 1024) return cudaErrorInvalidValue;
+  const int64_t blocks = (total + warps - 1) / warps;
+  if (blocks > 0x7fffffff) return cudaErrorInvalidValue;
+  cudaError_t e;
+  if (dtype == JAXCUDA_F32) {
+    if ((e = allow_smem(trisolve_kernel<float>, smem)) != cudaSuccess) return e;
+    trisolve_kernel<float><<<(unsigned)blocks, warps * 32, smem, stream>>>((const float*)a, (const float*)b, (float*)x, (int)n,
+                                                                           rows, total, unit_diagonal);
+  } else {
+    if ((e = allow_smem(trisolve_kernel<double>, smem)) != cudaSuccess) return e;
+    trisolve_kernel<double><<<(unsigned)blocks, warps * 32, smem, stream>>>((const double*)a, (const double*)b, (double*)x, (int)n,
+                                                                            rows, total, unit_diagonal);
+  }
+  if (launches) *launches = 1;
+  return cudaGetLastError();
+}
+
+int jaxcuda_lu_launch(cudaStream_t stream, int dtype, const void* a, void* lu, int32_t* pivots, int32_t* perm,
+                      int64_t batch, int64_t m, int64_t n, int* launches) {
+  if (launches) *launches = 0;
+  if (batch <= 0 || m <= 0 || n <= 0) return cudaSuccess;
+  if (batch > 0x7fffffff || m > 0x7fffffff || n > 0x7fffffff) return cudaErrorInvalidValue;
+  const int threads = m * n >= 65536 ? 1024 : m * n >= 4096 ? 256 : 64;
+  if (dtype == JAXCUDA_F32)
+    lu_kernel<float><<<(unsigned)batch, threads, 0, stream>>>((const float*)a, (float*)lu, pivots, perm, (int)m, (int)n);
+  else
+    lu_kernel<double><<<(unsigned)batch, threads, 0, stream>>>((const double*)a, (double*)lu, pivots, perm, (int)m, (int)n);
+  if (launches) *launches = 1;
+  return cudaGetLastError();
+}
+
+}  // extern "C"

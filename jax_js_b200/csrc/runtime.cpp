@@ -27,6 +27,7 @@
 #include "gemm_tc.hpp"
 #include "ir.hpp"
 #include "scatter.hpp"
+#include "linalg.hpp"
 
 extern "C" size_t jaxcuda_sort_work_bytes(int argsort, int64_t batch, int64_t n);
 extern "C" int jaxcuda_sort_launch(void* stream, int argsort, const void* x, void* y, int32_t* yi, int dtype,
@@ -170,6 +171,8 @@ struct jaxcuda_exe {
   // routine
   int rt_dtype = 0;
   int64_t rt_batch = 0, rt_n = 0;
+  int64_t rt_m = 0, rt_rows = 0;  // linalg routines: rows of a rectangular matrix; right-hand sides per matrix
+  int rt_flag = 0;                // TriangularSolve: unitDiagonal
   std::string describe;
   void* persistent_scratch = nullptr;  // zero-initialised once; reused by every dispatch (stream-ordered)
 };
@@ -640,11 +643,77 @@ static int prepare_scatter(jaxcuda_ctx* ctx, const jaxcuda_routine_type* type, c
   return JAXCUDA_OK;
 }
 
+// TriangularSolve / Cholesky / LU: shape rules and messages of src/routine.ts:298-381.
+static int prepare_linalg(jaxcuda_ctx* ctx, const char* name, const jaxcuda_routine_type* type, const char* params,
+                          jaxcuda_exe** out) {
+  const int kind = !strcmp(name, "TriangularSolve") ? 4 : !strcmp(name, "Cholesky") ? 5 : 6;
+  const int want_in = kind == 4 ? 2 : 1, want_out = kind == 6 ? 3 : 1;
+  if (type->n_inputs != want_in || type->n_outputs != want_out)
+    return fail(ctx, JAXCUDA_EINVAL, "%s: wrong number of inputs or outputs", name);
+  const int dt = type->input_dtypes[0];
+  if (dt != JAXCUDA_F32 && dt != JAXCUDA_F64)
+    return fail(ctx, JAXCUDA_EUNSUPPORTED, "%s<%s> not supported in cuda backend", name, dtype_name(dt));
+  const int ra = type->input_ranks[0];
+  const int64_t* as = type->input_shapes;
+  std::unique_ptr<jaxcuda_exe> exe(new jaxcuda_exe);
+  exe->ctx = ctx;
+  exe->kind = kind;
+  exe->rt_dtype = dt;
+  if (ra < 2)
+    return fail(ctx, JAXCUDA_EINVAL, "%s: %s must be at least 2D", kind == 4 ? "triangular_solve" : kind == 5 ? "cholesky" : "lu",
+                kind == 4 ? "a" : "input");
+  int64_t lead = 1;
+  for (int i = 0; i < ra - 2; i++) lead *= as[i];
+  const int64_t r0 = as[ra - 2], r1 = as[ra - 1];
+  if (kind == 4) {
+    const int rb = type->input_ranks[1];
+    const int64_t* bs = type->input_shapes + ra;
+    if (rb < 2) return fail(ctx, JAXCUDA_EINVAL, "triangular_solve: b must be at least 2D");
+    if (r0 != r1 || r0 != bs[rb - 1]) return fail(ctx, JAXCUDA_EINVAL, "triangular_solve: incompatible shapes");
+    if (type->input_dtypes[1] != dt) return fail(ctx, JAXCUDA_EINVAL, "triangular_solve: a and b differ in dtype");
+    int64_t blead = 1;
+    for (int i = 0; i < rb - 2; i++) blead *= bs[i];
+    if (blead != lead) return fail(ctx, JAXCUDA_EINVAL, "triangular_solve: batch dimensions of a and b differ");
+    exe->rt_batch = lead;
+    exe->rt_n = r0;
+    exe->rt_rows = bs[rb - 2];
+    const char* u = params ? json_value(params, "unitDiagonal") : nullptr;
+    exe->rt_flag = u && !strncmp(u, "true", 4);
+  } else if (kind == 5) {
+    if (r0 != r1) return fail(ctx, JAXCUDA_EINVAL, "cholesky: input must be square, got [%lld, %lld]", (long long)r0, (long long)r1);
+    exe->rt_batch = lead;
+    exe->rt_n = r0;
+  } else {
+    exe->rt_batch = lead;
+    exe->rt_m = r0;
+    exe->rt_n = r1;
+  }
+  if (exe->rt_n >= (1ll << 31) || exe->rt_m >= (1ll << 31)) return fail(ctx, JAXCUDA_EINVAL, "%s: matrix too large", name);
+  exe->describe = std::string(name) + " batch=" + std::to_string(exe->rt_batch) +
+                  (kind == 6 ? " m=" + std::to_string(exe->rt_m) : std::string()) + " n=" + std::to_string(exe->rt_n) +
+                  (kind == 4 ? " rows=" + std::to_string(exe->rt_rows) + (exe->rt_flag ? " unit" : "") : std::string());
+  exe->plan.describe = exe->describe;
+  const double e = dtype_bytes(dt), n = (double)exe->rt_n, b = (double)exe->rt_batch;
+  if (kind == 4) { exe->plan.algo_bytes = b * (n * n + 2.0 * exe->rt_rows * n) * e; exe->plan.algo_flops = b * exe->rt_rows * n * n; }
+  if (kind == 5) { exe->plan.algo_bytes = 2.0 * b * n * n * e; exe->plan.algo_flops = b * n * n * n / 3.0; }
+  if (kind == 6) {
+    const double m = (double)exe->rt_m, r = std::min(m, n);
+    exe->plan.algo_bytes = 2.0 * b * m * n * e + 4.0 * b * (r + m);
+    exe->plan.algo_flops = b * (2.0 * m * n * r - (m + n) * r * r + 2.0 * r * r * r / 3.0);
+  }
+  exe->handles = 1;
+  *out = exe.get();
+  ctx->routines.push_back(std::move(exe));
+  return JAXCUDA_OK;
+}
+
 int jaxcuda_prepare_routine(jaxcuda_ctx* ctx, const char* name, const jaxcuda_routine_type* type,
                             const char* params_json, jaxcuda_exe** out) {
   if (!ctx || !out || !name || !type) return JAXCUDA_EINVAL;
   *out = nullptr;
   if (!strcmp(name, "Scatter")) return prepare_scatter(ctx, type, params_json, out);
+  if (!strcmp(name, "TriangularSolve") || !strcmp(name, "Cholesky") || !strcmp(name, "LU"))
+    return prepare_linalg(ctx, name, type, params_json, out);
   const bool is_sort = !strcmp(name, "Sort"), is_argsort = !strcmp(name, "Argsort");
   if (!is_sort && !is_argsort)  // wording of UnsupportedRoutineError, src/backend.ts:236-240
     return fail(ctx, JAXCUDA_EUNSUPPORTED, "routine '%s' is not supported in cuda backend", name);
@@ -698,6 +767,33 @@ int jaxcuda_dispatch(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const jaxcuda_slot* inp
     ctx->launches += launches;
     if (work) ctx->alloc.put(work, wb);
     if (rc) return fail(ctx, JAXCUDA_ECUDA, "scatter launch: %s", cudaGetErrorString((cudaError_t)rc));
+    return JAXCUDA_OK;
+  }
+  if (exe->kind >= 4) {  // TriangularSolve / Cholesky / LU
+    const size_t e = dtype_bytes(exe->rt_dtype);
+    const size_t b = (size_t)exe->rt_batch, n = (size_t)exe->rt_n, m = (size_t)exe->rt_m, rows = (size_t)exe->rt_rows;
+    int launches = 0, rc = 0;
+    if (exe->kind == 4) {
+      if (n_inputs != 2 || n_outputs != 1) return fail(ctx, JAXCUDA_EINVAL, "TriangularSolve called with wrong slot counts");
+      if (in[0]->bytes < b * n * n * e || in[1]->bytes < b * rows * n * e || outv[0]->bytes < b * rows * n * e)
+        return fail(ctx, JAXCUDA_EINVAL, "routine buffers are smaller than its declared shapes");
+      rc = jaxcuda_triangular_solve_launch(ctx->stream, exe->rt_dtype, in[0]->ptr, in[1]->ptr, outv[0]->ptr, exe->rt_batch,
+                                           exe->rt_rows, exe->rt_n, exe->rt_flag, &launches);
+    } else if (exe->kind == 5) {
+      if (n_inputs != 1 || n_outputs != 1) return fail(ctx, JAXCUDA_EINVAL, "Cholesky called with wrong slot counts");
+      if (in[0]->bytes < b * n * n * e || outv[0]->bytes < b * n * n * e)
+        return fail(ctx, JAXCUDA_EINVAL, "routine buffers are smaller than its declared shapes");
+      rc = jaxcuda_cholesky_launch(ctx->stream, exe->rt_dtype, in[0]->ptr, outv[0]->ptr, exe->rt_batch, exe->rt_n, &launches);
+    } else {
+      if (n_inputs != 1 || n_outputs != 3) return fail(ctx, JAXCUDA_EINVAL, "LU called with wrong slot counts");
+      const size_t r = std::min(m, n);
+      if (in[0]->bytes < b * m * n * e || outv[0]->bytes < b * m * n * e || outv[1]->bytes < b * r * 4 || outv[2]->bytes < b * m * 4)
+        return fail(ctx, JAXCUDA_EINVAL, "routine buffers are smaller than its declared shapes");
+      rc = jaxcuda_lu_launch(ctx->stream, exe->rt_dtype, in[0]->ptr, outv[0]->ptr, (int32_t*)outv[1]->ptr, (int32_t*)outv[2]->ptr,
+                             exe->rt_batch, exe->rt_m, exe->rt_n, &launches);
+    }
+    ctx->launches += launches;
+    if (rc) return fail(ctx, JAXCUDA_ECUDA, "%s launch: %s", exe->describe.c_str(), cudaGetErrorString((cudaError_t)rc));
     return JAXCUDA_OK;
   }
   if (exe->kind != 0) {  // Sort / Argsort

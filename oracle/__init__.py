@@ -123,6 +123,51 @@ def scatter(updates: np.ndarray, indices, params: dict, dtype_code: int) -> np.n
     return out
 
 
+def _float_code(x: np.ndarray) -> int:
+    from jax_js_b200.alu import DType
+    return int({np.dtype(np.float32): DType.Float32, np.dtype(np.float64): DType.Float64}[x.dtype])
+
+
+def triangular_solve(a: np.ndarray, b: np.ndarray, unit_diagonal: bool = False) -> np.ndarray:
+    """`runTriangularSolve` (src/routine.ts:298-338): a [..., n, n] upper triangular, b [..., rows, n]."""
+    a, b = np.ascontiguousarray(a), np.ascontiguousarray(b)
+    n, rows = a.shape[-1], b.shape[-2]
+    x = np.empty_like(b)
+    L = lib()
+    L.oracle_triangular_solve.argtypes = [ctypes.c_int] + [ctypes.c_void_p] * 3 + [ctypes.c_int64] * 3 + [ctypes.c_int]
+    if a.size and L.oracle_triangular_solve(_float_code(a), a.ctypes.data, b.ctypes.data, x.ctypes.data,
+                                            a.size // (n * n), rows, n, int(unit_diagonal)):
+        raise RuntimeError("oracle_triangular_solve: unsupported dtype")
+    return x
+
+
+def cholesky(x: np.ndarray) -> np.ndarray:
+    """`runCholesky` (src/routine.ts:340-366)."""
+    x = np.ascontiguousarray(x)
+    n = x.shape[-1]
+    y = np.empty_like(x)
+    L = lib()
+    L.oracle_cholesky.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64]
+    if x.size and L.oracle_cholesky(_float_code(x), x.ctypes.data, y.ctypes.data, x.size // (n * n), n):
+        raise RuntimeError("oracle_cholesky: unsupported dtype")
+    return y
+
+
+def lu(a: np.ndarray):
+    """`runLU` (src/routine.ts:368-432): returns (lu, pivots int32 [..., min(m, n)], permutation int32 [..., m])."""
+    a = np.ascontiguousarray(a)
+    m, n = a.shape[-2:]
+    batch = a.size // (m * n) if m * n else 0
+    out = np.empty_like(a)
+    piv = np.zeros(a.shape[:-2] + (min(m, n),), np.int32)
+    perm = np.zeros(a.shape[:-2] + (m,), np.int32)
+    L = lib()
+    L.oracle_lu.argtypes = [ctypes.c_int] + [ctypes.c_void_p] * 4 + [ctypes.c_int64] * 3
+    if a.size and L.oracle_lu(_float_code(a), a.ctypes.data, out.ctypes.data, piv.ctypes.data, perm.ctypes.data, batch, m, n):
+        raise RuntimeError("oracle_lu: unsupported dtype")
+    return out, piv, perm
+
+
 def wasm_unary(op: int, x: float) -> float:
     return float(lib().oracle_wasm_unary(int(op), float(x)))
 

@@ -781,3 +781,101 @@ uint16_t oracle_double_to_half(double x) { return double_to_half(x); }
 double oracle_half_to_double(uint16_t h) { return half_to_double(h); }
 
 }  // extern "C"
+
+// ---- dense linear-algebra routines (src/routine.ts:298-432) --------------------------------------
+// The reference runs on typed arrays with JavaScript numbers: every intermediate is a double, a
+// value is rounded to the element type when it is stored and read back rounded.  T is float or
+// double; `volatile`-free plain code with -ffp-contract=off keeps multiply and subtract separate.
+namespace {
+
+template <class T>
+void triangular_solve_ref(const T* a, const T* b, T* x, int64_t mats, int64_t rows, int64_t n, bool unit) {  // :298-338
+  for (int64_t c = 0; c < mats; c++) {
+    const T* a1 = a + c * n * n;
+    for (int64_t t = 0; t < rows; t++) {
+      const T* b1 = b + (c * rows + t) * n;
+      T* x1 = x + (c * rows + t) * n;
+      for (int64_t i = n - 1; i >= 0; i--) {
+        double sum = b1[i];
+        for (int64_t j = i + 1; j < n; j++) sum -= (double)a1[i * n + j] * (double)x1[j];
+        x1[i] = (T)(unit ? sum : sum / (double)a1[i * n + i]);
+      }
+    }
+  }
+}
+
+template <class T>
+void cholesky_ref(const T* x, T* y, int64_t batch, int64_t n) {  // :340-366
+  for (int64_t i = 0; i < batch * n * n; i++) y[i] = 0;
+  for (int64_t m = 0; m < batch; m++) {
+    const T* ar = x + m * n * n;
+    T* out = y + m * n * n;
+    for (int64_t i = 0; i < n; i++)
+      for (int64_t j = 0; j <= i; j++) {
+        double sum = ar[i * n + j];
+        for (int64_t k = 0; k < j; k++) sum -= (double)out[i * n + k] * (double)out[j * n + k];
+        out[i * n + j] = (T)(i == j ? std::sqrt(sum) : sum / (double)out[j * n + j]);
+      }
+  }
+}
+
+template <class T>
+void lu_ref(const T* a, T* lu, int32_t* pivots, int32_t* perm, int64_t batch, int64_t m, int64_t n) {  // :368-432
+  const int64_t r = std::min(m, n);
+  for (int64_t bi = 0; bi < batch; bi++) {
+    const T* ar = a + bi * m * n;
+    T* out = lu + bi * m * n;
+    int32_t* piv = pivots + bi * r;
+    int32_t* p = perm + bi * m;
+    for (int64_t i = 0; i < m * n; i++) out[i] = ar[i];
+    for (int64_t i = 0; i < m; i++) p[i] = (int32_t)i;
+    for (int64_t j = 0; j < r; j++) {
+      double maxVal = std::fabs((double)out[j * n + j]);
+      int64_t maxRow = j;
+      for (int64_t i = j + 1; i < m; i++) {
+        const double val = std::fabs((double)out[i * n + j]);
+        if (val > maxVal) { maxVal = val; maxRow = i; }
+      }
+      piv[j] = (int32_t)maxRow;
+      if (maxRow != j) {
+        for (int64_t col = 0; col < n; col++) std::swap(out[j * n + col], out[maxRow * n + col]);
+        std::swap(p[j], p[maxRow]);
+      }
+      const double diag = out[j * n + j];
+      if (diag != 0) {
+        for (int64_t i = j + 1; i < m; i++) {
+          const double factor = (double)out[i * n + j] / diag;
+          out[i * n + j] = (T)factor;
+          for (int64_t col = j + 1; col < n; col++)
+            out[i * n + col] = (T)((double)out[i * n + col] - factor * (double)out[j * n + col]);
+        }
+      }
+    }
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+// dtype: JAXCUDA_F32 or JAXCUDA_F64; returns 0, or 1 for another dtype.
+int oracle_triangular_solve(int dtype, const void* a, const void* b, void* x, int64_t mats, int64_t rows, int64_t n, int unit) {
+  if (dtype == JAXCUDA_F32) triangular_solve_ref((const float*)a, (const float*)b, (float*)x, mats, rows, n, unit != 0);
+  else if (dtype == JAXCUDA_F64) triangular_solve_ref((const double*)a, (const double*)b, (double*)x, mats, rows, n, unit != 0);
+  else return 1;
+  return 0;
+}
+int oracle_cholesky(int dtype, const void* x, void* y, int64_t batch, int64_t n) {
+  if (dtype == JAXCUDA_F32) cholesky_ref((const float*)x, (float*)y, batch, n);
+  else if (dtype == JAXCUDA_F64) cholesky_ref((const double*)x, (double*)y, batch, n);
+  else return 1;
+  return 0;
+}
+int oracle_lu(int dtype, const void* a, void* lu, int32_t* pivots, int32_t* perm, int64_t batch, int64_t m, int64_t n) {
+  if (dtype == JAXCUDA_F32) lu_ref((const float*)a, (float*)lu, pivots, perm, batch, m, n);
+  else if (dtype == JAXCUDA_F64) lu_ref((const double*)a, (double*)lu, pivots, perm, batch, m, n);
+  else return 1;
+  return 0;
+}
+
+}  // extern "C"
