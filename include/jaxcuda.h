@@ -91,10 +91,11 @@ typedef struct {
 } jaxcuda_routine_type;
 
 /* Backend.prepareRoutine[Sync] (src/backend.ts:198-202).  name is a `Routines` member
- * (src/routine.ts:32-102): "Sort", "Argsort", "Scatter", "TriangularSolve", "Cholesky" and "LU" are
- * implemented; "JacobiEigh" and "Fft" return JAXCUDA_EUNSUPPORTED (UnsupportedRoutineError).
- * params_json is the routine's `params` object as JSON (Scatter: `ScatterParams`,
- * src/routine.ts:104-110; TriangularSolve: {"unitDiagonal": bool}).  Shapes the reference rejects
+ * (src/routine.ts:32-102): every member is implemented ("Sort", "Argsort", "Scatter", "TriangularSolve",
+ * "Cholesky", "LU", "JacobiEigh", "Fft"); any other name returns JAXCUDA_EUNSUPPORTED
+ * (UnsupportedRoutineError).  params_json is the routine's `params` object as JSON (Scatter:
+ * `ScatterParams`, src/routine.ts:104-110; TriangularSolve: {"unitDiagonal": bool}; JacobiEigh:
+ * {"maxSweeps": int, "tolerance": number}; Fft: {"factors": [int...], "inverse": bool}).  Shapes the reference rejects
  * (src/routine.ts:305-313, :341-346) return JAXCUDA_EINVAL with its message. */
 int jaxcuda_prepare_routine(jaxcuda_ctx* ctx, const char* name, const jaxcuda_routine_type* type,
                             const char* params_json, jaxcuda_exe** out);

@@ -18,7 +18,7 @@ CSRC = HERE / "csrc"
 LIB = HERE / "libjaxcuda.so"
 CUDA_HOME = Path("/usr/local/cuda")
 
-SOURCES = ["runtime.cpp", "ir.cpp", "emit.cpp", "gemm_tc.cpp", "sort.cu", "scatter.cu", "linalg.cu"]
+SOURCES = ["runtime.cpp", "ir.cpp", "emit.cpp", "gemm_tc.cpp", "sort.cu", "scatter.cu", "linalg.cu", "fft.cu"]
 
 
 def _stale() -> bool:

@@ -166,6 +166,98 @@ __global__ void __launch_bounds__(1024) lu_kernel(const T* __restrict__ a, T* __
   }
 }
 
+// ---- cyclic Jacobi eigendecomposition, one CTA per matrix (src/routine.ts:434-541) -------------------
+// The rotations run in the reference's order (p ascending, q ascending inside), one after the
+// other; the n-element row/column updates of one rotation are spread over the CTA.  Every formula
+// is evaluated with the reference's grouping in unfused double arithmetic, so convergence tests and
+// results follow the reference step by step.  `a` keeps only its lower triangle (symIndex).
+__device__ __forceinline__ double jmul(double a, double b) { return __dmul_rn(a, b); }
+
+template <class T>
+__device__ __forceinline__ double block_max(double v, double* red) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmax(v, __shfl_xor_sync(0xffffffffu, v, o));
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  v = red[0];
+  for (int w = 1; w < nw; w++) v = fmax(v, red[w]);
+  return v;
+}
+
+template <class T>
+__global__ void __launch_bounds__(1024) jacobi_kernel(const T* __restrict__ in, T* __restrict__ a_all, T* __restrict__ v_all,
+                                                      int n, int max_sweeps, double tolerance, int in_smem) {
+  extern __shared__ __align__(16) unsigned char jac_smem[];
+  __shared__ double red[32];
+  const size_t nn = (size_t)n * n;
+  const T* x = in + blockIdx.x * nn;
+  T* ag = a_all + blockIdx.x * nn;
+  T* vg = v_all + blockIdx.x * nn;
+  T* a = in_smem ? reinterpret_cast<T*>(jac_smem) : ag;
+  T* v = in_smem ? reinterpret_cast<T*>(jac_smem) + nn : vg;
+  for (size_t idx = threadIdx.x; idx < nn; idx += blockDim.x) {
+    const int i = (int)(idx / n), j = (int)(idx - (size_t)i * n);
+    a[idx] = j <= i ? x[idx] : (T)0;
+    v[idx] = i == j ? (T)1 : (T)0;
+  }
+  __syncthreads();
+  auto off_diagonal_max = [&](bool with_diagonal, double start) {
+    double m = start;
+    for (size_t idx = threadIdx.x; idx < nn; idx += blockDim.x) {
+      const int i = (int)(idx / n), j = (int)(idx - (size_t)i * n);
+      if (j < i || (with_diagonal && j == i)) {
+        const double val = fabs((double)a[idx]);
+        if (val > m) m = val;                 // Math.max would propagate a NaN; a NaN input is outside the contract
+      }
+    }
+    return block_max<T>(m, red);
+  };
+  const double threshold = jmul(tolerance, off_diagonal_max(true, 1.0));
+  double off = off_diagonal_max(false, 0.0);
+  for (int sweep = 0; sweep < max_sweeps && off > threshold; sweep++) {
+    for (int p = 0; p < n - 1; p++) {
+      for (int q = p + 1; q < n; q++) {
+        const size_t pp = (size_t)p * n + p, qq = (size_t)q * n + q, pq = (size_t)q * n + p;  // q > p: symIndex(p, q)
+        const double app = (double)a[pp], aqq = (double)a[qq], apq = (double)a[pq];
+        __syncthreads();                      // everyone has read the three before anyone writes them
+        if (apq == 0.0) continue;
+        const double tau = __ddiv_rn(__dsub_rn(aqq, app), jmul(2.0, apq));
+        const double sign = tau >= 0.0 ? 1.0 : -1.0;
+        const double t = __ddiv_rn(sign, __dadd_rn(fabs(tau), __dsqrt_rn(__dadd_rn(jmul(tau, tau), 1.0))));
+        const double c = __ddiv_rn(1.0, __dsqrt_rn(__dadd_rn(jmul(t, t), 1.0)));
+        const double s = jmul(t, c);
+        for (int k = threadIdx.x; k < n; k += blockDim.x) {
+          if (k != p && k != q) {
+            const size_t kp = k >= p ? (size_t)k * n + p : (size_t)p * n + k;
+            const size_t kq = k >= q ? (size_t)k * n + q : (size_t)q * n + k;
+            const double akp = (double)a[kp], akq = (double)a[kq];
+            a[kp] = (T)__dsub_rn(jmul(c, akp), jmul(s, akq));
+            a[kq] = (T)__dadd_rn(jmul(s, akp), jmul(c, akq));
+          }
+          const size_t vp = (size_t)k * n + p, vq = (size_t)k * n + q;
+          const double vkp = (double)v[vp], vkq = (double)v[vq];
+          v[vp] = (T)__dsub_rn(jmul(c, vkp), jmul(s, vkq));
+          v[vq] = (T)__dadd_rn(jmul(s, vkp), jmul(c, vkq));
+        }
+        if (threadIdx.x == 0) {
+          const double sc2 = jmul(jmul(jmul(2.0, s), c), apq);
+          a[pp] = (T)__dadd_rn(__dsub_rn(jmul(jmul(c, c), app), sc2), jmul(jmul(s, s), aqq));
+          a[qq] = (T)__dadd_rn(__dadd_rn(jmul(jmul(s, s), app), sc2), jmul(jmul(c, c), aqq));
+          a[pq] = (T)0;
+        }
+        __syncthreads();
+      }
+    }
+    off = off_diagonal_max(false, 0.0);
+  }
+  if (in_smem) {
+    __syncthreads();
+    for (size_t idx = threadIdx.x; idx < nn; idx += blockDim.x) { ag[idx] = a[idx]; vg[idx] = v[idx]; }
+  }
+}
+
 template <class K>
 cudaError_t allow_smem(K kernel, size_t bytes) {
   if (bytes <= 48 * 1024) return cudaSuccess;
@@ -229,6 +321,31 @@ int jaxcuda_lu_launch(cudaStream_t stream, int dtype, const void* a, void* lu, i
     lu_kernel<float><<<(unsigned)batch, threads, 0, stream>>>((const float*)a, (float*)lu, pivots, perm, (int)m, (int)n);
   else
     lu_kernel<double><<<(unsigned)batch, threads, 0, stream>>>((const double*)a, (double*)lu, pivots, perm, (int)m, (int)n);
+  if (launches) *launches = 1;
+  return cudaGetLastError();
+}
+
+int jaxcuda_jacobi_eigh_launch(cudaStream_t stream, int dtype, const void* x, void* diagonalized, void* vectors,
+                               int64_t batch, int64_t n, int max_sweeps, double tolerance, int* launches) {
+  if (launches) *launches = 0;
+  if (batch <= 0 || n <= 0) return cudaSuccess;
+  if (batch > 0x7fffffff || n > 32768) return cudaErrorInvalidValue;
+  const size_t e = dtype == JAXCUDA_F32 ? 4 : 8;
+  const size_t want = 2 * (size_t)n * n * e;
+  const int in_smem = want <= 200 * 1024;
+  const size_t smem = in_smem ? want : 0;
+  int threads = 32;
+  while (threads < n && threads < 1024) threads <<= 1;
+  cudaError_t err;
+  if (dtype == JAXCUDA_F32) {
+    if ((err = allow_smem(jacobi_kernel<float>, smem)) != cudaSuccess) return err;
+    jacobi_kernel<float><<<(unsigned)batch, threads, smem, stream>>>((const float*)x, (float*)diagonalized, (float*)vectors,
+                                                                     (int)n, max_sweeps, tolerance, in_smem);
+  } else {
+    if ((err = allow_smem(jacobi_kernel<double>, smem)) != cudaSuccess) return err;
+    jacobi_kernel<double><<<(unsigned)batch, threads, smem, stream>>>((const double*)x, (double*)diagonalized, (double*)vectors,
+                                                                      (int)n, max_sweeps, tolerance, in_smem);
+  }
   if (launches) *launches = 1;
   return cudaGetLastError();
 }

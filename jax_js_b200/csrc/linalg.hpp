@@ -1,5 +1,5 @@
-// Dense linear-algebra routines of src/routine.ts: TriangularSolve (:298-338), Cholesky (:340-366)
-// and LU (:368-432).  Plain C entry points over device pointers; compiled by nvcc for sm_100a.
+// Dense linear-algebra routines of src/routine.ts: TriangularSolve (:298-338), Cholesky (:340-366),
+// LU (:368-432) and JacobiEigh (:434-541).  Plain C entry points over device pointers; compiled by nvcc for sm_100a.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -20,6 +20,11 @@ int jaxcuda_triangular_solve_launch(cudaStream_t stream, int dtype, const void* 
 // a, lu: [batch, m, n]; pivots: int32 [batch, min(m, n)]; perm: int32 [batch, m].  Partial pivoting.
 int jaxcuda_lu_launch(cudaStream_t stream, int dtype, const void* a, void* lu, int32_t* pivots, int32_t* perm,
                       int64_t batch, int64_t m, int64_t n, int* launches);
+
+// x: [batch, n, n] symmetric (lower triangle read); diagonalized, vectors: [batch, n, n].  Cyclic Jacobi
+// sweeps until the largest off-diagonal magnitude is at most tolerance * max(1, max|x|) or max_sweeps.
+int jaxcuda_jacobi_eigh_launch(cudaStream_t stream, int dtype, const void* x, void* diagonalized, void* vectors,
+                               int64_t batch, int64_t n, int max_sweeps, double tolerance, int* launches);
 
 #ifdef __cplusplus
 }

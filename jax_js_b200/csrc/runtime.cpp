@@ -28,6 +28,7 @@
 #include "ir.hpp"
 #include "scatter.hpp"
 #include "linalg.hpp"
+#include "fft.hpp"
 
 extern "C" size_t jaxcuda_sort_work_bytes(int argsort, int64_t batch, int64_t n);
 extern "C" int jaxcuda_sort_launch(void* stream, int argsort, const void* x, void* y, int32_t* yi, int dtype,
@@ -172,7 +173,9 @@ struct jaxcuda_exe {
   int rt_dtype = 0;
   int64_t rt_batch = 0, rt_n = 0;
   int64_t rt_m = 0, rt_rows = 0;  // linalg routines: rows of a rectangular matrix; right-hand sides per matrix
-  int rt_flag = 0;                // TriangularSolve: unitDiagonal
+  int rt_flag = 0;                // TriangularSolve: unitDiagonal; JacobiEigh: maxSweeps; Fft: inverse
+  double rt_tolerance = 0.0;      // JacobiEigh
+  std::vector<int> rt_factors;    // Fft
   std::string describe;
   void* persistent_scratch = nullptr;  // zero-initialised once; reused by every dispatch (stream-ordered)
 };
@@ -646,8 +649,9 @@ static int prepare_scatter(jaxcuda_ctx* ctx, const jaxcuda_routine_type* type, c
 // TriangularSolve / Cholesky / LU: shape rules and messages of src/routine.ts:298-381.
 static int prepare_linalg(jaxcuda_ctx* ctx, const char* name, const jaxcuda_routine_type* type, const char* params,
                           jaxcuda_exe** out) {
-  const int kind = !strcmp(name, "TriangularSolve") ? 4 : !strcmp(name, "Cholesky") ? 5 : 6;
-  const int want_in = kind == 4 ? 2 : 1, want_out = kind == 6 ? 3 : 1;
+  const int kind = !strcmp(name, "TriangularSolve") ? 4 : !strcmp(name, "Cholesky") ? 5 : !strcmp(name, "LU") ? 6 :
+                   !strcmp(name, "JacobiEigh") ? 7 : 8;
+  const int want_in = (kind == 4 || kind == 8) ? 2 : 1, want_out = kind == 6 ? 3 : (kind == 7 || kind == 8) ? 2 : 1;
   if (type->n_inputs != want_in || type->n_outputs != want_out)
     return fail(ctx, JAXCUDA_EINVAL, "%s: wrong number of inputs or outputs", name);
   const int dt = type->input_dtypes[0];
@@ -659,9 +663,32 @@ static int prepare_linalg(jaxcuda_ctx* ctx, const char* name, const jaxcuda_rout
   exe->ctx = ctx;
   exe->kind = kind;
   exe->rt_dtype = dt;
+  if (kind == 8) {  // src/routine.ts:549-560
+    if (ra < 1) return fail(ctx, JAXCUDA_EINVAL, "fft: input must be at least 1D");
+    if (type->input_dtypes[1] != dt) return fail(ctx, JAXCUDA_EINVAL, "fft: expected matching floating-point real/imag arrays");
+    const int64_t n = as[ra - 1];
+    if (n < 1) return fail(ctx, JAXCUDA_EINVAL, "fft: final axis must be non-empty, got %lld", (long long)n);
+    exe->rt_n = n;
+    exe->rt_batch = 1;
+    for (int i = 0; i < ra - 1; i++) exe->rt_batch *= as[i];
+    std::vector<long long> f;
+    if (!params || !json_ints(params, "factors", f)) return fail(ctx, JAXCUDA_EINVAL, "fft: params need factors");
+    long long prod = 1;
+    for (long long v : f) { if (v < 1) return fail(ctx, JAXCUDA_EINVAL, "fft: bad factor"); prod *= v; exe->rt_factors.push_back((int)v); }
+    if (prod != n || f.size() > 32) return fail(ctx, JAXCUDA_EINVAL, "fft: factors do not multiply to the axis length %lld", (long long)n);
+    const char* inv = json_value(params, "inverse");
+    exe->rt_flag = inv && !strncmp(inv, "true", 4);
+    exe->describe = "Fft batch=" + std::to_string(exe->rt_batch) + " n=" + std::to_string(n) + (exe->rt_flag ? " inverse" : "");
+    exe->plan.describe = exe->describe;
+    exe->plan.algo_bytes = 4.0 * exe->rt_batch * n * dtype_bytes(dt);
+    exe->handles = 1;
+    *out = exe.get();
+    ctx->routines.push_back(std::move(exe));
+    return JAXCUDA_OK;
+  }
   if (ra < 2)
-    return fail(ctx, JAXCUDA_EINVAL, "%s: %s must be at least 2D", kind == 4 ? "triangular_solve" : kind == 5 ? "cholesky" : "lu",
-                kind == 4 ? "a" : "input");
+    return fail(ctx, JAXCUDA_EINVAL, "%s: %s must be at least 2D",
+                kind == 4 ? "triangular_solve" : kind == 5 ? "cholesky" : kind == 6 ? "lu" : "jacobi_eigh", kind == 4 ? "a" : "input");
   int64_t lead = 1;
   for (int i = 0; i < ra - 2; i++) lead *= as[i];
   const int64_t r0 = as[ra - 2], r1 = as[ra - 1];
@@ -683,6 +710,15 @@ static int prepare_linalg(jaxcuda_ctx* ctx, const char* name, const jaxcuda_rout
     if (r0 != r1) return fail(ctx, JAXCUDA_EINVAL, "cholesky: input must be square, got [%lld, %lld]", (long long)r0, (long long)r1);
     exe->rt_batch = lead;
     exe->rt_n = r0;
+  } else if (kind == 7) {  // src/routine.ts:440-447
+    if (r0 != r1) return fail(ctx, JAXCUDA_EINVAL, "jacobi_eigh: input must be square");
+    exe->rt_batch = lead;
+    exe->rt_n = r0;
+    const char* ms = params ? json_value(params, "maxSweeps") : nullptr;
+    const char* tol = params ? json_value(params, "tolerance") : nullptr;
+    if (!ms || !tol) return fail(ctx, JAXCUDA_EINVAL, "jacobi_eigh: params need maxSweeps and tolerance");
+    exe->rt_flag = atoi(ms);
+    exe->rt_tolerance = strtod(tol, nullptr);
   } else {
     exe->rt_batch = lead;
     exe->rt_m = r0;
@@ -696,6 +732,7 @@ static int prepare_linalg(jaxcuda_ctx* ctx, const char* name, const jaxcuda_rout
   const double e = dtype_bytes(dt), n = (double)exe->rt_n, b = (double)exe->rt_batch;
   if (kind == 4) { exe->plan.algo_bytes = b * (n * n + 2.0 * exe->rt_rows * n) * e; exe->plan.algo_flops = b * exe->rt_rows * n * n; }
   if (kind == 5) { exe->plan.algo_bytes = 2.0 * b * n * n * e; exe->plan.algo_flops = b * n * n * n / 3.0; }
+  if (kind == 7) exe->plan.algo_bytes = 3.0 * b * n * n * e;
   if (kind == 6) {
     const double m = (double)exe->rt_m, r = std::min(m, n);
     exe->plan.algo_bytes = 2.0 * b * m * n * e + 4.0 * b * (r + m);
@@ -712,7 +749,8 @@ int jaxcuda_prepare_routine(jaxcuda_ctx* ctx, const char* name, const jaxcuda_ro
   if (!ctx || !out || !name || !type) return JAXCUDA_EINVAL;
   *out = nullptr;
   if (!strcmp(name, "Scatter")) return prepare_scatter(ctx, type, params_json, out);
-  if (!strcmp(name, "TriangularSolve") || !strcmp(name, "Cholesky") || !strcmp(name, "LU"))
+  if (!strcmp(name, "TriangularSolve") || !strcmp(name, "Cholesky") || !strcmp(name, "LU") || !strcmp(name, "JacobiEigh") ||
+      !strcmp(name, "Fft"))
     return prepare_linalg(ctx, name, type, params_json, out);
   const bool is_sort = !strcmp(name, "Sort"), is_argsort = !strcmp(name, "Argsort");
   if (!is_sort && !is_argsort)  // wording of UnsupportedRoutineError, src/backend.ts:236-240
@@ -779,6 +817,19 @@ int jaxcuda_dispatch(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const jaxcuda_slot* inp
         return fail(ctx, JAXCUDA_EINVAL, "routine buffers are smaller than its declared shapes");
       rc = jaxcuda_triangular_solve_launch(ctx->stream, exe->rt_dtype, in[0]->ptr, in[1]->ptr, outv[0]->ptr, exe->rt_batch,
                                            exe->rt_rows, exe->rt_n, exe->rt_flag, &launches);
+    } else if (exe->kind == 7) {
+      if (n_inputs != 1 || n_outputs != 2) return fail(ctx, JAXCUDA_EINVAL, "JacobiEigh called with wrong slot counts");
+      if (in[0]->bytes < b * n * n * e || outv[0]->bytes < b * n * n * e || outv[1]->bytes < b * n * n * e)
+        return fail(ctx, JAXCUDA_EINVAL, "routine buffers are smaller than its declared shapes");
+      rc = jaxcuda_jacobi_eigh_launch(ctx->stream, exe->rt_dtype, in[0]->ptr, outv[0]->ptr, outv[1]->ptr, exe->rt_batch, exe->rt_n,
+                                      exe->rt_flag, exe->rt_tolerance, &launches);
+    } else if (exe->kind == 8) {
+      if (n_inputs != 2 || n_outputs != 2) return fail(ctx, JAXCUDA_EINVAL, "Fft called with wrong slot counts");
+      for (int i = 0; i < 2; i++)
+        if (in[i]->bytes < b * n * e || outv[i]->bytes < b * n * e)
+          return fail(ctx, JAXCUDA_EINVAL, "routine buffers are smaller than its declared shapes");
+      rc = jaxcuda_fft_launch(ctx->stream, exe->rt_dtype, in[0]->ptr, in[1]->ptr, outv[0]->ptr, outv[1]->ptr, exe->rt_batch, exe->rt_n,
+                              exe->rt_factors.data(), (int)exe->rt_factors.size(), exe->rt_flag, &launches);
     } else if (exe->kind == 5) {
       if (n_inputs != 1 || n_outputs != 1) return fail(ctx, JAXCUDA_EINVAL, "Cholesky called with wrong slot counts");
       if (in[0]->bytes < b * n * n * e || outv[0]->bytes < b * n * n * e)

@@ -8,7 +8,7 @@ from .alu import DType
 
 
 class Routines:
-    """src/routine.ts:32-102.  The cuda backend implements all but JacobiEigh and Fft."""
+    """src/routine.ts:32-102.  The cuda backend implements every member."""
     Sort = "Sort"
     Argsort = "Argsort"
     Scatter = "Scatter"

@@ -168,6 +168,33 @@ def lu(a: np.ndarray):
     return out, piv, perm
 
 
+def jacobi_eigh(x: np.ndarray, max_sweeps: int, tolerance: float):
+    """`runJacobiEigh` (src/routine.ts:434-541): returns (diagonalized, vectors), both [..., n, n]."""
+    x = np.ascontiguousarray(x)
+    n = x.shape[-1]
+    a, v = np.empty_like(x), np.empty_like(x)
+    L = lib()
+    L.oracle_jacobi_eigh.argtypes = [ctypes.c_int] + [ctypes.c_void_p] * 3 + [ctypes.c_int64] * 2 + [ctypes.c_int, ctypes.c_double]
+    if x.size and L.oracle_jacobi_eigh(_float_code(x), x.ctypes.data, a.ctypes.data, v.ctypes.data, x.size // (n * n), n,
+                                       int(max_sweeps), float(tolerance)):
+        raise RuntimeError("oracle_jacobi_eigh: unsupported dtype")
+    return a, v
+
+
+def fft(real: np.ndarray, imag: np.ndarray, factors, inverse: bool = False):
+    """`runFft` (src/routine.ts:543-624) along the last axis; `factors` multiply to its length."""
+    real, imag = np.ascontiguousarray(real), np.ascontiguousarray(imag)
+    n = real.shape[-1]
+    out_r, out_i = np.empty_like(real), np.empty_like(imag)
+    f = (ctypes.c_int * max(1, len(factors)))(*factors)
+    L = lib()
+    L.oracle_fft.argtypes = [ctypes.c_int] + [ctypes.c_void_p] * 4 + [ctypes.c_int64] * 2 + [ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
+    if real.size and L.oracle_fft(_float_code(real), real.ctypes.data, imag.ctypes.data, out_r.ctypes.data, out_i.ctypes.data,
+                                  real.size // n, n, f, len(factors), int(inverse)):
+        raise RuntimeError("oracle_fft: unsupported dtype")
+    return out_r, out_i
+
+
 def wasm_unary(op: int, x: float) -> float:
     return float(lib().oracle_wasm_unary(int(op), float(x)))
 

@@ -879,3 +879,138 @@ int oracle_lu(int dtype, const void* a, void* lu, int32_t* pivots, int32_t* perm
 }
 
 }  // extern "C"
+
+// ---- JacobiEigh (src/routine.ts:434-541) and Fft (:543-624) ----------------------------------------
+namespace {
+
+template <class T>
+void jacobi_eigh_ref(const T* input, T* diagonalized, T* vectors, int64_t batch, int64_t n, int max_sweeps, double tolerance) {
+  auto sym = [n](int64_t i, int64_t j) { return i >= j ? i * n + j : j * n + i; };
+  for (int64_t m = 0; m < batch; m++) {
+    const T* x = input + m * n * n;
+    T* a = diagonalized + m * n * n;
+    T* v = vectors + m * n * n;
+    for (int64_t i = 0; i < n * n; i++) { a[i] = 0; v[i] = 0; }
+    for (int64_t i = 0; i < n; i++) {
+      for (int64_t j = 0; j <= i; j++) a[i * n + j] = x[i * n + j];
+      v[i * n + i] = 1;
+    }
+    double max_abs = 1;
+    for (int64_t i = 0; i < n; i++)
+      for (int64_t j = 0; j <= i; j++) max_abs = std::max(max_abs, std::fabs((double)a[i * n + j]));
+    auto off_diagonal = [&]() {
+      double mx = 0;
+      for (int64_t i = 0; i < n; i++)
+        for (int64_t j = 0; j < i; j++) mx = std::max(mx, std::fabs((double)a[i * n + j]));
+      return mx;
+    };
+    const double threshold = tolerance * max_abs;
+    double off = off_diagonal();
+    for (int sweep = 0; sweep < max_sweeps && off > threshold; sweep++) {
+      for (int64_t p = 0; p < n - 1; p++)
+        for (int64_t q = p + 1; q < n; q++) {
+          const int64_t pp = p * n + p, qq = q * n + q, pq = sym(p, q);
+          const double app = a[pp], aqq = a[qq], apq = a[pq];
+          if (apq == 0) continue;
+          const double tau = (aqq - app) / (2 * apq);
+          const double tau_sign = tau >= 0 ? 1 : -1;
+          const double t = tau_sign / (std::fabs(tau) + std::sqrt(tau * tau + 1));
+          const double c = 1 / std::sqrt(t * t + 1);
+          const double s = t * c;
+          for (int64_t k = 0; k < n; k++) {
+            if (k == p || k == q) continue;
+            const int64_t kp = sym(k, p), kq = sym(k, q);
+            const double akp = a[kp], akq = a[kq];
+            a[kp] = (T)(c * akp - s * akq);
+            a[kq] = (T)(s * akp + c * akq);
+          }
+          a[pp] = (T)(c * c * app - 2 * s * c * apq + s * s * aqq);
+          a[qq] = (T)(s * s * app + 2 * s * c * apq + c * c * aqq);
+          a[pq] = 0;
+          for (int64_t k = 0; k < n; k++) {
+            const double vkp = v[k * n + p], vkq = v[k * n + q];
+            v[k * n + p] = (T)(c * vkp - s * vkq);
+            v[k * n + q] = (T)(s * vkp + c * vkq);
+          }
+        }
+      off = off_diagonal();
+    }
+  }
+}
+
+template <class T>
+void fft_ref(const T* real, const T* imag, T* out_real, T* out_imag, int64_t batch, int64_t n, const int* factors, int nf,
+             bool inverse) {
+  const double angle_scale = (inverse ? 2 : -2) * 3.141592653589793;
+  std::vector<int64_t> permutation(n);
+  int max_factor = 1;
+  for (int f = 0; f < nf; f++) max_factor = std::max(max_factor, factors[f]);
+  for (int64_t index = 0; index < n; index++) {
+    int64_t remaining = index, stride = 1, reversed = 0;
+    for (int f = 0; f < nf; f++) {
+      const int64_t digit = remaining % factors[f];
+      remaining /= factors[f];
+      stride *= factors[f];
+      reversed += digit * (n / stride);
+    }
+    permutation[index] = reversed;
+  }
+  std::vector<double> sr(max_factor), si(max_factor);
+  for (int64_t row = 0; row < batch; row++) {
+    const int64_t offset = row * n;
+    for (int64_t index = 0; index < n; index++) {
+      out_real[offset + index] = real[offset + permutation[index]];
+      out_imag[offset + index] = imag[offset + permutation[index]];
+    }
+    int64_t prev = 1;
+    for (int stage = 0; stage < nf; stage++) {
+      const int64_t radix = factors[stage], span = prev * radix;
+      const double stage_scale = (inverse && stage == nf - 1) ? 1.0 / (double)n : 1.0;
+      for (int64_t group = 0; group < n; group += span)
+        for (int64_t j = 0; j < prev; j++) {
+          for (int64_t q = 0; q < radix; q++) {
+            const int64_t idx = offset + group + j + q * prev;
+            const double angle = (angle_scale * (double)q * (double)j) / (double)span;
+            const double c = std::cos(angle), s = std::sin(angle);
+            const double xr = out_real[idx], xi = out_imag[idx];
+            sr[q] = xr * c - xi * s;
+            si[q] = xr * s + xi * c;
+          }
+          for (int64_t p = 0; p < radix; p++) {
+            double sum_real = 0, sum_imag = 0;
+            for (int64_t q = 0; q < radix; q++) {
+              const double angle = (angle_scale * (double)q * (double)p) / (double)radix;
+              const double c = std::cos(angle), s = std::sin(angle);
+              sum_real += sr[q] * c - si[q] * s;
+              sum_imag += sr[q] * s + si[q] * c;
+            }
+            const int64_t idx = offset + group + j + p * prev;
+            out_real[idx] = (T)(sum_real * stage_scale);
+            out_imag[idx] = (T)(sum_imag * stage_scale);
+          }
+        }
+      prev = span;
+    }
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int oracle_jacobi_eigh(int dtype, const void* x, void* diagonalized, void* vectors, int64_t batch, int64_t n, int max_sweeps,
+                       double tolerance) {
+  if (dtype == JAXCUDA_F32) jacobi_eigh_ref((const float*)x, (float*)diagonalized, (float*)vectors, batch, n, max_sweeps, tolerance);
+  else if (dtype == JAXCUDA_F64) jacobi_eigh_ref((const double*)x, (double*)diagonalized, (double*)vectors, batch, n, max_sweeps, tolerance);
+  else return 1;
+  return 0;
+}
+int oracle_fft(int dtype, const void* real, const void* imag, void* out_real, void* out_imag, int64_t batch, int64_t n,
+               const int* factors, int n_factors, int inverse) {
+  if (dtype == JAXCUDA_F32) fft_ref((const float*)real, (const float*)imag, (float*)out_real, (float*)out_imag, batch, n, factors, n_factors, inverse != 0);
+  else if (dtype == JAXCUDA_F64) fft_ref((const double*)real, (const double*)imag, (double*)out_real, (double*)out_imag, batch, n, factors, n_factors, inverse != 0);
+  else return 1;
+  return 0;
+}
+
+}  // extern "C"

@@ -166,8 +166,8 @@ def test_malloc_edge_cases(backend):
 
 def test_unsupported_routine_raises(backend):
     # src/backend.ts:236-240
-    rt = Routine(Routines.JacobiEigh, RoutineType([[2, 2]], [F32], [[2, 2], [2, 2]], [F32, F32]))
-    with pytest.raises(UnsupportedRoutineError, match="routine 'JacobiEigh' is not supported in cuda backend"):
+    rt = Routine("Conv", RoutineType([[2, 2]], [F32], [[2, 2]], [F32]))   # not a member of Routines
+    with pytest.raises(UnsupportedRoutineError, match="routine 'Conv' is not supported in cuda backend"):
         backend.prepare_routine(rt)
 
 

@@ -164,6 +164,131 @@ def test_cuda_lu_singular_ties_and_float64(backend):
     _close(lu, wlu, 1e-13)
 
 
+# ---- JacobiEigh and Fft ----------------------------------------------------------------------------
+
+def _sym(rng, batch, n, dtype=np.float32):
+    a = rng.standard_normal((batch, n, n))
+    return ((a + a.transpose(0, 2, 1)) / 2).astype(dtype)
+
+
+def _eigh_params(n, dtype=np.float32):
+    # src/library/lax-linalg.ts:78-79
+    return {"maxSweeps": max(8, 2 * n), "tolerance": 1e-12 if dtype == np.float64 else 1e-6}
+
+
+def factor_fft_size(n):
+    """`factorFftSize` (src/library/numpy-fft.ts:50-66): radices 4, 2, 3, 5, 7, then odd trial division."""
+    f = []
+    for radix in (4, 2, 3, 5, 7):
+        while n % radix == 0:
+            f.append(radix)
+            n //= radix
+    radix = 11
+    while radix * radix <= n:
+        while n % radix == 0:
+            f.append(radix)
+            n //= radix
+        radix += 2
+    if n > 1:
+        f.append(n)
+    return f
+
+
+def test_oracle_jacobi_eigh_reference_cases():
+    # test/lax-linalg.test.ts:153-165: a diagonal matrix is left alone (values 3, 1, 2; vectors = identity)
+    x = np.diag([3.0, 1.0, 2.0]).astype(np.float32)
+    a, v = oracle.jacobi_eigh(x, **{"max_sweeps": 8, "tolerance": 1e-6})
+    assert np.array_equal(np.diag(a), [3, 1, 2]) and np.array_equal(v, np.eye(3))
+    # :167-183: V diag(values) V^T reconstructs x and V is orthogonal, rtol = atol = 1e-3
+    x = np.array([[4.0, 1.0, 2.0], [1.0, 3.0, 0.5], [2.0, 0.5, 5.0]], np.float32)
+    a, v = oracle.jacobi_eigh(x, 8, 1e-6)
+    np.testing.assert_allclose(v @ np.diag(np.diag(a)) @ v.T, x, rtol=1e-3, atol=1e-3)
+    np.testing.assert_allclose(v.T @ v, np.eye(3), rtol=1e-3, atol=1e-3)
+    # :185-203: batched [[2,1],[1,2]] and [[3,1],[1,3]]: eigenvalues {1, 3} and {2, 4}
+    xb = np.array([[[2.0, 1.0], [1.0, 2.0]], [[3.0, 1.0], [1.0, 3.0]]], np.float32)
+    a, v = oracle.jacobi_eigh(xb, 8, 1e-6)
+    np.testing.assert_allclose(np.sort(np.diagonal(a, axis1=1, axis2=2)), [[1, 3], [2, 4]], rtol=1e-5)
+
+
+def test_oracle_fft_reference_vectors_and_numpy():
+    # test/numpy-fft.test.ts:91-96 and :170-174
+    r, i = oracle.fft(np.array([6, -2, -2, -2], np.float32), np.array([0, 2, 0, -2], np.float32), factor_fft_size(4), inverse=True)
+    np.testing.assert_allclose(r, [0, 1, 2, 3], atol=1e-6)
+    np.testing.assert_allclose(i, [0, 0, 0, 0], atol=1e-6)
+    r, i = oracle.fft(np.array([0, 1, 2, 3], np.float32), np.zeros(4, np.float32), factor_fft_size(4))
+    np.testing.assert_allclose(r, [6, -2, -2, -2], atol=1e-5)
+    np.testing.assert_allclose(i, [0, 2, 0, -2], atol=1e-5)
+    rng = np.random.default_rng(2)
+    for n in (1, 2, 3, 8, 12, 30, 49, 97, 128, 360, 1001):
+        z = rng.standard_normal((3, n)) + 1j * rng.standard_normal((3, n))
+        for inverse in (False, True):
+            r, i = oracle.fft(z.real.astype(np.float32), z.imag.astype(np.float32), factor_fft_size(n), inverse)
+            want = np.fft.ifft(z) if inverse else np.fft.fft(z)
+            np.testing.assert_allclose(r + 1j * i, want, atol=2e-6 * np.abs(want).max() * max(1, np.log2(n)))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("batch,n", [(1, 1), (2, 2), (3, 3), (4, 17), (2, 64), (1, 150), (1, 200)])
+def test_cuda_jacobi_eigh(backend, batch, n):
+    x = _sym(np.random.default_rng(n), batch, n)
+    x[:, np.triu_indices(n, 1)[0], np.triu_indices(n, 1)[1]] = 99.0      # only the lower triangle is read
+    p = _eigh_params(n)
+    a, v = _run(backend, Routines.JacobiEigh, [x], [x.shape, x.shape], [F32, F32], p)
+    wa, wv = oracle.jacobi_eigh(x, p["maxSweeps"], p["tolerance"])
+    # the same rotations in the same order with the same arithmetic: bit-identical
+    assert np.array_equal(a, wa) and np.array_equal(v, wv)
+    xs = np.tril(x) + np.tril(x, -1).transpose(0, 2, 1)
+    vals = np.diagonal(a, axis1=1, axis2=2).astype(np.float64)
+    vd = v.astype(np.float64)
+    np.testing.assert_allclose(np.einsum("bij,bj,bkj->bik", vd, vals, vd), xs, rtol=1e-3, atol=1e-3 * max(1, np.sqrt(n) / 4))
+    np.testing.assert_allclose(np.sort(vals), np.linalg.eigvalsh(xs.astype(np.float64)), rtol=1e-4, atol=1e-4 * np.sqrt(n))
+
+
+@pytest.mark.gpu
+def test_cuda_jacobi_eigh_float64_and_diagonal_input(backend):
+    x = _sym(np.random.default_rng(4), 2, 12, np.float64)
+    p = _eigh_params(12, np.float64)
+    a, v = _run(backend, Routines.JacobiEigh, [x], [x.shape, x.shape], [F64, F64], p)
+    wa, wv = oracle.jacobi_eigh(x, p["maxSweeps"], p["tolerance"])
+    assert np.array_equal(a, wa) and np.array_equal(v, wv)
+    d = np.diag([3.0, 1.0, 2.0]).astype(np.float32)[None]              # test/lax-linalg.test.ts:153-165
+    a, v = _run(backend, Routines.JacobiEigh, [d], [d.shape, d.shape], [F32, F32], _eigh_params(3))
+    assert np.array_equal(np.diag(a[0]), [3, 1, 2]) and np.array_equal(v[0], np.eye(3))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n", [1, 2, 3, 4, 8, 12, 30, 49, 97, 128, 360, 1001, 4096])
+@pytest.mark.parametrize("inverse", [False, True])
+def test_cuda_fft(backend, n, inverse):
+    rng = np.random.default_rng(n)
+    batch = 5 if n < 1000 else 2
+    re, im = rng.standard_normal((batch, n)).astype(np.float32), rng.standard_normal((batch, n)).astype(np.float32)
+    if n == 4:
+        re[0], im[0] = ([6, -2, -2, -2], [0, 2, 0, -2]) if inverse else ([0, 1, 2, 3], [0, 0, 0, 0])
+    f = factor_fft_size(n)
+    r, i = _run(backend, Routines.Fft, [re, im], [re.shape, im.shape], [F32, F32], {"factors": f, "inverse": inverse})
+    wr, wi = oracle.fft(re, im, f, inverse)
+    scale = max(np.abs(wr).max(), np.abs(wi).max())
+    # same arithmetic and stage rounding; the twiddles come from a table (one rounding apart from the reference's)
+    assert np.abs(r - wr).max() <= 2e-6 * scale and np.abs(i - wi).max() <= 2e-6 * scale
+    want = (np.fft.ifft if inverse else np.fft.fft)(re.astype(np.float64) + 1j * im.astype(np.float64))
+    np.testing.assert_allclose(r + 1j * i, want, atol=3e-6 * np.abs(want).max() * max(1, np.log2(n)))
+    if n == 4:      # test/numpy-fft.test.ts:91-96, :170-174
+        np.testing.assert_allclose(r[0], [0, 1, 2, 3] if inverse else [6, -2, -2, -2], atol=1e-5)
+        np.testing.assert_allclose(i[0], [0, 0, 0, 0] if inverse else [0, 2, 0, -2], atol=1e-5)
+
+
+@pytest.mark.gpu
+def test_cuda_fft_float64_and_bad_factors(backend):
+    rng = np.random.default_rng(11)
+    re, im = rng.standard_normal((3, 60)), rng.standard_normal((3, 60))
+    r, i = _run(backend, Routines.Fft, [re, im], [re.shape, im.shape], [F64, F64], {"factors": factor_fft_size(60), "inverse": False})
+    np.testing.assert_allclose(r + 1j * i, np.fft.fft(re + 1j * im), atol=1e-12)
+    t = RoutineType([[8], [8]], [F32, F32], [[8], [8]], [F32, F32])
+    with pytest.raises(ValueError, match="fft: factors do not multiply"):
+        backend.prepare_routine(Routine(Routines.Fft, t, {"factors": [2, 2], "inverse": False}))
+
+
 @pytest.mark.gpu
 def test_cuda_linalg_shape_errors(backend):
     # src/routine.ts:305-313, :341-346: the reference throws on these shapes
