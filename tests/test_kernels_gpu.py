@@ -297,6 +297,60 @@ def test_matvec_f16(backend, K, Nout, orientation):
     assert_close(got.astype(np.float64) / K, want.astype(np.float64) / K, 2e-3, scale / K, "matvec f16")
 
 
+# ---- convolution and pooling: Dot / Reduce over pooled views (src/frontend/jit.ts:620-660) --------------
+
+def _conv_kernel(N, Ci, H, W, Co, KH, KW, stride, pad):
+    """out[n, co, oh, ow] = sum_{ci, kh, kw} x[n, ci, oh*stride + kh - pad, ow*stride + kw - pad] * w[co, ci, kh, kw], the padded
+    taps read as Where(valid, load, 0): the Kernel `jitRules[Conv]` builds from `prepareConv`'s views."""
+    OH, OW = (H + 2 * pad - KH) // stride + 1, (W + 2 * pad - KW) // stride + 1
+    i = AluExp.i32
+    ow, oh = AluExp.mod(g, i(OW)), AluExp.mod(AluExp.idiv(g, i(OW)), i(OH))
+    co, n = AluExp.mod(AluExp.idiv(g, i(OW * OH)), i(Co)), AluExp.idiv(g, i(OW * OH * Co))
+    kw, kh, ci = AluExp.mod(r, i(KW)), AluExp.mod(AluExp.idiv(r, i(KW)), i(KH)), AluExp.idiv(r, i(KW * KH))
+    ih = AluExp.add(AluExp.add(AluExp.mul(oh, i(stride)), kh), i(-pad))
+    iw = AluExp.add(AluExp.add(AluExp.mul(ow, i(stride)), kw), i(-pad))
+    inside = lambda v, hi: AluExp.mul(AluExp.cast(I32, AluExp.cmplt(i(-1), v)), AluExp.cast(I32, AluExp.cmplt(v, i(hi))))
+    valid = AluExp.cmpne(AluExp.mul(inside(ih, H), inside(iw, W)), i(0))
+    xi = AluExp.add(AluExp.mul(AluExp.add(AluExp.mul(AluExp.add(AluExp.mul(n, i(Ci)), ci), i(H)), ih), i(W)), iw)
+    x = AluExp.where(valid, AluExp.global_index(F32, 0, N * Ci * H * W, xi), AluExp.f32(0))
+    wi = AluExp.add(AluExp.mul(co, i(Ci * KH * KW)), r)
+    wv = AluExp.global_index(F32, 1, Co * Ci * KH * KW, wi)
+    return Kernel(2, N * Co * OH * OW, AluExp.mul(x, wv), Reduction(F32, AluOp.Add, Ci * KH * KW)), (OH, OW)
+
+
+@pytest.mark.parametrize("N,Ci,H,W,Co,KH,KW,stride,pad", [(2, 3, 17, 19, 5, 3, 3, 1, 1), (1, 8, 32, 32, 16, 5, 5, 2, 2), (3, 4, 9, 9, 6, 1, 1, 1, 0)])
+def test_convolution_kernel_through_the_generic_skeletons(backend, N, Ci, H, W, Co, KH, KW, stride, pad):
+    rng = np.random.default_rng(3)
+    x, w = rng.standard_normal((N, Ci, H, W)).astype(np.float32), rng.standard_normal((Co, Ci, KH, KW)).astype(np.float32)
+    k, (OH, OW) = _conv_kernel(N, Ci, H, W, Co, KH, KW, stride, pad)
+    got = run_cuda(backend, k, [x, w]).reshape(N, Co, OH, OW)
+    want = oracle.run_kernel(k, [x, w], fma=True).reshape(N, Co, OH, OW)
+    xp = np.pad(x.astype(np.float64), ((0, 0), (0, 0), (pad, pad), (pad, pad)))
+    ref = np.zeros((N, Co, OH, OW))
+    for kh in range(KH):
+        for kw in range(KW):
+            patch = xp[:, :, kh: kh + stride * OH: stride, kw: kw + stride * OW: stride]
+            ref += np.einsum("nchw,oc->nohw", patch, w[:, :, kh, kw].astype(np.float64))
+    K = Ci * KH * KW
+    assert_close(got / K, want / K, 1e-4, np.abs(x).max() * np.abs(w).max(), "conv vs oracle")
+    assert_close(got, ref, 1e-5, np.abs(ref).max(), "conv vs float64")
+
+
+def test_max_pool_kernel(backend):
+    """`jitRules[Pool]` then a Max reduction: 2 x 2 windows, stride 2, over [N, C, H, W]."""
+    N, C, H, W = 3, 5, 16, 20
+    x = np.random.default_rng(4).standard_normal((N, C, H, W)).astype(np.float32)
+    i = AluExp.i32
+    OH, OW = H // 2, W // 2
+    ow, oh, nc = AluExp.mod(g, i(OW)), AluExp.mod(AluExp.idiv(g, i(OW)), i(OH)), AluExp.idiv(g, i(OW * OH))
+    ih, iw = AluExp.add(AluExp.mul(oh, i(2)), AluExp.idiv(r, i(2))), AluExp.add(AluExp.mul(ow, i(2)), AluExp.mod(r, i(2)))
+    ix = AluExp.add(AluExp.mul(AluExp.add(AluExp.mul(nc, i(H)), ih), i(W)), iw)
+    k = Kernel(1, N * C * OH * OW, AluExp.global_index(F32, 0, x.size, ix), Reduction(F32, AluOp.Max, 4))
+    got = run_cuda(backend, k, [x]).reshape(N, C, OH, OW)
+    assert_same_bits(got.reshape(-1), oracle.run_kernel(k, [x]), "max pool")
+    assert np.array_equal(got, x.reshape(N, C, OH, 2, OW, 2).max(axis=(3, 5)))
+
+
 # ---- GEMM-shaped kernels -------------------------------------------------------------------------
 
 def _gemm_case(backend, kernel, args, K, tol, dtype, rows=None):
