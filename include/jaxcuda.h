@@ -65,6 +65,18 @@ int jaxcuda_read(jaxcuda_ctx* ctx, jaxcuda_slot slot, size_t start, size_t count
  * slots between steps instead of reallocating; the Wasm backend writes through its memory view,
  * src/backend/wasm.ts:57-75). */
 int jaxcuda_write(jaxcuda_ctx* ctx, jaxcuda_slot slot, size_t start, size_t count, const void* src);
+/* Backend.read as the reference declares it, returning a Promise (src/backend.ts:182-186): the copy
+ * of bytes [start, start+count) to dst is enqueued on a copy stream of its own, after everything
+ * dispatched so far, and the call returns.  jaxcuda_read_wait(ticket) is where the Promise resolves.
+ * dst must be pinned memory (jaxcuda_host_alloc); until the wait returns the slot must stay alive and
+ * must not be the output of a dispatch (jaxcuda_write_async into it is ordered after the read).
+ * Uploads, kernels and downloads of consecutive steps then overlap. */
+int jaxcuda_read_async(jaxcuda_ctx* ctx, jaxcuda_slot slot, size_t start, size_t count, void* dst, uint64_t* ticket);
+int jaxcuda_read_wait(jaxcuda_ctx* ctx, uint64_t ticket);
+/* jaxcuda_write on a copy stream: starts after everything dispatched so far (earlier kernels may
+ * still read the slot); everything dispatched afterwards waits for it.  src must be pinned and
+ * unchanged until a later read_wait or sync has returned. */
+int jaxcuda_write_async(jaxcuda_ctx* ctx, jaxcuda_slot slot, size_t start, size_t count, const void* src);
 int jaxcuda_slot_size(jaxcuda_ctx* ctx, jaxcuda_slot slot, size_t* bytes);
 
 /* Backend.prepareKernel[Sync] (src/backend.ts:192-196).  `ir` is the lowered Kernel image of

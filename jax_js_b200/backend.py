@@ -67,6 +67,9 @@ SYMBOLS = {
     "jaxcuda_decref": (_I, [_P, _U32]),
     "jaxcuda_read": (_I, [_P, _U32, _SZ, _SZ, _P]),
     "jaxcuda_write": (_I, [_P, _U32, _SZ, _SZ, _P]),
+    "jaxcuda_read_async": (_I, [_P, _U32, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_void_p, ctypes.POINTER(ctypes.c_uint64)]),
+    "jaxcuda_read_wait": (_I, [_P, ctypes.c_uint64]),
+    "jaxcuda_write_async": (_I, [_P, _U32, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_void_p]),
     "jaxcuda_slot_size": (_I, [_P, _U32, ctypes.POINTER(_SZ)]),
     "jaxcuda_prepare_kernel": (_I, [_P, ctypes.c_char_p, _SZ, _U64, ctypes.POINTER(_P)]),
     "jaxcuda_check_kernel": (_I, [ctypes.c_char_p, _SZ, _I, _I, _I, ctypes.c_char_p, _SZ, ctypes.c_char_p, _SZ]),
@@ -249,6 +252,20 @@ class CudaBackend:
 
     def write(self, slot: int, src: np.ndarray, start: int = 0) -> None:
         self._check(self._lib.jaxcuda_write(self._ctx, slot, start, src.nbytes, src.ctypes.data))
+
+    def read_async(self, slot: int, dst: np.ndarray, start: int = 0) -> int:
+        """`read` as a Promise (src/backend.ts:182-186): enqueue the copy into pinned `dst` on the
+        download stream and return a ticket; `read_wait(ticket)` is where the Promise resolves."""
+        t = ctypes.c_uint64()
+        self._check(self._lib.jaxcuda_read_async(self._ctx, slot, start, dst.nbytes, dst.ctypes.data, ctypes.byref(t)))
+        return t.value
+
+    def read_wait(self, ticket: int) -> None:
+        self._check(self._lib.jaxcuda_read_wait(self._ctx, ticket))
+
+    def write_async(self, slot: int, src: np.ndarray, start: int = 0) -> None:
+        """Upload from pinned `src` on the upload stream, ordered between earlier and later dispatches."""
+        self._check(self._lib.jaxcuda_write_async(self._ctx, slot, start, src.nbytes, src.ctypes.data))
 
     def write_ptr(self, slot: int, ptr: int, nbytes: int, start: int = 0) -> None:
         self._check(self._lib.jaxcuda_write(self._ctx, slot, start, nbytes, ptr))

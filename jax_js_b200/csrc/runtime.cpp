@@ -154,6 +154,7 @@ struct SlotRec {
   void* ptr = nullptr;
   size_t bytes = 0;
   int refs = 0;
+  uint64_t read_ticket = 0;  // last asynchronous read of this slot (a later upload into it waits for that read)
 };
 
 }  // namespace jaxcuda_rt
@@ -217,6 +218,12 @@ struct jaxcuda_ctx {
   cudaStream_t comm_stream = nullptr;
   cudaEvent_t comm_fork = nullptr, comm_done = nullptr;
   bool comm_pending = false;
+  // copy streams of the asynchronous read / write calls, so that uploads, kernels and downloads of
+  // consecutive steps overlap (the GPU has separate copy engines per direction)
+  cudaStream_t up_stream = nullptr, down_stream = nullptr;
+  cudaEvent_t copy_fork = nullptr, up_done = nullptr;
+  std::vector<cudaEvent_t> tickets;  // ticket t = tickets[t - 1]
+  std::vector<uint64_t> free_tickets;
   // direction of the next streaming kernel's walk over its grid (JAXCUDA_SWEEP=0: always forward)
   int sweep = 0;
   bool sweep_alternate = true;
@@ -394,6 +401,15 @@ int jaxcuda_destroy(jaxcuda_ctx* ctx) {
   if (!ctx) return JAXCUDA_OK;
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->stream);
+  if (ctx->up_stream) {
+    cudaStreamSynchronize(ctx->up_stream);
+    cudaStreamSynchronize(ctx->down_stream);
+    for (cudaEvent_t ev : ctx->tickets) cudaEventDestroy(ev);
+    cudaEventDestroy(ctx->copy_fork);
+    cudaEventDestroy(ctx->up_done);
+    cudaStreamDestroy(ctx->up_stream);
+    cudaStreamDestroy(ctx->down_stream);
+  }
   if (ctx->comm_stream) {
     cudaStreamSynchronize(ctx->comm_stream);
     cudaEventDestroy(ctx->comm_fork);
@@ -493,6 +509,76 @@ int jaxcuda_write(jaxcuda_ctx* ctx, jaxcuda_slot slot, size_t start, size_t coun
     return fail(ctx, JAXCUDA_EINVAL, "write of %zu bytes at %zu beyond buffer of %zu bytes", count, start, s->bytes);
   cudaSetDevice(ctx->device);
   if (count) CUDA_TRY(ctx, cudaMemcpyAsync((char*)s->ptr + start, src, count, cudaMemcpyHostToDevice, ctx->stream));
+  return JAXCUDA_OK;
+}
+
+static int copy_streams(jaxcuda_ctx* ctx) {
+  if (ctx->up_stream) return JAXCUDA_OK;
+  CUDA_TRY(ctx, cudaStreamCreateWithFlags(&ctx->up_stream, cudaStreamNonBlocking));
+  CUDA_TRY(ctx, cudaStreamCreateWithFlags(&ctx->down_stream, cudaStreamNonBlocking));
+  CUDA_TRY(ctx, cudaEventCreateWithFlags(&ctx->copy_fork, cudaEventDisableTiming));
+  CUDA_TRY(ctx, cudaEventCreateWithFlags(&ctx->up_done, cudaEventDisableTiming));
+  return JAXCUDA_OK;
+}
+
+int jaxcuda_write_async(jaxcuda_ctx* ctx, jaxcuda_slot slot, size_t start, size_t count, const void* src) {
+  SlotRec* s = find_slot(ctx, slot);
+  if (!s) return slot_error(ctx, slot);
+  if (ctx->alloc.capturing) return fail(ctx, JAXCUDA_EINVAL, "write_async inside a capture");
+  if (start > s->bytes || count > s->bytes - start)
+    return fail(ctx, JAXCUDA_EINVAL, "write of %zu bytes at %zu beyond buffer of %zu bytes", count, start, s->bytes);
+  cudaSetDevice(ctx->device);
+  if (!count) return JAXCUDA_OK;
+  if (int rc = copy_streams(ctx)) return rc;
+  // after everything dispatched so far (earlier kernels may still read the slot) ...
+  CUDA_TRY(ctx, cudaEventRecord(ctx->copy_fork, ctx->stream));
+  CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->up_stream, ctx->copy_fork, 0));
+  if (s->read_ticket)  // ... and after a download of this very slot that may still be in flight
+    CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->up_stream, ctx->tickets[s->read_ticket - 1], 0));
+  CUDA_TRY(ctx, cudaMemcpyAsync((char*)s->ptr + start, src, count, cudaMemcpyHostToDevice, ctx->up_stream));
+  // ... and before everything dispatched from now on
+  CUDA_TRY(ctx, cudaEventRecord(ctx->up_done, ctx->up_stream));
+  CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->stream, ctx->up_done, 0));
+  return JAXCUDA_OK;
+}
+
+int jaxcuda_read_async(jaxcuda_ctx* ctx, jaxcuda_slot slot, size_t start, size_t count, void* dst, uint64_t* ticket) {
+  SlotRec* s = find_slot(ctx, slot);
+  if (!s) return slot_error(ctx, slot);
+  if (!ticket) return fail(ctx, JAXCUDA_EINVAL, "null ticket");
+  if (ctx->alloc.capturing) return fail(ctx, JAXCUDA_EINVAL, "read inside a capture: reads synchronise the stream");
+  if (start > s->bytes) return fail(ctx, JAXCUDA_EINVAL, "read start %zu beyond buffer of %zu bytes", start, s->bytes);
+  if (count == SIZE_MAX) count = s->bytes - start;
+  if (count > s->bytes - start) return fail(ctx, JAXCUDA_EINVAL, "read of %zu bytes at %zu beyond buffer of %zu bytes", count, start, s->bytes);
+  if (count && !dst) return fail(ctx, JAXCUDA_EINVAL, "null destination");
+  cudaSetDevice(ctx->device);
+  if (int rc = jaxcuda_comm_join(ctx)) return rc;
+  if (int rc = copy_streams(ctx)) return rc;
+  CUDA_TRY(ctx, cudaEventRecord(ctx->copy_fork, ctx->stream));
+  CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->down_stream, ctx->copy_fork, 0));
+  if (count) CUDA_TRY(ctx, cudaMemcpyAsync(dst, (const char*)s->ptr + start, count, cudaMemcpyDeviceToHost, ctx->down_stream));
+  uint64_t t;
+  if (!ctx->free_tickets.empty()) {
+    t = ctx->free_tickets.back();
+    ctx->free_tickets.pop_back();
+  } else {
+    cudaEvent_t ev;
+    CUDA_TRY(ctx, cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    ctx->tickets.push_back(ev);
+    t = ctx->tickets.size();
+  }
+  CUDA_TRY(ctx, cudaEventRecord(ctx->tickets[t - 1], ctx->down_stream));
+  s->read_ticket = t;
+  *ticket = t;
+  return JAXCUDA_OK;
+}
+
+int jaxcuda_read_wait(jaxcuda_ctx* ctx, uint64_t ticket) {
+  if (!ctx || ticket == 0 || ticket > ctx->tickets.size()) return JAXCUDA_EINVAL;
+  for (uint64_t f : ctx->free_tickets) if (f == ticket) return fail(ctx, JAXCUDA_EINVAL, "ticket %llu is not pending", (unsigned long long)ticket);
+  cudaSetDevice(ctx->device);
+  CUDA_TRY(ctx, cudaEventSynchronize(ctx->tickets[ticket - 1]));
+  ctx->free_tickets.push_back(ticket);
   return JAXCUDA_OK;
 }
 

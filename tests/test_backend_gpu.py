@@ -184,3 +184,40 @@ def test_dispatch_order_is_execution_order(backend):
     finally:
         backend.dec_ref(a)
         backend.dec_ref(b)
+
+
+def test_async_read_and_write_are_ordered_with_dispatches(backend):
+    # Backend.read returns a Promise (src/backend.ts:182-186): read_async enqueues, read_wait resolves.
+    # Two steps in flight over two input slots, as a caller awaiting the previous step would run them.
+    n = 1 << 20
+    inc = backend.prepare_kernel(Kernel(1, n, AluExp.add(AluExp.global_index(F32, 0, n, g), AluExp.f32(1))))
+    host_in = [backend.host_alloc(n * 4) for _ in range(2)]
+    host_out = [backend.host_alloc(n * 4) for _ in range(2)]
+    ins, pending, results = [backend.malloc(n * 4) for _ in range(2)], None, []
+    for step in range(6):
+        k = step % 2
+        if pending is not None and pending[0] == k:      # this pair of buffers is still in flight
+            backend.read_wait(pending[2]); results.append(host_out[k].view(np.float32).copy()); backend.dec_ref(pending[1]); pending = None
+        host_in[k].view(np.float32)[:] = step * 10
+        backend.write_async(ins[k], host_in[k])
+        out = backend.malloc(n * 4)
+        backend.dispatch(inc, [ins[k]], [out])
+        ticket = backend.read_async(out, host_out[k])
+        if pending is not None:
+            backend.read_wait(pending[2]); results.append(host_out[pending[0]].view(np.float32).copy()); backend.dec_ref(pending[1])
+        pending = (k, out, ticket)
+        backend.sync()                                    # the upload has been consumed: host_in[k] may change
+    backend.read_wait(pending[2]); results.append(host_out[pending[0]].view(np.float32).copy()); backend.dec_ref(pending[1])
+    assert [float(r[0]) for r in results] == [1, 11, 21, 31, 41, 51] and all((r == r[0]).all() for r in results)
+    with pytest.raises(ValueError):
+        backend.read_wait(pending[2])                     # a ticket resolves once
+    # partial ranges and a read ordered after a later write into the same slot
+    backend.write(ins[0], np.arange(n, dtype=np.float32))
+    t = backend.read_async(ins[0], host_out[0][:64], start=128)
+    backend.write_async(ins[0], host_in[1])               # must not overtake the read above
+    backend.read_wait(t)
+    assert host_out[0][:64].view(np.float32).tolist() == list(range(32, 48))
+    for s in ins:
+        backend.dec_ref(s)
+    for h in host_in + host_out:
+        backend.host_free(h)
