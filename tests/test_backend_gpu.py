@@ -221,3 +221,34 @@ def test_async_read_and_write_are_ordered_with_dispatches(backend):
         backend.dec_ref(s)
     for h in host_in + host_out:
         backend.host_free(h)
+
+
+def test_empty_and_largest_kernels(backend):
+    # size 0: nothing to do, nothing launched out of bounds
+    empty = Kernel(1, 0, AluExp.add(AluExp.global_index(F32, 0, 0, g), AluExp.f32(1)))
+    a, b = backend.malloc(0), backend.malloc(0)
+    backend.dispatch(backend.prepare_kernel(empty), [a], [b])
+    assert backend.read_sync(b).size == 0
+    backend.dec_ref(a)
+    backend.dec_ref(b)
+    # the largest index space the int32 gidx of the reference allows (src/alu.ts:1479): 2^31 - 8 outputs, 8.6 GB.
+    # out[g] = g * 3 (wrapping), then a wrapping uint32 row sum over [32768 - 1, 65536] checked in closed form.
+    n_cols = 1 << 16
+    n_rows = (1 << 15) - 1
+    n = n_rows * n_cols
+    big = backend.malloc(n * 4)
+    fill = Kernel(0, n, AluExp.mul(AluExp.cast(U32, g), AluExp.u32(3)))
+    backend.dispatch(backend.prepare_kernel(fill), [], [big])
+    r = AluVar.ridx
+    rows = Kernel(1, n_rows, AluExp.global_index(U32, 0, n, AluExp.add(AluExp.mul(g, AluExp.i32(n_cols)), r)),
+                  Reduction(U32, AluOp.Add, n_cols))
+    sums = backend.malloc(n_rows * 4)
+    backend.dispatch(backend.prepare_kernel(rows), [big], [sums])
+    got = backend.get(sums, U32)
+    i = np.arange(n_rows, dtype=np.uint64)
+    want = (3 * (i * n_cols * n_cols + n_cols * (n_cols - 1) // 2)) % (1 << 32)
+    assert np.array_equal(got.astype(np.uint64), want)
+    tail = backend.read_sync(big, (n - 4) * 4, 16).view(np.uint32)
+    assert tail.tolist() == [((n - 4 + j) * 3) % (1 << 32) for j in range(4)]
+    backend.dec_ref(big)
+    backend.dec_ref(sums)
