@@ -65,6 +65,7 @@ struct Options {
   int ew_blocks_per_sm = 4096;  // grid cap; at the default the grid covers the array in one pass
   int gemm_min_dim = 32;      // below this M or N a GEMM-shaped kernel stays on the reduce skeletons
   bool allow_tc = true;       // tcgen05 path allowed (JAXCUDA_NO_TC=1 clears it)
+  int tc_bn = 0;              // force the tensor-core tile width (64, 128, 192, 256); 0 = planner's choice (JAXCUDA_TC_BN)
   int force_skeleton = -1;    // tests: force SK_REDUCE_ROW / SK_REDUCE_COL / SK_GEMM_FFMA
   int exact_math = -1;        // 1: bit-faithful exp everywhere, 0: fast everywhere, -1: exact below exact_math_work
   double exact_math_work = 1 << 20;  // element evaluations (size x K) under which a kernel is latency-bound anyway

@@ -119,7 +119,7 @@ __device__ __forceinline__ u64 operand_desc(u32 base, int kk, int mn_major) {
 #define TILES_N ((GN + BN - 1) / BN)
 #define NUM_TILES (TILES_M * TILES_N * GBATCH)
 #define K_BLOCKS ((GK + BK - 1) / BK)
-#define TMEM_COLS (2 * BN)
+#define TMEM_COLS (2 * ACC_STRIDE)     /* a power of two; the two accumulators start ACC_STRIDE columns apart */
 #define NCHUNK ((K_BLOCKS + CHUNK_KB - 1) / CHUNK_KB)
 #define IDESC ((1u << 4) | ((KIND == 2 ? 2u : 0u) << 7) | ((KIND == 2 ? 2u : 0u) << 10) | ((u32)A_MN << 15) | \
                ((u32)B_MN << 16) | ((u32)(BN >> 3) << 17) | ((u32)(BM >> 4) << 24))
@@ -216,7 +216,7 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
           const int acc = cc & 1;
           if (cc >= 2 && !mbar_wait(tempty(acc), ((cc >> 1) + 1) & 1, status)) { atomicCAS((int*)status_ptr, 0, 2); failed = true; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const u32 d = tmem_base + acc * BN;
+          const u32 d = tmem_base + acc * ACC_STRIDE;
           const int kb_end = (ch + 1) * CHUNK_KB < K_BLOCKS ? (ch + 1) * CHUNK_KB : K_BLOCKS;
           for (int kb = ch * CHUNK_KB; kb < kb_end; kb++, it++) {
             const int s = it % STAGES;
@@ -257,7 +257,7 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
         const int acc_i = cc & 1;
         if (!mbar_wait(tfull(acc_i), (cc >> 1) & 1, status)) { atomicCAS((int*)status_ptr, 0, 4); failed = true; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const u32 trow = tmem_base + ((u32)(q * 32) << 16) + acc_i * BN;
+        const u32 trow = tmem_base + ((u32)(q * 32) << 16) + acc_i * ACC_STRIDE;
         #pragma unroll
         for (int c = 0; c < BN / 16; c++) {
           u32 v[16];
@@ -275,7 +275,7 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
       const int acc_i = cc & 1;
       if (!mbar_wait(tfull(acc_i), (cc >> 1) & 1, status)) { atomicCAS((int*)status_ptr, 0, 4); failed = true; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const u32 trow = tmem_base + ((u32)(q * 32) << 16) + acc_i * BN;
+      const u32 trow = tmem_base + ((u32)(q * 32) << 16) + acc_i * ACC_STRIDE;
 #if NCHUNK > 1
       #pragma unroll
 #else
@@ -398,6 +398,11 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
     if (cand <= g.N && (tiles >= (int64_t)opt.sm_count * 3 / 4 || cand == 64)) { BN = cand; break; }
   }
   if (BN > g.N) BN = 64;
+  // A 192-column tile would shorten the static schedule of f16 4096^3 (512 tiles of 256 columns are
+  // 3.46 waves of 148 CTAs), but measured slower (124 us against 108): narrower tiles re-read A from
+  // shared memory more often per flop, and the MMA pipe is already fed at its limit with 256 columns.
+  // The width stays selectable (Options::tc_bn) for experiments.
+  if (opt.tc_bn == 64 || opt.tc_bn == 128 || (kind == 1 && (opt.tc_bn == 192 || opt.tc_bn == 256))) BN = std::min<int>(opt.tc_bn, (int)(g.N / 64 * 64));
   const int planes = kind == 2 ? 2 : 1;
   const int stage_bytes = planes * (BM + BN) * 128;
   int stages = (227 * 1024 - 2048) / stage_bytes;
@@ -407,6 +412,7 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
   std::ostringstream os;
   os << kPrelude;
   os << "#define KIND " << kind << "\n#define ELEM " << e << "\n#define BM " << BM << "\n#define BN " << BN << "\n";
+  os << "#define ACC_STRIDE " << (BN > 128 ? 256 : BN) << "\n";
   os << "#define STAGES " << stages << "\n#define A_MN " << (a_mn ? 1 : 0) << "\n#define B_MN " << (b_mn ? 1 : 0) << "\n";
   os << "#define GM " << g.M << "\n#define GN " << g.N << "\n#define GK " << g.K << "\n#define GBATCH " << g.batch << "\n";
   // k-blocks accumulated in tensor memory before the partial sum is folded into registers with a

@@ -391,6 +391,7 @@ int jaxcuda_create(int device, jaxcuda_ctx** out) {
   ctx->opt.col_ty = env_int("JAXCUDA_COL_TY", ctx->opt.col_ty);
   ctx->opt.col_unroll = env_int("JAXCUDA_COL_UNROLL", ctx->opt.col_unroll);
   ctx->comm_sms = env_int("JAXCUDA_COMM_SMS", ctx->comm_sms);
+  ctx->opt.tc_bn = env_int("JAXCUDA_TC_BN", 0);
   ctx->sweep_alternate = env_int("JAXCUDA_SWEEP", 1) != 0;
   ctx->debug = env_int("JAXCUDA_DEBUG", 0);
   *out = ctx.release();
