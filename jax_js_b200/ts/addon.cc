@@ -5,6 +5,7 @@
 // Not compiled in this repository: the build image has neither Node nor node_api.h.
 #include <napi.h>
 
+#include <cstring>
 #include <vector>
 
 #include "jaxcuda.h"
@@ -63,6 +64,60 @@ Napi::Value Read(const Napi::CallbackInfo& info) {
   if (jaxcuda_read(ctx, slot, start, (size_t)count, out.Data()) != JAXCUDA_OK) Throw(info.Env(), ctx);
   return out;
 }
+// Backend.read as a Promise: the copy is enqueued on the library's download stream into pinned
+// memory right away (ordered after the dispatches so far); a worker thread blocks in
+// jaxcuda_read_wait, and the Promise resolves with a copy of the pinned buffer on the main thread.
+class ReadWorker : public Napi::AsyncWorker {
+ public:
+  ReadWorker(Napi::Env env, jaxcuda_ctx* ctx, jaxcuda_slot slot, void* pinned, size_t count, uint64_t ticket)
+      : Napi::AsyncWorker(env), deferred_(Napi::Promise::Deferred::New(env)), ctx_(ctx), slot_(slot), pinned_(pinned),
+        count_(count), ticket_(ticket) {}
+  Napi::Promise Promise() const { return deferred_.Promise(); }
+  void Execute() override {
+    if (jaxcuda_read_wait(ctx_, ticket_) != JAXCUDA_OK) SetError(jaxcuda_last_error(ctx_));
+  }
+  void OnOK() override {
+    auto out = Napi::Uint8Array::New(Env(), count_);
+    if (count_) memcpy(out.Data(), pinned_, count_);
+    jaxcuda_host_free(ctx_, pinned_);
+    jaxcuda_decref(ctx_, slot_);           // the reference taken in ReadAsync kept the buffer alive
+    deferred_.Resolve(out);
+  }
+  void OnError(const Napi::Error& e) override {
+    jaxcuda_host_free(ctx_, pinned_);
+    jaxcuda_decref(ctx_, slot_);
+    deferred_.Reject(e.Value());
+  }
+
+ private:
+  Napi::Promise::Deferred deferred_;
+  jaxcuda_ctx* ctx_;
+  jaxcuda_slot slot_;
+  void* pinned_;
+  size_t count_;
+  uint64_t ticket_;
+};
+Napi::Value ReadAsync(const Napi::CallbackInfo& info) {
+  jaxcuda_ctx* ctx = Ctx(info[0]);
+  const jaxcuda_slot slot = info[1].As<Napi::Number>().Uint32Value();
+  const size_t start = (size_t)info[2].As<Napi::Number>().Int64Value();
+  int64_t count = info[3].As<Napi::Number>().Int64Value();
+  size_t size = 0;
+  if (jaxcuda_slot_size(ctx, slot, &size) != JAXCUDA_OK) Throw(info.Env(), ctx);
+  if (count < 0) count = (int64_t)(size - start);
+  void* pinned = nullptr;
+  if (jaxcuda_host_alloc(ctx, (size_t)count > 0 ? (size_t)count : 1, &pinned) != JAXCUDA_OK) Throw(info.Env(), ctx);
+  uint64_t ticket = 0;
+  jaxcuda_incref(ctx, slot);               // a caller may drop its reference before the Promise resolves
+  if (jaxcuda_read_async(ctx, slot, start, (size_t)count, pinned, &ticket) != JAXCUDA_OK) {
+    jaxcuda_decref(ctx, slot);
+    jaxcuda_host_free(ctx, pinned);
+    Throw(info.Env(), ctx);
+  }
+  auto* worker = new ReadWorker(info.Env(), ctx, slot, pinned, (size_t)count, ticket);
+  worker->Queue();
+  return worker->Promise();
+}
 Napi::Value PrepareKernel(const Napi::CallbackInfo& info) {
   jaxcuda_ctx* ctx = Ctx(info[0]);
   auto image = info[1].As<Napi::Uint8Array>();
@@ -116,6 +171,7 @@ Napi::Object Init(Napi::Env env, Napi::Object exports) {
   exports.Set("incref", Napi::Function::New(env, IncRef));
   exports.Set("decref", Napi::Function::New(env, DecRef));
   exports.Set("read", Napi::Function::New(env, Read));
+  exports.Set("readAsync", Napi::Function::New(env, ReadAsync));
   exports.Set("prepareKernel", Napi::Function::New(env, PrepareKernel));
   exports.Set("prepareRoutine", Napi::Function::New(env, PrepareRoutine));
   exports.Set("dispatch", Napi::Function::New(env, Dispatch));

@@ -32,6 +32,7 @@ interface Native {
   incref(ctx: bigint, slot: number): number;           // returns jaxcuda_status
   decref(ctx: bigint, slot: number): number;
   read(ctx: bigint, slot: number, start: number, count: number): Uint8Array<ArrayBuffer>;
+  readAsync(ctx: bigint, slot: number, start: number, count: number): Promise<Uint8Array<ArrayBuffer>>;
   prepareKernel(ctx: bigint, image: Uint8Array, hash: bigint): bigint;
   prepareRoutine(ctx: bigint, name: string, type: unknown, params: string): bigint;
   dispatch(ctx: bigint, exe: bigint, inputs: Uint32Array, outputs: Uint32Array): number;
@@ -127,7 +128,11 @@ export class CudaBackend implements Backend {
   incRef(slot: Slot): void { this.#check(this.native.incref(this.ctx, slot), slot); }
   decRef(slot: Slot): void { this.#check(this.native.decref(this.ctx, slot), slot); }
 
-  async read(slot: Slot, start?: number, count?: number) { return this.readSync(slot, start, count); }
+  // The copy starts at once on the library's download stream; the Promise resolves on a worker thread,
+  // so the event loop keeps dispatching (and uploading) the next step meanwhile.
+  read(slot: Slot, start = 0, count = -1): Promise<Uint8Array<ArrayBuffer>> {
+    return this.native.readAsync(this.ctx, slot, start, count);
+  }
   readSync(slot: Slot, start = 0, count = -1): Uint8Array<ArrayBuffer> {
     return this.native.read(this.ctx, slot, start, count);   // count -1: to the end; 0: barrier only
   }
