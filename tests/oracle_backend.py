@@ -21,6 +21,7 @@ class OracleBackend:
 
     def __init__(self, dist=None, threads=None, fma=False):
         self.slots, self.next, self.dist, self.threads, self.fma = {}, 1, dist, threads, fma
+        self.async_calls, self.joined = [], True
 
     def malloc(self, size, initial_data=None):
         buf = np.zeros(size, np.uint8) if initial_data is None else np.frombuffer(bytes(initial_data), np.uint8).copy()
@@ -76,6 +77,16 @@ class OracleBackend:
         for s in slots:
             t = torch.from_numpy(self.slots[s][0].view(np.float32))
             self.dist.all_reduce(t)
+
+    def allreduce_sum_f32_async(self, slots):
+        """The trainer issues one such call per layer as soon as the layer's gradients exist; here the
+        sum simply happens at once.  The calls are logged so that a test can check their grouping."""
+        self.async_calls.append(len(slots))
+        self.joined = False
+        self.allreduce_sum_f32(slots)
+
+    def comm_join(self):
+        self.joined = True
 
     def sync(self):
         pass

@@ -443,6 +443,21 @@ def test_mlp_backward_dot_through_relu_gate(backend):
     assert_close(got, want, 1e-5, np.abs(dz).astype(np.float64) @ np.abs(W.T).astype(np.float64), "gated dot")
 
 
+@pytest.mark.parametrize("M,N,K,al,bl,skeleton", [(2048, 10, 4096, "km", "kn", "dot-skinny-t"), (4096, 512, 10, "mk", "nk", "dot-small-k"),
+                                                   (8192, 10, 1024, "mk", "kn", "dot-skinny")])
+def test_skinny_dots_f16(backend, M, N, K, al, bl, skeleton):
+    # float16 operands, float32 accumulation, float16 result: `cpu`-backend semantics (2e-3 per element after / K)
+    rng = np.random.default_rng(12)
+    A = (rng.standard_normal((M, K) if al == "mk" else (K, M)) * 0.05).astype(np.float16)
+    B = (rng.standard_normal((K, N) if bl == "kn" else (N, K)) * 0.05).astype(np.float16)
+    k = P.dot_kernel(M, N, K, F16, a_layout=al, b_layout=bl)
+    assert backend.prepare_kernel(k).describe.startswith(skeleton + " "), backend.prepare_kernel(k).describe
+    got = _gemm_case(backend, k, [A, B], K, 2e-3, F16).reshape(M, N)
+    Am, Bm = (A if al == "mk" else A.T), (B if bl == "kn" else B.T)
+    ref = Am.astype(np.float64) @ Bm.astype(np.float64)
+    assert_close(got, ref, 1e-3, np.abs(ref).max(), "f16 dot vs float64")
+
+
 @pytest.mark.parametrize("n", [256, 4096])
 def test_gemm_f16(backend, n):
     rng = np.random.default_rng(0)

@@ -123,6 +123,8 @@ def _rank_main(rank, world, port, out):
         s = tr.step(sx, sy, world=world)
         losses.append(float(be.get(s, "float32")[0]))
         be.dec_ref(s)
+    # each step summed the leaves layer by layer (last layer first, the loss with it) and joined before Adam
+    assert tr.overlap and be.joined and be.async_calls == [3, 2, 2] * 2, be.async_calls
     if rank == 0:
         np.savez(out, losses=np.array(losses), **{f"p{i}": be.get(s, "float32") for i, s in enumerate(tr.params)})
     dist.destroy_process_group()
