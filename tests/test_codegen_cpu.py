@@ -9,6 +9,7 @@ import numpy as np
 import pytest
 
 from jax_js_b200 import AluExp, AluOp, AluVar, DType, Kernel, Reduction, ShapeTracker, accessor_global
+from jax_js_b200 import mlp
 from jax_js_b200 import programs as P
 from jax_js_b200.alu import NODE_WORDS, WIRE_MAGIC
 from jax_js_b200.backend import (SYMBOLS, CudaBackend, CudaError, UnsupportedOpError, check_kernel)
@@ -86,6 +87,13 @@ CASES = {
     "short rows": (P.row_reduce_kernel(65536, 10, AluOp.Max), "reduce-col V=1"),
     "mid rows": (P.row_reduce_kernel(4096, 200, AluOp.Add), "reduce-row TPR=32"),
     "scalar sum": (P.row_reduce_kernel(1, 1 << 24, AluOp.Add), "splits="),
+    # the 10-class layer of the MLP: forward, weight gradient, back-propagated dot, bias gradient
+    "skinny forward": (P.dot_kernel(8192, 10, 2048), "dot-skinny 8192x10x2048"),
+    "skinny weight grad": (P.dot_kernel(2048, 10, 8192, a_layout="km"), "dot-skinny-t 2048x10x8192"),
+    "small-k backward": (mlp.backprop_dot_kernel(8192, 2048, 10), "dot-small-k 8192x2048x10"),
+    "bias grad": (mlp.column_sum_kernel(8192, 2048), "reduce-col V=4"),
+    "skinny f16": (P.dot_kernel(4096, 16, 512, F16, a_layout="km"), "dot-skinny-t"),
+    "small-k ragged": (P.dot_kernel(65, 1028, 16, a_layout="km", b_layout="nk"), "dot-small-k"),
 }
 
 
