@@ -236,3 +236,65 @@ def test_float16_uses_cpu_backend_semantics():
     np.testing.assert_array_equal(y, want)
     for v in [0.0, -0.0, 1.0, 65504.0, 65520.0, 1e-8, 6e-8, 5.96e-8, 0.333251953125, float("inf")]:
         assert oracle.lib().oracle_double_to_half(v) == int(np.array(v, np.float64).astype(np.float16).view(np.uint16))
+
+
+def _program(prog, arrays):
+    """Replay a step list on the oracle backend and return its outputs as numpy arrays."""
+    from oracle_backend import OracleBackend
+    be = OracleBackend()
+    outs = prog.execute(be, [be.put(a) for a in arrays])
+    return [be.slots[s][0] for s in outs]
+
+
+def test_softmax_logsumexp_argmax_program_known_answers():
+    from jax_js_b200 import programs as P
+    # test/nn.test.ts:107-117: softmax of [[1,2,3],[4,5,6]] over the last axis
+    x = np.array([[1, 2, 3], [4, 5, 6]], np.float32)
+    sm, lse, am = _program(P.softmax_lse_argmax_program(2, 3), [x, P.argmax_iota(3)])
+    np.testing.assert_allclose(sm.view(np.float32).reshape(2, 3), [[0.09003057, 0.24472848, 0.66524094]] * 2, rtol=1e-5)
+    assert am.view(np.int32).tolist() == [2, 2]
+    # test/nn.test.ts:164-178: logsumexp([-10,-1,1,2]) = 2.3490167; of [[1,2,3,4],[5,6,7,8]] as one row of 8 = 8.45834
+    _, lse, _ = _program(P.softmax_lse_argmax_program(1, 4), [f32(-10, -1, 1, 2).reshape(1, 4), P.argmax_iota(4)])
+    assert abs(float(lse.view(np.float32)[0]) - 2.3490167) < 1e-5
+    _, lse, _ = _program(P.softmax_lse_argmax_program(1, 8), [np.arange(1, 9, dtype=np.float32).reshape(1, 8), P.argmax_iota(8)])
+    assert abs(float(lse.view(np.float32)[0]) - 8.45834) < 1e-4
+    # test/argreduce.test.ts:15-44: first index on ties, negatives, all equal, row-wise
+    for row, want in (([3, 5, 5, 2, 5, 1], 1), ([-10, -5, -20, -5, -15], 1), ([1, 1, 1, 1, 1], 0)):
+        _, _, am = _program(P.softmax_lse_argmax_program(1, len(row)), [np.array([row], np.float32), P.argmax_iota(len(row))])
+        assert am.view(np.int32).tolist() == [want]
+    _, _, am = _program(P.softmax_lse_argmax_program(3, 3), [np.array([[1, 2, 3], [6, 5, 4], [7, 8, 9]], np.float32), P.argmax_iota(3)])
+    assert am.view(np.int32).tolist() == [2, 0, 2]
+
+
+def test_small_matmul_known_answers():
+    from jax_js_b200 import programs as P
+    # test/numpy.test.ts:1518-1550: 2 x 2 and 2 x 3 products, exact
+    k = P.dot_kernel(2, 2, 2)
+    assert oracle.run_kernel(k, [f32(1, 2, 3, 4), f32(5, 6, 7, 8)]).tolist() == [19, 22, 43, 50]
+    k = P.dot_kernel(2, 2, 3)
+    assert oracle.run_kernel(k, [f32(1, 2, 3, 4, 5, 6), f32(7, 8, 9, 10, 11, 12)]).tolist() == [58, 64, 139, 154]
+    # batched 3 x 3 (:1552-1580) against numpy, and a fused bias + ReLU epilogue (:1582-1608)
+    a = np.arange(1, 19, dtype=np.float32).reshape(2, 3, 3)
+    got = oracle.run_kernel(P.dot_kernel(3, 3, 3, batch=2), [a, a]).reshape(2, 3, 3)
+    assert np.array_equal(got, np.einsum("bij,bjk->bik", a, a))
+    x, w, b = f32(1, -2, 3, -4).reshape(2, 2), f32(1, 2, 3, 4).reshape(2, 2), f32(-20, 1)
+    got = oracle.run_kernel(P.dot_kernel(2, 2, 2, bias=True, relu=True), [x, w, b]).reshape(2, 2)
+    assert np.array_equal(got, np.maximum(x @ w + b, 0))
+
+
+def test_adam_first_steps_known_answers():
+    """optax.adam (packages/optax/src/transform.ts:29-69): with g constant the bias-corrected update is
+    -lr * g / (|g| + eps) at every step, so p_t = p_0 - t * lr * sign(g) to within eps/|g|."""
+    from jax_js_b200 import mlp
+    from oracle_backend import OracleBackend
+    be = OracleBackend()
+    prog = mlp.adam_program([4], ["w"], lr=1e-3)
+    p, grad = f32(1, -2, 0.5, 3), f32(0.1, -0.2, 4.0, -1e-3)
+    state = [be.put(np.zeros(1, np.uint32)), be.put(p), be.put(grad), be.put(np.zeros(4, np.float32)), be.put(np.zeros(4, np.float32))]
+    for t in range(1, 4):
+        cnt, pn, mu, nu = prog.execute(be, state)
+        assert be.get(cnt, "uint32")[0] == t
+        np.testing.assert_allclose(be.get(pn, "float32"), p - t * 1e-3 * np.sign(grad), rtol=0, atol=5e-7 * t)   # a few float32 ulps of p per step
+        np.testing.assert_allclose(be.get(mu, "float32"), (1 - 0.9 ** t) * grad, rtol=2e-6)
+        np.testing.assert_allclose(be.get(nu, "float32"), (1 - 0.999 ** t) * grad * grad, rtol=2e-6)
+        state = [cnt, pn, state[2], mu, nu]
