@@ -16,12 +16,16 @@
 //              only reference semantics that exists for float16
 //              (translation.ts:558-586 rejects it).
 //
-// Sort / Argsort follow src/routine.ts:185-214.
+// Routines follow src/routine.ts: Sort / Argsort :185-214, Scatter :226-296, TriangularSolve
+// :298-338, Cholesky :340-366, LU :368-432, JacobiEigh :434-541, Fft :543-624 (double
+// intermediates, one rounding per store, as JavaScript numbers over typed arrays behave).
 //
 // Parity pins: the known-answer vectors of the reference's own tests
 // (src/backend/backend.test.ts, src/alu.test.ts, src/backend/wasm/builtins.test.ts,
-// test/numpy.test.ts sort/argsort) are replayed against this file by
-// tests/test_oracle_golden.py.  The reference itself cannot be executed in the build
+// test/numpy.test.ts sort/argsort/matmul, test/nn.test.ts, test/argreduce.test.ts,
+// test/lax-linalg.test.ts, test/numpy-fft.test.ts) are replayed against this file by
+// tests/test_oracle_golden.py and the CPU halves of tests/test_scatter.py and
+// tests/test_linalg.py.  The reference itself cannot be executed in the build
 // container (no JavaScript or WebAssembly runtime), so the pins are those vectors.
 #include <algorithm>
 #include <cmath>
