@@ -903,7 +903,8 @@ struct Builder {
     const int e = dtype_bytes(g.dtA);
     const int VX = 16 / e;                                   // k elements per 128-bit load
     if (g.K % VX || (g.sAm * e) % 16 || (g.offA * e) % 16 || g.sAm <= 0) return false;
-    const int64_t smem = g.N * g.K * 4;
+    const int64_t pitch = g.K;
+    const int64_t smem = g.N * pitch * 4;
     if (smem > 160 * 1024) return false;
     p.skeleton = SK_REDUCE_ROW;
     p.gemm = g;
@@ -913,15 +914,17 @@ struct Builder {
     const int64_t blocks = (g.M + ROWS - 1) / ROWS;
     std::ostringstream os;
     os << header();
-    os << "#define GM " << g.M << "\n#define GN " << g.N << "\n#define GK " << g.K << "\n#define VX " << VX << "\n";
+    os << "#define GM " << g.M << "\n#define GN " << g.N << "\n#define GK " << g.K << "\n#define VX " << VX << "\n#define BP " << pitch << "\n";
     os << "#define OFFA " << g.offA << "LL\n#define SAM " << g.sAm << "LL\n";
     os << "#define OFFB " << g.offB << "LL\n#define SBN " << g.sBn << "LL\n#define SBK " << g.sBk << "LL\n";
     os << "typedef " << ptype(g.dtA) << " TA;\ntypedef " << ptype(g.dtB) << " TB;\n";
     os << "extern \"C\" __global__ void __launch_bounds__(" << T << ") jx_dot_skinny(" << params() << ") {\n";
-    os << "  extern __shared__ __align__(16) float Bs[];   // [GN][GK]\n";
+    os << "  extern __shared__ __align__(16) float Bs[];   // [GN][BP]\n";
     os << "  const TA* A = (const TA*)p" << g.gidA << " + OFFA;\n  const TB* B = (const TB*)p" << g.gidB << " + OFFB;\n";
+    // linear, conflict-free stores; the loads of a [K, N] operand are N elements apart (reading it in
+    // memory order and transposing through padded rows measured slower: 35 us against 29 at 8192 rows)
     os << "  for (int i = threadIdx.x; i < GN * GK; i += " << T << ") {\n    const int n = i / GK, kk = i - n * GK;\n";
-    os << "    Bs[i] = " << from_storage(g.dtB, "B[(i64)n * SBN + (i64)kk * SBK]") << ";\n  }\n  __syncthreads();\n";
+    os << "    Bs[n * BP + kk] = " << from_storage(g.dtB, "B[(i64)n * SBN + (i64)kk * SBK]") << ";\n  }\n  __syncthreads();\n";
     os << "  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;\n";
     os << "  for (int blk = blockIdx.x; blk < " << blocks << "; blk += gridDim.x) {\n";
     os << "    const int m0 = blk * " << ROWS << " + warp * " << R << ";\n";
@@ -930,7 +933,7 @@ struct Builder {
     os << "      jx_pack<TA, VX> x[" << R << "];\n      #pragma unroll\n      for (int r = 0; r < " << R << "; r++) {\n";
     os << "        const int m = (m0 + r < GM) ? m0 + r : GM - 1;\n        jx_load(x[r], A + (i64)m * SAM + k0);\n      }\n";
     os << "      #pragma unroll\n      for (int n = 0; n < GN; n++) {\n        #pragma unroll\n        for (int v = 0; v < VX; v += 4) {\n";
-    os << "          const float4 y = *reinterpret_cast<const float4*>(&Bs[n * GK + k0 + v]);\n";
+    os << "          const float4 y = *reinterpret_cast<const float4*>(&Bs[n * BP + k0 + v]);\n";
     os << "          #pragma unroll\n          for (int r = 0; r < " << R << "; r++) {\n";
     os << "            acc[r][n] = fmaf(" << from_storage(g.dtA, "x[r].e[v]") << ", y.x, acc[r][n]);\n";
     os << "            acc[r][n] = fmaf(" << from_storage(g.dtA, "x[r].e[v + 1]") << ", y.y, acc[r][n]);\n";
@@ -998,7 +1001,7 @@ struct Builder {
     const int e = dtype_bytes(g.dtA);
     if (g.sAm != 1 || g.M % 4 || (g.offA * e) % (4 * e) || (g.sAk * e) % (4 * e) || g.N > 16) return false;
     const int T = 256, U = 4;
-    const int TX = g.M / 4 >= 64 ? 64 : 32, TY = T / TX;
+    const int TX = 32, TY = T / TX;   // 128 rows of m per CTA: more column blocks, fewer splits for the last CTA to fold
     const int NP = (int)((g.N + 3) / 4 * 4);
     const int64_t gx = (g.M / 4 + TX - 1) / TX;
     int64_t splits = std::max<int64_t>(1, ((int64_t)opt.sm_count * 2 + gx - 1) / gx);
