@@ -171,10 +171,11 @@ def mlp_grad_program(batch: int, dims: Sequence[int], *, global_batch: int | Non
 ADAM_B1, ADAM_B2, ADAM_EPS = 0.9, 0.999, 1e-8
 
 
-def adam_program(sizes: Sequence[int], names: Sequence[str], lr: float = 1e-3) -> JitProgram:
+def adam_program(sizes: Sequence[int], names: Sequence[str], lr: float = 1e-3, order: Sequence[int] | None = None) -> JitProgram:
     """`optax.adam(lr)` update + `applyUpdates` over the parameter leaves.
 
     Inputs: count u32[1], then p, g, mu, nu per leaf.  Outputs: count', then p', mu', nu' per leaf.
+    `order` lists the leaves in the order their (mutually independent) kernels are dispatched.
     """
     ins, outs = ["count"], ["count_new"]
     for n in names:
@@ -190,7 +191,8 @@ def adam_program(sizes: Sequence[int], names: Sequence[str], lr: float = 1e-3) -
 
     p.run("c1", correction(ADAM_B1), ["count_new"])
     p.run("c2", correction(ADAM_B2), ["count_new"])
-    for n, size in zip(names, sizes):
+    for leaf in (range(len(names)) if order is None else order):
+        n, size = names[leaf], sizes[leaf]
         g, mu, nu = _ld(0, size, _g), _ld(1, size, _g), _ld(1, size, _g)
         p.run(f"mu_{n}_new", Kernel(2, size, AluExp.add(AluExp.mul(g, _f(1 - ADAM_B1)), AluExp.mul(mu, _f(ADAM_B1)))),
               [f"g_{n}", f"mu_{n}"])
@@ -234,7 +236,9 @@ class MlpTrainer:
         self.names = param_order(len(dims) - 1)
         self.sizes = leaf_sizes(dims)
         self.grad = mlp_grad_program(local_batch, dims, global_batch=global_batch)
-        self.adam = adam_program(self.sizes, self.names, lr)
+        # leaves of the last layer first: the first layer's gradients are the last to arrive, and
+        # with overlapped sums theirs is still in flight while the other leaves are updated
+        self.adam = adam_program(self.sizes, self.names, lr, order=list(reversed(range(len(self.names)))))
         self.grad.prepare(backend)
         self.adam.prepare(backend)
         self.allreduce = allreduce if allreduce is not None else backend.allreduce_sum_f32
@@ -262,14 +266,37 @@ class MlpTrainer:
             def on_output(name, slot):
                 ready.append(slot)
                 if name.startswith("db"):        # a layer's last leaf: dW and db go out together
+                    if name == "db1":
+                        # everything summed so far is waited for here; the first layer's own sum, begun
+                        # next, is only waited for by the Adam kernels that read it (`_adam`)
+                        be.comm_join()
+                        self._tail = True
                     be.allreduce_sum_f32_async(ready)
                     ready.clear()
 
+            self._tail = False
             outs = self.grad.execute(be, ins, on_output)
             if ready:
                 be.allreduce_sum_f32_async(ready)
-            be.comm_join()
+            if not self._tail:
+                be.comm_join()
         return outs[0], list(outs[1:])
+
+    def _adam(self, ins, out_slots=None):
+        """The Adam program; joins a first-layer gradient sum still in flight just before its first reader."""
+        be = self.be
+        first_layer = {f"g_{self.names[0]}", f"g_{self.names[1]}"}
+
+        def before_step(step):
+            if self._tail and first_layer.intersection(step.inputs):
+                be.comm_join()
+                self._tail = False
+
+        new = self.adam.execute(be, ins, out_slots=out_slots, before_step=before_step if getattr(self, "_tail", False) else None)
+        if getattr(self, "_tail", False):
+            be.comm_join()
+            self._tail = False
+        return new
 
     def _state(self):
         return [self.count] + [s for i in range(len(self.names)) for s in (self.params[i], self.mu[i], self.nu[i])]
@@ -299,7 +326,7 @@ class MlpTrainer:
                 ins = [src[0]]
                 for i in range(len(self.names)):
                     ins += [src[1 + 3 * i], grads[i], src[2 + 3 * i], src[3 + 3 * i]]
-                self.adam.execute(be, ins, out_slots=dict(zip(out_names, dst)))
+                self._adam(ins, out_slots=dict(zip(out_names, dst)))
                 for s in grads:
                     be.dec_ref(s)
             except Exception:
@@ -328,7 +355,7 @@ class MlpTrainer:
         ins = [self.count]
         for i in range(len(self.names)):
             ins += [self.params[i], grads[i], self.mu[i], self.nu[i]]
-        new = self.adam.execute(be, ins)
+        new = self._adam(ins)
         for s in [self.count] + self.params + self.mu + self.nu + grads:
             be.dec_ref(s)
         self.count = new[0]

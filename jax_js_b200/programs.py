@@ -161,12 +161,13 @@ class JitProgram:
             if s.kind == "execute" and id(s) not in self._exes:
                 self._exes[id(s)] = backend.prepare_kernel_sync(s.kernel)
 
-    def execute(self, backend, slots: Sequence[int], on_output=None, out_slots=None) -> list:
+    def execute(self, backend, slots: Sequence[int], on_output=None, out_slots=None, before_step=None) -> list:
         """Replays the steps; `slots` are the input slots (not consumed).  Returns output slots
         with reference count 1, owned by the caller.  `on_output(name, slot)` is called right after
         the kernel that produces a program output has been dispatched.  `out_slots` maps names of
         program outputs to slots the caller already owns: those outputs are written there instead of
-        into fresh slots (they must not alias an input of the kernel that writes them)."""
+        into fresh slots (they must not alias an input of the kernel that writes them).
+        `before_step(step)` is called before each kernel is dispatched."""
         self.prepare(backend)
         env = dict(zip(self.inputs, slots))
         owned = set()
@@ -178,6 +179,8 @@ class JitProgram:
                 env[s.name] = backend.malloc(s.nbytes)
                 owned.add(s.name)
             elif s.kind == "execute":
+                if before_step is not None:
+                    before_step(s)
                 backend.dispatch(self._exes[id(s)], [env[n] for n in s.inputs], [env[s.name]])
                 if on_output is not None and s.name in self.outputs:
                     on_output(s.name, env[s.name])
