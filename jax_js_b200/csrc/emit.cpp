@@ -1184,7 +1184,25 @@ struct Builder {
         p.gemm = g;
         account(p);
         p.algo_flops = 2.0 * g.M * g.N * g.K * g.batch;
-        if (plan_gemm_tc(k, g, opt, p, epilogue_body("      ", "JX_DST"), params())) return p;
+        // the tensor-core epilogue hands a thread 16 consecutive outputs of one row
+        std::string body, pre;
+        if (g.N % 16 == 0) {
+          std::map<size_t, std::string> ov;
+          std::ostringstream decl, fetch, bos;
+          std::vector<std::string> bnames(k.epi.size()), en(k.epi.size());
+          std::vector<char> eall(k.epi.size(), 1);
+          Env env;
+          env.prefix = "e";
+          preload(decl, fetch, k.epi, an_epi, eall, 0, 16, env, "g0", "", "", "j", ov, bnames, "          ");
+          pre = decl.str() + fetch.str();
+          env.load_override = &ov;
+          emit_nodes(bos, k.epi, an_epi, en, eall, env, "      ");
+          bos << "      JX_DST = " << to_storage(out_dt, en.back()) << ";\n";
+          body = bos.str();
+        } else {
+          body = epilogue_body("      ", "JX_DST");
+        }
+        if (plan_gemm_tc(k, g, opt, p, body, params(), pre)) return p;
       }
       return gemm_ffma(g);
     }

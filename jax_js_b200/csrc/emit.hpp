@@ -84,6 +84,7 @@ Plan make_plan(const KernelIR& k, const Options& opt);
 
 // Implemented in gemm_tc.cpp: rewrites `plan` to the tcgen05 skeleton when `g` qualifies.
 bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan& plan,
-                  const std::string& epilogue_body, const std::string& params_decl);
+                  const std::string& epilogue_body, const std::string& params_decl,
+                  const std::string& epilogue_preload = std::string());
 
 }  // namespace jaxcuda

@@ -288,6 +288,8 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
         const int n0 = n_blk * BN + c * 16;
         if (m < GM && n0 < GN) {
           __align__(16) JX_OUT_T res[16];
+          const int g0 = (int)(((i64)b * GM + m) * GN + n0);
+          JX_EPI_PRELOAD
           #pragma unroll
           for (int j = 0; j < 16; j++) {
             const int n = n0 + j;
@@ -373,7 +375,7 @@ int64_t pad64(int64_t n) { return (n + 63) / 64 * 64; }  // planes start on 256-
 }  // namespace
 
 bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan& plan,
-                  const std::string& epilogue_body, const std::string& params_decl) {
+                  const std::string& epilogue_body, const std::string& params_decl, const std::string& epilogue_preload) {
   if (g.dtA != g.dtB) return false;
   const int kind = g.dtA == JAXCUDA_F16 ? 1 : g.dtA == JAXCUDA_F32 ? 2 : 0;
   if (!kind) return false;
@@ -429,6 +431,11 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
   std::string escaped;
   for (char c : body) { if (c == '\n') escaped += " \\\n"; else escaped += c; }
   os << "#define JX_EPILOGUE " << escaped << "\n";
+  // loads of the epilogue that are contiguous over a thread's 16 outputs, fetched as 128-bit vectors
+  // ahead of the per-element code (empty when there are none or rows are not a multiple of 16 wide)
+  std::string pre;
+  for (char c : epilogue_preload) { if (c == '\n') pre += " \\\n"; else pre += c; }
+  os << "#define JX_EPI_PRELOAD " << pre << "\n";
   os << kTcSource;
   plan.source = os.str();
   plan.skeleton = SK_GEMM_TC;
