@@ -18,7 +18,7 @@ The line also carries: `roofline` for the dominant kernel (timed with CUDA event
 timed region, against MEASURED_PEAKS.json), `e2e` (same program with the host->device copy
 of X from pinned memory and the device->host read of all results inside every step),
 `cpu_baseline` (the CPU oracle, a restatement of the reference's Wasm backend, on a bounded
-sample of rows), `configs` (the other BASELINE configs, one figure each) and `clocks`.
+sample of rows), `configs` (the other benchmark configurations, one figure each) and `clocks`.
 """
 from __future__ import annotations
 
@@ -115,7 +115,7 @@ def time_kernel(be, kernel, arrays, iters=20, warmup=3, copies=1):
 
 
 def other_configs(be, peaks, iters=None):
-    """One figure for each remaining BASELINE config kernel (resident inputs, CUDA events)."""
+    """One figure for each remaining benchmark configuration (resident inputs, CUDA events)."""
     from jax_js_b200 import DType
     from jax_js_b200 import programs as P
     rng = np.random.default_rng(0)

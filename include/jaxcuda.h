@@ -3,7 +3,7 @@
  *
  * Each entry point stands behind one method of the reference's `Backend` interface
  * (src/backend.ts:158-211); the TypeScript class that implements that interface calls
- * these through a Node addon.  Plain pointers and sizes only.
+ * these through a Node addon (jax_js_b200/ts/addon.cc).  Plain pointers and sizes only.
  *
  * Every call returns a jaxcuda_status; on failure jaxcuda_last_error(ctx) holds a
  * message (NVRTC logs and the generated source included for compile errors, as the

@@ -1,6 +1,6 @@
 """Parity of the CUDA skeletons with the CPU oracle on seeded inputs, through the C ABI.
 
-Bars (BASELINE north_star): bit-exact for integer, comparison, argmax and sort outputs;
+Bars: bit-exact for integer, comparison, argmax and sort outputs;
 within 1e-5 relative for f32 elementwise and reduce kernels; f32 GEMM within 1e-4 and f16
 GEMM/matvec within 2e-3 per element after normalising by K.  Where a result can cancel to
 nearly zero (sums, dot products) "relative" is taken against the sum of absolute terms.
