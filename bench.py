@@ -2,6 +2,7 @@
 """Benchmark of the cuda backend's hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl cuda|reference]
+                    [--skip-extras | --only-configs | --only-mlp]
 
 Headline workload (`config.workload` = "softmax_lse_argmax_f32_8192x4096"): one jit program
 computing softmax, log-sum-exp and argmax over the last axis of f32 X[8192, 4096] ~ N(0, 1):
@@ -16,7 +17,8 @@ gradients is reported beside it under "mlp_train".
 
 The line also carries: `roofline` for the dominant kernel (timed with CUDA events inside the
 timed region, against MEASURED_PEAKS.json), `e2e` (same program with the host->device copy
-of X from pinned memory and the device->host read of all results inside every step),
+of X from pinned memory and the device->host read of all results inside every step; the reads
+are the Promise form of Backend.read, so a step's read-back overlaps the next step's upload),
 `cpu_baseline` (the CPU oracle, a restatement of the reference's Wasm backend, on a bounded
 sample of rows), `configs` (the other benchmark configurations, one figure each) and `clocks`.
 """
