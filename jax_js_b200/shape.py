@@ -1,11 +1,11 @@
 """Lazy views lowered to flat index expressions.
 
 Host-side mirror of the part of src/shape.ts the backend boundary depends on:
-a single strided/masked `View` (shape.ts:168), its lowering to an index and a
-validity expression (shape.ts:277-300 `toAluExp`), `unravelAlu` (shape.ts:631)
-and `accessorGlobal` (src/alu.ts:1664-1679).  Multi-view composition
-(shape.ts:312, :648) stays on the reference's TypeScript side: kernels reach
-the backend already lowered.
+a strided/masked `View` (shape.ts:168), its lowering to an index and a validity
+expression (shape.ts:277-300 `toAluExp`), a `ShapeTracker` as a stack of views
+(shape.ts:312: a movement that one view cannot express, such as reshaping a
+permuted or padded array, starts a new view over the flattened previous one),
+`unravelAlu` (shape.ts:631) and `accessorGlobal` (src/alu.ts:1664-1679).
 """
 from __future__ import annotations
 
@@ -22,8 +22,8 @@ def _contiguous_strides(shape: Sequence[int]) -> tuple:
     return tuple(reversed(strides))
 
 
-class ShapeTracker:
-    """One `View`: shape, strides, offset and an optional per-axis valid mask."""
+class View:
+    """Shape, strides, offset and an optional per-axis valid mask."""
 
     def __init__(self, shape, strides, offset=0, mask=None):
         self.shape = tuple(int(s) for s in shape)
@@ -32,8 +32,8 @@ class ShapeTracker:
         self.mask = tuple(mask) if mask is not None else None
 
     @staticmethod
-    def from_shape(shape: Sequence[int]) -> "ShapeTracker":
-        return ShapeTracker(shape, _contiguous_strides(shape))
+    def from_shape(shape: Sequence[int]) -> "View":
+        return View(shape, _contiguous_strides(shape))
 
     @property
     def ndim(self) -> int:
@@ -51,11 +51,11 @@ class ShapeTracker:
             hi += max(ends)
         return (lo, hi + 1)
 
-    def permute(self, axes: Sequence[int]) -> "ShapeTracker":
-        return ShapeTracker([self.shape[a] for a in axes], [self.strides[a] for a in axes],
+    def permute(self, axes: Sequence[int]) -> "View":
+        return View([self.shape[a] for a in axes], [self.strides[a] for a in axes],
                             self.offset, [self.mask[a] for a in axes] if self.mask else None)
 
-    def expand(self, shape: Sequence[int]) -> "ShapeTracker":
+    def expand(self, shape: Sequence[int]) -> "View":
         strides, mask = [], []
         for i, (old, new) in enumerate(zip(self.shape, shape)):
             if old != new and old != 1:
@@ -63,9 +63,9 @@ class ShapeTracker:
             strides.append(self.strides[i] if old == new else 0)
             if self.mask:
                 mask.append(self.mask[i] if old == new else (0, new))
-        return ShapeTracker(shape, strides, self.offset, mask if self.mask else None)
+        return View(shape, strides, self.offset, mask if self.mask else None)
 
-    def flip(self, axes: Sequence[bool]) -> "ShapeTracker":
+    def flip(self, axes: Sequence[bool]) -> "View":
         strides, offset, mask = list(self.strides), self.offset, list(self.mask) if self.mask else None
         for i, f in enumerate(axes):
             if f:
@@ -74,18 +74,18 @@ class ShapeTracker:
                 if mask:
                     a, b = mask[i]
                     mask[i] = (self.shape[i] - b, self.shape[i] - a)
-        return ShapeTracker(self.shape, strides, offset, mask)
+        return View(self.shape, strides, offset, mask)
 
-    def pad(self, widths: Sequence[tuple]) -> "ShapeTracker":
+    def pad(self, widths: Sequence[tuple]) -> "View":
         shape, offset, mask = [], self.offset, []
         for i, (lo, hi) in enumerate(widths):
             a, b = (self.mask[i] if self.mask else (0, self.shape[i]))
             shape.append(self.shape[i] + lo + hi)
             offset -= lo * self.strides[i]
             mask.append((a + lo, b + lo))
-        return ShapeTracker(shape, self.strides, offset, mask)
+        return View(shape, self.strides, offset, mask)
 
-    def shrink(self, ranges: Sequence[tuple]) -> "ShapeTracker":
+    def shrink(self, ranges: Sequence[tuple]) -> "View":
         shape, offset, mask = [], self.offset, []
         for i, (lo, hi) in enumerate(ranges):
             shape.append(hi - lo)
@@ -93,9 +93,9 @@ class ShapeTracker:
             if self.mask:
                 a, b = self.mask[i]
                 mask.append((max(a - lo, 0), min(b - lo, hi - lo)))
-        return ShapeTracker(shape, self.strides, offset, mask if self.mask else None)
+        return View(shape, self.strides, offset, mask if self.mask else None)
 
-    def reshape(self, shape: Sequence[int]) -> "ShapeTracker":
+    def reshape(self, shape: Sequence[int]) -> "View":
         """Reshape without copying; only the cases one view can express
         (merge/split of axes whose strides nest, and unit axes)."""
         shape = tuple(int(s) for s in shape)
@@ -131,7 +131,7 @@ class ShapeTracker:
                 i = j + 1
         if i != len(old):
             raise ValueError(f"cannot reshape {self.shape} to {shape}")
-        return ShapeTracker(shape, strides, self.offset)
+        return View(shape, strides, self.offset)
 
     def to_alu_exp(self, idxs: Sequence[AluExp]) -> tuple:
         """(flat index, valid) for the given per-axis indices (shape.ts:277-300)."""
@@ -147,6 +147,88 @@ class ShapeTracker:
                     vexpr = AluExp.mul(AluExp.cmplt(idx, AluExp.i32(a)).not_(), vexpr)
                 if b != self.shape[i]:
                     vexpr = AluExp.mul(AluExp.cmplt(idx, AluExp.i32(b)), vexpr)
+        return iexpr, vexpr
+
+
+class ShapeTracker:
+    """A stack of views (shape.ts:312-420).  The first view addresses the buffer; every later one
+    indexes the flattened shape of the view before it.  Movement operations act on the last view;
+    a reshape that the last view cannot express pushes a contiguous view of the new shape."""
+
+    def __init__(self, shape=None, strides=None, offset=0, mask=None, views=None):
+        self.views = list(views) if views is not None else [View(shape, strides, offset, mask)]
+
+    @staticmethod
+    def from_shape(shape: Sequence[int]) -> "ShapeTracker":
+        return ShapeTracker(views=[View.from_shape(shape)])
+
+    # the last view is what the tracker looks like from outside
+    @property
+    def shape(self) -> tuple:
+        return self.views[-1].shape
+
+    @property
+    def strides(self) -> tuple:
+        return self.views[-1].strides
+
+    @property
+    def offset(self) -> int:
+        return self.views[-1].offset
+
+    @property
+    def mask(self):
+        return self.views[-1].mask
+
+    @property
+    def ndim(self) -> int:
+        return len(self.shape)
+
+    def data_range(self) -> tuple:
+        """Flat offsets of the buffer that can be touched: only the first view addresses it."""
+        if len(self.views) == 1:
+            return self.views[0].data_range()
+        lo, hi = self.views[0].data_range()
+        return (min(lo, 0), hi)
+
+    def _with_last(self, view: View) -> "ShapeTracker":
+        return ShapeTracker(views=self.views[:-1] + [view])
+
+    def permute(self, axes: Sequence[int]) -> "ShapeTracker":
+        return self._with_last(self.views[-1].permute(axes))
+
+    def expand(self, shape: Sequence[int]) -> "ShapeTracker":
+        return self._with_last(self.views[-1].expand(shape))
+
+    def flip(self, axes: Sequence[bool]) -> "ShapeTracker":
+        return self._with_last(self.views[-1].flip(axes))
+
+    def pad(self, widths: Sequence[tuple]) -> "ShapeTracker":
+        return self._with_last(self.views[-1].pad(widths))
+
+    def shrink(self, ranges: Sequence[tuple]) -> "ShapeTracker":
+        return self._with_last(self.views[-1].shrink(ranges))
+
+    def reshape(self, shape: Sequence[int]) -> "ShapeTracker":
+        shape = tuple(int(d) for d in shape)
+        size = 1
+        for d in self.shape:
+            size *= d
+        new = 1
+        for d in shape:
+            new *= d
+        if new != size:
+            raise ValueError(f"cannot reshape {self.shape} to {shape}")
+        try:
+            return self._with_last(self.views[-1].reshape(shape))
+        except ValueError:
+            return ShapeTracker(views=self.views + [View.from_shape(shape)])
+
+    def to_alu_exp(self, idxs: Sequence[AluExp]) -> tuple:
+        """(flat index into the buffer, valid) for per-axis indices of the last view (shape.ts:404-420)."""
+        iexpr, vexpr = self.views[-1].to_alu_exp(idxs)
+        for view in reversed(self.views[:-1]):
+            iexpr, valid = view.to_alu_exp(unravel_alu(view.shape, iexpr))
+            vexpr = AluExp.mul(vexpr, valid)
         return iexpr, vexpr
 
 

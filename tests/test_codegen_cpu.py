@@ -8,7 +8,7 @@ from pathlib import Path
 import numpy as np
 import pytest
 
-from jax_js_b200 import AluExp, AluOp, AluVar, DType, Kernel, Reduction, ShapeTracker, accessor_global
+from jax_js_b200 import AluExp, AluOp, AluVar, DType, Kernel, Reduction, ShapeTracker, accessor_global, unravel_alu
 from jax_js_b200 import mlp
 from jax_js_b200 import programs as P
 from jax_js_b200.alu import NODE_WORDS, WIRE_MAGIC
@@ -131,3 +131,56 @@ def test_shape_tracker_views_lower_to_expected_indices():
     assert padded.shape == (6,) and padded.data_range() == (0, 3)
     e = accessor_global(F32, 0, padded, [g])
     assert e.op == AluOp.Where
+
+
+def test_shape_tracker_movement_sequences_match_numpy():
+    """Random chains of permute / expand / flip / pad / shrink / reshape, including the ones that
+    need a second view (reshape after permute, after pad, after flip), lowered to an index and a
+    validity expression and evaluated by the oracle, against the same chain applied with numpy."""
+    import oracle
+    rng = np.random.default_rng(7)
+    multi = 0
+    for trial in range(300):
+        shape = [int(d) for d in rng.integers(1, 5, rng.integers(1, 4))]
+        base = rng.standard_normal(shape).astype(np.float32)
+        base[base == 0] = 1.0                                   # zeros mark padding below
+        arr, st = base, ShapeTracker.from_shape(shape)
+        for _ in range(int(rng.integers(1, 6))):
+            op = rng.choice(["permute", "expand", "flip", "pad", "shrink", "reshape", "reshape"])
+            nd = arr.ndim
+            if op == "permute":
+                axes = [int(a) for a in rng.permutation(nd)]
+                arr, st = arr.transpose(axes), st.permute(axes)
+            elif op == "expand":
+                arr = arr.reshape((1,) + arr.shape)
+                st = st.reshape((1,) + st.shape)
+                k = int(rng.integers(1, 4))
+                arr, st = np.broadcast_to(arr, (k,) + arr.shape[1:]), st.expand((k,) + st.shape[1:])
+            elif op == "flip":
+                f = [bool(b) for b in rng.integers(0, 2, nd)]
+                arr = arr[tuple(slice(None, None, -1) if b else slice(None) for b in f)]
+                st = st.flip(f)
+            elif op == "pad":
+                w = [(int(a), int(b)) for a, b in rng.integers(0, 3, (nd, 2))]
+                arr, st = np.pad(arr, w), st.pad(w)
+            elif op == "shrink":
+                r = []
+                for d in arr.shape:
+                    lo = int(rng.integers(0, d))
+                    r.append((lo, int(rng.integers(lo + 1, d + 1))))
+                arr, st = arr[tuple(slice(a, b) for a, b in r)], st.shrink(r)
+            else:
+                size = arr.size
+                divs = [d for d in range(1, size + 1) if size % d == 0]
+                a = int(rng.choice(divs))
+                b = int(rng.choice([d for d in divs if (size // a) % d == 0]))
+                new = [a, b, size // (a * b)]
+                arr, st = np.ascontiguousarray(arr).reshape(new), st.reshape(new)
+            assert tuple(st.shape) == arr.shape
+            if arr.size > 4096:
+                break
+        multi += len(st.views) > 1
+        k = Kernel(1, arr.size, accessor_global(DType.Float32, 0, st, unravel_alu(st.shape, AluVar.gidx)))
+        got = oracle.run_kernel(k, [base.reshape(-1)])
+        assert np.array_equal(got, np.ascontiguousarray(arr).reshape(-1)), (trial, [v.shape for v in st.views])
+    assert multi >= 30, multi     # the multi-view path was exercised
