@@ -162,7 +162,11 @@ export class CudaBackend implements Backend {
       return new Executable(routine, this.native.prepareRoutine(this.ctx, routine.name, routine.type,
                                                                 JSON.stringify(routine.params ?? {})));
     } catch {
-      throw new UnsupportedRoutineError(routine.name, this.type);
+      // an unknown routine name (src/backend.ts:236-240); anything else is a shape or dtype the
+      // reference's own routine rejects, with its message (src/routine.ts:305-313, :341-346)
+      const msg = this.native.lastError(this.ctx);
+      if (/^routine '.*' is not supported in cuda backend/.test(msg)) throw new UnsupportedRoutineError(routine.name, this.type);
+      throw new Error(msg);
     }
   }
 
