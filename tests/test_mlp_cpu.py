@@ -146,3 +146,26 @@ def test_two_gloo_ranks_train_like_one(tmp_path):
     np.testing.assert_allclose(got["losses"], losses, rtol=1e-5)
     for i, s in enumerate(tr.params):
         np.testing.assert_allclose(got[f"p{i}"], be.get(s, "float32"), rtol=1e-4, atol=1e-6)
+
+
+def test_step_list_hooks_and_caller_owned_outputs():
+    """`JitProgram.execute`: outputs written into slots the caller owns, and the two hooks (after a
+    program output is dispatched, before each kernel) fire in dispatch order."""
+    from jax_js_b200 import programs as P
+    be = OracleBackend()
+    rows, cols = 4, 6
+    x = np.arange(rows * cols, dtype=np.float32).reshape(rows, cols) / 7
+    prog = P.softmax_lse_argmax_program(rows, cols)
+    sx, si = be.put(x), be.put(P.argmax_iota(cols))
+    want = [be.slots[s][0].copy() for s in prog.execute(be, [sx, si])]
+    mine = {"lse": be.malloc(rows * 4), "argmax": be.malloc(rows * 4)}
+    events = []
+    outs = prog.execute(be, [sx, si], on_output=lambda name, slot: events.append(("out", name)),
+                        out_slots=mine, before_step=lambda step: events.append(("run", step.name)))
+    assert outs[1] == mine["lse"] and outs[2] == mine["argmax"] and outs[0] not in mine.values()
+    for got, w in zip(outs, want):
+        assert np.array_equal(be.slots[got][0], w)
+    runs = [n for kind, n in events if kind == "run"]
+    assert runs == ["m1", "u", "s", "softmax", "m2", "s2", "lse", "m3", "argmax"]
+    assert [n for kind, n in events if kind == "out"] == ["softmax", "lse", "argmax"]
+    assert events.index(("out", "softmax")) == events.index(("run", "softmax")) + 1
