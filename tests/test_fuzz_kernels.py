@@ -1,7 +1,9 @@
-"""Seeded random Kernels through the planner, the CUDA C emitter and NVRTC (no GPU needed), and
+"""Seeded random Kernels.  On CPU: through the planner, the CUDA C emitter and NVRTC (no GPU needed), and
 through the oracle: whatever expression the frontend could hand over must either compile for
 sm_100a or be refused with the reference's UnsupportedOpError wording, never produce source that
-does not compile; and the oracle must evaluate every accepted kernel."""
+does not compile; and the oracle must evaluate every accepted kernel.  On a GPU: the same kernels
+run through the C ABI and are compared with the oracle (integer chains bit-exact, float chains
+within the amplified single-op bar)."""
 import numpy as np
 import pytest
 
@@ -123,3 +125,50 @@ def test_random_kernel_compiles_or_is_refused_and_the_oracle_runs_it(seed):
     assert describe and 'extern "C" __global__' in source
     out = oracle.run_kernel(kernel, arrays, end=min(kernel.size, 256))
     assert out.shape == (kernel.size,)
+
+
+def _inputs_for(args, seed):
+    rng = np.random.default_rng(1000 + seed)
+    arrays = []
+    for dtype, length in args:
+        if dtype in (F32, F16):
+            arrays.append(rng.uniform(-2, 2, length).astype(np_dtype(dtype)))
+        elif dtype == BOOL:
+            arrays.append(rng.integers(0, 2, length).astype(np.int32))
+        else:
+            arrays.append(rng.integers(0, 50, length).astype(np_dtype(dtype)))
+    return arrays
+
+
+def _is_exact(kernel):
+    """Integer and Bool results that never pass through a float: bit-exact by construction."""
+    roots = [kernel.exp] + ([kernel.reduction.epilogue] if kernel.reduction else [])
+    return kernel.dtype in (I32, U32, BOOL) and all(e.dtype in (I32, U32, BOOL) for root in roots for e in root.toposort())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("seed", range(48))
+def test_random_kernel_matches_the_oracle_on_the_gpu(backend, seed):
+    from util import run_cuda
+    kernel, args = random_kernel(seed)
+    arrays = _inputs_for(args, seed)
+    got = run_cuda(backend, kernel, arrays)
+    want = oracle.run_kernel(kernel, arrays)
+    if _is_exact(kernel):
+        assert np.array_equal(got, want)
+        return
+    if kernel.dtype in (I32, U32, BOOL):
+        # an integer made from floats (casts, comparisons): a float within rounding of a boundary may
+        # land on either side; all but a sliver must agree
+        assert (got != want).mean() <= 0.01
+        return
+    got, want = got.astype(np.float64), want.astype(np.float64)
+    tame = np.isfinite(want) & (np.abs(want) < 1e30)
+    assert (np.isnan(got) == np.isnan(want))[np.abs(np.nan_to_num(want)) < 1e30].mean() >= 0.99
+    # float chains: 1e-4 of max(|want|, 1) (the bar for a single op is 1e-5; three nested ops and a
+    # reduction amplify it), for all but a sliver of elements (discontinuities: floor, casts, where)
+    tol = (2e-3 if kernel.dtype == F16 else 1e-4) * np.maximum(np.abs(want), 1.0)
+    if kernel.reduction is not None:
+        tol = tol * np.sqrt(kernel.reduction.size)
+    bad = tame & np.isfinite(got) & (np.abs(got - want) > tol)
+    assert bad.mean() <= 0.01, (bad.mean(), np.abs(got - want)[bad].max())
