@@ -172,3 +172,31 @@ def test_random_kernel_matches_the_oracle_on_the_gpu(backend, seed):
         tol = tol * np.sqrt(kernel.reduction.size)
     bad = tame & np.isfinite(got) & (np.abs(got - want) > tol)
     assert bad.mean() <= 0.01, (bad.mean(), np.abs(got - want)[bad].max())
+
+
+def _random_dot(seed):
+    from jax_js_b200 import programs as P
+    rng = np.random.default_rng(5000 + seed)
+    pick = lambda seq: seq[int(rng.integers(len(seq)))]
+    M = pick([1, 3, 10, 64, 65, 100, 128, 260, 784, 1000, 2048, 8192])
+    N = pick([1, 4, 10, 16, 64, 100, 128, 192, 512, 1028, 2048])
+    K = pick([1, 7, 10, 16, 33, 64, 256, 300, 784, 4096])
+    dtype = pick([F32, F32, F16])
+    kw = dict(a_layout=pick(["mk", "km"]), b_layout=pick(["kn", "nk"]), bias=bool(rng.integers(2)), relu=bool(rng.integers(2)))
+    if rng.random() < 0.2:
+        kw["batch"] = int(pick([2, 5]))
+    if rng.random() < 0.15:
+        kw["swap"] = True
+    return P.dot_kernel(M, N, K, dtype, **kw), (M, N, K, dtype, kw)
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_random_dot_shapes_plan_and_compile(seed):
+    """Every dot skeleton (tensor-core f16 / 3xTF32 with any tile width and operand majorness, FFMA,
+    the three skinny ones, plain reductions) over ragged and degenerate shapes: the generated source
+    must compile for sm_100a whatever the route."""
+    kernel, what = _random_dot(seed)
+    describe, source = check_kernel(kernel, compile=True)
+    assert describe.split()[0] in ("gemm-tcgen05", "gemm-ffma", "dot-skinny", "dot-skinny-t", "dot-small-k", "reduce-row",
+                                   "reduce-col"), (what, describe)
+    assert 'extern "C" __global__' in source
