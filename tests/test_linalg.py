@@ -66,6 +66,30 @@ def test_oracle_triangular_solve():
     np.testing.assert_allclose(np.einsum("cij,ctj->cti", a.astype(np.float64), x.astype(np.float64)), b, rtol=1e-4, atol=1e-5)
 
 
+def test_oracle_routines_against_lapack_in_float64():
+    """The restatements against independent implementations (LAPACK through numpy / scipy) in float64:
+    same pivoting rule as getrf (largest magnitude, first occurrence), same factors to rounding."""
+    import scipy.linalg as sl
+    rng = np.random.default_rng(21)
+    a = rng.standard_normal((60, 60))
+    lu, piv, perm = oracle.lu(a)
+    ref_lu, ref_piv = sl.lu_factor(a)
+    assert np.array_equal(piv, ref_piv)
+    np.testing.assert_allclose(lu, ref_lu, rtol=1e-10, atol=1e-12)
+    x = _spd(rng, 3, 40, np.float64)
+    np.testing.assert_allclose(oracle.cholesky(x), np.linalg.cholesky(x), rtol=1e-12, atol=1e-13)
+    u = np.triu(rng.standard_normal((50, 50))) + 8 * np.eye(50)
+    b = rng.standard_normal((7, 50))
+    np.testing.assert_allclose(oracle.triangular_solve(u, b), sl.solve_triangular(u, b.T).T, rtol=1e-11, atol=1e-12)
+    np.testing.assert_allclose(oracle.triangular_solve(u, b, unit_diagonal=True),
+                               sl.solve_triangular(u, b.T, unit_diagonal=True).T, rtol=1e-9, atol=1e-9)
+    s = _sym(rng, 2, 24, np.float64)
+    d, v = oracle.jacobi_eigh(s, max_sweeps=48, tolerance=1e-12)
+    full = np.tril(s) + np.tril(s, -1).transpose(0, 2, 1)
+    np.testing.assert_allclose(np.sort(np.diagonal(d, axis1=1, axis2=2)), np.linalg.eigvalsh(full), rtol=1e-9, atol=1e-9)
+    np.testing.assert_allclose(v.transpose(0, 2, 1) @ v, np.broadcast_to(np.eye(24), (2, 24, 24)), atol=1e-10)
+
+
 # ---- the CUDA routines against the oracle (GPU) ---------------------------------------------------
 
 def _run(backend, name, ins, out_shapes, out_dtypes, params=None):
