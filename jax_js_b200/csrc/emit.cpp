@@ -678,24 +678,7 @@ struct Builder {
       os << "  " << AT << "* parts = (" << AT << "*)((char*)scratch + " << counter_pad << ");\n";
       os << "  if (ty == 0 && active) {\n    " << AT << "* part = parts + (size_t)blockIdx.y * " << k.size << " + g0;\n";
       os << "    #pragma unroll\n    for (int u = 0; u < " << V << "; u++) part[u] = acc[u];\n  }\n";
-      os << "  __shared__ int last;\n  __threadfence();\n  __syncthreads();\n";
-      os << "  if (threadIdx.x == 0) last = atomicAdd((int*)scratch + blockIdx.x, 1) == " << splits - 1 << ";\n";
-      os << "  __syncthreads();\n  if (!last) return;\n  __threadfence();\n";
-      os << "  for (int o = threadIdx.x; o < " << TX * V << "; o += " << T << ") {\n";
-      os << "    const long long gl = (long long)blockIdx.x * " << TX * V << " + o;\n    if (gl >= " << k.size << "LL) break;\n";
-      os << "    const int gidx = (int)gl;\n    " << AT << " acc_u = " << identity_literal(k.red_op, k.red_dtype) << ";\n";
-      os << "    for (int s = 0; s < " << splits << "; s++) { const " << AT << " v = __ldcg(parts + (size_t)s * " << k.size
-         << " + gidx); acc_u = " << red("acc_u", "v") << "; }\n";
-      {
-        std::vector<std::string> en(k.epi.size());
-        std::vector<char> eall(k.epi.size(), 1);
-        Env ee;
-        ee.prefix = "e";
-        ee.acc = "acc_u";
-        emit_nodes(os, k.epi, an_epi, en, eall, ee, "    ");
-        os << "    out[gidx] = " << to_storage(out_dt, en.back()) << ";\n  }\n";
-      }
-      os << "  if (threadIdx.x == 0) ((int*)scratch)[blockIdx.x] = 0;\n";
+      emit_split_tail(os, splits, (int64_t)TX * V, T);
     } else {
       os << "  if (ty != 0 || !active) return;\n";
       os << "  #pragma unroll\n  for (int u = 0; u < " << V << "; u++) {\n    const int gidx = g0 + u;\n    const " << AT << " acc_u = acc[u];\n";
