@@ -438,6 +438,17 @@ struct Builder {
     os << indent << dst << " = " << to_storage(out_dt, names.back()) << ";\n";
   }
 
+  // The Kernel's epilogue for one output: expects `gidx` and the accumulator `acc_name` in scope.
+  void emit_epilogue(std::ostream& os, const std::string& indent, const std::string& acc_name, const std::string& dst) const {
+    std::vector<std::string> en(k.epi.size());
+    std::vector<char> eall(k.epi.size(), 1);
+    Env ee;
+    ee.prefix = "e";
+    ee.acc = acc_name;
+    emit_nodes(os, k.epi, an_epi, en, eall, ee, indent);
+    os << indent << dst << " = " << to_storage(out_dt, en.back()) << ";\n";
+  }
+
   void emit_finish_kernel(std::ostream& os, int splits) const {
     const char* AT = ctype(k.red_dtype);
     os << "extern \"C\" __global__ void __launch_bounds__(256) jx_finish(" << params() << ") {\n";
@@ -682,13 +693,8 @@ struct Builder {
     } else {
       os << "  if (ty != 0 || !active) return;\n";
       os << "  #pragma unroll\n  for (int u = 0; u < " << V << "; u++) {\n    const int gidx = g0 + u;\n    const " << AT << " acc_u = acc[u];\n";
-      std::vector<std::string> en(k.epi.size());
-      std::vector<char> eall(k.epi.size(), 1);
-      Env ee;
-      ee.prefix = "e";
-      ee.acc = "acc_u";
-      emit_nodes(os, k.epi, an_epi, en, eall, ee, "    ");
-      os << "    out[gidx] = " << to_storage(out_dt, en.back()) << ";\n  }\n";
+      emit_epilogue(os, "    ", "acc_u", "out[gidx]");
+      os << "  }\n";
     }
     os << "}\n";
     p.source = os.str();
@@ -929,15 +935,7 @@ struct Builder {
     os << "    #pragma unroll\n    for (int r = 0; r < " << R << "; r++) {\n      #pragma unroll\n      for (int n = 0; n < GN; n++) {\n";
     os << "        if (lane == ((r * GN + n) & 31) && m0 + r < GM) {\n";
     os << "          const int gidx = (m0 + r) * GN + n;\n          const float acc_v = acc[r][n];\n";
-    {
-      std::vector<std::string> en(k.epi.size());
-      std::vector<char> eall(k.epi.size(), 1);
-      Env ee;
-      ee.prefix = "e";
-      ee.acc = "acc_v";
-      emit_nodes(os, k.epi, an_epi, en, eall, ee, "          ");
-      os << "          out[gidx] = " << to_storage(out_dt, en.back()) << ";\n";
-    }
+    emit_epilogue(os, "          ", "acc_v", "out[gidx]");
     os << "        }\n      }\n    }\n  }\n}\n";
     p.source = os.str();
     Stage st;
@@ -964,13 +962,8 @@ struct Builder {
     os << "    const int gidx = (int)gl;\n    " << AT << " acc_u = " << identity_literal(k.red_op, k.red_dtype) << ";\n";
     os << "    for (int s = 0; s < " << splits << "; s++) { const " << AT << " v = __ldcg(parts + (size_t)s * " << k.size
        << " + gidx); acc_u = " << red("acc_u", "v") << "; }\n";
-    std::vector<std::string> en(k.epi.size());
-    std::vector<char> eall(k.epi.size(), 1);
-    Env ee;
-    ee.prefix = "e";
-    ee.acc = "acc_u";
-    emit_nodes(os, k.epi, an_epi, en, eall, ee, "    ");
-    os << "    out[gidx] = " << to_storage(out_dt, en.back()) << ";\n  }\n";
+    emit_epilogue(os, "    ", "acc_u", "out[gidx]");
+    os << "  }\n";
     os << "  if (threadIdx.x == 0) ((int*)scratch)[blockIdx.x] = 0;\n";
   }
 
@@ -1034,13 +1027,8 @@ struct Builder {
     } else {
       os << "  if (ty != 0 || !active) return;\n  #pragma unroll\n  for (int q = 0; q < 4 * GN; q++) {\n";
       os << "    const int gidx = m0 * GN + q;\n    const float acc_u = acc[q];\n";
-      std::vector<std::string> en(k.epi.size());
-      std::vector<char> eall(k.epi.size(), 1);
-      Env ee;
-      ee.prefix = "e";
-      ee.acc = "acc_u";
-      emit_nodes(os, k.epi, an_epi, en, eall, ee, "    ");
-      os << "    out[gidx] = " << to_storage(out_dt, en.back()) << ";\n  }\n";
+      emit_epilogue(os, "    ", "acc_u", "out[gidx]");
+      os << "  }\n";
     }
     os << "}\n";
     p.source = os.str();
