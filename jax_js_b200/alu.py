@@ -110,6 +110,8 @@ class AluExp:
 
     def __new__(cls, op: AluOp, dtype: DType, src: Sequence["AluExp"] = (), arg: Any = None):
         src = tuple(src)
+        if src and op in _FOLDABLE and all(s.op == AluOp.Const for s in src):
+            return AluExp(AluOp.Const, dtype, (), _const_arg(DType(dtype), _fold(AluOp(op), DType(dtype), src, arg)))
         key = (int(op), int(dtype), tuple(id(s) for s in src), _arg_key(arg))
         hit = cls._interned.get(key)
         if hit is not None:
@@ -279,6 +281,84 @@ class AluExp:
         return f"{self.op.name}{tag}({inner})"
 
 
+def _fold(op: AluOp, dtype: DType, src, arg):
+    """Value of an operation on constants, in the double arithmetic of `evaluate`
+    (src/alu.ts:1059-1213): the reference folds such nodes when a Kernel is simplified
+    (alu.ts:672-676), so e.g. log(0.999) reaches a backend as a constant."""
+    v = [s.arg for s in src]
+    flt = is_float(dtype)
+
+    def wrap(r):
+        if dtype == DType.Int32:
+            return _wrap_i32(int(r))
+        if dtype == DType.Uint32:
+            return int(r) & 0xFFFFFFFF
+        return r
+    if op == AluOp.Add:
+        return int(bool(v[0] or v[1])) if dtype == DType.Bool else wrap(v[0] + v[1])
+    if op == AluOp.Sub:
+        return wrap(v[0] - v[1])
+    if op == AluOp.Mul:
+        return int(bool(v[0] and v[1])) if dtype == DType.Bool else wrap(v[0] * v[1])
+    if op == AluOp.Idiv:
+        if v[1] == 0:
+            return (math.copysign(math.inf, v[0]) if v[0] else math.nan) if flt else 0
+        q = v[0] / v[1]
+        return float(math.trunc(q)) if flt and math.isfinite(q) else (q if flt else wrap(math.trunc(q)))
+    if op == AluOp.Mod:
+        if v[1] == 0:
+            return math.nan if flt else 0
+        return math.fmod(v[0], v[1]) if flt else wrap(int(math.fmod(v[0], v[1])))
+    if op in (AluOp.Min, AluOp.Max):
+        if flt and (math.isnan(v[0]) or math.isnan(v[1])):
+            return math.nan
+        return min(v) if op == AluOp.Min else max(v)
+    if op == AluOp.Cmplt:
+        return int(v[0] < v[1])
+    if op == AluOp.Cmpne:
+        return int(v[0] != v[1])
+    if op == AluOp.Where:
+        return v[1] if v[0] else v[2]
+    x = v[0]
+    try:
+        if op == AluOp.Sin: return math.sin(x)
+        if op == AluOp.Cos: return math.cos(x)
+        if op == AluOp.Asin: return math.asin(x)
+        if op == AluOp.Atan: return math.atan(x)
+        if op == AluOp.Exp: return math.exp(x)
+        if op == AluOp.Log: return math.log(x) if x > 0 else (-math.inf if x == 0 else math.nan)
+        if op == AluOp.Sqrt: return math.sqrt(x)
+        if op == AluOp.Floor: return float(math.floor(x)) if math.isfinite(x) else x
+        if op == AluOp.Ceil: return float(math.ceil(x)) if math.isfinite(x) else x
+        if op == AluOp.Reciprocal: return 1.0 / x if x else math.copysign(math.inf, x)
+    except (ValueError, OverflowError):
+        return math.nan if op != AluOp.Exp else math.inf
+    if op == AluOp.Cast:
+        was_float = is_float(src[0].dtype)
+        if dtype == DType.Int32:
+            if was_float:
+                x = 0 if math.isnan(x) else builtins_max(-2147483648, builtins_min(2147483647, x))
+            return _wrap_i32(int(x))
+        if dtype == DType.Uint32:
+            if was_float:
+                x = 0 if math.isnan(x) else builtins_max(0, builtins_min(4294967295, x))
+            return int(x) & 0xFFFFFFFF
+        if dtype == DType.Bool:
+            return int(bool(x))
+        return float(x)
+    raise AssertionError(op)
+
+
+def _const_arg(dtype: DType, value):
+    return float(value) if is_float(dtype) else int(value)
+
+
+builtins_max, builtins_min = max, min
+_FOLDABLE = {AluOp.Add, AluOp.Sub, AluOp.Mul, AluOp.Idiv, AluOp.Mod, AluOp.Min, AluOp.Max, AluOp.Cmplt,
+             AluOp.Cmpne, AluOp.Where, AluOp.Sin, AluOp.Cos, AluOp.Asin, AluOp.Atan, AluOp.Exp, AluOp.Log,
+             AluOp.Sqrt, AluOp.Floor, AluOp.Ceil, AluOp.Reciprocal, AluOp.Cast}
+
+
 def _arg_key(arg):
     if isinstance(arg, float):
         return ("f", struct.pack("<d", arg))
@@ -328,6 +408,18 @@ def _binary(op: AluOp, a: AluExp, b: AluExp) -> AluExp:
             if _is_const(a, 0): return b
             if _is_const(b, 0): return a
             if _is_const(a) and _is_const(b): return AluExp.const(dt, a.arg + b.arg)
+            # digits of one index put back together (the "shape tracking" rules of alu.ts:765-791):
+            # (x/A)*A + x%A => x   and   ((x/A)%B)*A + x%A => x % (A*B)
+            if (a.op == AluOp.Mul and _is_const(a.src[1]) and b.op == AluOp.Mod and _is_const(b.src[1])
+                    and a.src[1].arg == b.src[1].arg and a.src[1].arg > 0):
+                x, A = b.src[0], b.src[1].arg
+                hi = a.src[0]
+                def is_x_over_a(e):
+                    return e.op == AluOp.Idiv and _is_const(e.src[1], A) and e.src[0] is x
+                if is_x_over_a(hi):
+                    return x
+                if hi.op == AluOp.Mod and _is_const(hi.src[1]) and is_x_over_a(hi.src[0]):
+                    return _binary(AluOp.Mod, x, AluExp.const(dt, A * hi.src[1].arg))
         elif op == AluOp.Sub:
             if _is_const(b, 0): return a
         elif op == AluOp.Mul:

@@ -1,24 +1,44 @@
-"""Kernel lists of the MLP programs: per-example gradients under `vmap` and the
-data-parallel Adam training step.
+"""The MLP programs as Jaxprs: `valueAndGrad(loss)` of a ReLU MLP with softmax cross-entropy,
+its `vmap` over the batch (per-example gradients), and the `optax.adam` update.
 
-What is restated here is only the *output* of the reference's device-independent frontend
-for these programs -- the Kernels that `jit(valueAndGrad(loss))` and `optax.adam` hand to
-`Backend.dispatch`:
+The reference's frontend turns these functions into Jaxprs by tracing (`jvp`, partial evaluation
+and transposition, src/frontend/jvp.ts and linearize.ts) and cuts the Jaxprs into Kernels
+(`jitCompile`).  The cutting is restated in `jaxpr.py`; the tracing is not, so the equations are
+written out here, each group with the rule it comes from:
 
-  * forward layer = one Dot kernel with bias and ReLU fused as its epilogue
-    (src/frontend/jit.ts:833-885; `nn.relu = maximum(x, 0)`, src/library/nn.ts:47-49);
-  * loss = softmax cross-entropy composed as in website/src/routes/mnist/+page.svelte:70-148:
-    logSoftmax (src/library/nn.ts:311-322) times `oneHot(y)` = `eye(C)[y]`
-    (nn.ts:430-435; a Gather whose index is itself a load, src/frontend/jit.ts:715-763);
-  * backward = transposed Dots (`transposeDot`, src/frontend/linearize.ts:676-701): dW is a
-    contraction over the batch axis with both operands read with stride = row length,
-    dX = dY * W^T with the ReLU mask fused; bias gradients are column sums over a strided axis;
-  * `optax.adam`: moments, bias correction from a uint32 step counter and the parameter update
-    (packages/optax/src/transform.ts:29-72, treeUtils.ts:29-60, base.ts:74-79), per leaf.
+forward (the known half of the partial evaluation)
+  * non-differentiated arguments pass through `stopGradient` (`valueAndGrad`,
+    linearize.ts:1126-1128); the copy of x this causes is real: `stop_gradient` is not a view
+    primitive, so the producer in front of the first Dot is materialised (jit.ts:887-947);
+  * `np.dot(x, W)` = `lax.dot` contracting x's last with W's second-to-last axis: W transposed,
+    both reshaped to [B,1,K] and [1,N,K], `core.dot` (numpy.ts:1764-1782, lax.ts:87-128);
+  * `nn.relu(z) = max(z, 0)` (nn.ts:47-49); its JVP also evaluates `less(z, 0)` on the
+    pre-activation (jvp.ts:205-207), a residual of the backward pass;
+  * `nn.logSoftmax` (nn.ts:311-322); the JVP of `log` evaluates `reciprocal(s)` (jvp.ts:262-265);
+  * `nn.oneHot(y, C) = eye(C)[y]`, a Gather on a constant (nn.ts:430-435);
+  * loss = `logits.mul(oneHot).sum().mul(-1 / batch)`
+    (website/src/routes/mnist/+page.svelte:139-150).
 
-Under `vmap` the batch axis of a per-example gradient ends up last
-(src/frontend/vmap.ts:297-303), so per-example dW is an outer-product kernel (K = 1) that
-streams out [in, out, batch].
+backward (`evalJaxprTransposed` over the linear half, linearize.ts:553-634, last equation first)
+  * Mul by a known factor: `mul(ct, known)`, un-broadcast to the operand (linearize.ts:722-731,
+    `unbroadcast` :637-673); Add: the cotangent to both operands (:736-744); Neg: `neg(ct)`;
+    Reduce(add): broadcast back (:745-754); Reshape: reshape back (:902-906);
+  * a cotangent that arrives twice is `add(old, new)` (:579-586);
+  * `where(less(z, 0), 0, dz)`: `where(cond, 0, ct)` (:838-855), so a pre-activation of exactly
+    zero passes its cotangent;
+  * Dot: `transposeDot` (:676-701): the cotangent broadcast along the contracted axis, both
+    operands permuted so that the target's missing axes are contracted, `core.dot`, reshape to
+    the target; the parameter's own reshape and transpose are then undone (:885-906), which is
+    why each weight gradient ends in a transposing Kernel;
+  * order: the equations of the linear Jaxpr come from a depth-first topological sort
+    (`partialEvalGraphToJaxpr`, linearize.ts:464-513; `toposort`, utils.ts:252-290) that follows
+    the activation chain before the weight operands, so the pullback visits, per layer from
+    the last, bias gradient and input cotangent, and only then the weight gradients, first
+    layer first.
+
+Under `vmap` every primitive is batched by `vmap_jaxpr` (the reference's batching rules).
+`optax.adam`: packages/optax/src/transform.ts:29-72, treeUtils.ts:29-60, base.ts:74-79,
+alias.ts:35-40; `np.power` as in numpy.ts:2982-2999.
 """
 from __future__ import annotations
 
@@ -27,185 +47,232 @@ from typing import Sequence
 
 import numpy as np
 
-from .alu import AluExp, AluOp, AluVar, DType, Kernel, Reduction
-from .programs import JitProgram, dot_kernel, row_reduce_kernel, softmax_exp_kernel
+from .alu import AluOp, DType
+from .jaxpr import Builder, Jaxpr, Lit, Var, general_broadcast, jit_compile, vmap_jaxpr
+from .programs import JitProgram
 
 F32, I32, U32 = DType.Float32, DType.Int32, DType.Uint32
-_g, _r = AluVar.gidx, AluVar.ridx
 
 
-def _i(v: int) -> AluExp:
-    return AluExp.i32(v)
+# ---- library functions over a Builder ---------------------------------------------------------
+
+def np_dot(b: Builder, x: Var, w: Var, name: str | None = None):
+    """x[B,K] . w[K,N]; returns (product, x reshaped, w reshaped): the reshaped operands are what
+    the backward pass contracts against."""
+    B, K = x.shape
+    N = w.shape[1]
+    xr = b.reshape(x, (B, 1, K))
+    wr = b.reshape(b.transpose(w, (1, 0)), (1, N, K))
+    return b.dot(xr, wr, name), xr, wr
 
 
-def _f(v: float) -> AluExp:
-    return AluExp.f32(v)
+def unbroadcast(b: Builder, x: Var, shape: Sequence[int]) -> Var:
+    """linearize.ts:637-673."""
+    shape = tuple(shape)
+    extra = list(range(len(x.shape) - len(shape)))
+    unsqueeze, kept = [], []
+    for i, d in enumerate(shape):
+        ix = len(x.shape) - (len(shape) - i)
+        if x.shape[ix] > 1 and d == 1:
+            unsqueeze.append(i)
+            kept.append(ix)
+    dims = extra + kept
+    if not dims:
+        return x
+    r = b.reduce(x, AluOp.Add, dims)
+    if tuple(r.shape) != shape:
+        r = b.broadcast(r, shape, unsqueeze)
+    return r
 
 
-def _ld(gid: int, length: int, ix: AluExp, dtype: DType = F32) -> AluExp:
-    return AluExp.global_index(dtype, gid, length, ix)
+def transpose_dot(b: Builder, ct: Var, known: Var, target_shape: Sequence[int], name: str | None = None) -> Var:
+    """linearize.ts:676-701."""
+    full = general_broadcast(target_shape, known.shape)
+    nd = len(full)
+    tshape = [1] * (nd - len(target_shape)) + list(target_shape)
+    kshape = [1] * (nd - len(known.shape)) + list(known.shape)
+    contracting = [a for a in range(nd) if tshape[a] == 1]
+    batch = [a for a in range(nd) if tshape[a] != 1]
+    perm = batch + contracting
+
+    def dot_shape(shape):
+        return [shape[a] for a in batch] + [math.prod(shape[a] for a in contracting)]
+    lhs = b.reshape(b.transpose(b.broadcast(ct, full, [nd - 1]), perm), dot_shape(full))
+    rhs = b.reshape(b.transpose(b.reshape(known, kshape), perm), dot_shape(kshape))
+    return b.reshape(b.dot(lhs, rhs, name), target_shape)
 
 
-# ---- loss pieces ------------------------------------------------------------------------------
-
-def nll_rows_kernel(batch: int, classes: int, scale: float) -> Kernel:
-    """l[b] = scale * sum_j (logits[b,j] - m[b] - log s[b]) * eye[y[b], j]; args logits, m, s, y, eye."""
-    logit = _ld(0, batch * classes, AluExp.add(AluExp.mul(_g, _i(classes)), _r))
-    m, s = _ld(1, batch, _g), _ld(2, batch, _g)
-    y = _ld(3, batch, _g, I32)
-    hot = _ld(4, classes * classes, AluExp.add(AluExp.mul(y, _i(classes)), _r))
-    logp = AluExp.sub(AluExp.add(logit, AluExp.sub(_f(0), m)), AluExp.log(s))
-    epilogue = AluExp.mul(AluVar.acc(F32), _f(scale))
-    return Kernel(5, batch, AluExp.mul(logp, hot), Reduction(F32, AluOp.Add, classes, epilogue))
-
-
-def sum_all_kernel(n: int, scale: float) -> Kernel:
-    """Scalar scale * sum(v): the mean over the batch."""
-    return Kernel(1, 1, _ld(0, n, _r), Reduction(F32, AluOp.Add, n, AluExp.mul(AluVar.acc(F32), _f(scale))))
-
-
-def dlogits_kernel(batch: int, classes: int, scale: float) -> Kernel:
-    """(softmax - onehot) * scale from e = exp(logits - max), s = sum e; args e, s, y, eye."""
-    b = AluExp.idiv(_g, _i(classes))
-    e, s = _ld(0, batch * classes, _g), _ld(1, batch, b)
-    y = _ld(2, batch, b, I32)
-    hot = _ld(3, classes * classes, AluExp.add(AluExp.mul(y, _i(classes)), AluExp.mod(_g, _i(classes))))
-    return Kernel(4, batch * classes, AluExp.mul(AluExp.sub(AluExp.mul(e, AluExp.reciprocal(s)), hot), _f(scale)))
-
-
-def backprop_dot_kernel(batch: int, n_in: int, n_out: int) -> Kernel:
-    """dz_prev[b,i] = where(a_prev[b,i] > 0, sum_j dz[b,j] * W[i,j], 0); args dz, W, a_prev."""
-    k = dot_kernel(batch, n_in, n_out, F32, a_layout="mk", b_layout="nk")
-    act = _ld(2, batch * n_in, _g)
-    mask = AluExp.cmplt(_f(0), act)
-    k.reduction.epilogue = AluExp.where(mask, AluVar.acc(F32), _f(0))
-    return Kernel(3, k.size, k.exp, k.reduction)
-
-
-def column_sum_kernel(rows: int, cols: int) -> Kernel:
-    """db[j] = sum_b dz[b,j]."""
-    return Kernel(1, cols, _ld(0, rows * cols, AluExp.add(_g, AluExp.mul(_r, _i(cols)))), Reduction(F32, AluOp.Add, rows))
-
-
-def outer_product_kernel(n_in: int, n_out: int, batch: int) -> Kernel:
-    """Per-example dW[i,j,b] = a[b,i] * dz[b,j] (a Dot with K = 1); args a [batch,n_in], dz [batch,n_out]."""
-    b = AluExp.mod(_g, _i(batch))
-    j = AluExp.mod(AluExp.idiv(_g, _i(batch)), _i(n_out))
-    i = AluExp.idiv(_g, _i(batch * n_out))
-    a = _ld(0, batch * n_in, AluExp.add(AluExp.mul(b, _i(n_in)), i))
-    dz = _ld(1, batch * n_out, AluExp.add(AluExp.mul(b, _i(n_out)), j))
-    return Kernel(2, n_in * n_out * batch, AluExp.mul(a, dz))
-
-
-def batch_last_kernel(batch: int, n: int) -> Kernel:
-    """Per-example db[j,b] = dz[b,j]: the batch axis moved last."""
-    ix = AluExp.add(AluExp.mul(AluExp.mod(_g, _i(batch)), _i(n)), AluExp.idiv(_g, _i(batch)))
-    return Kernel(1, batch * n, _ld(0, batch * n, ix))
-
-
-# ---- programs ---------------------------------------------------------------------------------
-
-def _names(n_layers: int):
-    return [f"W{l}" for l in range(1, n_layers + 1)], [f"b{l}" for l in range(1, n_layers + 1)]
-
+# ---- valueAndGrad(loss) -----------------------------------------------------------------------
 
 def param_order(n_layers: int) -> list:
     """Leaf order of the parameter pytree: W1, b1, W2, b2, ..."""
-    ws, bs = _names(n_layers)
-    return [n for pair in zip(ws, bs) for n in pair]
+    return [n for l in range(1, n_layers + 1) for n in (f"W{l}", f"b{l}")]
+
+
+def mlp_grad_jaxpr(batch: int | None, dims: Sequence[int], scale: float) -> Jaxpr:
+    """`valueAndGrad(loss)(params, x, y)`: inputs x, y, eye, then the parameter leaves; outputs the
+    loss and one gradient per leaf.  loss = scale * sum(logSoftmax(mlp(x)) * oneHot(y)).
+    `batch=None` is the function of a single example (x[D], y[]), the one `vmap` maps."""
+    L, C = len(dims) - 1, dims[-1]
+    b = Builder()
+    single = batch is None
+    B = 1 if single else batch
+    x_in = b.input("x", (dims[0],) if single else (B, dims[0]))
+    y_in = b.input("y", () if single else (B,), I32)
+    eye = b.input("eye", (C, C))
+    W = [None] + [None] * L
+    bias = list(W)
+    for l in range(1, L + 1):
+        W[l] = b.input(f"W{l}", (dims[l - 1], dims[l]))
+        bias[l] = b.input(f"b{l}", (dims[l],))
+
+    # forward
+    x = b.stop_gradient(x_in, "x_sg")
+    y = b.stop_gradient(y_in)
+    if single:
+        x = b.reshape(x, (1, dims[0]))
+    a, z, lt, ar, wr = [x], [None], [None], [None], [None]
+    for l in range(1, L + 1):
+        d, xr, w_r = np_dot(b, a[-1], W[l])
+        ar.append(xr)
+        wr.append(w_r)
+        z.append(b.add(d, bias[l], f"z{l}"))
+        if l < L:
+            a.append(b.max(z[l], Lit(0.0), f"a{l}"))
+            lt.append(b.compare(z[l], Lit(0.0), "less"))
+    logits = z[L]
+    m = b.stop_gradient(b.reshape(b.reduce(logits, AluOp.Max, [1], "m"), (B, 1)))
+    sh = b.add(logits, b.neg(m), "shifted")
+    e = b.exp(sh, "e")
+    sk = b.reshape(b.reduce(e, AluOp.Add, [1], "s"), (B, 1))
+    lg = b.log(sk)
+    rs = b.reciprocal(sk)
+    logp = b.add(sh, b.neg(lg))
+    oh = b.gather(eye, [y], [0], 0, "onehot")
+    loss = b.mul(b.reduce(b.mul(logp, oh), AluOp.Add, [0, 1]), Lit(scale), "loss")
+
+    # backward from a cotangent of 1
+    ct_tot = b.mul(Lit(1.0), Lit(scale))
+    ct_prod = b.broadcast(ct_tot, (B, C), [0, 1])
+    g0 = b.mul(ct_prod, oh)                                     # cotangent of logp
+    ct_lg = b.neg(unbroadcast(b, g0, (B, 1)))                   # add -> (shifted, neg(log s)); neg
+    ct_s = b.reshape(b.mul(rs, ct_lg), (B,))                    # log's tangent is reciprocal(s) * ds; reshape
+    ct_e = b.broadcast(ct_s, (B, C), [1])                       # reduce(add)
+    dz = b.add(g0, b.mul(e, ct_e), f"dz{L}")                    # exp's tangent is e * dshifted; second arrival
+    grads = {}
+    pending = []
+    for l in range(L, 0, -1):
+        grads[f"b{l}"] = unbroadcast_to_bias(b, dz, dims[l], f"db{l}")
+        pending.append((l, dz))
+        if l > 1:
+            ct_ar = transpose_dot(b, dz, wr[l], ar[l].shape)   # cotangent of a_{l-1} reshaped [B,1,K]
+            ct_a = b.reshape(ct_ar, (B, dims[l - 1]))
+            dz = b.where(lt[l - 1], Lit(0.0), ct_a, f"dz{l - 1}")
+    for l, dzl in reversed(pending):
+        ct_wr = transpose_dot(b, dzl, ar[l], wr[l].shape, f"dW{l}_nk")
+        grads[f"W{l}"] = b.transpose(b.reshape(ct_wr, (dims[l], dims[l - 1])), (1, 0), f"dW{l}")
+    return b.build([loss] + [grads[n] for n in param_order(L)])
+
+
+def unbroadcast_to_bias(b: Builder, ct: Var, n: int, name: str) -> Var:
+    r = unbroadcast(b, ct, (n,))
+    r.name = name
+    return r
+
+
+def mlp_predict_jaxpr(batch: int, dims: Sequence[int]) -> Jaxpr:
+    """`(x, W1, b1, ...) => logSoftmax(mlp(x))`, the forward pass alone (the function jitted in
+    test/platform-test/node.test.ts:29-58 and website/src/routes/mnist/+page.svelte:70-79).
+    Without a backward pass every pre-activation has one consumer, so bias and ReLU fuse into
+    the Dot's epilogue (src/frontend/jit.ts:833-885)."""
+    L = len(dims) - 1
+    b = Builder()
+    a = b.input("x", (batch, dims[0]))
+    params = []
+    for l in range(1, L + 1):
+        params.append((b.input(f"W{l}", (dims[l - 1], dims[l])), b.input(f"b{l}", (dims[l],))))
+    for l, (w, bias) in enumerate(params, 1):
+        z = b.add(np_dot(b, a, w)[0], bias)
+        a = b.max(z, Lit(0.0), f"a{l}") if l < L else z
+    m = b.stop_gradient(b.reshape(b.reduce(a, AluOp.Max, [1], "m"), (batch, 1)))
+    sh = b.add(a, b.neg(m), "shifted")
+    lg = b.log(b.reshape(b.reduce(b.exp(sh), AluOp.Add, [1], "s"), (batch, 1)))
+    return b.build([b.add(sh, b.neg(lg), "logp")])
 
 
 def mlp_grad_program(batch: int, dims: Sequence[int], *, global_batch: int | None = None,
                      per_example: bool = False) -> JitProgram:
-    """`valueAndGrad(loss)(params, x, y)` for an MLP with ReLU hidden layers and softmax
-    cross-entropy.
+    """`jit(valueAndGrad(loss))(params, x, y)` as the backend sees it.
 
     per_example=False: loss = mean NLL over `global_batch` examples of which this program sees
     `batch` (the data-parallel shard; the gradient sum over shards is then the global mean
     gradient).  Outputs: loss (scalar partial sum) and d<leaf> for every parameter.
-    per_example=True: the `vmap`-ed program: per-example loss [batch] and per-example gradients
-    with the batch axis last.
+    per_example=True: `jit(vmap(valueAndGrad(loss1), [null, 0, 0]))` with loss1 the negative log
+    likelihood of one example: per-example loss [batch] and per-example gradients, batch axis
+    first.
     Inputs: x f32[batch, dims[0]], y i32[batch], eye f32[C, C], then the parameter leaves.
     """
     L = len(dims) - 1
-    C = dims[-1]
-    ws, bs = _names(L)
-    leaves = param_order(L)
-    p = JitProgram(inputs=["x", "y", "eye"] + leaves, outputs=["loss"] + [f"d{n}" for n in leaves])
-    scale = 1.0 if per_example else 1.0 / float(global_batch or batch)
-    acts = ["x"]
-    for l in range(1, L + 1):
-        k = dot_kernel(batch, dims[l], dims[l - 1], F32, bias=True, relu=l < L)
-        p.run(f"a{l}", k, [acts[-1], ws[l - 1], bs[l - 1]])
-        acts.append(f"a{l}")
-    logits = acts[-1]
-    p.run("m", row_reduce_kernel(batch, C, AluOp.Max), [logits])
-    p.run("e", softmax_exp_kernel(batch, C), [logits, "m"])
-    p.run("s", row_reduce_kernel(batch, C, AluOp.Add), ["e"])
     if per_example:
-        p.run("loss", nll_rows_kernel(batch, C, -1.0), [logits, "m", "s", "y", "eye"])
+        inner = mlp_grad_jaxpr(None, dims, -1.0)
+        jaxpr = vmap_jaxpr(inner, batch, [0, 0, None] + [None] * (2 * L))
     else:
-        p.run("nll", nll_rows_kernel(batch, C, 1.0), [logits, "m", "s", "y", "eye"])
-        p.run("loss", sum_all_kernel(batch, -scale), ["nll"])
-        p.free("nll")
-    p.run(f"dz{L}", dlogits_kernel(batch, C, scale), ["e", "s", "y", "eye"])
-    for n in ("m", "e", "s"):
-        p.free(n)
-    for l in range(L, 0, -1):
-        dz, a_prev = f"dz{l}", acts[l - 1]
-        if per_example:
-            p.run(f"dW{l}", outer_product_kernel(dims[l - 1], dims[l], batch), [a_prev, dz])
-            p.run(f"db{l}", batch_last_kernel(batch, dims[l]), [dz])
-        else:
-            p.run(f"dW{l}", dot_kernel(dims[l - 1], dims[l], batch, F32, a_layout="km", b_layout="kn"), [a_prev, dz])
-            p.run(f"db{l}", column_sum_kernel(batch, dims[l]), [dz])
-        if l > 1:
-            p.run(f"dz{l - 1}", backprop_dot_kernel(batch, dims[l - 1], dims[l]), [dz, ws[l - 1], a_prev])
-        p.free(dz)
-        if l < L:
-            p.free(acts[l])
-    p.free(acts[L])
-    return p
+        jaxpr = mlp_grad_jaxpr(batch, dims, -1.0 / float(global_batch or batch))
+    return jit_compile(jaxpr)
 
 
 ADAM_B1, ADAM_B2, ADAM_EPS = 0.9, 0.999, 1e-8
 
 
+def _power(b: Builder, x1, x2: Var) -> Var:
+    """`np.power` (numpy.ts:2982-2999) of a literal base and a float32 exponent."""
+    x2i = b.idiv(x2, Lit(1.0))                                   # trunc
+    should_nan = b.mul(b.compare(x2, x2i, "not_equal"), b.compare(x1, Lit(0.0), "less"))
+    sign = b.where(b.compare(b.mod(x2i, Lit(2.0)), Lit(0.0), "not_equal"),
+                   b.where(b.compare(x1, Lit(0.0), "less"), Lit(-1.0), Lit(1.0)), Lit(1.0))
+    absx = b.where(b.compare(x1, Lit(0.0), "less"), b.mul(x1, Lit(-1.0)), x1)
+    return b.where(should_nan, Lit(float("nan")), b.mul(b.exp(b.mul(b.log(absx), x2)), sign))
+
+
+def adam_jaxpr(sizes: Sequence[int], names: Sequence[str], lr: float = 1e-3, order: Sequence[int] | None = None) -> Jaxpr:
+    """One jitted `optax.adam(lr)` update followed by `applyUpdates`.
+
+    Inputs: count u32[], then p, g, mu, nu per leaf.  Outputs: count', then p', mu', nu' per leaf.
+    `order` lists the leaves in the order their (mutually independent) equations are written."""
+    b = Builder()
+    count = b.input("count", (), U32)
+    leaves = []
+    for n, size in zip(names, sizes):
+        leaves.append((b.input(n, (size,)), b.input(f"g_{n}", (size,)), b.input(f"mu_{n}", (size,)), b.input(f"nu_{n}", (size,))))
+    count_new = b.add(count, Lit(1, U32), "count_new")
+
+    def correction(decay: float, name: str) -> Var:       # treeBiasCorrection
+        t = b.cast(count_new, F32)
+        return b.reciprocal(b.add(Lit(1.0), b.neg(_power(b, Lit(decay), t))), name)
+    outs = {}
+    idx = list(range(len(names))) if order is None else list(order)
+    mu_new, nu_new = {}, {}
+    for i in idx:                                          # treeUpdateMoment, first then second
+        p, g, mu, nu = leaves[i]
+        mu_new[i] = b.add(b.mul(g, Lit(1 - ADAM_B1)), b.mul(mu, Lit(ADAM_B1)), f"mu_{names[i]}_new")
+    for i in idx:
+        p, g, mu, nu = leaves[i]
+        nu_new[i] = b.add(b.mul(b.mul(g, g), Lit(1 - ADAM_B2)), b.mul(nu, Lit(ADAM_B2)), f"nu_{names[i]}_new")
+    c1 = correction(ADAM_B1, "c1")
+    c2 = correction(ADAM_B2, "c2")
+    for i in idx:
+        p = leaves[i][0]
+        mu_hat, nu_hat = b.mul(mu_new[i], c1), b.mul(nu_new[i], c2)
+        upd = b.mul(mu_hat, b.reciprocal(b.add(b.sqrt(b.add(nu_hat, Lit(0.0))), Lit(ADAM_EPS))))
+        outs[i] = b.add(p, b.mul(upd, Lit(-lr)), f"{names[i]}_new")
+    flat = [count_new]
+    for i in range(len(names)):
+        flat += [outs[i], mu_new[i], nu_new[i]]
+    return b.build(flat)
+
+
 def adam_program(sizes: Sequence[int], names: Sequence[str], lr: float = 1e-3, order: Sequence[int] | None = None) -> JitProgram:
-    """`optax.adam(lr)` update + `applyUpdates` over the parameter leaves.
-
-    Inputs: count u32[1], then p, g, mu, nu per leaf.  Outputs: count', then p', mu', nu' per leaf.
-    `order` lists the leaves in the order their (mutually independent) kernels are dispatched.
-    """
-    ins, outs = ["count"], ["count_new"]
-    for n in names:
-        ins += [n, f"g_{n}", f"mu_{n}", f"nu_{n}"]
-        outs += [f"{n}_new", f"mu_{n}_new", f"nu_{n}_new"]
-    p = JitProgram(inputs=ins, outputs=outs)
-    one = AluExp.u32(1)
-    p.run("count_new", Kernel(1, 1, AluExp.add(_ld(0, 1, _g, U32), one)), ["count"])
-
-    def correction(decay: float) -> Kernel:   # 1 / (1 - decay**t), t from the uint32 counter
-        t = AluExp.cast(F32, _ld(0, 1, _g, U32))
-        return Kernel(1, 1, AluExp.reciprocal(AluExp.sub(_f(1), AluExp.exp(AluExp.mul(t, _f(math.log(decay)))))))
-
-    p.run("c1", correction(ADAM_B1), ["count_new"])
-    p.run("c2", correction(ADAM_B2), ["count_new"])
-    for leaf in (range(len(names)) if order is None else order):
-        n, size = names[leaf], sizes[leaf]
-        g, mu, nu = _ld(0, size, _g), _ld(1, size, _g), _ld(1, size, _g)
-        p.run(f"mu_{n}_new", Kernel(2, size, AluExp.add(AluExp.mul(g, _f(1 - ADAM_B1)), AluExp.mul(mu, _f(ADAM_B1)))),
-              [f"g_{n}", f"mu_{n}"])
-        p.run(f"nu_{n}_new", Kernel(2, size, AluExp.add(AluExp.mul(AluExp.mul(g, g), _f(1 - ADAM_B2)), AluExp.mul(nu, _f(ADAM_B2)))),
-              [f"g_{n}", f"nu_{n}"])
-        par, m2, n2 = _ld(0, size, _g), _ld(1, size, _g), _ld(2, size, _g)
-        c1, c2 = _ld(3, 1, _i(0)), _ld(4, 1, _i(0))
-        denom = AluExp.add(AluExp.sqrt(AluExp.mul(n2, c2)), _f(ADAM_EPS))
-        upd = AluExp.mul(AluExp.mul(AluExp.mul(m2, c1), AluExp.reciprocal(denom)), _f(-lr))
-        p.run(f"{n}_new", Kernel(5, size, AluExp.add(par, upd)), [n, f"mu_{n}_new", f"nu_{n}_new", "c1", "c2"])
-    p.free("c1")
-    p.free("c2")
-    return p
+    return jit_compile(adam_jaxpr(sizes, names, lr, order))
 
 
 def leaf_sizes(dims: Sequence[int]) -> list:
@@ -236,9 +303,10 @@ class MlpTrainer:
         self.names = param_order(len(dims) - 1)
         self.sizes = leaf_sizes(dims)
         self.grad = mlp_grad_program(local_batch, dims, global_batch=global_batch)
-        # leaves of the last layer first: the first layer's gradients are the last to arrive, and
-        # with overlapped sums theirs is still in flight while the other leaves are updated
-        self.adam = adam_program(self.sizes, self.names, lr, order=list(reversed(range(len(self.names)))))
+        # the last layer's weights last: their gradient is the last to arrive, and with overlapped
+        # sums it is still in flight while the other leaves are updated
+        n = len(self.names)
+        self.adam = adam_program(self.sizes, self.names, lr, order=[i for i in range(n) if i != n - 2] + [n - 2])
         self.grad.prepare(backend)
         self.adam.prepare(backend)
         self.allreduce = allreduce if allreduce is not None else backend.allreduce_sum_f32
@@ -261,18 +329,21 @@ class MlpTrainer:
             outs = self.grad.execute(be, ins)
             self.allreduce(list(outs[1:]) + [outs[0]])
         else:
+            # The program yields the loss and the bias gradients first (last layer first), then the
+            # weight gradients from the first layer up.  Loss and biases go out as one group once the
+            # last bias exists, every weight gradient on its own as soon as it exists, under the
+            # kernels that follow it.  The last group (the last layer's weights) stays in flight into
+            # the Adam program, which waits for it just before its first reader (`_adam`).
             ready = []
+            last = f"dW{len(self.dims) - 1}"
 
             def on_output(name, slot):
                 ready.append(slot)
-                if name.startswith("db"):        # a layer's last leaf: dW and db go out together
-                    if name == "db1":
-                        # everything summed so far is waited for here; the first layer's own sum, begun
-                        # next, is only waited for by the Adam kernels that read it (`_adam`)
-                        be.comm_join()
-                        self._tail = True
+                if name == "db1" or name.startswith("dW"):
                     be.allreduce_sum_f32_async(ready)
                     ready.clear()
+                    if name == last:
+                        self._tail = True
 
             self._tail = False
             outs = self.grad.execute(be, ins, on_output)
@@ -283,12 +354,12 @@ class MlpTrainer:
         return outs[0], list(outs[1:])
 
     def _adam(self, ins, out_slots=None):
-        """The Adam program; joins a first-layer gradient sum still in flight just before its first reader."""
+        """The Adam program; joins the gradient sum still in flight just before its first reader."""
         be = self.be
-        first_layer = {f"g_{self.names[0]}", f"g_{self.names[1]}"}
+        late = {f"g_W{len(self.dims) - 1}"}
 
         def before_step(step):
-            if self._tail and first_layer.intersection(step.inputs):
+            if self._tail and late.intersection(step.inputs):
                 be.comm_join()
                 self._tail = False
 

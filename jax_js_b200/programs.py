@@ -220,31 +220,45 @@ class JitProgram:
         return tuple(tot)
 
 
-def softmax_lse_argmax_program(rows: int, cols: int) -> JitProgram:
-    """One jit computing softmax, logsumexp and argmax of x[rows, cols] over the last axis.
+def softmax_lse_argmax_jaxpr(rows: int, cols: int):
+    """`(x) => [nn.softmax(x), nn.logsumexp(x, -1), np.argmax(x, -1)]` as the Jaxpr tracing yields:
+    src/library/nn.ts:291-301 (softmax), :332-345 (logsumexp), src/library/numpy.ts:533-556 (argmax;
+    its `arange(n, 0, -1)` is a closed-over constant, here the second input).  `sub` is `add(neg)`
+    and float `div` is `mul(reciprocal)` (src/frontend/core.ts:945-955); a `keepdims` reduction is
+    a Reduce followed by a Reshape (core.ts:271-289)."""
+    from .jaxpr import Builder, Lit
+    b = Builder()
+    x = b.input("x", (rows, cols))
+    iota = b.input("iota", (cols,), I32)
+    keep = (rows, 1)
+    # softmax
+    m1 = b.stop_gradient(b.reshape(b.reduce(x, AluOp.Max, [1], "m1"), keep))
+    u = b.exp(b.add(x, b.neg(m1)), "u")
+    s = b.reshape(b.reduce(u, AluOp.Add, [1], "s"), keep)
+    softmax = b.mul(u, b.reciprocal(s), "softmax")
+    # logsumexp
+    m2 = b.stop_gradient(b.reshape(b.reduce(x, AluOp.Max, [1], "m2"), keep), "m2k")
+    s2 = b.reshape(b.reduce(b.exp(b.add(x, b.neg(m2))), AluOp.Add, [1], "s2"), keep)
+    lse = b.reshape(b.add(m2, b.log(s2)), (rows,), "lse")
+    # argmax
+    m3 = b.reshape(b.reduce(x, AluOp.Max, [1], "m3"), keep)
+    idx = b.mul(b.cast(b.compare(x, m3, "equal"), I32), b.reshape(iota, (cols,)))
+    argmax = b.add(Lit(cols, I32), b.neg(b.reduce(idx, AluOp.Max, [1])), "argmax")
+    return b.build([softmax, lse, argmax])
 
-    `Jaxpr.simplify` does no common-subexpression elimination (src/frontend/jaxpr.ts:252-257),
-    so the row max is computed three times, once per consumer; inputs: x and the constant
-    arange(cols, 0, -1); outputs: softmax f32[rows, cols], lse f32[rows], argmax i32[rows].
-    """
-    p = JitProgram(inputs=["x", "iota"], outputs=["softmax", "lse", "argmax"])
-    k1 = row_reduce_kernel(rows, cols, AluOp.Max)
-    p.run("m1", k1, ["x"])
-    p.run("u", softmax_exp_kernel(rows, cols), ["x", "m1"])
-    p.free("m1")
-    p.run("s", row_reduce_kernel(rows, cols, AluOp.Add), ["u"])
-    p.run("softmax", softmax_scale_kernel(rows, cols), ["u", "s"])
-    p.free("u")
-    p.free("s")
-    p.run("m2", k1, ["x"])
-    p.run("s2", lse_sum_kernel(rows, cols), ["x", "m2"])
-    p.run("lse", lse_finish_kernel(rows), ["s2", "m2"])
-    p.free("s2")
-    p.free("m2")
-    p.run("m3", k1, ["x"])
-    p.run("argmax", argmax_index_kernel(rows, cols), ["x", "m3", "iota"])
-    p.free("m3")
-    return p
+
+def softmax_lse_argmax_program(rows: int, cols: int) -> JitProgram:
+    """One jit computing softmax, logsumexp and argmax of x[rows, cols] over the last axis, cut into
+    Kernels by the reference's rules (`jaxpr.jit_compile`).
+
+    `Jaxpr.simplify` does no common-subexpression elimination (src/frontend/jaxpr.ts:252-257), so
+    the row max is computed three times, once per consumer.  logsumexp uses its stop-gradient row
+    max twice (in the shift and in the result), which makes that value reach two dispatched
+    Kernels and therefore a Kernel of its own (a copy of `rows` elements; src/frontend/jit.ts:1006-1028).
+    Inputs: x and the constant arange(cols, 0, -1); outputs: softmax f32[rows, cols], lse f32[rows],
+    argmax i32[rows]; ten Kernels."""
+    from .jaxpr import jit_compile
+    return jit_compile(softmax_lse_argmax_jaxpr(rows, cols))
 
 
 def argmax_iota(cols: int) -> np.ndarray:

@@ -43,6 +43,9 @@ VECTORS = [
     {"kind": "matmul", "cite": "test/numpy.test.ts:1518-1532", "a": [[1, 2], [3, 4]], "b": [[5, 6], [7, 8]], "want": [[19, 22], [43, 50]]},
     {"kind": "matmul", "cite": "test/numpy.test.ts:1534-1550", "a": [[1, 2, 3], [4, 5, 6]], "b": [[7, 8], [9, 10], [11, 12]],
      "want": [[58, 64], [139, 154]]},
+    # ---- a jitted two-layer MLP with logSoftmax, end to end (exact) -------------------------------------
+    {"kind": "mlp_predict", "cite": "test/platform-test/node.test.ts:29-58", "dims": [2, 2, 2],
+     "x": [[1, 2], [3, 4]], "params": [[[1, 2], [3, 4]], [1, 2], [[1, 2], [3, 4]], [1, 2]], "want": [[-21, 0], [-41, 0]]},
     # ---- linear algebra routines --------------------------------------------------------------------
     {"kind": "lu", "cite": "test/lax-linalg.test.ts:277-290", "a": [[4, 3], [6, 3]],
      "lu": [[6, 3], [0.6666667, 1.0]], "pivots": [1, 1], "permutation": [1, 0], "rtol": 1e-6},

@@ -90,8 +90,9 @@ CASES = {
     # the 10-class layer of the MLP: forward, weight gradient, back-propagated dot, bias gradient
     "skinny forward": (P.dot_kernel(8192, 10, 2048), "dot-skinny 8192x10x2048"),
     "skinny weight grad": (P.dot_kernel(2048, 10, 8192, a_layout="km"), "dot-skinny-t 2048x10x8192"),
-    "small-k backward": (mlp.backprop_dot_kernel(8192, 2048, 10), "dot-small-k 8192x2048x10"),
-    "bias grad": (mlp.column_sum_kernel(8192, 2048), "reduce-col V=4"),
+    "small-k backward": (P.dot_kernel(8192, 2048, 10), "dot-small-k 8192x2048x10"),
+    "bias grad": (Kernel(1, 2048, AluExp.global_index(F32, 0, 8192 * 2048, AluExp.add(g, AluExp.mul(AluVar.ridx, AluExp.i32(2048)))),
+                         Reduction(F32, AluOp.Add, 8192)), "reduce-col V=4"),
     "skinny f16": (P.dot_kernel(4096, 16, 512, F16, a_layout="km"), "dot-skinny-t"),
     "small-k ragged": (P.dot_kernel(65, 1028, 16, a_layout="km", b_layout="nk"), "dot-small-k"),
 }
@@ -118,7 +119,7 @@ def test_vector_loads_only_where_provably_aligned(lib):
 
 
 def test_unsupported_combination_uses_reference_wording(lib):
-    bad = Kernel(0, 4, AluExp(AluOp.Sub, DType.Bool, [AluExp.bool(True), AluExp.bool(False)]))
+    bad = Kernel(1, 4, AluExp(AluOp.Sub, DType.Bool, [AluExp.global_index(DType.Bool, 0, 4, g), AluExp.bool(False)]))
     with pytest.raises(UnsupportedOpError, match=r"Sub<bool> not supported in cuda backend"):
         check_kernel(bad)
 

@@ -145,6 +145,13 @@ def check(run, v):
         a, b = _arr(v["a"]), _arr(v["b"])
         got = run.kernel(P.dot_kernel(a.shape[0], b.shape[1], a.shape[1]), [a, b]).reshape(a.shape[0], b.shape[1])
         assert got.tolist() == v["want"], v["cite"]
+    elif kind == "mlp_predict":
+        from jax_js_b200 import mlp
+        from jax_js_b200.jaxpr import jit_compile
+        x = _arr(v["x"])
+        prog = jit_compile(mlp.mlp_predict_jaxpr(x.shape[0], v["dims"]))
+        (logp,) = run.program(prog, [x] + [_arr(p) for p in v["params"]])
+        assert logp.view(np.float32).reshape(x.shape[0], -1).tolist() == v["want"], v["cite"]   # toEqual: exact
     elif kind == "lu":
         lu, piv, perm = run.lu(_arr(v["a"]))
         np.testing.assert_allclose(lu, v["lu"], rtol=v["rtol"], err_msg=v["cite"])

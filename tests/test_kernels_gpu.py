@@ -427,15 +427,17 @@ def test_skinny_and_small_k_dots(backend, M, N, K, al, bl, kw):
     assert np.array_equal(run_cuda(backend, k, [A, B, bias][: k.nargs]), got.reshape(-1).astype(np.float32))
 
 
-def test_mlp_backward_dot_through_relu_gate(backend):
-    """dz[b, j] = (sum_k dz_next[b, k] W[j, k]) gated by the activation a[b, j] > 0: the K = 10 kernel of
-    the MLP's backward pass, whose epilogue reads a third array contiguously in gidx."""
-    from jax_js_b200 import mlp
+def test_small_k_dot_with_a_gate_in_its_epilogue(backend):
+    """dz[b, j] = (sum_k dz_next[b, k] W[j, k]) gated by a third array a[b, j] > 0: a K = 10 dot whose
+    epilogue reads contiguously in gidx."""
     B, H, C = 515, 2048, 10
     rng = np.random.default_rng(8)
     dz, W = rng.standard_normal((B, C)).astype(np.float32), rng.standard_normal((H, C)).astype(np.float32)
     a = np.maximum(rng.standard_normal((B, H)), 0).astype(np.float32)
-    k = mlp.backprop_dot_kernel(B, H, C)
+    k = P.dot_kernel(B, H, C, b_layout="nk")
+    gate = AluExp.cmplt(AluExp.f32(0), AluExp.global_index(F32, 2, B * H, AluVar.gidx))
+    k.reduction.epilogue = AluExp.where(gate, AluVar.acc(F32), AluExp.f32(0))
+    k = Kernel(3, k.size, k.exp, k.reduction)
     assert backend.prepare_kernel(k).describe.startswith("dot-small-k")
     got = run_cuda(backend, k, [dz, W, a]).reshape(B, H)
     want = oracle.run_kernel(k, [dz, W, a], fma=True).reshape(B, H)

@@ -78,14 +78,14 @@ def test_per_example_program_matches_float64_model():
     slots = [be.put(x), be.put(y), be.put(np.eye(10, dtype=np.float32))] + [be.put(p) for p in params]
     outs = prog.execute(be, slots)
     loss = be.get(outs[0], "float32")
-    dW1 = be.get(outs[1], "float32", (dims[0], dims[1], B))
-    db2 = be.get(outs[4], "float32", (dims[2], B))
+    dW1 = be.get(outs[1], "float32", (B, dims[0], dims[1]))      # vmap puts the batch axis first
+    db2 = be.get(outs[4], "float32", (B, dims[2]))
     for b in (0, 7, B - 1):
         state = {"t": 0, "mu": [0.0] * 4, "nu": [0.0] * 4}
         want_loss, grads, _ = numpy_mlp_step(params, x[b:b + 1], y[b:b + 1], state)
         assert abs(loss[b] - want_loss) <= 1e-5 * max(abs(want_loss), 1e-3)
-        np.testing.assert_allclose(dW1[:, :, b], grads[0], rtol=1e-4, atol=1e-6)
-        np.testing.assert_allclose(db2[:, b], grads[3], rtol=1e-4, atol=1e-6)
+        np.testing.assert_allclose(dW1[b], grads[0], rtol=1e-4, atol=1e-6)
+        np.testing.assert_allclose(db2[b], grads[3], rtol=1e-4, atol=1e-6)
 
 
 @pytest.mark.parametrize("which", ["config4", "config5", "adam"])
@@ -123,8 +123,8 @@ def _rank_main(rank, world, port, out):
         s = tr.step(sx, sy, world=world)
         losses.append(float(be.get(s, "float32")[0]))
         be.dec_ref(s)
-    # each step summed the leaves layer by layer (last layer first, the loss with it) and joined before Adam
-    assert tr.overlap and be.joined and be.async_calls == [3, 2, 2] * 2, be.async_calls
+    # each step summed loss and bias gradients as one group, then every weight gradient as it appeared
+    assert tr.overlap and be.joined and be.async_calls == [4, 1, 1, 1] * 2, be.async_calls
     if rank == 0:
         np.savez(out, losses=np.array(losses), **{f"p{i}": be.get(s, "float32") for i, s in enumerate(tr.params)})
     dist.destroy_process_group()
@@ -166,6 +166,6 @@ def test_step_list_hooks_and_caller_owned_outputs():
     for got, w in zip(outs, want):
         assert np.array_equal(be.slots[got][0], w)
     runs = [n for kind, n in events if kind == "run"]
-    assert runs == ["m1", "u", "s", "softmax", "m2", "s2", "lse", "m3", "argmax"]
+    assert runs == ["m1", "u", "s", "softmax", "m2", "m2k", "s2", "lse", "m3", "argmax"]
     assert [n for kind, n in events if kind == "out"] == ["softmax", "lse", "argmax"]
     assert events.index(("out", "softmax")) == events.index(("run", "softmax")) + 1

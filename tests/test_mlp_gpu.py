@@ -192,3 +192,57 @@ def test_config5_shard_gradients_against_float64(backend):
         assert (err <= 1e-4 * scale).mean() >= 0.95, f"d{name}"
         assert err.max() <= 1e-2 * scale, f"d{name}"
         assert err.mean() <= 3e-5 * scale, f"d{name}"
+
+
+def test_config5_shard_against_the_oracle(backend):
+    """One gradient program and one Adam program at the benchmark's own shard: 784-2048-2048-10 with the
+    8192 examples one of eight GPUs sees, global batch 65536, against the oracle replaying the same
+    Kernel list on the same inputs."""
+    dims, B, GB = [784, 2048, 2048, 10], 8192, 65536
+    x, y = _data(B, dims[0], dims[-1], 3)
+    params = mlp.init_params(dims, 0)
+    params[1] = params[1] + 0.01
+    eye = np.eye(10, dtype=np.float32)
+    prog = mlp.mlp_grad_program(B, dims, global_batch=GB)
+    ob = OracleBackend(fma=True)
+    res = {}
+    for key, be in (("cuda", backend), ("oracle", ob)):
+        slots = [be.put(x), be.put(y), be.put(eye)] + [be.put(p) for p in params]
+        outs = prog.execute(be, slots)
+        res[key] = [be.get(s, "float32").astype(np.float64) for s in outs]
+        for s in slots + outs:
+            be.dec_ref(s)
+    # hidden units within f32 summation error of zero may take their ReLU gate either way (see
+    # test_each_step_from_the_oracle_state); count them in float64
+    h, edge = x.astype(np.float64), 0
+    for l in range(2):
+        z = h @ params[2 * l].astype(np.float64) + params[2 * l + 1].astype(np.float64)
+        edge += int((np.abs(z) < 4e-6).sum())
+        h = np.maximum(z, 0)
+    assert abs(res["cuda"][0][0] - res["oracle"][0][0]) <= 1e-5 * abs(res["oracle"][0][0])
+    for name, got, want in zip(mlp.param_order(3), res["cuda"][1:], res["oracle"][1:]):
+        scale = np.abs(want).max()
+        err = np.abs(got - want)
+        # f32, GEMM-dominated: 1e-4 of the leaf's scale for every element; a unit on the edge moves one
+        # example's share (1/8192 of a column) of the gradient, far inside the same bar at this batch
+        assert err.max() <= 1e-4 * scale, (name, err.max(), scale, edge)
+        assert np.median(err) <= 1e-5 * scale, (name, np.median(err), scale)
+    # Adam on the oracle's gradients: elementwise, 1e-5
+    sizes, names = mlp.leaf_sizes(dims), mlp.param_order(3)
+    adam = mlp.adam_program(sizes, names)
+    grads = [g.astype(np.float32) for g in res["oracle"][1:]]
+    rng = np.random.default_rng(4)
+    mu = [(rng.standard_normal(n) * 1e-4).astype(np.float32) for n in sizes]
+    nu = [(rng.uniform(0, 1, n) * 1e-8).astype(np.float32) for n in sizes]
+    new = {}
+    for key, be in (("cuda", backend), ("oracle", ob)):
+        ins = [be.put(np.array([6], np.uint32))]
+        for i in range(len(names)):
+            ins += [be.put(params[i]), be.put(grads[i]), be.put(mu[i]), be.put(nu[i])]
+        outs = adam.execute(be, ins)
+        assert be.get(outs[0], "uint32")[0] == 7
+        new[key] = [be.get(s, "float32").astype(np.float64) for s in outs[1:]]
+        for s in ins + outs:
+            be.dec_ref(s)
+    for got, want in zip(new["cuda"], new["oracle"]):
+        assert (np.abs(got - want) <= 1e-5 * np.maximum(np.abs(want), 1e-3)).all()
