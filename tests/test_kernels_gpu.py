@@ -171,7 +171,7 @@ def test_float64_and_float16_elementwise(backend):
 
 def test_unsupported_op_is_reported_not_emulated(backend):
     # UnsupportedOpError wording of src/backend.ts:228-234; nothing falls back to the host
-    bad = Kernel(0, 4, AluExp(AluOp.Sub, BOOL, [AluExp.bool(True), AluExp.bool(False)]))
+    bad = Kernel(1, 4, AluExp(AluOp.Sub, BOOL, [AluExp.global_index(BOOL, 0, 4, g), AluExp.bool(False)]))
     with pytest.raises(UnsupportedOpError, match=r"Sub<bool> not supported in cuda backend"):
         backend.prepare_kernel(bad)
 
