@@ -145,13 +145,35 @@ uint64_t jaxcuda_launch_count(jaxcuda_ctx* ctx);
  * belongs to the graph until it is destroyed, so slots that are still alive at capture_end (the
  * step's outputs) keep their addresses and are rewritten in place by every launch.  Dispatch each
  * program eagerly at least once before capturing it.  read / sync / event_record are refused
- * inside a capture. */
+ * inside a capture.
+ *
+ * Because a captured list is in hand as a whole, runs of consecutive Kernels that walk the rows of
+ * one [rows, cols] array (row reductions, elementwise Kernels over rows*cols and per-row Kernels,
+ * the shape in which softmax, logsumexp and argmax arrive: src/library/nn.ts:291-345,
+ * src/library/numpy.ts:533-556) are replaced by one row-resident kernel that reads every outside
+ * array once and writes only the slots still alive when the run ends; a Kernel repeated on the same
+ * arrays is computed once.  Results are those of the separate Kernels up to the summation order
+ * of the row reductions.  JAXCUDA_FUSE=0 in the environment turns the replacement off. */
 int jaxcuda_capture_begin(jaxcuda_ctx* ctx);
 int jaxcuda_capture_end(jaxcuda_ctx* ctx, jaxcuda_graph** out);
 int jaxcuda_graph_launch(jaxcuda_ctx* ctx, jaxcuda_graph* graph);
 int jaxcuda_graph_destroy(jaxcuda_ctx* ctx, jaxcuda_graph* graph);
+/* What one launch of the graph does: kernels launched, their algorithmic bytes (distinct bytes each
+ * kernel reads plus bytes it writes; a fused kernel counts its own), and how many runs were fused.
+ * Any pointer may be null.  Plays the part of `JitProgram.toString()` (src/frontend/jit.ts:466). */
+int jaxcuda_graph_cost(jaxcuda_graph* graph, uint64_t* launches, double* algo_bytes, int* fused_groups);
 /* Device-to-device copy between two slots of equal size, in stream order (capturable). */
 int jaxcuda_copy(jaxcuda_ctx* ctx, jaxcuda_slot dst, jaxcuda_slot src);
+
+/* Diagnostic that needs no GPU: what a capture would launch for a list of n Kernels.  Kernel i has
+ * n_inputs[i] entries of `inputs` (array ids, consecutive over the list) and writes array outputs[i];
+ * output_freed[i] != 0 says that this output's slot is released before the capture ends (an
+ * intermediate of the step list).  `report` receives one line per launch: the positions it covers
+ * and its plan; `message` the error text or, when compile == 0, the CUDA C of the fused kernels.
+ * Used by CPU-side tests; no counterpart in the reference. */
+int jaxcuda_check_step_list(int n, const uint8_t* const* irs, const size_t* lens, const int* n_inputs, const int* inputs,
+                            const int* outputs, const uint8_t* output_freed, int compile, char* report, size_t report_len,
+                            char* message, size_t message_len);
 
 /* Interop for host code that shares the CUDA primary context (torch): raw pointer of a slot and
  * the stream handle (cudaStream_t) as integers.  No counterpart in the reference. */

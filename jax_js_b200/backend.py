@@ -62,6 +62,7 @@ SYMBOLS = {
     "jaxcuda_destroy": (_I, [_P]),
     "jaxcuda_last_error": (ctypes.c_char_p, [_P]),
     "jaxcuda_max_args": (_I, []),
+    "jaxcuda_check_step_list": (_I, None),
     "jaxcuda_malloc": (_I, [_P, _SZ, _P, _SZ, ctypes.POINTER(_U32)]),
     "jaxcuda_incref": (_I, [_P, _U32]),
     "jaxcuda_decref": (_I, [_P, _U32]),
@@ -97,6 +98,7 @@ SYMBOLS = {
     "jaxcuda_capture_end": (_I, [_P, ctypes.POINTER(_P)]),
     "jaxcuda_graph_launch": (_I, [_P, _P]),
     "jaxcuda_graph_destroy": (_I, [_P, _P]),
+    "jaxcuda_graph_cost": (_I, [_P, ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_int)]),
     "jaxcuda_copy": (_I, [_P, _U32, _U32]),
     "jaxcuda_sort_no_alloc": (_I, [_P, _I, _P, _P, ctypes.c_int64, ctypes.c_int64, ctypes.c_char_p, _SZ]),
 }
@@ -130,6 +132,42 @@ def check_kernel(kernel: Kernel, *, sm_count: int = 148, force_skeleton: int = -
     if rc != OK:
         _raise(rc, msg.value.decode())
     return desc.value.decode(), source
+
+
+def check_step_list(program, *, compile: bool = True):
+    """What a capture of `program` (a `JitProgram`) would launch, without a GPU: returns (report
+    lines, CUDA C of the fused kernels).  An output counts as released inside the capture when the
+    step list frees it."""
+    lib = load_library()
+    ids: dict = {}
+    freed = {s.name for s in program.steps if s.kind == "free"}
+    images, n_in, ins, outs, flags = [], [], [], [], []
+    for s in program.steps:
+        if s.kind != "execute":
+            continue
+        images.append(s.kernel.serialize())
+        n_in.append(len(s.inputs))
+        ins += [ids.setdefault(n, len(ids)) for n in s.inputs]
+        outs.append(ids.setdefault(s.name, len(ids)))
+        flags.append(1 if s.name in freed else 0)
+    n = len(images)
+    arr = (ctypes.c_char_p * n)(*images)
+    lens = (ctypes.c_size_t * n)(*[len(i) for i in images])
+    rep = ctypes.create_string_buffer(1 << 16)
+    msg = ctypes.create_string_buffer(1 << 22)
+    lib.jaxcuda_check_step_list.restype = ctypes.c_int
+    lib.jaxcuda_check_step_list.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_char_p), ctypes.POINTER(ctypes.c_size_t),
+                                            ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int),
+                                            ctypes.c_char_p, ctypes.c_int, ctypes.c_char_p, ctypes.c_size_t, ctypes.c_char_p, ctypes.c_size_t]
+    source = ""
+    for comp in ((0, 1) if compile else (0,)):
+        rc = lib.jaxcuda_check_step_list(n, arr, lens, (ctypes.c_int * n)(*n_in), (ctypes.c_int * max(1, len(ins)))(*ins),
+                                         (ctypes.c_int * n)(*outs), bytes(flags), comp, rep, len(rep), msg, len(msg))
+        if rc != OK:
+            _raise(rc, msg.value.decode())
+        if comp == 0:
+            source = msg.value.decode()
+    return rep.value.decode().splitlines(), source
 
 
 def _raise(status: int, message: str):
@@ -383,6 +421,12 @@ class CudaBackend:
 
     def graph_launch(self, graph: int) -> None:
         self._check(self._lib.jaxcuda_graph_launch(self._ctx, graph))
+
+    def graph_cost(self, graph: int) -> tuple:
+        """(kernel launches, algorithmic bytes, fused runs) of one launch of the graph."""
+        n, b, f = ctypes.c_uint64(), ctypes.c_double(), ctypes.c_int()
+        self._check(self._lib.jaxcuda_graph_cost(graph, ctypes.byref(n), ctypes.byref(b), ctypes.byref(f)))
+        return n.value, b.value, f.value
 
     def graph_destroy(self, graph: int) -> None:
         self._check(self._lib.jaxcuda_graph_destroy(self._ctx, graph))

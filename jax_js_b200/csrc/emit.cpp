@@ -1195,4 +1195,294 @@ Plan make_plan(const KernelIR& k, const Options& opt) {
   return b.build();
 }
 
+// ---- row programs: several Kernels over the rows of one array as one kernel -------------------
+
+namespace {
+
+enum RowLoad { RL_BAD = 0, RL_BIG, RL_VEC, RL_COL, RL_SCALAR };
+
+// How a load addresses its argument in terms of (row, column).  `row_index` is true where gidx is
+// the row itself: in a per-row Kernel and in the epilogue of a row reduction.
+RowLoad classify_row_load(RowStageType type, bool row_index, const Node& nd, const std::optional<Affine>& ix, int64_t R,
+                          int64_t C) {
+  if (!ix || dtype_bytes(nd.dtype) != 4) return RL_BAD;
+  const int64_t len = nd.arg1;
+  if (ix->terms.empty()) return (ix->c0 >= 0 && ix->c0 < len) ? RL_SCALAR : RL_BAD;
+  if (ix->c0 != 0) return RL_BAD;
+  auto is = [&](size_t i, int var, int64_t div, int64_t mod, int64_t coef) {
+    const Term& t = ix->terms[i];
+    return t.var == var && t.div == div && t.mod == mod && t.coef == coef;
+  };
+  const size_t n = ix->terms.size();
+  if (row_index || type == RS_PER_ROW) return (n == 1 && is(0, 0, 1, 0, 1) && len >= R) ? RL_VEC : RL_BAD;
+  if (type == RS_REDUCE) {
+    if (n == 2 && ((is(0, 0, 1, 0, C) && is(1, 1, 1, 0, 1)) || (is(1, 0, 1, 0, C) && is(0, 1, 1, 0, 1))))
+      return len == R * C ? RL_BIG : RL_BAD;
+    if (n == 1 && is(0, 0, 1, 0, 1)) return len >= R ? RL_VEC : RL_BAD;
+    if (n == 1 && is(0, 1, 1, 0, 1)) return len >= C ? RL_COL : RL_BAD;
+    return RL_BAD;
+  }
+  if (n != 1) return RL_BAD;
+  if (is(0, 0, 1, 0, 1)) return len == R * C ? RL_BIG : RL_BAD;   // gidx
+  if (is(0, 0, C, 0, 1)) return len >= R ? RL_VEC : RL_BAD;       // gidx / cols
+  if (is(0, 0, 1, C, 1)) return len >= C ? RL_COL : RL_BAD;       // gidx % cols
+  return RL_BAD;
+}
+
+bool four_byte_nodes(const std::vector<Node>& nodes) {
+  for (const Node& nd : nodes)
+    if (dtype_bytes(nd.dtype) != 4) return false;
+  return true;
+}
+
+// The nodes a root needs, not descending into the index of a load (every load of a row program is
+// replaced by a register or by a (row, column) access).
+std::vector<char> closure_above_loads(const std::vector<Node>& nodes, size_t root) {
+  std::vector<char> m(nodes.size(), 0);
+  m[root] = 1;
+  for (size_t i = root + 1; i-- > 0;)
+    if (m[i] && nodes[i].op != JAXCUDA_OP_GLOBALINDEX)
+      for (uint32_t s = 0; s < nodes[i].nsrc; s++) m[nodes[i].src[s]] = 1;
+  return m;
+}
+
+}  // namespace
+
+RowStageType row_stage_type(const KernelIR& k, int64_t R, int64_t C) {
+  if (R < 2 || C < 2 || R * C >= (int64_t)1 << 31) return RS_NONE;
+  if (!four_byte_nodes(k.exp) || (k.has_red && !four_byte_nodes(k.epi))) return RS_NONE;
+  RowStageType type;
+  if (k.has_red) {
+    if ((int64_t)k.size != R || (int64_t)k.red_size != C || dtype_bytes(k.red_dtype) != 4) return RS_NONE;
+    type = RS_REDUCE;
+  } else if ((int64_t)k.size == R * C) {
+    type = RS_ELEMENTWISE;
+  } else if ((int64_t)k.size == R) {
+    type = RS_PER_ROW;
+  } else {
+    return RS_NONE;
+  }
+  const Analysis an = analyze(k.exp, k.size, k.has_red ? k.red_size : 0);
+  for (size_t i = 0; i < k.exp.size(); i++)
+    if (k.exp[i].op == JAXCUDA_OP_GLOBALINDEX &&
+        classify_row_load(type, false, k.exp[i], an.affine[k.exp[i].src[0]], R, C) == RL_BAD)
+      return RS_NONE;
+  if (k.has_red) {
+    const Analysis ae = analyze(k.epi, k.size, 0);
+    for (size_t i = 0; i < k.epi.size(); i++)
+      if (k.epi[i].op == JAXCUDA_OP_GLOBALINDEX &&
+          classify_row_load(type, true, k.epi[i], ae.affine[k.epi[i].src[0]], R, C) == RL_BAD)
+        return RS_NONE;
+  }
+  return type;
+}
+
+bool plan_row_fusion(const std::vector<FuseStage>& stages, const std::vector<FuseBuffer>& bufs, int64_t R, int64_t C,
+                     const Options& opt, Plan& plan, std::vector<int>& params, std::string& why) {
+  auto no = [&](const std::string& m) { why = m; return false; };
+  if (C % 4) return no("cols is not a multiple of 4");
+  const int64_t chunks = C / 4;   // 128-bit pieces of a row
+  int T = 32;
+  while (T < 1024 && (int64_t)T * 4 < chunks) T *= 2;
+  const int E = (int)((chunks + T - 1) / T);
+  if (E > 4) return no("row too long for one CTA's registers");
+  const int NW = T / 32;
+
+  // what every buffer is inside the program
+  const int nb = (int)bufs.size();
+  std::vector<int> kind(nb, 0);         // 1: rows x cols, 2: one value per row (produced inside)
+  std::vector<uint32_t> dtype(nb, JAXCUDA_F32);
+  std::vector<char> produced(nb, 0), read_later(nb, 0), preload(nb, 0), used(nb, 0);
+  std::vector<double> ext_bytes(nb, 0.0);   // what the program reads of every outside array
+  std::vector<RowStageType> types(stages.size());
+  for (size_t s = 0; s < stages.size(); s++) {
+    const KernelIR& k = *stages[s].ir;
+    types[s] = row_stage_type(k, R, C);
+    if (types[s] == RS_NONE) return no("stage " + S((int64_t)s) + " is not a row stage");
+  }
+  struct LoadRef { RowLoad how; int buf; };
+  std::vector<std::map<size_t, LoadRef>> exp_loads(stages.size()), epi_loads(stages.size());
+  for (size_t s = 0; s < stages.size(); s++) {
+    const KernelIR& k = *stages[s].ir;
+    auto scan = [&](const std::vector<Node>& nodes, bool epi, std::map<size_t, LoadRef>& out) -> bool {
+      const Analysis an = analyze(nodes, k.size, (!epi && k.has_red) ? k.red_size : 0);
+      for (size_t i = 0; i < nodes.size(); i++) {
+        const Node& nd = nodes[i];
+        if (nd.op != JAXCUDA_OP_GLOBALINDEX) continue;
+        const RowLoad how = classify_row_load(types[s], epi, nd, an.affine[nd.src[0]], R, C);
+        const int b = stages[s].in_buf[nd.arg0];
+        used[b] = 1;
+        if (produced[b]) {
+          if ((kind[b] == 1 && how != RL_BIG) || (kind[b] == 2 && how != RL_VEC)) return false;
+          if (dtype[b] != nd.dtype) return false;
+          read_later[b] = 1;
+        } else {
+          if (!bufs[b].external) return false;
+          ext_bytes[b] = std::max(ext_bytes[b], how == RL_BIG ? (double)R * C * 4 : how == RL_VEC ? (double)R * 4
+                                                : how == RL_COL ? (double)C * 4 : 4.0);
+          if (how == RL_BIG) {
+            if (preload[b] && dtype[b] != nd.dtype) return false;
+            preload[b] = 1;
+            dtype[b] = nd.dtype;
+          }
+        }
+        out[i] = LoadRef{how, b};
+      }
+      return true;
+    };
+    if (!scan(k.exp, false, exp_loads[s])) return no("a load of stage " + S((int64_t)s) + " does not match its producer");
+    if (k.has_red && !scan(k.epi, true, epi_loads[s])) return no("an epilogue load of stage " + S((int64_t)s) + " does not match its producer");
+    const int ob = stages[s].out_buf;
+    if (bufs[ob].external && used[ob]) return no("a stage overwrites an array the program reads");
+    produced[ob] = 1;
+    kind[ob] = types[s] == RS_ELEMENTWISE ? 1 : 2;
+    dtype[ob] = k.out_dtype();
+  }
+  int arrays = 0;
+  for (int b = 0; b < nb; b++) arrays += preload[b] || (produced[b] && kind[b] == 1 && read_later[b]);
+  if (arrays * E > 16) return no("too many rows x cols arrays live at once");
+
+  params.clear();
+  for (int b = 0; b < nb; b++)
+    if ((bufs[b].external && used[b]) || (produced[b] && bufs[b].store)) params.push_back(b);
+
+  const double work = (double)R * (double)C;
+  const bool exact = opt.exact_math == 1 || (opt.exact_math < 0 && work < opt.exact_math_work);
+  std::ostringstream os;
+  os << (exact ? "#define JX_EXACT_TRANSCENDENTALS 1\n" : "") << "#define JX_LD_HINT " << opt.ld_hint << "\n" << kPrelude;
+  os << "extern \"C\" __global__ void __launch_bounds__(" << T << ") jx_rowfuse(";
+  for (size_t i = 0; i < params.size(); i++) {
+    const int b = params[i];
+    const bool written = produced[b] && bufs[b].store;
+    os << (i ? ", " : "") << (written ? "" : "const ") << "void* __restrict__ b" << b;
+  }
+  os << ") {\n";
+  os << "  const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;\n";
+  os << "  (void)lane; (void)warp;\n";
+  const std::string row_off = "(size_t)row * " + S(C);
+  auto loop_open = [&](const std::string& ind) {
+    os << ind << "#pragma unroll\n" << ind << "for (int e = 0; e < " << E << "; e++) {\n";
+    os << ind << "  const int c0 = (e * " << T << " + tid) * 4;\n";
+    os << ind << "  if (c0 < " << C << ") {\n";
+  };
+  auto loop_close = [&](const std::string& ind) { os << ind << "  }\n" << ind << "}\n"; };
+  // register arrays and per-row values
+  for (int b = 0; b < nb; b++) {
+    if (preload[b] || (produced[b] && kind[b] == 1 && read_later[b])) os << "  " << ctype(dtype[b]) << " B" << b << "[" << E * 4 << "];\n";
+    if (produced[b] && kind[b] == 2) os << "  " << ctype(dtype[b]) << " v" << b << ";\n";
+  }
+  for (int b = 0; b < nb; b++) {
+    if (!preload[b]) continue;
+    loop_open("  ");
+    os << "      jx_pack<" << ptype(dtype[b]) << ", 4> t;\n";
+    os << "      jx_load(t, (const " << ptype(dtype[b]) << "*)b" << b << " + " << row_off << " + c0);\n";
+    os << "      #pragma unroll\n      for (int j = 0; j < 4; j++) B" << b << "[e * 4 + j] = t.e[j];\n";
+    loop_close("  ");
+  }
+  auto overrides = [&](const std::map<size_t, LoadRef>& loads, const std::vector<Node>& nodes, const std::string& col,
+                       std::map<size_t, std::string>& ov) {
+    for (const auto& kv : loads) {
+      const Node& nd = nodes[kv.first];
+      const int b = kv.second.buf;
+      const std::string ptr = std::string("((const ") + ptype(nd.dtype) + "*)b" + S(b) + ")";
+      switch (kv.second.how) {
+        case RL_BIG: ov[kv.first] = "B" + S(b) + "[e * 4 + j]"; break;
+        case RL_VEC: ov[kv.first] = produced[b] ? "v" + S(b) : ptr + "[row]"; break;
+        case RL_COL: ov[kv.first] = ptr + "[" + col + "]"; break;
+        default: {
+          const Analysis an = analyze(nodes, 1, 0);
+          ov[kv.first] = ptr + "[" + S(an.affine[nd.src[0]] ? an.affine[nd.src[0]]->c0 : 0) + "]";
+        }
+      }
+    }
+  };
+  // `produced` now restarts: a value is "in registers" only from its producing stage on
+  std::fill(produced.begin(), produced.end(), 0);
+  double bytes = 0;
+  for (int b = 0; b < nb; b++) bytes += ext_bytes[b];
+  for (size_t s = 0; s < stages.size(); s++) {
+    const KernelIR& k = *stages[s].ir;
+    const int ob = stages[s].out_buf;
+    const uint32_t odt = k.out_dtype();
+    const Analysis an = analyze(k.exp, k.size, k.has_red ? k.red_size : 0);
+    const size_t root = k.exp.size() - 1;
+    const std::vector<char> want = closure_above_loads(k.exp, root);
+    std::map<size_t, std::string> ov;
+    Env env;
+    env.prefix = "s" + S((int64_t)s) + "_";
+    env.load_override = &ov;
+    os << "  {  // stage " << s << "\n";
+    if (types[s] == RS_REDUCE) {
+      overrides(exp_loads[s], k.exp, "ridx", ov);
+      const char* AT = ctype(k.red_dtype);
+      auto red = [&](const std::string& a, const std::string& b) { return binary_expr(k.red_op, k.red_dtype, a, b, 0, nullptr); };
+      os << "    " << AT << " acc = " << identity_literal(k.red_op, k.red_dtype) << ";\n";
+      env.gidx = "row";
+      loop_open("    ");
+      os << "        #pragma unroll\n        for (int j = 0; j < 4; j++) {\n          const int ridx = c0 + j;\n";
+      std::vector<std::string> names(k.exp.size());
+      emit_nodes(os, k.exp, an, names, want, env, "          ");
+      os << "          acc = " << red("acc", names[root]) << ";\n        }\n";
+      loop_close("    ");
+      os << "    #pragma unroll\n    for (int o = 16; o > 0; o >>= 1) { const " << AT
+         << " v = __shfl_xor_sync(0xffffffffu, acc, o); acc = " << red("acc", "v") << "; }\n";
+      if (NW > 1) {
+        os << "    __shared__ " << AT << " sm" << s << "[" << NW << "];\n";
+        os << "    if (lane == 0) sm" << s << "[warp] = acc;\n    __syncthreads();\n";
+        os << "    acc = sm" << s << "[0];\n";
+        os << "    #pragma unroll\n    for (int w = 1; w < " << NW << "; w++) acc = " << red("acc", "sm" + S((int64_t)s) + "[w]") << ";\n";
+      }
+      const Analysis ae = analyze(k.epi, k.size, 0);
+      std::map<size_t, std::string> eov;
+      overrides(epi_loads[s], k.epi, "0", eov);
+      Env ee;
+      ee.prefix = "s" + S((int64_t)s) + "e_";
+      ee.gidx = "row";
+      ee.load_override = &eov;
+      std::vector<std::string> en(k.epi.size());
+      emit_nodes(os, k.epi, ae, en, closure_above_loads(k.epi, k.epi.size() - 1), ee, "    ");
+      os << "    v" << ob << " = " << en.back() << ";\n";
+    } else if (types[s] == RS_PER_ROW) {
+      overrides(exp_loads[s], k.exp, "0", ov);
+      env.gidx = "row";
+      std::vector<std::string> names(k.exp.size());
+      emit_nodes(os, k.exp, an, names, want, env, "    ");
+      os << "    v" << ob << " = " << names[root] << ";\n";
+    } else {
+      overrides(exp_loads[s], k.exp, "cidx", ov);
+      const bool keep = read_later[ob];
+      loop_open("    ");
+      os << "        jx_pack<" << ptype(odt) << ", 4> o;\n";
+      os << "        #pragma unroll\n        for (int j = 0; j < 4; j++) {\n";
+      os << "          const int cidx = c0 + j;\n          const int gidx = row * " << C << " + cidx;\n          (void)gidx;\n";
+      std::vector<std::string> names(k.exp.size());
+      emit_nodes(os, k.exp, an, names, want, env, "          ");
+      os << "          o.e[j] = " << names[root] << ";\n";
+      if (keep) os << "          B" << ob << "[e * 4 + j] = " << names[root] << ";\n";
+      os << "        }\n";
+      if (bufs[ob].store) os << "        jx_store((" << ptype(odt) << "*)b" << ob << " + " << row_off << " + c0, o);\n";
+      loop_close("    ");
+    }
+    if (types[s] != RS_ELEMENTWISE && bufs[ob].store)
+      os << "    if (tid == 0) ((" << ptype(odt) << "*)b" << ob << ")[row] = v" << ob << ";\n";
+    os << "  }\n";
+    produced[ob] = 1;
+    if (bufs[ob].store) bytes += types[s] == RS_ELEMENTWISE ? (double)R * C * 4 : (double)R * 4;
+  }
+  os << "}\n";
+
+  plan = Plan();
+  plan.skeleton = SK_ELEMENTWISE;
+  plan.source = os.str();
+  Stage st;
+  st.entry = "jx_rowfuse";
+  st.grid[0] = (unsigned)R;
+  st.block[0] = (unsigned)T;
+  plan.stages.push_back(st);
+  plan.algo_bytes = bytes;
+  plan.algo_flops = 0;
+  plan.describe = "row-fused " + S((int64_t)stages.size()) + " kernels rows=" + S(R) + " cols=" + S(C) + " T=" + S(T) + " E=" + S(E);
+  return true;
+}
+
 }  // namespace jaxcuda

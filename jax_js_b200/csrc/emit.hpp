@@ -82,6 +82,35 @@ struct Options {
 // ("Op<dtype> not supported in cuda backend") for combinations that cannot be emitted.
 Plan make_plan(const KernelIR& k, const Options& opt);
 
+// ---- several Kernels of one step list as one row-resident kernel ---------------------------------
+//
+// `jit` hands over softmax, logsumexp or argmax over the last axis as chains of Kernels that all
+// walk the same [rows, cols] array: row reductions (size rows, reduction size cols), elementwise
+// Kernels over rows*cols elements and per-row Kernels over rows elements (src/library/nn.ts:291-345,
+// src/frontend/jit.ts:833-885 for why the frontend cannot fuse them).  A captured step list is in
+// hand as a whole, so a run of such Kernels is replaced by one kernel: a CTA per row keeps the row
+// and every intermediate in registers, reads each outside array once and writes only what lives on.
+enum RowStageType { RS_NONE = 0, RS_REDUCE = 1, RS_ELEMENTWISE = 2, RS_PER_ROW = 3 };
+
+// Can this Kernel be a stage of a row program over [rows, cols]?
+RowStageType row_stage_type(const KernelIR& k, int64_t rows, int64_t cols);
+
+struct FuseStage {
+  const KernelIR* ir = nullptr;
+  std::vector<int> in_buf;  // per Kernel argument: index into the buffer table
+  int out_buf = -1;
+};
+struct FuseBuffer {
+  bool external = false;  // holds data before the first stage: read from global memory
+  bool store = false;     // lives on after the last stage: written to global memory
+  size_t bytes = 0;
+};
+
+// Builds the fused kernel.  `params` lists the buffers that become pointer parameters, in order.
+// Returns false (with a reason) where the stages do not fit the row program.
+bool plan_row_fusion(const std::vector<FuseStage>& stages, const std::vector<FuseBuffer>& bufs, int64_t rows, int64_t cols,
+                     const Options& opt, Plan& plan, std::vector<int>& params, std::string& why);
+
 // Implemented in gemm_tc.cpp: rewrites `plan` to the tcgen05 skeleton when `g` qualifies.
 bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan& plan,
                   const std::string& epilogue_body, const std::string& params_decl,

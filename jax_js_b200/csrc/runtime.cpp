@@ -30,6 +30,8 @@
 #include "linalg.hpp"
 #include "fft.hpp"
 
+#include <sstream>
+
 extern "C" size_t jaxcuda_sort_work_bytes(int argsort, int64_t batch, int64_t n);
 extern "C" int jaxcuda_sort_launch(void* stream, int argsort, const void* x, void* y, int32_t* yi, int dtype,
                                    int64_t batch, int64_t n, void* work, int* launches);
@@ -179,6 +181,7 @@ struct jaxcuda_exe {
   std::vector<int> rt_factors;    // Fft
   std::string describe;
   void* persistent_scratch = nullptr;  // zero-initialised once; reused by every dispatch (stream-ordered)
+  std::vector<int> fuse_params;        // row program: buffer (of the group's table) behind each pointer parameter
 };
 
 struct jaxcuda_graph {
@@ -187,12 +190,31 @@ struct jaxcuda_graph {
   cudaGraph_t graph = nullptr;
   cudaGraphExec_t exec = nullptr;
   uint64_t kernels = 0;  // kernel launches recorded in the graph
+  double algo_bytes = 0;  // algorithmic bytes of those launches (a fused kernel counts what it reads and writes itself)
+  int fused_groups = 0;
+};
+
+// A Kernel dispatched inside a capture is not launched at once: the list is kept until something
+// other than a Kernel needs the stream (or the capture ends), so that runs of Kernels over the rows
+// of one array can be replaced by one row-resident kernel (emit.hpp, plan_row_fusion).
+struct PendingDispatch {
+  jaxcuda_exe* exe = nullptr;
+  std::vector<void*> in;
+  std::vector<size_t> in_bytes;
+  void* out = nullptr;
+  size_t out_bytes = 0;
+  bool out_freed = false;  // the output's slot was released before the list was flushed: nobody else can read it
 };
 
 struct jaxcuda_ctx {
   int device = 0;
   int next_graph_id = 1;
   uint64_t capture_launches0 = 0;
+  std::vector<PendingDispatch> pending;
+  bool fuse_rows = true;          // JAXCUDA_FUSE=0: captured Kernels are launched one by one
+  double capture_bytes = 0;
+  int capture_groups = 0;
+  std::map<std::string, std::unique_ptr<jaxcuda_exe>> fused;  // compiled row programs by wiring
   cudaStream_t stream = nullptr;
   Driver drv;
   Allocator alloc;
@@ -342,6 +364,9 @@ int env_int(const char* name, int dflt) {
 
 }  // namespace
 
+static int launch_kernel(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const std::vector<void*>& inptr, void* outptr);
+static int flush_pending(jaxcuda_ctx* ctx);
+
 extern "C" {
 
 int jaxcuda_max_args(void) { return 64; }
@@ -393,6 +418,7 @@ int jaxcuda_create(int device, jaxcuda_ctx** out) {
   ctx->comm_sms = env_int("JAXCUDA_COMM_SMS", ctx->comm_sms);
   ctx->opt.tc_bn = env_int("JAXCUDA_TC_BN", 0);
   ctx->sweep_alternate = env_int("JAXCUDA_SWEEP", 1) != 0;
+  ctx->fuse_rows = env_int("JAXCUDA_FUSE", 1) != 0;
   ctx->debug = env_int("JAXCUDA_DEBUG", 0);
   *out = ctx.release();
   return JAXCUDA_OK;
@@ -469,6 +495,8 @@ int jaxcuda_decref(jaxcuda_ctx* ctx, jaxcuda_slot slot) {
   SlotRec* s = find_slot(ctx, slot);
   if (!s) return slot_error(ctx, slot);
   if (--s->refs == 0) {
+    for (size_t i = ctx->pending.size(); i-- > 0;)   // the latest pending writer of this block produced it
+      if (ctx->pending[i].out == s->ptr) { ctx->pending[i].out_freed = true; break; }
     if (s->ptr) ctx->alloc.put(s->ptr, s->bytes);
     ctx->slots.erase(slot);
   }
@@ -873,6 +901,8 @@ int jaxcuda_dispatch(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const jaxcuda_slot* inp
   for (int i = 0; i < n_inputs; i++) if (!(in[i] = find_slot(ctx, inputs[i]))) return slot_error(ctx, inputs[i]);
   for (int i = 0; i < n_outputs; i++) if (!(outv[i] = find_slot(ctx, outputs[i]))) return slot_error(ctx, outputs[i]);
 
+  if (exe->kind != 0)
+    if (int rc = flush_pending(ctx)) return rc;
   if (exe->kind == 3) {  // Scatter
     const jaxcuda_scatter_desc& d = exe->scatter;
     if (n_inputs != 1 + d.n_index || n_outputs != 1) return fail(ctx, JAXCUDA_EINVAL, "Scatter called with wrong slot counts");
@@ -974,7 +1004,30 @@ int jaxcuda_dispatch(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const jaxcuda_slot* inp
     if (in[i]->ptr && in[i]->ptr == outv[0]->ptr)
       return fail(ctx, JAXCUDA_EINVAL, "output slot %u is also input %d; kernels read inputs through the read-only path", outputs[0], i);
   if (k.size == 0) return JAXCUDA_OK;
+  std::vector<void*> inptr(n_inputs);
+  for (int i = 0; i < n_inputs; i++) inptr[i] = in[i]->ptr;
+  if (ctx->alloc.capturing && ctx->fuse_rows && exe->plan.skeleton != SK_GEMM_TC) {
+    if (exe->plan.scratch_bytes && exe->plan.scratch_persistent && !exe->persistent_scratch)
+      return fail(ctx, JAXCUDA_EINVAL, "dispatch the program once before capturing it: a kernel still has to set up its arrival counters");
+    PendingDispatch pd;
+    pd.exe = exe;
+    pd.in = inptr;
+    for (int i = 0; i < n_inputs; i++) pd.in_bytes.push_back(in[i]->bytes);
+    pd.out = outv[0]->ptr;
+    pd.out_bytes = outv[0]->bytes;
+    ctx->pending.push_back(std::move(pd));
+    return JAXCUDA_OK;
+  }
+  if (int rc = flush_pending(ctx)) return rc;
+  return launch_kernel(ctx, exe, inptr, outv[0]->ptr);
+}
 
+}  // extern "C"
+
+// Launches one prepared Kernel on the context's stream.
+static int launch_kernel(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const std::vector<void*>& inptr, void* outptr) {
+  const int n_inputs = (int)inptr.size();
+  if (ctx->alloc.capturing) ctx->capture_bytes += exe->plan.algo_bytes;
   void* scratch = nullptr;
   if (exe->plan.scratch_bytes && exe->plan.scratch_persistent) {
     if (!exe->persistent_scratch && ctx->alloc.capturing)
@@ -991,11 +1044,9 @@ int jaxcuda_dispatch(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const jaxcuda_slot* inp
   }
   int rc = JAXCUDA_OK;
   if (exe->plan.skeleton == SK_GEMM_TC) {
-    std::vector<void*> inptr(n_inputs);
-    for (int i = 0; i < n_inputs; i++) inptr[i] = in[i]->ptr;
     std::string err;
     int nl = launch_gemm_tc(ctx->drv.TensorMapEncodeTiled, (void*)ctx->drv.LaunchKernel, exe->plan, exe->fns, inptr,
-                            outv[0]->ptr, scratch, ctx->stream, ctx->status_dev, err,
+                            outptr, scratch, ctx->stream, ctx->status_dev, err,
                             // a persistent GEMM that holds every SM would keep a sum begun on the second
                             // stream waiting until it ends; leave that sum a few SMs while one is in flight
                             ctx->comm_pending && ctx->comm_sms > 0 ? std::max(1, ctx->opt.sm_count - ctx->comm_sms) : 0);
@@ -1011,8 +1062,8 @@ int jaxcuda_dispatch(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const jaxcuda_slot* inp
       if (exe->plan.algo_bytes >= 16.0 * 1024 * 1024) ctx->sweep ^= 1;
     }
     args[n_inputs + 2] = &rev;
-    for (int i = 0; i < n_inputs; i++) ptrs[i] = in[i]->ptr;
-    ptrs[n_inputs] = outv[0]->ptr;
+    for (int i = 0; i < n_inputs; i++) ptrs[i] = inptr[i];
+    ptrs[n_inputs] = outptr;
     ptrs[n_inputs + 1] = scratch;
     for (size_t i = 0; i < ptrs.size(); i++) args[i] = &ptrs[i];
     for (size_t s = 0; s < exe->plan.stages.size() && rc == JAXCUDA_OK; s++) {
@@ -1025,6 +1076,212 @@ int jaxcuda_dispatch(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const jaxcuda_slot* inp
   }
   if (scratch && !exe->plan.scratch_persistent) ctx->alloc.put(scratch, exe->plan.scratch_bytes);
   return rc;
+}
+
+// The Kernels list[i..end) as stages of one row program over [R, C]: a buffer table with one entry
+// per array instance (an address that is written again is a new instance), the stages, the address
+// behind every buffer and a key that identifies the wiring.  False where the group must not be
+// fused as it stands (a stage would overwrite an array the group reads).
+struct RowGroup {
+  std::vector<FuseBuffer> bufs;
+  std::vector<void*> ptr_of;
+  std::vector<FuseStage> stages;
+  std::string key;
+};
+
+static bool build_row_group(const std::vector<PendingDispatch>& list, size_t i, size_t end, int64_t R, int64_t C, RowGroup& g) {
+  std::unordered_map<void*, int> cur;
+  std::map<std::string, int> seen;  // Kernel + inputs -> output buffer, for repeated Kernels
+  std::ostringstream key;
+  key << R << "x" << C;
+  for (size_t s = i; s < end; s++) {
+    const PendingDispatch& pd = list[s];
+    FuseStage st;
+    st.ir = &pd.exe->ir;
+    std::ostringstream sk;
+    sk << std::hex << pd.exe->hash << ":";
+    for (size_t a = 0; a < pd.in.size(); a++) {
+      auto it = cur.find(pd.in[a]);
+      int b;
+      if (it != cur.end()) b = it->second;
+      else {
+        FuseBuffer fb;
+        fb.external = true;
+        fb.bytes = pd.in_bytes[a];
+        b = (int)g.bufs.size();
+        g.bufs.push_back(fb);
+        g.ptr_of.push_back(pd.in[a]);
+        cur[pd.in[a]] = b;
+      }
+      st.in_buf.push_back(b);
+      sk << b << ",";
+    }
+    auto oit = cur.find(pd.out);
+    if (oit != cur.end() && g.bufs[oit->second].external) return false;
+    auto dup = seen.find(sk.str());
+    if (dup != seen.end() && pd.out_freed) {  // the same Kernel on the same arrays again: reuse its result
+      cur[pd.out] = dup->second;
+      key << "|=" << dup->second;
+      continue;
+    }
+    FuseBuffer ob;
+    ob.store = !pd.out_freed;
+    ob.bytes = pd.out_bytes;
+    st.out_buf = (int)g.bufs.size();
+    g.bufs.push_back(ob);
+    g.ptr_of.push_back(pd.out);
+    cur[pd.out] = st.out_buf;
+    seen[sk.str()] = st.out_buf;
+    key << "|" << sk.str() << ">" << st.out_buf << (ob.store ? "s" : "");
+    g.stages.push_back(st);
+  }
+  g.key = key.str();
+  return !g.stages.empty();
+}
+
+// The longest run of row stages that starts at list[i] (a row reduction); 0 if there is none.
+static size_t row_group_extent(const std::vector<PendingDispatch>& list, size_t i, int64_t& R, int64_t& C) {
+  const KernelIR& seed = list[i].exe->ir;
+  if (list[i].exe->kind != 0 || !seed.has_red) return 0;
+  R = (int64_t)seed.size;
+  C = (int64_t)seed.red_size;
+  if (C % 4 || row_stage_type(seed, R, C) != RS_REDUCE) return 0;
+  size_t end = i;
+  while (end < list.size() && list[end].exe->kind == 0 && row_stage_type(list[end].exe->ir, R, C) != RS_NONE) end++;
+  return end - i >= 2 ? end : 0;
+}
+
+// Tries to replace the Kernels pending[i..] by one row program; returns the index after the last
+// Kernel it covered, or i if it launched nothing.
+static size_t launch_row_group(jaxcuda_ctx* ctx, std::vector<PendingDispatch>& list, size_t i) {
+  int64_t R = 0, C = 0;
+  size_t end = row_group_extent(list, i, R, C);
+  for (; end >= i + 2; end--) {
+    RowGroup g;
+    if (!build_row_group(list, i, end, R, C, g)) continue;
+    jaxcuda_exe* fx = nullptr;
+    auto hit = ctx->fused.find(g.key);
+    if (hit != ctx->fused.end()) fx = hit->second.get();
+    else {
+      std::unique_ptr<jaxcuda_exe> exe(new jaxcuda_exe);
+      exe->ctx = ctx;
+      std::string why;
+      bool planned = false;
+      try {
+        planned = plan_row_fusion(g.stages, g.bufs, R, C, ctx->opt, exe->plan, exe->fuse_params, why);
+      } catch (const std::exception& e) { why = e.what(); }
+      if (!planned) {
+        if (ctx->debug >= 4) fprintf(stderr, "[jaxcuda] no row program for %zu kernels: %s\n", end - i, why.c_str());
+        ctx->fused[g.key] = nullptr;   // remember the refusal
+        continue;
+      }
+      exe->describe = exe->plan.describe;
+      if (ctx->debug >= 4) fprintf(stderr, "[jaxcuda] %s\n", exe->describe.c_str());
+      if (ctx->debug >= 2) fprintf(stderr, "%s\n", exe->plan.source.c_str());
+      if (compile_plan(ctx, exe.get()) != JAXCUDA_OK) {
+        if (ctx->debug >= 1) fprintf(stderr, "[jaxcuda] row program failed to compile: %s\n", ctx->last_error.c_str());
+        free_exe(ctx, exe.get());
+        ctx->fused[g.key] = nullptr;
+        continue;
+      }
+      fx = exe.get();
+      ctx->fused[g.key] = std::move(exe);
+    }
+    if (!fx) continue;
+    std::vector<void*> ptrs(fx->fuse_params.size());
+    std::vector<void*> args(ptrs.size());
+    for (size_t a = 0; a < ptrs.size(); a++) { ptrs[a] = g.ptr_of[fx->fuse_params[a]]; args[a] = &ptrs[a]; }
+    const Stage& st = fx->plan.stages[0];
+    CUresult cr = ctx->drv.LaunchKernel(fx->fns[0], st.grid[0], st.grid[1], st.grid[2], st.block[0], st.block[1], st.block[2],
+                                        st.smem, (CUstream)ctx->stream, args.data(), nullptr);
+    if (cr != CUDA_SUCCESS) { drv_fail(ctx, "cuLaunchKernel (row program)", cr); return i; }
+    ctx->launches++;
+    ctx->capture_bytes += fx->plan.algo_bytes;
+    ctx->capture_groups++;
+    return end;
+  }
+  return i;
+}
+
+// Launches everything dispatched so far inside the capture, in order.
+static int flush_pending(jaxcuda_ctx* ctx) {
+  if (ctx->pending.empty()) return JAXCUDA_OK;
+  std::vector<PendingDispatch> list = std::move(ctx->pending);
+  ctx->pending.clear();
+  for (size_t i = 0; i < list.size();) {
+    const size_t next = launch_row_group(ctx, list, i);
+    if (next > i) { i = next; continue; }
+    if (int rc = launch_kernel(ctx, list[i].exe, list[i].in, list[i].out)) return rc;
+    i++;
+  }
+  return JAXCUDA_OK;
+}
+
+extern "C" {
+
+int jaxcuda_check_step_list(int n, const uint8_t* const* irs, const size_t* lens, const int* n_inputs, const int* inputs,
+                            const int* outputs, const uint8_t* output_freed, int compile, char* report, size_t report_len,
+                            char* message, size_t message_len) {
+  auto put = [](char* dst, size_t cap, const std::string& s) {
+    if (dst && cap) { snprintf(dst, cap, "%s", s.c_str()); }
+  };
+  if (n < 0 || (n > 0 && (!irs || !lens || !n_inputs || !inputs || !outputs))) return JAXCUDA_EINVAL;
+  std::vector<std::unique_ptr<jaxcuda_exe>> exes;
+  std::vector<PendingDispatch> list;
+  Options opt;
+  opt.allow_tc = env_int("JAXCUDA_NO_TC", 0) == 0;
+  size_t at = 0;
+  for (int i = 0; i < n; i++) {
+    std::unique_ptr<jaxcuda_exe> exe(new jaxcuda_exe);
+    std::string err = parse_kernel(irs[i], lens[i], exe->ir);
+    if (!err.empty()) { put(message, message_len, err); return JAXCUDA_EINVAL; }
+    exe->hash = fnv1a(irs[i], lens[i]);
+    PendingDispatch pd;
+    pd.exe = exe.get();
+    // the diagnostic has no buffers: array ids stand in for addresses, sizes are taken as sufficient
+    for (int a = 0; a < n_inputs[i]; a++) { pd.in.push_back((void*)(uintptr_t)(inputs[at + a] + 1)); pd.in_bytes.push_back((size_t)1 << 40); }
+    at += n_inputs[i];
+    pd.out = (void*)(uintptr_t)(outputs[i] + 1);
+    pd.out_bytes = (size_t)1 << 40;
+    pd.out_freed = output_freed && output_freed[i];
+    list.push_back(std::move(pd));
+    exes.push_back(std::move(exe));
+  }
+  std::ostringstream rep, src;
+  for (size_t i = 0; i < list.size();) {
+    int64_t R = 0, C = 0;
+    size_t end = row_group_extent(list, i, R, C), done = 0;
+    for (; end >= i + 2 && !done; end--) {
+      RowGroup g;
+      if (!build_row_group(list, i, end, R, C, g)) continue;
+      Plan plan;
+      std::vector<int> params;
+      std::string why;
+      try {
+        if (!plan_row_fusion(g.stages, g.bufs, R, C, opt, plan, params, why)) continue;
+      } catch (const std::exception& e) { continue; }
+      if (compile) {
+        std::vector<char> cubin;
+        std::string err;
+        if (!nvrtc_compile(plan.source, cubin, err)) { put(message, message_len, err); return JAXCUDA_ECOMPILE; }
+      }
+      rep << i << "-" << end - 1 << ": " << plan.describe << " bytes=" << (long long)plan.algo_bytes << "\n";
+      src << plan.source << "\n";
+      done = end;
+    }
+    if (done) { i = done; continue; }
+    try {
+      Plan plan = make_plan(list[i].exe->ir, opt);
+      rep << i << ": " << plan.describe << " bytes=" << (long long)plan.algo_bytes << "\n";
+    } catch (const std::exception& e) {
+      put(message, message_len, e.what());
+      return JAXCUDA_EUNSUPPORTED;
+    }
+    i++;
+  }
+  put(report, report_len, rep.str());
+  if (!compile) put(message, message_len, src.str());
+  return JAXCUDA_OK;
 }
 
 int jaxcuda_exe_release(jaxcuda_exe* exe) {
@@ -1094,6 +1351,7 @@ int jaxcuda_copy(jaxcuda_ctx* ctx, jaxcuda_slot dst, jaxcuda_slot src) {
   if (!s) return slot_error(ctx, src);
   if (d->bytes != s->bytes) return fail(ctx, JAXCUDA_EINVAL, "copy between slots of %zu and %zu bytes", s->bytes, d->bytes);
   cudaSetDevice(ctx->device);
+  if (int rc = flush_pending(ctx)) return rc;
   if (d->bytes && d->ptr != s->ptr)
     CUDA_TRY(ctx, cudaMemcpyAsync(d->ptr, s->ptr, d->bytes, cudaMemcpyDeviceToDevice, ctx->stream));
   return JAXCUDA_OK;
@@ -1108,6 +1366,9 @@ int jaxcuda_capture_begin(jaxcuda_ctx* ctx) {
   CUDA_TRY(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeRelaxed));
   ctx->alloc.capturing = ctx->next_graph_id++;
   ctx->capture_launches0 = ctx->launches;
+  ctx->capture_bytes = 0;
+  ctx->capture_groups = 0;
+  ctx->pending.clear();
   return JAXCUDA_OK;
 }
 
@@ -1115,6 +1376,7 @@ int jaxcuda_capture_end(jaxcuda_ctx* ctx, jaxcuda_graph** out) {
   if (!ctx || !out) return JAXCUDA_EINVAL;
   *out = nullptr;
   if (!ctx->alloc.capturing) return fail(ctx, JAXCUDA_EINVAL, "no capture is open");
+  const int flush_rc = flush_pending(ctx);
   jaxcuda_comm_join(ctx);  // a forked stream must rejoin before the capture closes
   const int id = ctx->alloc.capturing;
   ctx->alloc.capturing = 0;
@@ -1123,6 +1385,11 @@ int jaxcuda_capture_end(jaxcuda_ctx* ctx, jaxcuda_graph** out) {
   if (e != cudaSuccess || !graph) {
     ctx->alloc.release_graph(id);
     return fail(ctx, JAXCUDA_ECUDA, "cudaStreamEndCapture: %s", cudaGetErrorString(e));
+  }
+  if (flush_rc) {
+    cudaGraphDestroy(graph);
+    ctx->alloc.release_graph(id);
+    return flush_rc;
   }
   cudaGraphExec_t exec = nullptr;
   e = cudaGraphInstantiate(&exec, graph, 0);
@@ -1134,6 +1401,8 @@ int jaxcuda_capture_end(jaxcuda_ctx* ctx, jaxcuda_graph** out) {
   jaxcuda_graph* g = new jaxcuda_graph;
   g->ctx = ctx; g->id = id; g->graph = graph; g->exec = exec;
   g->kernels = ctx->launches - ctx->capture_launches0;
+  g->algo_bytes = ctx->capture_bytes;
+  g->fused_groups = ctx->capture_groups;
   ctx->launches = ctx->capture_launches0;  // nothing has run yet: launches count when the graph does
   *out = g;
   return JAXCUDA_OK;
@@ -1146,6 +1415,14 @@ int jaxcuda_graph_launch(jaxcuda_ctx* ctx, jaxcuda_graph* g) {
   CUDA_TRY(ctx, cudaGraphLaunch(g->exec, ctx->stream));
   ctx->launches += g->kernels;
   ctx->tc_dispatched = true;
+  return JAXCUDA_OK;
+}
+
+int jaxcuda_graph_cost(jaxcuda_graph* g, uint64_t* launches, double* algo_bytes, int* fused_groups) {
+  if (!g) return JAXCUDA_EINVAL;
+  if (launches) *launches = g->kernels;
+  if (algo_bytes) *algo_bytes = g->algo_bytes;
+  if (fused_groups) *fused_groups = g->fused_groups;
   return JAXCUDA_OK;
 }
 
@@ -1223,6 +1500,7 @@ int jaxcuda_allreduce_sum_f32(jaxcuda_ctx* ctx, const jaxcuda_slot* slots, int n
     if (ctx->nranks == 1) return JAXCUDA_OK;  // a single rank: the sum is the input
     return fail(ctx, JAXCUDA_EINVAL, "communicator not initialised");
   }
+  if (int rc = flush_pending(ctx)) return rc;
   if (int rc = jaxcuda_comm_join(ctx)) return rc;  // keep NCCL calls of this rank in one order
   return allreduce_on(ctx, slots, n, ctx->stream);
 }
@@ -1247,6 +1525,7 @@ int jaxcuda_allreduce_sum_f32_async(jaxcuda_ctx* ctx, const jaxcuda_slot* slots,
     CUDA_TRY(ctx, cudaEventCreateWithFlags(&ctx->comm_fork, cudaEventDisableTiming));
     CUDA_TRY(ctx, cudaEventCreateWithFlags(&ctx->comm_done, cudaEventDisableTiming));
   }
+  if (int rc = flush_pending(ctx)) return rc;
   CUDA_TRY(ctx, cudaEventRecord(ctx->comm_fork, ctx->stream));
   CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->comm_stream, ctx->comm_fork, 0));
   ctx->comm_pending = true;
@@ -1257,6 +1536,7 @@ int jaxcuda_comm_join(jaxcuda_ctx* ctx) {
   if (!ctx) return JAXCUDA_EINVAL;
   if (!ctx->comm_pending) return JAXCUDA_OK;
   cudaSetDevice(ctx->device);
+  if (int rc = flush_pending(ctx)) return rc;
   CUDA_TRY(ctx, cudaEventRecord(ctx->comm_done, ctx->comm_stream));
   CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->stream, ctx->comm_done, 0));
   ctx->comm_pending = false;

@@ -185,3 +185,26 @@ def test_shape_tracker_movement_sequences_match_numpy():
         got = oracle.run_kernel(k, [base.reshape(-1)])
         assert np.array_equal(got, np.ascontiguousarray(arr).reshape(-1)), (trial, [v.shape for v in st.views])
     assert multi >= 30, multi     # the multi-view path was exercised
+
+
+@pytest.mark.parametrize("rows,cols", [(8192, 4096), (100, 1000), (16, 12), (4, 16384)])
+def test_softmax_step_list_becomes_one_row_program(lib, rows, cols):
+    """What a capture would launch for the softmax / logsumexp / argmax program: one row-resident kernel
+    (NVRTC-compiled here) that moves only the program's own inputs and outputs."""
+    from jax_js_b200.backend import check_step_list
+    report, source = check_step_list(P.softmax_lse_argmax_program(rows, cols))
+    assert len(report) == 1 and report[0].startswith("0-9: row-fused 8 kernels"), report     # 10 Kernels, two repeated row maxima folded
+    assert report[0].endswith(f"bytes={2 * rows * cols * 4 + 2 * rows * 4 + cols * 4}")
+    assert source.count("__global__") == 1 and "jx_rowfuse" in source
+    assert source.count("jx_store(") == 1            # of the rows x cols arrays only the softmax is written
+
+
+def test_step_lists_that_are_no_row_programs_stay_as_they_are(lib):
+    from jax_js_b200 import mlp
+    from jax_js_b200.backend import check_step_list
+    # rows of 10 classes are not 128-bit runs, GEMMs and transposes are no row stages
+    report, _ = check_step_list(mlp.mlp_grad_program(256, [64, 128, 10], global_batch=256), compile=False)
+    assert not any("row-fused" in r for r in report), report
+    # a row too long for one CTA's registers is left to the row-reduce skeleton
+    report, _ = check_step_list(P.softmax_lse_argmax_program(4, 65536), compile=False)
+    assert not any("row-fused" in r for r in report), report
