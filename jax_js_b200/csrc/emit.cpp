@@ -1282,8 +1282,9 @@ bool plan_row_fusion(const std::vector<FuseStage>& stages, const std::vector<Fus
   auto no = [&](const std::string& m) { why = m; return false; };
   if (C % 4) return no("cols is not a multiple of 4");
   const int64_t chunks = C / 4;   // 128-bit pieces of a row
+  const int per_thread = (opt.fuse_chunks == 1 || opt.fuse_chunks == 2 || opt.fuse_chunks == 4) ? opt.fuse_chunks : 4;
   int T = 32;
-  while (T < 1024 && (int64_t)T * 4 < chunks) T *= 2;
+  while (T < 1024 && (int64_t)T * per_thread < chunks) T *= 2;
   const int E = (int)((chunks + T - 1) / T);
   if (E > 4) return no("row too long for one CTA's registers");
   const int NW = T / 32;
@@ -1350,7 +1351,11 @@ bool plan_row_fusion(const std::vector<FuseStage>& stages, const std::vector<Fus
   const bool exact = opt.exact_math == 1 || (opt.exact_math < 0 && work < opt.exact_math_work);
   std::ostringstream os;
   os << (exact ? "#define JX_EXACT_TRANSCENDENTALS 1\n" : "") << "#define JX_LD_HINT " << opt.ld_hint << "\n" << kPrelude;
-  os << "extern \"C\" __global__ void __launch_bounds__(" << T << ") jx_rowfuse(";
+  os << "extern \"C\" __global__ void __launch_bounds__(" << T;
+  // 1536 resident threads per SM hold the allocation at 42 registers: measured best for 4096-column rows (44 us against 47 at 1024)
+  const int min_ctas = opt.fuse_min_ctas > 0 ? std::min(opt.fuse_min_ctas, 2048 / T) : opt.fuse_min_ctas < 0 ? 0 : std::max(1, 1536 / T);
+  if (min_ctas > 0) os << ", " << std::min(min_ctas, 32);
+  os << ") jx_rowfuse(";
   for (size_t i = 0; i < params.size(); i++) {
     const int b = params[i];
     const bool written = produced[b] && bufs[b].store;
@@ -1380,7 +1385,7 @@ bool plan_row_fusion(const std::vector<FuseStage>& stages, const std::vector<Fus
     loop_close("  ");
   }
   auto overrides = [&](const std::map<size_t, LoadRef>& loads, const std::vector<Node>& nodes, const std::string& col,
-                       std::map<size_t, std::string>& ov) {
+                       std::map<size_t, std::string>& ov, std::map<int, uint32_t>* col_packs = nullptr) {
     for (const auto& kv : loads) {
       const Node& nd = nodes[kv.first];
       const int b = kv.second.buf;
@@ -1388,7 +1393,11 @@ bool plan_row_fusion(const std::vector<FuseStage>& stages, const std::vector<Fus
       switch (kv.second.how) {
         case RL_BIG: ov[kv.first] = "B" + S(b) + "[e * 4 + j]"; break;
         case RL_VEC: ov[kv.first] = produced[b] ? "v" + S(b) : ptr + "[row]"; break;
-        case RL_COL: ov[kv.first] = ptr + "[" + col + "]"; break;
+        case RL_COL:
+          // fetched as one 128-bit load per run of four columns (see `col_fetch`)
+          if (col_packs) { (*col_packs)[b] = nd.dtype; ov[kv.first] = "cp" + S(b) + ".e[j]"; }
+          else ov[kv.first] = ptr + "[" + col + "]";
+          break;
         default: {
           const Analysis an = analyze(nodes, 1, 0);
           ov[kv.first] = ptr + "[" + S(an.affine[nd.src[0]] ? an.affine[nd.src[0]]->c0 : 0) + "]";
@@ -1396,41 +1405,113 @@ bool plan_row_fusion(const std::vector<FuseStage>& stages, const std::vector<Fus
       }
     }
   };
-  // `produced` now restarts: a value is "in registers" only from its producing stage on
-  std::fill(produced.begin(), produced.end(), 0);
+  auto col_fetch = [&](const std::map<int, uint32_t>& packs) {
+    for (const auto& kv : packs) {
+      os << "        jx_pack<" << ptype(kv.second) << ", 4> cp" << kv.first << ";\n";
+      os << "        jx_load(cp" << kv.first << ", (const " << ptype(kv.second) << "*)b" << kv.first << " + c0);\n";
+    }
+  };
   double bytes = 0;
   for (int b = 0; b < nb; b++) bytes += ext_bytes[b];
-  for (size_t s = 0; s < stages.size(); s++) {
-    const KernelIR& k = *stages[s].ir;
-    const int ob = stages[s].out_buf;
-    const uint32_t odt = k.out_dtype();
-    const Analysis an = analyze(k.exp, k.size, k.has_red ? k.red_size : 0);
-    const size_t root = k.exp.size() - 1;
-    const std::vector<char> want = closure_above_loads(k.exp, root);
-    std::map<size_t, std::string> ov;
+
+  // Emission order.  A row reduction costs a CTA-wide barrier, so reductions whose inputs are ready
+  // are accumulated together and folded behind one barrier; per-row and elementwise stages that can
+  // run first do, because they may make further reductions ready.  Dependences are by buffer.
+  const size_t ns = stages.size();
+  std::vector<int> producer(nb, -1);
+  for (size_t s = 0; s < ns; s++) producer[stages[s].out_buf] = (int)s;
+  std::vector<char> done(ns, 0), accumulated(ns, 0);
+  auto ready = [&](size_t s) {
+    for (int b : stages[s].in_buf)
+      if (producer[b] >= 0 && !done[producer[b]]) return false;
+    return true;
+  };
+  auto stage_env = [&](size_t s, std::map<size_t, std::string>& ov) {
     Env env;
     env.prefix = "s" + S((int64_t)s) + "_";
     env.load_override = &ov;
-    os << "  {  // stage " << s << "\n";
-    if (types[s] == RS_REDUCE) {
-      overrides(exp_loads[s], k.exp, "ridx", ov);
-      const char* AT = ctype(k.red_dtype);
-      auto red = [&](const std::string& a, const std::string& b) { return binary_expr(k.red_op, k.red_dtype, a, b, 0, nullptr); };
-      os << "    " << AT << " acc = " << identity_literal(k.red_op, k.red_dtype) << ";\n";
-      env.gidx = "row";
-      loop_open("    ");
-      os << "        #pragma unroll\n        for (int j = 0; j < 4; j++) {\n          const int ridx = c0 + j;\n";
-      std::vector<std::string> names(k.exp.size());
-      emit_nodes(os, k.exp, an, names, want, env, "          ");
-      os << "          acc = " << red("acc", names[root]) << ";\n        }\n";
-      loop_close("    ");
-      os << "    #pragma unroll\n    for (int o = 16; o > 0; o >>= 1) { const " << AT
-         << " v = __shfl_xor_sync(0xffffffffu, acc, o); acc = " << red("acc", "v") << "; }\n";
+    return env;
+  };
+  auto store_row_value = [&](size_t s) {
+    const int ob = stages[s].out_buf;
+    if (bufs[ob].store)
+      os << "    if (tid == 0) ((" << ptype(stages[s].ir->out_dtype()) << "*)b" << ob << ")[row] = v" << ob << ";\n";
+  };
+  auto red_of = [&](size_t s, const std::string& x, const std::string& y) {
+    return binary_expr(stages[s].ir->red_op, stages[s].ir->red_dtype, x, y, 0, nullptr);
+  };
+  auto emit_per_row = [&](size_t s) {
+    const KernelIR& k = *stages[s].ir;
+    const Analysis an = analyze(k.exp, k.size, 0);
+    std::map<size_t, std::string> ov;
+    overrides(exp_loads[s], k.exp, "0", ov);
+    Env env = stage_env(s, ov);
+    env.gidx = "row";
+    os << "  {  // stage " << s << ": per row\n";
+    std::vector<std::string> names(k.exp.size());
+    emit_nodes(os, k.exp, an, names, closure_above_loads(k.exp, k.exp.size() - 1), env, "    ");
+    os << "    v" << stages[s].out_buf << " = " << names.back() << ";\n";
+    store_row_value(s);
+    os << "  }\n";
+  };
+  auto emit_elementwise = [&](size_t s) {
+    const KernelIR& k = *stages[s].ir;
+    const int ob = stages[s].out_buf;
+    const uint32_t odt = k.out_dtype();
+    const Analysis an = analyze(k.exp, k.size, 0);
+    std::map<size_t, std::string> ov;
+    std::map<int, uint32_t> col_packs;
+    overrides(exp_loads[s], k.exp, "cidx", ov, &col_packs);
+    Env env = stage_env(s, ov);
+    os << "  {  // stage " << s << ": elementwise\n";
+    loop_open("    ");
+    col_fetch(col_packs);
+    os << "        jx_pack<" << ptype(odt) << ", 4> o;\n";
+    os << "        #pragma unroll\n        for (int j = 0; j < 4; j++) {\n";
+    os << "          const int cidx = c0 + j;\n          const int gidx = row * " << C << " + cidx;\n          (void)gidx;\n";
+    std::vector<std::string> names(k.exp.size());
+    emit_nodes(os, k.exp, an, names, closure_above_loads(k.exp, k.exp.size() - 1), env, "          ");
+    os << "          o.e[j] = " << names.back() << ";\n";
+    if (read_later[ob]) os << "          B" << ob << "[e * 4 + j] = " << names.back() << ";\n";
+    os << "        }\n";
+    if (bufs[ob].store) os << "        jx_store((" << ptype(odt) << "*)b" << ob << " + " << row_off << " + c0, o);\n";
+    loop_close("    ");
+    os << "  }\n";
+  };
+  auto emit_accumulate = [&](size_t s) {   // this thread's share and the warp's: leaves the warp's value in acc<s>
+    const KernelIR& k = *stages[s].ir;
+    const Analysis an = analyze(k.exp, k.size, k.red_size);
+    const char* AT = ctype(k.red_dtype);
+    std::map<size_t, std::string> ov;
+    std::map<int, uint32_t> col_packs;
+    overrides(exp_loads[s], k.exp, "ridx", ov, &col_packs);
+    Env env = stage_env(s, ov);
+    env.gidx = "row";
+    const std::string acc = "acc" + S((int64_t)s);
+    os << "  " << AT << " " << acc << " = " << identity_literal(k.red_op, k.red_dtype) << ";  // stage " << s << ": row reduction\n";
+    if (NW > 1) os << "  __shared__ " << AT << " sm" << s << "[" << NW << "];\n";
+    os << "  {\n";
+    loop_open("    ");
+    col_fetch(col_packs);
+    os << "        #pragma unroll\n        for (int j = 0; j < 4; j++) {\n          const int ridx = c0 + j;\n          (void)ridx;\n";
+    std::vector<std::string> names(k.exp.size());
+    emit_nodes(os, k.exp, an, names, closure_above_loads(k.exp, k.exp.size() - 1), env, "          ");
+    os << "          " << acc << " = " << red_of(s, acc, names.back()) << ";\n        }\n";
+    loop_close("    ");
+    os << "    #pragma unroll\n    for (int o = 16; o > 0; o >>= 1) { const " << AT << " v = __shfl_xor_sync(0xffffffffu, " << acc
+       << ", o); " << acc << " = " << red_of(s, acc, "v") << "; }\n";
+    if (NW > 1) os << "    if (lane == 0) sm" << s << "[warp] = " << acc << ";\n";
+    os << "  }\n";
+  };
+  auto emit_finish = [&](const std::vector<size_t>& group) {   // one barrier for all of them, then fold and epilogue
+    if (NW > 1) os << "  __syncthreads();\n";
+    for (size_t s : group) {
+      const KernelIR& k = *stages[s].ir;
+      const std::string acc = "acc" + S((int64_t)s);
+      os << "  {  // stage " << s << ": fold and epilogue\n";
       if (NW > 1) {
-        os << "    __shared__ " << AT << " sm" << s << "[" << NW << "];\n";
-        os << "    if (lane == 0) sm" << s << "[warp] = acc;\n    __syncthreads();\n";
-        os << "    acc = sm" << s << "[0];\n";
-        os << "    #pragma unroll\n    for (int w = 1; w < " << NW << "; w++) acc = " << red("acc", "sm" + S((int64_t)s) + "[w]") << ";\n";
+        os << "    " << acc << " = sm" << s << "[0];\n";
+        os << "    #pragma unroll\n    for (int w = 1; w < " << NW << "; w++) " << acc << " = " << red_of(s, acc, "sm" + S((int64_t)s) + "[w]") << ";\n";
       }
       const Analysis ae = analyze(k.epi, k.size, 0);
       std::map<size_t, std::string> eov;
@@ -1438,37 +1519,41 @@ bool plan_row_fusion(const std::vector<FuseStage>& stages, const std::vector<Fus
       Env ee;
       ee.prefix = "s" + S((int64_t)s) + "e_";
       ee.gidx = "row";
+      ee.acc = acc;
       ee.load_override = &eov;
       std::vector<std::string> en(k.epi.size());
       emit_nodes(os, k.epi, ae, en, closure_above_loads(k.epi, k.epi.size() - 1), ee, "    ");
-      os << "    v" << ob << " = " << en.back() << ";\n";
-    } else if (types[s] == RS_PER_ROW) {
-      overrides(exp_loads[s], k.exp, "0", ov);
-      env.gidx = "row";
-      std::vector<std::string> names(k.exp.size());
-      emit_nodes(os, k.exp, an, names, want, env, "    ");
-      os << "    v" << ob << " = " << names[root] << ";\n";
-    } else {
-      overrides(exp_loads[s], k.exp, "cidx", ov);
-      const bool keep = read_later[ob];
-      loop_open("    ");
-      os << "        jx_pack<" << ptype(odt) << ", 4> o;\n";
-      os << "        #pragma unroll\n        for (int j = 0; j < 4; j++) {\n";
-      os << "          const int cidx = c0 + j;\n          const int gidx = row * " << C << " + cidx;\n          (void)gidx;\n";
-      std::vector<std::string> names(k.exp.size());
-      emit_nodes(os, k.exp, an, names, want, env, "          ");
-      os << "          o.e[j] = " << names[root] << ";\n";
-      if (keep) os << "          B" << ob << "[e * 4 + j] = " << names[root] << ";\n";
-      os << "        }\n";
-      if (bufs[ob].store) os << "        jx_store((" << ptype(odt) << "*)b" << ob << " + " << row_off << " + c0, o);\n";
-      loop_close("    ");
+      os << "    v" << stages[s].out_buf << " = " << en.back() << ";\n";
+      store_row_value(s);
+      os << "  }\n";
     }
-    if (types[s] != RS_ELEMENTWISE && bufs[ob].store)
-      os << "    if (tid == 0) ((" << ptype(odt) << "*)b" << ob << ")[row] = v" << ob << ";\n";
-    os << "  }\n";
-    produced[ob] = 1;
-    if (bufs[ob].store) bytes += types[s] == RS_ELEMENTWISE ? (double)R * C * 4 : (double)R * 4;
+  };
+  size_t left = ns;
+  while (left) {
+    bool progress = false;
+    for (size_t s = 0; s < ns; s++)   // cheap stages first: they can only make more work ready
+      if (!done[s] && types[s] == RS_PER_ROW && ready(s)) { emit_per_row(s); done[s] = 1; left--; progress = true; }
+    if (progress) continue;
+    // an elementwise stage that feeds a reduction goes before the reductions; the others wait
+    for (size_t s = 0; s < ns; s++) {
+      if (done[s] || types[s] != RS_ELEMENTWISE || !ready(s) || !read_later[stages[s].out_buf]) continue;
+      emit_elementwise(s); done[s] = 1; left--; progress = true;
+    }
+    if (progress) continue;
+    std::vector<size_t> group;
+    for (size_t s = 0; s < ns; s++)
+      if (!done[s] && types[s] == RS_REDUCE && ready(s)) { emit_accumulate(s); group.push_back(s); }
+    if (!group.empty()) {
+      emit_finish(group);
+      for (size_t s : group) { done[s] = 1; left--; }
+      continue;
+    }
+    for (size_t s = 0; s < ns; s++)
+      if (!done[s] && types[s] == RS_ELEMENTWISE && ready(s)) { emit_elementwise(s); done[s] = 1; left--; progress = true; }
+    if (!progress) return no("the stages depend on each other in a cycle");
   }
+  for (size_t s = 0; s < ns; s++)
+    if (bufs[stages[s].out_buf].store) bytes += types[s] == RS_ELEMENTWISE ? (double)R * C * 4 : (double)R * 4;
   os << "}\n";
 
   plan = Plan();

@@ -76,6 +76,8 @@ struct Options {
   int col_ctas_per_sm = 4;    // spread ridx over threads and CTAs until the grid holds this many 256-thread CTAs per SM
   int col_ty = 0;             // threads sharing one output vector inside a CTA (0: chosen)
   int col_unroll = 4;         // independent loads in flight per thread in the column-reduce loop
+  int fuse_chunks = 0;        // 128-bit pieces of a row per thread in a row program (1, 2 or 4; 0: chosen)
+  int fuse_min_ctas = 0;      // CTAs per SM the row program's register allocation is held to (0: compiler's choice)
 };
 
 // Throws std::runtime_error with the reference's UnsupportedOpError wording

@@ -101,7 +101,8 @@ __device__ __forceinline__ float jx_exp_fast(float x) {
   float e = fmaf(x, 1.4426950408889634f, -t);
   e = fmaf(x, 1.925963033500978e-8f, e);        // log2 e - float(log2 e)
   float p;
-  asm("ex2.approx.f32 %0, %1;" : "=f"(p) : "f"(t));
+  // .ftz: results below 2^-126 become 0, which is what the reference returns there (k < -126)
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p) : "f"(t));
   float res = fmaf(p, e * 0.6931471805599453f, p);
   res = (t > 127.5f) ? JX_INF : res;
   return (t < -126.5f) ? 0.0f : res;

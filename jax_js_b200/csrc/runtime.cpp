@@ -419,6 +419,8 @@ int jaxcuda_create(int device, jaxcuda_ctx** out) {
   ctx->opt.tc_bn = env_int("JAXCUDA_TC_BN", 0);
   ctx->sweep_alternate = env_int("JAXCUDA_SWEEP", 1) != 0;
   ctx->fuse_rows = env_int("JAXCUDA_FUSE", 1) != 0;
+  ctx->opt.fuse_chunks = env_int("JAXCUDA_FUSE_CHUNKS", ctx->opt.fuse_chunks);
+  ctx->opt.fuse_min_ctas = env_int("JAXCUDA_FUSE_MIN_CTAS", ctx->opt.fuse_min_ctas);
   ctx->debug = env_int("JAXCUDA_DEBUG", 0);
   *out = ctx.release();
   return JAXCUDA_OK;
