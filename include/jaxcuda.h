@@ -68,11 +68,22 @@ int jaxcuda_write(jaxcuda_ctx* ctx, jaxcuda_slot slot, size_t start, size_t coun
 /* Backend.read as the reference declares it, returning a Promise (src/backend.ts:182-186): the copy
  * of bytes [start, start+count) to dst is enqueued on a copy stream of its own, after everything
  * dispatched so far, and the call returns.  jaxcuda_read_wait(ticket) is where the Promise resolves.
- * dst must be pinned memory (jaxcuda_host_alloc); until the wait returns the slot must stay alive and
- * must not be the output of a dispatch (jaxcuda_write_async into it is ordered after the read).
- * Uploads, kernels and downloads of consecutive steps then overlap. */
+ * dst must be pinned memory (jaxcuda_host_alloc).  The slot may be released, written or dispatched
+ * into before the wait returns: the runtime orders whatever touches its memory next behind the copy.
+ * Uploads, kernels and downloads of consecutive steps then overlap.  read_wait also reports a
+ * tensor-core kernel that abandoned a bounded wait, as jaxcuda_read and jaxcuda_sync do. */
 int jaxcuda_read_async(jaxcuda_ctx* ctx, jaxcuda_slot slot, size_t start, size_t count, void* dst, uint64_t* ticket);
 int jaxcuda_read_wait(jaxcuda_ctx* ctx, uint64_t ticket);
+/* For callers that wait on another thread (the Promise of a Node-API addon): one host thread drives
+ * a context at a time, so a worker thread must not enter the calls above.  jaxcuda_read_event gives,
+ * on the driving thread, the event behind a ticket; jaxcuda_event_block waits for it from any thread
+ * and touches no context state; jaxcuda_read_wait on the driving thread then returns at once and
+ * retires the ticket. */
+int jaxcuda_read_event(jaxcuda_ctx* ctx, uint64_t ticket, void** event);
+int jaxcuda_event_block(void* event);
+/* How often the compute stream had to be ordered behind a download or a sum that still used a slot
+ * which was being released, written or dispatched into (diagnostic). */
+uint64_t jaxcuda_order_waits(jaxcuda_ctx* ctx);
 /* jaxcuda_write on a copy stream: starts after everything dispatched so far (earlier kernels may
  * still read the slot); everything dispatched afterwards waits for it.  src must be pinned and
  * unchanged until a later read_wait or sync has returned. */
@@ -188,8 +199,10 @@ int jaxcuda_comm_init(jaxcuda_ctx* ctx, int rank, int nranks, const void* id128)
 int jaxcuda_allreduce_sum_f32(jaxcuda_ctx* ctx, const jaxcuda_slot* slots, int n);
 /* The same sum on a second stream: it starts after everything dispatched so far and runs under
  * what is dispatched next.  jaxcuda_comm_join makes later dispatches wait for every sum begun
- * this way; read, sync, event_record and capture_end join by themselves.  The slots must not be
- * read, written or released between the two calls. */
+ * this way; read, sync, event_record and capture_end join by themselves, and so does releasing,
+ * writing or dispatching into one of the slots (the runtime joins first, so the sum is never
+ * overtaken).  A Kernel that only reads one of the slots before the join sees unsummed or
+ * partly summed data: that ordering is the caller's. */
 int jaxcuda_allreduce_sum_f32_async(jaxcuda_ctx* ctx, const jaxcuda_slot* slots, int n);
 int jaxcuda_comm_join(jaxcuda_ctx* ctx);
 int jaxcuda_comm_destroy(jaxcuda_ctx* ctx);

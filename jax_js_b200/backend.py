@@ -98,6 +98,9 @@ SYMBOLS = {
     "jaxcuda_capture_end": (_I, [_P, ctypes.POINTER(_P)]),
     "jaxcuda_graph_launch": (_I, [_P, _P]),
     "jaxcuda_graph_destroy": (_I, [_P, _P]),
+    "jaxcuda_read_event": (_I, [_P, ctypes.c_uint64, ctypes.POINTER(_P)]),
+    "jaxcuda_event_block": (_I, [_P]),
+    "jaxcuda_order_waits": (ctypes.c_uint64, [_P]),
     "jaxcuda_graph_cost": (_I, [_P, ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_int)]),
     "jaxcuda_copy": (_I, [_P, _U32, _U32]),
     "jaxcuda_sort_no_alloc": (_I, [_P, _I, _P, _P, ctypes.c_int64, ctypes.c_int64, ctypes.c_char_p, _SZ]),
@@ -421,6 +424,19 @@ class CudaBackend:
 
     def graph_launch(self, graph: int) -> None:
         self._check(self._lib.jaxcuda_graph_launch(self._ctx, graph))
+
+    def order_waits(self) -> int:
+        return int(self._lib.jaxcuda_order_waits(self._ctx))
+
+    def read_event(self, ticket: int) -> int:
+        ev = ctypes.c_void_p()
+        self._check(self._lib.jaxcuda_read_event(self._ctx, ticket, ctypes.byref(ev)))
+        return ev.value
+
+    def event_block(self, event: int) -> None:
+        """Waits for a ticket's event; safe on a thread other than the one driving the backend."""
+        if self._lib.jaxcuda_event_block(event) != OK:
+            raise CudaError("cudaEventSynchronize failed")
 
     def graph_cost(self, graph: int) -> tuple:
         """(kernel launches, algorithmic bytes, fused runs) of one launch of the graph."""

@@ -31,6 +31,7 @@
 #include "fft.hpp"
 
 #include <sstream>
+#include <unordered_set>
 
 extern "C" size_t jaxcuda_sort_work_bytes(int argsort, int64_t batch, int64_t n);
 extern "C" int jaxcuda_sort_launch(void* stream, int argsort, const void* x, void* y, int32_t* yi, int dtype,
@@ -246,6 +247,9 @@ struct jaxcuda_ctx {
   cudaEvent_t copy_fork = nullptr, up_done = nullptr;
   std::vector<cudaEvent_t> tickets;  // ticket t = tickets[t - 1]
   std::vector<uint64_t> free_tickets;
+  std::vector<char> ticket_pending;  // read_async issued, read_wait not yet returned
+  std::unordered_set<void*> comm_ptrs;  // blocks a sum on the second stream is still working on
+  uint64_t order_waits = 0;          // times the compute stream was made to wait for a copy or a sum (see order_after_users)
   // direction of the next streaming kernel's walk over its grid (JAXCUDA_SWEEP=0: always forward)
   int sweep = 0;
   bool sweep_alternate = true;
@@ -286,6 +290,23 @@ SlotRec* find_slot(jaxcuda_ctx* ctx, jaxcuda_slot s) {
 int slot_error(jaxcuda_ctx* ctx, jaxcuda_slot s) {
   // wording of SlotError, src/backend.ts:222-226
   return fail(ctx, JAXCUDA_ESLOT, "Used a buffer that is invalid or already freed: %u", s);
+}
+
+// The caching allocator hands a released block out again at once, and a write or a dispatch may
+// target a slot directly; both are ordered on the compute stream only.  A download on the copy
+// stream or a sum on the second stream that still uses the block is not, so before the block
+// changes hands (or is written) the compute stream is made to wait for them.
+int order_after_users(jaxcuda_ctx* ctx, SlotRec* s) {
+  if (s->read_ticket && s->read_ticket <= ctx->ticket_pending.size() && ctx->ticket_pending[s->read_ticket - 1]) {
+    CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->stream, ctx->tickets[s->read_ticket - 1], 0));
+    ctx->order_waits++;
+    s->read_ticket = 0;
+  }
+  if (ctx->comm_pending && s->ptr && ctx->comm_ptrs.count(s->ptr)) {
+    ctx->order_waits++;
+    return jaxcuda_comm_join(ctx);
+  }
+  return JAXCUDA_OK;
 }
 
 // After a stream sync: has a kernel abandoned a bounded wait?
@@ -497,6 +518,7 @@ int jaxcuda_decref(jaxcuda_ctx* ctx, jaxcuda_slot slot) {
   SlotRec* s = find_slot(ctx, slot);
   if (!s) return slot_error(ctx, slot);
   if (--s->refs == 0) {
+    if (int rc = order_after_users(ctx, s)) return rc;
     for (size_t i = ctx->pending.size(); i-- > 0;)   // the latest pending writer of this block produced it
       if (ctx->pending[i].out == s->ptr) { ctx->pending[i].out_freed = true; break; }
     if (s->ptr) ctx->alloc.put(s->ptr, s->bytes);
@@ -539,6 +561,8 @@ int jaxcuda_write(jaxcuda_ctx* ctx, jaxcuda_slot slot, size_t start, size_t coun
   if (start > s->bytes || count > s->bytes - start)
     return fail(ctx, JAXCUDA_EINVAL, "write of %zu bytes at %zu beyond buffer of %zu bytes", count, start, s->bytes);
   cudaSetDevice(ctx->device);
+  if (int rc = flush_pending(ctx)) return rc;
+  if (int rc = order_after_users(ctx, s)) return rc;
   if (count) CUDA_TRY(ctx, cudaMemcpyAsync((char*)s->ptr + start, src, count, cudaMemcpyHostToDevice, ctx->stream));
   return JAXCUDA_OK;
 }
@@ -596,9 +620,15 @@ int jaxcuda_read_async(jaxcuda_ctx* ctx, jaxcuda_slot slot, size_t start, size_t
     cudaEvent_t ev;
     CUDA_TRY(ctx, cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
     ctx->tickets.push_back(ev);
+    ctx->ticket_pending.push_back(0);
     t = ctx->tickets.size();
   }
+  if (ctx->tc_dispatched) {  // a tensor-core kernel that gave up a bounded wait reports through this word
+    CUDA_TRY(ctx, cudaMemcpyAsync(ctx->status_host, ctx->status_dev, sizeof(int), cudaMemcpyDeviceToHost, ctx->down_stream));
+    ctx->tc_dispatched = false;
+  }
   CUDA_TRY(ctx, cudaEventRecord(ctx->tickets[t - 1], ctx->down_stream));
+  ctx->ticket_pending[t - 1] = 1;
   s->read_ticket = t;
   *ticket = t;
   return JAXCUDA_OK;
@@ -609,9 +639,23 @@ int jaxcuda_read_wait(jaxcuda_ctx* ctx, uint64_t ticket) {
   for (uint64_t f : ctx->free_tickets) if (f == ticket) return fail(ctx, JAXCUDA_EINVAL, "ticket %llu is not pending", (unsigned long long)ticket);
   cudaSetDevice(ctx->device);
   CUDA_TRY(ctx, cudaEventSynchronize(ctx->tickets[ticket - 1]));
+  ctx->ticket_pending[ticket - 1] = 0;
   ctx->free_tickets.push_back(ticket);
+  return check_device_status(ctx);
+}
+
+int jaxcuda_read_event(jaxcuda_ctx* ctx, uint64_t ticket, void** event) {
+  if (!ctx || !event || ticket == 0 || ticket > ctx->tickets.size()) return JAXCUDA_EINVAL;
+  *event = (void*)ctx->tickets[ticket - 1];
   return JAXCUDA_OK;
 }
+
+int jaxcuda_event_block(void* event) {
+  if (!event) return JAXCUDA_EINVAL;
+  return cudaEventSynchronize((cudaEvent_t)event) == cudaSuccess ? JAXCUDA_OK : JAXCUDA_ECUDA;
+}
+
+uint64_t jaxcuda_order_waits(jaxcuda_ctx* ctx) { return ctx ? ctx->order_waits : 0; }
 
 int jaxcuda_prepare_kernel(jaxcuda_ctx* ctx, const uint8_t* ir, size_t len, uint64_t hash, jaxcuda_exe** out) {
   if (!ctx || !out) return JAXCUDA_EINVAL;
@@ -902,6 +946,7 @@ int jaxcuda_dispatch(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const jaxcuda_slot* inp
   std::vector<SlotRec*> in(n_inputs), outv(n_outputs);
   for (int i = 0; i < n_inputs; i++) if (!(in[i] = find_slot(ctx, inputs[i]))) return slot_error(ctx, inputs[i]);
   for (int i = 0; i < n_outputs; i++) if (!(outv[i] = find_slot(ctx, outputs[i]))) return slot_error(ctx, outputs[i]);
+  for (int i = 0; i < n_outputs; i++) if (int rc = order_after_users(ctx, outv[i])) return rc;
 
   if (exe->kind != 0)
     if (int rc = flush_pending(ctx)) return rc;
@@ -1354,6 +1399,7 @@ int jaxcuda_copy(jaxcuda_ctx* ctx, jaxcuda_slot dst, jaxcuda_slot src) {
   if (d->bytes != s->bytes) return fail(ctx, JAXCUDA_EINVAL, "copy between slots of %zu and %zu bytes", s->bytes, d->bytes);
   cudaSetDevice(ctx->device);
   if (int rc = flush_pending(ctx)) return rc;
+  if (int rc = order_after_users(ctx, d)) return rc;
   if (d->bytes && d->ptr != s->ptr)
     CUDA_TRY(ctx, cudaMemcpyAsync(d->ptr, s->ptr, d->bytes, cudaMemcpyDeviceToDevice, ctx->stream));
   return JAXCUDA_OK;
@@ -1531,6 +1577,8 @@ int jaxcuda_allreduce_sum_f32_async(jaxcuda_ctx* ctx, const jaxcuda_slot* slots,
   CUDA_TRY(ctx, cudaEventRecord(ctx->comm_fork, ctx->stream));
   CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->comm_stream, ctx->comm_fork, 0));
   ctx->comm_pending = true;
+  for (int i = 0; i < n; i++)
+    if (SlotRec* r = find_slot(ctx, slots[i])) ctx->comm_ptrs.insert(r->ptr);
   return allreduce_on(ctx, slots, n, ctx->comm_stream);
 }
 
@@ -1542,6 +1590,7 @@ int jaxcuda_comm_join(jaxcuda_ctx* ctx) {
   CUDA_TRY(ctx, cudaEventRecord(ctx->comm_done, ctx->comm_stream));
   CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->stream, ctx->comm_done, 0));
   ctx->comm_pending = false;
+  ctx->comm_ptrs.clear();
   return JAXCUDA_OK;
 }
 

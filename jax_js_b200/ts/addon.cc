@@ -6,6 +6,7 @@
 #include <napi.h>
 
 #include <cstring>
+#include <map>
 #include <vector>
 
 #include "jaxcuda.h"
@@ -64,38 +65,65 @@ Napi::Value Read(const Napi::CallbackInfo& info) {
   if (jaxcuda_read(ctx, slot, start, (size_t)count, out.Data()) != JAXCUDA_OK) Throw(info.Env(), ctx);
   return out;
 }
-// Backend.read as a Promise: the copy is enqueued on the library's download stream into pinned
-// memory right away (ordered after the dispatches so far); a worker thread blocks in
-// jaxcuda_read_wait, and the Promise resolves with a copy of the pinned buffer on the main thread.
+// Backend.read as a Promise.  The copy is enqueued on the library's download stream into pinned
+// memory right away (ordered after the dispatches so far).  One host thread drives a context at a
+// time, so the worker thread never enters the context: it blocks on the ticket's event alone
+// (jaxcuda_event_block), and the ticket is retired, the result copied and the staging buffer
+// recycled back on the JS thread.
+class PinnedPool {  // staging buffers by capacity: allocating pinned memory synchronises the device, so they are kept
+ public:
+  void* Get(jaxcuda_ctx* ctx, size_t bytes, size_t* capacity) {
+    size_t cap = 4096;
+    while (cap < bytes) cap <<= 1;
+    *capacity = cap;
+    auto& list = free_[cap];
+    if (!list.empty()) { void* p = list.back(); list.pop_back(); return p; }
+    void* p = nullptr;
+    return jaxcuda_host_alloc(ctx, cap, &p) == JAXCUDA_OK ? p : nullptr;
+  }
+  void Put(size_t capacity, void* p) { free_[capacity].push_back(p); }
+
+ private:
+  std::map<size_t, std::vector<void*>> free_;
+};
+static PinnedPool g_pinned;   // used on the JS thread only
+
 class ReadWorker : public Napi::AsyncWorker {
  public:
-  ReadWorker(Napi::Env env, jaxcuda_ctx* ctx, jaxcuda_slot slot, void* pinned, size_t count, uint64_t ticket)
+  ReadWorker(Napi::Env env, jaxcuda_ctx* ctx, jaxcuda_slot slot, void* pinned, size_t capacity, size_t count, uint64_t ticket,
+             void* event)
       : Napi::AsyncWorker(env), deferred_(Napi::Promise::Deferred::New(env)), ctx_(ctx), slot_(slot), pinned_(pinned),
-        count_(count), ticket_(ticket) {}
+        capacity_(capacity), count_(count), ticket_(ticket), event_(event) {}
   Napi::Promise Promise() const { return deferred_.Promise(); }
-  void Execute() override {
-    if (jaxcuda_read_wait(ctx_, ticket_) != JAXCUDA_OK) SetError(jaxcuda_last_error(ctx_));
+  void Execute() override {   // worker thread: no context state is touched here
+    if (jaxcuda_event_block(event_) != JAXCUDA_OK) SetError("waiting for the device-to-host copy failed");
   }
-  void OnOK() override {
+  void OnOK() override {      // JS thread
+    const int rc = jaxcuda_read_wait(ctx_, ticket_);   // returns at once; reports a kernel that gave up a bounded wait
     auto out = Napi::Uint8Array::New(Env(), count_);
     if (count_) memcpy(out.Data(), pinned_, count_);
-    jaxcuda_host_free(ctx_, pinned_);
-    jaxcuda_decref(ctx_, slot_);           // the reference taken in ReadAsync kept the buffer alive
-    deferred_.Resolve(out);
+    Release();
+    if (rc == JAXCUDA_OK) deferred_.Resolve(out);
+    else deferred_.Reject(Napi::Error::New(Env(), jaxcuda_last_error(ctx_)).Value());
   }
   void OnError(const Napi::Error& e) override {
-    jaxcuda_host_free(ctx_, pinned_);
-    jaxcuda_decref(ctx_, slot_);
+    jaxcuda_read_wait(ctx_, ticket_);
+    Release();
     deferred_.Reject(e.Value());
   }
 
  private:
+  void Release() {
+    g_pinned.Put(capacity_, pinned_);
+    jaxcuda_decref(ctx_, slot_);           // the reference taken in ReadAsync kept the buffer alive
+  }
   Napi::Promise::Deferred deferred_;
   jaxcuda_ctx* ctx_;
   jaxcuda_slot slot_;
   void* pinned_;
-  size_t count_;
+  size_t capacity_, count_;
   uint64_t ticket_;
+  void* event_;
 };
 Napi::Value ReadAsync(const Napi::CallbackInfo& info) {
   jaxcuda_ctx* ctx = Ctx(info[0]);
@@ -105,16 +133,19 @@ Napi::Value ReadAsync(const Napi::CallbackInfo& info) {
   size_t size = 0;
   if (jaxcuda_slot_size(ctx, slot, &size) != JAXCUDA_OK) Throw(info.Env(), ctx);
   if (count < 0) count = (int64_t)(size - start);
-  void* pinned = nullptr;
-  if (jaxcuda_host_alloc(ctx, (size_t)count > 0 ? (size_t)count : 1, &pinned) != JAXCUDA_OK) Throw(info.Env(), ctx);
+  size_t capacity = 0;
+  void* pinned = g_pinned.Get(ctx, (size_t)count, &capacity);
+  if (!pinned) Throw(info.Env(), ctx);
   uint64_t ticket = 0;
+  void* event = nullptr;
   jaxcuda_incref(ctx, slot);               // a caller may drop its reference before the Promise resolves
-  if (jaxcuda_read_async(ctx, slot, start, (size_t)count, pinned, &ticket) != JAXCUDA_OK) {
+  if (jaxcuda_read_async(ctx, slot, start, (size_t)count, pinned, &ticket) != JAXCUDA_OK ||
+      jaxcuda_read_event(ctx, ticket, &event) != JAXCUDA_OK) {
     jaxcuda_decref(ctx, slot);
-    jaxcuda_host_free(ctx, pinned);
+    g_pinned.Put(capacity, pinned);
     Throw(info.Env(), ctx);
   }
-  auto* worker = new ReadWorker(info.Env(), ctx, slot, pinned, (size_t)count, ticket);
+  auto* worker = new ReadWorker(info.Env(), ctx, slot, pinned, capacity, (size_t)count, ticket, event);
   worker->Queue();
   return worker->Promise();
 }

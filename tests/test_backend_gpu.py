@@ -252,3 +252,58 @@ def test_empty_and_largest_kernels(backend):
     assert tail.tolist() == [((n - 4 + j) * 3) % (1 << 32) for j in range(4)]
     backend.dec_ref(big)
     backend.dec_ref(sums)
+
+
+def test_block_reuse_is_ordered_behind_a_pending_async_read(backend):
+    """A slot released right after `read_async` hands its block back to the allocator; the next owner
+    of the block must not overwrite it before the download has finished."""
+    n = 8 << 20                                   # 32 MB: the copy takes a while on PCIe
+    src = np.arange(n, dtype=np.float32)
+    a = backend.put(src)
+    host = backend.host_alloc(n * 4)
+    before = backend.order_waits()
+    t = backend.read_async(a, host)
+    backend.dec_ref(a)                            # released while the copy is in flight
+    assert backend.order_waits() == before + 1    # the compute stream now waits for that copy
+    b = backend.put(np.full(n, -1.0, np.float32)) # same size class: gets the block that was just released
+    backend.read_wait(t)
+    assert np.array_equal(host.view(np.float32), src)
+    backend.dec_ref(b)
+    backend.host_free(host)
+
+
+def test_async_read_can_be_waited_for_on_another_thread(backend):
+    """The Promise pattern of a Node-API addon: a worker thread blocks on the ticket's event alone, the
+    driving thread keeps dispatching and retires the ticket afterwards."""
+    import threading
+    n = 1 << 20
+    x = np.arange(n, dtype=np.float32)
+    k = Kernel(1, n, AluExp.add(AluExp.global_index(F32, 0, n, g), AluExp.f32(1)))
+    exe = backend.prepare_kernel(k)
+    a, b = backend.put(x), backend.malloc(n * 4)
+    backend.dispatch(exe, [a], [b])
+    host = backend.host_alloc(n * 4)
+    t = backend.read_async(b, host)
+    ev = backend.read_event(t)
+    th = threading.Thread(target=backend.event_block, args=(ev,))
+    th.start()
+    for _ in range(20):                           # the driving thread goes on using the context meanwhile
+        backend.dispatch(exe, [a], [b])
+        t2 = backend.read_async(b, backend_scratch(backend, n * 4))
+        backend.read_wait(t2)
+    th.join()
+    backend.read_wait(t)
+    assert np.array_equal(host.view(np.float32), x + 1)
+    for s in (a, b):
+        backend.dec_ref(s)
+    backend.host_free(host)
+    backend.host_free(_SCRATCH.pop("buf"))
+
+
+_SCRATCH = {}
+
+
+def backend_scratch(backend, nbytes):
+    if "buf" not in _SCRATCH:
+        _SCRATCH["buf"] = backend.host_alloc(nbytes)
+    return _SCRATCH["buf"]
