@@ -1,6 +1,7 @@
 #include "emit.hpp"
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <sstream>
@@ -356,10 +357,100 @@ struct Builder {
   }
 
   // ---- elementwise -----------------------------------------------------------------
+  // An elementwise Kernel whose largest load walks memory along another digit of gidx than the
+  // output does (a materialised transpose: `jit` emits them for the weight gradients that
+  // `transposeDot` produces in [out, in] order and for the batch axis that `vmap` moves to the
+  // front).  Read directly, a warp's 32 loads hit 32 different 128-byte lines.  Here a CTA takes
+  // a 32 x 32 tile over the output's unit digit A and the load's unit digit B: the load is read
+  // with B across the lanes into shared memory, then the Kernel's body runs with A across the lanes.
+  bool elementwise_transposed(Plan& p) const {
+    if (k.size < (1u << 18) || dtype_bytes(out_dt) != 4) return false;
+    size_t best = 0;
+    int64_t dB = 0, mB = 0, mA = 0;
+    uint64_t best_len = 0;
+    for (size_t i = 0; i < k.exp.size(); i++) {
+      const Node& nd = k.exp[i];
+      if (nd.op != JAXCUDA_OP_GLOBALINDEX || dtype_bytes(nd.dtype) != 4) continue;
+      const std::optional<Affine>& ix = an_exp.affine[nd.src[0]];
+      if (!ix || !in_range(ix, nd.arg1)) continue;
+      const Term* ta = nullptr;
+      const Term* tb = nullptr;
+      for (const Term& t : ix->terms) {
+        if (t.var != 0) continue;
+        if (t.div == 1) ta = &t;
+        else if (t.coef == 1) tb = &t;
+      }
+      if (!tb) continue;
+      const int64_t a_mod = ta ? (ta->mod ? ta->mod : (int64_t)k.size) : 0;
+      if (!ta || std::llabs(ta->coef) < 32 || a_mod < 16) continue;       // the output's unit digit must stride the load
+      if (tb->div % a_mod) continue;
+      const int64_t b_mod = tb->mod ? tb->mod : (int64_t)k.size / tb->div;
+      if (b_mod < 16 || nd.arg1 < best_len) continue;
+      best = i; best_len = nd.arg1; dB = tb->div; mB = b_mod; mA = a_mod;
+    }
+    if (!best_len || (int64_t)k.size % (dB * mB)) return false;
+    // the staged load must be a good part of all the bytes the Kernel moves, or staging it changes little
+    if ((double)best_len * 4 < 0.25 * p.algo_bytes) return false;
+    const int64_t tilesA = (mA + 31) / 32, tilesB = (mB + 31) / 32, mids = dB / mA, his = (int64_t)k.size / (dB * mB);
+    const int64_t blocks = tilesA * tilesB * mids * his;
+    if (blocks > 0x7fffffffLL) return false;
+    const Node& ld = k.exp[best];
+    std::ostringstream os;
+    os << header();
+    os << "extern \"C\" __global__ void __launch_bounds__(256) jx_transpose(" << params() << ") {\n";
+    os << "  __shared__ " << ctype(ld.dtype) << " tile[32][33];\n";
+    os << "  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;\n";
+    os << "  long long blk = blockIdx.x;\n";
+    os << "  const int ta = (int)(blk % " << tilesA << "LL); blk /= " << tilesA << "LL;\n";
+    os << "  const int tb = (int)(blk % " << tilesB << "LL); blk /= " << tilesB << "LL;\n";
+    os << "  const long long mid = blk % " << mids << "LL, hi = blk / " << mids << "LL;\n";
+    os << "  const long long base = hi * " << dB * mB << "LL + mid * " << mA << "LL;\n";
+    // phase 1: lanes along B
+    os << "  {\n    const int b = tb * 32 + tx;\n    #pragma unroll\n    for (int i = ty; i < 32; i += 8) {\n";
+    os << "      const int a = ta * 32 + i;\n      if (a < " << mA << " && b < " << mB << ") {\n";
+    os << "        const int gidx = (int)(base + (long long)b * " << dB << "LL + a);\n";
+    {
+      std::vector<std::string> names(k.exp.size());
+      Env env;
+      env.prefix = "l";
+      emit_nodes(os, k.exp, an_exp, names, closure(k.exp, best), env, "        ");
+      os << "        tile[i][tx] = " << names[best] << ";\n";
+    }
+    os << "      }\n    }\n  }\n  __syncthreads();\n";
+    // phase 2: lanes along A
+    os << "  {\n    const int a = ta * 32 + tx;\n    #pragma unroll\n    for (int i = ty; i < 32; i += 8) {\n";
+    os << "      const int b = tb * 32 + i;\n      if (a < " << mA << " && b < " << mB << ") {\n";
+    os << "        const int gidx = (int)(base + (long long)b * " << dB << "LL + a);\n";
+    {
+      std::map<size_t, std::string> ov;
+      ov[best] = "tile[tx][i]";
+      // every node except the staged load's own index arithmetic (unless something else uses it)
+      std::vector<char> want(k.exp.size(), 0);
+      want.back() = 1;
+      for (size_t i = k.exp.size(); i-- > 0;)
+        if (want[i] && i != best) for (uint32_t sidx = 0; sidx < k.exp[i].nsrc; sidx++) want[k.exp[i].src[sidx]] = 1;
+      std::vector<std::string> names(k.exp.size());
+      Env env;
+      env.load_override = &ov;
+      emit_nodes(os, k.exp, an_exp, names, want, env, "        ");
+      os << "        out[gidx] = " << to_storage(out_dt, names.back()) << ";\n";
+    }
+    os << "      }\n    }\n  }\n}\n";
+    p.source = os.str();
+    Stage st;
+    st.entry = "jx_transpose";
+    st.grid[0] = (unsigned)blocks;
+    st.block[0] = 256;
+    p.stages.push_back(st);
+    p.describe = "elementwise transposed tile 32x32 A=" + S(mA) + " B=" + S(mB) + "@" + S(dB) + " grid=" + S(blocks);
+    return true;
+  }
+
   Plan elementwise() const {
     Plan p;
     p.skeleton = SK_ELEMENTWISE;
     account(p);
+    if (opt.force_skeleton < 0 && elementwise_transposed(p)) return p;
     const int T = 256;
     int V = std::max(1, 16 / dtype_bytes(out_dt));
     if (k.size < (uint64_t)V * 64) V = 1;
@@ -777,6 +868,118 @@ struct Builder {
     return g;
   }
 
+  // ---- convolution recognition ------------------------------------------------------------
+  // `jitRules[Conv]` (src/frontend/jit.ts:649-660) builds a convolution as a Dot over pooled views:
+  // body = Mul(patch, weight) under an f32 Add reduction, where the weight is a plain load indexed by
+  // one digit of gidx (the output channel) and ridx, and the patch is any expression (guarded,
+  // div/mod-indexed loads of the input, src/frontend/convolution.ts) of the other digits of gidx
+  // and ridx.  With gidx = (b * M + m) * N + n, m the weight's digit, this is, per b,
+  // C[m, n] = sum_k W[m, k] * P[k, n]: a GEMM whose B operand is gathered by evaluating the patch.
+  // Returns the GEMM description (b_gathered) and the node of the patch.
+  GemmDesc match_conv(size_t& patch_node) const {
+    GemmDesc g;
+    if (!k.has_red || k.red_op != JAXCUDA_OP_ADD || k.red_dtype != JAXCUDA_F32 || k.red_size < 1) return g;
+    const Node* mul = &k.exp.back();
+    if (mul->op == JAXCUDA_OP_CAST && mul->dtype == JAXCUDA_F32 && k.exp[mul->src[0]].dtype == JAXCUDA_F16) {
+      mul = &k.exp[mul->src[0]];
+      g.round_product_f16 = true;
+    }
+    if (mul->op != JAXCUDA_OP_MUL) return g;
+    for (int wside = 0; wside < 2; wside++) {
+      const Node* w = &k.exp[mul->src[wside]];
+      if (w->op == JAXCUDA_OP_CAST && w->dtype == JAXCUDA_F32) w = &k.exp[w->src[0]];
+      if (w->op != JAXCUDA_OP_GLOBALINDEX || (w->dtype != JAXCUDA_F32 && w->dtype != JAXCUDA_F16)) continue;
+      const std::optional<Affine>& wi = an_exp.affine[w->src[0]];
+      if (!wi || !in_range(wi, w->arg1) || !wi->only_plain(1) || wi->coef_of(1, 1) == 0) continue;
+      // exactly one digit of gidx
+      const Term* digit = nullptr;
+      int gterms = 0;
+      for (const Term& t : wi->terms) if (t.var == 0) { digit = &t; gterms++; }
+      if (gterms != 1 || digit->div < 2) continue;
+      const int64_t N = digit->div;
+      if ((int64_t)k.size % N) continue;
+      const int64_t M = digit->mod ? digit->mod : (int64_t)k.size / N;
+      if (M < 1 || ((int64_t)k.size / N) % M) continue;
+      const int64_t batch = (int64_t)k.size / (M * N);
+      // The patch must not look at the weight's digit.  An index expression in affine form is judged
+      // by its digits of gidx (only digits under the channel digit or the batch digits above it);
+      // any other node is clean when all its sources are.  Wide forms such as gidx itself may only
+      // feed further index arithmetic.
+      const size_t proot = mul->src[1 - wside];
+      const std::vector<char> in_patch = closure(k.exp, proot);
+      std::vector<char> wide(k.exp.size(), 0);
+      bool ok = true;
+      for (size_t i = 0; i <= proot && ok; i++) {
+        if (!in_patch[i]) continue;
+        const Node& nd = k.exp[i];
+        if (an_exp.affine[i]) {
+          for (const Term& t : an_exp.affine[i]->terms) {
+            if (t.var != 0) continue;
+            const bool below = t.mod != 0 && t.div * t.mod <= N;
+            const bool above = t.div >= M * N;
+            if (!below && !above) wide[i] = 1;
+          }
+        } else if (nd.op == JAXCUDA_OP_SPECIAL) {
+          wide[i] = nd.arg0 == 0;
+        } else {
+          for (uint32_t sidx = 0; sidx < nd.nsrc; sidx++)
+            if (wide[nd.src[sidx]]) ok = false;
+        }
+      }
+      if (wide[proot]) ok = false;
+      if (!ok) continue;
+      const int eb = dtype_bytes(w->dtype);
+      g.valid = true;
+      g.b_gathered = true;
+      g.b_pitch = (N + 63) / 64 * 64;
+      g.gidA = (uint32_t)w->arg0; g.gidB = 0;
+      g.dtA = w->dtype; g.dtB = w->dtype;
+      g.lenA = w->arg1;
+      g.M = M; g.N = N; g.K = k.red_size; g.batch = batch;
+      g.offA = wi->c0; g.sAm = digit->coef; g.sAk = wi->coef_of(1, 1); g.sAb = 0;
+      g.offB = 0; g.sBn = 1; g.sBk = g.b_pitch; g.sBb = g.K * g.b_pitch;
+      g.lenB = (uint64_t)(batch * g.K * g.b_pitch);
+      (void)eb;
+      patch_node = proot;
+      if (k.exp[proot].dtype != w->dtype && !(k.exp[proot].dtype == JAXCUDA_F32 && w->dtype == JAXCUDA_F32)) { g.valid = false; continue; }
+      return g;
+    }
+    return g;
+  }
+
+  // CUDA C of the stage that evaluates a convolution's patch expression into the B operand
+  // [batch][K][pitch] (n contiguous, zero beyond N) at the start of the scratch, followed for f32 by
+  // the 3xTF32 remainder plane.  A thread produces four consecutive n of one (batch, k) row.
+  std::string gather_source(const GemmDesc& g, size_t patch_node) const {
+    const bool f16 = g.dtB == JAXCUDA_F16;
+    std::ostringstream os;
+    os << "extern \"C\" __global__ void __launch_bounds__(256) jx_gather_b(" << params() << ") {\n";
+    os << "  const i64 quads = " << g.b_pitch / 4 << "LL, total = quads * " << g.K << "LL * " << g.batch << "LL;\n";
+    os << "  for (i64 t = (i64)blockIdx.x * 256 + threadIdx.x; t < total; t += (i64)gridDim.x * 256) {\n";
+    os << "    const int n0 = (int)(t % quads) * 4;\n    const i64 row = t / quads;\n";
+    os << "    const int ridx = (int)(row % " << g.K << "LL), b = (int)(row / " << g.K << "LL);\n";
+    os << "    float v[4];\n";
+    os << "    #pragma unroll\n    for (int j = 0; j < 4; j++) {\n      v[j] = 0.0f;\n";
+    os << "      if (n0 + j < " << g.N << ") {\n";
+    os << "        const int gidx = b * " << g.M * g.N << " + n0 + j;\n";
+    std::vector<std::string> names(k.exp.size());
+    Env env;
+    env.prefix = "q";
+    emit_nodes(os, k.exp, an_exp, names, closure(k.exp, patch_node), env, "        ");
+    os << "        v[j] = " << names[patch_node] << ";\n      }\n    }\n";
+    if (f16) {
+      os << "    jx_pack<jx_half, 4> h;\n    #pragma unroll\n    for (int j = 0; j < 4; j++) h.e[j] = jx_f2h(v[j]);\n";
+      os << "    jx_store((jx_half*)scratch + row * " << g.b_pitch << "LL + n0, h);\n";
+    } else {
+      os << "    jx_pack<float, 4> hi, lo;\n    #pragma unroll\n    for (int j = 0; j < 4; j++) {\n";
+      os << "      hi.e[j] = v[j];\n      lo.e[j] = v[j] - __uint_as_float(__float_as_uint(v[j]) & 0xffffe000u);\n    }\n";
+      os << "    jx_store((float*)scratch + row * " << g.b_pitch << "LL + n0, hi);\n";
+      os << "    jx_store((float*)scratch + LEN_B_PAD + row * " << g.b_pitch << "LL + n0, lo);\n";
+    }
+    os << "  }\n}\n";
+    return os.str();
+  }
+
   // Epilogue statements for one output: expects `acc` (float) and `gidx` (int) in scope and
   // assigns the storage-typed result to `dst`.
   std::string epilogue_body(const std::string& indent, const std::string& dst) const {
@@ -952,16 +1155,18 @@ struct Builder {
   // in a persistent scratch area: the CTA that arrives last at its column block's counter folds the
   // partials in split order (so the result does not depend on arrival order), applies the epilogue
   // and re-arms the counter.  `outs` = outputs per column block, T = threads per CTA.
-  void emit_split_tail(std::ostream& os, int splits, int64_t outs, int T) const {
+  // `gidx_of_gl`: the Kernel's output index of the skeleton's linear output position `gl`, where
+  // the two differ (empty: they are the same).
+  void emit_split_tail(std::ostream& os, int splits, int64_t outs, int T, const std::string& gidx_of_gl = "") const {
     const char* AT = ctype(k.red_dtype);
     os << "  __shared__ int last;\n  __threadfence();\n  __syncthreads();\n";
     os << "  if (threadIdx.x == 0) last = atomicAdd((int*)scratch + blockIdx.x, 1) == " << splits - 1 << ";\n";
     os << "  __syncthreads();\n  if (!last) return;\n  __threadfence();\n";
     os << "  for (int o = threadIdx.x; o < " << outs << "; o += " << T << ") {\n";
     os << "    const long long gl = (long long)blockIdx.x * " << outs << " + o;\n    if (gl >= " << k.size << "LL) break;\n";
-    os << "    const int gidx = (int)gl;\n    " << AT << " acc_u = " << identity_literal(k.red_op, k.red_dtype) << ";\n";
+    os << "    const int gidx = " << (gidx_of_gl.empty() ? "(int)gl" : gidx_of_gl) << ";\n    " << AT << " acc_u = " << identity_literal(k.red_op, k.red_dtype) << ";\n";
     os << "    for (int s = 0; s < " << splits << "; s++) { const " << AT << " v = __ldcg(parts + (size_t)s * " << k.size
-       << " + gidx); acc_u = " << red("acc_u", "v") << "; }\n";
+       << " + gl); acc_u = " << red("acc_u", "v") << "; }\n";
     emit_epilogue(os, "    ", "acc_u", "out[gidx]");
     os << "  }\n";
     os << "  if (threadIdx.x == 0) ((int*)scratch)[blockIdx.x] = 0;\n";
@@ -973,7 +1178,10 @@ struct Builder {
   // and keep four loads in flight each; the CTA's slice of B sits in shared memory, rows padded to
   // a multiple of four floats, so that a warp reads it with broadcast 128-bit loads.  K is split
   // over grid.y; partials are folded by the last CTA to arrive (deterministic order).
-  bool dot_skinny_t(const GemmDesc& g, Plan& p) const {
+  // `transposed`: the description has its operands swapped (the big, m-contiguous operand is the
+  // Kernel's right factor), so the output element (m, n) of this skeleton is the Kernel's
+  // gidx = n * GM + m.
+  bool dot_skinny_t(const GemmDesc& g, Plan& p, bool transposed = false) const {
     const int e = dtype_bytes(g.dtA);
     if (g.sAm != 1 || g.M % 4 || (g.offA * e) % (4 * e) || (g.sAk * e) % (4 * e) || g.N > 16) return false;
     const int T = 256, U = 4;
@@ -1023,10 +1231,10 @@ struct Builder {
       os << "  float* parts = (float*)((char*)scratch + " << counter_pad << ");\n";
       os << "  if (ty == 0 && active) {\n    float* part = parts + (size_t)blockIdx.y * " << k.size << " + (size_t)m0 * GN;\n";
       os << "    #pragma unroll\n    for (int q = 0; q < 4 * GN; q += 4) *reinterpret_cast<float4*>(part + q) = make_float4(acc[q], acc[q + 1], acc[q + 2], acc[q + 3]);\n  }\n";
-      emit_split_tail(os, (int)splits, outs, T);
+      emit_split_tail(os, (int)splits, outs, T, transposed ? "(int)(gl % GN) * GM + (int)(gl / GN)" : "");
     } else {
       os << "  if (ty != 0 || !active) return;\n  #pragma unroll\n  for (int q = 0; q < 4 * GN; q++) {\n";
-      os << "    const int gidx = m0 * GN + q;\n    const float acc_u = acc[q];\n";
+      os << "    const int gidx = " << (transposed ? "(q % GN) * GM + m0 + q / GN" : "m0 * GN + q") << ";\n    const float acc_u = acc[q];\n";
       emit_epilogue(os, "    ", "acc_u", "out[gidx]");
       os << "  }\n";
     }
@@ -1043,7 +1251,7 @@ struct Builder {
       p.scratch_bytes = (size_t)counter_pad + (size_t)splits * k.size * 4;
       p.scratch_persistent = true;
     }
-    p.describe = "dot-skinny-t " + S(g.M) + "x" + S(g.N) + "x" + S(g.K) + " TY=" + S(TY) + " splits=" + S(splits) + " grid=" + S(gx) + "x" + S(T);
+    p.describe = std::string("dot-skinny-t ") + (transposed ? "(operands swapped) " : "") + S(g.M) + "x" + S(g.N) + "x" + S(g.K) + " TY=" + S(TY) + " splits=" + S(splits) + " grid=" + S(gx) + "x" + S(T);
     return true;
   }
 
@@ -1147,6 +1355,16 @@ struct Builder {
         }
       }
       if (g.K <= 16) { Plan p; if (dot_small_k(g, p)) return p; }
+      // few output rows, many columns, a long contraction (the weight gradient of a class-count sized
+      // layer written [classes, hidden]): the same skinny skeleton with the operands' roles swapped
+      if (g.M <= 16 && g.N >= 256 && g.K >= 256 && g.sBn == 1) {
+        GemmDesc t = g;
+        t.gidA = g.gidB; t.gidB = g.gidA; t.dtA = g.dtB; t.dtB = g.dtA; t.lenA = g.lenB; t.lenB = g.lenA;
+        t.M = g.N; t.N = g.M;
+        t.offA = g.offB; t.sAm = g.sBn; t.sAk = g.sBk; t.offB = g.offA; t.sBn = g.sAm; t.sBk = g.sAk;
+        Plan p;
+        if (dot_skinny_t(t, p, true)) return p;
+      }
     }
     if (g.valid && g.batch <= 65535 &&
         ((g.M >= opt.gemm_min_dim && g.N >= opt.gemm_min_dim && g.K >= 8) || opt.force_skeleton == SK_GEMM_FFMA)) {
@@ -1177,6 +1395,22 @@ struct Builder {
       }
       return gemm_ffma(g);
     }
+    if (!g.valid && opt.allow_tc && opt.force_skeleton < 0) {
+      size_t patch = 0;
+      GemmDesc c = match_conv(patch);
+      // worth the gather pass once the GEMM is large enough to fill the machine
+      if (c.valid && c.M >= 64 && c.N >= 64 && c.K >= 32 && c.batch <= 65535 &&
+          2.0 * c.M * c.N * c.K * c.batch >= 2e8) {
+        Plan p;
+        p.gemm = c;
+        account(p);
+        p.algo_flops = 2.0 * c.M * c.N * c.K * c.batch;
+        if (plan_gemm_tc(k, c, opt, p, epilogue_body("      ", "JX_DST"), params(), std::string(), gather_source(c, patch))) {
+          p.describe = "conv as " + p.describe;
+          return p;
+        }
+      }
+    }
     const int64_t K = k.red_size;
     const bool r_contig = has_load(1), g_contig = has_load(0);
     bool row;
@@ -1190,7 +1424,52 @@ struct Builder {
 
 }  // namespace
 
+namespace {
+
+// A reduction over a single element is no reduction: out = epilogue(exp at ridx 0).  The batching
+// rules produce such Kernels (a Dot or Reduce over an axis of size 1 under vmap); as elementwise
+// Kernels they get the vectorised streaming skeleton instead of a reduce loop that runs once.
+KernelIR fold_unit_reduction(const KernelIR& k) {
+  KernelIR f;
+  f.nargs = k.nargs;
+  f.size = k.size;
+  f.has_red = false;
+  f.exp = k.exp;
+  for (Node& nd : f.exp)
+    if (nd.op == JAXCUDA_OP_SPECIAL && nd.arg0 == 1) { nd.op = JAXCUDA_OP_CONST; nd.dtype = JAXCUDA_I32; nd.nsrc = 0; nd.arg0 = 0; nd.arg1 = 0; }
+  uint32_t root = (uint32_t)f.exp.size() - 1;
+  if (f.exp[root].dtype != k.red_dtype) {   // the accumulator's type (an f16 product accumulates in f32)
+    Node c;
+    c.op = JAXCUDA_OP_CAST; c.dtype = k.red_dtype; c.nsrc = 1; c.src[0] = root;
+    f.exp.push_back(c);
+    root++;
+  }
+  std::vector<uint32_t> at(k.epi.size());
+  for (size_t i = 0; i < k.epi.size(); i++) {
+    const Node& nd = k.epi[i];
+    if (nd.op == JAXCUDA_OP_VARIABLE) { at[i] = root; continue; }
+    Node c = nd;
+    for (uint32_t s = 0; s < c.nsrc; s++) c.src[s] = at[nd.src[s]];
+    f.exp.push_back(c);
+    at[i] = (uint32_t)f.exp.size() - 1;
+  }
+  if (at.back() != f.exp.size() - 1) {   // the epilogue is the accumulator itself: the root must come last
+    Node c = f.exp[at.back()];
+    f.exp.push_back(c);
+  }
+  return f;
+}
+
+}  // namespace
+
 Plan make_plan(const KernelIR& k, const Options& opt) {
+  if (k.has_red && k.red_size == 1 && opt.force_skeleton < 0 && !k.exp.empty() && !k.epi.empty()) {
+    const KernelIR folded = fold_unit_reduction(k);
+    Builder b(folded, opt);
+    Plan p = b.build();
+    p.describe += " (unit reduction folded)";
+    return p;
+  }
   Builder b(k, opt);
   return b.build();
 }

@@ -31,6 +31,11 @@ struct GemmDesc {
   int64_t offA = 0, sAm = 0, sAk = 0, sAb = 0;
   int64_t offB = 0, sBn = 0, sBk = 0, sBb = 0;
   bool round_product_f16 = false;  // body is Cast<f32>(Mul<f16>(a, b))
+  // Convolutions: the B operand is not an argument but a [batch][K][b_pitch] array that a gather
+  // stage of the same plan writes into the plan's scratch (with its 3xTF32 remainder plane behind
+  // it); then gidB is unused, sBn = 1, sBk = b_pitch, sBb = K * b_pitch, offB = 0.
+  bool b_gathered = false;
+  int64_t b_pitch = 0;
 };
 
 struct Stage {
@@ -114,8 +119,10 @@ bool plan_row_fusion(const std::vector<FuseStage>& stages, const std::vector<Fus
                      const Options& opt, Plan& plan, std::vector<int>& params, std::string& why);
 
 // Implemented in gemm_tc.cpp: rewrites `plan` to the tcgen05 skeleton when `g` qualifies.
+// `gather_source` (with g.b_gathered) is the CUDA C of the kernel `jx_gather_b` that fills the B
+// operand; it is compiled with the GEMM and launched first.
 bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan& plan,
                   const std::string& epilogue_body, const std::string& params_decl,
-                  const std::string& epilogue_preload = std::string());
+                  const std::string& epilogue_preload = std::string(), const std::string& gather_source = std::string());
 
 }  // namespace jaxcuda

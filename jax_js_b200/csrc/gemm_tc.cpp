@@ -182,23 +182,24 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
           mbar_expect_tx(full(s), STAGE_BYTES);
           const u32 sa = smem_base + s * STAGE_BYTES, sb = sa + NPLANES * A_BYTES;
           const int k0 = kb * BK;
+          const int ba = A_SHARED ? 0 : b, bb = B_SHARED ? 0 : b;   // an operand all batches share has one plane
 #if A_MN
           for (int j = 0; j < BM / BK; j++) {
-            tma_load_3d(sa + j * BOX_BYTES, &tmA, full(s), m_blk * BM + j * BK, k0, b);
-            if (KIND == 2) tma_load_3d(sa + A_BYTES + j * BOX_BYTES, &tmA2, full(s), m_blk * BM + j * BK, k0, b);
+            tma_load_3d(sa + j * BOX_BYTES, &tmA, full(s), m_blk * BM + j * BK, k0, ba);
+            if (KIND == 2) tma_load_3d(sa + A_BYTES + j * BOX_BYTES, &tmA2, full(s), m_blk * BM + j * BK, k0, ba);
           }
 #else
-          tma_load_3d(sa, &tmA, full(s), k0, m_blk * BM, b);
-          if (KIND == 2) tma_load_3d(sa + A_BYTES, &tmA2, full(s), k0, m_blk * BM, b);
+          tma_load_3d(sa, &tmA, full(s), k0, m_blk * BM, ba);
+          if (KIND == 2) tma_load_3d(sa + A_BYTES, &tmA2, full(s), k0, m_blk * BM, ba);
 #endif
 #if B_MN
           for (int j = 0; j < BN / BK; j++) {
-            tma_load_3d(sb + j * BOX_BYTES, &tmB, full(s), n_blk * BN + j * BK, k0, b);
-            if (KIND == 2) tma_load_3d(sb + B_BYTES + j * BOX_BYTES, &tmB2, full(s), n_blk * BN + j * BK, k0, b);
+            tma_load_3d(sb + j * BOX_BYTES, &tmB, full(s), n_blk * BN + j * BK, k0, bb);
+            if (KIND == 2) tma_load_3d(sb + B_BYTES + j * BOX_BYTES, &tmB2, full(s), n_blk * BN + j * BK, k0, bb);
           }
 #else
-          tma_load_3d(sb, &tmB, full(s), k0, n_blk * BN, b);
-          if (KIND == 2) tma_load_3d(sb + B_BYTES, &tmB2, full(s), k0, n_blk * BN, b);
+          tma_load_3d(sb, &tmB, full(s), k0, n_blk * BN, bb);
+          if (KIND == 2) tma_load_3d(sb + B_BYTES, &tmB2, full(s), k0, n_blk * BN, bb);
 #endif
         }
       }
@@ -375,7 +376,8 @@ int64_t pad64(int64_t n) { return (n + 63) / 64 * 64; }  // planes start on 256-
 }  // namespace
 
 bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan& plan,
-                  const std::string& epilogue_body, const std::string& params_decl, const std::string& epilogue_preload) {
+                  const std::string& epilogue_body, const std::string& params_decl, const std::string& epilogue_preload,
+                  const std::string& gather_source) {
   if (g.dtA != g.dtB) return false;
   const int kind = g.dtA == JAXCUDA_F16 ? 1 : g.dtA == JAXCUDA_F32 ? 2 : 0;
   if (!kind) return false;
@@ -415,13 +417,15 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
   os << kPrelude;
   os << "#define KIND " << kind << "\n#define ELEM " << e << "\n#define BM " << BM << "\n#define BN " << BN << "\n";
   os << "#define ACC_STRIDE " << (BN > 128 ? 256 : BN) << "\n";
+  os << "#define A_SHARED " << ((g.batch > 1 && g.sAb == 0) ? 1 : 0) << "\n#define B_SHARED " << ((g.batch > 1 && g.sBb == 0) ? 1 : 0) << "\n";
   os << "#define STAGES " << stages << "\n#define A_MN " << (a_mn ? 1 : 0) << "\n#define B_MN " << (b_mn ? 1 : 0) << "\n";
   os << "#define GM " << g.M << "\n#define GN " << g.N << "\n#define GK " << g.K << "\n#define GBATCH " << g.batch << "\n";
   // k-blocks accumulated in tensor memory before the partial sum is folded into registers with a
   // rounded f32 add: 256 elements of K for 3xTF32; the whole K for f16 (its f16 result absorbs the bias)
   const int64_t k_blocks = (g.K + bk - 1) / bk;
   os << "#define CHUNK_KB " << (kind == 2 ? 8 : k_blocks) << "\n";
-  os << "#define LEN_A " << g.lenA << "LL\n#define LEN_B " << g.lenB << "LL\n";
+  // a gathered B operand arrives with its remainder plane already written: only A is split
+  os << "#define LEN_A " << g.lenA << "LL\n#define LEN_B " << (g.b_gathered ? 0 : g.lenB) << "LL\n";
   os << "#define LEN_A_PAD " << pad64(g.lenA) << "LL\n#define LEN_B_PAD " << pad64(g.lenB) << "LL\n";
   const char* out_t = k.out_dtype() == JAXCUDA_F16 ? "jx_half" : k.out_dtype() == JAXCUDA_F64 ? "double"
                       : k.out_dtype() == JAXCUDA_U32 ? "u32" : k.out_dtype() == JAXCUDA_F32 ? "float" : "int";
@@ -437,18 +441,29 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
   for (char c : epilogue_preload) { if (c == '\n') pre += " \\\n"; else pre += c; }
   os << "#define JX_EPI_PRELOAD " << pre << "\n";
   os << kTcSource;
+  if (g.b_gathered) os << gather_source;
   plan.source = os.str();
   plan.skeleton = SK_GEMM_TC;
   plan.tc_kind = kind;
   plan.tc_bm = BM; plan.tc_bn = BN; plan.tc_bk = bk; plan.tc_stages = stages;
   plan.stages.clear();
+  plan.scratch_bytes = 0;
+  if (g.b_gathered) {   // scratch: [B][B remainder plane (3xTF32)][A remainder plane (3xTF32)]
+    Stage ga;
+    ga.entry = "jx_gather_b";
+    ga.grid[0] = (unsigned)std::max<int64_t>(1, std::min<int64_t>(((int64_t)g.lenB / 4 + 255) / 256, (int64_t)opt.sm_count * 32));
+    ga.block[0] = 256;
+    plan.stages.push_back(ga);
+    plan.scratch_bytes = (size_t)pad64(g.lenB) * e * planes;
+  }
   if (kind == 2) {
     Stage sp;
     sp.entry = "jx_split";
-    sp.grid[0] = (unsigned)std::max<int64_t>(1, std::min<int64_t>(((int64_t)(g.lenA + g.lenB) / 4 + 255) / 256, (int64_t)opt.sm_count * 32));
+    const int64_t split_len = g.lenA + (g.b_gathered ? 0 : g.lenB);
+    sp.grid[0] = (unsigned)std::max<int64_t>(1, std::min<int64_t>((split_len / 4 + 255) / 256, (int64_t)opt.sm_count * 32));
     sp.block[0] = 256;
     plan.stages.push_back(sp);
-    plan.scratch_bytes = (size_t)(pad64(g.lenA) + pad64(g.lenB)) * 4;
+    plan.scratch_bytes += (size_t)(pad64(g.lenA) + (g.b_gathered ? 0 : pad64(g.lenB))) * 4;
   }
   Stage st;
   st.entry = "jx_gemm";
@@ -473,26 +488,49 @@ int launch_gemm_tc(void* encode_fn, void* launch_fn, const Plan& plan, const std
   const int e = kind == 1 ? 2 : 4;
   const bool a_mn = g.sAm == 1 && g.sAk != 1, b_mn = g.sBn == 1 && g.sBk != 1;
   int launches = 0;
+  size_t stage_i = 0;
   const char* baseA = (const char*)inputs[g.gidA];
-  const char* baseB = (const char*)inputs[g.gidB];
+  const char* baseB = g.b_gathered ? (const char*)scratch : (const char*)inputs[g.gidB];
   const char* baseA2 = baseA;
   const char* baseB2 = baseB;
+  char* split_planes = (char*)scratch;
+  if (g.b_gathered) {
+    // the gather kernel takes the Kernel's own parameters (inputs, out, scratch) and fills B (and its
+    // remainder plane) at the start of the scratch
+    std::vector<void*> gp(inputs.begin(), inputs.end());
+    gp.push_back(out);
+    gp.push_back(scratch);
+    std::vector<void*> gargs;
+    for (auto& p : gp) gargs.push_back(&p);
+    const Stage& ga = plan.stages[stage_i];
+    CUresult r = launch(fns[stage_i], ga.grid[0], 1, 1, ga.block[0], 1, 1, 0, (CUstream)stream, gargs.data(), nullptr);
+    if (r != CUDA_SUCCESS) { err = "launch of the operand gather kernel failed"; return -1; }
+    launches++;
+    stage_i++;
+    const size_t plane_bytes = (size_t)pad64(g.lenB) * e;
+    baseB2 = baseB + plane_bytes;
+    split_planes = (char*)scratch + plane_bytes * (kind == 2 ? 2 : 1);
+  }
   if (kind == 2) {
-    float* planes = (float*)scratch;
-    void* args[] = {(void*)&baseA, (void*)&baseB, (void*)&planes};
-    const Stage& sp = plan.stages[0];
-    CUresult r = launch(fns[0], sp.grid[0], 1, 1, sp.block[0], 1, 1, 0, (CUstream)stream, args, nullptr);
+    float* planes = (float*)split_planes;
+    const char* split_b = g.b_gathered ? baseA : baseB;   // not read when LEN_B is 0
+    void* args[] = {(void*)&baseA, (void*)&split_b, (void*)&planes};
+    const Stage& sp = plan.stages[stage_i];
+    CUresult r = launch(fns[stage_i], sp.grid[0], 1, 1, sp.block[0], 1, 1, 0, (CUstream)stream, args, nullptr);
     if (r != CUDA_SUCCESS) { err = "launch of the TF32 split kernel failed"; return -1; }
     launches++;
+    stage_i++;
     baseA2 = (const char*)planes;                     // lo planes; the operands themselves are the hi terms
-    baseB2 = (const char*)(planes + pad64(g.lenA));
+    if (!g.b_gathered) baseB2 = (const char*)(planes + pad64(g.lenA));
   }
   const CUtensorMapDataType dt = kind == 1 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
   const cuuint32_t inner_box = 128 / e;
   auto make_map = [&](CUtensorMap* m, const char* base, int64_t off, bool mn, int64_t mn_extent, int64_t k_extent,
                       int64_t outer_stride, int64_t batch_stride, int rows_box) -> bool {
     // dim 0 is the contiguous one: k for a K-major operand, m/n for an MN-major one
-    cuuint64_t dims[3] = {(cuuint64_t)(mn ? mn_extent : k_extent), (cuuint64_t)(mn ? k_extent : mn_extent), (cuuint64_t)g.batch};
+    // an operand every batch shares (batch stride 0) is described as a single plane; the kernel reads it at batch 0
+    cuuint64_t dims[3] = {(cuuint64_t)(mn ? mn_extent : k_extent), (cuuint64_t)(mn ? k_extent : mn_extent),
+                          (cuuint64_t)((g.batch > 1 && batch_stride == 0) ? 1 : g.batch)};
     cuuint64_t bs = batch_stride > 0 ? (cuuint64_t)batch_stride * e : dims[1] * (cuuint64_t)outer_stride * e;
     cuuint64_t strides[2] = {(cuuint64_t)outer_stride * e, bs};
     cuuint32_t box[3] = {inner_box, (cuuint32_t)rows_box, 1};

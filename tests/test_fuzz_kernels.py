@@ -197,6 +197,6 @@ def test_random_dot_shapes_plan_and_compile(seed):
     must compile for sm_100a whatever the route."""
     kernel, what = _random_dot(seed)
     describe, source = check_kernel(kernel, compile=True)
-    assert describe.split()[0] in ("gemm-tcgen05", "gemm-ffma", "dot-skinny", "dot-skinny-t", "dot-small-k", "reduce-row",
+    assert describe.split()[0] in ("gemm-tcgen05", "gemm-ffma", "dot-skinny", "dot-skinny-t", "dot-small-k", "reduce-row", "elementwise",
                                    "reduce-col"), (what, describe)
     assert 'extern "C" __global__' in source

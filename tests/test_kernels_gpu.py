@@ -299,7 +299,7 @@ def test_matvec_f16(backend, K, Nout, orientation):
 
 # ---- convolution and pooling: Dot / Reduce over pooled views (src/frontend/jit.ts:620-660) --------------
 
-def _conv_kernel(N, Ci, H, W, Co, KH, KW, stride, pad):
+def _conv_kernel(N, Ci, H, W, Co, KH, KW, stride, pad, dt=F32):
     """out[n, co, oh, ow] = sum_{ci, kh, kw} x[n, ci, oh*stride + kh - pad, ow*stride + kw - pad] * w[co, ci, kh, kw], the padded
     taps read as Where(valid, load, 0): the Kernel `jitRules[Conv]` builds from `prepareConv`'s views."""
     OH, OW = (H + 2 * pad - KH) // stride + 1, (W + 2 * pad - KW) // stride + 1
@@ -312,10 +312,10 @@ def _conv_kernel(N, Ci, H, W, Co, KH, KW, stride, pad):
     inside = lambda v, hi: AluExp.mul(AluExp.cast(I32, AluExp.cmplt(i(-1), v)), AluExp.cast(I32, AluExp.cmplt(v, i(hi))))
     valid = AluExp.cmpne(AluExp.mul(inside(ih, H), inside(iw, W)), i(0))
     xi = AluExp.add(AluExp.mul(AluExp.add(AluExp.mul(AluExp.add(AluExp.mul(n, i(Ci)), ci), i(H)), ih), i(W)), iw)
-    x = AluExp.where(valid, AluExp.global_index(F32, 0, N * Ci * H * W, xi), AluExp.f32(0))
+    x = AluExp.where(valid, AluExp.global_index(dt, 0, N * Ci * H * W, xi), AluExp.const(dt, 0))
     wi = AluExp.add(AluExp.mul(co, i(Ci * KH * KW)), r)
-    wv = AluExp.global_index(F32, 1, Co * Ci * KH * KW, wi)
-    return Kernel(2, N * Co * OH * OW, AluExp.mul(x, wv), Reduction(F32, AluOp.Add, Ci * KH * KW)), (OH, OW)
+    wv = AluExp.global_index(dt, 1, Co * Ci * KH * KW, wi)
+    return Kernel(2, N * Co * OH * OW, AluExp.mul(x, wv), Reduction(dt, AluOp.Add, Ci * KH * KW)), (OH, OW)
 
 
 @pytest.mark.parametrize("N,Ci,H,W,Co,KH,KW,stride,pad", [(2, 3, 17, 19, 5, 3, 3, 1, 1), (1, 8, 32, 32, 16, 5, 5, 2, 2), (3, 4, 9, 9, 6, 1, 1, 1, 0)])
@@ -334,6 +334,37 @@ def test_convolution_kernel_through_the_generic_skeletons(backend, N, Ci, H, W, 
     K = Ci * KH * KW
     assert_close(got / K, want / K, 1e-4, np.abs(x).max() * np.abs(w).max(), "conv vs oracle")
     assert_close(got, ref, 1e-5, np.abs(ref).max(), "conv vs float64")
+
+
+@pytest.mark.parametrize("N,Ci,H,W,Co,KH,KW,pad,dt", [(32, 64, 56, 56, 128, 3, 3, 1, F32), (8, 32, 30, 30, 96, 5, 5, 0, F32),
+                                                       (16, 64, 28, 28, 128, 3, 3, 1, F16)])
+def test_convolution_kernel_on_the_tensor_pipe(backend, N, Ci, H, W, Co, KH, KW, pad, dt):
+    """A convolution large enough to be worth it runs as a gather of the patch operand followed by the
+    tcgen05 GEMM (3xTF32 for float32): same Kernel, same oracle, GEMM tolerances."""
+    rng = np.random.default_rng(11)
+    npdt = np.float32 if dt == F32 else np.float16
+    x = (rng.standard_normal((N, Ci, H, W)) * (1.0 if dt == F32 else 0.25)).astype(npdt)
+    w = (rng.standard_normal((Co, Ci, KH, KW)) * (1.0 if dt == F32 else 0.05)).astype(npdt)
+    k, (OH, OW) = _conv_kernel(N, Ci, H, W, Co, KH, KW, 1, pad, dt)
+    assert backend.prepare_kernel(k).describe.startswith("conv as gemm-tcgen05"), backend.prepare_kernel(k).describe
+    got = run_cuda(backend, k, [x, w]).astype(np.float64).reshape(N, Co, OH, OW)
+    K = Ci * KH * KW
+    # the oracle on a sample of output ranges (whole images of a few channels, first and last batch)
+    want = np.zeros(k.size, npdt)
+    P = OH * OW
+    ranges = [(0, 3 * P), ((N * Co - 2) * P, N * Co * P), ((Co + 5) * P + 17, (Co + 6) * P + 17)]
+    for b, e in ranges:
+        oracle.run_kernel(k, [x, w], begin=b, end=e, fma=True, out=want)
+    sel = np.concatenate([np.arange(b, e) for b, e in ranges])
+    tol = 1e-4 if dt == F32 else 2e-3
+    assert_close(got.reshape(-1)[sel] / K, want.astype(np.float64)[sel] / K, tol, np.abs(x).max() * np.abs(w).max(), "conv vs oracle")
+    # and all of it against float64
+    xp = np.pad(x.astype(np.float64), ((0, 0), (0, 0), (pad, pad), (pad, pad)))
+    ref = np.zeros((N, Co, OH, OW))
+    for kh in range(KH):
+        for kw in range(KW):
+            ref += np.einsum("nchw,oc->nohw", xp[:, :, kh: kh + OH, kw: kw + OW], w[:, :, kh, kw].astype(np.float64), optimize=True)
+    assert_close(got, ref, 1e-5 if dt == F32 else 2e-3, np.abs(ref).max(), "conv vs float64")
 
 
 def test_max_pool_kernel(backend):
@@ -473,3 +504,45 @@ def test_gemm_f16(backend, n):
     got2 = run_cuda(backend, k, [(A * np.float16(2)), B]).astype(np.float64).reshape(n, n)
     normal = np.abs(got) >= 2.0 ** -13
     np.testing.assert_array_equal(got2[normal], 2 * got[normal])
+
+
+# ---- skeletons added for the Kernels `jit` emits around dots: transposing copies, unit reductions ----------
+
+@pytest.mark.parametrize("shape,perm", [((2048, 784), (1, 0)), ((1000, 333), (1, 0)), ((64, 50, 130), (2, 1, 0)), ((7, 600, 520), (0, 2, 1))])
+def test_materialised_transposes_use_the_tiled_skeleton_and_are_exact(backend, shape, perm):
+    from jax_js_b200 import ShapeTracker, accessor_global, unravel_alu
+    rng = np.random.default_rng(2)
+    x = rng.standard_normal(shape).astype(np.float32)
+    st = ShapeTracker.from_shape(shape).permute(perm)
+    n = x.size
+    k = Kernel(1, n, AluExp.mul(accessor_global(F32, 0, st, unravel_alu(st.shape, g)), AluExp.f32(2)))
+    assert backend.prepare_kernel(k).describe.startswith("elementwise transposed"), backend.prepare_kernel(k).describe
+    got = run_cuda(backend, k, [x])
+    assert np.array_equal(got, (x.transpose(perm) * 2).reshape(-1))
+    assert_same_bits(got, oracle.run_kernel(k, [x]), "transpose")
+
+
+def test_reduction_over_one_element_runs_as_elementwise(backend):
+    # an outer product written as a Dot with K = 1 (what vmap makes of a per-example weight gradient),
+    # with an epilogue that reads a third array
+    M, N = 300, 520
+    rng = np.random.default_rng(6)
+    a, b, c = rng.standard_normal(M).astype(np.float32), rng.standard_normal(N).astype(np.float32), rng.standard_normal(M * N).astype(np.float32)
+    k = P.dot_kernel(M, N, 1)
+    k.reduction.epilogue = AluExp.add(AluVar.acc(F32), AluExp.global_index(F32, 2, M * N, g))
+    k = Kernel(3, k.size, k.exp, k.reduction)
+    assert "unit reduction folded" in backend.prepare_kernel(k).describe
+    got = run_cuda(backend, k, [a, b, c])
+    assert_same_bits(got, oracle.run_kernel(k, [a, b, c]), "K = 1 dot")
+    assert np.array_equal(got.reshape(M, N), np.outer(a, b) + c.reshape(M, N))
+
+
+def test_skinny_dot_with_few_rows_and_many_columns(backend):
+    # C[10, 2048] = sum_b dz[b, 10] * a[b, 2048]: the weight gradient of the class layer as `transposeDot` writes it
+    M, N, K = 10, 2048, 5000
+    rng = np.random.default_rng(13)
+    A, B = rng.standard_normal((K, M)).astype(np.float32), rng.standard_normal((K, N)).astype(np.float32)
+    k = P.dot_kernel(M, N, K, a_layout="km", b_layout="kn")
+    assert backend.prepare_kernel(k).describe.startswith("dot-skinny-t (operands swapped)"), backend.prepare_kernel(k).describe
+    got = _gemm_case(backend, k, [A, B], K, 1e-4, F32).reshape(M, N)
+    assert_close(got, A.T.astype(np.float64) @ B.astype(np.float64), 1e-5, np.abs(A).max() * np.abs(B).max() * np.sqrt(K), "vs float64")
