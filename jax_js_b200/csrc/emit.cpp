@@ -389,8 +389,8 @@ struct Builder {
       best = i; best_len = nd.arg1; dB = tb->div; mB = b_mod; mA = a_mod;
     }
     if (!best_len || (int64_t)k.size % (dB * mB)) return false;
-    // the staged load must be a good part of all the bytes the Kernel moves, or staging it changes little
-    if ((double)best_len * 4 < 0.25 * p.algo_bytes) return false;
+    // (a small strided array is staged as well: read directly, each of a warp's loads touches 32
+    // lines whatever the array's size, and that is what bounds such a Kernel, not the bytes)
     const int64_t tilesA = (mA + 31) / 32, tilesB = (mB + 31) / 32, mids = dB / mA, his = (int64_t)k.size / (dB * mB);
     const int64_t blocks = tilesA * tilesB * mids * his;
     if (blocks > 0x7fffffffLL) return false;

@@ -8,8 +8,8 @@
 //
 // Parallelism: independent matrices (and right-hand sides) go to different CTAs (warps); inside a
 // matrix the algorithms are the reference's, column by column, with the work of one column spread
-// over the CTA.  A matrix stays in L2/L1 while its CTA works on it.  Large single matrices would
-// want a blocked, multi-CTA factorisation on top of the GEMM skeleton; that is not built.
+// over the CTA.  A matrix stays in L2/L1 while its CTA works on it.  Cholesky of matrices with 256
+// rows or more runs blocked over many CTAs (below); LU and the triangular solve do not.
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -58,6 +58,144 @@ __global__ void __launch_bounds__(1024) cholesky_kernel(const T* __restrict__ x,
     }
     __syncthreads();
   }
+}
+
+// ---- blocked Cholesky over many CTAs, for matrices of 256 rows and more ---------------------------
+// The reference switches to a blocked multi-pass variant on its GPU backend for large matrices
+// (src/backend/webgpu/routines.ts:630-634).  Here the matrix is cut into block columns of NB = 64.
+// L[i, j] = (A[i, j] - sum_{k<j} L[i, k] L[j, k]) / L[j, j] keeps the reference's arithmetic: the sum
+// is a double from k = 0 to j - 1 and the only rounding is the store.  For the block column that
+// starts at column J0 the sum is split at J0:
+//   chol_update   S[i, c] = sum_{k < J0} L[i, k] L[J0 + c, k]       every row i >= J0, many CTAs, double
+//   chol_diag     the NB x NB diagonal block, column by column, from S  one CTA
+//   chol_rows     rows below the block, each on its own (a row needs  a warp per row, many CTAs
+//                 only itself and the diagonal block)
+// S stays in double in a work buffer, so no value is rounded before its store.
+constexpr int kCholNB = 64;
+
+template <class T>
+__global__ void __launch_bounds__(256) chol_update(const T* __restrict__ y, double* __restrict__ S, int n, int J0) {
+  // CTA: 64 rows x 64 block columns; thread: 4 x 4 outputs; K in slices of 16 through shared memory
+  __shared__ double As[16][64 + 1], Bs[16][64 + 1];
+  const T* L = y + (size_t)blockIdx.y * n * n;
+  double* Sm = S + (size_t)blockIdx.y * n * kCholNB;
+  const int r0 = J0 + blockIdx.x * 64;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  double acc[4][4] = {};
+  for (int k0 = 0; k0 < J0; k0 += 16) {
+    for (int e = threadIdx.x; e < 64 * 16; e += 256) {
+      const int rr = e >> 4, kk = e & 15;
+      const int i = r0 + rr, c = J0 + rr;
+      As[kk][rr] = (i < n) ? (double)L[(size_t)i * n + k0 + kk] : 0.0;
+      Bs[kk][rr] = (c < n) ? (double)L[(size_t)c * n + k0 + kk] : 0.0;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 16; kk++) {
+      double a[4], b[4];
+#pragma unroll
+      for (int u = 0; u < 4; u++) { a[u] = As[kk][ty * 4 + u]; b[u] = Bs[kk][tx * 4 + u]; }
+#pragma unroll
+      for (int u = 0; u < 4; u++)
+#pragma unroll
+        for (int v = 0; v < 4; v++) acc[u][v] = fma(a[u], b[v], acc[u][v]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int u = 0; u < 4; u++) {
+    const int i = r0 + ty * 4 + u;
+    if (i >= n) continue;
+#pragma unroll
+    for (int v = 0; v < 4; v++) Sm[(size_t)i * kCholNB + tx * 4 + v] = acc[u][v];
+  }
+}
+
+template <class T>
+__global__ void __launch_bounds__(256) chol_diag(const T* __restrict__ x, T* __restrict__ y, const double* __restrict__ S, int n, int J0) {
+  __shared__ double Lb[kCholNB][kCholNB + 1];   // the block's entries as stored
+  const T* A = x + (size_t)blockIdx.x * n * n;
+  T* L = y + (size_t)blockIdx.x * n * n;
+  const double* Sm = S + (size_t)blockIdx.x * n * kCholNB;
+  const int nb = min(kCholNB, n - J0);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int c = 0; c < nb; c++) {
+    const int j = J0 + c;
+    if (warp == 0) {
+      double s = 0.0;
+      for (int k = lane; k < c; k += 32) s = fma(Lb[c][k], Lb[c][k], s);
+      s = warp_sum(s);
+      if (lane == 0) {
+        const T d = (T)sqrt((double)A[(size_t)j * n + j] - (Sm[(size_t)j * kCholNB + c] + s));
+        L[(size_t)j * n + j] = d;
+        Lb[c][c] = (double)d;
+      }
+    }
+    __syncthreads();
+    const double d = Lb[c][c];
+    for (int r = c + 1 + warp; r < nb; r += nw) {
+      double s = 0.0;
+      for (int k = lane; k < c; k += 32) s = fma(Lb[r][k], Lb[c][k], s);
+      s = warp_sum(s);
+      if (lane == 0) {
+        const int i = J0 + r;
+        const T v = (T)(((double)A[(size_t)i * n + j] - (Sm[(size_t)i * kCholNB + c] + s)) / d);
+        L[(size_t)i * n + j] = v;
+        Lb[r][c] = (double)v;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+template <class T>
+__global__ void __launch_bounds__(256) chol_rows(const T* __restrict__ x, T* __restrict__ y, const double* __restrict__ S, int n, int J0) {
+  __shared__ double Lb[kCholNB][kCholNB + 1];
+  __shared__ double rowv[8][kCholNB];
+  const T* A = x + (size_t)blockIdx.y * n * n;
+  T* L = y + (size_t)blockIdx.y * n * n;
+  const double* Sm = S + (size_t)blockIdx.y * n * kCholNB;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int e = threadIdx.x; e < kCholNB * kCholNB; e += 256) {
+    const int r = e / kCholNB, c = e % kCholNB;
+    Lb[r][c] = (c <= r && J0 + r < n) ? (double)L[(size_t)(J0 + r) * n + J0 + c] : 0.0;
+  }
+  __syncthreads();
+  const int i = J0 + kCholNB + blockIdx.x * 8 + warp;
+  if (i >= n) return;
+  double* rv = rowv[warp];
+  for (int c = 0; c < kCholNB; c++) {
+    double s = 0.0;
+    for (int k = lane; k < c; k += 32) s = fma(rv[k], Lb[c][k], s);
+    s = warp_sum(s);
+    if (lane == 0) {
+      const int j = J0 + c;
+      const T v = (T)(((double)A[(size_t)i * n + j] - (Sm[(size_t)i * kCholNB + c] + s)) / Lb[c][c]);
+      L[(size_t)i * n + j] = v;
+      rv[c] = (double)v;
+    }
+    __syncwarp();
+  }
+}
+
+template <class T>
+cudaError_t cholesky_blocked(cudaStream_t stream, const T* x, T* y, double* work, int64_t batch, int n, int* launches) {
+  cudaError_t e = cudaMemsetAsync(y, 0, (size_t)batch * n * n * sizeof(T), stream);
+  if (e != cudaSuccess) return e;
+  for (int J0 = 0; J0 < n; J0 += kCholNB) {
+    const int rows = n - J0;
+    if (J0 > 0) {
+      chol_update<T><<<dim3((rows + 63) / 64, (unsigned)batch), 256, 0, stream>>>(y, work, n, J0);
+    } else {
+      e = cudaMemsetAsync(work, 0, (size_t)batch * n * kCholNB * sizeof(double), stream);
+      if (e != cudaSuccess) return e;
+    }
+    chol_diag<T><<<(unsigned)batch, 256, 0, stream>>>(x, y, work, n, J0);
+    const int below = rows - kCholNB;
+    if (below > 0) chol_rows<T><<<dim3((below + 7) / 8, (unsigned)batch), 256, 0, stream>>>(x, y, work, n, J0);
+    if (launches) *launches += 3;
+  }
+  return cudaGetLastError();
 }
 
 // ---- back substitution, one warp per right-hand side ----------------------------------------------
@@ -268,9 +406,19 @@ cudaError_t allow_smem(K kernel, size_t bytes) {
 
 extern "C" {
 
-int jaxcuda_cholesky_launch(cudaStream_t stream, int dtype, const void* x, void* y, int64_t batch, int64_t n, int* launches) {
+size_t jaxcuda_cholesky_work_bytes(int64_t batch, int64_t n) {
+  return n >= 256 ? (size_t)batch * (size_t)n * kCholNB * sizeof(double) : 0;
+}
+
+int jaxcuda_cholesky_launch(cudaStream_t stream, int dtype, const void* x, void* y, int64_t batch, int64_t n, void* work,
+                            int* launches) {
   if (launches) *launches = 0;
   if (batch <= 0 || n <= 0) return cudaSuccess;
+  if (n >= 256) {
+    if (!work || batch > 65535 || n > 0x7fffffff / 2) return cudaErrorInvalidValue;
+    if (dtype == JAXCUDA_F32) return cholesky_blocked<float>(stream, (const float*)x, (float*)y, (double*)work, batch, (int)n, launches);
+    return cholesky_blocked<double>(stream, (const double*)x, (double*)y, (double*)work, batch, (int)n, launches);
+  }
   const size_t smem = (size_t)(n + 1) * sizeof(double);
   if (smem > 200 * 1024 || batch > 0x7fffffff) return cudaErrorInvalidValue;
   const int threads = n >= 256 ? 1024 : n >= 64 ? 256 : 64;

@@ -11,7 +11,11 @@ extern "C" {
 // dtype: JAXCUDA_F32 or JAXCUDA_F64.  Each returns a cudaError_t value (0 = launched).
 
 // y[b] = lower-triangular L with x[b] = L L^T, upper triangle zero-filled; x, y: [batch, n, n].
-int jaxcuda_cholesky_launch(cudaStream_t stream, int dtype, const void* x, void* y, int64_t batch, int64_t n, int* launches);
+// Matrices of 256 rows or more are factored block column by block column over many CTAs and need
+// `work` (jaxcuda_cholesky_work_bytes bytes; null below that size).
+size_t jaxcuda_cholesky_work_bytes(int64_t batch, int64_t n);
+int jaxcuda_cholesky_launch(cudaStream_t stream, int dtype, const void* x, void* y, int64_t batch, int64_t n, void* work,
+                            int* launches);
 
 // a: [mats, n, n] upper triangular, b and x: [mats, rows, n]; each row solves a x = b.
 int jaxcuda_triangular_solve_launch(cudaStream_t stream, int dtype, const void* a, const void* b, void* x, int64_t mats,

@@ -33,7 +33,7 @@
 #include <sstream>
 #include <unordered_set>
 
-extern "C" size_t jaxcuda_sort_work_bytes(int argsort, int64_t batch, int64_t n);
+extern "C" size_t jaxcuda_sort_work_bytes(int argsort, int dtype, int64_t batch, int64_t n);
 extern "C" int jaxcuda_sort_launch(void* stream, int argsort, const void* x, void* y, int32_t* yi, int dtype,
                                    int64_t batch, int64_t n, void* work, int* launches);
 
@@ -921,7 +921,6 @@ int jaxcuda_prepare_routine(jaxcuda_ctx* ctx, const char* name, const jaxcuda_ro
   const int rank = type->input_ranks[0];
   if (rank == 0) return fail(ctx, JAXCUDA_EINVAL, "%s: cannot sort a scalar", is_sort ? "sort" : "argsort");  // routine.ts:187, :197
   const int dt = type->input_dtypes[0];
-  if (dt == JAXCUDA_F64) return fail(ctx, JAXCUDA_EUNSUPPORTED, "%s<float64> not supported in cuda backend", name);
   std::unique_ptr<jaxcuda_exe> exe(new jaxcuda_exe);
   exe->ctx = ctx;
   exe->kind = is_sort ? 1 : 2;
@@ -992,13 +991,29 @@ int jaxcuda_dispatch(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const jaxcuda_slot* inp
       for (int i = 0; i < 2; i++)
         if (in[i]->bytes < b * n * e || outv[i]->bytes < b * n * e)
           return fail(ctx, JAXCUDA_EINVAL, "routine buffers are smaller than its declared shapes");
+      int max_radix = 1;
+      for (int f : exe->rt_factors) max_radix = std::max(max_radix, f);
+      const size_t wb = jaxcuda_fft_work_bytes(exe->rt_dtype, exe->rt_batch, exe->rt_n, max_radix);
+      void* work = nullptr;
+      if (wb) {
+        cudaError_t ae = ctx->alloc.get(wb, &work);
+        if (ae != cudaSuccess) return fail(ctx, JAXCUDA_ENOMEM, "fft work space of %zu bytes: %s", wb, cudaGetErrorString(ae));
+      }
       rc = jaxcuda_fft_launch(ctx->stream, exe->rt_dtype, in[0]->ptr, in[1]->ptr, outv[0]->ptr, outv[1]->ptr, exe->rt_batch, exe->rt_n,
-                              exe->rt_factors.data(), (int)exe->rt_factors.size(), exe->rt_flag, &launches);
+                              exe->rt_factors.data(), (int)exe->rt_factors.size(), exe->rt_flag, work, &launches);
+      if (work) ctx->alloc.put(work, wb);  // stream order keeps it alive for the launches above
     } else if (exe->kind == 5) {
       if (n_inputs != 1 || n_outputs != 1) return fail(ctx, JAXCUDA_EINVAL, "Cholesky called with wrong slot counts");
       if (in[0]->bytes < b * n * n * e || outv[0]->bytes < b * n * n * e)
         return fail(ctx, JAXCUDA_EINVAL, "routine buffers are smaller than its declared shapes");
-      rc = jaxcuda_cholesky_launch(ctx->stream, exe->rt_dtype, in[0]->ptr, outv[0]->ptr, exe->rt_batch, exe->rt_n, &launches);
+      const size_t wb = jaxcuda_cholesky_work_bytes(exe->rt_batch, exe->rt_n);
+      void* work = nullptr;
+      if (wb) {
+        cudaError_t ae = ctx->alloc.get(wb, &work);
+        if (ae != cudaSuccess) return fail(ctx, JAXCUDA_ENOMEM, "cholesky work space of %zu bytes: %s", wb, cudaGetErrorString(ae));
+      }
+      rc = jaxcuda_cholesky_launch(ctx->stream, exe->rt_dtype, in[0]->ptr, outv[0]->ptr, exe->rt_batch, exe->rt_n, work, &launches);
+      if (work) ctx->alloc.put(work, wb);
     } else {
       if (n_inputs != 1 || n_outputs != 3) return fail(ctx, JAXCUDA_EINVAL, "LU called with wrong slot counts");
       const size_t r = std::min(m, n);
@@ -1017,7 +1032,7 @@ int jaxcuda_dispatch(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const jaxcuda_slot* inp
     const size_t need = (size_t)exe->rt_batch * exe->rt_n * dtype_bytes(exe->rt_dtype);
     if (in[0]->bytes < need || outv[0]->bytes < need || (arg && outv[1]->bytes < (size_t)exe->rt_batch * exe->rt_n * 4))
       return fail(ctx, JAXCUDA_EINVAL, "routine buffers are smaller than its declared shapes");
-    const size_t wb = jaxcuda_sort_work_bytes(arg, exe->rt_batch, exe->rt_n);
+    const size_t wb = jaxcuda_sort_work_bytes(arg, exe->rt_dtype, exe->rt_batch, exe->rt_n);
     void* work = nullptr;
     if (wb) {
       cudaError_t e = ctx->alloc.get(wb, &work);

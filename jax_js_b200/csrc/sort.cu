@@ -7,7 +7,7 @@
 //            (src/routine.ts:195-214); outputs the gathered values and int32 indices.
 //
 // Both are compare-only, so results are bit-exact.  Values are mapped to order-preserving
-// uint32 keys and sorted with a bitonic network: one CTA per row in shared memory while the
+// unsigned keys (32 bits; 64 bits for float64) and sorted with a bitonic network: one CTA per row in shared memory while the
 // padded row fits (the reference's WGSL routine has the same shape,
 // src/backend/webgpu/routines.ts:57-261), otherwise chunk sorts in shared memory joined by
 // global compare-exchange passes.  Argsort sorts (key, index) pairs as one 64-bit composite,
@@ -58,17 +58,69 @@ __device__ __forceinline__ void copy_elem(void* dst, const void* src, int dtype,
   else ((uint32_t*)dst)[di] = ((const uint32_t*)src)[si];
 }
 
-template <bool ARG> struct Item;
-template <> struct Item<false> { typedef uint32_t T; };
-template <> struct Item<true> { typedef unsigned long long T; };
+// float64: the same mapping on 64 bits.
+__device__ __forceinline__ unsigned long long make_key64(const void* row, int64_t i, bool canon) {
+  unsigned long long bits = ((const unsigned long long*)row)[i];
+  const bool nan = (bits & 0x7fffffffffffffffull) > 0x7ff0000000000000ull;
+  if (nan) return canon ? ~0ull : (0xfff8000000000000ull | (bits & 0x0007ffffffffffffull));
+  if (canon && bits == 0x8000000000000000ull) bits = 0;
+  return (bits & 0x8000000000000000ull) ? ~bits : (bits | 0x8000000000000000ull);
+}
+__device__ __forceinline__ unsigned long long bits_from_key64(unsigned long long key) {
+  return (key & 0x8000000000000000ull) ? (key & 0x7fffffffffffffffull) : ~key;
+}
 
-template <bool ARG>
-__device__ __forceinline__ typename Item<ARG>::T load_item(const void* row, int dtype, int64_t n, int64_t i) {
-  if (ARG) {
+// A 64-bit key with the element's index: Argsort of float64.
+struct KeyIndex {
+  unsigned long long key;
+  unsigned long long idx;
+  __device__ __forceinline__ bool operator>(const KeyIndex& o) const { return key > o.key || (key == o.key && idx > o.idx); }
+};
+
+// ARG: Argsort (items carry the index); WIDE: float64 (64-bit keys).
+template <bool ARG, bool WIDE> struct Item;
+template <> struct Item<false, false> { typedef uint32_t T; };
+template <> struct Item<true, false> { typedef unsigned long long T; };
+template <> struct Item<false, true> { typedef unsigned long long T; };
+template <> struct Item<true, true> { typedef KeyIndex T; };
+
+__device__ __forceinline__ uint32_t item_index(unsigned long long it) { return (uint32_t)it; }
+__device__ __forceinline__ uint32_t item_index(const KeyIndex& it) { return (uint32_t)it.idx; }
+__device__ __forceinline__ uint32_t item_index(uint32_t) { return 0; }
+
+template <bool ARG, bool WIDE>
+__device__ __forceinline__ typename Item<ARG, WIDE>::T load_item(const void* row, int dtype, int64_t n, int64_t i) {
+  typedef typename Item<ARG, WIDE>::T T;
+  if constexpr (WIDE && ARG) {
+    KeyIndex it;
+    it.key = i < n ? make_key64(row, i, true) : ~0ull;
+    it.idx = (unsigned long long)i;
+    return it;
+  } else if constexpr (WIDE) {
+    return (T)(i < n ? make_key64(row, i, false) : ~0ull);
+  } else if constexpr (ARG) {
     uint32_t key = i < n ? make_key(row, dtype, i, true) : 0xffffffffu;
-    return (typename Item<ARG>::T)(((unsigned long long)key << 32) | (uint32_t)i);
+    return (T)(((unsigned long long)key << 32) | (uint32_t)i);
+  } else {
+    return (T)(i < n ? make_key(row, dtype, i, false) : 0xffffffffu);
   }
-  return (typename Item<ARG>::T)(i < n ? make_key(row, dtype, i, false) : 0xffffffffu);
+}
+
+// Writes output element i of a row from its sorted item (Sort: the key mapped back; Argsort: the
+// index and the value gathered from the input row).
+template <bool ARG, bool WIDE>
+__device__ __forceinline__ void store_item(const typename Item<ARG, WIDE>::T& it, const void* xr, void* yr, int32_t* yi_row,
+                                           int dtype, int64_t i) {
+  if constexpr (ARG) {
+    const uint32_t src = item_index(it);
+    yi_row[i] = (int32_t)src;
+    if constexpr (WIDE) ((unsigned long long*)yr)[i] = ((const unsigned long long*)xr)[src];
+    else copy_elem(yr, xr, dtype, i, src);
+  } else if constexpr (WIDE) {
+    ((unsigned long long*)yr)[i] = bits_from_key64(it);
+  } else {
+    store_from_key(yr, dtype, i, (uint32_t)it);
+  }
 }
 
 template <class T>
@@ -93,35 +145,30 @@ __device__ __forceinline__ void bitonic_smem(T* s, int cnt, int64_t base, int64_
 }
 
 // Whole padded row (P items) fits in shared memory: one CTA per row.
-template <bool ARG>
+__device__ __forceinline__ int elem_bytes(int dtype) { return dtype == JAXCUDA_F16 ? 2 : dtype == JAXCUDA_F64 ? 8 : 4; }
+
+template <bool ARG, bool WIDE>
 __global__ void sort_rows_smem(const void* x, void* y, int32_t* yi, int dtype, int64_t n, int P) {
-  typedef typename Item<ARG>::T T;
+  typedef typename Item<ARG, WIDE>::T T;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   T* s = (T*)smem_raw;
-  const int eb = dtype == JAXCUDA_F16 ? 2 : 4;
+  const int eb = elem_bytes(dtype);
   const unsigned char* xr = (const unsigned char*)x + (size_t)blockIdx.x * n * eb;
   unsigned char* yr = (unsigned char*)y + (size_t)blockIdx.x * n * eb;
-  for (int i = threadIdx.x; i < P; i += blockDim.x) s[i] = load_item<ARG>(xr, dtype, n, i);
+  for (int i = threadIdx.x; i < P; i += blockDim.x) s[i] = load_item<ARG, WIDE>(xr, dtype, n, i);
   __syncthreads();
   bitonic_smem(s, P, 0, 2, P);
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    if (ARG) {
-      const uint32_t src = (uint32_t)s[i];
-      yi[(size_t)blockIdx.x * n + i] = (int32_t)src;
-      copy_elem(yr, xr, dtype, i, src);
-    } else {
-      store_from_key(yr, dtype, i, (uint32_t)s[i]);
-    }
-  }
+  for (int i = threadIdx.x; i < n; i += blockDim.x)
+    store_item<ARG, WIDE>(s[i], xr, yr, ARG ? yi + (size_t)blockIdx.x * n : nullptr, dtype, i);
 }
 
 // Large rows: items live in a global work buffer of batch * P items.
-template <bool ARG>
-__global__ void sort_fill(const void* x, typename Item<ARG>::T* work, int dtype, int64_t n, int64_t P, int64_t total) {
-  const int eb = dtype == JAXCUDA_F16 ? 2 : 4;
+template <bool ARG, bool WIDE>
+__global__ void sort_fill(const void* x, typename Item<ARG, WIDE>::T* work, int dtype, int64_t n, int64_t P, int64_t total) {
+  const int eb = elem_bytes(dtype);
   for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
     const int64_t row = t / P, i = t % P;
-    work[t] = load_item<ARG>((const unsigned char*)x + (size_t)row * n * eb, dtype, n, i);
+    work[t] = load_item<ARG, WIDE>((const unsigned char*)x + (size_t)row * n * eb, dtype, n, i);
   }
 }
 
@@ -147,37 +194,30 @@ __global__ void sort_global_step(T* work, int64_t P, int64_t k, int64_t j, int64
   }
 }
 
-template <bool ARG>
-__global__ void sort_drain(const typename Item<ARG>::T* work, const void* x, void* y, int32_t* yi, int dtype,
+template <bool ARG, bool WIDE>
+__global__ void sort_drain(const typename Item<ARG, WIDE>::T* work, const void* x, void* y, int32_t* yi, int dtype,
                            int64_t n, int64_t P, int64_t total) {
-  const int eb = dtype == JAXCUDA_F16 ? 2 : 4;
+  const int eb = elem_bytes(dtype);
   for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
     const int64_t row = t / n, i = t % n;
-    const typename Item<ARG>::T it = work[row * P + i];
-    unsigned char* yr = (unsigned char*)y + (size_t)row * n * eb;
-    if (ARG) {
-      const uint32_t src = (uint32_t)it;
-      yi[t] = (int32_t)src;
-      copy_elem(yr, (const unsigned char*)x + (size_t)row * n * eb, dtype, i, src);
-    } else {
-      store_from_key(yr, dtype, i, (uint32_t)it);
-    }
+    store_item<ARG, WIDE>(work[row * P + i], (const unsigned char*)x + (size_t)row * n * eb,
+                          (unsigned char*)y + (size_t)row * n * eb, ARG ? yi + row * n : nullptr, dtype, i);
   }
 }
 
-template <bool ARG>
+template <bool ARG, bool WIDE>
 cudaError_t run(cudaStream_t st, const void* x, void* y, int32_t* yi, int dtype, int64_t batch, int64_t n,
                 void* work, int* launches) {
-  typedef typename Item<ARG>::T T;
+  typedef typename Item<ARG, WIDE>::T T;
   int64_t P = 2;
   while (P < n) P <<= 1;
-  const int64_t smem_items = ARG ? 16384 : 32768;  // 128 KiB of items
+  const int64_t smem_items = (128 * 1024) / (int64_t)sizeof(T);  // 128 KiB of items
   if (P <= smem_items) {
     const int threads = (int)(P / 2 < 32 ? 32 : P / 2 > 1024 ? 1024 : P / 2);
     const size_t smem = (size_t)P * sizeof(T);
-    cudaError_t e = cudaFuncSetAttribute(sort_rows_smem<ARG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(sort_rows_smem<ARG, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
     if (e != cudaSuccess) return e;
-    sort_rows_smem<ARG><<<(unsigned)batch, threads, smem, st>>>(x, y, yi, dtype, n, (int)P);
+    sort_rows_smem<ARG, WIDE><<<(unsigned)batch, threads, smem, st>>>(x, y, yi, dtype, n, (int)P);
     (*launches)++;
     return cudaGetLastError();
   }
@@ -187,7 +227,7 @@ cudaError_t run(cudaStream_t st, const void* x, void* y, int32_t* yi, int dtype,
   const unsigned wide = (unsigned)((total + 255) / 256 > 148 * 32 ? 148 * 32 : (total + 255) / 256);
   cudaError_t e = cudaFuncSetAttribute(sort_chunks<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
   if (e != cudaSuccess) return e;
-  sort_fill<ARG><<<wide, 256, 0, st>>>(x, w, dtype, n, P, total);
+  sort_fill<ARG, WIDE><<<wide, 256, 0, st>>>(x, w, dtype, n, P, total);
   sort_chunks<T><<<(unsigned)(total / C), 1024, (size_t)C * sizeof(T), st>>>(w, C, P, 2, C);
   *launches += 2;
   for (int64_t k = (int64_t)C * 2; k <= P; k <<= 1) {
@@ -199,7 +239,7 @@ cudaError_t run(cudaStream_t st, const void* x, void* y, int32_t* yi, int dtype,
     (*launches)++;
   }
   const int64_t out_total = batch * n;
-  sort_drain<ARG><<<(unsigned)((out_total + 255) / 256 > 148 * 32 ? 148 * 32 : (out_total + 255) / 256), 256, 0, st>>>(
+  sort_drain<ARG, WIDE><<<(unsigned)((out_total + 255) / 256 > 148 * 32 ? 148 * 32 : (out_total + 255) / 256), 256, 0, st>>>(
       w, x, y, yi, dtype, n, P, out_total);
   (*launches)++;
   return cudaGetLastError();
@@ -208,20 +248,23 @@ cudaError_t run(cudaStream_t st, const void* x, void* y, int32_t* yi, int dtype,
 }  // namespace jaxcuda_sort
 
 // Bytes of global work space a sort of rows of n items needs (0 when rows fit in shared memory).
-extern "C" size_t jaxcuda_sort_work_bytes(int argsort, int64_t batch, int64_t n) {
+extern "C" size_t jaxcuda_sort_work_bytes(int argsort, int dtype, int64_t batch, int64_t n) {
   int64_t P = 2;
   while (P < n) P <<= 1;
-  const int64_t smem_items = argsort ? 16384 : 32768;
-  if (P <= smem_items) return 0;
-  return (size_t)batch * P * (argsort ? 8 : 4);
+  const int64_t item = dtype == JAXCUDA_F64 ? (argsort ? 16 : 8) : (argsort ? 8 : 4);
+  if (P <= (128 * 1024) / item) return 0;
+  return (size_t)batch * P * item;
 }
 
 extern "C" int jaxcuda_sort_launch(void* stream, int argsort, const void* x, void* y, int32_t* yi, int dtype,
                                    int64_t batch, int64_t n, void* work, int* launches) {
   cudaStream_t st = (cudaStream_t)stream;
   if (batch == 0 || n == 0) return 0;
-  return (int)(argsort ? jaxcuda_sort::run<true>(st, x, y, yi, dtype, batch, n, work, launches)
-                       : jaxcuda_sort::run<false>(st, x, y, yi, dtype, batch, n, work, launches));
+  if (dtype == JAXCUDA_F64)
+    return (int)(argsort ? jaxcuda_sort::run<true, true>(st, x, y, yi, dtype, batch, n, work, launches)
+                         : jaxcuda_sort::run<false, true>(st, x, y, yi, dtype, batch, n, work, launches));
+  return (int)(argsort ? jaxcuda_sort::run<true, false>(st, x, y, yi, dtype, batch, n, work, launches)
+                       : jaxcuda_sort::run<false, false>(st, x, y, yi, dtype, batch, n, work, launches));
 }
 
 // ---- Sort without any allocation --------------------------------------------------------------
@@ -275,6 +318,10 @@ extern "C" int jaxcuda_sort_no_alloc(void* stream, int dtype, const void* x, voi
   }
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(5, "sort_no_alloc: no current CUDA device");
+  // the static buffer that is looked up below belongs to the current device: the data must live there too
+  cudaPointerAttributes at;
+  if (cudaPointerGetAttributes(&at, x) == cudaSuccess && at.type == cudaMemoryTypeDevice && at.device != dev)
+    return fail(3, "sort_no_alloc: the input lives on another device than the current one");
   if (!g_static_work_addr[dev]) {
     void* p = nullptr;
     cudaError_t e = cudaGetSymbolAddress(&p, jx_sort_static_work);
@@ -282,7 +329,7 @@ extern "C" int jaxcuda_sort_no_alloc(void* stream, int dtype, const void* x, voi
     g_static_work_addr[dev] = p;
   }
   int launches = 0;
-  cudaError_t e = jaxcuda_sort::run<false>((cudaStream_t)stream, x, y, nullptr, dtype, batch, n, g_static_work_addr[dev], &launches);
+  cudaError_t e = jaxcuda_sort::run<false, false>((cudaStream_t)stream, x, y, nullptr, dtype, batch, n, g_static_work_addr[dev], &launches);
   if (e != cudaSuccess) return fail(5, cudaGetErrorString(e));
   return 0;
 }

@@ -113,7 +113,7 @@ def _close(got, want, tol=2e-6):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("batch,n", [(1, 1), (1, 2), (5, 3), (3, 33), (2, 130), (1, 512)])
+@pytest.mark.parametrize("batch,n", [(1, 1), (1, 2), (5, 3), (3, 33), (2, 130), (2, 255), (1, 256), (3, 300), (1, 512), (1, 1500)])   # 256 and up: blocked over many CTAs
 def test_cuda_cholesky(backend, batch, n):
     x = _spd(np.random.default_rng(n), batch, n)
     (L,) = _run(backend, Routines.Cholesky, [x], [x.shape], [F32])
@@ -126,9 +126,10 @@ def test_cuda_cholesky(backend, batch, n):
 
 @pytest.mark.gpu
 def test_cuda_cholesky_float64_and_indefinite_input(backend):
-    x = _spd(np.random.default_rng(3), 2, 40, np.float64)
-    (L,) = _run(backend, Routines.Cholesky, [x], [x.shape], [F64])
-    _close(L, oracle.cholesky(x), 1e-13)
+    for n in (40, 321):
+        x = _spd(np.random.default_rng(3), 2, n, np.float64)
+        (L,) = _run(backend, Routines.Cholesky, [x], [x.shape], [F64])
+        _close(L, oracle.cholesky(x), 1e-13)
     bad = np.array([[[1.0, 2.0], [2.0, 1.0]]], np.float32)  # not positive definite: sqrt of a negative number
     (L,) = _run(backend, Routines.Cholesky, [bad], [bad.shape], [F32])
     want = oracle.cholesky(bad)
@@ -281,7 +282,7 @@ def test_cuda_jacobi_eigh_float64_and_diagonal_input(backend):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("n", [1, 2, 3, 4, 8, 12, 30, 49, 97, 128, 360, 1001, 4096])
+@pytest.mark.parametrize("n", [1, 2, 3, 4, 8, 12, 30, 49, 97, 128, 360, 1001, 4096, 8192, 30030, 65536])   # from 8192 on a row exceeds shared memory
 @pytest.mark.parametrize("inverse", [False, True])
 def test_cuda_fft(backend, n, inverse):
     rng = np.random.default_rng(n)
@@ -308,6 +309,9 @@ def test_cuda_fft_float64_and_bad_factors(backend):
     re, im = rng.standard_normal((3, 60)), rng.standard_normal((3, 60))
     r, i = _run(backend, Routines.Fft, [re, im], [re.shape, im.shape], [F64, F64], {"factors": factor_fft_size(60), "inverse": False})
     np.testing.assert_allclose(r + 1j * i, np.fft.fft(re + 1j * im), atol=1e-12)
+    re, im = rng.standard_normal((2, 6000)), rng.standard_normal((2, 6000))      # float64 rows beyond shared memory
+    r, i = _run(backend, Routines.Fft, [re, im], [re.shape, im.shape], [F64, F64], {"factors": factor_fft_size(6000), "inverse": True})
+    np.testing.assert_allclose(r + 1j * i, np.fft.ifft(re + 1j * im), atol=1e-13)
     t = RoutineType([[8], [8]], [F32, F32], [[8], [8]], [F32, F32])
     with pytest.raises(ValueError, match="fft: factors do not multiply"):
         backend.prepare_routine(Routine(Routines.Fft, t, {"factors": [2, 2], "inverse": False}))

@@ -10,7 +10,7 @@ from jax_js_b200.routine import Routine, Routines, RoutineType
 from util import assert_same_bits
 
 pytestmark = pytest.mark.gpu
-F32, I32, U32, BOOL, F16 = DType.Float32, DType.Int32, DType.Uint32, DType.Bool, DType.Float16
+F32, I32, U32, BOOL, F16, F64 = DType.Float32, DType.Int32, DType.Uint32, DType.Bool, DType.Float16, DType.Float64
 
 
 def cuda_sort(backend, x, dtype, arg=False):
@@ -57,10 +57,10 @@ def test_reference_argsort_vectors(backend):
 
 
 @pytest.mark.parametrize("shape", [(1, 1), (7, 2), (5, 1000), (128, 1024), (3, 16384), (2, 40000), (1, 300001)])
-@pytest.mark.parametrize("dtype", [F32, I32, U32, F16])
+@pytest.mark.parametrize("dtype", [F32, I32, U32, F16, F64])
 def test_sort_and_argsort_match_oracle(backend, shape, dtype):
     rng = np.random.default_rng(shape[1] + int(dtype))
-    if dtype in (F32, F16):
+    if dtype in (F32, F16, F64):   # float64 sorts on 64-bit keys (rows beyond 16384 / 8192 items take the multi-pass path)
         x = rng.standard_normal(shape).astype(np_dtype(dtype))
         x.flat[::97] = np.nan
         x.flat[1::89] = 0.0
