@@ -62,6 +62,7 @@ struct Plan {
   // tensor-core GEMM launch parameters (SK_GEMM_TC), filled by gemm_tc.cpp
   int tc_kind = 0;            // 1 f16, 2 3xTF32
   int tc_bm = 0, tc_bn = 0, tc_bk = 0, tc_stages = 0;
+  size_t tc_sk_offset = 0, tc_sk_counter_bytes = 0;  // stream-K arrival counters inside the scratch (cleared per launch)
 };
 
 struct Options {
@@ -71,6 +72,9 @@ struct Options {
   int gemm_min_dim = 32;      // below this M or N a GEMM-shaped kernel stays on the reduce skeletons
   bool allow_tc = true;       // tcgen05 path allowed (JAXCUDA_NO_TC=1 clears it)
   int tc_bn = 0;              // force the tensor-core tile width (64, 128, 192, 256); 0 = planner's choice (JAXCUDA_TC_BN)
+  int tc_streamk = 1;         // 0: whole tiles only; 1: left-over tiles are shared out by k-blocks where that pays; 2: whenever tiles are left over (JAXCUDA_TC_STREAMK)
+  int tc_spin_limit = 20000000;  // polls of a tensor-core pipeline wait before it gives up (JAXCUDA_TC_SPIN_LIMIT)
+  int tc_fault = 0;           // tests of the wind-down only: 1 = one CTA's producer announces a stage and never loads it (JAXCUDA_TC_FAULT)
   int force_skeleton = -1;    // tests: force SK_REDUCE_ROW / SK_REDUCE_COL / SK_GEMM_FFMA
   int exact_math = -1;        // 1: bit-faithful exp everywhere, 0: fast everywhere, -1: exact below exact_math_work
   double exact_math_work = 1 << 20;  // element evaluations (size x K) under which a kernel is latency-bound anyway

@@ -34,7 +34,8 @@ namespace {
 const char* const kTcSource = R"TCGEMM(
 struct __align__(64) CUtensorMap { unsigned long long opaque[16]; };
 
-#define SPIN_LIMIT 20000000
+// SPIN_LIMIT (polls of a pipeline wait before it gives up, about a second at the default) and
+// FAULT_SKIP_LOAD (tests of the wind-down only) are defined by the planner.
 
 __device__ __forceinline__ u32 smem_u32(const void* p) { return (u32)__cvta_generic_to_shared(p); }
 
@@ -137,12 +138,49 @@ __device__ __forceinline__ void tile_coords(int t, int& b, int& m_blk, int& n_bl
   n_blk = in / gsz;
 }
 
+// Work of one CTA, in order: whole tiles t = blockIdx.x, + gridDim.x, ... while full waves last, then
+// (STREAMK) an even share of the k-blocks of the tiles that are left over, which is at most the tail
+// of one tile and the head of the next.  A piece of a tile goes to scratch and the CTA that
+// delivers a tile's last piece adds the pieces up in k order and runs the epilogue, so the last,
+// partly filled wave costs its share of a wave instead of a whole one (and an output with fewer
+// tiles than SMs still uses every SM).
+struct Seg { int tile, kb0, kb1, partial, slot; };
+__device__ __forceinline__ int sk_tiles_full() { return STREAMK ? (NUM_TILES / (int)gridDim.x) * (int)gridDim.x : NUM_TILES; }
+__device__ __forceinline__ i64 sk_first_unit(int c) { return (i64)(NUM_TILES - sk_tiles_full()) * K_BLOCKS * c / (int)gridDim.x; }
+__device__ __forceinline__ bool get_segment(int i, Seg& s) {
+  const int P = gridDim.x, c = blockIdx.x;
+  const int tiles_full = sk_tiles_full();
+  const int n_static = tiles_full > c ? (tiles_full - c + P - 1) / P : 0;
+  if (i < n_static) { s.tile = c + i * P; s.kb0 = 0; s.kb1 = K_BLOCKS; s.partial = 0; s.slot = 0; return true; }
+  if (!STREAMK || tiles_full == NUM_TILES) return false;
+  const i64 u0 = sk_first_unit(c), u1 = sk_first_unit(c + 1);
+  i64 b0 = (u0 / K_BLOCKS + 1) * K_BLOCKS;
+  if (b0 > u1) b0 = u1;
+  const int j = i - n_static;
+  if (j == 0) {
+    if (u0 >= u1) return false;
+    s.tile = tiles_full + (int)(u0 / K_BLOCKS); s.kb0 = (int)(u0 % K_BLOCKS); s.kb1 = s.kb0 + (int)(b0 - u0);
+  } else if (j == 1) {
+    if (b0 >= u1) return false;
+    s.tile = tiles_full + (int)(b0 / K_BLOCKS); s.kb0 = 0; s.kb1 = (int)(u1 - b0);
+  } else {
+    return false;
+  }
+  s.partial = !(s.kb0 == 0 && s.kb1 == K_BLOCKS);
+  s.slot = c * 2 + j;
+  return true;
+}
+
 extern "C" __global__ void __launch_bounds__(192, 1)
 jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA2,
         const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmB2,
         JX_PARAMS, int* status_ptr) {
   extern __shared__ unsigned char smem_raw[];
   volatile int* status = status_ptr;
+  // stream-K pieces and arrival counters live at SK_OFFSET of the scratch (counters first)
+  int* sk_counters = reinterpret_cast<int*>(reinterpret_cast<char*>(scratch) + SK_OFFSET);
+  float* sk_pieces = reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + SK_OFFSET + SK_COUNTER_BYTES);
+  (void)sk_counters; (void)sk_pieces;
   const u32 smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;     // swizzle atoms are 1024-byte aligned
   const u32 bars = smem_base + STAGES * STAGE_BYTES;                // full[STAGES], empty[STAGES], tfull[2], tempty[2]
   const u32 tmem_slot = bars + (2 * STAGES + 4) * 8;
@@ -173,13 +211,19 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
       int it = 0;
-      for (int t = blockIdx.x; t < NUM_TILES && !failed; t += gridDim.x) {
+      Seg sg;
+      for (int si = 0; !failed && get_segment(si, sg); si++) {
         int b, m_blk, n_blk;
-        tile_coords(t, b, m_blk, n_blk);
-        for (int kb = 0; kb < K_BLOCKS; kb++, it++) {
+        tile_coords(sg.tile, b, m_blk, n_blk);
+        for (int kb = sg.kb0; kb < sg.kb1; kb++, it++) {
           const int s = it % STAGES;
           if (it >= STAGES && !mbar_wait(empty(s), ((it / STAGES) + 1) & 1, status)) { atomicCAS((int*)status_ptr, 0, 1); failed = true; break; }
           mbar_expect_tx(full(s), STAGE_BYTES);
+#if FAULT_SKIP_LOAD
+          // test of the wind-down: CTA 0 announces its second stage and never loads it, so the MMA
+          // role's bounded wait on that stage runs out
+          if (blockIdx.x == 0 && it == 1) continue;
+#endif
           const u32 sa = smem_base + s * STAGE_BYTES, sb = sa + NPLANES * A_BYTES;
           const int k0 = kb * BK;
           const int ba = A_SHARED ? 0 : b, bb = B_SHARED ? 0 : b;   // an operand all batches share has one plane
@@ -212,21 +256,24 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
     // length of the chain; short chains joined by round-to-nearest f32 adds keep f32 accuracy.
     if (lane == 0) {
       int it = 0, cc = 0;
-      for (int t = blockIdx.x; t < NUM_TILES && !failed; t += gridDim.x) {
-        for (int ch = 0; ch < NCHUNK && !failed; ch++, cc++) {
+      Seg sg;
+      for (int si = 0; !failed && get_segment(si, sg); si++) {
+        const int nch = (sg.kb1 - sg.kb0 + CHUNK_KB - 1) / CHUNK_KB;
+        for (int ch = 0; ch < nch && !failed; ch++, cc++) {
           const int acc = cc & 1;
           if (cc >= 2 && !mbar_wait(tempty(acc), ((cc >> 1) + 1) & 1, status)) { atomicCAS((int*)status_ptr, 0, 2); failed = true; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const u32 d = tmem_base + acc * ACC_STRIDE;
-          const int kb_end = (ch + 1) * CHUNK_KB < K_BLOCKS ? (ch + 1) * CHUNK_KB : K_BLOCKS;
-          for (int kb = ch * CHUNK_KB; kb < kb_end; kb++, it++) {
+          const int kb_first = sg.kb0 + ch * CHUNK_KB;
+          const int kb_end = kb_first + CHUNK_KB < sg.kb1 ? kb_first + CHUNK_KB : sg.kb1;
+          for (int kb = kb_first; kb < kb_end; kb++, it++) {
             const int s = it % STAGES;
             if (!mbar_wait(full(s), (it / STAGES) & 1, status)) { atomicCAS((int*)status_ptr, 0, 3); failed = true; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const u32 sa = smem_base + s * STAGE_BYTES, sb = sa + NPLANES * A_BYTES;
             #pragma unroll
             for (int kk = 0; kk < 4; kk++) {
-              const u32 first = (kb != ch * CHUNK_KB || kk) ? 1u : 0u;
+              const u32 first = (kb != kb_first || kk) ? 1u : 0u;
 #if KIND == 1
               umma(d, operand_desc(sa, kk, A_MN), operand_desc(sb, kk, B_MN), IDESC, first);
 #else
@@ -246,15 +293,44 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
     // ---------------------------------------------------------------- epilogue warps 2..5
     const int q = warp & 3;                 // TMEM lane quarter this warp may access
     int cc = 0;
-    for (int t = blockIdx.x; t < NUM_TILES && !failed; t += gridDim.x) {
+    Seg sg;
+    for (int si = 0; !failed && get_segment(si, sg); si++) {
       int b, m_blk, n_blk;
-      tile_coords(t, b, m_blk, n_blk);
+      tile_coords(sg.tile, b, m_blk, n_blk);
       const int m = m_blk * BM + q * 32 + lane;
+      // epilogue and store of 16 consecutive outputs of this thread's row, from their accumulators
+      auto finish16 = [&](int c, const float* accv) {
+        const int n0 = n_blk * BN + c * 16;
+        if (m < GM && n0 < GN) {
+          __align__(16) JX_OUT_T res[16];
+          const int g0 = (int)(((i64)b * GM + m) * GN + n0);
+          (void)g0;
+          JX_EPI_PRELOAD
+          #pragma unroll
+          for (int j = 0; j < 16; j++) {
+            const int n = n0 + j;
+            const int gidx = (int)(((i64)b * GM + m) * GN + (n < GN ? n : GN - 1));
+            const float acc = accv[j];
+#define JX_DST res[j]
+JX_EPILOGUE
+#undef JX_DST
+          }
+          JX_OUT_T* dst = out + (((i64)b * GM + m) * GN + n0);
+          if (n0 + 16 <= GN && (GN * sizeof(JX_OUT_T)) % 16 == 0) {
+            #pragma unroll
+            for (int j = 0; j < 16; j += 16 / sizeof(JX_OUT_T))
+              *reinterpret_cast<jx_vec<16>*>(dst + j) = *reinterpret_cast<const jx_vec<16>*>(&res[j]);
+          } else {
+            for (int j = 0; j < 16 && n0 + j < GN; j++) dst[j] = res[j];
+          }
+        }
+      };
+      const int nch = (sg.kb1 - sg.kb0 + CHUNK_KB - 1) / CHUNK_KB;
 #if NCHUNK > 1
       float sum[BN];
       #pragma unroll
       for (int j = 0; j < BN; j++) sum[j] = 0.0f;
-      for (int ch = 0; ch < NCHUNK - 1 && !failed; ch++, cc++) {
+      for (int ch = 0; ch < nch - 1 && !failed; ch++, cc++) {
         const int acc_i = cc & 1;
         if (!mbar_wait(tfull(acc_i), (cc >> 1) & 1, status)) { atomicCAS((int*)status_ptr, 0, 4); failed = true; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -277,6 +353,7 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
       if (!mbar_wait(tfull(acc_i), (cc >> 1) & 1, status)) { atomicCAS((int*)status_ptr, 0, 4); failed = true; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const u32 trow = tmem_base + ((u32)(q * 32) << 16) + acc_i * ACC_STRIDE;
+      float* piece = sk_pieces + ((size_t)sg.slot * BM + q * 32 + lane) * BN;   // this row of this CTA's piece
 #if NCHUNK > 1
       #pragma unroll
 #else
@@ -286,38 +363,73 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
         u32 v[16];
         tmem_ld16(trow + c * 16, v);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        const int n0 = n_blk * BN + c * 16;
-        if (m < GM && n0 < GN) {
-          __align__(16) JX_OUT_T res[16];
-          const int g0 = (int)(((i64)b * GM + m) * GN + n0);
-          JX_EPI_PRELOAD
-          #pragma unroll
-          for (int j = 0; j < 16; j++) {
-            const int n = n0 + j;
-            const int gidx = (int)(((i64)b * GM + m) * GN + (n < GN ? n : GN - 1));
+        float accv[16];
+        #pragma unroll
+        for (int j = 0; j < 16; j++) {
 #if NCHUNK > 1
-            const float acc = sum[c * 16 + j] + __uint_as_float(v[j]);
+          accv[j] = sum[c * 16 + j] + __uint_as_float(v[j]);
 #else
-            const float acc = __uint_as_float(v[j]);
+          accv[j] = __uint_as_float(v[j]);
 #endif
-#define JX_DST res[j]
-JX_EPILOGUE
-#undef JX_DST
-          }
-          JX_OUT_T* dst = out + (((i64)b * GM + m) * GN + n0);
-          if (n0 + 16 <= GN && (GN * sizeof(JX_OUT_T)) % 16 == 0) {
-            #pragma unroll
-            for (int j = 0; j < 16; j += 16 / sizeof(JX_OUT_T))
-              *reinterpret_cast<jx_vec<16>*>(dst + j) = *reinterpret_cast<const jx_vec<16>*>(&res[j]);
-          } else {
-            for (int j = 0; j < 16 && n0 + j < GN; j++) dst[j] = res[j];
-          }
+        }
+        if (!sg.partial) {
+          finish16(c, accv);
+        } else {
+          #pragma unroll
+          for (int j = 0; j < 16; j += 4)
+            __stcg(reinterpret_cast<float4*>(piece + c * 16 + j), make_float4(accv[j], accv[j + 1], accv[j + 2], accv[j + 3]));
         }
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty(acc_i));
       cc++;
+#if STREAMK
+      if (sg.partial) {
+        // Which CTAs hold pieces of this tile, in k order: those whose share of the left-over
+        // k-blocks overlaps the tile's.  Every quarter of the tile (32 rows, one epilogue warp in
+        // each of those CTAs) is finished by the warp that arrives last.
+        const int sk_tile = sg.tile - sk_tiles_full();
+        const i64 t0 = (i64)sk_tile * K_BLOCKS, t1 = t0 + K_BLOCKS;
+        const i64 W = (i64)(NUM_TILES - sk_tiles_full()) * K_BLOCKS;
+        int c_first = (int)((t0 * (int)gridDim.x) / W);
+        while (c_first > 0 && sk_first_unit(c_first) > t0) c_first--;
+        while (sk_first_unit(c_first + 1) <= t0) c_first++;
+        int pieces = 0;
+        for (int c2 = c_first; c2 < (int)gridDim.x && sk_first_unit(c2) < t1; c2++)
+          if (sk_first_unit(c2 + 1) > sk_first_unit(c2)) pieces++;
+        __threadfence();
+        __syncwarp();
+        int last = 0;
+        if (lane == 0) last = atomicAdd(sk_counters + sk_tile * 4 + q, 1) == pieces - 1;
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (last) {
+          __threadfence();
+          #pragma unroll 1
+          for (int c = 0; c < BN / 16; c++) {
+            float accv[16];
+            #pragma unroll
+            for (int j = 0; j < 16; j++) accv[j] = 0.0f;
+            bool first_piece = true;
+            for (int c2 = c_first; c2 < (int)gridDim.x && sk_first_unit(c2) < t1; c2++) {
+              const i64 v0 = sk_first_unit(c2), v1 = sk_first_unit(c2 + 1);
+              if (v1 <= v0) continue;
+              const int slot = c2 * 2 + (v0 < t0 ? 1 : 0);     // a share that began in the tile before: its second segment
+              const float* src = sk_pieces + ((size_t)slot * BM + q * 32 + lane) * BN + c * 16;
+              #pragma unroll
+              for (int j = 0; j < 16; j += 4) {
+                const float4 f = __ldcg(reinterpret_cast<const float4*>(src + j));
+                if (first_piece) { accv[j] = f.x; accv[j + 1] = f.y; accv[j + 2] = f.z; accv[j + 3] = f.w; }
+                else { accv[j] += f.x; accv[j + 1] += f.y; accv[j + 2] += f.z; accv[j + 3] += f.w; }
+              }
+              first_piece = false;
+            }
+            finish16(c, accv);
+          }
+          if (lane == 0) sk_counters[sk_tile * 4 + q] = 0;   // ready for the next launch
+        }
+      }
+#endif
     }
   }
   if (*status != 0) {
@@ -407,6 +519,25 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
   // shared memory more often per flop, and the MMA pipe is already fed at its limit with 256 columns.
   // The width stays selectable (Options::tc_bn) for experiments.
   if (opt.tc_bn == 64 || opt.tc_bn == 128 || (kind == 1 && (opt.tc_bn == 192 || opt.tc_bn == 256))) BN = std::min<int>(opt.tc_bn, (int)(g.N / 64 * 64));
+  // Stream-K (see get_segment in the kernel): worth it when the last wave of whole tiles would be
+  // mostly empty.  With it, wider tiles can be afforded where the output has few tiles, as long as
+  // every CTA still gets a few k-blocks.
+  const int64_t kb_total = (g.K + bk - 1) / bk;
+  auto tiles_for = [&](int bn) { return ((g.M + BM - 1) / BM) * ((g.N + bn - 1) / bn) * g.batch; };
+  bool streamk = opt.tc_streamk != 0;
+  if (streamk && opt.tc_bn == 0) {
+    for (int cand : {256, 128, 64}) {
+      if (kind == 2 && cand == 256) continue;
+      if (cand > g.N) continue;
+      if (tiles_for(cand) * kb_total >= (int64_t)opt.sm_count * 8 || cand == 64) { BN = std::max(BN, cand); break; }
+    }
+  }
+  {
+    const int64_t tiles = tiles_for(BN), rest = tiles % opt.sm_count;
+    // no left-over tiles, or a last wave that is nearly full anyway: the static schedule is as good
+    if (rest == 0 || rest * 10 >= (int64_t)opt.sm_count * 9 || kb_total < 2) streamk = false;
+    if (opt.tc_streamk == 2 && rest != 0) streamk = true;   // forced (tests)
+  }
   const int planes = kind == 2 ? 2 : 1;
   const int stage_bytes = planes * (BM + BN) * 128;
   int stages = (227 * 1024 - 2048) / stage_bytes;
@@ -418,6 +549,8 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
   os << "#define KIND " << kind << "\n#define ELEM " << e << "\n#define BM " << BM << "\n#define BN " << BN << "\n";
   os << "#define ACC_STRIDE " << (BN > 128 ? 256 : BN) << "\n";
   os << "#define A_SHARED " << ((g.batch > 1 && g.sAb == 0) ? 1 : 0) << "\n#define B_SHARED " << ((g.batch > 1 && g.sBb == 0) ? 1 : 0) << "\n";
+  os << "#define STREAMK " << (streamk ? 1 : 0) << "\n";
+  os << "#define SPIN_LIMIT " << std::max(1024, opt.tc_spin_limit) << "\n#define FAULT_SKIP_LOAD " << (opt.tc_fault == 1 ? 1 : 0) << "\n";
   os << "#define STAGES " << stages << "\n#define A_MN " << (a_mn ? 1 : 0) << "\n#define B_MN " << (b_mn ? 1 : 0) << "\n";
   os << "#define GM " << g.M << "\n#define GN " << g.N << "\n#define GK " << g.K << "\n#define GBATCH " << g.batch << "\n";
   // k-blocks accumulated in tensor memory before the partial sum is folded into registers with a
@@ -427,6 +560,14 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
   // a gathered B operand arrives with its remainder plane already written: only A is split
   os << "#define LEN_A " << g.lenA << "LL\n#define LEN_B " << (g.b_gathered ? 0 : g.lenB) << "LL\n";
   os << "#define LEN_A_PAD " << pad64(g.lenA) << "LL\n#define LEN_B_PAD " << pad64(g.lenB) << "LL\n";
+  // scratch: [gathered B and its remainder plane][remainder planes of the operands][stream-K counters][stream-K pieces]
+  size_t sk_offset = 0;
+  if (g.b_gathered) sk_offset += (size_t)pad64(g.lenB) * e * planes;
+  if (kind == 2) sk_offset += (size_t)(pad64(g.lenA) + (g.b_gathered ? 0 : pad64(g.lenB))) * 4;
+  sk_offset = (sk_offset + 255) / 256 * 256;
+  const size_t sk_counter_bytes = 4096;   // 4 counters per left-over tile, fewer than 148 of them
+  const size_t sk_bytes = streamk ? sk_counter_bytes + (size_t)2 * opt.sm_count * BM * BN * 4 : 0;
+  os << "#define SK_OFFSET " << sk_offset << "ULL\n#define SK_COUNTER_BYTES " << sk_counter_bytes << "ULL\n";
   const char* out_t = k.out_dtype() == JAXCUDA_F16 ? "jx_half" : k.out_dtype() == JAXCUDA_F64 ? "double"
                       : k.out_dtype() == JAXCUDA_U32 ? "u32" : k.out_dtype() == JAXCUDA_F32 ? "float" : "int";
   os << "#define JX_OUT_T " << out_t << "\n";
@@ -465,16 +606,20 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
     plan.stages.push_back(sp);
     plan.scratch_bytes += (size_t)(pad64(g.lenA) + (g.b_gathered ? 0 : pad64(g.lenB))) * 4;
   }
+  if (streamk) plan.scratch_bytes = sk_offset + sk_bytes;
+  plan.tc_sk_offset = streamk ? sk_offset : 0;
+  plan.tc_sk_counter_bytes = streamk ? sk_counter_bytes : 0;
   Stage st;
   st.entry = "jx_gemm";
-  st.grid[0] = (unsigned)std::min<int64_t>(tiles, opt.sm_count);
+  st.grid[0] = streamk ? (unsigned)opt.sm_count : (unsigned)std::min<int64_t>(tiles, opt.sm_count);
   st.block[0] = 192;
   st.smem = (unsigned)(stages * stage_bytes + 1024 + (2 * stages + 4) * 8 + 16);
   plan.stages.push_back(st);
   plan.describe = std::string("gemm-tcgen05 ") + (kind == 1 ? "f16" : "3xtf32") + " " + std::to_string(g.batch) + "x" +
                   std::to_string(g.M) + "x" + std::to_string(g.N) + "x" + std::to_string(g.K) + " tile 128x" +
                   std::to_string(BN) + "x" + std::to_string(bk) + " stages=" + std::to_string(stages) + " A:" +
-                  (a_mn ? "MN" : "K") + " B:" + (b_mn ? "MN" : "K") + " ctas=" + std::to_string(st.grid[0]);
+                  (a_mn ? "MN" : "K") + " B:" + (b_mn ? "MN" : "K") + " ctas=" + std::to_string(st.grid[0]) +
+                  (streamk ? " stream-k" : "");
   return true;
 }
 
@@ -556,6 +701,12 @@ int launch_gemm_tc(void* encode_fn, void* launch_fn, const Plan& plan, const std
   args.push_back(&tmA); args.push_back(&tmA2); args.push_back(&tmB); args.push_back(&tmB2);
   for (auto& p : ptrs) args.push_back(&p);
   args.push_back(&status_dev);
+  if (plan.tc_sk_counter_bytes) {   // arrival counters of the stream-K pieces start every launch at zero
+    if (cudaMemsetAsync((char*)scratch + plan.tc_sk_offset, 0, plan.tc_sk_counter_bytes, stream) != cudaSuccess) {
+      err = "clearing the stream-K counters failed";
+      return -1;
+    }
+  }
   const Stage& st = plan.stages.back();
   const unsigned grid = max_ctas > 0 ? std::min<unsigned>(st.grid[0], (unsigned)max_ctas) : st.grid[0];
   CUresult r = launch(fns.back(), grid, 1, 1, st.block[0], 1, 1, st.smem, (CUstream)stream, args.data(), nullptr);

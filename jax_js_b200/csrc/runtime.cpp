@@ -438,6 +438,9 @@ int jaxcuda_create(int device, jaxcuda_ctx** out) {
   ctx->opt.col_unroll = env_int("JAXCUDA_COL_UNROLL", ctx->opt.col_unroll);
   ctx->comm_sms = env_int("JAXCUDA_COMM_SMS", ctx->comm_sms);
   ctx->opt.tc_bn = env_int("JAXCUDA_TC_BN", 0);
+  ctx->opt.tc_streamk = env_int("JAXCUDA_TC_STREAMK", ctx->opt.tc_streamk);
+  ctx->opt.tc_spin_limit = env_int("JAXCUDA_TC_SPIN_LIMIT", ctx->opt.tc_spin_limit);
+  ctx->opt.tc_fault = env_int("JAXCUDA_TC_FAULT", 0);
   ctx->sweep_alternate = env_int("JAXCUDA_SWEEP", 1) != 0;
   ctx->fuse_rows = env_int("JAXCUDA_FUSE", 1) != 0;
   ctx->opt.fuse_chunks = env_int("JAXCUDA_FUSE_CHUNKS", ctx->opt.fuse_chunks);
