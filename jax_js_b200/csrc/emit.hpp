@@ -72,7 +72,7 @@ struct Options {
   int gemm_min_dim = 32;      // below this M or N a GEMM-shaped kernel stays on the reduce skeletons
   bool allow_tc = true;       // tcgen05 path allowed (JAXCUDA_NO_TC=1 clears it)
   int tc_bn = 0;              // force the tensor-core tile width (64, 128, 192, 256); 0 = planner's choice (JAXCUDA_TC_BN)
-  int tc_streamk = 1;         // 0: whole tiles only; 1: left-over tiles are shared out by k-blocks where that pays; 2: whenever tiles are left over (JAXCUDA_TC_STREAMK)
+  int tc_streamk = 1;         // 0: whole tiles only; 1: an output with at most half as many tiles as SMs and a long K is cut along K; 2: so is any last wave that is at most half full (JAXCUDA_TC_STREAMK)
   int tc_spin_limit = 20000000;  // polls of a tensor-core pipeline wait before it gives up (JAXCUDA_TC_SPIN_LIMIT)
   int tc_fault = 0;           // tests of the wind-down only: 1 = one CTA's producer announces a stage and never loads it (JAXCUDA_TC_FAULT)
   int force_skeleton = -1;    // tests: force SK_REDUCE_ROW / SK_REDUCE_COL / SK_GEMM_FFMA

@@ -138,36 +138,39 @@ __device__ __forceinline__ void tile_coords(int t, int& b, int& m_blk, int& n_bl
   n_blk = in / gsz;
 }
 
-// Work of one CTA, in order: whole tiles t = blockIdx.x, + gridDim.x, ... while full waves last, then
-// (STREAMK) an even share of the k-blocks of the tiles that are left over, which is at most the tail
-// of one tile and the head of the next.  A piece of a tile goes to scratch and the CTA that
-// delivers a tile's last piece adds the pieces up in k order and runs the epilogue, so the last,
-// partly filled wave costs its share of a wave instead of a whole one (and an output with fewer
-// tiles than SMs still uses every SM).
+// Work of one CTA, in order: whole tiles t = blockIdx.x, + gridDim.x, ... while full waves last.  The
+// R < gridDim.x tiles that are left over would occupy R CTAs for a whole tile's time; with SPLITK
+// each of them is cut along K into S = gridDim.x / R slices (at most 8) that run side by side, so the
+// last wave takes 1 / S of a tile's time (and an output with fewer tiles than SMs uses S times as
+// many of them).  CTA c takes slice c / R of left-over tile c % R: CTAs that run at the same time
+// work at the same depth of K in different tiles and so still share operand panels through L2.
+// (Sharing the left-over k-blocks out evenly instead, each CTA continuing where its neighbour
+// stops, was measured 20 to 40 % slower than no split at all: neighbours then read different
+// k-ranges of the same panels and every operand byte comes from DRAM.)  A slice's accumulators go to
+// scratch; the CTA that delivers a tile's last slice adds them up in k order and runs the epilogue.
 struct Seg { int tile, kb0, kb1, partial, slot; };
 __device__ __forceinline__ int sk_tiles_full() { return STREAMK ? (NUM_TILES / (int)gridDim.x) * (int)gridDim.x : NUM_TILES; }
-__device__ __forceinline__ i64 sk_first_unit(int c) { return (i64)(NUM_TILES - sk_tiles_full()) * K_BLOCKS * c / (int)gridDim.x; }
+__device__ __forceinline__ int sk_slices() {
+  const int rest = NUM_TILES - sk_tiles_full();
+  int s = rest > 0 ? (int)gridDim.x / rest : 1;
+  s = s > 8 ? 8 : s;
+  return s > K_BLOCKS ? K_BLOCKS : s;
+}
 __device__ __forceinline__ bool get_segment(int i, Seg& s) {
   const int P = gridDim.x, c = blockIdx.x;
   const int tiles_full = sk_tiles_full();
   const int n_static = tiles_full > c ? (tiles_full - c + P - 1) / P : 0;
   if (i < n_static) { s.tile = c + i * P; s.kb0 = 0; s.kb1 = K_BLOCKS; s.partial = 0; s.slot = 0; return true; }
-  if (!STREAMK || tiles_full == NUM_TILES) return false;
-  const i64 u0 = sk_first_unit(c), u1 = sk_first_unit(c + 1);
-  i64 b0 = (u0 / K_BLOCKS + 1) * K_BLOCKS;
-  if (b0 > u1) b0 = u1;
-  const int j = i - n_static;
-  if (j == 0) {
-    if (u0 >= u1) return false;
-    s.tile = tiles_full + (int)(u0 / K_BLOCKS); s.kb0 = (int)(u0 % K_BLOCKS); s.kb1 = s.kb0 + (int)(b0 - u0);
-  } else if (j == 1) {
-    if (b0 >= u1) return false;
-    s.tile = tiles_full + (int)(b0 / K_BLOCKS); s.kb0 = 0; s.kb1 = (int)(u1 - b0);
-  } else {
-    return false;
-  }
-  s.partial = !(s.kb0 == 0 && s.kb1 == K_BLOCKS);
-  s.slot = c * 2 + j;
+  const int rest = NUM_TILES - tiles_full;
+  if (!STREAMK || rest == 0 || i > n_static) return false;
+  const int S = sk_slices();
+  if (c >= rest * S) return false;
+  const int slice = c / rest;
+  s.tile = tiles_full + c % rest;
+  s.kb0 = (int)((i64)K_BLOCKS * slice / S);
+  s.kb1 = (int)((i64)K_BLOCKS * (slice + 1) / S);
+  s.partial = S > 1;
+  s.slot = c;
   return true;
 }
 
@@ -177,7 +180,7 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
         JX_PARAMS, int* status_ptr) {
   extern __shared__ unsigned char smem_raw[];
   volatile int* status = status_ptr;
-  // stream-K pieces and arrival counters live at SK_OFFSET of the scratch (counters first)
+  // the slices' accumulators and their arrival counters live at SK_OFFSET of the scratch (counters first)
   int* sk_counters = reinterpret_cast<int*>(reinterpret_cast<char*>(scratch) + SK_OFFSET);
   float* sk_pieces = reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + SK_OFFSET + SK_COUNTER_BYTES);
   (void)sk_counters; (void)sk_pieces;
@@ -353,7 +356,8 @@ JX_EPILOGUE
       if (!mbar_wait(tfull(acc_i), (cc >> 1) & 1, status)) { atomicCAS((int*)status_ptr, 0, 4); failed = true; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const u32 trow = tmem_base + ((u32)(q * 32) << 16) + acc_i * ACC_STRIDE;
-      float* piece = sk_pieces + ((size_t)sg.slot * BM + q * 32 + lane) * BN;   // this row of this CTA's piece
+      // a piece is laid out [16-column group][row][16]: a warp's 32 rows of one group are 2 KB in a row
+      float* piece = sk_pieces + (size_t)sg.slot * BM * BN + (size_t)(q * 32 + lane) * 16;
 #if NCHUNK > 1
       #pragma unroll
 #else
@@ -377,7 +381,7 @@ JX_EPILOGUE
         } else {
           #pragma unroll
           for (int j = 0; j < 16; j += 4)
-            __stcg(reinterpret_cast<float4*>(piece + c * 16 + j), make_float4(accv[j], accv[j + 1], accv[j + 2], accv[j + 3]));
+            __stcg(reinterpret_cast<float4*>(piece + (size_t)c * BM * 16 + j), make_float4(accv[j], accv[j + 1], accv[j + 2], accv[j + 3]));
         }
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -386,43 +390,39 @@ JX_EPILOGUE
       cc++;
 #if STREAMK
       if (sg.partial) {
-        // Which CTAs hold pieces of this tile, in k order: those whose share of the left-over
-        // k-blocks overlaps the tile's.  Every quarter of the tile (32 rows, one epilogue warp in
-        // each of those CTAs) is finished by the warp that arrives last.
+        // Every quarter of the tile (32 rows: one epilogue warp in each of the S CTAs that hold a
+        // slice) is finished by the warp that arrives last.
+        const int rest = NUM_TILES - sk_tiles_full(), S = sk_slices();
         const int sk_tile = sg.tile - sk_tiles_full();
-        const i64 t0 = (i64)sk_tile * K_BLOCKS, t1 = t0 + K_BLOCKS;
-        const i64 W = (i64)(NUM_TILES - sk_tiles_full()) * K_BLOCKS;
-        int c_first = (int)((t0 * (int)gridDim.x) / W);
-        while (c_first > 0 && sk_first_unit(c_first) > t0) c_first--;
-        while (sk_first_unit(c_first + 1) <= t0) c_first++;
-        int pieces = 0;
-        for (int c2 = c_first; c2 < (int)gridDim.x && sk_first_unit(c2) < t1; c2++)
-          if (sk_first_unit(c2 + 1) > sk_first_unit(c2)) pieces++;
         __threadfence();
         __syncwarp();
         int last = 0;
-        if (lane == 0) last = atomicAdd(sk_counters + sk_tile * 4 + q, 1) == pieces - 1;
+        if (lane == 0) last = atomicAdd(sk_counters + sk_tile * 4 + q, 1) == S - 1;
         last = __shfl_sync(0xffffffffu, last, 0);
         if (last) {
           __threadfence();
           #pragma unroll 1
           for (int c = 0; c < BN / 16; c++) {
             float accv[16];
+            const size_t at = (size_t)c * BM * 16 + (size_t)(q * 32 + lane) * 16;
             #pragma unroll
             for (int j = 0; j < 16; j++) accv[j] = 0.0f;
-            bool first_piece = true;
-            for (int c2 = c_first; c2 < (int)gridDim.x && sk_first_unit(c2) < t1; c2++) {
-              const i64 v0 = sk_first_unit(c2), v1 = sk_first_unit(c2 + 1);
-              if (v1 <= v0) continue;
-              const int slot = c2 * 2 + (v0 < t0 ? 1 : 0);     // a share that began in the tile before: its second segment
-              const float* src = sk_pieces + ((size_t)slot * BM + q * 32 + lane) * BN + c * 16;
+            #pragma unroll 1
+            for (int p0 = 0; p0 < S; p0 += 4) {      // four slices' loads in flight at a time, added in k order
+              float4 f[4][4];
               #pragma unroll
-              for (int j = 0; j < 16; j += 4) {
-                const float4 f = __ldcg(reinterpret_cast<const float4*>(src + j));
-                if (first_piece) { accv[j] = f.x; accv[j + 1] = f.y; accv[j + 2] = f.z; accv[j + 3] = f.w; }
-                else { accv[j] += f.x; accv[j + 1] += f.y; accv[j + 2] += f.z; accv[j + 3] += f.w; }
-              }
-              first_piece = false;
+              for (int p = 0; p < 4; p++)
+                if (p0 + p < S) {
+                  const float* src = sk_pieces + (size_t)((p0 + p) * rest + sk_tile) * BM * BN + at;   // slice p is CTA p * rest + sk_tile
+                  #pragma unroll
+                  for (int j = 0; j < 4; j++) f[p][j] = __ldcg(reinterpret_cast<const float4*>(src) + j);
+                }
+              #pragma unroll
+              for (int p = 0; p < 4; p++)
+                if (p0 + p < S) {
+                  #pragma unroll
+                  for (int j = 0; j < 4; j++) { accv[4 * j] += f[p][j].x; accv[4 * j + 1] += f[p][j].y; accv[4 * j + 2] += f[p][j].z; accv[4 * j + 3] += f[p][j].w; }
+                }
             }
             finish16(c, accv);
           }
@@ -519,24 +519,26 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
   // shared memory more often per flop, and the MMA pipe is already fed at its limit with 256 columns.
   // The width stays selectable (Options::tc_bn) for experiments.
   if (opt.tc_bn == 64 || opt.tc_bn == 128 || (kind == 1 && (opt.tc_bn == 192 || opt.tc_bn == 256))) BN = std::min<int>(opt.tc_bn, (int)(g.N / 64 * 64));
-  // Stream-K (see get_segment in the kernel): worth it when the last wave of whole tiles would be
-  // mostly empty.  With it, wider tiles can be afforded where the output has few tiles, as long as
-  // every CTA still gets a few k-blocks.
+  // Split-K (see get_segment in the kernel).  Measured on B200: an output with at most half as many
+  // tiles as SMs and a long K gains (f32 512 x 512 x 4096: 80 -> 44 us); a last wave behind full waves
+  // does not (f16 4096^3: 108 -> 121 us, f32 1024^3 at 128 x 128 tiles: 30 -> 33 us), because the warp
+  // that adds a tile's slices up does so at the very end of the kernel in a chain of dependent L2
+  // reads that costs more than the part of a wave it saves.  So only the first case is split; the
+  // kernel handles both (JAXCUDA_TC_STREAMK=2 splits whenever at most half a wave is left over).
   const int64_t kb_total = (g.K + bk - 1) / bk;
   auto tiles_for = [&](int bn) { return ((g.M + BM - 1) / BM) * ((g.N + bn - 1) / bn) * g.batch; };
   bool streamk = opt.tc_streamk != 0;
-  if (streamk && opt.tc_bn == 0) {
-    for (int cand : {256, 128, 64}) {
+  if (streamk && opt.tc_bn == 0 && kb_total >= 64) {
+    for (int cand : {256, 128}) {   // few tiles anyway: take the widest that still leaves two slices per tile
       if (kind == 2 && cand == 256) continue;
-      if (cand > g.N) continue;
-      if (tiles_for(cand) * kb_total >= (int64_t)opt.sm_count * 8 || cand == 64) { BN = std::max(BN, cand); break; }
+      if (cand > g.N || cand <= BN) continue;
+      if (tiles_for(cand) * 2 <= opt.sm_count) { BN = cand; break; }
     }
   }
   {
     const int64_t tiles = tiles_for(BN), rest = tiles % opt.sm_count;
-    // no left-over tiles, or a last wave that is nearly full anyway: the static schedule is as good
-    if (rest == 0 || rest * 10 >= (int64_t)opt.sm_count * 9 || kb_total < 2) streamk = false;
-    if (opt.tc_streamk == 2 && rest != 0) streamk = true;   // forced (tests)
+    if (rest == 0 || rest * 2 > opt.sm_count || kb_total < 4) streamk = false;
+    if (opt.tc_streamk != 2 && (tiles >= opt.sm_count || kb_total < 64)) streamk = false;
   }
   const int planes = kind == 2 ? 2 : 1;
   const int stage_bytes = planes * (BM + BN) * 128;
@@ -566,7 +568,7 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
   if (kind == 2) sk_offset += (size_t)(pad64(g.lenA) + (g.b_gathered ? 0 : pad64(g.lenB))) * 4;
   sk_offset = (sk_offset + 255) / 256 * 256;
   const size_t sk_counter_bytes = 4096;   // 4 counters per left-over tile, fewer than 148 of them
-  const size_t sk_bytes = streamk ? sk_counter_bytes + (size_t)2 * opt.sm_count * BM * BN * 4 : 0;
+  const size_t sk_bytes = streamk ? sk_counter_bytes + (size_t)opt.sm_count * BM * BN * 4 : 0;   // one slice per CTA
   os << "#define SK_OFFSET " << sk_offset << "ULL\n#define SK_COUNTER_BYTES " << sk_counter_bytes << "ULL\n";
   const char* out_t = k.out_dtype() == JAXCUDA_F16 ? "jx_half" : k.out_dtype() == JAXCUDA_F64 ? "double"
                       : k.out_dtype() == JAXCUDA_U32 ? "u32" : k.out_dtype() == JAXCUDA_F32 ? "float" : "int";
@@ -619,7 +621,7 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
                   std::to_string(g.M) + "x" + std::to_string(g.N) + "x" + std::to_string(g.K) + " tile 128x" +
                   std::to_string(BN) + "x" + std::to_string(bk) + " stages=" + std::to_string(stages) + " A:" +
                   (a_mn ? "MN" : "K") + " B:" + (b_mn ? "MN" : "K") + " ctas=" + std::to_string(st.grid[0]) +
-                  (streamk ? " stream-k" : "");
+                  (streamk ? " split-k" : "");
   return true;
 }
 

@@ -534,8 +534,9 @@ def test_reduction_over_one_element_runs_as_elementwise(backend):
     assert "unit reduction folded" in backend.prepare_kernel(k).describe
     got = run_cuda(backend, k, [a, b, c])
     # elementwise f32: 1e-5 (the product and the sum may be contracted into one fused multiply-add)
-    assert_close(got, oracle.run_kernel(k, [a, b, c]), 1e-5, 1e-3, "K = 1 dot")
-    assert_close(got.reshape(M, N), np.outer(a.astype(np.float64), b) + c.reshape(M, N), 1e-6, 1e-3, "vs float64")
+    scale = np.abs(np.outer(a, b)).reshape(-1) + np.abs(c)      # the sum may cancel: relative to its terms
+    assert_close(got, oracle.run_kernel(k, [a, b, c]), 1e-5, scale, "K = 1 dot")
+    assert_close(got, (np.outer(a.astype(np.float64), b) + c.reshape(M, N)).reshape(-1), 1e-6, scale, "vs float64")
 
 
 def test_skinny_dot_with_few_rows_and_many_columns(backend):
@@ -547,3 +548,21 @@ def test_skinny_dot_with_few_rows_and_many_columns(backend):
     assert backend.prepare_kernel(k).describe.startswith("dot-skinny-t (operands swapped)"), backend.prepare_kernel(k).describe
     got = _gemm_case(backend, k, [A, B], K, 1e-4, F32).reshape(M, N)
     assert_close(got, A.T.astype(np.float64) @ B.astype(np.float64), 1e-5, np.abs(A).max() * np.abs(B).max() * np.sqrt(K), "vs float64")
+
+
+@pytest.mark.parametrize("M,N,K,dt,al,bl", [(512, 512, 4096, F32, "mk", "kn"), (300, 200, 4100, F32, "mk", "nk"), (520, 1000, 6000, F32, "km", "kn"),
+                                            (256, 256, 8192, F16, "mk", "kn"), (130, 700, 5000, F16, "mk", "nk")])
+def test_gemm_with_few_tiles_and_a_long_k_is_split_along_k(backend, M, N, K, dt, al, bl):
+    """Outputs with at most half as many tiles as SMs: the tiles' K ranges are sliced over otherwise idle
+    CTAs, the slices' accumulators added up in k order by whichever CTA finishes a tile last."""
+    rng = np.random.default_rng(M + N)
+    npdt = np.float32 if dt == F32 else np.float16
+    sc = 1.0 if dt == F32 else 0.05
+    A = (rng.standard_normal((M, K) if al == "mk" else (K, M)) * sc).astype(npdt)
+    B = (rng.standard_normal((K, N) if bl == "kn" else (N, K)) * sc).astype(npdt)
+    k = P.dot_kernel(M, N, K, dt, a_layout=al, b_layout=bl, bias=True, relu=True)
+    bias = (rng.standard_normal(N) * sc).astype(npdt)
+    assert backend.prepare_kernel(k).describe.endswith("split-k"), backend.prepare_kernel(k).describe
+    first = run_cuda(backend, k, [A, B, bias])
+    got = _gemm_case(backend, k, [A, B, bias], K, 1e-4 if dt == F32 else 2e-3, dt)
+    assert np.array_equal(first.astype(np.float64), got)          # slices are added in a fixed order: bit-reproducible
