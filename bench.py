@@ -156,6 +156,20 @@ def other_configs(be, peaks, iters=None):
     ms, exe = time_kernel(be, P.dot_kernel(n, n, n, DType.Float16), [a, b], iters=iters or 10, warmup=2)
     tf = 2 * n**3 / ms / 1e9
     out["matmul_f16_4096"] = {"tflops": tf, "frac_tensor_burst": tf / peaks["bf16_tflops"], "ms": ms, "kernel": exe.describe}
+    # a convolution as `jitRules[Conv]` emits it: NCHW 32 x 64 x 56 x 56, 128 filters of 3 x 3, padding 1.
+    # No TF32 peak is measured: the stand-in ceiling for 3xTF32 is the measured bf16 burst / 2 / 3.
+    N, Ci, H, Co = 32, 64, 56, 128
+    x = rng.standard_normal((N, Ci, H, H)).astype(np.float32)
+    w = (rng.standard_normal((Co, Ci, 3, 3)) * 0.05).astype(np.float32)
+    flops = 2.0 * N * Co * H * H * Ci * 9
+    ms, exe = time_kernel(be, P.conv2d_kernel(N, Ci, H, H, Co, 3, 3, 1, 1), [x, w], iters=iters or 10, warmup=2)
+    out["conv2d_f32_32x64x56x56_k3"] = {"tflops": flops / ms / 1e9, "frac_3xtf32_ceiling": flops / ms / 1e9 / (peaks["bf16_tflops"] / 6),
+                                        "ms": ms, "kernel": exe.describe,
+                                        "stages": "patch operand gathered to [batch][576][3136] (+ its 3xTF32 remainder plane), then the tcgen05 GEMM"}
+    x16, w16 = x.astype(np.float16), w.astype(np.float16)
+    ms, exe = time_kernel(be, P.conv2d_kernel(N, Ci, H, H, Co, 3, 3, 1, 1, DType.Float16), [x16, w16], iters=iters or 10, warmup=2)
+    out["conv2d_f16_32x64x56x56_k3"] = {"tflops": flops / ms / 1e9, "frac_tensor_burst": flops / ms / 1e9 / peaks["bf16_tflops"],
+                                        "ms": ms, "kernel": exe.describe}
     return out
 
 
@@ -572,7 +586,7 @@ def _run():
                                      "ms": top["ms"], "algorithmic_bytes": top["bytes"], "traffic": None})
         if world == 1 and not args.skip_extras:
             cfgs = other_configs(be, peaks)
-            line["configs_head"] = {k: {kk: vv for kk, vv in v.items() if kk in ("tflops", "gbs", "ms", "frac_hbm", "frac_tensor_burst")}
+            line["configs_head"] = {k: {kk: vv for kk, vv in v.items() if kk in ("tflops", "gbs", "ms", "frac_hbm", "frac_tensor_burst", "frac_3xtf32_ceiling")}
                                     for k, v in cfgs.items()}
             line["configs"] = cfgs
             line["cpu_baseline"] = cpu_baseline(budget_s=10.0, threads=1)

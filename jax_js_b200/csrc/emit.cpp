@@ -279,10 +279,10 @@ struct Builder {
 
   // Source header: the prelude, with the bit-faithful transcendentals selected for kernels small
   // enough to be latency-bound (and for all kernels when asked).
-  std::string header() const {
+  std::string header(int hint_default = 0) const {
     const double work = (double)k.size * (k.has_red ? (double)k.red_size : 1.0);
     const bool exact = opt.exact_math == 1 || (opt.exact_math < 0 && work < opt.exact_math_work);
-    return std::string(exact ? "#define JX_EXACT_TRANSCENDENTALS 1\n" : "") + "#define JX_LD_HINT " + S(opt.ld_hint) + "\n" + kPrelude;
+    return std::string(exact ? "#define JX_EXACT_TRANSCENDENTALS 1\n" : "") + "#define JX_LD_HINT " + S(opt.ld_hint >= 0 ? opt.ld_hint : hint_default) + "\n" + kPrelude;
   }
 
   Analysis an_exp, an_epi;
@@ -583,9 +583,6 @@ struct Builder {
     // (and their loads) in flight per SM while the special-function unit is busy.
     bool heavy = false;
     for (const Node& nd : k.exp) heavy = heavy || (nd.op >= JAXCUDA_OP_SIN && nd.op <= JAXCUDA_OP_ERFC);
-    int TPR = K >= 1024 ? (heavy ? 128 : 256) : K >= 128 ? 32 : 8;
-    if (opt.row_tpr == 8 || opt.row_tpr == 32 || opt.row_tpr == 64 || opt.row_tpr == 128 || opt.row_tpr == 256)
-      TPR = opt.row_tpr;
     // vector width over ridx
     int V = 1;
     for (int cand : {8, 4, 2}) {
@@ -593,6 +590,11 @@ struct Builder {
       int eb = min_load_bytes(1, cand);
       if (eb && eb * cand <= 16) { V = cand; break; }
     }
+    // Rows of at least 1024 elements: 256 threads per row once every thread still has four 128-bit
+    // loads of its own, else 128 (f16 matvec over 4096 columns: 0.81 of the copy rate against 0.75).
+    int TPR = K >= 1024 ? (heavy || K < 256 * 4 * V ? 128 : 256) : K >= 128 ? 32 : 8;
+    if (opt.row_tpr == 8 || opt.row_tpr == 32 || opt.row_tpr == 64 || opt.row_tpr == 128 || opt.row_tpr == 256)
+      TPR = opt.row_tpr;
     const int RPC = T / TPR;
     int64_t row_blocks = ((int64_t)k.size + RPC - 1) / RPC;
     // few outputs and a long axis: split ridx across CTAs, finish in a second pass
@@ -718,12 +720,35 @@ struct Builder {
     rchunk = (rchunk + TY - 1) / TY * TY;
     splits = (int)((K + rchunk - 1) / std::max<int64_t>(1, rchunk));
     if (K == 0) { splits = 1; rchunk = 0; }
+    if (splits > 1) {
+      // All CTAs of such a grid are resident at once, so the kernel lasts as long as the SM with the
+      // most CTAs: 602 CTAs on 148 SMs leave some SMs five chunks and most of them four.  Among the
+      // split counts near the wanted one take that with the smallest (CTAs on the fullest SM) x
+      // (rows per chunk), at most six CTAs per SM.
+      int64_t best_cost = 0;
+      int best_s = splits;
+      for (int s = std::max(2, splits * 2 / 3); s <= splits * 3 / 2 + 1; s++) {
+        int64_t rc = ((K + s - 1) / s + TY - 1) / TY * TY;
+        int64_t se = (K + rc - 1) / rc;
+        int64_t per_sm = (gblocks * se + opt.sm_count - 1) / opt.sm_count;
+        if (per_sm > 6 || rc < (int64_t)TY * opt.col_unroll) continue;
+        int64_t cost = per_sm * rc;
+        if (!best_cost || cost < best_cost || (cost == best_cost && std::abs(s - splits) < std::abs(best_s - splits))) {
+          best_cost = cost;
+          best_s = s;
+        }
+      }
+      if (best_cost) {
+        rchunk = ((K + best_s - 1) / best_s + TY - 1) / TY * TY;
+        splits = (int)((K + rchunk - 1) / rchunk);
+      }
+    }
     const char* AT = ctype(k.red_dtype);
     const size_t root = k.exp.size() - 1;
     std::vector<char> all(k.exp.size(), 1);
 
     std::ostringstream os;
-    os << header();
+    os << header(1);  // streamed once, column by column: the no-allocate hint measured 3 % faster here, slower in the row skeleton
     os << "extern \"C\" __global__ void __launch_bounds__(" << T << ") jx_reduce_col(" << params() << ") {\n";
     os << "  const int tx = threadIdx.x % " << TX << ", ty = threadIdx.x / " << TX << ";\n";
     os << "  const int gv = blockIdx.x * " << TX << " + tx;\n  const bool active = gv < " << nvec << ";\n";
@@ -1629,7 +1654,7 @@ bool plan_row_fusion(const std::vector<FuseStage>& stages, const std::vector<Fus
   const double work = (double)R * (double)C;
   const bool exact = opt.exact_math == 1 || (opt.exact_math < 0 && work < opt.exact_math_work);
   std::ostringstream os;
-  os << (exact ? "#define JX_EXACT_TRANSCENDENTALS 1\n" : "") << "#define JX_LD_HINT " << opt.ld_hint << "\n" << kPrelude;
+  os << (exact ? "#define JX_EXACT_TRANSCENDENTALS 1\n" : "") << "#define JX_LD_HINT " << std::max(0, opt.ld_hint) << "\n" << kPrelude;
   os << "extern \"C\" __global__ void __launch_bounds__(" << T;
   // 1536 resident threads per SM hold the allocation at 42 registers: measured best for 4096-column rows (44 us against 47 at 1024)
   const int min_ctas = opt.fuse_min_ctas > 0 ? std::min(opt.fuse_min_ctas, 2048 / T) : opt.fuse_min_ctas < 0 ? 0 : std::max(1, 1536 / T);

@@ -78,7 +78,7 @@ struct Options {
   int force_skeleton = -1;    // tests: force SK_REDUCE_ROW / SK_REDUCE_COL / SK_GEMM_FFMA
   int exact_math = -1;        // 1: bit-faithful exp everywhere, 0: fast everywhere, -1: exact below exact_math_work
   double exact_math_work = 1 << 20;  // element evaluations (size x K) under which a kernel is latency-bound anyway
-  int ld_hint = 0;            // 1: 128-bit loads use ld.global.nc.L1::no_allocate.L2::256B
+  int ld_hint = -1;           // 1: 128-bit loads use ld.global.nc.L1::no_allocate.L2::256B; 0: plain loads; -1: per skeleton (column reduce only)
   int row_tpr = 0;            // threads per output row in the row-reduce skeleton (0: chosen from K)
   int row_unroll = 0;         // vector loads in flight per thread in the row-reduce loop (0: trip count, at most 4)
   int col_threads = 128;      // CTA size of the column-reduce skeleton

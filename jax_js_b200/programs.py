@@ -124,6 +124,29 @@ def matvec_kernel(rows: int, cols: int, dtype: DType = F16, *, orientation: str 
     return Kernel(2, rows, AluExp.mul(w, x), Reduction(dtype, AluOp.Add, cols))
 
 
+def conv2d_kernel(N: int, Ci: int, H: int, W: int, Co: int, KH: int, KW: int, stride: int = 1, pad: int = 0,
+                  dtype: DType = F32) -> Kernel:
+    """out[n, co, oh, ow] = sum_{ci, kh, kw} x[n, ci, oh*stride + kh - pad, ow*stride + kw - pad] * w[co, ci, kh, kw]
+    over NCHW input and OIHW weights, the padded taps read as Where(valid, load, 0): the Kernel
+    `jitRules[Conv]` builds from the pooled views of `prepareConv` (src/frontend/jit.ts:649-660,
+    src/frontend/convolution.ts)."""
+    OH, OW = (H + 2 * pad - KH) // stride + 1, (W + 2 * pad - KW) // stride + 1
+    i = _i
+    ow, oh = AluExp.mod(_g, i(OW)), AluExp.mod(AluExp.idiv(_g, i(OW)), i(OH))
+    co, n = AluExp.mod(AluExp.idiv(_g, i(OW * OH)), i(Co)), AluExp.idiv(_g, i(OW * OH * Co))
+    kw, kh, ci = AluExp.mod(_r, i(KW)), AluExp.mod(AluExp.idiv(_r, i(KW)), i(KH)), AluExp.idiv(_r, i(KW * KH))
+    ih = AluExp.add(AluExp.add(AluExp.mul(oh, i(stride)), kh), i(-pad))
+    iw = AluExp.add(AluExp.add(AluExp.mul(ow, i(stride)), kw), i(-pad))
+
+    def inside(v, hi):
+        return AluExp.mul(AluExp.cast(I32, AluExp.cmplt(i(-1), v)), AluExp.cast(I32, AluExp.cmplt(v, i(hi))))
+    valid = AluExp.cmpne(AluExp.mul(inside(ih, H), inside(iw, W)), i(0))
+    xi = AluExp.add(AluExp.mul(AluExp.add(AluExp.mul(AluExp.add(AluExp.mul(n, i(Ci)), ci), i(H)), ih), i(W)), iw)
+    x = AluExp.where(valid, AluExp.global_index(dtype, 0, N * Ci * H * W, xi), AluExp.const(dtype, 0))
+    wv = AluExp.global_index(dtype, 1, Co * Ci * KH * KW, AluExp.add(AluExp.mul(co, i(Ci * KH * KW)), _r))
+    return Kernel(2, N * Co * OH * OW, AluExp.mul(x, wv), Reduction(dtype, AluOp.Add, Ci * KH * KW))
+
+
 # ---- step lists ---------------------------------------------------------------------------
 
 @dataclass

@@ -76,7 +76,7 @@ CASES = {
     "k3' tiny": (P.lse_finish_kernel(8192), "elementwise"),
     "k5 argmax": (P.argmax_index_kernel(8192, 4096), "reduce-row TPR=256 V=4"),
     "matvec xW": (P.matvec_kernel(4096, 11008, F16, orientation="xW"), "reduce-col V=8"),
-    "matvec Wx": (P.matvec_kernel(11008, 4096, F16, orientation="Wx"), "reduce-row TPR=256 V=8"),
+    "matvec Wx": (P.matvec_kernel(11008, 4096, F16, orientation="Wx"), "reduce-row TPR=128 V=8"),
     "dot f32": (P.dot_kernel(1024, 1024, 1024), "gemm"),
     "dot f16": (P.dot_kernel(4096, 4096, 4096, F16), "gemm"),
     "dot TN": (P.dot_kernel(784, 2048, 8192, a_layout="km"), "gemm"),

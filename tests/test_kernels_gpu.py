@@ -300,22 +300,8 @@ def test_matvec_f16(backend, K, Nout, orientation):
 # ---- convolution and pooling: Dot / Reduce over pooled views (src/frontend/jit.ts:620-660) --------------
 
 def _conv_kernel(N, Ci, H, W, Co, KH, KW, stride, pad, dt=F32):
-    """out[n, co, oh, ow] = sum_{ci, kh, kw} x[n, ci, oh*stride + kh - pad, ow*stride + kw - pad] * w[co, ci, kh, kw], the padded
-    taps read as Where(valid, load, 0): the Kernel `jitRules[Conv]` builds from `prepareConv`'s views."""
     OH, OW = (H + 2 * pad - KH) // stride + 1, (W + 2 * pad - KW) // stride + 1
-    i = AluExp.i32
-    ow, oh = AluExp.mod(g, i(OW)), AluExp.mod(AluExp.idiv(g, i(OW)), i(OH))
-    co, n = AluExp.mod(AluExp.idiv(g, i(OW * OH)), i(Co)), AluExp.idiv(g, i(OW * OH * Co))
-    kw, kh, ci = AluExp.mod(r, i(KW)), AluExp.mod(AluExp.idiv(r, i(KW)), i(KH)), AluExp.idiv(r, i(KW * KH))
-    ih = AluExp.add(AluExp.add(AluExp.mul(oh, i(stride)), kh), i(-pad))
-    iw = AluExp.add(AluExp.add(AluExp.mul(ow, i(stride)), kw), i(-pad))
-    inside = lambda v, hi: AluExp.mul(AluExp.cast(I32, AluExp.cmplt(i(-1), v)), AluExp.cast(I32, AluExp.cmplt(v, i(hi))))
-    valid = AluExp.cmpne(AluExp.mul(inside(ih, H), inside(iw, W)), i(0))
-    xi = AluExp.add(AluExp.mul(AluExp.add(AluExp.mul(AluExp.add(AluExp.mul(n, i(Ci)), ci), i(H)), ih), i(W)), iw)
-    x = AluExp.where(valid, AluExp.global_index(dt, 0, N * Ci * H * W, xi), AluExp.const(dt, 0))
-    wi = AluExp.add(AluExp.mul(co, i(Ci * KH * KW)), r)
-    wv = AluExp.global_index(dt, 1, Co * Ci * KH * KW, wi)
-    return Kernel(2, N * Co * OH * OW, AluExp.mul(x, wv), Reduction(dt, AluOp.Add, Ci * KH * KW)), (OH, OW)
+    return P.conv2d_kernel(N, Ci, H, W, Co, KH, KW, stride, pad, dt), (OH, OW)
 
 
 @pytest.mark.parametrize("N,Ci,H,W,Co,KH,KW,stride,pad", [(2, 3, 17, 19, 5, 3, 3, 1, 1), (1, 8, 32, 32, 16, 5, 5, 2, 2), (3, 4, 9, 9, 6, 1, 1, 1, 0)])
