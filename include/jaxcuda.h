@@ -119,7 +119,12 @@ typedef struct {
  * (UnsupportedRoutineError).  params_json is the routine's `params` object as JSON (Scatter:
  * `ScatterParams`, src/routine.ts:104-110; TriangularSolve: {"unitDiagonal": bool}; JacobiEigh:
  * {"maxSweeps": int, "tolerance": number}; Fft: {"factors": [int...], "inverse": bool}).  Shapes the reference rejects
- * (src/routine.ts:305-313, :341-346) return JAXCUDA_EINVAL with its message. */
+ * (src/routine.ts:305-313, :341-346) return JAXCUDA_EINVAL with its message.
+ * Size limits, checked here (JAXCUDA_EUNSUPPORTED with the limit in the message), never at
+ * dispatch: the sorted axis and every matrix dimension below 2^31; TriangularSolve n <= 25600;
+ * JacobiEigh n <= 32768; Cholesky of n >= 256 in batches of at most 65535 matrices, n <= 2^30;
+ * at most 2^31-1 matrices per call.  Sort/Argsort, Scatter and Fft have no limit besides memory
+ * (work space comes from the allocator at dispatch: JAXCUDA_ENOMEM). */
 int jaxcuda_prepare_routine(jaxcuda_ctx* ctx, const char* name, const jaxcuda_routine_type* type,
                             const char* params_json, jaxcuda_exe** out);
 

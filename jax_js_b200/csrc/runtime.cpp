@@ -889,6 +889,13 @@ static int prepare_linalg(jaxcuda_ctx* ctx, const char* name, const jaxcuda_rout
     exe->rt_n = r1;
   }
   if (exe->rt_n >= (1ll << 31) || exe->rt_m >= (1ll << 31)) return fail(ctx, JAXCUDA_EINVAL, "%s: matrix too large", name);
+  // Size limits of the routine kernels, reported here and not at the first dispatch.
+  if (kind == 4 && exe->rt_n > 25600)
+    return fail(ctx, JAXCUDA_EUNSUPPORTED, "TriangularSolve: n = %lld exceeds 25600 (one right-hand side of doubles per warp in shared memory)", (long long)exe->rt_n);
+  if (kind == 7 && exe->rt_n > 32768) return fail(ctx, JAXCUDA_EUNSUPPORTED, "JacobiEigh: n = %lld exceeds 32768", (long long)exe->rt_n);
+  if (kind == 5 && exe->rt_n >= 256 && (exe->rt_batch > 65535 || exe->rt_n > 0x7fffffff / 2))
+    return fail(ctx, JAXCUDA_EUNSUPPORTED, "Cholesky: matrices of 256 rows or more come in batches of at most 65535, n at most 2^30");
+  if (exe->rt_batch > 0x7fffffff) return fail(ctx, JAXCUDA_EUNSUPPORTED, "%s: more than 2^31-1 matrices", name);
   exe->describe = std::string(name) + " batch=" + std::to_string(exe->rt_batch) +
                   (kind == 6 ? " m=" + std::to_string(exe->rt_m) : std::string()) + " n=" + std::to_string(exe->rt_n) +
                   (kind == 4 ? " rows=" + std::to_string(exe->rt_rows) + (exe->rt_flag ? " unit" : "") : std::string());

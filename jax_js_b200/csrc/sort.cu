@@ -12,6 +12,7 @@
 // src/backend/webgpu/routines.ts:57-261), otherwise chunk sorts in shared memory joined by
 // global compare-exchange passes.  Argsort sorts (key, index) pairs as one 64-bit composite,
 // which makes the network's result the stable order.
+#include <atomic>
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
@@ -281,7 +282,9 @@ static __device__ __align__(256) uint32_t jx_sort_static_work[JX_SORT_STATIC_ITE
 
 // In host code the array's name is only a handle for the runtime, not an address a kernel could
 // use; the device address is looked up once per device and cached here.
-static void* g_static_work_addr[64] = {};
+// Two threads that make a device's first call at once both look the address up and store the same
+// value; the slots are atomic so that neither reads a torn pointer.
+static std::atomic<void*> g_static_work_addr[64];
 
 // Sorts each row of a contiguous [batch, n] array along the last axis (same order as the Sort
 // routine: numeric, -0 before +0, NaN last) from device pointer x to device pointer y, on `stream`,
@@ -322,14 +325,14 @@ extern "C" int jaxcuda_sort_no_alloc(void* stream, int dtype, const void* x, voi
   cudaPointerAttributes at;
   if (cudaPointerGetAttributes(&at, x) == cudaSuccess && at.type == cudaMemoryTypeDevice && at.device != dev)
     return fail(3, "sort_no_alloc: the input lives on another device than the current one");
-  if (!g_static_work_addr[dev]) {
-    void* p = nullptr;
-    cudaError_t e = cudaGetSymbolAddress(&p, jx_sort_static_work);
-    if (e != cudaSuccess || !p) return fail(5, cudaGetErrorString(e));
-    g_static_work_addr[dev] = p;
+  void* work = g_static_work_addr[dev].load(std::memory_order_acquire);
+  if (!work) {
+    cudaError_t e = cudaGetSymbolAddress(&work, jx_sort_static_work);
+    if (e != cudaSuccess || !work) return fail(5, cudaGetErrorString(e));
+    g_static_work_addr[dev].store(work, std::memory_order_release);
   }
   int launches = 0;
-  cudaError_t e = jaxcuda_sort::run<false, false>((cudaStream_t)stream, x, y, nullptr, dtype, batch, n, g_static_work_addr[dev], &launches);
+  cudaError_t e = jaxcuda_sort::run<false, false>((cudaStream_t)stream, x, y, nullptr, dtype, batch, n, work, &launches);
   if (e != cudaSuccess) return fail(5, cudaGetErrorString(e));
   return 0;
 }

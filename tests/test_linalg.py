@@ -329,3 +329,21 @@ def test_cuda_linalg_shape_errors(backend):
     t = RoutineType([[3, 3], [2, 4]], [F32, F32], [[2, 4]], [F32])
     with pytest.raises(ValueError, match="triangular_solve: incompatible shapes"):
         backend.prepare_routine(Routine(Routines.TriangularSolve, t, {"unitDiagonal": False}))
+
+
+@pytest.mark.gpu
+def test_cuda_routine_size_limits_are_reported_at_prepare(backend):
+    """Sizes beyond what the routine kernels hold fail when the routine is prepared, with the limit
+    in the message, not at the first dispatch."""
+    from jax_js_b200.backend import UnsupportedOpError
+    n = 30000
+    t = RoutineType([[n, n], [1, n]], [F32, F32], [[1, n]], [F32])
+    with pytest.raises(UnsupportedOpError, match="TriangularSolve: n = 30000 exceeds 25600"):
+        backend.prepare_routine(Routine(Routines.TriangularSolve, t, {"unitDiagonal": False}))
+    n = 40000
+    t = RoutineType([[n, n]], [F32], [[n, n], [n, n]], [F32, F32])
+    with pytest.raises(UnsupportedOpError, match="JacobiEigh: n = 40000 exceeds 32768"):
+        backend.prepare_routine(Routine(Routines.JacobiEigh, t, {"maxSweeps": 10, "tolerance": 1e-6}))
+    t = RoutineType([[70000, 256, 256]], [F32], [[70000, 256, 256]], [F32])
+    with pytest.raises(UnsupportedOpError, match="batches of at most 65535"):
+        backend.prepare_routine(Routine(Routines.Cholesky, t))
