@@ -972,26 +972,130 @@ struct Builder {
     return g;
   }
 
+  // ---- evaluating a convolution's patch expression for a run of consecutive pixels ------------------
+  // Both gather variants give a thread `per` consecutive n (gidx0 .. gidx0 + per - 1) and many k.  The
+  // nodes of the patch are emitted in three groups: what depends on gidx alone (once per thread),
+  // what depends on ridx alone (once per k) and the mixed rest (per element).  When N is a multiple
+  // of `per` a run never leaves its row of pixels, and most of the mixed part is the same for the
+  // whole run or moves by a constant per pixel: a digit (gidx / d) % m with d a multiple of `per` is
+  // constant over the run, the lowest digit gidx % m (m a multiple of `per`) grows by one, and any
+  // node all of whose sources are constant over the run is constant too.  Those nodes are computed
+  // for the first pixel only (for a 3 x 3 window over [N, C, H, W]: the row test of the window, the
+  // row part of the address; per pixel remain the column test, one add for the address, the load).
+  struct PatchRun {
+    const Builder& bd;
+    size_t root;
+    int per;
+    bool aligned;
+    std::vector<char> patch, only_g, not_g, uniform, sloped;
+    std::vector<int64_t> slope;
+    std::vector<std::vector<std::string>> names;
+
+    PatchRun(const Builder& b, size_t patch_node, int per_, bool aligned_)
+        : bd(b), root(patch_node), per(per_), aligned(aligned_), patch(closure(b.k.exp, patch_node)) {
+      const auto& exp = bd.k.exp;
+      const size_t n = exp.size();
+      only_g.assign(n, 0); not_g.assign(n, 0); uniform.assign(n, 0); sloped.assign(n, 0); slope.assign(n, 0);
+      names.assign(per, std::vector<std::string>(n));
+      for (size_t i = 0; i < n; i++) {
+        if (!patch[i]) continue;
+        const Node& nd = exp[i];
+        only_g[i] = !bd.an_exp.dep_r[i];
+        not_g[i] = !bd.an_exp.dep_g[i];
+        if (!aligned) continue;
+        if (!bd.an_exp.dep_g[i]) { uniform[i] = 1; continue; }
+        if (nd.op == JAXCUDA_OP_SPECIAL) { sloped[i] = 1; slope[i] = 1; continue; }   // gidx itself
+        if (bd.an_exp.affine[i] && nd.dtype == JAXCUDA_I32) {
+          bool ok = true;
+          int64_t sl = 0;
+          for (const Term& t : bd.an_exp.affine[i]->terms) {
+            if (t.var != 0 || t.div % per == 0) continue;
+            if (t.div == 1 && (t.mod == 0 || t.mod % per == 0)) sl += t.coef;
+            else ok = false;
+          }
+          if (ok) {
+            if (sl == 0) uniform[i] = 1; else { sloped[i] = 1; slope[i] = sl; }
+            continue;
+          }
+        }
+        bool all = nd.nsrc > 0;
+        for (uint32_t sidx = 0; sidx < nd.nsrc; sidx++) all = all && uniform[nd.src[sidx]];
+        uniform[i] = all;
+      }
+    }
+    // pixels after the first take over what the first one computed
+    void share(int j, const std::vector<char>& mask) {
+      if (j == 0 || !aligned) return;
+      for (size_t i = 0; i < names[j].size(); i++) {
+        if (!mask[i] || !names[j][i].empty() || names[0][i].empty()) continue;
+        if (uniform[i]) names[j][i] = names[0][i];
+        else if (sloped[i]) names[j][i] = "(" + names[0][i] + " + " + S((int64_t)j * slope[i]) + ")";
+      }
+    }
+    // once per thread; expects `gidx0 .. gidx<per-1>` in scope
+    void hoisted(std::ostream& os, const std::string& indent) {
+      for (int j = 0; j < per; j++) {
+        Env env;
+        env.prefix = "h" + S(j) + "_";
+        env.gidx = "gidx" + S(j);
+        share(j, only_g);
+        emit_nodes(os, bd.k.exp, bd.an_exp, names[j], only_g, env, indent);
+      }
+    }
+    // once per k; expects `ridx` in scope and returns the value expressions of the run
+    std::vector<std::string> row(std::ostream& os, const std::string& indent) {
+      std::vector<std::vector<std::string>> local = names;   // names of this k only
+      {
+        std::vector<std::string> shared(bd.k.exp.size());
+        Env env;
+        env.prefix = "r";
+        emit_nodes(os, bd.k.exp, bd.an_exp, shared, not_g, env, indent);
+        for (int j = 0; j < per; j++)
+          for (size_t i = 0; i < shared.size(); i++)
+            if (local[j][i].empty() && !shared[i].empty()) local[j][i] = shared[i];
+      }
+      std::vector<std::string> out;
+      names.swap(local);
+      for (int j = 0; j < per; j++) {
+        Env env;
+        env.prefix = "q" + S(j) + "_";
+        env.gidx = "gidx" + S(j);
+        share(j, patch);
+        emit_nodes(os, bd.k.exp, bd.an_exp, names[j], patch, env, indent);
+        out.push_back(names[j][root]);
+      }
+      names.swap(local);
+      return out;
+    }
+  };
+
   // CUDA C of the stage that evaluates a convolution's patch expression into the B operand
   // [batch][K][pitch] (n contiguous, zero beyond N) at the start of the scratch, followed for f32 by
-  // the 3xTF32 remainder plane.  A thread produces four consecutive n of one (batch, k) row.
+  // the 3xTF32 remainder plane.  A thread owns four consecutive n of one batch entry and walks a
+  // chunk of k (grid.y).
+  static constexpr int kGatherKChunk = 32;
   std::string gather_source(const GemmDesc& g, size_t patch_node) const {
     const bool f16 = g.dtB == JAXCUDA_F16;
+    const bool aligned = g.N % 4 == 0;
+    PatchRun run(*this, patch_node, 4, aligned);
     std::ostringstream os;
     os << "extern \"C\" __global__ void __launch_bounds__(256) jx_gather_b(" << params() << ") {\n";
-    os << "  const i64 quads = " << g.b_pitch / 4 << "LL, total = quads * " << g.K << "LL * " << g.batch << "LL;\n";
-    os << "  for (i64 t = (i64)blockIdx.x * 256 + threadIdx.x; t < total; t += (i64)gridDim.x * 256) {\n";
-    os << "    const int n0 = (int)(t % quads) * 4;\n    const i64 row = t / quads;\n";
-    os << "    const int ridx = (int)(row % " << g.K << "LL), b = (int)(row / " << g.K << "LL);\n";
+    os << "  const i64 quads = " << g.b_pitch / 4 << "LL, total = quads * " << g.batch << "LL;\n";
+    os << "  const i64 t = (i64)blockIdx.x * 256 + threadIdx.x;\n  if (t >= total) return;\n";
+    os << "  const int n0 = (int)(t % quads) * 4, b = (int)(t / quads);\n";
+    os << "  const int k0 = blockIdx.y * " << kGatherKChunk << ", k1 = min(" << g.K << ", k0 + " << kGatherKChunk << ");\n";
+    os << "  const bool n_in = n0 < " << g.N << ";   // the padding between N and the pitch is written as zeros\n";
+    for (int j = 0; j < 4; j++) {
+      if (aligned) os << "  const int gidx" << j << " = b * " << g.M * g.N << " + (n_in ? n0 : 0) + " << j << ";\n";
+      else os << "  const int gidx" << j << " = b * " << g.M * g.N << " + min(n0 + " << j << ", " << g.N - 1 << ");\n";
+    }
+    run.hoisted(os, "  ");
+    os << "  #pragma unroll 2\n  for (int ridx = k0; ridx < k1; ridx++) {\n";
+    const std::vector<std::string> val = run.row(os, "    ");
     os << "    float v[4];\n";
-    os << "    #pragma unroll\n    for (int j = 0; j < 4; j++) {\n      v[j] = 0.0f;\n";
-    os << "      if (n0 + j < " << g.N << ") {\n";
-    os << "        const int gidx = b * " << g.M * g.N << " + n0 + j;\n";
-    std::vector<std::string> names(k.exp.size());
-    Env env;
-    env.prefix = "q";
-    emit_nodes(os, k.exp, an_exp, names, closure(k.exp, patch_node), env, "        ");
-    os << "        v[j] = " << names[patch_node] << ";\n      }\n    }\n";
+    for (int j = 0; j < 4; j++)
+      os << "    v[" << j << "] = n0 + " << j << " < " << g.N << " ? (float)" << val[j] << " : 0.0f;\n";
+    os << "    const i64 row = (i64)b * " << g.K << "LL + ridx;\n";
     if (f16) {
       os << "    jx_pack<jx_half, 4> h;\n    #pragma unroll\n    for (int j = 0; j < 4; j++) h.e[j] = jx_f2h(v[j]);\n";
       os << "    jx_store((jx_half*)scratch + row * " << g.b_pitch << "LL + n0, h);\n";
@@ -1002,6 +1106,52 @@ struct Builder {
       os << "    jx_store((float*)scratch + LEN_B_PAD + row * " << g.b_pitch << "LL + n0, lo);\n";
     }
     os << "  }\n}\n";
+    return os.str();
+  }
+
+  // The same evaluation as a device function of the GEMM kernel (implicit GEMM): the gather threads
+  // of a CTA fill rows k0 .. k0 + BK of one [BK x BN] tile of the patch operand in shared memory, in
+  // the layout a TMA load of an MN-major operand produces (boxes of BK rows x 128 bytes, swizzled).
+  // A thread owns one 16-byte piece of the tile's n-extent (4 or 8 consecutive pixels, the same for
+  // the whole tile, so what depends on the pixels alone stays in registers over the K loop) and
+  // every rgs-th row of k.  Rows beyond K and pixels beyond N are written as zeros.
+  std::string gather_tile_source(const GemmDesc& g, size_t patch_node) const {
+    const bool f16 = g.dtB == JAXCUDA_F16;
+    const int per = f16 ? 8 : 4;
+    const bool aligned = g.N % per == 0;
+    PatchRun run(*this, patch_node, per, aligned);
+    std::ostringstream os;
+    os << "#if B_GATHER\n";
+    os << "__device__ __forceinline__ void jx_gather_tile(JX_PARAMS, u32 sb, int b, int n_tile, int k0, int gt) {\n";
+    os << "  const int piece = gt % (BN / " << per << "), rg = gt / (BN / " << per << ");\n";
+    os << "  const int rgs = GROUP_WARPS * 32 / (BN / " << per << ");\n";
+    os << "  const int n_first = n_tile + piece * " << per << ";\n";
+    os << "  const bool n_in = n_first < " << g.N << ";\n";
+    os << "  const u32 box = sb + (u32)(piece * " << per << " / BK) * BOX_BYTES, in_row = (u32)(piece * " << per << " % BK) * ELEM;\n";
+    for (int j = 0; j < per; j++) {
+      if (aligned) os << "  const int gidx" << j << " = b * " << g.M * g.N << " + (n_in ? n_first : 0) + " << j << ";\n";
+      else os << "  const int gidx" << j << " = b * " << g.M * g.N << " + min(n_first + " << j << ", " << g.N - 1 << ");\n";
+    }
+    run.hoisted(os, "  ");
+    os << "  #pragma unroll " << (f16 ? 4 : 8) << "\n  for (int ri = 0; ri < (BK + rgs - 1) / rgs; ri++) {\n    const int r = rg + ri * rgs;\n";
+    os << "    if (r >= BK) break;\n";
+    os << "    const bool k_in = k0 + r < " << g.K << ";\n    const int ridx = k_in ? k0 + r : " << g.K - 1 << ";\n";
+    const std::vector<std::string> val = run.row(os, "    ");
+    os << "    float v[" << per << "];\n";
+    for (int j = 0; j < per; j++)
+      os << "    v[" << j << "] = (k_in && n_first + " << j << " < " << g.N << ") ? (float)" << val[j] << " : 0.0f;\n";
+    os << "    const u32 at = box + box_swizzle((u32)r * 128u + in_row);\n";
+    if (f16) {
+      os << "    __align__(16) jx_half h[8];\n    #pragma unroll\n    for (int j = 0; j < 8; j++) h[j] = jx_f2h(v[j]);\n";
+      os << "    st_shared_16(at, *reinterpret_cast<const uint4*>(h));\n";
+    } else {
+      os << "    uint4 hi, lo;\n";
+      os << "    hi.x = __float_as_uint(v[0]); hi.y = __float_as_uint(v[1]); hi.z = __float_as_uint(v[2]); hi.w = __float_as_uint(v[3]);\n";
+      os << "    lo.x = __float_as_uint(v[0] - __uint_as_float(hi.x & 0xffffe000u)); lo.y = __float_as_uint(v[1] - __uint_as_float(hi.y & 0xffffe000u));\n";
+      os << "    lo.z = __float_as_uint(v[2] - __uint_as_float(hi.z & 0xffffe000u)); lo.w = __float_as_uint(v[3] - __uint_as_float(hi.w & 0xffffe000u));\n";
+      os << "    st_shared_16(at, hi);\n    st_shared_16(at + B_BYTES, lo);\n";
+    }
+    os << "  }\n}\n#endif\n";
     return os.str();
   }
 
@@ -1424,14 +1574,17 @@ struct Builder {
       size_t patch = 0;
       GemmDesc c = match_conv(patch);
       // worth the gather pass once the GEMM is large enough to fill the machine
-      if (c.valid && c.M >= 64 && c.N >= 64 && c.K >= 32 && c.batch <= 65535 &&
+      if (c.valid && c.M >= 64 && c.N >= 64 && c.K >= 32 && c.K <= 32 * 65535 && c.batch <= 65535 &&
           2.0 * c.M * c.N * c.K * c.batch >= 2e8) {
         Plan p;
         p.gemm = c;
         account(p);
         p.algo_flops = 2.0 * c.M * c.N * c.K * c.batch;
-        if (plan_gemm_tc(k, c, opt, p, epilogue_body("      ", "JX_DST"), params(), std::string(), gather_source(c, patch))) {
-          p.describe = "conv as " + p.describe;
+        c.b_implicit = opt.conv_implicit != 0;
+        p.gemm = c;
+        if (plan_gemm_tc(k, c, opt, p, epilogue_body("      ", "JX_DST"), params(), std::string(),
+                         c.b_implicit ? gather_tile_source(c, patch) : gather_source(c, patch))) {
+          p.describe = "conv as " + p.describe + (c.b_implicit ? " patches gathered in the kernel" : " patches gathered first");
           return p;
         }
       }

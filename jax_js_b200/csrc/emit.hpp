@@ -36,6 +36,9 @@ struct GemmDesc {
   // it); then gidB is unused, sBn = 1, sBk = b_pitch, sBb = K * b_pitch, offB = 0.
   bool b_gathered = false;
   int64_t b_pitch = 0;
+  // ... or, with b_implicit as well, no array at all: warps of the GEMM kernel evaluate the patch
+  // expression straight into the shared-memory stages (gemm_tc.cpp, B_GATHER).
+  bool b_implicit = false;
 };
 
 struct Stage {
@@ -85,6 +88,7 @@ struct Options {
   int col_ctas_per_sm = 4;    // spread ridx over threads and CTAs until the grid holds this many 256-thread CTAs per SM
   int col_ty = 0;             // threads sharing one output vector inside a CTA (0: chosen)
   int col_unroll = 4;         // independent loads in flight per thread in the column-reduce loop
+  int conv_implicit = 1;      // convolutions: 1 = the patch operand is gathered inside the GEMM kernel, 0 = by a stage of its own through global memory (JAXCUDA_CONV_IMPLICIT)
   int fuse_chunks = 0;        // 128-bit pieces of a row per thread in a row program (1, 2 or 4; 0: chosen)
   int fuse_min_ctas = 0;      // CTAs per SM the row program's register allocation is held to (0: compiler's choice)
 };

@@ -12,6 +12,10 @@
 //               descriptors into one of two TMEM accumulators; tcgen05.commit frees the stage
 //   warps 2-5   epilogue: tcgen05.ld the finished accumulator, apply the Kernel's spliced
 //               epilogue (Cast, bias, ReLU ...) and store, while warp 1 fills the other one
+//   warps 6+    convolutions only (B_GATHER): evaluate the Kernel's patch expression for the stage's
+//               [BK x BN] slice of the B operand and write it (and its 3xTF32 remainder) straight
+//               into the stage in the swizzled layout a TMA box would have, so that the patch
+//               operand never exists in global memory (implicit GEMM); TMA then loads A only
 //
 // The kernel is persistent (one CTA per SM, static tile schedule).  float16 operands use
 // kind::f16 with f32 accumulation.  float32 operands use kind::tf32 three times per k-step on
@@ -88,6 +92,15 @@ __device__ __forceinline__ void tmem_ld16(u32 taddr, u32* v) {
                : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
                  "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
                : "r"(taddr));
+}
+
+__device__ __forceinline__ void st_shared_16(u32 addr, uint4 v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+// Where byte `o` (row * 128 + byte in row) of a [rows][128 bytes] TMA box lands inside the box:
+// the 128-byte swizzle in 16-byte units (16-bit elements) or in 32-byte units (32-bit elements).
+__device__ __forceinline__ u32 box_swizzle(u32 o) {
+  return ELEM == 4 ? (o ^ (((o >> 7) & 3u) << 5)) : (o ^ (((o >> 7) & 7u) << 4));
 }
 
 // Shared-memory matrix descriptor (sm_100): start address, leading / stride byte offsets in
@@ -174,7 +187,22 @@ __device__ __forceinline__ bool get_segment(int i, Seg& s) {
   return true;
 }
 
-extern "C" __global__ void __launch_bounds__(192, 1)
+#if B_GATHER
+// Emitted behind this source from the Kernel's patch expression: fills rows k0 .. k0 + BK of the B
+// tile whose first column is n_tile (batch entry b) at shared address sb; gt is the calling thread's
+// index among the GROUP_WARPS * 32 threads that fill this stage.
+__device__ __forceinline__ void jx_gather_tile(JX_PARAMS, u32 sb, int b, int n_tile, int k0, int gt);
+#define TX_BYTES (NPLANES * A_BYTES)
+#else
+#define TX_BYTES STAGE_BYTES
+#endif
+#define NTHREADS (192 + 32 * GATHER_WARPS)
+#define GROUP_WARPS (GATHER_WARPS / GATHER_GROUPS)
+#if B_GATHER && (GATHER_GROUPS > STAGES || GATHER_WARPS % GATHER_GROUPS)
+#error "gather groups must divide the gather warps and not outnumber the stages"
+#endif
+
+extern "C" __global__ void __launch_bounds__(NTHREADS, 1)
 jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA2,
         const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmB2,
         JX_PARAMS, int* status_ptr) {
@@ -194,7 +222,7 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; s++) { mbar_init(full(s), 1); mbar_init(empty(s), 1); }
+    for (int s = 0; s < STAGES; s++) { mbar_init(full(s), 1 + GROUP_WARPS); mbar_init(empty(s), 1); }
     for (int a = 0; a < 2; a++) { mbar_init(tfull(a), 1); mbar_init(tempty(a), 4); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -221,7 +249,7 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
         for (int kb = sg.kb0; kb < sg.kb1; kb++, it++) {
           const int s = it % STAGES;
           if (it >= STAGES && !mbar_wait(empty(s), ((it / STAGES) + 1) & 1, status)) { atomicCAS((int*)status_ptr, 0, 1); failed = true; break; }
-          mbar_expect_tx(full(s), STAGE_BYTES);
+          mbar_expect_tx(full(s), TX_BYTES);
 #if FAULT_SKIP_LOAD
           // test of the wind-down: CTA 0 announces its second stage and never loads it, so the MMA
           // role's bounded wait on that stage runs out
@@ -239,7 +267,9 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
           tma_load_3d(sa, &tmA, full(s), k0, m_blk * BM, ba);
           if (KIND == 2) tma_load_3d(sa + A_BYTES, &tmA2, full(s), k0, m_blk * BM, ba);
 #endif
-#if B_MN
+#if B_GATHER
+          (void)sb; (void)bb; (void)n_blk;
+#elif B_MN
           for (int j = 0; j < BN / BK; j++) {
             tma_load_3d(sb + j * BOX_BYTES, &tmB, full(s), n_blk * BN + j * BK, k0, bb);
             if (KIND == 2) tma_load_3d(sb + B_BYTES + j * BOX_BYTES, &tmB2, full(s), n_blk * BN + j * BK, k0, bb);
@@ -292,6 +322,32 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
         }
       }
     }
+#if B_GATHER
+  } else if (warp >= 6) {
+    // ---------------------------------------------------------------- patch gatherers (convolutions)
+    // GATHER_GROUPS groups of GROUP_WARPS warps take the stages in turn, so that as many stages are
+    // being filled at a time: one group's pass over a stage is a chain of address arithmetic, loads
+    // that mostly come from L2 and stores, longer than the MMAs of a stage take.  GATHER_GROUPS <=
+    // STAGES (the planner sees to it): the parity wait below cannot tell a stage that is two uses
+    // behind from one that is free.
+    const int grp = (threadIdx.x - 192) / (GROUP_WARPS * 32), gt = (threadIdx.x - 192) % (GROUP_WARPS * 32);
+    int it = 0;
+    Seg sg;
+    for (int si = 0; !failed && get_segment(si, sg); si++) {
+      int b, m_blk, n_blk;
+      tile_coords(sg.tile, b, m_blk, n_blk);
+      for (int kb = sg.kb0; kb < sg.kb1; kb++, it++) {
+        if (it % GATHER_GROUPS != grp) continue;
+        const int s = it % STAGES;
+        if (it >= STAGES && !mbar_wait(empty(s), ((it / STAGES) + 1) & 1, status)) { atomicCAS((int*)status_ptr, 0, 5); failed = true; break; }
+        jx_gather_tile(JX_PARAM_NAMES, smem_base + s * STAGE_BYTES + NPLANES * A_BYTES, b, n_blk * BN, kb * BK, gt);
+        // the tensor core reads shared memory through the async proxy: order these writes before it
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full(s));
+      }
+    }
+#endif
   } else {
     // ---------------------------------------------------------------- epilogue warps 2..5
     const int q = warp & 3;                 // TMEM lane quarter this warp may access
@@ -553,6 +609,16 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
   os << "#define A_SHARED " << ((g.batch > 1 && g.sAb == 0) ? 1 : 0) << "\n#define B_SHARED " << ((g.batch > 1 && g.sBb == 0) ? 1 : 0) << "\n";
   os << "#define STREAMK " << (streamk ? 1 : 0) << "\n";
   os << "#define SPIN_LIMIT " << std::max(1024, opt.tc_spin_limit) << "\n#define FAULT_SKIP_LOAD " << (opt.tc_fault == 1 ? 1 : 0) << "\n";
+  // Gather warps of a convolution (B_GATHER): groups of four warps, each group filling every
+  // gather_groups-th stage.  Never more groups than stages: a group waits for "stage free" by phase
+  // parity, which only tells apart two consecutive phases, and the wait of one group for a stage's
+  // next use is behind the previous use's completion only while groups <= stages (with four groups
+  // on three stages a group ran two phases ahead, passed its wait at once and overwrote a stage that
+  // was still being read: "unspecified launch failure").  Measured for N=32, 64 -> 128 channels,
+  // 56 x 56, 3 x 3: f32 8 warps in 2 groups 132 us (12 in 3: 140), f16 12 warps in 3 groups 69 us (8 in 2: 74).
+  const int gather_groups = g.b_implicit ? std::min(stages, kind == 2 ? 2 : 3) : 1;
+  const int gather_warps = g.b_implicit ? 4 * gather_groups : 0;
+  os << "#define B_GATHER " << (g.b_implicit ? 1 : 0) << "\n#define GATHER_WARPS " << gather_warps << "\n#define GATHER_GROUPS " << gather_groups << "\n";
   os << "#define STAGES " << stages << "\n#define A_MN " << (a_mn ? 1 : 0) << "\n#define B_MN " << (b_mn ? 1 : 0) << "\n";
   os << "#define GM " << g.M << "\n#define GN " << g.N << "\n#define GK " << g.K << "\n#define GBATCH " << g.batch << "\n";
   // k-blocks accumulated in tensor memory before the partial sum is folded into registers with a
@@ -564,7 +630,7 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
   os << "#define LEN_A_PAD " << pad64(g.lenA) << "LL\n#define LEN_B_PAD " << pad64(g.lenB) << "LL\n";
   // scratch: [gathered B and its remainder plane][remainder planes of the operands][stream-K counters][stream-K pieces]
   size_t sk_offset = 0;
-  if (g.b_gathered) sk_offset += (size_t)pad64(g.lenB) * e * planes;
+  if (g.b_gathered && !g.b_implicit) sk_offset += (size_t)pad64(g.lenB) * e * planes;
   if (kind == 2) sk_offset += (size_t)(pad64(g.lenA) + (g.b_gathered ? 0 : pad64(g.lenB))) * 4;
   sk_offset = (sk_offset + 255) / 256 * 256;
   const size_t sk_counter_bytes = 4096;   // 4 counters per left-over tile, fewer than 148 of them
@@ -574,6 +640,20 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
                       : k.out_dtype() == JAXCUDA_U32 ? "u32" : k.out_dtype() == JAXCUDA_F32 ? "float" : "int";
   os << "#define JX_OUT_T " << out_t << "\n";
   os << "#define JX_PARAMS " << params_decl << "\n";
+  {  // the same parameters by name, for calls that pass them on
+    std::string names, decl = params_decl + ",";
+    size_t start = 0;
+    for (size_t i = 0; i < decl.size(); i++) {
+      if (decl[i] != ',') continue;
+      size_t end = i;
+      while (end > start && isspace((unsigned char)decl[end - 1])) end--;
+      size_t b0 = end;
+      while (b0 > start && (isalnum((unsigned char)decl[b0 - 1]) || decl[b0 - 1] == '_')) b0--;
+      names += (names.empty() ? "" : ", ") + decl.substr(b0, end - b0);
+      start = i + 1;
+    }
+    os << "#define JX_PARAM_NAMES " << names << "\n";
+  }
   std::string body = epilogue_body;  // newlines inside a macro need continuation
   std::string escaped;
   for (char c : body) { if (c == '\n') escaped += " \\\n"; else escaped += c; }
@@ -591,10 +671,11 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
   plan.tc_bm = BM; plan.tc_bn = BN; plan.tc_bk = bk; plan.tc_stages = stages;
   plan.stages.clear();
   plan.scratch_bytes = 0;
-  if (g.b_gathered) {   // scratch: [B][B remainder plane (3xTF32)][A remainder plane (3xTF32)]
+  if (g.b_gathered && !g.b_implicit) {   // scratch: [B][B remainder plane (3xTF32)][A remainder plane (3xTF32)]
     Stage ga;
     ga.entry = "jx_gather_b";
-    ga.grid[0] = (unsigned)std::max<int64_t>(1, std::min<int64_t>(((int64_t)g.lenB / 4 + 255) / 256, (int64_t)opt.sm_count * 32));
+    ga.grid[0] = (unsigned)std::max<int64_t>(1, (g.b_pitch / 4 * g.batch + 255) / 256);  // a thread per four pixels ...
+    ga.grid[1] = (unsigned)std::max<int64_t>(1, (g.K + 31) / 32);                         // ... and 32 values of k (emit.cpp: kGatherKChunk)
     ga.block[0] = 256;
     plan.stages.push_back(ga);
     plan.scratch_bytes = (size_t)pad64(g.lenB) * e * planes;
@@ -614,7 +695,7 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
   Stage st;
   st.entry = "jx_gemm";
   st.grid[0] = streamk ? (unsigned)opt.sm_count : (unsigned)std::min<int64_t>(tiles, opt.sm_count);
-  st.block[0] = 192;
+  st.block[0] = 192 + 32 * gather_warps;
   st.smem = (unsigned)(stages * stage_bytes + 1024 + (2 * stages + 4) * 8 + 16);
   plan.stages.push_back(st);
   plan.describe = std::string("gemm-tcgen05 ") + (kind == 1 ? "f16" : "3xtf32") + " " + std::to_string(g.batch) + "x" +
@@ -637,11 +718,11 @@ int launch_gemm_tc(void* encode_fn, void* launch_fn, const Plan& plan, const std
   int launches = 0;
   size_t stage_i = 0;
   const char* baseA = (const char*)inputs[g.gidA];
-  const char* baseB = g.b_gathered ? (const char*)scratch : (const char*)inputs[g.gidB];
+  const char* baseB = g.b_implicit ? (const char*)inputs[g.gidA] : g.b_gathered ? (const char*)scratch : (const char*)inputs[g.gidB];
   const char* baseA2 = baseA;
   const char* baseB2 = baseB;
   char* split_planes = (char*)scratch;
-  if (g.b_gathered) {
+  if (g.b_gathered && !g.b_implicit) {
     // the gather kernel takes the Kernel's own parameters (inputs, out, scratch) and fills B (and its
     // remainder plane) at the start of the scratch
     std::vector<void*> gp(inputs.begin(), inputs.end());
@@ -650,7 +731,7 @@ int launch_gemm_tc(void* encode_fn, void* launch_fn, const Plan& plan, const std
     std::vector<void*> gargs;
     for (auto& p : gp) gargs.push_back(&p);
     const Stage& ga = plan.stages[stage_i];
-    CUresult r = launch(fns[stage_i], ga.grid[0], 1, 1, ga.block[0], 1, 1, 0, (CUstream)stream, gargs.data(), nullptr);
+    CUresult r = launch(fns[stage_i], ga.grid[0], ga.grid[1], 1, ga.block[0], 1, 1, 0, (CUstream)stream, gargs.data(), nullptr);
     if (r != CUDA_SUCCESS) { err = "launch of the operand gather kernel failed"; return -1; }
     launches++;
     stage_i++;
@@ -693,8 +774,9 @@ int launch_gemm_tc(void* encode_fn, void* launch_fn, const Plan& plan, const std
   const int64_t a_outer = a_mn ? g.sAk : g.sAm, b_outer = b_mn ? g.sBk : g.sBn;
   bool ok = make_map(&tmA, baseA, g.offA, a_mn, g.M, g.K, a_outer, g.sAb, a_mn ? bk : plan.tc_bm) &&
             make_map(&tmA2, baseA2, g.offA, a_mn, g.M, g.K, a_outer, g.sAb, a_mn ? bk : plan.tc_bm) &&
-            make_map(&tmB, baseB, g.offB, b_mn, g.N, g.K, b_outer, g.sBb, b_mn ? bk : plan.tc_bn) &&
-            make_map(&tmB2, baseB2, g.offB, b_mn, g.N, g.K, b_outer, g.sBb, b_mn ? bk : plan.tc_bn);
+            (g.b_implicit || (make_map(&tmB, baseB, g.offB, b_mn, g.N, g.K, b_outer, g.sBb, b_mn ? bk : plan.tc_bn) &&
+                              make_map(&tmB2, baseB2, g.offB, b_mn, g.N, g.K, b_outer, g.sBb, b_mn ? bk : plan.tc_bn)));
+  if (g.b_implicit) { tmB = tmA; tmB2 = tmA; }   // not read: the kernel fills the B stages itself
   if (!ok) { err = "cuTensorMapEncodeTiled rejected a GEMM operand"; return -1; }
   std::vector<void*> ptrs(inputs.begin(), inputs.end());
   ptrs.push_back(out);

@@ -353,6 +353,43 @@ def test_convolution_kernel_on_the_tensor_pipe(backend, N, Ci, H, W, Co, KH, KW,
     assert_close(got, ref, 1e-5 if dt == F32 else 2e-3, np.abs(ref).max(), "conv vs float64")
 
 
+def test_convolution_gather_routes_agree_and_repeat(backend):
+    """The patch operand is gathered inside the GEMM kernel (the default) or by a stage of its own
+    through global memory (JAXCUDA_CONV_IMPLICIT=0): the same values enter the same MMAs, so the
+    results are the same bits; and forty launches in a row of the in-kernel gather (stages refilled by
+    alternating warp groups) reproduce them."""
+    import os
+    from jax_js_b200.backend import CudaBackend
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((8, 64, 28, 28)).astype(np.float32)
+    w = rng.standard_normal((128, 64, 3, 3)).astype(np.float32)
+    k, _ = _conv_kernel(8, 64, 28, 28, 128, 3, 3, 1, 1, F32)
+    exe = backend.prepare_kernel(k)
+    assert exe.describe.endswith("patches gathered in the kernel"), exe.describe
+    sx, sw, so = backend.put(x), backend.put(w), backend.malloc(k.bytes)
+    backend.dispatch(exe, [sx, sw], [so])
+    first = backend.read_sync(so).copy()
+    for _ in range(40):
+        backend.dispatch(exe, [sx, sw], [so])
+    assert np.array_equal(backend.read_sync(so), first)
+    for s_ in (sx, sw, so):
+        backend.dec_ref(s_)
+    old = os.environ.get("JAXCUDA_CONV_IMPLICIT")
+    os.environ["JAXCUDA_CONV_IMPLICIT"] = "0"
+    try:
+        other = CudaBackend(backend.device)
+    finally:
+        if old is None:
+            os.environ.pop("JAXCUDA_CONV_IMPLICIT")
+        else:
+            os.environ["JAXCUDA_CONV_IMPLICIT"] = old
+    try:
+        assert other.prepare_kernel(k).describe.endswith("patches gathered first")
+        assert np.array_equal(run_cuda(other, k, [x, w]).view(np.uint8).reshape(-1), first.reshape(-1))
+    finally:
+        other.close()
+
+
 def test_max_pool_kernel(backend):
     """`jitRules[Pool]` then a Max reduction: 2 x 2 windows, stride 2, over [N, C, H, W]."""
     N, C, H, W = 3, 5, 16, 20
