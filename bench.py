@@ -165,7 +165,7 @@ def other_configs(be, peaks, iters=None):
     ms, exe = time_kernel(be, P.conv2d_kernel(N, Ci, H, H, Co, 3, 3, 1, 1), [x, w], iters=iters or 10, warmup=2)
     out["conv2d_f32_32x64x56x56_k3"] = {"tflops": flops / ms / 1e9, "frac_3xtf32_ceiling": flops / ms / 1e9 / (peaks["bf16_tflops"] / 6),
                                         "ms": ms, "kernel": exe.describe,
-                                        "stages": "patch operand gathered to [batch][576][3136] (+ its 3xTF32 remainder plane), then the tcgen05 GEMM"}
+                                        "stages": "implicit GEMM: warp groups of the tcgen05 kernel evaluate the patch operand (and its 3xTF32 remainder) into the shared-memory stages; TMA loads the weights"}
     x16, w16 = x.astype(np.float16), w.astype(np.float16)
     ms, exe = time_kernel(be, P.conv2d_kernel(N, Ci, H, H, Co, 3, 3, 1, 1, DType.Float16), [x16, w16], iters=iters or 10, warmup=2)
     out["conv2d_f16_32x64x56x56_k3"] = {"tflops": flops / ms / 1e9, "frac_tensor_burst": flops / ms / 1e9 / peaks["bf16_tflops"],
