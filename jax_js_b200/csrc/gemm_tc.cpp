@@ -12,6 +12,8 @@
 //               descriptors into one of two TMEM accumulators; tcgen05.commit frees the stage
 //   warps 2-5   epilogue: tcgen05.ld the finished accumulator, apply the Kernel's spliced
 //               epilogue (Cast, bias, ReLU ...) and store, while warp 1 fills the other one
+//   then        3xTF32 with LO_IN_KERNEL: four warps that derive the remainder tiles from the loaded
+//               operands inside the stage (after the gather warps, when there are any)
 //   warps 6+    convolutions only (B_GATHER): evaluate the Kernel's patch expression for the stage's
 //               [BK x BN] slice of the B operand and write it (and its 3xTF32 remainder) straight
 //               into the stage in the swizzled layout a TMA box would have, so that the patch
@@ -94,6 +96,11 @@ __device__ __forceinline__ void tmem_ld16(u32 taddr, u32* v) {
                : "r"(taddr));
 }
 
+__device__ __forceinline__ uint4 ld_shared_16(u32 addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
 __device__ __forceinline__ void st_shared_16(u32 addr, uint4 v) {
   asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
@@ -192,11 +199,14 @@ __device__ __forceinline__ bool get_segment(int i, Seg& s) {
 // tile whose first column is n_tile (batch entry b) at shared address sb; gt is the calling thread's
 // index among the GROUP_WARPS * 32 threads that fill this stage.
 __device__ __forceinline__ void jx_gather_tile(JX_PARAMS, u32 sb, int b, int n_tile, int k0, int gt);
-#define TX_BYTES (NPLANES * A_BYTES)
-#else
-#define TX_BYTES STAGE_BYTES
 #endif
-#define NTHREADS (192 + 32 * GATHER_WARPS)
+// LO_IN_KERNEL (3xTF32): TMA brings only the operands themselves and signals raw(s); XFORM_WARPS
+// warps then write the remainder tiles lo = x - tf32(x) beside them, chunk for chunk at the same
+// offsets (so the swizzle needs no thought), and arrive on full(s).  No split pass over global
+// memory, half the TMA traffic.
+#define TMA_PLANES (LO_IN_KERNEL ? 1 : NPLANES)
+#define TX_BYTES (B_GATHER ? TMA_PLANES * A_BYTES : TMA_PLANES * (A_BYTES + B_BYTES))
+#define NTHREADS (192 + 32 * (GATHER_WARPS + XFORM_WARPS))
 #define GROUP_WARPS (GATHER_WARPS / GATHER_GROUPS)
 #if B_GATHER && (GATHER_GROUPS > STAGES || GATHER_WARPS % GATHER_GROUPS)
 #error "gather groups must divide the gather warps and not outnumber the stages"
@@ -214,15 +224,22 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
   (void)sk_counters; (void)sk_pieces;
   const u32 smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;     // swizzle atoms are 1024-byte aligned
   const u32 bars = smem_base + STAGES * STAGE_BYTES;                // full[STAGES], empty[STAGES], tfull[2], tempty[2]
-  const u32 tmem_slot = bars + (2 * STAGES + 4) * 8;
+  const u32 tmem_slot = bars + (2 * STAGES + 4 + (LO_IN_KERNEL ? STAGES : 0)) * 8;
   auto full = [&](int s) { return bars + s * 8; };
   auto empty = [&](int s) { return bars + (STAGES + s) * 8; };
   auto tfull = [&](int a) { return bars + (2 * STAGES + a) * 8; };
   auto tempty = [&](int a) { return bars + (2 * STAGES + 2 + a) * 8; };
+  auto raw = [&](int s) { return bars + (2 * STAGES + 4 + s) * 8; };   // LO_IN_KERNEL only
+  auto tma_bar = [&](int s) { return LO_IN_KERNEL ? raw(s) : full(s); };
+  (void)raw;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; s++) { mbar_init(full(s), 1 + GROUP_WARPS); mbar_init(empty(s), 1); }
+    for (int s = 0; s < STAGES; s++) {
+      mbar_init(full(s), (LO_IN_KERNEL ? XFORM_WARPS : 1) + (B_GATHER ? GROUP_WARPS : 0));
+      mbar_init(empty(s), 1);
+      if (LO_IN_KERNEL) mbar_init(raw(s), 1);
+    }
     for (int a = 0; a < 2; a++) { mbar_init(tfull(a), 1); mbar_init(tempty(a), 4); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -249,7 +266,7 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
         for (int kb = sg.kb0; kb < sg.kb1; kb++, it++) {
           const int s = it % STAGES;
           if (it >= STAGES && !mbar_wait(empty(s), ((it / STAGES) + 1) & 1, status)) { atomicCAS((int*)status_ptr, 0, 1); failed = true; break; }
-          mbar_expect_tx(full(s), TX_BYTES);
+          mbar_expect_tx(tma_bar(s), TX_BYTES);
 #if FAULT_SKIP_LOAD
           // test of the wind-down: CTA 0 announces its second stage and never loads it, so the MMA
           // role's bounded wait on that stage runs out
@@ -260,23 +277,23 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
           const int ba = A_SHARED ? 0 : b, bb = B_SHARED ? 0 : b;   // an operand all batches share has one plane
 #if A_MN
           for (int j = 0; j < BM / BK; j++) {
-            tma_load_3d(sa + j * BOX_BYTES, &tmA, full(s), m_blk * BM + j * BK, k0, ba);
-            if (KIND == 2) tma_load_3d(sa + A_BYTES + j * BOX_BYTES, &tmA2, full(s), m_blk * BM + j * BK, k0, ba);
+            tma_load_3d(sa + j * BOX_BYTES, &tmA, tma_bar(s), m_blk * BM + j * BK, k0, ba);
+            if (KIND == 2 && !LO_IN_KERNEL) tma_load_3d(sa + A_BYTES + j * BOX_BYTES, &tmA2, tma_bar(s), m_blk * BM + j * BK, k0, ba);
           }
 #else
-          tma_load_3d(sa, &tmA, full(s), k0, m_blk * BM, ba);
-          if (KIND == 2) tma_load_3d(sa + A_BYTES, &tmA2, full(s), k0, m_blk * BM, ba);
+          tma_load_3d(sa, &tmA, tma_bar(s), k0, m_blk * BM, ba);
+          if (KIND == 2 && !LO_IN_KERNEL) tma_load_3d(sa + A_BYTES, &tmA2, tma_bar(s), k0, m_blk * BM, ba);
 #endif
 #if B_GATHER
           (void)sb; (void)bb; (void)n_blk;
 #elif B_MN
           for (int j = 0; j < BN / BK; j++) {
-            tma_load_3d(sb + j * BOX_BYTES, &tmB, full(s), n_blk * BN + j * BK, k0, bb);
-            if (KIND == 2) tma_load_3d(sb + B_BYTES + j * BOX_BYTES, &tmB2, full(s), n_blk * BN + j * BK, k0, bb);
+            tma_load_3d(sb + j * BOX_BYTES, &tmB, tma_bar(s), n_blk * BN + j * BK, k0, bb);
+            if (KIND == 2 && !LO_IN_KERNEL) tma_load_3d(sb + B_BYTES + j * BOX_BYTES, &tmB2, tma_bar(s), n_blk * BN + j * BK, k0, bb);
           }
 #else
-          tma_load_3d(sb, &tmB, full(s), k0, n_blk * BN, bb);
-          if (KIND == 2) tma_load_3d(sb + B_BYTES, &tmB2, full(s), k0, n_blk * BN, bb);
+          tma_load_3d(sb, &tmB, tma_bar(s), k0, n_blk * BN, bb);
+          if (KIND == 2 && !LO_IN_KERNEL) tma_load_3d(sb + B_BYTES, &tmB2, tma_bar(s), k0, n_blk * BN, bb);
 #endif
         }
       }
@@ -301,6 +318,7 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
           const int kb_end = kb_first + CHUNK_KB < sg.kb1 ? kb_first + CHUNK_KB : sg.kb1;
           for (int kb = kb_first; kb < kb_end; kb++, it++) {
             const int s = it % STAGES;
+            if (LO_IN_KERNEL && !mbar_wait(raw(s), (it / STAGES) & 1, status)) { atomicCAS((int*)status_ptr, 0, 3); failed = true; break; }
             if (!mbar_wait(full(s), (it / STAGES) & 1, status)) { atomicCAS((int*)status_ptr, 0, 3); failed = true; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const u32 sa = smem_base + s * STAGE_BYTES, sb = sa + NPLANES * A_BYTES;
@@ -323,7 +341,7 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
       }
     }
 #if B_GATHER
-  } else if (warp >= 6) {
+  } else if (warp >= 6 && warp < 6 + GATHER_WARPS) {
     // ---------------------------------------------------------------- patch gatherers (convolutions)
     // GATHER_GROUPS groups of GROUP_WARPS warps take the stages in turn, so that as many stages are
     // being filled at a time: one group's pass over a stage is a chain of address arithmetic, loads
@@ -342,6 +360,40 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
         if (it >= STAGES && !mbar_wait(empty(s), ((it / STAGES) + 1) & 1, status)) { atomicCAS((int*)status_ptr, 0, 5); failed = true; break; }
         jx_gather_tile(JX_PARAM_NAMES, smem_base + s * STAGE_BYTES + NPLANES * A_BYTES, b, n_blk * BN, kb * BK, gt);
         // the tensor core reads shared memory through the async proxy: order these writes before it
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full(s));
+      }
+    }
+#endif
+#if LO_IN_KERNEL
+  } else if (warp >= 6 + GATHER_WARPS) {
+    // ---------------------------------------------------------------- remainder tiles (3xTF32)
+    const int xt = threadIdx.x - 192 - 32 * GATHER_WARPS;
+    auto lo_of = [](uint4 v) {
+      uint4 r;
+      r.x = __float_as_uint(__uint_as_float(v.x) - __uint_as_float(v.x & 0xffffe000u));
+      r.y = __float_as_uint(__uint_as_float(v.y) - __uint_as_float(v.y & 0xffffe000u));
+      r.z = __float_as_uint(__uint_as_float(v.z) - __uint_as_float(v.z & 0xffffe000u));
+      r.w = __float_as_uint(__uint_as_float(v.w) - __uint_as_float(v.w & 0xffffe000u));
+      return r;
+    };
+    int it = 0;
+    Seg sg;
+    for (int si = 0; !failed && get_segment(si, sg); si++) {
+      for (int kb = sg.kb0; kb < sg.kb1; kb++, it++) {
+        const int s = it % STAGES;
+        // the TMA of this use of the stage was issued after the MMAs of the previous use had
+        // finished, so once it has landed the remainder tiles are free to overwrite as well
+        if (!mbar_wait(raw(s), (it / STAGES) & 1, status)) { atomicCAS((int*)status_ptr, 0, 6); failed = true; break; }
+        const u32 sa = smem_base + s * STAGE_BYTES;
+        #pragma unroll 4
+        for (int c = xt; c < A_BYTES / 16; c += XFORM_WARPS * 32) st_shared_16(sa + A_BYTES + c * 16, lo_of(ld_shared_16(sa + c * 16)));
+#if !B_GATHER
+        const u32 sb = sa + 2 * A_BYTES;
+        #pragma unroll 4
+        for (int c = xt; c < B_BYTES / 16; c += XFORM_WARPS * 32) st_shared_16(sb + B_BYTES + c * 16, lo_of(ld_shared_16(sb + c * 16)));
+#endif
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(full(s));
@@ -618,6 +670,15 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
   // 56 x 56, 3 x 3: f32 8 warps in 2 groups 132 us (12 in 3: 140), f16 12 warps in 3 groups 69 us (8 in 2: 74).
   const int gather_groups = g.b_implicit ? std::min(stages, kind == 2 ? 2 : 3) : 1;
   const int gather_warps = g.b_implicit ? 4 * gather_groups : 0;
+  // Remainder tiles made in the kernel save the split pass (a launch and a round trip of both
+  // operands through global memory) but add a read and a write of every stage to the shared-memory
+  // traffic that already bounds the 3xTF32 main loop.  Measured: 1024^3 (one wave of tiles) 30.1 ->
+  // 27.2 us, 8192 x 2048 x 2048 320 -> 339 us, the convolution 131 -> 149 us.  So: outputs of at most
+  // one wave of tiles only (JAXCUDA_TC_LO_IN_KERNEL = 0 never, 2 always).
+  const bool lo_in_kernel = kind == 2 && !(g.b_gathered && !g.b_implicit) &&
+                            (opt.tc_lo_in_kernel == 2 || (opt.tc_lo_in_kernel == 1 && !g.b_gathered && tiles <= opt.sm_count));
+  const int xform_warps = lo_in_kernel ? 4 : 0;
+  os << "#define LO_IN_KERNEL " << (lo_in_kernel ? 1 : 0) << "\n#define XFORM_WARPS " << xform_warps << "\n";
   os << "#define B_GATHER " << (g.b_implicit ? 1 : 0) << "\n#define GATHER_WARPS " << gather_warps << "\n#define GATHER_GROUPS " << gather_groups << "\n";
   os << "#define STAGES " << stages << "\n#define A_MN " << (a_mn ? 1 : 0) << "\n#define B_MN " << (b_mn ? 1 : 0) << "\n";
   os << "#define GM " << g.M << "\n#define GN " << g.N << "\n#define GK " << g.K << "\n#define GBATCH " << g.batch << "\n";
@@ -631,7 +692,7 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
   // scratch: [gathered B and its remainder plane][remainder planes of the operands][stream-K counters][stream-K pieces]
   size_t sk_offset = 0;
   if (g.b_gathered && !g.b_implicit) sk_offset += (size_t)pad64(g.lenB) * e * planes;
-  if (kind == 2) sk_offset += (size_t)(pad64(g.lenA) + (g.b_gathered ? 0 : pad64(g.lenB))) * 4;
+  if (kind == 2 && !lo_in_kernel) sk_offset += (size_t)(pad64(g.lenA) + (g.b_gathered ? 0 : pad64(g.lenB))) * 4;
   sk_offset = (sk_offset + 255) / 256 * 256;
   const size_t sk_counter_bytes = 4096;   // 4 counters per left-over tile, fewer than 148 of them
   const size_t sk_bytes = streamk ? sk_counter_bytes + (size_t)opt.sm_count * BM * BN * 4 : 0;   // one slice per CTA
@@ -680,7 +741,8 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
     plan.stages.push_back(ga);
     plan.scratch_bytes = (size_t)pad64(g.lenB) * e * planes;
   }
-  if (kind == 2) {
+  plan.tc_lo_in_kernel = lo_in_kernel;
+  if (kind == 2 && !lo_in_kernel) {
     Stage sp;
     sp.entry = "jx_split";
     const int64_t split_len = g.lenA + (g.b_gathered ? 0 : g.lenB);
@@ -695,14 +757,14 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
   Stage st;
   st.entry = "jx_gemm";
   st.grid[0] = streamk ? (unsigned)opt.sm_count : (unsigned)std::min<int64_t>(tiles, opt.sm_count);
-  st.block[0] = 192 + 32 * gather_warps;
-  st.smem = (unsigned)(stages * stage_bytes + 1024 + (2 * stages + 4) * 8 + 16);
+  st.block[0] = 192 + 32 * (gather_warps + xform_warps);
+  st.smem = (unsigned)(stages * stage_bytes + 1024 + (3 * stages + 4) * 8 + 16);
   plan.stages.push_back(st);
   plan.describe = std::string("gemm-tcgen05 ") + (kind == 1 ? "f16" : "3xtf32") + " " + std::to_string(g.batch) + "x" +
                   std::to_string(g.M) + "x" + std::to_string(g.N) + "x" + std::to_string(g.K) + " tile 128x" +
                   std::to_string(BN) + "x" + std::to_string(bk) + " stages=" + std::to_string(stages) + " A:" +
                   (a_mn ? "MN" : "K") + " B:" + (b_mn ? "MN" : "K") + " ctas=" + std::to_string(st.grid[0]) +
-                  (streamk ? " split-k" : "");
+                  (lo_in_kernel ? " lo-in-kernel" : "") + (streamk ? " split-k" : "");
   return true;
 }
 
@@ -739,7 +801,7 @@ int launch_gemm_tc(void* encode_fn, void* launch_fn, const Plan& plan, const std
     baseB2 = baseB + plane_bytes;
     split_planes = (char*)scratch + plane_bytes * (kind == 2 ? 2 : 1);
   }
-  if (kind == 2) {
+  if (kind == 2 && !plan.tc_lo_in_kernel) {
     float* planes = (float*)split_planes;
     const char* split_b = g.b_gathered ? baseA : baseB;   // not read when LEN_B is 0
     void* args[] = {(void*)&baseA, (void*)&split_b, (void*)&planes};

@@ -315,7 +315,7 @@ int check_device_status(jaxcuda_ctx* ctx) {
     const int code = *ctx->status_host;
     *ctx->status_host = 0;
     cudaMemsetAsync(ctx->status_dev, 0, sizeof(int), ctx->stream);
-    return fail(ctx, JAXCUDA_ECUDA, "tcgen05 GEMM pipeline wait timed out (role %d: 1 producer, 2/3 mma, 4 epilogue, 5 patch gatherer); "
+    return fail(ctx, JAXCUDA_ECUDA, "tcgen05 GEMM pipeline wait timed out (role %d: 1 producer, 2/3 mma, 4 epilogue, 5 patch gatherer, 6 remainder tiles); "
                 "results of that dispatch are invalid", code);
   }
   return JAXCUDA_OK;
@@ -431,6 +431,7 @@ int jaxcuda_create(int device, jaxcuda_ctx** out) {
   ctx->opt.exact_math = env_int("JAXCUDA_EXACT_MATH", ctx->opt.exact_math);
   ctx->opt.ld_hint = env_int("JAXCUDA_LD_HINT", ctx->opt.ld_hint);
   ctx->opt.conv_implicit = env_int("JAXCUDA_CONV_IMPLICIT", ctx->opt.conv_implicit);
+  ctx->opt.tc_lo_in_kernel = env_int("JAXCUDA_TC_LO_IN_KERNEL", ctx->opt.tc_lo_in_kernel);
   ctx->opt.row_tpr = env_int("JAXCUDA_ROW_TPR", ctx->opt.row_tpr);
   ctx->opt.row_unroll = env_int("JAXCUDA_ROW_UNROLL", ctx->opt.row_unroll);
   ctx->opt.col_threads = env_int("JAXCUDA_COL_THREADS", ctx->opt.col_threads);

@@ -390,6 +390,39 @@ def test_convolution_gather_routes_agree_and_repeat(backend):
         other.close()
 
 
+def test_remainder_tiles_made_in_the_kernel_match_the_split_pass(backend):
+    """3xTF32: the remainder tiles lo = x - tf32(x) come from a split pass through global memory or
+    are derived inside the GEMM kernel from the loaded operands; the MMAs see the same values, so the
+    results are the same bits (several waves of tiles, a K tail, a bias epilogue)."""
+    import os
+    from jax_js_b200.backend import CudaBackend
+    rng = np.random.default_rng(21)
+    m, n, kk = 1536, 1280, 1000
+    a = rng.uniform(-1, 1, (m, kk)).astype(np.float32)
+    b = rng.uniform(-1, 1, (kk, n)).astype(np.float32)
+    k = P.dot_kernel(m, n, kk)
+    got = {}
+    for mode in ("0", "2"):
+        old = os.environ.get("JAXCUDA_TC_LO_IN_KERNEL")
+        os.environ["JAXCUDA_TC_LO_IN_KERNEL"] = mode
+        try:
+            other = CudaBackend(backend.device)
+        finally:
+            if old is None:
+                os.environ.pop("JAXCUDA_TC_LO_IN_KERNEL")
+            else:
+                os.environ["JAXCUDA_TC_LO_IN_KERNEL"] = old
+        try:
+            assert ("lo-in-kernel" in other.prepare_kernel(k).describe) == (mode == "2")
+            for _ in range(3):
+                got[mode] = run_cuda(other, k, [a, b])
+        finally:
+            other.close()
+    assert np.array_equal(got["0"].view(np.uint32), got["2"].view(np.uint32))
+    want = a.astype(np.float64) @ b.astype(np.float64)
+    assert_close(got["2"].reshape(m, n) / kk, want / kk, 1e-5, 1.0, "3xTF32 with in-kernel remainder tiles")
+
+
 def test_max_pool_kernel(backend):
     """`jitRules[Pool]` then a Max reduction: 2 x 2 windows, stride 2, over [N, C, H, W]."""
     N, C, H, W = 3, 5, 16, 20
