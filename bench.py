@@ -131,29 +131,30 @@ def time_kernel(be, kernel, arrays, iters=20, warmup=3, copies=1):
     return ms, exe
 
 
-def other_configs(be, peaks, iters=None):
-    """One figure for each remaining benchmark configuration (resident inputs, CUDA events)."""
+def other_configs(be, peaks, iters=None, warmup=None):
+    """One figure for each remaining benchmark configuration (resident inputs, CUDA events).  `warmup`
+    overrides every config's own warm-up count (the profiler run wants few launches)."""
     from jax_js_b200 import DType
     from jax_js_b200 import programs as P
     rng = np.random.default_rng(0)
     out = {}
     n = 1024
     a, b = rng.uniform(-1, 1, (n, n)).astype(np.float32), rng.uniform(-1, 1, (n, n)).astype(np.float32)
-    ms, exe = time_kernel(be, P.dot_kernel(n, n, n), [a, b], iters=iters or 50)
+    ms, exe = time_kernel(be, P.dot_kernel(n, n, n), [a, b], iters=iters or 50, warmup=warmup or 3)
     out["matmul_f32_1024"] = {"tflops": 2 * n**3 / ms / 1e9, "ms": ms, "kernel": exe.describe}
     w = (rng.standard_normal((4096, 11008)) * 0.02).astype(np.float16)
     x = (rng.standard_normal(4096) * 0.02).astype(np.float16)
     for name, k, args in (("matvec_f16_xW_4096x11008", P.matvec_kernel(4096, 11008, DType.Float16, orientation="xW"), [x, w]),
                           ("matvec_f16_Wx_11008x4096", P.matvec_kernel(11008, 4096, DType.Float16, orientation="Wx"),
                            [w.reshape(11008, 4096), x])):
-        ms, exe = time_kernel(be, k, args, iters=iters or 60, copies=3)
+        ms, exe = time_kernel(be, k, args, iters=iters or 60, warmup=warmup or 3, copies=3)
         nbytes = exe.cost()[0]
         out[name] = {"gbs": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"], "ms": ms,
                      "kernel": exe.describe, "l2": "launches rotate over 3 copies of W (270 MB), larger than L2"}
     n = 4096
     a = (rng.standard_normal((n, n)) * 0.02).astype(np.float16)
     b = (rng.standard_normal((n, n)) * 0.02).astype(np.float16)
-    ms, exe = time_kernel(be, P.dot_kernel(n, n, n, DType.Float16), [a, b], iters=iters or 10, warmup=2)
+    ms, exe = time_kernel(be, P.dot_kernel(n, n, n, DType.Float16), [a, b], iters=iters or 10, warmup=warmup or 2)
     tf = 2 * n**3 / ms / 1e9
     out["matmul_f16_4096"] = {"tflops": tf, "frac_tensor_burst": tf / peaks["bf16_tflops"], "ms": ms, "kernel": exe.describe}
     # a convolution as `jitRules[Conv]` emits it: NCHW 32 x 64 x 56 x 56, 128 filters of 3 x 3, padding 1.
@@ -162,12 +163,12 @@ def other_configs(be, peaks, iters=None):
     x = rng.standard_normal((N, Ci, H, H)).astype(np.float32)
     w = (rng.standard_normal((Co, Ci, 3, 3)) * 0.05).astype(np.float32)
     flops = 2.0 * N * Co * H * H * Ci * 9
-    ms, exe = time_kernel(be, P.conv2d_kernel(N, Ci, H, H, Co, 3, 3, 1, 1), [x, w], iters=iters or 10, warmup=2)
+    ms, exe = time_kernel(be, P.conv2d_kernel(N, Ci, H, H, Co, 3, 3, 1, 1), [x, w], iters=iters or 10, warmup=warmup or 2)
     out["conv2d_f32_32x64x56x56_k3"] = {"tflops": flops / ms / 1e9, "frac_3xtf32_ceiling": flops / ms / 1e9 / (peaks["bf16_tflops"] / 6),
                                         "ms": ms, "kernel": exe.describe,
                                         "stages": "implicit GEMM: warp groups of the tcgen05 kernel evaluate the patch operand (and its 3xTF32 remainder) into the shared-memory stages; TMA loads the weights"}
     x16, w16 = x.astype(np.float16), w.astype(np.float16)
-    ms, exe = time_kernel(be, P.conv2d_kernel(N, Ci, H, H, Co, 3, 3, 1, 1, DType.Float16), [x16, w16], iters=iters or 10, warmup=2)
+    ms, exe = time_kernel(be, P.conv2d_kernel(N, Ci, H, H, Co, 3, 3, 1, 1, DType.Float16), [x16, w16], iters=iters or 10, warmup=warmup or 2)
     out["conv2d_f16_32x64x56x56_k3"] = {"tflops": flops / ms / 1e9, "frac_tensor_burst": flops / ms / 1e9 / peaks["bf16_tflops"],
                                         "ms": ms, "kernel": exe.describe}
     return out
@@ -381,7 +382,7 @@ def _run():
     if args.only_configs:
         from jax_js_b200.backend import CudaBackend
         be = CudaBackend(int(os.environ.get("LOCAL_RANK", "0")))
-        out = {"configs": other_configs(be, measured_peaks(), iters=args.steps or 2)}
+        out = {"configs": other_configs(be, measured_peaks(), iters=args.steps or 2, warmup=args.warmup)}
         be.close()
         return out
     steps = args.steps if args.steps is not None else 1000
