@@ -322,16 +322,19 @@ def test_convolution_kernel_through_the_generic_skeletons(backend, N, Ci, H, W, 
     assert_close(got, ref, 1e-5, np.abs(ref).max(), "conv vs float64")
 
 
-@pytest.mark.parametrize("N,Ci,H,W,Co,KH,KW,pad,dt", [(32, 64, 56, 56, 128, 3, 3, 1, F32), (8, 32, 30, 30, 96, 5, 5, 0, F32),
-                                                       (16, 64, 28, 28, 128, 3, 3, 1, F16)])
-def test_convolution_kernel_on_the_tensor_pipe(backend, N, Ci, H, W, Co, KH, KW, pad, dt):
+@pytest.mark.parametrize("N,Ci,H,W,Co,KH,KW,pad,dt,stride", [
+    (32, 64, 56, 56, 128, 3, 3, 1, F32, 1), (8, 32, 30, 30, 96, 5, 5, 0, F32, 1), (16, 64, 28, 28, 128, 3, 3, 1, F16, 1),
+    (8, 32, 30, 30, 96, 5, 5, 0, F16, 1),      # 676 pixels: not a multiple of the 8 a gather thread owns
+    (8, 64, 56, 56, 128, 3, 3, 1, F32, 2),     # stride 2: neighbouring pixels read every other input column
+    (6, 48, 31, 29, 80, 3, 3, 1, F32, 1)])     # 899 pixels: odd, runs cross image rows, K = 432 is no multiple of BK tail-free
+def test_convolution_kernel_on_the_tensor_pipe(backend, N, Ci, H, W, Co, KH, KW, pad, dt, stride):
     """A convolution large enough to be worth it runs as a gather of the patch operand followed by the
     tcgen05 GEMM (3xTF32 for float32): same Kernel, same oracle, GEMM tolerances."""
     rng = np.random.default_rng(11)
     npdt = np.float32 if dt == F32 else np.float16
     x = (rng.standard_normal((N, Ci, H, W)) * (1.0 if dt == F32 else 0.25)).astype(npdt)
     w = (rng.standard_normal((Co, Ci, KH, KW)) * (1.0 if dt == F32 else 0.05)).astype(npdt)
-    k, (OH, OW) = _conv_kernel(N, Ci, H, W, Co, KH, KW, 1, pad, dt)
+    k, (OH, OW) = _conv_kernel(N, Ci, H, W, Co, KH, KW, stride, pad, dt)
     assert backend.prepare_kernel(k).describe.startswith("conv as gemm-tcgen05"), backend.prepare_kernel(k).describe
     got = run_cuda(backend, k, [x, w]).astype(np.float64).reshape(N, Co, OH, OW)
     K = Ci * KH * KW
@@ -349,7 +352,8 @@ def test_convolution_kernel_on_the_tensor_pipe(backend, N, Ci, H, W, Co, KH, KW,
     ref = np.zeros((N, Co, OH, OW))
     for kh in range(KH):
         for kw in range(KW):
-            ref += np.einsum("nchw,oc->nohw", xp[:, :, kh: kh + OH, kw: kw + OW], w[:, :, kh, kw].astype(np.float64), optimize=True)
+            ref += np.einsum("nchw,oc->nohw", xp[:, :, kh: kh + stride * OH: stride, kw: kw + stride * OW: stride],
+                             w[:, :, kh, kw].astype(np.float64), optimize=True)
     assert_close(got, ref, 1e-5 if dt == F32 else 2e-3, np.abs(ref).max(), "conv vs float64")
 
 
