@@ -1640,6 +1640,57 @@ KernelIR fold_unit_reduction(const KernelIR& k) {
 
 }  // namespace
 
+bool compose_elementwise(const KernelIR& a_in, const KernelIR& b, uint32_t b_arg, KernelIR& out, std::string& why) {
+  if (b.has_red) { why = "the consumer reduces"; return false; }
+  if (a_in.has_red && (a_in.red_size != 1 || a_in.exp.empty() || a_in.epi.empty())) { why = "the producer reduces"; return false; }
+  const KernelIR a = a_in.has_red ? fold_unit_reduction(a_in) : a_in;
+  if (a.exp.empty() || b.exp.empty() || b_arg >= b.nargs) { why = "empty kernel"; return false; }
+  const uint32_t a_dt = a.exp.back().dtype;
+  if (dtype_bytes(a_dt) != 4) { why = "the producer's output is not a 4-byte type"; return false; }   // f16 rounds on its store
+  if (b.nargs - 1 + a.nargs > 64) { why = "too many arguments"; return false; }
+  int loads = 0;
+  size_t load_at = 0;
+  for (size_t i = 0; i < b.exp.size(); i++)
+    if (b.exp[i].op == JAXCUDA_OP_GLOBALINDEX && b.exp[i].arg0 == b_arg) { loads++; load_at = i; }
+  if (loads != 1) { why = "the consumer loads the array more than once"; return false; }
+  const Node& ld = b.exp[load_at];
+  if (ld.dtype != a_dt || ld.arg1 != a.size) { why = "the load does not see the whole output in its own type"; return false; }
+  const Analysis an = analyze(b.exp, b.size, 1);
+  if (!in_range(an.affine[ld.src[0]], ld.arg1)) { why = "the load's index is not proven in range"; return false; }
+  for (const Node& nd : a.exp)
+    if (nd.op == JAXCUDA_OP_SPECIAL && nd.arg0 != 0) { why = "the producer reads ridx"; return false; }
+  out = KernelIR();
+  out.nargs = b.nargs - 1 + a.nargs;
+  out.size = b.size;
+  out.has_red = false;
+  std::vector<uint32_t> bmap(b.exp.size(), 0);
+  auto b_argno = [&](uint64_t g) { return g < b_arg ? g : g - 1; };
+  for (size_t i = 0; i < b.exp.size(); i++) {
+    if (i == load_at) {
+      const uint32_t index_node = bmap[ld.src[0]];
+      std::vector<uint32_t> amap(a.exp.size(), 0);
+      for (size_t j = 0; j < a.exp.size(); j++) {
+        const Node& nd = a.exp[j];
+        if (nd.op == JAXCUDA_OP_SPECIAL) { amap[j] = index_node; continue; }   // A's gidx is B's load index
+        Node c = nd;
+        for (uint32_t sidx = 0; sidx < c.nsrc; sidx++) c.src[sidx] = amap[nd.src[sidx]];
+        if (c.op == JAXCUDA_OP_GLOBALINDEX) c.arg0 = (b.nargs - 1) + nd.arg0;
+        out.exp.push_back(c);
+        amap[j] = (uint32_t)out.exp.size() - 1;
+      }
+      bmap[i] = amap.back();
+      continue;
+    }
+    Node c = b.exp[i];
+    for (uint32_t sidx = 0; sidx < c.nsrc; sidx++) c.src[sidx] = bmap[b.exp[i].src[sidx]];
+    if (c.op == JAXCUDA_OP_GLOBALINDEX) c.arg0 = b_argno(c.arg0);
+    out.exp.push_back(c);
+    bmap[i] = (uint32_t)out.exp.size() - 1;
+  }
+  if (bmap.back() != out.exp.size() - 1) out.exp.push_back(out.exp[bmap.back()]);   // the root comes last
+  return true;
+}
+
 Plan make_plan(const KernelIR& k, const Options& opt) {
   if (k.has_red && k.red_size == 1 && opt.force_skeleton < 0 && !k.exp.empty() && !k.epi.empty()) {
     const KernelIR folded = fold_unit_reduction(k);

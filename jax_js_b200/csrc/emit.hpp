@@ -128,6 +128,18 @@ struct FuseBuffer {
 bool plan_row_fusion(const std::vector<FuseStage>& stages, const std::vector<FuseBuffer>& bufs, int64_t rows, int64_t cols,
                      const Options& opt, Plan& plan, std::vector<int>& params, std::string& why);
 
+// ---- a producer substituted into its only consumer ---------------------------------------------
+//
+// `vmap` of a gradient hands over a per-example outer product as a Dot with the batch axis last
+// followed by the Kernel that moves the batch axis first (src/frontend/vmap.ts:297-303 and the
+// moveaxis of the outputs): the 205 MB result is written, read and written again.  Where a captured
+// step list shows that Kernel B is the only reader of Kernel A's output (which the list then frees),
+// A elementwise (a reduction of size 1 counts) and B elementwise with one load of that output at an
+// index proven in range, B runs with A's expression in place of the load, evaluated at B's index:
+// what `jit` itself does for views of elementwise producers, across the Kernel boundary the
+// reduction put there.  Arguments of the result: B's without `b_arg`, then A's.
+bool compose_elementwise(const KernelIR& a, const KernelIR& b, uint32_t b_arg, KernelIR& out, std::string& why);
+
 // Implemented in gemm_tc.cpp: rewrites `plan` to the tcgen05 skeleton when `g` qualifies.
 // `gather_source` (with g.b_gathered) is the CUDA C of the kernel `jx_gather_b` that fills the B
 // operand; it is compiled with the GEMM and launched first.

@@ -159,6 +159,27 @@ std::optional<Affine> scale(const Affine& x, int64_t s, const Space& sp) {
 bool is_const(const Affine& a) { return a.terms.empty(); }
 bool single_digit(const Affine& a) { return a.c0 == 0 && a.terms.size() == 1 && a.terms[0].coef == 1; }
 
+// A non-negative mixed-radix form splits at c into the digits whose weights are multiples of c and
+// the rest, when the rest never reaches c: x = c * high + low with 0 <= low < c.  This is what
+// recovers the digits of an index that an earlier Kernel's view had flattened
+// ((a * 64 + b * 65536 + d) / 65536 = b when a * 64 + d stays below 65536).
+bool split_at(const Affine& x, int64_t c, const Space& sp, Affine& high, Affine& low) {
+  if (x.lo < 0 || x.c0 < 0) return false;
+  high = Affine();
+  low = Affine();
+  high.c0 = x.c0 / c;
+  low.c0 = x.c0 % c;
+  for (Term t : x.terms) {
+    if (t.coef < 0) return false;
+    if (t.coef % c == 0) { t.coef /= c; high.terms.push_back(t); }
+    else low.terms.push_back(t);
+  }
+  normalize(low, sp);
+  if (low.hi >= c) return false;
+  normalize(high, sp);
+  return true;
+}
+
 std::optional<Affine> idiv(const Affine& x, int64_t c, const Space& sp) {
   if (c <= 0) return std::nullopt;
   if (x.lo >= 0 && x.hi < c) { Affine z; normalize(z, sp); return z; }
@@ -169,14 +190,17 @@ std::optional<Affine> idiv(const Affine& x, int64_t c, const Space& sp) {
     if (t.mod) t.mod /= c;
     Affine r; r.terms = {t}; normalize(r, sp); return r;
   }
-  if (x.lo >= 0 && x.c0 % c == 0) {  // every part divisible: exact
-    for (const Term& t : x.terms) if (t.coef % c != 0 || t.coef < 0) return std::nullopt;
+  bool divisible = x.lo >= 0 && x.c0 % c == 0;
+  for (const Term& t : x.terms) divisible = divisible && t.coef % c == 0 && t.coef >= 0;
+  if (divisible) {  // every part divisible: exact
     Affine r = x;
     r.c0 /= c;
     for (Term& t : r.terms) t.coef /= c;
     normalize(r, sp);
     return r;
   }
+  Affine high, low;
+  if (split_at(x, c, sp, high, low)) return high;
   return std::nullopt;
 }
 
@@ -189,6 +213,8 @@ std::optional<Affine> mod(const Affine& x, int64_t c, const Space& sp) {
     t.mod = c;
     Affine r; r.terms = {t}; normalize(r, sp); return r;
   }
+  Affine high, low;
+  if (split_at(x, c, sp, high, low)) return low;
   return std::nullopt;
 }
 

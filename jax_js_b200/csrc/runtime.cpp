@@ -205,6 +205,7 @@ struct PendingDispatch {
   void* out = nullptr;
   size_t out_bytes = 0;
   bool out_freed = false;  // the output's slot was released before the list was flushed: nobody else can read it
+  size_t freed_at = (size_t)-1;  // ... after this many dispatches of the list (later users of the address see another array)
 };
 
 struct jaxcuda_ctx {
@@ -525,7 +526,7 @@ int jaxcuda_decref(jaxcuda_ctx* ctx, jaxcuda_slot slot) {
   if (--s->refs == 0) {
     if (int rc = order_after_users(ctx, s)) return rc;
     for (size_t i = ctx->pending.size(); i-- > 0;)   // the latest pending writer of this block produced it
-      if (ctx->pending[i].out == s->ptr) { ctx->pending[i].out_freed = true; break; }
+      if (ctx->pending[i].out == s->ptr) { ctx->pending[i].out_freed = true; ctx->pending[i].freed_at = ctx->pending.size(); break; }
     if (s->ptr) ctx->alloc.put(s->ptr, s->bytes);
     ctx->slots.erase(slot);
   }
@@ -1277,13 +1278,78 @@ static size_t launch_row_group(jaxcuda_ctx* ctx, std::vector<PendingDispatch>& l
   return i;
 }
 
+// Kernel list[i] (elementwise, a reduction of size 1 included) feeds only list[i + 1], which is
+// elementwise, and its output is released afterwards: the consumer with the producer's expression
+// in place of its load (emit.hpp: compose_elementwise).  Returns the argument of the consumer that
+// is replaced, or -1.
+static int composable_pair(const std::vector<PendingDispatch>& list, size_t i, KernelIR& composed) {
+  if (i + 1 >= list.size()) return -1;
+  const PendingDispatch& a = list[i];
+  const PendingDispatch& b = list[i + 1];
+  if (a.exe->kind != 0 || b.exe->kind != 0 || !a.out_freed || a.freed_at < i + 2) return -1;
+  int b_arg = -1;
+  for (size_t k = 0; k < b.in.size(); k++)
+    if (b.in[k] == a.out) { if (b_arg >= 0) return -1; b_arg = (int)k; }
+  if (b_arg < 0) return -1;
+  for (size_t r = i + 2; r < list.size() && r < a.freed_at; r++)   // another reader of the same array
+    for (void* p : list[r].in) if (p == a.out) return -1;
+  for (void* p : a.in) if (p == b.out) return -1;                  // the consumer's output replaces one of the producer's inputs
+  std::string why;
+  if (!compose_elementwise(a.exe->ir, b.exe->ir, (uint32_t)b_arg, composed, why)) return -1;
+  return b_arg;
+}
+
+static std::vector<void*> composed_inputs(const PendingDispatch& a, const PendingDispatch& b, int b_arg) {
+  std::vector<void*> in;
+  for (size_t k = 0; k < b.in.size(); k++) if ((int)k != b_arg) in.push_back(b.in[k]);
+  for (void* p : a.in) in.push_back(p);
+  return in;
+}
+
+// Launches list[i] and list[i + 1] as one Kernel where that is possible; returns i + 2 then, else i.
+static size_t launch_composed_pair(jaxcuda_ctx* ctx, std::vector<PendingDispatch>& list, size_t i) {
+  KernelIR composed;
+  const int b_arg = composable_pair(list, i, composed);
+  if (b_arg < 0) return i;
+  std::ostringstream key;
+  key << "compose:" << std::hex << list[i].exe->hash << ">" << list[i + 1].exe->hash << "@" << b_arg;
+  jaxcuda_exe* fx = nullptr;
+  auto hit = ctx->fused.find(key.str());
+  if (hit != ctx->fused.end()) fx = hit->second.get();
+  else {
+    std::unique_ptr<jaxcuda_exe> exe(new jaxcuda_exe);
+    exe->ctx = ctx;
+    exe->ir = composed;
+    bool ok = false;
+    try {
+      exe->plan = make_plan(exe->ir, ctx->opt);
+      ok = true;
+    } catch (const std::exception&) {}
+    if (ok) {
+      exe->describe = exe->plan.describe + " (producer substituted)";
+      if (ctx->debug >= 4) fprintf(stderr, "[jaxcuda] %s\n", exe->describe.c_str());
+      if (ctx->debug >= 2) fprintf(stderr, "%s\n", exe->plan.source.c_str());
+      if (compile_plan(ctx, exe.get()) != JAXCUDA_OK) { free_exe(ctx, exe.get()); ok = false; }
+    }
+    if (!ok) { ctx->fused[key.str()] = nullptr; return i; }
+    fx = exe.get();
+    ctx->fused[key.str()] = std::move(exe);
+  }
+  if (!fx) return i;
+  if (launch_kernel(ctx, fx, composed_inputs(list[i], list[i + 1], b_arg), list[i + 1].out) != JAXCUDA_OK) return i;
+  ctx->capture_groups++;
+  return i + 2;
+}
+
 // Launches everything dispatched so far inside the capture, in order.
 static int flush_pending(jaxcuda_ctx* ctx) {
   if (ctx->pending.empty()) return JAXCUDA_OK;
   std::vector<PendingDispatch> list = std::move(ctx->pending);
   ctx->pending.clear();
   for (size_t i = 0; i < list.size();) {
-    const size_t next = launch_row_group(ctx, list, i);
+    size_t next = launch_row_group(ctx, list, i);
+    if (next > i) { i = next; continue; }
+    next = launch_composed_pair(ctx, list, i);
     if (next > i) { i = next; continue; }
     if (int rc = launch_kernel(ctx, list[i].exe, list[i].in, list[i].out)) return rc;
     i++;
@@ -1344,6 +1410,23 @@ int jaxcuda_check_step_list(int n, const uint8_t* const* irs, const size_t* lens
       done = end;
     }
     if (done) { i = done; continue; }
+    {
+      KernelIR composed;
+      if (composable_pair(list, i, composed) >= 0) {
+        try {
+          Plan plan = make_plan(composed, opt);
+          if (compile) {
+            std::vector<char> cubin;
+            std::string err;
+            if (!nvrtc_compile(plan.source, cubin, err)) { put(message, message_len, err); return JAXCUDA_ECOMPILE; }
+          }
+          rep << i << "-" << i + 1 << ": " << plan.describe << " (producer substituted) bytes=" << (long long)plan.algo_bytes << "\n";
+          src << plan.source << "\n";
+          i += 2;
+          continue;
+        } catch (const std::exception&) {}
+      }
+    }
     try {
       Plan plan = make_plan(list[i].exe->ir, opt);
       rep << i << ": " << plan.describe << " bytes=" << (long long)plan.algo_bytes << "\n";

@@ -209,3 +209,19 @@ def test_step_lists_that_are_no_row_programs_stay_as_they_are(lib):
     # a row too long for one CTA's registers is left to the row-reduce skeleton
     report, _ = check_step_list(P.softmax_lse_argmax_program(4, 65536), compile=False)
     assert not any("row-fused" in r for r in report), report
+
+
+def test_step_list_check_substitutes_an_elementwise_producer_into_its_only_consumer(lib):
+    """The vmapped gradient program ends in per-example outer products written batch-last and the
+    Kernels that move the batch axis first; the step-list check reports each pair as one Kernel
+    whose loads are contiguous or broadcast again (the flattened index splits back into its digits)."""
+    from jax_js_b200 import mlp
+    from jax_js_b200.backend import check_step_list
+    prog = mlp.mlp_grad_program(64, [784, 1024, 10], per_example=True)
+    report, source = check_step_list(prog, compile=True)
+    fused = [l for l in report if "producer substituted" in l]
+    big = [l for l in fused if "bytes=205983744" in l]   # x, dz1 in; f32[64, 784, 1024] out, once
+    assert len(big) == 1 and len(fused) >= 2, report
+    assert big[0].split(":")[1].strip().startswith("elementwise V=4"), big[0]
+    body = source[source.index("jx_elementwise("):]
+    assert "jx_load(pk" in body.split("jx_store")[0]     # the row of dz1 comes as 128-bit vectors
