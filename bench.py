@@ -262,6 +262,7 @@ def vmap_grad(be, rank, world, dist, steps=30, warmup=3):
         for s in prog.execute(be, slots):
             be.dec_ref(s)
     graph, outs = prog.capture(be, slots)
+    launches, graph_bytes, fused = be.graph_cost(graph)
     be.graph_launch(graph)
     be.sync()
     if dist:
@@ -281,10 +282,14 @@ def vmap_grad(be, rank, world, dist, steps=30, warmup=3):
     for s in slots:
         be.dec_ref(s)
     return {"steps_per_s": steps / ms * 1e3, "ms_per_step": ms / steps, "batch": GB, "local_batch": local,
-            "algorithmic_gbs": nbytes * world * steps / ms / 1e6, "scaling": "strong",
+            "algorithmic_gbs": graph_bytes * world * steps / ms / 1e6, "scaling": "strong",
+            "bytes_per_step": graph_bytes, "bytes_per_step_kernel_by_kernel": nbytes,
+            "kernels_per_step": launches, "fused_runs": fused,
             "memory": "L2-resident: this rank's arrays fit the 126 MB L2, so the figure is not HBM throughput"
-                      if nbytes < 126e6 else "streams from HBM",
-            "note": "per-example dW1 is f32[batch,784,1024]: a batch-last Dot result plus the transposing Kernel that moves the batch axis first"}
+                      if graph_bytes < 126e6 else "streams from HBM",
+            "note": "per-example dW1 is f32[batch,784,1024]; the reference's list writes it batch-last and moves the batch axis "
+                    "first in a second Kernel, the captured replay substitutes the product into that Kernel and writes it once; "
+                    "bytes are what the launched kernels address (inputs + outputs), summed"}
 
 
 def oracle_program_runner(rows, threads):

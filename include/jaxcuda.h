@@ -169,7 +169,13 @@ uint64_t jaxcuda_launch_count(jaxcuda_ctx* ctx);
  * src/library/numpy.ts:533-556) are replaced by one row-resident kernel that reads every outside
  * array once and writes only the slots still alive when the run ends; a Kernel repeated on the same
  * arrays is computed once.  Results are those of the separate Kernels up to the summation order
- * of the row reductions.  JAXCUDA_FUSE=0 in the environment turns the replacement off. */
+ * of the row reductions.  Likewise an elementwise Kernel (a reduction of size 1 included) whose
+ * output only the next Kernel reads, elementwise too, before the list releases it, is substituted
+ * into that Kernel: the consumer evaluates the producer's expression at the index of its load and
+ * the intermediate array is never written (a vmapped gradient's per-example products, which
+ * arrive batch-last followed by the Kernel that moves the batch axis first,
+ * src/frontend/vmap.ts:297-303).  Same operations on the same values: same bits.
+ * JAXCUDA_FUSE=0 in the environment turns both replacements off. */
 int jaxcuda_capture_begin(jaxcuda_ctx* ctx);
 int jaxcuda_capture_end(jaxcuda_ctx* ctx, jaxcuda_graph** out);
 int jaxcuda_graph_launch(jaxcuda_ctx* ctx, jaxcuda_graph* graph);
