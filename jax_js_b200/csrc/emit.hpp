@@ -46,6 +46,7 @@ struct Stage {
   unsigned grid[3] = {1, 1, 1};
   unsigned block[3] = {1, 1, 1};
   unsigned smem = 0;
+  unsigned cluster = 1;   // CTAs per thread-block cluster along x (the paired tensor-core GEMM launches with 2)
 };
 
 struct Plan {
@@ -65,6 +66,7 @@ struct Plan {
   // tensor-core GEMM launch parameters (SK_GEMM_TC), filled by gemm_tc.cpp
   int tc_kind = 0;            // 1 f16, 2 3xTF32
   int tc_bm = 0, tc_bn = 0, tc_bk = 0, tc_stages = 0;
+  bool tc_pair = false;          // CTA pairs (tcgen05 cta_group::2) on 256 x BN tiles
   bool tc_lo_in_kernel = false;  // 3xTF32 remainder tiles are made inside the GEMM kernel: no split stage, no planes in scratch
   size_t tc_sk_offset = 0, tc_sk_counter_bytes = 0;  // stream-K arrival counters inside the scratch (cleared per launch)
 };
@@ -77,6 +79,7 @@ struct Options {
   bool allow_tc = true;       // tcgen05 path allowed (JAXCUDA_NO_TC=1 clears it)
   int tc_bn = 0;              // force the tensor-core tile width (64, 128, 192, 256); 0 = planner's choice (JAXCUDA_TC_BN)
   int tc_streamk = 1;         // 0: whole tiles only; 1: an output with at most half as many tiles as SMs and a long K is cut along K; 2: so is any last wave that is at most half full (JAXCUDA_TC_STREAMK)
+  int tc_pair = 1;            // CTA pairs on 256-row tiles (cta_group::2): 0 never, 1 f16 GEMMs, 2 3xTF32 as well (JAXCUDA_TC_PAIR)
   int tc_spin_limit = 20000000;  // polls of a tensor-core pipeline wait before it gives up (JAXCUDA_TC_SPIN_LIMIT)
   int tc_lo_in_kernel = 1;    // 3xTF32 remainder tiles derived in shared memory by warps of the GEMM kernel instead of a split pass through global memory: 0 never, 1 for outputs of at most one wave of tiles, 2 always (JAXCUDA_TC_LO_IN_KERNEL)
   int tc_fault = 0;           // tests of the wind-down only: 1 = one CTA's producer announces a stage and never loads it (JAXCUDA_TC_FAULT)

@@ -75,8 +75,39 @@ __device__ __forceinline__ void tma_load_3d(u32 dst, const CUtensorMap* map, u32
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
+// CTA_PAIR: two CTAs of a cluster work on one 256 x BN tile (tcgen05 cta_group::2).  Each CTA loads
+// its own 128 rows of A and its own half of the columns of B; the MMAs, issued by the even CTA alone,
+// read B from both.  Per output a CTA so fetches a third less (f16, BN = 256) through L2 and shared
+// memory, which is what bounds the single-CTA kernel.  The loads carry no multicast: each CTA's own
+// TMA (cta_group::2 form) reports to the even CTA's mbarrier, whose address is the own one with the
+// rank bit cleared.
+__device__ __forceinline__ void tma_load_3d_pair(u32 dst, const CUtensorMap* map, u32 bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar & 0xFEFFFFFFu), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(u32 bar) {   // arrives on the barrier at this offset in both CTAs
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"((unsigned short)3) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_at(u32 bar, u32 cta_rank) {   // arrive on CTA cta_rank's barrier at this offset
+  asm volatile("{\n\t.reg .b32 r;\n\tmapa.shared::cluster.u32 r, %0, %1;\n\t"
+               "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [r];\n\t}" ::"r"(bar), "r"(cta_rank) : "memory");
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void umma(u32 d_tmem, u64 adesc, u64 bdesc, u32 idesc, u32 accumulate) {
-#if KIND == 1
+#if CTA_PAIR && KIND == 1
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+#elif CTA_PAIR
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+#elif KIND == 1
   asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
@@ -132,18 +163,22 @@ __device__ __forceinline__ u64 operand_desc(u32 base, int kk, int mn_major) {
                    : make_desc(base + kk * KROWS * 128, BOX_BYTES, 1024, 2);
 }
 
+#define TILE_M (CTA_PAIR ? 2 * BM : BM)     /* rows of a tile: a CTA pair covers 256 */
+#define B_COLS (CTA_PAIR ? BN / 2 : BN)     /* columns of B a CTA holds per stage */
+#define WORKER ((int)blockIdx.x / (CTA_PAIR ? 2 : 1))   /* index of this CTA (pair) in the tile schedule */
+#define WORKERS ((int)gridDim.x / (CTA_PAIR ? 2 : 1))
 #define A_BYTES (BM * 128)
-#define B_BYTES (BN * 128)
+#define B_BYTES (B_COLS * 128)
 #define NPLANES (KIND == 2 ? 2 : 1)
 #define STAGE_BYTES (NPLANES * (A_BYTES + B_BYTES))
-#define TILES_M ((GM + BM - 1) / BM)
+#define TILES_M ((GM + TILE_M - 1) / TILE_M)
 #define TILES_N ((GN + BN - 1) / BN)
 #define NUM_TILES (TILES_M * TILES_N * GBATCH)
 #define K_BLOCKS ((GK + BK - 1) / BK)
 #define TMEM_COLS (2 * ACC_STRIDE)     /* a power of two; the two accumulators start ACC_STRIDE columns apart */
 #define NCHUNK ((K_BLOCKS + CHUNK_KB - 1) / CHUNK_KB)
 #define IDESC ((1u << 4) | ((KIND == 2 ? 2u : 0u) << 7) | ((KIND == 2 ? 2u : 0u) << 10) | ((u32)A_MN << 15) | \
-               ((u32)B_MN << 16) | ((u32)(BN >> 3) << 17) | ((u32)(BM >> 4) << 24))
+               ((u32)B_MN << 16) | ((u32)(BN >> 3) << 17) | ((u32)(TILE_M >> 4) << 24))
 
 __device__ __forceinline__ void tile_coords(int t, int& b, int& m_blk, int& n_blk) {
   const int per_batch = TILES_M * TILES_N;
@@ -169,15 +204,15 @@ __device__ __forceinline__ void tile_coords(int t, int& b, int& m_blk, int& n_bl
 // k-ranges of the same panels and every operand byte comes from DRAM.)  A slice's accumulators go to
 // scratch; the CTA that delivers a tile's last slice adds them up in k order and runs the epilogue.
 struct Seg { int tile, kb0, kb1, partial, slot; };
-__device__ __forceinline__ int sk_tiles_full() { return STREAMK ? (NUM_TILES / (int)gridDim.x) * (int)gridDim.x : NUM_TILES; }
+__device__ __forceinline__ int sk_tiles_full() { return STREAMK ? (NUM_TILES / WORKERS) * WORKERS : NUM_TILES; }
 __device__ __forceinline__ int sk_slices() {
   const int rest = NUM_TILES - sk_tiles_full();
-  int s = rest > 0 ? (int)gridDim.x / rest : 1;
+  int s = rest > 0 ? WORKERS / rest : 1;
   s = s > 8 ? 8 : s;
   return s > K_BLOCKS ? K_BLOCKS : s;
 }
 __device__ __forceinline__ bool get_segment(int i, Seg& s) {
-  const int P = gridDim.x, c = blockIdx.x;
+  const int P = WORKERS, c = WORKER;
   const int tiles_full = sk_tiles_full();
   const int n_static = tiles_full > c ? (tiles_full - c + P - 1) / P : 0;
   if (i < n_static) { s.tile = c + i * P; s.kb0 = 0; s.kb1 = K_BLOCKS; s.partial = 0; s.slot = 0; return true; }
@@ -208,6 +243,9 @@ __device__ __forceinline__ void jx_gather_tile(JX_PARAMS, u32 sb, int b, int n_t
 #define TX_BYTES (B_GATHER ? TMA_PLANES * A_BYTES : TMA_PLANES * (A_BYTES + B_BYTES))
 #define NTHREADS (192 + 32 * (GATHER_WARPS + XFORM_WARPS))
 #define GROUP_WARPS (GATHER_WARPS / GATHER_GROUPS)
+#if CTA_PAIR && (STREAMK || B_GATHER || LO_IN_KERNEL)
+#error "CTA pairs run whole tiles with TMA-loaded operands only"
+#endif
 #if B_GATHER && (GATHER_GROUPS > STAGES || GATHER_WARPS % GATHER_GROUPS)
 #error "gather groups must divide the gather warps and not outnumber the stages"
 #endif
@@ -233,6 +271,8 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
   auto tma_bar = [&](int s) { return LO_IN_KERNEL ? raw(s) : full(s); };
   (void)raw;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  u32 rank = 0;                              // CTA_PAIR: 0 for the even CTA of the pair, which issues the MMAs
+  if (CTA_PAIR) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) {
@@ -240,16 +280,22 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
       mbar_init(empty(s), 1);
       if (LO_IN_KERNEL) mbar_init(raw(s), 1);
     }
-    for (int a = 0; a < 2; a++) { mbar_init(tfull(a), 1); mbar_init(tempty(a), 4); }
+    for (int a = 0; a < 2; a++) { mbar_init(tfull(a), 1); mbar_init(tempty(a), CTA_PAIR ? 8 : 4); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
+#if CTA_PAIR
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"((u32)TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+#else
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"((u32)TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+#endif
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (CTA_PAIR) cluster_sync();              // the peer's barriers exist before anything is signalled across
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   u32 tmem_base;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
@@ -266,7 +312,8 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
         for (int kb = sg.kb0; kb < sg.kb1; kb++, it++) {
           const int s = it % STAGES;
           if (it >= STAGES && !mbar_wait(empty(s), ((it / STAGES) + 1) & 1, status)) { atomicCAS((int*)status_ptr, 0, 1); failed = true; break; }
-          mbar_expect_tx(tma_bar(s), TX_BYTES);
+          if (!CTA_PAIR) mbar_expect_tx(tma_bar(s), TX_BYTES);
+          else if (rank == 0) mbar_expect_tx(full(s), 2 * TX_BYTES);   // both CTAs' loads report to the even CTA's barrier
 #if FAULT_SKIP_LOAD
           // test of the wind-down: CTA 0 announces its second stage and never loads it, so the MMA
           // role's bounded wait on that stage runs out
@@ -275,26 +322,33 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
           const u32 sa = smem_base + s * STAGE_BYTES, sb = sa + NPLANES * A_BYTES;
           const int k0 = kb * BK;
           const int ba = A_SHARED ? 0 : b, bb = B_SHARED ? 0 : b;   // an operand all batches share has one plane
+          const int m0 = m_blk * TILE_M + (int)rank * BM, n0 = n_blk * BN + (int)rank * B_COLS;   // this CTA's rows of A and columns of B
+#if CTA_PAIR
+#define TMA_LOAD tma_load_3d_pair
+#else
+#define TMA_LOAD tma_load_3d
+#endif
 #if A_MN
           for (int j = 0; j < BM / BK; j++) {
-            tma_load_3d(sa + j * BOX_BYTES, &tmA, tma_bar(s), m_blk * BM + j * BK, k0, ba);
-            if (KIND == 2 && !LO_IN_KERNEL) tma_load_3d(sa + A_BYTES + j * BOX_BYTES, &tmA2, tma_bar(s), m_blk * BM + j * BK, k0, ba);
+            TMA_LOAD(sa + j * BOX_BYTES, &tmA, tma_bar(s), m0 + j * BK, k0, ba);
+            if (KIND == 2 && !LO_IN_KERNEL) TMA_LOAD(sa + A_BYTES + j * BOX_BYTES, &tmA2, tma_bar(s), m0 + j * BK, k0, ba);
           }
 #else
-          tma_load_3d(sa, &tmA, tma_bar(s), k0, m_blk * BM, ba);
-          if (KIND == 2 && !LO_IN_KERNEL) tma_load_3d(sa + A_BYTES, &tmA2, tma_bar(s), k0, m_blk * BM, ba);
+          TMA_LOAD(sa, &tmA, tma_bar(s), k0, m0, ba);
+          if (KIND == 2 && !LO_IN_KERNEL) TMA_LOAD(sa + A_BYTES, &tmA2, tma_bar(s), k0, m0, ba);
 #endif
 #if B_GATHER
-          (void)sb; (void)bb; (void)n_blk;
+          (void)sb; (void)bb; (void)n0;
 #elif B_MN
-          for (int j = 0; j < BN / BK; j++) {
-            tma_load_3d(sb + j * BOX_BYTES, &tmB, tma_bar(s), n_blk * BN + j * BK, k0, bb);
-            if (KIND == 2 && !LO_IN_KERNEL) tma_load_3d(sb + B_BYTES + j * BOX_BYTES, &tmB2, tma_bar(s), n_blk * BN + j * BK, k0, bb);
+          for (int j = 0; j < B_COLS / BK; j++) {
+            TMA_LOAD(sb + j * BOX_BYTES, &tmB, tma_bar(s), n0 + j * BK, k0, bb);
+            if (KIND == 2 && !LO_IN_KERNEL) TMA_LOAD(sb + B_BYTES + j * BOX_BYTES, &tmB2, tma_bar(s), n0 + j * BK, k0, bb);
           }
 #else
-          tma_load_3d(sb, &tmB, tma_bar(s), k0, n_blk * BN, bb);
-          if (KIND == 2 && !LO_IN_KERNEL) tma_load_3d(sb + B_BYTES, &tmB2, tma_bar(s), k0, n_blk * BN, bb);
+          TMA_LOAD(sb, &tmB, tma_bar(s), k0, n0, bb);
+          if (KIND == 2 && !LO_IN_KERNEL) TMA_LOAD(sb + B_BYTES, &tmB2, tma_bar(s), k0, n0, bb);
 #endif
+#undef TMA_LOAD
         }
       }
     }
@@ -304,7 +358,7 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
     // accumulator (alternating between the two TMEM buffers) that the epilogue warps fold into
     // registers.  Tensor cores add into the accumulator with truncation, a bias that grows with the
     // length of the chain; short chains joined by round-to-nearest f32 adds keep f32 accuracy.
-    if (lane == 0) {
+    if (lane == 0 && rank == 0) {            // of a CTA pair only the even CTA issues MMAs
       int it = 0, cc = 0;
       Seg sg;
       for (int si = 0; !failed && get_segment(si, sg); si++) {
@@ -334,9 +388,10 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
               umma(d, operand_desc(sa, kk, A_MN), operand_desc(sb, kk, B_MN), IDESC, 1u);
 #endif
             }
-            umma_commit(empty(s));            // the stage is free once these MMAs have read it
+            // the stage is free once these MMAs have read it (in both CTAs of a pair)
+            if (CTA_PAIR) umma_commit_pair(empty(s)); else umma_commit(empty(s));
           }
-          if (!failed) umma_commit(tfull(acc));  // this chunk's accumulator is complete
+          if (!failed) { if (CTA_PAIR) umma_commit_pair(tfull(acc)); else umma_commit(tfull(acc)); }  // this chunk's accumulator is complete
         }
       }
     }
@@ -408,7 +463,7 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
     for (int si = 0; !failed && get_segment(si, sg); si++) {
       int b, m_blk, n_blk;
       tile_coords(sg.tile, b, m_blk, n_blk);
-      const int m = m_blk * BM + q * 32 + lane;
+      const int m = m_blk * TILE_M + (int)rank * BM + q * 32 + lane;
       // epilogue and store of 16 consecutive outputs of this thread's row, from their accumulators
       auto finish16 = [&](int c, const float* accv) {
         const int n0 = n_blk * BN + c * 16;
@@ -456,7 +511,7 @@ JX_EPILOGUE
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
-        if (lane == 0) mbar_arrive(tempty(acc_i));
+        if (lane == 0) { if (CTA_PAIR) mbar_arrive_at(tempty(acc_i), 0); else mbar_arrive(tempty(acc_i)); }
       }
       if (failed) break;
 #endif
@@ -494,7 +549,7 @@ JX_EPILOGUE
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive(tempty(acc_i));
+      if (lane == 0) { if (CTA_PAIR) mbar_arrive_at(tempty(acc_i), 0); else mbar_arrive(tempty(acc_i)); }
       cc++;
 #if STREAMK
       if (sg.partial) {
@@ -547,8 +602,13 @@ JX_EPILOGUE
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (CTA_PAIR) cluster_sync();              // neither CTA frees tensor memory the other's MMAs or loads still use
   if (warp == 1) {
+#if CTA_PAIR
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((u32)TMEM_COLS) : "memory");
+#else
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((u32)TMEM_COLS) : "memory");
+#endif
   }
 }
 
@@ -649,17 +709,27 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
     if (opt.tc_streamk != 2 && (tiles >= opt.sm_count || kb_total < 64)) streamk = false;
   }
   const int planes = kind == 2 ? 2 : 1;
-  const int stage_bytes = planes * (BM + BN) * 128;
+  // CTA pairs (cta_group::2) on 256 x BN tiles: each CTA loads half of the B columns, so a third less
+  // (BN = 256) or a quarter less (BN = 128) comes through L2 and shared memory per output.  Whole
+  // tiles only, operands from TMA, and enough tiles to fill the 74 pairs.
+  const int64_t pair_tiles = ((g.M + 2 * BM - 1) / (2 * BM)) * ((g.N + BN - 1) / BN) * g.batch;
+  // Measured (B200): f16 4096^3 109 -> 104 us (1318 TFLOP/s); with K = 1024 or less the pair's extra
+  // set-up costs more than it saves (23.0 -> 24.5 us), and 3xTF32 neither gains nor loses (its tiles
+  // stay 128 columns wide per CTA), so by default pairs run f16 GEMMs with at least 32 k-blocks.
+  // JAXCUDA_TC_PAIR: 0 never, 2 whenever the shape allows.
+  const bool pair = !streamk && !g.b_gathered && g.M >= 2 * BM && BN >= 128 && pair_tiles * 2 >= opt.sm_count &&
+                    (opt.tc_pair == 2 || (opt.tc_pair == 1 && kind == 1 && kb_total >= 32));
+  const int stage_bytes = planes * (BM + (pair ? BN / 2 : BN)) * 128;
   int stages = (227 * 1024 - 2048) / stage_bytes;
-  stages = std::max(2, std::min(stages, 6));
-  const int64_t tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN) * g.batch;
+  stages = std::max(2, std::min(stages, pair ? 8 : 6));
+  const int64_t tiles = pair ? pair_tiles : ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN) * g.batch;
 
   std::ostringstream os;
   os << kPrelude;
   os << "#define KIND " << kind << "\n#define ELEM " << e << "\n#define BM " << BM << "\n#define BN " << BN << "\n";
   os << "#define ACC_STRIDE " << (BN > 128 ? 256 : BN) << "\n";
   os << "#define A_SHARED " << ((g.batch > 1 && g.sAb == 0) ? 1 : 0) << "\n#define B_SHARED " << ((g.batch > 1 && g.sBb == 0) ? 1 : 0) << "\n";
-  os << "#define STREAMK " << (streamk ? 1 : 0) << "\n";
+  os << "#define STREAMK " << (streamk ? 1 : 0) << "\n#define CTA_PAIR " << (pair ? 1 : 0) << "\n";
   os << "#define SPIN_LIMIT " << std::max(1024, opt.tc_spin_limit) << "\n#define FAULT_SKIP_LOAD " << (opt.tc_fault == 1 ? 1 : 0) << "\n";
   // Gather warps of a convolution (B_GATHER): groups of four warps, each group filling every
   // gather_groups-th stage.  Never more groups than stages: a group waits for "stage free" by phase
@@ -676,7 +746,7 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
   // 27.2 us, 8192 x 2048 x 2048 320 -> 339 us, the convolution 131 -> 149 us.  So: outputs of at most
   // one wave of tiles only (JAXCUDA_TC_LO_IN_KERNEL = 0 never, 2 always).
   const bool lo_in_kernel = kind == 2 && !(g.b_gathered && !g.b_implicit) &&
-                            (opt.tc_lo_in_kernel == 2 || (opt.tc_lo_in_kernel == 1 && !g.b_gathered && tiles <= opt.sm_count));
+                            !pair && (opt.tc_lo_in_kernel == 2 || (opt.tc_lo_in_kernel == 1 && !g.b_gathered && tiles <= opt.sm_count));
   const int xform_warps = lo_in_kernel ? 4 : 0;
   os << "#define LO_IN_KERNEL " << (lo_in_kernel ? 1 : 0) << "\n#define XFORM_WARPS " << xform_warps << "\n";
   os << "#define B_GATHER " << (g.b_implicit ? 1 : 0) << "\n#define GATHER_WARPS " << gather_warps << "\n#define GATHER_GROUPS " << gather_groups << "\n";
@@ -756,19 +826,23 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
   plan.tc_sk_counter_bytes = streamk ? sk_counter_bytes : 0;
   Stage st;
   st.entry = "jx_gemm";
-  st.grid[0] = streamk ? (unsigned)opt.sm_count : (unsigned)std::min<int64_t>(tiles, opt.sm_count);
+  st.grid[0] = streamk ? (unsigned)opt.sm_count
+               : pair  ? (unsigned)std::min<int64_t>(2 * tiles, opt.sm_count & ~1)
+                       : (unsigned)std::min<int64_t>(tiles, opt.sm_count);
+  st.cluster = pair ? 2 : 1;
+  plan.tc_pair = pair;
   st.block[0] = 192 + 32 * (gather_warps + xform_warps);
   st.smem = (unsigned)(stages * stage_bytes + 1024 + (3 * stages + 4) * 8 + 16);
   plan.stages.push_back(st);
   plan.describe = std::string("gemm-tcgen05 ") + (kind == 1 ? "f16" : "3xtf32") + " " + std::to_string(g.batch) + "x" +
-                  std::to_string(g.M) + "x" + std::to_string(g.N) + "x" + std::to_string(g.K) + " tile 128x" +
+                  std::to_string(g.M) + "x" + std::to_string(g.N) + "x" + std::to_string(g.K) + " tile " + (pair ? "256x" : "128x") +
                   std::to_string(BN) + "x" + std::to_string(bk) + " stages=" + std::to_string(stages) + " A:" +
                   (a_mn ? "MN" : "K") + " B:" + (b_mn ? "MN" : "K") + " ctas=" + std::to_string(st.grid[0]) +
-                  (lo_in_kernel ? " lo-in-kernel" : "") + (streamk ? " split-k" : "");
+                  (pair ? " cta-pairs" : "") + (lo_in_kernel ? " lo-in-kernel" : "") + (streamk ? " split-k" : "");
   return true;
 }
 
-int launch_gemm_tc(void* encode_fn, void* launch_fn, const Plan& plan, const std::vector<CUfunction>& fns,
+int launch_gemm_tc(void* encode_fn, void* launch_fn, void* launch_ex_fn, const Plan& plan, const std::vector<CUfunction>& fns,
                    const std::vector<void*>& inputs, void* out, void* scratch, cudaStream_t stream,
                    int* status_dev, std::string& err, int max_ctas) {
   auto encode = (EncodeTiledFn)encode_fn;
@@ -833,11 +907,12 @@ int launch_gemm_tc(void* encode_fn, void* launch_fn, const Plan& plan, const std
   };
   alignas(64) CUtensorMap tmA, tmA2, tmB, tmB2;
   const int bk = plan.tc_bk;
+  const int b_rows = plan.tc_pair ? plan.tc_bn / 2 : plan.tc_bn;   // columns of B one CTA loads per stage
   const int64_t a_outer = a_mn ? g.sAk : g.sAm, b_outer = b_mn ? g.sBk : g.sBn;
   bool ok = make_map(&tmA, baseA, g.offA, a_mn, g.M, g.K, a_outer, g.sAb, a_mn ? bk : plan.tc_bm) &&
             make_map(&tmA2, baseA2, g.offA, a_mn, g.M, g.K, a_outer, g.sAb, a_mn ? bk : plan.tc_bm) &&
-            (g.b_implicit || (make_map(&tmB, baseB, g.offB, b_mn, g.N, g.K, b_outer, g.sBb, b_mn ? bk : plan.tc_bn) &&
-                              make_map(&tmB2, baseB2, g.offB, b_mn, g.N, g.K, b_outer, g.sBb, b_mn ? bk : plan.tc_bn)));
+            (g.b_implicit || (make_map(&tmB, baseB, g.offB, b_mn, g.N, g.K, b_outer, g.sBb, b_mn ? bk : b_rows) &&
+                              make_map(&tmB2, baseB2, g.offB, b_mn, g.N, g.K, b_outer, g.sBb, b_mn ? bk : b_rows)));
   if (g.b_implicit) { tmB = tmA; tmB2 = tmA; }   // not read: the kernel fills the B stages itself
   if (!ok) { err = "cuTensorMapEncodeTiled rejected a GEMM operand"; return -1; }
   std::vector<void*> ptrs(inputs.begin(), inputs.end());
@@ -854,8 +929,31 @@ int launch_gemm_tc(void* encode_fn, void* launch_fn, const Plan& plan, const std
     }
   }
   const Stage& st = plan.stages.back();
-  const unsigned grid = max_ctas > 0 ? std::min<unsigned>(st.grid[0], (unsigned)max_ctas) : st.grid[0];
-  CUresult r = launch(fns.back(), grid, 1, 1, st.block[0], 1, 1, st.smem, (CUstream)stream, args.data(), nullptr);
+  unsigned grid = max_ctas > 0 ? std::min<unsigned>(st.grid[0], (unsigned)max_ctas) : st.grid[0];
+  CUresult r;
+  if (st.cluster > 1) {
+    typedef CUresult (*LaunchExFn)(const CUlaunchConfig*, CUfunction, void**, void**);
+    auto launch_ex = (LaunchExFn)launch_ex_fn;
+    if (!launch_ex) { err = "cuLaunchKernelEx is unavailable"; return -1; }
+    grid = std::max(st.cluster, grid / st.cluster * st.cluster);
+    CUlaunchAttribute attr;
+    memset(&attr, 0, sizeof attr);
+    attr.id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
+    attr.value.clusterDim.x = st.cluster;
+    attr.value.clusterDim.y = 1;
+    attr.value.clusterDim.z = 1;
+    CUlaunchConfig cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDimX = grid; cfg.gridDimY = 1; cfg.gridDimZ = 1;
+    cfg.blockDimX = st.block[0]; cfg.blockDimY = 1; cfg.blockDimZ = 1;
+    cfg.sharedMemBytes = st.smem;
+    cfg.hStream = (CUstream)stream;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    r = launch_ex(&cfg, fns.back(), args.data(), nullptr);
+  } else {
+    r = launch(fns.back(), grid, 1, 1, st.block[0], 1, 1, st.smem, (CUstream)stream, args.data(), nullptr);
+  }
   if (r != CUDA_SUCCESS) { err = "launch of the tcgen05 GEMM kernel failed"; return -1; }
   launches++;
   return launches;

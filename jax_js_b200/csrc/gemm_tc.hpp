@@ -14,8 +14,8 @@ namespace jaxcuda {
 // Launches the stages of a SK_GEMM_TC plan.  Returns the number of kernels launched, or -1
 // with `err` set.  `status_dev` is a device-visible word the kernel writes a code to when a
 // pipeline wait times out (0 = healthy).  `max_ctas` > 0 caps the persistent grid (the tile loop strides by
-// the grid size, so any grid is correct): used to leave SMs to a collective running beside the GEMM.  `encode_fn` is cuTensorMapEncodeTiled, `launch_fn` cuLaunchKernel.
-int launch_gemm_tc(void* encode_fn, void* launch_fn, const Plan& plan, const std::vector<CUfunction>& fns,
+// the grid size, so any grid is correct): used to leave SMs to a collective running beside the GEMM.  `encode_fn` is cuTensorMapEncodeTiled, `launch_fn` cuLaunchKernel, `launch_ex_fn` cuLaunchKernelEx (cluster launch of the paired kernel).
+int launch_gemm_tc(void* encode_fn, void* launch_fn, void* launch_ex_fn, const Plan& plan, const std::vector<CUfunction>& fns,
                    const std::vector<void*>& inputs, void* out, void* scratch, cudaStream_t stream,
                    int* status_dev, std::string& err, int max_ctas = 0);
 

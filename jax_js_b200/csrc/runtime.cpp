@@ -49,6 +49,7 @@ struct Driver {
   CUresult (*ModuleGetFunction)(CUfunction*, CUmodule, const char*) = nullptr;
   CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned,
                            CUstream, void**, void**) = nullptr;
+  CUresult (*LaunchKernelEx)(const CUlaunchConfig*, CUfunction, void**, void**) = nullptr;   // optional: cluster launches
   CUresult (*FuncSetAttribute)(CUfunction, CUfunction_attribute, int) = nullptr;
   CUresult (*GetErrorString)(CUresult, const char**) = nullptr;
   void* TensorMapEncodeTiled = nullptr;
@@ -72,6 +73,13 @@ bool load_driver(Driver& d, std::string& err) {
   if (!get("cuFuncSetAttribute", (void**)&d.FuncSetAttribute)) return false;
   if (!get("cuGetErrorString", (void**)&d.GetErrorString)) return false;
   if (!get("cuTensorMapEncodeTiled", &d.TensorMapEncodeTiled)) return false;
+  {
+    std::string ignored;
+    cudaDriverEntryPointQueryResult q;
+    void* fn = nullptr;
+    if (cudaGetDriverEntryPoint("cuLaunchKernelEx", &fn, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      d.LaunchKernelEx = (CUresult (*)(const CUlaunchConfig*, CUfunction, void**, void**))fn;
+  }
   d.loaded = true;
   return true;
 }
@@ -433,6 +441,7 @@ int jaxcuda_create(int device, jaxcuda_ctx** out) {
   ctx->opt.ld_hint = env_int("JAXCUDA_LD_HINT", ctx->opt.ld_hint);
   ctx->opt.conv_implicit = env_int("JAXCUDA_CONV_IMPLICIT", ctx->opt.conv_implicit);
   ctx->opt.tc_lo_in_kernel = env_int("JAXCUDA_TC_LO_IN_KERNEL", ctx->opt.tc_lo_in_kernel);
+  ctx->opt.tc_pair = ctx->drv.LaunchKernelEx ? env_int("JAXCUDA_TC_PAIR", ctx->opt.tc_pair) : 0;
   ctx->opt.row_tpr = env_int("JAXCUDA_ROW_TPR", ctx->opt.row_tpr);
   ctx->opt.row_unroll = env_int("JAXCUDA_ROW_UNROLL", ctx->opt.row_unroll);
   ctx->opt.col_threads = env_int("JAXCUDA_COL_THREADS", ctx->opt.col_threads);
@@ -1120,7 +1129,7 @@ static int launch_kernel(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const std::vector<v
   int rc = JAXCUDA_OK;
   if (exe->plan.skeleton == SK_GEMM_TC) {
     std::string err;
-    int nl = launch_gemm_tc(ctx->drv.TensorMapEncodeTiled, (void*)ctx->drv.LaunchKernel, exe->plan, exe->fns, inptr,
+    int nl = launch_gemm_tc(ctx->drv.TensorMapEncodeTiled, (void*)ctx->drv.LaunchKernel, (void*)ctx->drv.LaunchKernelEx, exe->plan, exe->fns, inptr,
                             outptr, scratch, ctx->stream, ctx->status_dev, err,
                             // a persistent GEMM that holds every SM would keep a sum begun on the second
                             // stream waiting until it ends; leave that sum a few SMs while one is in flight

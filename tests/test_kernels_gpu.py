@@ -427,6 +427,46 @@ def test_remainder_tiles_made_in_the_kernel_match_the_split_pass(backend):
     assert_close(got["2"].reshape(m, n) / kk, want / kk, 1e-5, 1.0, "3xTF32 with in-kernel remainder tiles")
 
 
+@pytest.mark.parametrize("m,n,kk,dt,layout", [
+    (2304, 2304, 192, F16, "mk-kn"),     # 9 x 9 tiles of 256 x 256 on 74 pairs: two waves, the second ragged
+    (2200, 2120, 200, F16, "mk-kn"),     # M, N and K tails: the odd CTA of the last pair row holds 24 valid rows
+    (2304, 2304, 160, F16, "km-nk"),     # A read as [K, M], B as [N, K]
+    (4864, 1100, 96, F32, "mk-kn")])     # 3xTF32 pairs on 256 x 128 tiles, 19 x 9 of them
+def test_gemm_on_cta_pairs_matches_single_ctas(backend, m, n, kk, dt, layout):
+    """Two CTAs of a cluster on one 256-row tile (tcgen05 cta_group::2, each CTA loading half of B's
+    columns): every output accumulates the same products in the same order as on single CTAs, so the
+    bits agree; and both agree with float64 within the GEMM tolerance."""
+    import os
+    from jax_js_b200.backend import CudaBackend
+    rng = np.random.default_rng(m + kk)
+    npdt = np.float32 if dt == F32 else np.float16
+    a = (rng.standard_normal((m, kk)) * 0.5).astype(npdt)
+    b = (rng.standard_normal((kk, n)) * 0.5).astype(npdt)
+    a_t, b_t = layout.split("-")
+    k = P.dot_kernel(m, n, kk, dt, a_layout=a_t, b_layout=b_t)
+    args = [a if a_t == "mk" else np.ascontiguousarray(a.T), b if b_t == "kn" else np.ascontiguousarray(b.T)]
+    got = {}
+    for mode in ("0", "2"):
+        old = os.environ.get("JAXCUDA_TC_PAIR")
+        os.environ["JAXCUDA_TC_PAIR"] = mode
+        try:
+            other = CudaBackend(backend.device)
+        finally:
+            if old is None:
+                os.environ.pop("JAXCUDA_TC_PAIR")
+            else:
+                os.environ["JAXCUDA_TC_PAIR"] = old
+        try:
+            assert ("cta-pairs" in other.prepare_kernel(k).describe) == (mode == "2"), other.prepare_kernel(k).describe
+            for _ in range(3):
+                got[mode] = run_cuda(other, k, args)
+        finally:
+            other.close()
+    assert np.array_equal(got["0"].view(np.uint8), got["2"].view(np.uint8))
+    want = a.astype(np.float64) @ b.astype(np.float64)
+    assert_close(got["2"].astype(np.float64).reshape(m, n) / kk, want / kk, 1e-5 if dt == F32 else 2e-3, 0.25, "GEMM on CTA pairs")
+
+
 def test_max_pool_kernel(backend):
     """`jitRules[Pool]` then a Max reduction: 2 x 2 windows, stride 2, over [N, C, H, W]."""
     N, C, H, W = 3, 5, 16, 20
