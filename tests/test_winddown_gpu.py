@@ -54,3 +54,43 @@ def test_a_stage_that_never_arrives_is_reported_and_the_context_survives(backend
     got = run_cuda(backend, k, [a, b]).astype(np.float64)
     want = oracle.run_kernel(k, [a, b], fma=True).astype(np.float64)
     assert_close(got / 512, want / 512, 2e-3, 0.1 * 0.1 * 9, "gemm after the wind-down")
+
+
+def test_a_missing_stage_winds_down_a_cta_pair_too(backend):
+    """The same on the paired kernel (two CTAs of a cluster on one tile): the even CTA's MMA role gives
+    up on the stage that was announced and never loaded, both CTAs of every pair leave their loops,
+    meet at the cluster barrier and free their tensor memory; the error names the role and the next
+    GEMM on the ordinary context is correct."""
+    m = n = 2304
+    kk = 192
+    rng = np.random.default_rng(1)
+    a = (rng.standard_normal((m, kk)) * 0.1).astype(np.float16)
+    b = (rng.standard_normal((kk, n)) * 0.1).astype(np.float16)
+    k = P.dot_kernel(m, n, kk, DType.Float16)
+    env = {"JAXCUDA_TC_FAULT": "1", "JAXCUDA_TC_SPIN_LIMIT": "4096", "JAXCUDA_TC_PAIR": "2"}
+    old = {key: os.environ.get(key) for key in env}
+    os.environ.update(env)
+    try:
+        faulty = CudaBackend(backend.device)
+    finally:
+        for key, v in old.items():
+            if v is None:
+                os.environ.pop(key, None)
+            else:
+                os.environ[key] = v
+    try:
+        assert "cta-pairs" in faulty.prepare_kernel(k).describe
+        sa, sb, sc = faulty.put(a), faulty.put(b), faulty.malloc(k.bytes)
+        faulty.dispatch(faulty.prepare_kernel(k), [sa, sb], [sc])
+        with pytest.raises(CudaError, match=r"pipeline wait timed out \(role [1-4]"):
+            faulty.read_sync(sc)
+        x = rng.standard_normal(4096).astype(np.float32)
+        sx = faulty.put(x)
+        assert np.array_equal(faulty.read_sync(sx).view(np.float32), x)
+        for s_ in (sa, sb, sc, sx):
+            faulty.dec_ref(s_)
+    finally:
+        faulty.close()
+    got = run_cuda(backend, k, [a, b]).astype(np.float64).reshape(m, n)
+    want = a.astype(np.float64) @ b.astype(np.float64)
+    assert_close(got / kk, want / kk, 2e-3, 0.01, "gemm after the wind-down of a pair")
