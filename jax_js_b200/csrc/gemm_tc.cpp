@@ -241,8 +241,15 @@ __device__ __forceinline__ void jx_gather_tile(JX_PARAMS, u32 sb, int b, int n_t
 // memory, half the TMA traffic.
 #define TMA_PLANES (LO_IN_KERNEL ? 1 : NPLANES)
 #define TX_BYTES (B_GATHER ? TMA_PLANES * A_BYTES : TMA_PLANES * (A_BYTES + B_BYTES))
-#define NTHREADS (192 + 32 * (GATHER_WARPS + XFORM_WARPS))
+// EPI_SPLIT groups of four epilogue warps share a tile's columns (2 for the 256-column 3xTF32 pairs,
+// whose partial sums would not fit one thread's registers); they sit behind warps 0 and 1, and the
+// gather and remainder-tile warps, which never coexist with a second group, behind the first group.
+#define EPI_COLS (BN / EPI_SPLIT)
+#define NTHREADS (64 + 128 * EPI_SPLIT + 32 * (GATHER_WARPS + XFORM_WARPS))
 #define GROUP_WARPS (GATHER_WARPS / GATHER_GROUPS)
+#if EPI_SPLIT > 1 && (STREAMK || B_GATHER || LO_IN_KERNEL)
+#error "a second group of epilogue warps takes the place of the gather and remainder-tile warps"
+#endif
 #if CTA_PAIR && (STREAMK || B_GATHER || LO_IN_KERNEL)
 #error "CTA pairs run whole tiles with TMA-loaded operands only"
 #endif
@@ -280,7 +287,7 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
       mbar_init(empty(s), 1);
       if (LO_IN_KERNEL) mbar_init(raw(s), 1);
     }
-    for (int a = 0; a < 2; a++) { mbar_init(tfull(a), 1); mbar_init(tempty(a), CTA_PAIR ? 8 : 4); }
+    for (int a = 0; a < 2; a++) { mbar_init(tfull(a), 1); mbar_init(tempty(a), 4 * EPI_SPLIT * (CTA_PAIR ? 2 : 1)); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -458,6 +465,7 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
   } else {
     // ---------------------------------------------------------------- epilogue warps 2..5
     const int q = warp & 3;                 // TMEM lane quarter this warp may access
+    const int cg0 = ((warp - 2) / 4) * (EPI_COLS / 16);   // first 16-column group of this warp's share of the tile
     int cc = 0;
     Seg sg;
     for (int si = 0; !failed && get_segment(si, sg); si++) {
@@ -493,18 +501,18 @@ JX_EPILOGUE
       };
       const int nch = (sg.kb1 - sg.kb0 + CHUNK_KB - 1) / CHUNK_KB;
 #if NCHUNK > 1
-      float sum[BN];
+      float sum[EPI_COLS];
       #pragma unroll
-      for (int j = 0; j < BN; j++) sum[j] = 0.0f;
+      for (int j = 0; j < EPI_COLS; j++) sum[j] = 0.0f;
       for (int ch = 0; ch < nch - 1 && !failed; ch++, cc++) {
         const int acc_i = cc & 1;
         if (!mbar_wait(tfull(acc_i), (cc >> 1) & 1, status)) { atomicCAS((int*)status_ptr, 0, 4); failed = true; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const u32 trow = tmem_base + ((u32)(q * 32) << 16) + acc_i * ACC_STRIDE;
         #pragma unroll
-        for (int c = 0; c < BN / 16; c++) {
+        for (int c = 0; c < EPI_COLS / 16; c++) {
           u32 v[16];
-          tmem_ld16(trow + c * 16, v);
+          tmem_ld16(trow + (cg0 + c) * 16, v);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
           #pragma unroll
           for (int j = 0; j < 16; j++) sum[c * 16 + j] += __uint_as_float(v[j]);
@@ -526,9 +534,9 @@ JX_EPILOGUE
 #else
       #pragma unroll 1
 #endif
-      for (int c = 0; c < BN / 16; c++) {
+      for (int c = 0; c < EPI_COLS / 16; c++) {
         u32 v[16];
-        tmem_ld16(trow + c * 16, v);
+        tmem_ld16(trow + (cg0 + c) * 16, v);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         float accv[16];
         #pragma unroll
@@ -540,7 +548,7 @@ JX_EPILOGUE
 #endif
         }
         if (!sg.partial) {
-          finish16(c, accv);
+          finish16(cg0 + c, accv);
         } else {
           #pragma unroll
           for (int j = 0; j < 16; j += 4)
@@ -682,6 +690,14 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
     if (cand <= g.N && (tiles >= (int64_t)opt.sm_count * 3 / 4 || cand == 64)) { BN = cand; break; }
   }
   if (BN > g.N) BN = 64;
+  // 3xTF32 on CTA pairs takes 256 columns after all: a CTA then holds half of B's columns per stage
+  // (64 KB a stage, three stages), and two groups of epilogue warps split the columns so that each
+  // thread keeps 128 partial sums.  Per k-block a CTA moves 208 KB through shared memory (TMA writes
+  // plus the MMAs' operand reads, B's half served to both CTAs) for twice the products of a
+  // 128 x 128 tile's 160 KB: that traffic, at 128 bytes a clock, is what bounds this kernel.
+  const bool wide_pairs = kind == 2 && opt.tc_pair != 0 && opt.tc_bn == 0 && !g.b_gathered && g.M >= 2 * BM && g.N >= 256 &&
+                          ((g.M + 2 * BM - 1) / (2 * BM)) * ((g.N + 255) / 256) * g.batch * 2 >= opt.sm_count;
+  if (wide_pairs) BN = 256;
   // A 192-column tile would shorten the static schedule of f16 4096^3 (512 tiles of 256 columns are
   // 3.46 waves of 148 CTAs), but measured slower (124 us against 108): narrower tiles re-read A from
   // shared memory more often per flop, and the MMA pipe is already fed at its limit with 256 columns.
@@ -718,7 +734,9 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
   // stay 128 columns wide per CTA), so by default pairs run f16 GEMMs with at least 32 k-blocks.
   // JAXCUDA_TC_PAIR: 0 never, 2 whenever the shape allows.
   const bool pair = !streamk && !g.b_gathered && g.M >= 2 * BM && BN >= 128 && pair_tiles * 2 >= opt.sm_count &&
-                    (opt.tc_pair == 2 || (opt.tc_pair == 1 && kind == 1 && kb_total >= 32));
+                    (opt.tc_pair == 2 || wide_pairs || (opt.tc_pair == 1 && kind == 1 && kb_total >= 32));
+  const int epi_split = (pair && kind == 2 && BN == 256) ? 2 : 1;
+  if (kind == 2 && BN == 256 && !pair) return false;   // (cannot happen: wide_pairs implies the pair conditions)
   const int stage_bytes = planes * (BM + (pair ? BN / 2 : BN)) * 128;
   int stages = (227 * 1024 - 2048) / stage_bytes;
   stages = std::max(2, std::min(stages, pair ? 8 : 6));
@@ -729,7 +747,7 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
   os << "#define KIND " << kind << "\n#define ELEM " << e << "\n#define BM " << BM << "\n#define BN " << BN << "\n";
   os << "#define ACC_STRIDE " << (BN > 128 ? 256 : BN) << "\n";
   os << "#define A_SHARED " << ((g.batch > 1 && g.sAb == 0) ? 1 : 0) << "\n#define B_SHARED " << ((g.batch > 1 && g.sBb == 0) ? 1 : 0) << "\n";
-  os << "#define STREAMK " << (streamk ? 1 : 0) << "\n#define CTA_PAIR " << (pair ? 1 : 0) << "\n";
+  os << "#define STREAMK " << (streamk ? 1 : 0) << "\n#define CTA_PAIR " << (pair ? 1 : 0) << "\n#define EPI_SPLIT " << epi_split << "\n";
   os << "#define SPIN_LIMIT " << std::max(1024, opt.tc_spin_limit) << "\n#define FAULT_SKIP_LOAD " << (opt.tc_fault == 1 ? 1 : 0) << "\n";
   // Gather warps of a convolution (B_GATHER): groups of four warps, each group filling every
   // gather_groups-th stage.  Never more groups than stages: a group waits for "stage free" by phase
@@ -831,7 +849,7 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
                        : (unsigned)std::min<int64_t>(tiles, opt.sm_count);
   st.cluster = pair ? 2 : 1;
   plan.tc_pair = pair;
-  st.block[0] = 192 + 32 * (gather_warps + xform_warps);
+  st.block[0] = 64 + 128 * epi_split + 32 * (gather_warps + xform_warps);
   st.smem = (unsigned)(stages * stage_bytes + 1024 + (3 * stages + 4) * 8 + 16);
   plan.stages.push_back(st);
   plan.describe = std::string("gemm-tcgen05 ") + (kind == 1 ? "f16" : "3xtf32") + " " + std::to_string(g.batch) + "x" +
