@@ -696,7 +696,7 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
   // plus the MMAs' operand reads, B's half served to both CTAs) for twice the products of a
   // 128 x 128 tile's 160 KB: that traffic, at 128 bytes a clock, is what bounds this kernel.
   const bool wide_pairs = kind == 2 && opt.tc_pair != 0 && opt.tc_bn == 0 && !g.b_gathered && g.M >= 2 * BM && g.N >= 256 &&
-                          ((g.M + 2 * BM - 1) / (2 * BM)) * ((g.N + 255) / 256) * g.batch * 2 >= opt.sm_count;
+                          ((g.M + 2 * BM - 1) / (2 * BM)) * ((g.N + 255) / 256) * g.batch * 2 >= opt.sm_count * 3 / 4;   // 1.5 times the work per byte is worth a quarter of the SMs idle
   if (wide_pairs) BN = 256;
   // A 192-column tile would shorten the static schedule of f16 4096^3 (512 tiles of 256 columns are
   // 3.46 waves of 148 CTAs), but measured slower (124 us against 108): narrower tiles re-read A from
@@ -733,7 +733,7 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
   // set-up costs more than it saves (23.0 -> 24.5 us), and 3xTF32 neither gains nor loses (its tiles
   // stay 128 columns wide per CTA), so by default pairs run f16 GEMMs with at least 32 k-blocks.
   // JAXCUDA_TC_PAIR: 0 never, 2 whenever the shape allows.
-  const bool pair = !streamk && !g.b_gathered && g.M >= 2 * BM && BN >= 128 && pair_tiles * 2 >= opt.sm_count &&
+  const bool pair = !streamk && !g.b_gathered && g.M >= 2 * BM && BN >= 128 && (wide_pairs || pair_tiles * 2 >= opt.sm_count) &&
                     (opt.tc_pair == 2 || wide_pairs || (opt.tc_pair == 1 && kind == 1 && kb_total >= 32));
   const int epi_split = (pair && kind == 2 && BN == 256) ? 2 : 1;
   if (kind == 2 && BN == 256 && !pair) return false;   // (cannot happen: wide_pairs implies the pair conditions)
@@ -761,10 +761,11 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
   // Remainder tiles made in the kernel save the split pass (a launch and a round trip of both
   // operands through global memory) but add a read and a write of every stage to the shared-memory
   // traffic that already bounds the 3xTF32 main loop.  Measured: 1024^3 (one wave of tiles) 30.1 ->
-  // 27.2 us, 8192 x 2048 x 2048 320 -> 339 us, the convolution 131 -> 149 us.  So: outputs of at most
-  // one wave of tiles only (JAXCUDA_TC_LO_IN_KERNEL = 0 never, 2 always).
+  // 27.2 us, 8192 x 2048 x 2048 320 -> 339 us, the convolution 131 -> 149 us, one wave of tiles over a long K
+  // (784 x 2048 x 65536) 1427 -> 1501 us.  So: outputs of at most one wave of tiles and at most 64
+  // k-blocks (JAXCUDA_TC_LO_IN_KERNEL = 0 never, 2 always).
   const bool lo_in_kernel = kind == 2 && !(g.b_gathered && !g.b_implicit) &&
-                            !pair && (opt.tc_lo_in_kernel == 2 || (opt.tc_lo_in_kernel == 1 && !g.b_gathered && tiles <= opt.sm_count));
+                            !pair && (opt.tc_lo_in_kernel == 2 || (opt.tc_lo_in_kernel == 1 && !g.b_gathered && tiles <= opt.sm_count && kb_total <= 64));
   const int xform_warps = lo_in_kernel ? 4 : 0;
   os << "#define LO_IN_KERNEL " << (lo_in_kernel ? 1 : 0) << "\n#define XFORM_WARPS " << xform_warps << "\n";
   os << "#define B_GATHER " << (g.b_implicit ? 1 : 0) << "\n#define GATHER_WARPS " << gather_warps << "\n#define GATHER_GROUPS " << gather_groups << "\n";
