@@ -174,7 +174,9 @@ uint64_t jaxcuda_launch_count(jaxcuda_ctx* ctx);
  * into that Kernel: the consumer evaluates the producer's expression at the index of its load and
  * the intermediate array is never written (a vmapped gradient's per-example products, which
  * arrive batch-last followed by the Kernel that moves the batch axis first,
- * src/frontend/vmap.ts:297-303).  Same operations on the same values: same bits.
+ * src/frontend/vmap.ts:297-303); and an elementwise Kernel that reads a tensor-core GEMM's output at
+ * gidx, as its only reader, runs as the tail of that GEMM's epilogue.  Same operations on the same
+ * values: same bits.
  * JAXCUDA_FUSE=0 in the environment turns both replacements off. */
 int jaxcuda_capture_begin(jaxcuda_ctx* ctx);
 int jaxcuda_capture_end(jaxcuda_ctx* ctx, jaxcuda_graph** out);

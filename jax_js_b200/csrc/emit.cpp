@@ -1691,6 +1691,41 @@ bool compose_elementwise(const KernelIR& a_in, const KernelIR& b, uint32_t b_arg
   return true;
 }
 
+bool compose_epilogue(const KernelIR& a, const KernelIR& b, uint32_t b_arg, KernelIR& out, std::string& why) {
+  if (!a.has_red || a.epi.empty() || a.red_size < 2) { why = "the producer does not reduce"; return false; }
+  if (b.has_red || b.exp.empty() || b.size != a.size || b_arg >= b.nargs) { why = "the consumer is no elementwise Kernel over the same outputs"; return false; }
+  const uint32_t a_dt = a.epi.back().dtype;
+  if (dtype_bytes(a_dt) != 4) { why = "the producer's output is not a 4-byte type"; return false; }
+  if (a.nargs + b.nargs - 1 > 64) { why = "too many arguments"; return false; }
+  int loads = 0;
+  size_t load_at = 0;
+  for (size_t i = 0; i < b.exp.size(); i++)
+    if (b.exp[i].op == JAXCUDA_OP_GLOBALINDEX && b.exp[i].arg0 == b_arg) { loads++; load_at = i; }
+  if (loads != 1) { why = "the consumer loads the array more than once"; return false; }
+  const Node& ld = b.exp[load_at];
+  if (ld.dtype != a_dt || ld.arg1 != a.size) { why = "the load does not see the whole output in its own type"; return false; }
+  const Analysis an = analyze(b.exp, b.size, 1);
+  const std::optional<Affine>& ix = an.affine[ld.src[0]];
+  if (!ix || ix->c0 != 0 || ix->terms.size() != 1 || ix->terms[0].var != 0 || ix->terms[0].div != 1 || ix->terms[0].mod != 0 ||
+      ix->terms[0].coef != 1) { why = "the consumer does not read the output at gidx"; return false; }
+  for (const Node& nd : b.exp)
+    if (nd.op == JAXCUDA_OP_SPECIAL && nd.arg0 != 0) { why = "the consumer reads ridx"; return false; }
+  out = a;
+  out.nargs = a.nargs + b.nargs - 1;
+  const uint32_t a_root = (uint32_t)out.epi.size() - 1;
+  std::vector<uint32_t> bmap(b.exp.size(), 0);
+  for (size_t i = 0; i < b.exp.size(); i++) {
+    if (i == load_at) { bmap[i] = a_root; continue; }
+    Node c = b.exp[i];
+    for (uint32_t sidx = 0; sidx < c.nsrc; sidx++) c.src[sidx] = bmap[b.exp[i].src[sidx]];
+    if (c.op == JAXCUDA_OP_GLOBALINDEX) c.arg0 = a.nargs + (c.arg0 < b_arg ? c.arg0 : c.arg0 - 1);
+    out.epi.push_back(c);
+    bmap[i] = (uint32_t)out.epi.size() - 1;
+  }
+  if (bmap.back() != out.epi.size() - 1) out.epi.push_back(out.epi[bmap.back()]);   // the root comes last
+  return true;
+}
+
 Plan make_plan(const KernelIR& k, const Options& opt) {
   if (k.has_red && k.red_size == 1 && opt.force_skeleton < 0 && !k.exp.empty() && !k.epi.empty()) {
     const KernelIR folded = fold_unit_reduction(k);

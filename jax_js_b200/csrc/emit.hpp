@@ -143,6 +143,12 @@ bool plan_row_fusion(const std::vector<FuseStage>& stages, const std::vector<Fus
 // reduction put there.  Arguments of the result: B's without `b_arg`, then A's.
 bool compose_elementwise(const KernelIR& a, const KernelIR& b, uint32_t b_arg, KernelIR& out, std::string& why);
 
+// The mirror case: A reduces (a Dot), B is elementwise over the same index space and loads A's
+// output at gidx itself; then B's expression becomes the tail of A's epilogue (the back-propagated
+// cotangent t = dz W^T masked by the ReLU gate: the GEMM writes the masked product and t is never
+// stored).  Arguments of the result: A's, then B's without `b_arg`.
+bool compose_epilogue(const KernelIR& a, const KernelIR& b, uint32_t b_arg, KernelIR& out, std::string& why);
+
 // Implemented in gemm_tc.cpp: rewrites `plan` to the tcgen05 skeleton when `g` qualifies.
 // `gather_source` (with g.b_gathered) is the CUDA C of the kernel `jx_gather_b` that fills the B
 // operand; it is compiled with the GEMM and launched first.

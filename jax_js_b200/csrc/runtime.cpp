@@ -1090,7 +1090,7 @@ int jaxcuda_dispatch(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const jaxcuda_slot* inp
   if (k.size == 0) return JAXCUDA_OK;
   std::vector<void*> inptr(n_inputs);
   for (int i = 0; i < n_inputs; i++) inptr[i] = in[i]->ptr;
-  if (ctx->alloc.capturing && ctx->fuse_rows && exe->plan.skeleton != SK_GEMM_TC) {
+  if (ctx->alloc.capturing && ctx->fuse_rows) {
     if (exe->plan.scratch_bytes && exe->plan.scratch_persistent && !exe->persistent_scratch)
       return fail(ctx, JAXCUDA_EINVAL, "dispatch the program once before capturing it: a kernel still has to set up its arrival counters");
     PendingDispatch pd;
@@ -1291,7 +1291,7 @@ static size_t launch_row_group(jaxcuda_ctx* ctx, std::vector<PendingDispatch>& l
 // elementwise, and its output is released afterwards: the consumer with the producer's expression
 // in place of its load (emit.hpp: compose_elementwise).  Returns the argument of the consumer that
 // is replaced, or -1.
-static int composable_pair(const std::vector<PendingDispatch>& list, size_t i, KernelIR& composed) {
+static int composable_pair(const std::vector<PendingDispatch>& list, size_t i, KernelIR& composed, bool& epilogue) {
   if (i + 1 >= list.size()) return -1;
   const PendingDispatch& a = list[i];
   const PendingDispatch& b = list[i + 1];
@@ -1304,21 +1304,30 @@ static int composable_pair(const std::vector<PendingDispatch>& list, size_t i, K
     for (void* p : list[r].in) if (p == a.out) return -1;
   for (void* p : a.in) if (p == b.out) return -1;                  // the consumer's output replaces one of the producer's inputs
   std::string why;
-  if (!compose_elementwise(a.exe->ir, b.exe->ir, (uint32_t)b_arg, composed, why)) return -1;
-  return b_arg;
+  if (compose_elementwise(a.exe->ir, b.exe->ir, (uint32_t)b_arg, composed, why)) { epilogue = false; return b_arg; }
+  // a tensor-core GEMM takes an elementwise consumer of its own outputs into its epilogue
+  if (a.exe->plan.skeleton == SK_GEMM_TC && compose_epilogue(a.exe->ir, b.exe->ir, (uint32_t)b_arg, composed, why)) {
+    epilogue = true;
+    return b_arg;
+  }
+  return -1;
 }
 
-static std::vector<void*> composed_inputs(const PendingDispatch& a, const PendingDispatch& b, int b_arg) {
+// arguments of the composed Kernel: the consumer's without the replaced one, then the producer's
+// (the other way round when the consumer went into the producer's epilogue)
+static std::vector<void*> composed_inputs(const PendingDispatch& a, const PendingDispatch& b, int b_arg, bool epilogue) {
   std::vector<void*> in;
+  if (epilogue) for (void* p : a.in) in.push_back(p);
   for (size_t k = 0; k < b.in.size(); k++) if ((int)k != b_arg) in.push_back(b.in[k]);
-  for (void* p : a.in) in.push_back(p);
+  if (!epilogue) for (void* p : a.in) in.push_back(p);
   return in;
 }
 
 // Launches list[i] and list[i + 1] as one Kernel where that is possible; returns i + 2 then, else i.
 static size_t launch_composed_pair(jaxcuda_ctx* ctx, std::vector<PendingDispatch>& list, size_t i) {
   KernelIR composed;
-  const int b_arg = composable_pair(list, i, composed);
+  bool epilogue = false;
+  const int b_arg = composable_pair(list, i, composed, epilogue);
   if (b_arg < 0) return i;
   std::ostringstream key;
   key << "compose:" << std::hex << list[i].exe->hash << ">" << list[i + 1].exe->hash << "@" << b_arg;
@@ -1332,10 +1341,10 @@ static size_t launch_composed_pair(jaxcuda_ctx* ctx, std::vector<PendingDispatch
     bool ok = false;
     try {
       exe->plan = make_plan(exe->ir, ctx->opt);
-      ok = true;
+      ok = !epilogue || exe->plan.skeleton == SK_GEMM_TC;   // the longer epilogue must not cost the GEMM its skeleton
     } catch (const std::exception&) {}
     if (ok) {
-      exe->describe = exe->plan.describe + " (producer substituted)";
+      exe->describe = exe->plan.describe + (epilogue ? " (consumer in the epilogue)" : " (producer substituted)");
       if (ctx->debug >= 4) fprintf(stderr, "[jaxcuda] %s\n", exe->describe.c_str());
       if (ctx->debug >= 2) fprintf(stderr, "%s\n", exe->plan.source.c_str());
       if (compile_plan(ctx, exe.get()) != JAXCUDA_OK) { free_exe(ctx, exe.get()); ok = false; }
@@ -1345,7 +1354,7 @@ static size_t launch_composed_pair(jaxcuda_ctx* ctx, std::vector<PendingDispatch
     ctx->fused[key.str()] = std::move(exe);
   }
   if (!fx) return i;
-  if (launch_kernel(ctx, fx, composed_inputs(list[i], list[i + 1], b_arg), list[i + 1].out) != JAXCUDA_OK) return i;
+  if (launch_kernel(ctx, fx, composed_inputs(list[i], list[i + 1], b_arg, epilogue), list[i + 1].out) != JAXCUDA_OK) return i;
   ctx->capture_groups++;
   return i + 2;
 }
@@ -1385,6 +1394,7 @@ int jaxcuda_check_step_list(int n, const uint8_t* const* irs, const size_t* lens
     std::string err = parse_kernel(irs[i], lens[i], exe->ir);
     if (!err.empty()) { put(message, message_len, err); return JAXCUDA_EINVAL; }
     exe->hash = fnv1a(irs[i], lens[i]);
+    try { exe->plan = make_plan(exe->ir, opt); } catch (const std::exception&) {}   // reported (or refused) per Kernel below
     PendingDispatch pd;
     pd.exe = exe.get();
     // the diagnostic has no buffers: array ids stand in for addresses, sizes are taken as sufficient
@@ -1421,15 +1431,17 @@ int jaxcuda_check_step_list(int n, const uint8_t* const* irs, const size_t* lens
     if (done) { i = done; continue; }
     {
       KernelIR composed;
-      if (composable_pair(list, i, composed) >= 0) {
+      bool epilogue = false;
+      if (composable_pair(list, i, composed, epilogue) >= 0) {
         try {
           Plan plan = make_plan(composed, opt);
+          if (epilogue && plan.skeleton != SK_GEMM_TC) throw std::runtime_error("skeleton lost");
           if (compile) {
             std::vector<char> cubin;
             std::string err;
             if (!nvrtc_compile(plan.source, cubin, err)) { put(message, message_len, err); return JAXCUDA_ECOMPILE; }
           }
-          rep << i << "-" << i + 1 << ": " << plan.describe << " (producer substituted) bytes=" << (long long)plan.algo_bytes << "\n";
+          rep << i << "-" << i + 1 << ": " << plan.describe << (epilogue ? " (consumer in the epilogue)" : " (producer substituted)") << " bytes=" << (long long)plan.algo_bytes << "\n";
           src << plan.source << "\n";
           i += 2;
           continue;
