@@ -1305,8 +1305,9 @@ static int composable_pair(const std::vector<PendingDispatch>& list, size_t i, K
   for (void* p : a.in) if (p == b.out) return -1;                  // the consumer's output replaces one of the producer's inputs
   std::string why;
   if (compose_elementwise(a.exe->ir, b.exe->ir, (uint32_t)b_arg, composed, why)) { epilogue = false; return b_arg; }
-  // a tensor-core GEMM takes an elementwise consumer of its own outputs into its epilogue
-  if (a.exe->plan.skeleton == SK_GEMM_TC && compose_epilogue(a.exe->ir, b.exe->ir, (uint32_t)b_arg, composed, why)) {
+  // a GEMM-shaped Kernel takes an elementwise consumer of its own outputs into its epilogue
+  if ((a.exe->plan.skeleton == SK_GEMM_TC || a.exe->plan.skeleton == SK_GEMM_FFMA) &&
+      compose_epilogue(a.exe->ir, b.exe->ir, (uint32_t)b_arg, composed, why)) {
     epilogue = true;
     return b_arg;
   }
@@ -1341,7 +1342,9 @@ static size_t launch_composed_pair(jaxcuda_ctx* ctx, std::vector<PendingDispatch
     bool ok = false;
     try {
       exe->plan = make_plan(exe->ir, ctx->opt);
-      ok = !epilogue || exe->plan.skeleton == SK_GEMM_TC;   // the longer epilogue must not cost the GEMM its skeleton
+      // the longer epilogue must not cost the producer its skeleton
+      auto family = [](const std::string& d) { return d.substr(0, d.find(' ')); };
+      ok = !epilogue || (exe->plan.skeleton == list[i].exe->plan.skeleton && family(exe->plan.describe) == family(list[i].exe->plan.describe));
     } catch (const std::exception&) {}
     if (ok) {
       exe->describe = exe->plan.describe + (epilogue ? " (consumer in the epilogue)" : " (producer substituted)");
@@ -1435,7 +1438,9 @@ int jaxcuda_check_step_list(int n, const uint8_t* const* irs, const size_t* lens
       if (composable_pair(list, i, composed, epilogue) >= 0) {
         try {
           Plan plan = make_plan(composed, opt);
-          if (epilogue && plan.skeleton != SK_GEMM_TC) throw std::runtime_error("skeleton lost");
+          if (epilogue && (plan.skeleton != list[i].exe->plan.skeleton ||
+                           plan.describe.substr(0, plan.describe.find(' ')) != list[i].exe->plan.describe.substr(0, list[i].exe->plan.describe.find(' '))))
+            throw std::runtime_error("skeleton lost");
           if (compile) {
             std::vector<char> cubin;
             std::string err;
