@@ -503,7 +503,8 @@ def _gemm_case(backend, kernel, args, K, tol, dtype, rows=None):
 
 
 @pytest.mark.parametrize("M,N,K,al,bl", [(1024, 1024, 1024, "mk", "kn"), (100, 130, 70, "mk", "kn"),
-                                         (256, 192, 520, "km", "kn"), (192, 256, 136, "mk", "nk"), (130, 100, 64, "km", "nk")])
+                                         (256, 192, 520, "km", "kn"), (192, 256, 136, "mk", "nk"), (130, 100, 64, "km", "nk"),
+                                         (1024, 32, 784, "km", "nk"), (512, 48, 200, "mk", "kn")])   # 32-column tiles (a vmapped batch of 32)
 def test_gemm_f32(backend, M, N, K, al, bl):
     rng = np.random.default_rng(0)
     A = rng.uniform(-1, 1, (M, K) if al == "mk" else (K, M)).astype(np.float32)
