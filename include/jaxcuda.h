@@ -175,8 +175,9 @@ uint64_t jaxcuda_launch_count(jaxcuda_ctx* ctx);
  * the intermediate array is never written (a vmapped gradient's per-example products, which
  * arrive batch-last followed by the Kernel that moves the batch axis first,
  * src/frontend/vmap.ts:297-303); and an elementwise Kernel that reads a tensor-core GEMM's output at
- * gidx, as its only reader, runs as the tail of that GEMM's epilogue.  Same operations on the same
- * values: same bits.
+ * gidx, as its only reader, runs as the tail of that GEMM's epilogue; and a run of three or more
+ * Kernels of at most 16384 element evaluations each is recorded as one single-CTA kernel that
+ * evaluates them in turn.  Same operations on the same values in the same order: same bits.
  * JAXCUDA_FUSE=0 in the environment turns both replacements off. */
 int jaxcuda_capture_begin(jaxcuda_ctx* ctx);
 int jaxcuda_capture_end(jaxcuda_ctx* ctx, jaxcuda_graph** out);

@@ -529,6 +529,27 @@ struct Builder {
     os << indent << dst << " = " << to_storage(out_dt, names.back()) << ";\n";
   }
 
+  // The whole Kernel as a loop nest of one CTA of `threads` threads (a stage of a small batch): expects
+  // the arguments as p0 .. and `out` in scope.
+  void emit_serial(std::ostream& os, int threads, const std::string& indent) const {
+    std::vector<char> all(k.exp.size(), 1);
+    std::vector<std::string> names(k.exp.size());
+    Env env;
+    os << indent << "for (int gidx = threadIdx.x; gidx < " << k.size << "; gidx += " << threads << ") {\n";
+    if (!k.has_red) {
+      emit_nodes(os, k.exp, an_exp, names, all, env, indent + "  ");
+      os << indent << "  out[gidx] = " << to_storage(out_dt, names.back()) << ";\n";
+    } else {
+      const char* AT = ctype(k.red_dtype);
+      os << indent << "  " << AT << " acc = " << identity_literal(k.red_op, k.red_dtype) << ";\n";
+      os << indent << "  for (int ridx = 0; ridx < " << k.red_size << "; ridx++) {\n";
+      emit_nodes(os, k.exp, an_exp, names, all, env, indent + "    ");
+      os << indent << "    acc = " << red("acc", names.back()) << ";\n" << indent << "  }\n";
+      emit_epilogue(os, indent + "  ", "acc", "out[gidx]");
+    }
+    os << indent << "}\n";
+  }
+
   // The Kernel's epilogue for one output: expects `gidx` and the accumulator `acc_name` in scope.
   void emit_epilogue(std::ostream& os, const std::string& indent, const std::string& acc_name, const std::string& dst) const {
     std::vector<std::string> en(k.epi.size());
@@ -1723,6 +1744,44 @@ bool compose_epilogue(const KernelIR& a, const KernelIR& b, uint32_t b_arg, Kern
     bmap[i] = (uint32_t)out.epi.size() - 1;
   }
   if (bmap.back() != out.epi.size() - 1) out.epi.push_back(out.epi[bmap.back()]);   // the root comes last
+  return true;
+}
+
+bool plan_small_batch(const std::vector<BatchStage>& stages, int n_params, const Options& opt, Plan& plan, std::string& why) {
+  if (stages.size() < 2) { why = "nothing to batch"; return false; }
+  const int T = 512;
+  std::ostringstream os;
+  os << "#define JX_EXACT_TRANSCENDENTALS 1\n#define JX_LD_HINT 0\n" << kPrelude;
+  // plain pointers, no __restrict__ and no read-only path: a later stage reads what an earlier one wrote
+  os << "extern \"C\" __global__ void __launch_bounds__(" << T << ") jx_batch(";
+  for (int i = 0; i < n_params; i++) os << (i ? ", " : "") << "void* q" << i;
+  os << ") {\n";
+  plan = Plan();
+  plan.skeleton = SK_ELEMENTWISE;
+  for (size_t s = 0; s < stages.size(); s++) {
+    const KernelIR& k = *stages[s].ir;
+    KernelIR folded;
+    const KernelIR* use = &k;
+    if (k.has_red && k.red_size == 1 && !k.exp.empty() && !k.epi.empty()) { folded = fold_unit_reduction(k); use = &folded; }
+    Builder b(*use, opt);
+    Plan acc;
+    b.account(acc);
+    plan.algo_bytes += acc.algo_bytes;
+    plan.algo_flops += acc.algo_flops;
+    if (s) os << "  __threadfence_block();\n  __syncthreads();\n";
+    os << "  {  // Kernel " << s << "\n";
+    for (uint32_t a = 0; a < use->nargs; a++) os << "    const void* p" << a << " = q" << stages[s].in_param[a] << ";\n";
+    os << "    " << ptype(b.out_dt) << "* out = (" << ptype(b.out_dt) << "*)q" << stages[s].out_param << ";\n";
+    b.emit_serial(os, T, "    ");
+    os << "  }\n";
+  }
+  os << "}\n";
+  plan.source = os.str();
+  Stage st;
+  st.entry = "jx_batch";
+  st.block[0] = T;
+  plan.stages.push_back(st);
+  plan.describe = "batch of " + S((int64_t)stages.size()) + " small kernels, one CTA of " + S(T);
   return true;
 }
 

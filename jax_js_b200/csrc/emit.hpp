@@ -149,6 +149,23 @@ bool compose_elementwise(const KernelIR& a, const KernelIR& b, uint32_t b_arg, K
 // stored).  Arguments of the result: A's, then B's without `b_arg`.
 bool compose_epilogue(const KernelIR& a, const KernelIR& b, uint32_t b_arg, KernelIR& out, std::string& why);
 
+// ---- a run of small Kernels as one launch ------------------------------------------------------
+//
+// A jitted step ends up with many Kernels over a few hundred or thousand elements (the softmax of a
+// [64, 10] logit array is six of them, an Adam step of a bias two): inside a graph each costs its
+// node-to-node latency, about 2 us, whatever it computes.  A run of such Kernels becomes one kernel
+// of a single CTA that evaluates them one after the other, `__syncthreads()` between them, arrays
+// passing through global memory exactly as before (so any Kernel qualifies: reductions are looped
+// per output).  `in_param` / `out_param` index the kernel's pointer parameters.
+struct BatchStage {
+  const KernelIR* ir = nullptr;
+  std::vector<int> in_param;
+  int out_param = -1;
+};
+// work (outputs x reduction length) up to which a Kernel counts as small
+inline double small_kernel_work() { return 16384; }
+bool plan_small_batch(const std::vector<BatchStage>& stages, int n_params, const Options& opt, Plan& plan, std::string& why);
+
 // Implemented in gemm_tc.cpp: rewrites `plan` to the tcgen05 skeleton when `g` qualifies.
 // `gather_source` (with g.b_gathered) is the CUDA C of the kernel `jx_gather_b` that fills the B
 // operand; it is compiled with the GEMM and launched first.

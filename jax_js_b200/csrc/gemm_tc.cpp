@@ -679,6 +679,7 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
   if ((g.offA * e) % 16 || (g.offB * e) % 16 || g.offA < 0 || g.offB < 0) return false;
   if (g.batch > 1 && (!ok16(g.sAb == 0 ? 16 : g.sAb) || !ok16(g.sBb == 0 ? 16 : g.sBb) || g.sAb < 0 || g.sBb < 0)) return false;
   if (g.M < 64 || g.N < 32 || g.K < 32) return false;
+  if (g.N < 64 && (g.M < 256 || kind == 1)) return false;   // 32-column tiles: tall f32 outputs only (an MN-major f16 box is 64 columns wide)
   if ((uint64_t)g.lenA >= (1ull << 31) || (uint64_t)g.lenB >= (1ull << 31)) return false;
 
   const int BM = 128;
@@ -690,7 +691,6 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
     if (cand <= g.N && (tiles >= (int64_t)opt.sm_count * 3 / 4 || cand == 64)) { BN = cand; break; }
   }
   if (BN > g.N) BN = g.N >= 64 ? 64 : 32;   // 32 columns: one 128-byte box of f32, half a box of f16 columns (a vmapped batch of 32)
-  if (BN == 32 && kind == 1) return false;  // an MN-major f16 box is 64 columns wide
   // 3xTF32 on CTA pairs takes 256 columns after all: a CTA then holds half of B's columns per stage
   // (64 KB a stage, three stages), and two groups of epilogue warps split the columns so that each
   // thread keeps 128 partial sums.  Per k-block a CTA moves 208 KB through shared memory (TMA writes

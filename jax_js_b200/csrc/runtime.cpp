@@ -1362,6 +1362,92 @@ static size_t launch_composed_pair(jaxcuda_ctx* ctx, std::vector<PendingDispatch
   return i + 2;
 }
 
+// ---- runs of small Kernels as one launch (emit.hpp: plan_small_batch) ---------------------------
+static bool is_small_kernel(const PendingDispatch& pd) {
+  if (pd.exe->kind != 0) return false;
+  const KernelIR& k = pd.exe->ir;
+  if (k.size == 0 || (double)k.size * (k.has_red ? std::max<uint32_t>(1, k.red_size) : 1) > small_kernel_work() || k.nargs > 16) return false;
+  // A reduction joins only if its own kernel also adds up one output's terms in order in one thread
+  // (the batch does): then a replay keeps the bits of the Kernels one by one.
+  if (k.has_red && k.red_size > 1) {
+    const std::string& d = pd.exe->plan.describe;
+    if (pd.exe->plan.skeleton != SK_REDUCE_COL || d.find(" TY=1 splits=1") == std::string::npos) return false;
+  }
+  return true;
+}
+
+struct SmallBatch {
+  std::vector<BatchStage> stages;
+  std::vector<void*> params;
+  std::string key;
+};
+
+static size_t small_batch_extent(const std::vector<PendingDispatch>& list, size_t i) {
+  size_t end = i;
+  while (end < list.size() && end - i < 24 && is_small_kernel(list[end])) end++;
+  return end - i >= 3 ? end : 0;
+}
+
+static void build_small_batch(const std::vector<PendingDispatch>& list, size_t i, size_t end, SmallBatch& b) {
+  std::unordered_map<void*, int> at;
+  auto param = [&](void* p) {
+    auto it = at.find(p);
+    if (it != at.end()) return it->second;
+    const int n = (int)b.params.size();
+    b.params.push_back(p);
+    at[p] = n;
+    return n;
+  };
+  std::ostringstream key;
+  key << "batch";
+  for (size_t s = i; s < end; s++) {
+    BatchStage st;
+    st.ir = &list[s].exe->ir;
+    key << "|" << std::hex << list[s].exe->hash << ":";
+    for (void* p : list[s].in) { st.in_param.push_back(param(p)); key << st.in_param.back() << ","; }
+    st.out_param = param(list[s].out);
+    key << ">" << st.out_param;
+    b.stages.push_back(st);
+  }
+  b.key = key.str();
+}
+
+static size_t launch_small_batch(jaxcuda_ctx* ctx, std::vector<PendingDispatch>& list, size_t i) {
+  const size_t end = small_batch_extent(list, i);
+  if (!end) return i;
+  SmallBatch b;
+  build_small_batch(list, i, end, b);
+  jaxcuda_exe* fx = nullptr;
+  auto hit = ctx->fused.find(b.key);
+  if (hit != ctx->fused.end()) fx = hit->second.get();
+  else {
+    std::unique_ptr<jaxcuda_exe> exe(new jaxcuda_exe);
+    exe->ctx = ctx;
+    std::string why;
+    bool ok = false;
+    try { ok = plan_small_batch(b.stages, (int)b.params.size(), ctx->opt, exe->plan, why); } catch (const std::exception&) {}
+    if (ok) {
+      exe->describe = exe->plan.describe;
+      if (ctx->debug >= 4) fprintf(stderr, "[jaxcuda] %s\n", exe->describe.c_str());
+      if (ctx->debug >= 2) fprintf(stderr, "%s\n", exe->plan.source.c_str());
+      if (compile_plan(ctx, exe.get()) != JAXCUDA_OK) { free_exe(ctx, exe.get()); ok = false; }
+    }
+    if (!ok) { ctx->fused[b.key] = nullptr; return i; }
+    fx = exe.get();
+    ctx->fused[b.key] = std::move(exe);
+  }
+  if (!fx) return i;
+  std::vector<void*> args(b.params.size());
+  for (size_t a = 0; a < args.size(); a++) args[a] = &b.params[a];
+  const Stage& st = fx->plan.stages[0];
+  CUresult cr = ctx->drv.LaunchKernel(fx->fns[0], 1, 1, 1, st.block[0], 1, 1, 0, (CUstream)ctx->stream, args.data(), nullptr);
+  if (cr != CUDA_SUCCESS) { drv_fail(ctx, "cuLaunchKernel (small batch)", cr); return i; }
+  ctx->launches++;
+  ctx->capture_bytes += fx->plan.algo_bytes;
+  ctx->capture_groups++;
+  return end;
+}
+
 // Launches everything dispatched so far inside the capture, in order.
 static int flush_pending(jaxcuda_ctx* ctx) {
   if (ctx->pending.empty()) return JAXCUDA_OK;
@@ -1371,6 +1457,8 @@ static int flush_pending(jaxcuda_ctx* ctx) {
     size_t next = launch_row_group(ctx, list, i);
     if (next > i) { i = next; continue; }
     next = launch_composed_pair(ctx, list, i);
+    if (next > i) { i = next; continue; }
+    next = launch_small_batch(ctx, list, i);
     if (next > i) { i = next; continue; }
     if (int rc = launch_kernel(ctx, list[i].exe, list[i].in, list[i].out)) return rc;
     i++;
@@ -1451,6 +1539,25 @@ int jaxcuda_check_step_list(int n, const uint8_t* const* irs, const size_t* lens
           i += 2;
           continue;
         } catch (const std::exception&) {}
+      }
+    }
+    if (const size_t bend = small_batch_extent(list, i)) {
+      SmallBatch b;
+      build_small_batch(list, i, bend, b);
+      Plan plan;
+      std::string why;
+      bool ok = false;
+      try { ok = plan_small_batch(b.stages, (int)b.params.size(), opt, plan, why); } catch (const std::exception&) {}
+      if (ok && compile) {
+        std::vector<char> cubin;
+        std::string err;
+        if (!nvrtc_compile(plan.source, cubin, err)) { put(message, message_len, err); return JAXCUDA_ECOMPILE; }
+      }
+      if (ok) {
+        rep << i << "-" << bend - 1 << ": " << plan.describe << " bytes=" << (long long)plan.algo_bytes << "\n";
+        src << plan.source << "\n";
+        i = bend;
+        continue;
       }
     }
     try {

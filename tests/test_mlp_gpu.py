@@ -174,7 +174,7 @@ def test_captured_per_example_program_substitutes_the_batch_last_products(backen
     n_kernels = sum(1 for s in prog.steps if s.kind == "execute")
     graph, outs = prog.capture(backend, slots)
     launches, nbytes, groups = backend.graph_cost(graph)
-    assert groups >= 2 and launches == n_kernels - groups, (launches, n_kernels, groups)
+    assert groups >= 2 and launches <= n_kernels - groups, (launches, n_kernels, groups)   # a batch of small Kernels saves more than one launch
     for _ in range(2):
         backend.graph_launch(graph)
     for name, s, w in zip(["loss", "dW1", "db1", "dW2", "db2"], outs, want):
