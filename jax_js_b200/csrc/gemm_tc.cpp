@@ -626,8 +626,10 @@ JX_EPILOGUE
 // those 13 bits (verified on B200: results are bit-identical with explicit hi planes), so the
 // original operand serves as hi.  Planes keep the operand's own indexing.
 extern "C" __global__ void __launch_bounds__(256) jx_split(const float* __restrict__ a, const float* __restrict__ b,
-                                                          float* __restrict__ planes) {
-  const i64 na4 = (i64)LEN_A / 4, nb4 = (i64)LEN_B / 4;
+                                                          float* __restrict__ plane_a, float* __restrict__ plane_b,
+                                                          int do_a, int do_b) {
+  // do_a / do_b: a plane that an earlier GEMM of the same step list already wrote is not written again
+  const i64 na4 = do_a ? (i64)LEN_A / 4 : 0, nb4 = do_b ? (i64)LEN_B / 4 : 0;
   const i64 total4 = na4 + nb4;
   for (i64 i = (i64)blockIdx.x * 256 + threadIdx.x; i < total4; i += (i64)gridDim.x * 256) {
     const bool is_a = i < na4;
@@ -638,15 +640,15 @@ extern "C" __global__ void __launch_bounds__(256) jx_split(const float* __restri
     lo.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xffffe000u);
     lo.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xffffe000u);
     lo.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xffffe000u);
-    reinterpret_cast<float4*>(planes + (is_a ? 0 : (i64)LEN_A_PAD))[j] = lo;
+    reinterpret_cast<float4*>(is_a ? plane_a : plane_b)[j] = lo;
   }
   if (blockIdx.x == 0 && threadIdx.x < 8) {     // the up to three trailing elements of each operand
     const bool is_a = threadIdx.x < 4;
     const i64 len = is_a ? (i64)LEN_A : (i64)LEN_B;
     const i64 j = (len / 4) * 4 + (threadIdx.x & 3);
-    if (j < len) {
+    if (j < len && (is_a ? do_a : do_b)) {
       const float v = (is_a ? a : b)[j];
-      (planes + (is_a ? 0 : (i64)LEN_A_PAD))[j] = v - __uint_as_float(__float_as_uint(v) & 0xffffe000u);
+      (is_a ? plane_a : plane_b)[j] = v - __uint_as_float(__float_as_uint(v) & 0xffffe000u);
     }
   }
 }
@@ -864,7 +866,7 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
 
 int launch_gemm_tc(void* encode_fn, void* launch_fn, void* launch_ex_fn, const Plan& plan, const std::vector<CUfunction>& fns,
                    const std::vector<void*>& inputs, void* out, void* scratch, cudaStream_t stream,
-                   int* status_dev, std::string& err, int max_ctas) {
+                   int* status_dev, std::string& err, int max_ctas, const LoPlanes* lo) {
   auto encode = (EncodeTiledFn)encode_fn;
   auto launch = (LaunchFn)launch_fn;
   const GemmDesc& g = plan.gemm;
@@ -896,16 +898,21 @@ int launch_gemm_tc(void* encode_fn, void* launch_fn, void* launch_ex_fn, const P
     split_planes = (char*)scratch + plane_bytes * (kind == 2 ? 2 : 1);
   }
   if (kind == 2 && !plan.tc_lo_in_kernel) {
-    float* planes = (float*)split_planes;
+    // remainder planes: in the scratch, or where the caller keeps them across the GEMMs of a step list
+    float* plane_a = (lo && lo->a) ? lo->a : (float*)split_planes;
+    float* plane_b = (lo && lo->b) ? lo->b : (float*)split_planes + pad64(g.lenA);
+    int do_a = !(lo && lo->a && !lo->compute_a), do_b = !(lo && lo->b && !lo->compute_b);
     const char* split_b = g.b_gathered ? baseA : baseB;   // not read when LEN_B is 0
-    void* args[] = {(void*)&baseA, (void*)&split_b, (void*)&planes};
-    const Stage& sp = plan.stages[stage_i];
-    CUresult r = launch(fns[stage_i], sp.grid[0], 1, 1, sp.block[0], 1, 1, 0, (CUstream)stream, args, nullptr);
-    if (r != CUDA_SUCCESS) { err = "launch of the TF32 split kernel failed"; return -1; }
-    launches++;
+    if (do_a || (do_b && !g.b_gathered)) {
+      void* args[] = {(void*)&baseA, (void*)&split_b, (void*)&plane_a, (void*)&plane_b, (void*)&do_a, (void*)&do_b};
+      const Stage& sp = plan.stages[stage_i];
+      CUresult r = launch(fns[stage_i], sp.grid[0], 1, 1, sp.block[0], 1, 1, 0, (CUstream)stream, args, nullptr);
+      if (r != CUDA_SUCCESS) { err = "launch of the TF32 split kernel failed"; return -1; }
+      launches++;
+    }
     stage_i++;
-    baseA2 = (const char*)planes;                     // lo planes; the operands themselves are the hi terms
-    if (!g.b_gathered) baseB2 = (const char*)(planes + pad64(g.lenA));
+    baseA2 = (const char*)plane_a;                    // lo planes; the operands themselves are the hi terms
+    if (!g.b_gathered) baseB2 = (const char*)plane_b;
   }
   const CUtensorMapDataType dt = kind == 1 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
   const cuuint32_t inner_box = 128 / e;

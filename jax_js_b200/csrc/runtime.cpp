@@ -214,6 +214,7 @@ struct PendingDispatch {
   size_t out_bytes = 0;
   bool out_freed = false;  // the output's slot was released before the list was flushed: nobody else can read it
   size_t freed_at = (size_t)-1;  // ... after this many dispatches of the list (later users of the address see another array)
+  LoPlanes lo;             // 3xTF32 GEMMs: remainder planes kept across the GEMMs of the list (see plane_ticket)
 };
 
 struct jaxcuda_ctx {
@@ -222,6 +223,14 @@ struct jaxcuda_ctx {
   uint64_t capture_launches0 = 0;
   std::vector<PendingDispatch> pending;
   bool fuse_rows = true;          // JAXCUDA_FUSE=0: captured Kernels are launched one by one
+  // Remainder planes lo = x - tf32(x) of arrays that 3xTF32 GEMMs of the step list being captured
+  // read, by the array's address: an activation is the operand of a forward GEMM and of a
+  // weight-gradient GEMM, a weight of a forward and a backward one, and is split once.  Entries are
+  // made and dropped in program order (at dispatch, at the release or overwrite of the array), the
+  // order in which the deferred launches then happen.
+  struct LoPlane { void* plane; size_t bytes; uint64_t len; };
+  std::unordered_map<void*, LoPlane> lo_planes;
+  bool keep_lo_planes = true;     // JAXCUDA_TC_PLANE_CACHE=0: every GEMM splits its own operands
   double capture_bytes = 0;
   int capture_groups = 0;
   std::map<std::string, std::unique_ptr<jaxcuda_exe>> fused;  // compiled row programs by wiring
@@ -258,6 +267,11 @@ struct jaxcuda_ctx {
   std::vector<uint64_t> free_tickets;
   std::vector<char> ticket_pending;  // read_async issued, read_wait not yet returned
   std::unordered_set<void*> comm_ptrs;  // blocks a sum on the second stream is still working on
+  // ... and, per block, the event behind the sum that works on it: a Kernel that reads the block makes
+  // the compute stream wait for exactly that sum (not for those begun after it)
+  std::unordered_map<void*, cudaEvent_t> comm_ptr_event;
+  std::vector<cudaEvent_t> comm_events;   // pool; the first comm_events_used are taken
+  size_t comm_events_used = 0;
   uint64_t order_waits = 0;          // times the compute stream was made to wait for a copy or a sum (see order_after_users)
   // direction of the next streaming kernel's walk over its grid (JAXCUDA_SWEEP=0: always forward)
   int sweep = 0;
@@ -394,8 +408,32 @@ int env_int(const char* name, int dflt) {
 
 }  // namespace
 
-static int launch_kernel(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const std::vector<void*>& inptr, void* outptr);
+static int launch_kernel(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const std::vector<void*>& inptr, void* outptr, const LoPlanes* lo = nullptr);
 static int flush_pending(jaxcuda_ctx* ctx);
+
+// A dispatch is about to read `s`: if a sum on the second stream still works on it, everything
+// dispatched from here on waits for that sum.
+static int order_after_sum(jaxcuda_ctx* ctx, SlotRec* s) {
+  if (!ctx->comm_pending || !s->ptr) return JAXCUDA_OK;
+  auto it = ctx->comm_ptr_event.find(s->ptr);
+  if (it == ctx->comm_ptr_event.end()) return JAXCUDA_OK;
+  if (int rc = flush_pending(ctx)) return rc;
+  CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->stream, it->second, 0));
+  ctx->order_waits++;
+  // sums complete in the order they were begun: every block of this sum and of earlier ones is settled
+  const cudaEvent_t waited = it->second;
+  size_t upto = 0;
+  while (upto < ctx->comm_events_used && ctx->comm_events[upto] != waited) upto++;
+  for (auto e = ctx->comm_ptr_event.begin(); e != ctx->comm_ptr_event.end();) {
+    size_t at = 0;
+    while (at < ctx->comm_events_used && ctx->comm_events[at] != e->second) at++;
+    if (at <= upto) { ctx->comm_ptrs.erase(e->first); e = ctx->comm_ptr_event.erase(e); }
+    else ++e;
+  }
+  return JAXCUDA_OK;
+}
+
+
 
 extern "C" {
 
@@ -455,6 +493,7 @@ int jaxcuda_create(int device, jaxcuda_ctx** out) {
   ctx->opt.tc_fault = env_int("JAXCUDA_TC_FAULT", 0);
   ctx->sweep_alternate = env_int("JAXCUDA_SWEEP", 1) != 0;
   ctx->fuse_rows = env_int("JAXCUDA_FUSE", 1) != 0;
+  ctx->keep_lo_planes = env_int("JAXCUDA_TC_PLANE_CACHE", 1) != 0;
   ctx->opt.fuse_chunks = env_int("JAXCUDA_FUSE_CHUNKS", ctx->opt.fuse_chunks);
   ctx->opt.fuse_min_ctas = env_int("JAXCUDA_FUSE_MIN_CTAS", ctx->opt.fuse_min_ctas);
   ctx->debug = env_int("JAXCUDA_DEBUG", 0);
@@ -479,6 +518,7 @@ int jaxcuda_destroy(jaxcuda_ctx* ctx) {
     cudaStreamSynchronize(ctx->comm_stream);
     cudaEventDestroy(ctx->comm_fork);
     cudaEventDestroy(ctx->comm_done);
+    for (cudaEvent_t ev : ctx->comm_events) cudaEventDestroy(ev);
     cudaStreamDestroy(ctx->comm_stream);
   }
   jaxcuda_comm_destroy(ctx);
@@ -522,6 +562,34 @@ int jaxcuda_malloc(jaxcuda_ctx* ctx, size_t bytes, const void* init, size_t init
   return JAXCUDA_OK;
 }
 
+// The array at `ptr` is about to change or to go away: its remainder plane is of no use any more.
+static void drop_lo_plane(jaxcuda_ctx* ctx, void* ptr) {
+  if (ctx->lo_planes.empty()) return;
+  auto it = ctx->lo_planes.find(ptr);
+  if (it == ctx->lo_planes.end()) return;
+  ctx->alloc.put(it->second.plane, it->second.bytes);
+  ctx->lo_planes.erase(it);
+}
+static void drop_all_lo_planes(jaxcuda_ctx* ctx) {
+  for (auto& kv : ctx->lo_planes) ctx->alloc.put(kv.second.plane, kv.second.bytes);
+  ctx->lo_planes.clear();
+}
+// The plane of the operand at `ptr` (`len` elements): the one an earlier GEMM of the list made, or a
+// new one that this GEMM fills.
+static int plane_ticket(jaxcuda_ctx* ctx, void* ptr, uint64_t len, float*& plane, bool& compute) {
+  auto it = ctx->lo_planes.find(ptr);
+  if (it != ctx->lo_planes.end() && it->second.len == len) { plane = (float*)it->second.plane; compute = false; return JAXCUDA_OK; }
+  if (it != ctx->lo_planes.end()) drop_lo_plane(ctx, ptr);
+  const size_t bytes = (size_t)((len + 63) / 64 * 64) * 4;
+  void* p = nullptr;
+  cudaError_t e = ctx->alloc.get(bytes, &p);
+  if (e != cudaSuccess) return fail(ctx, JAXCUDA_ENOMEM, "remainder plane of %zu bytes: %s", bytes, cudaGetErrorString(e));
+  ctx->lo_planes[ptr] = jaxcuda_ctx::LoPlane{p, bytes, len};
+  plane = (float*)p;
+  compute = true;
+  return JAXCUDA_OK;
+}
+
 int jaxcuda_incref(jaxcuda_ctx* ctx, jaxcuda_slot slot) {
   SlotRec* s = find_slot(ctx, slot);
   if (!s) return slot_error(ctx, slot);
@@ -536,7 +604,7 @@ int jaxcuda_decref(jaxcuda_ctx* ctx, jaxcuda_slot slot) {
     if (int rc = order_after_users(ctx, s)) return rc;
     for (size_t i = ctx->pending.size(); i-- > 0;)   // the latest pending writer of this block produced it
       if (ctx->pending[i].out == s->ptr) { ctx->pending[i].out_freed = true; ctx->pending[i].freed_at = ctx->pending.size(); break; }
-    if (s->ptr) ctx->alloc.put(s->ptr, s->bytes);
+    if (s->ptr) { drop_lo_plane(ctx, s->ptr); ctx->alloc.put(s->ptr, s->bytes); }
     ctx->slots.erase(slot);
   }
   return JAXCUDA_OK;
@@ -578,6 +646,7 @@ int jaxcuda_write(jaxcuda_ctx* ctx, jaxcuda_slot slot, size_t start, size_t coun
   cudaSetDevice(ctx->device);
   if (int rc = flush_pending(ctx)) return rc;
   if (int rc = order_after_users(ctx, s)) return rc;
+  drop_lo_plane(ctx, s->ptr);
   if (count) CUDA_TRY(ctx, cudaMemcpyAsync((char*)s->ptr + start, src, count, cudaMemcpyHostToDevice, ctx->stream));
   return JAXCUDA_OK;
 }
@@ -968,6 +1037,8 @@ int jaxcuda_dispatch(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const jaxcuda_slot* inp
   for (int i = 0; i < n_inputs; i++) if (!(in[i] = find_slot(ctx, inputs[i]))) return slot_error(ctx, inputs[i]);
   for (int i = 0; i < n_outputs; i++) if (!(outv[i] = find_slot(ctx, outputs[i]))) return slot_error(ctx, outputs[i]);
   for (int i = 0; i < n_outputs; i++) if (int rc = order_after_users(ctx, outv[i])) return rc;
+  for (int i = 0; i < n_inputs; i++) if (int rc = order_after_sum(ctx, in[i])) return rc;
+  for (int i = 0; i < n_outputs; i++) drop_lo_plane(ctx, outv[i]->ptr);
 
   if (exe->kind != 0)
     if (int rc = flush_pending(ctx)) return rc;
@@ -1099,6 +1170,12 @@ int jaxcuda_dispatch(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const jaxcuda_slot* inp
     for (int i = 0; i < n_inputs; i++) pd.in_bytes.push_back(in[i]->bytes);
     pd.out = outv[0]->ptr;
     pd.out_bytes = outv[0]->bytes;
+    const Plan& pl = exe->plan;
+    if (ctx->keep_lo_planes && pl.skeleton == SK_GEMM_TC && pl.tc_kind == 2 && !pl.tc_lo_in_kernel && !pl.gemm.b_gathered &&
+        pl.tc_sk_counter_bytes == 0) {
+      if (int rc = plane_ticket(ctx, inptr[pl.gemm.gidA], pl.gemm.lenA, pd.lo.a, pd.lo.compute_a)) return rc;
+      if (int rc = plane_ticket(ctx, inptr[pl.gemm.gidB], pl.gemm.lenB, pd.lo.b, pd.lo.compute_b)) return rc;
+    }
     ctx->pending.push_back(std::move(pd));
     return JAXCUDA_OK;
   }
@@ -1109,7 +1186,7 @@ int jaxcuda_dispatch(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const jaxcuda_slot* inp
 }  // extern "C"
 
 // Launches one prepared Kernel on the context's stream.
-static int launch_kernel(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const std::vector<void*>& inptr, void* outptr) {
+static int launch_kernel(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const std::vector<void*>& inptr, void* outptr, const LoPlanes* lo) {
   const int n_inputs = (int)inptr.size();
   if (ctx->alloc.capturing) ctx->capture_bytes += exe->plan.algo_bytes;
   void* scratch = nullptr;
@@ -1122,7 +1199,7 @@ static int launch_kernel(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const std::vector<v
       if (e != cudaSuccess) return fail(ctx, JAXCUDA_ENOMEM, "scratch of %zu bytes: %s", exe->plan.scratch_bytes, cudaGetErrorString(e));
     }
     scratch = exe->persistent_scratch;
-  } else if (exe->plan.scratch_bytes) {
+  } else if (exe->plan.scratch_bytes && !(lo && lo->a && lo->b)) {   // (kept remainder planes are all the scratch such a GEMM has)
     cudaError_t e = ctx->alloc.get(exe->plan.scratch_bytes, &scratch);
     if (e != cudaSuccess) return fail(ctx, JAXCUDA_ENOMEM, "scratch of %zu bytes: %s", exe->plan.scratch_bytes, cudaGetErrorString(e));
   }
@@ -1133,7 +1210,8 @@ static int launch_kernel(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const std::vector<v
                             outptr, scratch, ctx->stream, ctx->status_dev, err,
                             // a persistent GEMM that holds every SM would keep a sum begun on the second
                             // stream waiting until it ends; leave that sum a few SMs while one is in flight
-                            ctx->comm_pending && ctx->comm_sms > 0 ? std::max(1, ctx->opt.sm_count - ctx->comm_sms) : 0);
+                            ctx->comm_pending && ctx->comm_sms > 0 ? std::max(1, ctx->opt.sm_count - ctx->comm_sms) : 0,
+                            (lo && lo->a && lo->b) ? lo : nullptr);
     if (nl < 0) rc = fail(ctx, JAXCUDA_ECUDA, "%s", err.c_str());
     else { ctx->launches += nl; ctx->tc_dispatched = true; }
   } else {
@@ -1357,7 +1435,8 @@ static size_t launch_composed_pair(jaxcuda_ctx* ctx, std::vector<PendingDispatch
     ctx->fused[key.str()] = std::move(exe);
   }
   if (!fx) return i;
-  if (launch_kernel(ctx, fx, composed_inputs(list[i], list[i + 1], b_arg, epilogue), list[i + 1].out) != JAXCUDA_OK) return i;
+  // (a GEMM that took its consumer into the epilogue has the GEMM's operands first: its planes apply)
+  if (launch_kernel(ctx, fx, composed_inputs(list[i], list[i + 1], b_arg, epilogue), list[i + 1].out, epilogue ? &list[i].lo : nullptr) != JAXCUDA_OK) return i;
   ctx->capture_groups++;
   return i + 2;
 }
@@ -1460,7 +1539,7 @@ static int flush_pending(jaxcuda_ctx* ctx) {
     if (next > i) { i = next; continue; }
     next = launch_small_batch(ctx, list, i);
     if (next > i) { i = next; continue; }
-    if (int rc = launch_kernel(ctx, list[i].exe, list[i].in, list[i].out)) return rc;
+    if (int rc = launch_kernel(ctx, list[i].exe, list[i].in, list[i].out, &list[i].lo)) return rc;
     i++;
   }
   return JAXCUDA_OK;
@@ -1643,6 +1722,7 @@ int jaxcuda_copy(jaxcuda_ctx* ctx, jaxcuda_slot dst, jaxcuda_slot src) {
   cudaSetDevice(ctx->device);
   if (int rc = flush_pending(ctx)) return rc;
   if (int rc = order_after_users(ctx, d)) return rc;
+  drop_lo_plane(ctx, d->ptr);
   if (d->bytes && d->ptr != s->ptr)
     CUDA_TRY(ctx, cudaMemcpyAsync(d->ptr, s->ptr, d->bytes, cudaMemcpyDeviceToDevice, ctx->stream));
   return JAXCUDA_OK;
@@ -1668,6 +1748,7 @@ int jaxcuda_capture_end(jaxcuda_ctx* ctx, jaxcuda_graph** out) {
   *out = nullptr;
   if (!ctx->alloc.capturing) return fail(ctx, JAXCUDA_EINVAL, "no capture is open");
   const int flush_rc = flush_pending(ctx);
+  drop_all_lo_planes(ctx);   // (graph-owned blocks: they return to the graph's own pool)
   jaxcuda_comm_join(ctx);  // a forked stream must rejoin before the capture closes
   const int id = ctx->alloc.capturing;
   ctx->alloc.capturing = 0;
@@ -1822,7 +1903,17 @@ int jaxcuda_allreduce_sum_f32_async(jaxcuda_ctx* ctx, const jaxcuda_slot* slots,
   ctx->comm_pending = true;
   for (int i = 0; i < n; i++)
     if (SlotRec* r = find_slot(ctx, slots[i])) ctx->comm_ptrs.insert(r->ptr);
-  return allreduce_on(ctx, slots, n, ctx->comm_stream);
+  if (int rc = allreduce_on(ctx, slots, n, ctx->comm_stream)) return rc;
+  if (ctx->comm_events_used == ctx->comm_events.size()) {
+    cudaEvent_t ev;
+    CUDA_TRY(ctx, cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    ctx->comm_events.push_back(ev);
+  }
+  cudaEvent_t done = ctx->comm_events[ctx->comm_events_used++];
+  CUDA_TRY(ctx, cudaEventRecord(done, ctx->comm_stream));
+  for (int i = 0; i < n; i++)
+    if (SlotRec* r = find_slot(ctx, slots[i])) ctx->comm_ptr_event[r->ptr] = done;
+  return JAXCUDA_OK;
 }
 
 int jaxcuda_comm_join(jaxcuda_ctx* ctx) {
@@ -1834,6 +1925,8 @@ int jaxcuda_comm_join(jaxcuda_ctx* ctx) {
   CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->stream, ctx->comm_done, 0));
   ctx->comm_pending = false;
   ctx->comm_ptrs.clear();
+  ctx->comm_ptr_event.clear();
+  ctx->comm_events_used = 0;
   return JAXCUDA_OK;
 }
 
@@ -1845,6 +1938,7 @@ static int allreduce_on(jaxcuda_ctx* ctx, const jaxcuda_slot* slots, int n, cuda
   if (!allreduce || !gstart || !gend) return fail(ctx, JAXCUDA_ECUDA, "NCCL symbols missing");
   cudaSetDevice(ctx->device);
   for (int i = 0; i < n; i++) if (!find_slot(ctx, slots[i])) return slot_error(ctx, slots[i]);
+  for (int i = 0; i < n; i++) drop_lo_plane(ctx, find_slot(ctx, slots[i])->ptr);   // summed in place
   gstart();
   int r = 0;
   for (int i = 0; i < n && r == 0; i++) {

@@ -332,8 +332,8 @@ class MlpTrainer:
             # The program yields the loss and the bias gradients first (last layer first), then the
             # weight gradients from the first layer up.  Loss and biases go out as one group once the
             # last bias exists, every weight gradient on its own as soon as it exists, under the
-            # kernels that follow it.  The last group (the last layer's weights) stays in flight into
-            # the Adam program, which waits for it just before its first reader (`_adam`).
+            # kernels that follow it.  The sums stay in flight into the Adam program: the backend makes
+            # every Kernel that reads a gradient wait for that gradient's sum (and for no later one).
             ready = []
             last = f"dW{len(self.dims) - 1}"
 

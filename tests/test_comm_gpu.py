@@ -68,3 +68,35 @@ def test_sum_inside_a_captured_step_list(solo):
     solo.graph_destroy(graph)
     solo.dec_ref(a)
     solo.dec_ref(b)
+
+
+def test_a_reader_waits_for_the_sum_of_its_operand_only(solo):
+    """A Kernel that reads a slot whose sum is still running on the second stream makes the compute
+    stream wait for exactly that sum (no join is needed for correctness); sums begun later stay in
+    flight.  Eagerly and inside a captured step list."""
+    n = 1 << 20
+    inc = _inc(solo, n)
+    a = solo.put(np.ones(n, np.float32))
+    b, c, d, e = (solo.malloc(n * 4) for _ in range(4))
+
+    def run():
+        solo.dispatch(inc, [a], [b])               # b = a + 1
+        solo.allreduce_sum_f32_async([b])
+        solo.dispatch(inc, [a], [c])               # c = a + 1
+        solo.allreduce_sum_f32_async([c])
+        solo.dispatch(inc, [b], [d])               # reads b: waits for the first sum, not for the second
+        solo.dispatch(inc, [c], [e])               # reads c: waits for the second
+    w0 = solo.order_waits()
+    run()
+    assert solo.order_waits() - w0 == 2
+    assert (solo.get(d, F32) == 3).all() and (solo.get(e, F32) == 3).all()
+    solo.capture_begin()
+    run()
+    solo.dispatch(inc, [d], [a])                   # a <- a + 3 per replay
+    graph = solo.capture_end()
+    for _ in range(3):
+        solo.graph_launch(graph)
+    assert (solo.get(a, F32) == 10).all() and (solo.get(e, F32) == 9).all()
+    solo.graph_destroy(graph)
+    for s in (a, b, c, d, e):
+        solo.dec_ref(s)

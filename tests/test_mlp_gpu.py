@@ -184,6 +184,47 @@ def test_captured_per_example_program_substitutes_the_batch_last_products(backen
         backend.dec_ref(s)
 
 
+def test_kept_remainder_planes_do_not_change_a_captured_training_step(backend):
+    """Inside a capture the 3xTF32 remainder plane of an array is written once and read by every GEMM
+    that has the array as an operand (an activation: its forward and its weight-gradient GEMM); with
+    JAXCUDA_TC_PLANE_CACHE=0 every GEMM splits its own operands.  Same planes, same bits, also after
+    the parameters have moved (the planes of the new values are made anew in every replay)."""
+    import os
+    from jax_js_b200.backend import CudaBackend
+    dims, B = [784, 2048, 2048, 10], 4096
+    x, y = _data(B, dims[0], dims[-1], 4)
+    results = {}
+    for mode in ("1", "0"):
+        old = os.environ.get("JAXCUDA_TC_PLANE_CACHE")
+        os.environ["JAXCUDA_TC_PLANE_CACHE"] = mode
+        try:
+            be = CudaBackend(backend.device)
+        finally:
+            if old is None:
+                os.environ.pop("JAXCUDA_TC_PLANE_CACHE")
+            else:
+                os.environ["JAXCUDA_TC_PLANE_CACHE"] = old
+        try:
+            sx, sy = be.put(x), be.put(y)
+            tr = mlp.MlpTrainer(be, dims, B, B)
+            be.dec_ref(tr.step(sx, sy))
+            tr.capture(sx, sy)
+            losses = []
+            for _ in range(4):
+                s_ = tr.step(sx, sy)
+                losses.append(be.get(s_, "float32")[0])
+                be.dec_ref(s_)
+            results[mode] = (np.array(losses), [be.read_sync(p).copy() for p in tr.params])
+            tr.close()
+            be.dec_ref(sx)
+            be.dec_ref(sy)
+        finally:
+            be.close()
+    assert np.array_equal(results["1"][0].view(np.uint32), results["0"][0].view(np.uint32)), (results["1"][0], results["0"][0])
+    for a, b in zip(results["1"][1], results["0"][1]):
+        assert np.array_equal(a, b)
+
+
 def test_config5_shard_gradients_against_float64(backend):
     import torch
     dims, B, GB = [784, 2048, 2048, 10], 8192, 65536
