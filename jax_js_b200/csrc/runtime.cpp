@@ -1252,6 +1252,14 @@ struct RowGroup {
 };
 
 static bool build_row_group(const std::vector<PendingDispatch>& list, size_t i, size_t end, int64_t R, int64_t C, RowGroup& g) {
+  // An output that the list releases needs no store only if nothing behind the group reads it before
+  // the release.
+  auto dies_inside = [&](const PendingDispatch& pd) {
+    if (!pd.out_freed) return false;
+    for (size_t r = end; r < list.size() && r < pd.freed_at; r++)
+      for (void* p : list[r].in) if (p == pd.out) return false;
+    return true;
+  };
   std::unordered_map<void*, int> cur;
   std::map<std::string, int> seen;  // Kernel + inputs -> output buffer, for repeated Kernels
   std::ostringstream key;
@@ -1281,13 +1289,13 @@ static bool build_row_group(const std::vector<PendingDispatch>& list, size_t i, 
     auto oit = cur.find(pd.out);
     if (oit != cur.end() && g.bufs[oit->second].external) return false;
     auto dup = seen.find(sk.str());
-    if (dup != seen.end() && pd.out_freed) {  // the same Kernel on the same arrays again: reuse its result
+    if (dup != seen.end() && dies_inside(pd)) {  // the same Kernel on the same arrays again: reuse its result
       cur[pd.out] = dup->second;
       key << "|=" << dup->second;
       continue;
     }
     FuseBuffer ob;
-    ob.store = !pd.out_freed;
+    ob.store = !dies_inside(pd);
     ob.bytes = pd.out_bytes;
     st.out_buf = (int)g.bufs.size();
     g.bufs.push_back(ob);
