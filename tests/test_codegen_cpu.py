@@ -225,3 +225,20 @@ def test_step_list_check_substitutes_an_elementwise_producer_into_its_only_consu
     assert big[0].split(":")[1].strip().startswith("elementwise V=4"), big[0]
     body = source[source.index("jx_elementwise("):]
     assert "jx_load(pk" in body.split("jx_store")[0]     # the row of dz1 comes as 128-bit vectors
+
+
+def test_step_list_check_reports_epilogue_fusion_and_small_batches(lib):
+    """Without a GPU: the back-propagated cotangents of the training step go into the epilogues of the
+    Dot Kernels that produce them, and the log-softmax chain of the vmapped program, a dozen Kernels
+    over a few hundred elements, is one launch."""
+    from jax_js_b200 import mlp
+    from jax_js_b200.backend import check_step_list
+    report, _ = check_step_list(mlp.mlp_grad_program(8192, [784, 2048, 2048, 10], global_batch=65536), compile=True)
+    fused = [l for l in report if "consumer in the epilogue" in l]
+    assert len(fused) == 2 and any("gemm-tcgen05" in l and "cta-pairs" in l for l in fused) and any("dot-small-k" in l for l in fused), report
+    report, source = check_step_list(mlp.mlp_grad_program(64, [784, 1024, 10], per_example=True), compile=True)
+    batches = [l for l in report if "batch of" in l]
+    assert len(batches) == 1 and "batch of 12 small kernels" in batches[0], report
+    assert len(report) == 12                     # 27 Kernels in 12 launches
+    body = source[source.index("jx_batch("):]
+    assert body.count("__syncthreads();") == 11 and "__restrict__" not in body.split("{")[0]
