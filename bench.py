@@ -232,6 +232,27 @@ def mlp_train(be, rank, world, dist, steps=8, warmup=2):
     ms = float(t.item())
     flops = 2.0 * GB * (784 * 2048 + 2048 * 2048 + 2048 * 10) * 3 - 2.0 * GB * 784 * 2048
     tr.close()
+    phases = None
+    if world > 1:
+        # the same shard without the sums (a trainer of its own, world 1 on the local batch): what the
+        # step costs in kernels alone; the rest of the step is sums that nothing hides and waiting
+        # for the slowest rank
+        solo = mlp.MlpTrainer(be, dims, local, GB)
+        for _ in range(2):
+            be.dec_ref(solo.step(sx, sy, 1))
+        solo.capture(sx, sy, 1)
+        be.dec_ref(solo.step(sx, sy, 1))
+        be.sync()
+        be.event_record(4)
+        for _ in range(steps):
+            be.dec_ref(solo.step(sx, sy, 1))
+        be.event_record(5)
+        be.sync()
+        ts = torch.tensor([be.event_elapsed_ms(4, 5) / steps], dtype=torch.float64, device="cuda")
+        dist.all_reduce(ts, op=dist.ReduceOp.MAX)
+        solo.close()
+        phases = {"shard_kernels_ms": float(ts.item()), "sums_and_waiting_ms": ms / steps - float(ts.item()),
+                  "note": "shard_kernels_ms: the same local batch replayed without the gradient sums (max over ranks)"}
     be.dec_ref(sx)
     be.dec_ref(sy)
     return {"steps_per_s": steps / ms * 1e3, "ms_per_step": ms / steps, "global_batch": GB, "local_batch": local,
@@ -239,7 +260,7 @@ def mlp_train(be, rank, world, dist, steps=8, warmup=2):
             "allreduce_bytes": 4 * sum(mlp.leaf_sizes(dims)), "loss_last": vals[-1],
             "replay": "one CUDA graph launch per step (gradient program + NCCL sum + Adam program; two graphs alternate between two state buffers)",
             "gradient_sum": "per layer on a second stream, under back-propagation" if tr.overlap and world > 1 else "after the gradient program",
-            "eager_ms_per_step": eager_ms,
+            "eager_ms_per_step": eager_ms, "phases": phases,
             "gemm": "3xTF32 on tcgen05 (f32 accuracy), f32 accumulate"}
 
 
