@@ -330,16 +330,16 @@ class MlpTrainer:
             self.allreduce(list(outs[1:]) + [outs[0]])
         else:
             # The program yields the loss and the bias gradients first (last layer first), then the
-            # weight gradients from the first layer up.  Loss and biases go out as one group once the
-            # last bias exists, every weight gradient on its own as soon as it exists, under the
-            # kernels that follow it.  The sums stay in flight into the Adam program: the backend makes
-            # every Kernel that reads a gradient wait for that gradient's sum (and for no later one).
+            # weight gradients from the first layer up.  Every weight gradient goes out as soon as it
+            # exists, under the kernels that follow it; the loss and the biases (a few KB) ride with the
+            # first of them.  The sums stay in flight into the Adam program: the backend makes every
+            # Kernel that reads a gradient wait for that gradient's sum (and for no later one).
             ready = []
             last = f"dW{len(self.dims) - 1}"
 
             def on_output(name, slot):
                 ready.append(slot)
-                if name == "db1" or name.startswith("dW"):
+                if name.startswith("dW"):
                     be.allreduce_sum_f32_async(ready)
                     ready.clear()
                     if name == last:

@@ -124,7 +124,7 @@ def _rank_main(rank, world, port, out):
         losses.append(float(be.get(s, "float32")[0]))
         be.dec_ref(s)
     # each step summed loss and bias gradients as one group, then every weight gradient as it appeared
-    assert tr.overlap and be.joined and be.async_calls == [4, 1, 1, 1] * 2, be.async_calls
+    assert tr.overlap and be.joined and be.async_calls == [5, 1, 1] * 2, be.async_calls   # loss + biases ride with dW1
     if rank == 0:
         np.savez(out, losses=np.array(losses), **{f"p{i}": be.get(s, "float32") for i, s in enumerate(tr.params)})
     dist.destroy_process_group()
