@@ -80,6 +80,7 @@ struct Options {
   int tc_bn = 0;              // force the tensor-core tile width (64, 128, 192, 256); 0 = planner's choice (JAXCUDA_TC_BN)
   int tc_streamk = 1;         // 0: whole tiles only; 1: an output with at most half as many tiles as SMs and a long K is cut along K; 2: so is any last wave that is at most half full (JAXCUDA_TC_STREAMK)
   int tc_pair = 1;            // CTA pairs on 256-row tiles (cta_group::2): 0 never, 1 f16 GEMMs, 2 3xTF32 as well (JAXCUDA_TC_PAIR)
+  int tc_half_last = 1;       // CTA pairs: a last wave that is at most half full runs as half-width tiles: 0 never, 1 3xTF32, 2 f16 as well (JAXCUDA_TC_HALF_LAST)
   int tc_spin_limit = 20000000;  // polls of a tensor-core pipeline wait before it gives up (JAXCUDA_TC_SPIN_LIMIT)
   int tc_lo_in_kernel = 1;    // 3xTF32 remainder tiles derived in shared memory by warps of the GEMM kernel instead of a split pass through global memory: 0 never, 1 for outputs of at most one wave of tiles, 2 always (JAXCUDA_TC_LO_IN_KERNEL)
   int tc_fault = 0;           // tests of the wind-down only: 1 = one CTA's producer announces a stage and never loads it (JAXCUDA_TC_FAULT)

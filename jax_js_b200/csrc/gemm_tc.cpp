@@ -179,6 +179,7 @@ __device__ __forceinline__ u64 operand_desc(u32 base, int kk, int mn_major) {
 #define NCHUNK ((K_BLOCKS + CHUNK_KB - 1) / CHUNK_KB)
 #define IDESC ((1u << 4) | ((KIND == 2 ? 2u : 0u) << 7) | ((KIND == 2 ? 2u : 0u) << 10) | ((u32)A_MN << 15) | \
                ((u32)B_MN << 16) | ((u32)(BN >> 3) << 17) | ((u32)(TILE_M >> 4) << 24))
+#define IDESC_N(bn) (HALF_LAST ? ((IDESC & ~(0x3fu << 17)) | ((u32)((bn) >> 3) << 17)) : IDESC)
 
 __device__ __forceinline__ void tile_coords(int t, int& b, int& m_blk, int& n_blk) {
   const int per_batch = TILES_M * TILES_N;
@@ -203,8 +204,12 @@ __device__ __forceinline__ void tile_coords(int t, int& b, int& m_blk, int& n_bl
 // stops, was measured 20 to 40 % slower than no split at all: neighbours then read different
 // k-ranges of the same panels and every operand byte comes from DRAM.)  A slice's accumulators go to
 // scratch; the CTA that delivers a tile's last slice adds them up in k order and runs the epilogue.
-struct Seg { int tile, kb0, kb1, partial, slot; };
-__device__ __forceinline__ int sk_tiles_full() { return STREAMK ? (NUM_TILES / WORKERS) * WORKERS : NUM_TILES; }
+struct Seg { int tile, kb0, kb1, partial, slot, n_off, bn; };   // n_off, bn: the columns of the tile this segment covers
+__device__ __forceinline__ int sk_tiles_full() {
+  const int full = (NUM_TILES / WORKERS) * WORKERS;
+  if (HALF_LAST) return 2 * (NUM_TILES - full) <= WORKERS ? full : NUM_TILES;   // (the grid may be smaller than planned)
+  return STREAMK ? full : NUM_TILES;
+}
 __device__ __forceinline__ int sk_slices() {
   const int rest = NUM_TILES - sk_tiles_full();
   int s = rest > 0 ? WORKERS / rest : 1;
@@ -215,7 +220,21 @@ __device__ __forceinline__ bool get_segment(int i, Seg& s) {
   const int P = WORKERS, c = WORKER;
   const int tiles_full = sk_tiles_full();
   const int n_static = tiles_full > c ? (tiles_full - c + P - 1) / P : 0;
+  s.n_off = 0; s.bn = BN;
   if (i < n_static) { s.tile = c + i * P; s.kb0 = 0; s.kb1 = K_BLOCKS; s.partial = 0; s.slot = 0; return true; }
+#if HALF_LAST
+  // CTA pairs: the tiles left over behind the whole waves, at most half as many as pairs, are cut
+  // in two along N and run as 256 x BN/2 tiles on twice as many pairs, every pair still walking the
+  // whole K in step with the others and nothing to add up afterwards.  A half tile takes about 0.7
+  // of a whole tile's time (its CTA stores a quarter of B per stage instead of a half).
+  {
+    const int rest_h = NUM_TILES - tiles_full;
+    if (rest_h == 0 || i > n_static || c >= 2 * rest_h) return false;
+    s.tile = tiles_full + c / 2; s.kb0 = 0; s.kb1 = K_BLOCKS; s.partial = 0; s.slot = 0;
+    s.bn = BN / 2; s.n_off = (c & 1) * (BN / 2);
+    return true;
+  }
+#endif
   const int rest = NUM_TILES - tiles_full;
   if (!STREAMK || rest == 0 || i > n_static) return false;
   const int S = sk_slices();
@@ -247,6 +266,9 @@ __device__ __forceinline__ void jx_gather_tile(JX_PARAMS, u32 sb, int b, int n_t
 #define EPI_COLS (BN / EPI_SPLIT)
 #define NTHREADS (64 + 128 * EPI_SPLIT + 32 * (GATHER_WARPS + XFORM_WARPS))
 #define GROUP_WARPS (GATHER_WARPS / GATHER_GROUPS)
+#if HALF_LAST && (!CTA_PAIR || !B_MN || BN < 256)
+#error "half tiles in the last wave: CTA pairs on 256-column tiles with B read as [K, N]"
+#endif
 #if EPI_SPLIT > 1 && (STREAMK || B_GATHER || LO_IN_KERNEL)
 #error "a second group of epilogue warps takes the place of the gather and remainder-tile warps"
 #endif
@@ -320,7 +342,8 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
           const int s = it % STAGES;
           if (it >= STAGES && !mbar_wait(empty(s), ((it / STAGES) + 1) & 1, status)) { atomicCAS((int*)status_ptr, 0, 1); failed = true; break; }
           if (!CTA_PAIR) mbar_expect_tx(tma_bar(s), TX_BYTES);
-          else if (rank == 0) mbar_expect_tx(full(s), 2 * TX_BYTES);   // both CTAs' loads report to the even CTA's barrier
+          else if (rank == 0)   // both CTAs' loads report to the even CTA's barrier
+            mbar_expect_tx(full(s), 2 * (TX_BYTES - (HALF_LAST ? (BN - sg.bn) / 2 * 128 * TMA_PLANES : 0)));
 #if FAULT_SKIP_LOAD
           // test of the wind-down: CTA 0 announces its second stage and never loads it, so the MMA
           // role's bounded wait on that stage runs out
@@ -329,7 +352,8 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
           const u32 sa = smem_base + s * STAGE_BYTES, sb = sa + NPLANES * A_BYTES;
           const int k0 = kb * BK;
           const int ba = A_SHARED ? 0 : b, bb = B_SHARED ? 0 : b;   // an operand all batches share has one plane
-          const int m0 = m_blk * TILE_M + (int)rank * BM, n0 = n_blk * BN + (int)rank * B_COLS;   // this CTA's rows of A and columns of B
+          const int b_cols = HALF_LAST ? sg.bn / 2 : B_COLS;   // columns of B this CTA loads (a pair's half tile: a quarter of BN)
+          const int m0 = m_blk * TILE_M + (int)rank * BM, n0 = n_blk * BN + sg.n_off + (int)rank * b_cols;   // this CTA's rows of A and columns of B
 #if CTA_PAIR
 #define TMA_LOAD tma_load_3d_pair
 #else
@@ -347,7 +371,7 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
 #if B_GATHER
           (void)sb; (void)bb; (void)n0;
 #elif B_MN
-          for (int j = 0; j < B_COLS / BK; j++) {
+          for (int j = 0; j < b_cols / BK; j++) {
             TMA_LOAD(sb + j * BOX_BYTES, &tmB, tma_bar(s), n0 + j * BK, k0, bb);
             if (KIND == 2 && !LO_IN_KERNEL) TMA_LOAD(sb + B_BYTES + j * BOX_BYTES, &tmB2, tma_bar(s), n0 + j * BK, k0, bb);
           }
@@ -387,12 +411,12 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
             for (int kk = 0; kk < 4; kk++) {
               const u32 first = (kb != kb_first || kk) ? 1u : 0u;
 #if KIND == 1
-              umma(d, operand_desc(sa, kk, A_MN), operand_desc(sb, kk, B_MN), IDESC, first);
+              umma(d, operand_desc(sa, kk, A_MN), operand_desc(sb, kk, B_MN), IDESC_N(sg.bn), first);
 #else
               // 3xTF32: small cross terms first, then the main product
-              umma(d, operand_desc(sa + A_BYTES, kk, A_MN), operand_desc(sb, kk, B_MN), IDESC, first);
-              umma(d, operand_desc(sa, kk, A_MN), operand_desc(sb + B_BYTES, kk, B_MN), IDESC, 1u);
-              umma(d, operand_desc(sa, kk, A_MN), operand_desc(sb, kk, B_MN), IDESC, 1u);
+              umma(d, operand_desc(sa + A_BYTES, kk, A_MN), operand_desc(sb, kk, B_MN), IDESC_N(sg.bn), first);
+              umma(d, operand_desc(sa, kk, A_MN), operand_desc(sb + B_BYTES, kk, B_MN), IDESC_N(sg.bn), 1u);
+              umma(d, operand_desc(sa, kk, A_MN), operand_desc(sb, kk, B_MN), IDESC_N(sg.bn), 1u);
 #endif
             }
             // the stage is free once these MMAs have read it (in both CTAs of a pair)
@@ -474,7 +498,7 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
       const int m = m_blk * TILE_M + (int)rank * BM + q * 32 + lane;
       // epilogue and store of 16 consecutive outputs of this thread's row, from their accumulators
       auto finish16 = [&](int c, const float* accv) {
-        const int n0 = n_blk * BN + c * 16;
+        const int n0 = n_blk * BN + sg.n_off + c * 16;
         if (m < GM && n0 < GN) {
           __align__(16) JX_OUT_T res[16];
           const int g0 = (int)(((i64)b * GM + m) * GN + n0);
@@ -511,6 +535,7 @@ JX_EPILOGUE
         const u32 trow = tmem_base + ((u32)(q * 32) << 16) + acc_i * ACC_STRIDE;
         #pragma unroll
         for (int c = 0; c < EPI_COLS / 16; c++) {
+          if (HALF_LAST && (cg0 + c) * 16 >= sg.bn) break;   // a half tile has no columns for the second group
           u32 v[16];
           tmem_ld16(trow + (cg0 + c) * 16, v);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -535,6 +560,7 @@ JX_EPILOGUE
       #pragma unroll 1
 #endif
       for (int c = 0; c < EPI_COLS / 16; c++) {
+        if (HALF_LAST && (cg0 + c) * 16 >= sg.bn) break;
         u32 v[16];
         tmem_ld16(trow + (cg0 + c) * 16, v);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -750,7 +776,16 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
   os << "#define KIND " << kind << "\n#define ELEM " << e << "\n#define BM " << BM << "\n#define BN " << BN << "\n";
   os << "#define ACC_STRIDE " << (BN > 128 ? 256 : BN) << "\n";
   os << "#define A_SHARED " << ((g.batch > 1 && g.sAb == 0) ? 1 : 0) << "\n#define B_SHARED " << ((g.batch > 1 && g.sBb == 0) ? 1 : 0) << "\n";
-  os << "#define STREAMK " << (streamk ? 1 : 0) << "\n#define CTA_PAIR " << (pair ? 1 : 0) << "\n#define EPI_SPLIT " << epi_split << "\n";
+  // CTA pairs on 256-column tiles whose last wave is at most half full run it as half-width tiles
+  // (see get_segment; JAXCUDA_TC_HALF_LAST=0 keeps whole tiles)
+  const int64_t pairs_in_grid = std::min<int64_t>(tiles, opt.sm_count / 2);
+  // Measured: 3xTF32 8192 x 2048 x 2048 296 -> 284 us; f16 4096^3 103 -> 106 us (there a half tile
+  // costs 0.8 of a whole one and the tensor pipe, not shared memory, is the bound), so 3xTF32 only
+  // unless the option is 2.
+  const bool half_last = pair && b_mn && BN == 256 && (opt.tc_half_last == 2 || (opt.tc_half_last == 1 && kind == 2)) && tiles > pairs_in_grid &&
+                         tiles % pairs_in_grid != 0 && 2 * (tiles % pairs_in_grid) <= pairs_in_grid;
+  os << "#define STREAMK " << (streamk ? 1 : 0) << "\n#define CTA_PAIR " << (pair ? 1 : 0) << "\n#define EPI_SPLIT " << epi_split
+     << "\n#define HALF_LAST " << (half_last ? 1 : 0) << "\n";
   os << "#define SPIN_LIMIT " << std::max(1024, opt.tc_spin_limit) << "\n#define FAULT_SKIP_LOAD " << (opt.tc_fault == 1 ? 1 : 0) << "\n";
   // Gather warps of a convolution (B_GATHER): groups of four warps, each group filling every
   // gather_groups-th stage.  Never more groups than stages: a group waits for "stage free" by phase
@@ -860,7 +895,8 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
                   std::to_string(g.M) + "x" + std::to_string(g.N) + "x" + std::to_string(g.K) + " tile " + (pair ? "256x" : "128x") +
                   std::to_string(BN) + "x" + std::to_string(bk) + " stages=" + std::to_string(stages) + " A:" +
                   (a_mn ? "MN" : "K") + " B:" + (b_mn ? "MN" : "K") + " ctas=" + std::to_string(st.grid[0]) +
-                  (pair ? " cta-pairs" : "") + (lo_in_kernel ? " lo-in-kernel" : "") + (streamk ? " split-k" : "");
+                  (pair ? " cta-pairs" : "") + (half_last ? " half-tiles-last" : "") + (lo_in_kernel ? " lo-in-kernel" : "") +
+                  (streamk ? " split-k" : "");
   return true;
 }
 

@@ -479,6 +479,7 @@ int jaxcuda_create(int device, jaxcuda_ctx** out) {
   ctx->opt.ld_hint = env_int("JAXCUDA_LD_HINT", ctx->opt.ld_hint);
   ctx->opt.conv_implicit = env_int("JAXCUDA_CONV_IMPLICIT", ctx->opt.conv_implicit);
   ctx->opt.tc_lo_in_kernel = env_int("JAXCUDA_TC_LO_IN_KERNEL", ctx->opt.tc_lo_in_kernel);
+  ctx->opt.tc_half_last = env_int("JAXCUDA_TC_HALF_LAST", ctx->opt.tc_half_last);
   ctx->opt.tc_pair = ctx->drv.LaunchKernelEx ? env_int("JAXCUDA_TC_PAIR", ctx->opt.tc_pair) : 0;
   ctx->opt.row_tpr = env_int("JAXCUDA_ROW_TPR", ctx->opt.row_tpr);
   ctx->opt.row_unroll = env_int("JAXCUDA_ROW_UNROLL", ctx->opt.row_unroll);
