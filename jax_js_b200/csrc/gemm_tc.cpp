@@ -266,8 +266,8 @@ __device__ __forceinline__ void jx_gather_tile(JX_PARAMS, u32 sb, int b, int n_t
 #define EPI_COLS (BN / EPI_SPLIT)
 #define NTHREADS (64 + 128 * EPI_SPLIT + 32 * (GATHER_WARPS + XFORM_WARPS))
 #define GROUP_WARPS (GATHER_WARPS / GATHER_GROUPS)
-#if HALF_LAST && (!CTA_PAIR || !B_MN || BN < 256)
-#error "half tiles in the last wave: CTA pairs on 256-column tiles with B read as [K, N]"
+#if HALF_LAST && (!CTA_PAIR || BN < 256)
+#error "half tiles in the last wave: CTA pairs on 256-column tiles"
 #endif
 #if EPI_SPLIT > 1 && (STREAMK || B_GATHER || LO_IN_KERNEL)
 #error "a second group of epilogue warps takes the place of the gather and remainder-tile warps"
@@ -343,7 +343,7 @@ jx_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
           if (it >= STAGES && !mbar_wait(empty(s), ((it / STAGES) + 1) & 1, status)) { atomicCAS((int*)status_ptr, 0, 1); failed = true; break; }
           if (!CTA_PAIR) mbar_expect_tx(tma_bar(s), TX_BYTES);
           else if (rank == 0)   // both CTAs' loads report to the even CTA's barrier
-            mbar_expect_tx(full(s), 2 * (TX_BYTES - (HALF_LAST ? (BN - sg.bn) / 2 * 128 * TMA_PLANES : 0)));
+            mbar_expect_tx(full(s), 2 * (TX_BYTES - ((HALF_LAST && B_MN) ? (BN - sg.bn) / 2 * 128 * TMA_PLANES : 0)));   // (a K-major box of B is always B_COLS rows: a half tile uses the first half of it)
 #if FAULT_SKIP_LOAD
           // test of the wind-down: CTA 0 announces its second stage and never loads it, so the MMA
           // role's bounded wait on that stage runs out
@@ -782,7 +782,7 @@ bool plan_gemm_tc(const KernelIR& k, const GemmDesc& g, const Options& opt, Plan
   // Measured: 3xTF32 8192 x 2048 x 2048 296 -> 284 us; f16 4096^3 103 -> 106 us (there a half tile
   // costs 0.8 of a whole one and the tensor pipe, not shared memory, is the bound), so 3xTF32 only
   // unless the option is 2.
-  const bool half_last = pair && b_mn && BN == 256 && (opt.tc_half_last == 2 || (opt.tc_half_last == 1 && kind == 2)) && tiles > pairs_in_grid &&
+  const bool half_last = pair && BN == 256 && (opt.tc_half_last == 2 || (opt.tc_half_last == 1 && kind == 2)) && tiles > pairs_in_grid &&
                          tiles % pairs_in_grid != 0 && 2 * (tiles % pairs_in_grid) <= pairs_in_grid;
   os << "#define STREAMK " << (streamk ? 1 : 0) << "\n#define CTA_PAIR " << (pair ? 1 : 0) << "\n#define EPI_SPLIT " << epi_split
      << "\n#define HALF_LAST " << (half_last ? 1 : 0) << "\n";

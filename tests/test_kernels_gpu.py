@@ -433,7 +433,8 @@ def test_remainder_tiles_made_in_the_kernel_match_the_split_pass(backend):
     (2304, 2304, 160, F16, "km-nk"),     # A read as [K, M], B as [N, K]
     (4864, 1100, 96, F32, "mk-kn"),      # 3xTF32 pairs on 256 x 256 tiles (two groups of epilogue warps), N tail
     (2048, 2048, 544, F32, "km-kn"),     # the weight-gradient shape: A read as [K, M], 64 pair tiles, three chunks of K
-    (6912, 1024, 96, F32, "mk-kn")])     # 27 x 4 = 108 pair tiles on 74 pairs: the last 34 run as 68 half-width tiles
+    (6912, 1024, 96, F32, "mk-kn"),      # 27 x 4 = 108 pair tiles on 74 pairs: the last 34 run as 68 half-width tiles
+    (6912, 1024, 96, F32, "mk-nk")])     # the same with B read as [N, K]: a half tile uses the first half of its box of B
 def test_gemm_on_cta_pairs_matches_single_ctas(backend, m, n, kk, dt, layout):
     """Two CTAs of a cluster on one 256-row tile (tcgen05 cta_group::2, each CTA loading half of B's
     columns): every output accumulates the same products in the same order as on single CTAs, so the
