@@ -194,6 +194,45 @@ Napi::Value Dispatch(const Napi::CallbackInfo& info) {
                                                         out.Data(), (int)out.ElementLength()));
 }
 
+jaxcuda_graph* Graph(const Napi::Value& v) {
+  bool lossless;
+  return reinterpret_cast<jaxcuda_graph*>((uintptr_t)v.As<Napi::BigInt>().Uint64Value(&lossless));
+}
+
+// Replay of a static step list as one CUDA graph (the counterpart of JitProgram.execute,
+// src/frontend/jit.ts:111-162): between captureBegin and captureEnd the calls above are recorded.
+Napi::Value CaptureBegin(const Napi::CallbackInfo& info) {
+  if (jaxcuda_capture_begin(Ctx(info[0])) != JAXCUDA_OK) Throw(info.Env(), Ctx(info[0]));
+  return info.Env().Undefined();
+}
+Napi::Value CaptureEnd(const Napi::CallbackInfo& info) {
+  jaxcuda_graph* graph = nullptr;
+  if (jaxcuda_capture_end(Ctx(info[0]), &graph) != JAXCUDA_OK) Throw(info.Env(), Ctx(info[0]));
+  return Handle(info.Env(), graph);
+}
+Napi::Value GraphLaunch(const Napi::CallbackInfo& info) {
+  jaxcuda_graph* graph = Graph(info[1]);
+  if (jaxcuda_graph_launch(Ctx(info[0]), graph) != JAXCUDA_OK) Throw(info.Env(), Ctx(info[0]));
+  return info.Env().Undefined();
+}
+Napi::Value GraphDestroy(const Napi::CallbackInfo& info) {
+  jaxcuda_graph* graph = Graph(info[1]);
+  if (jaxcuda_graph_destroy(Ctx(info[0]), graph) != JAXCUDA_OK) Throw(info.Env(), Ctx(info[0]));
+  return info.Env().Undefined();
+}
+Napi::Value GraphCost(const Napi::CallbackInfo& info) {   // what JitProgram.toString() would print about the replay
+  jaxcuda_graph* graph = Graph(info[0]);
+  uint64_t launches = 0;
+  double bytes = 0;
+  int fused = 0;
+  jaxcuda_graph_cost(graph, &launches, &bytes, &fused);
+  auto out = Napi::Object::New(info.Env());
+  out.Set("launches", Napi::Number::New(info.Env(), (double)launches));
+  out.Set("bytes", Napi::Number::New(info.Env(), bytes));
+  out.Set("fusedRuns", Napi::Number::New(info.Env(), fused));
+  return out;
+}
+
 Napi::Object Init(Napi::Env env, Napi::Object exports) {
   exports.Set("create", Napi::Function::New(env, Create));
   exports.Set("destroy", Napi::Function::New(env, Destroy));
@@ -206,6 +245,11 @@ Napi::Object Init(Napi::Env env, Napi::Object exports) {
   exports.Set("prepareKernel", Napi::Function::New(env, PrepareKernel));
   exports.Set("prepareRoutine", Napi::Function::New(env, PrepareRoutine));
   exports.Set("dispatch", Napi::Function::New(env, Dispatch));
+  exports.Set("captureBegin", Napi::Function::New(env, CaptureBegin));
+  exports.Set("captureEnd", Napi::Function::New(env, CaptureEnd));
+  exports.Set("graphLaunch", Napi::Function::New(env, GraphLaunch));
+  exports.Set("graphDestroy", Napi::Function::New(env, GraphDestroy));
+  exports.Set("graphCost", Napi::Function::New(env, GraphCost));
   return exports;
 }
 

@@ -36,6 +36,11 @@ interface Native {
   prepareKernel(ctx: bigint, image: Uint8Array, hash: bigint): bigint;
   prepareRoutine(ctx: bigint, name: string, type: unknown, params: string): bigint;
   dispatch(ctx: bigint, exe: bigint, inputs: Uint32Array, outputs: Uint32Array): number;
+  captureBegin(ctx: bigint): void;
+  captureEnd(ctx: bigint): bigint;
+  graphLaunch(ctx: bigint, graph: bigint): void;
+  graphDestroy(ctx: bigint, graph: bigint): void;
+  graphCost(graph: bigint): { launches: number; bytes: number; fusedRuns: number };
 }
 
 // Codes of include/jaxcuda_ir.h, in the declaration order of AluOp (src/alu.ts:1365-1407).
@@ -172,5 +177,27 @@ export class CudaBackend implements Backend {
 
   dispatch(exe: Executable<bigint>, inputs: Slot[], outputs: Slot[]): void {
     this.#check(this.native.dispatch(this.ctx, exe.data, Uint32Array.from(inputs), Uint32Array.from(outputs)));
+  }
+
+  /**
+   * Beyond `Backend`: records `steps` (the malloc / dispatch / decRef calls of one
+   * `JitProgram.execute`, src/frontend/jit.ts:111-162) as a CUDA graph and returns a function that
+   * replays it.  Slots alive when `steps` returns keep their addresses and are rewritten by every
+   * replay.  Inside the recording the backend fuses what the list allows (rows of softmax-like
+   * chains, producers into their only consumer, runs of small kernels).
+   */
+  record(steps: () => void): { replay: () => void; destroy: () => void; cost: { launches: number; bytes: number; fusedRuns: number } } {
+    this.native.captureBegin(this.ctx);
+    let graph: bigint;
+    try {
+      steps();
+    } finally {
+      graph = this.native.captureEnd(this.ctx);
+    }
+    return {
+      replay: () => this.native.graphLaunch(this.ctx, graph),
+      destroy: () => this.native.graphDestroy(this.ctx, graph),
+      cost: this.native.graphCost(graph),
+    };
   }
 }
