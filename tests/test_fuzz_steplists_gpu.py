@@ -127,3 +127,93 @@ def test_random_step_lists_replay_the_bits_of_their_kernels(backend, seed, rows,
     backend.graph_destroy(graph)
     for s in list(outs.values()) + list(slots.values()):
         backend.dec_ref(s)
+
+
+def _make_dot_list(rng, M, N, K, n_kernels):
+    """Lists around Dot Kernels: operands [M, K] ("a") and [K, N] ("b"), results and other matrices
+    [M, N] ("c").  Dots reuse operands (the remainder planes of a captured list are shared), their
+    results feed elementwise Kernels once (epilogue fusion) or several times, arrays are rescaled in
+    between (a plane must not outlive the values it was made from)."""
+    from jax_js_b200 import programs as P
+    live = {"a0": "a", "b0": "b", "c0": "c"}
+    steps = []
+    mn = M * N
+
+    def ew(kind_size, ins, e):
+        return Kernel(len(ins), kind_size, e)
+
+    for s in range(n_kernels):
+        out = f"t{s}"
+        names = sorted(live)
+        pick = rng.random()
+        a_s = [nm for nm in names if live[nm] == "a"]
+        b_s = [nm for nm in names if live[nm] == "b"]
+        c_s = [nm for nm in names if live[nm] == "c"]
+        if pick < 0.35:
+            a, b = a_s[int(rng.integers(len(a_s)))], b_s[int(rng.integers(len(b_s)))]
+            steps.append((P.dot_kernel(M, N, K), [a, b], out, "c"))
+            live[out] = "c"
+        elif pick < 0.5:       # a new operand made from an old one
+            kind = "a" if rng.random() < 0.5 else "b"
+            src = (a_s if kind == "a" else b_s)
+            src = src[int(rng.integers(len(src)))]
+            size = M * K if kind == "a" else K * N
+            e = AluExp.mul(AluExp.global_index(F32, 0, size, g), AluExp.f32(float(rng.choice([0.5, -1.25, 2.0]))))
+            steps.append((ew(size, [src], e), [src], out, kind))
+            live[out] = kind
+        else:                  # elementwise over [M, N]: gate, sum or product of one or two matrices
+            k_in = 1 if rng.random() < 0.4 else 2
+            ins = list(dict.fromkeys(c_s[int(rng.integers(len(c_s)))] for _ in range(k_in)))
+            terms = [AluExp.global_index(F32, j, mn, g) for j in range(len(ins))]
+            if len(terms) == 2:
+                e = AluExp.where(AluExp.cmplt(terms[1], AluExp.f32(0.0)), AluExp.f32(0.0), terms[0]) if rng.random() < 0.5 \
+                    else AluExp.add(terms[0], terms[1])
+            else:
+                e = AluExp.max(terms[0], AluExp.f32(0.0)) if rng.random() < 0.5 else AluExp.mul(terms[0], AluExp.f32(0.125))
+            steps.append((ew(mn, ins, e), ins, out, "c"))
+            live[out] = "c"
+    return steps, ["a0", "b0", "c0"]
+
+
+@pytest.mark.parametrize("seed,M,N,K", [(1, 256, 256, 128), (2, 4096, 1024, 96), (3, 512, 384, 64), (4, 4096, 1024, 160),
+                                        (5, 1024, 512, 4096), (6, 2048, 2048, 64)])
+def test_random_lists_around_dots_replay_the_bits_of_their_kernels(backend, seed, M, N, K):
+    rng = np.random.default_rng(100 + seed)
+    steps, inputs = _make_dot_list(rng, M, N, K, 12)
+    last_use = {}
+    for idx, (_, ins, out, _) in enumerate(steps):
+        for nm in ins:
+            last_use[nm] = idx
+    keep = {out for _, _, out, _ in steps if rng.random() < 0.3} | {steps[-1][2]}
+    sizes = {"a": M * K, "b": K * N, "c": M * N}
+    data = {"a0": rng.standard_normal(M * K), "b0": rng.uniform(-1, 1, K * N), "c0": rng.standard_normal(M * N)}
+    exes = [backend.prepare_kernel(k) for k, _, _, _ in steps]
+
+    def run(slots):
+        env = dict(slots)
+        for idx, ((k, ins, out, kind), exe) in enumerate(zip(steps, exes)):
+            env[out] = backend.malloc(sizes[kind] * 4)
+            backend.dispatch(exe, [env[nm] for nm in ins], [env[out]])
+            for nm in list(env):
+                if nm not in slots and nm not in keep and last_use.get(nm, -1) <= idx and nm != out:
+                    backend.dec_ref(env.pop(nm))
+            if out not in keep and out not in last_use:
+                backend.dec_ref(env.pop(out))
+        return {nm: s for nm, s in env.items() if nm not in slots}
+
+    slots = {nm: backend.put(data[nm].astype(np.float32)) for nm in inputs}
+    eager = run(slots)
+    want = {nm: backend.read_sync(s).copy() for nm, s in eager.items()}
+    for s in eager.values():
+        backend.dec_ref(s)
+    backend.capture_begin()
+    outs = run(slots)
+    graph = backend.capture_end()
+    for _ in range(2):
+        backend.graph_launch(graph)
+    assert set(outs) == set(want)
+    for nm, s in outs.items():
+        assert np.array_equal(backend.read_sync(s), want[nm]), (nm, backend.graph_cost(graph))
+    backend.graph_destroy(graph)
+    for s in list(outs.values()) + list(slots.values()):
+        backend.dec_ref(s)
