@@ -357,6 +357,37 @@ def test_convolution_kernel_on_the_tensor_pipe(backend, N, Ci, H, W, Co, KH, KW,
     assert_close(got, ref, 1e-5 if dt == F32 else 2e-3, np.abs(ref).max(), "conv vs float64")
 
 
+def _random_conv_shapes(n, seed):
+    rng = np.random.default_rng(seed)
+    out = []
+    while len(out) < n:
+        N, Ci = int(rng.choice([2, 4, 6, 8, 12, 16])), int(rng.choice([8, 24, 32, 40, 64, 72, 96, 128]))
+        H, W, Co = int(rng.integers(8, 40)), int(rng.integers(8, 40)), int(rng.choice([32, 64, 80, 128, 136, 200, 256]))
+        KH, KW, stride, pad = int(rng.integers(1, 6)), int(rng.integers(1, 6)), int(rng.choice([1, 1, 2, 3])), int(rng.integers(0, 3))
+        if H + 2 * pad >= KH and W + 2 * pad >= KW:
+            out.append((N, Ci, H, W, Co, KH, KW, stride, pad, F32 if rng.random() < 0.6 else F16))
+    return out
+
+
+@pytest.mark.parametrize("N,Ci,H,W,Co,KH,KW,stride,pad,dt", _random_conv_shapes(24, 10))
+def test_random_convolutions_against_float64(backend, N, Ci, H, W, Co, KH, KW, stride, pad, dt):
+    """Random shapes, filters that are not square, strides 1..3 and paddings 0..2, on whichever skeleton
+    the planner takes (generic reductions or the implicit GEMM), against the sum in float64."""
+    rng = np.random.default_rng(1)
+    npdt = np.float32 if dt == F32 else np.float16
+    x = (rng.standard_normal((N, Ci, H, W)) * (1.0 if dt == F32 else 0.25)).astype(npdt)
+    w = (rng.standard_normal((Co, Ci, KH, KW)) * (1.0 if dt == F32 else 0.05)).astype(npdt)
+    k, (OH, OW) = _conv_kernel(N, Ci, H, W, Co, KH, KW, stride, pad, dt)
+    got = run_cuda(backend, k, [x, w]).astype(np.float64).reshape(N, Co, OH, OW)
+    xp = np.pad(x.astype(np.float64), ((0, 0), (0, 0), (pad, pad), (pad, pad)))
+    ref = np.zeros((N, Co, OH, OW))
+    for kh in range(KH):
+        for kw in range(KW):
+            ref += np.einsum("nchw,oc->nohw", xp[:, :, kh: kh + stride * (OH - 1) + 1: stride, kw: kw + stride * (OW - 1) + 1: stride],
+                             w[:, :, kh, kw].astype(np.float64), optimize=True)
+    assert_close(got, ref, 1e-5 if dt == F32 else 2e-3, np.abs(ref).max(), backend.prepare_kernel(k).describe)
+
+
 def test_convolution_gather_routes_agree_and_repeat(backend):
     """The patch operand is gathered inside the GEMM kernel (the default) or by a stage of its own
     through global memory (JAXCUDA_CONV_IMPLICIT=0): the same values enter the same MMAs, so the
