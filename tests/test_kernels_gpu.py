@@ -458,6 +458,42 @@ def test_remainder_tiles_made_in_the_kernel_match_the_split_pass(backend):
     assert_close(got["2"].reshape(m, n) / kk, want / kk, 1e-5, 1.0, "3xTF32 with in-kernel remainder tiles")
 
 
+def _random_dot_shapes(n, seed):
+    rng = np.random.default_rng(seed)
+    dims = [8, 24, 77, 250, 1001, 130, 64, 96, 128, 136, 200, 256, 320, 384, 512, 520, 768, 1000, 1024, 1536, 2048, 3000, 4096]
+    ks = [8, 20, 33, 100, 1001, 32, 40, 64, 72, 96, 128, 136, 256, 520, 1024, 2048, 4096, 8192]
+    out = []
+    while len(out) < n:
+        M, N, K, batch = int(rng.choice(dims)), int(rng.choice(dims)), int(rng.choice(ks)), int(rng.choice([1, 1, 1, 2, 3, 8]))
+        if batch * M * N * K <= 2 ** 32 and batch * (M * K + K * N + M * N) <= 2 ** 26:
+            out.append((M, N, K, F32 if rng.random() < 0.55 else F16, str(rng.choice(["mk", "km"])), str(rng.choice(["kn", "nk"])), batch,
+                        bool(rng.random() < 0.3), bool(rng.random() < 0.3), bool(rng.random() < 0.15)))
+    return out
+
+
+@pytest.mark.parametrize("M,N,K,dt,al,bl,batch,bias,relu,swap", _random_dot_shapes(40, 3))
+def test_random_dots_against_float64(backend, M, N, K, dt, al, bl, batch, bias, relu, swap):
+    """Random extents (tails in M, N and K, strides that rule TMA out), layouts, batches and epilogues, on
+    whichever skeleton the planner takes for them, against the product in float64."""
+    rng = np.random.default_rng(1)
+    npdt = np.float32 if dt == F32 else np.float16
+    a = (rng.standard_normal((batch, M, K)) * (1.0 if dt == F32 else 0.25)).astype(npdt)
+    b = (rng.standard_normal((batch, K, N)) / np.sqrt(K)).astype(npdt)
+    ins = [a if al == "mk" else np.ascontiguousarray(a.transpose(0, 2, 1)), b if bl == "kn" else np.ascontiguousarray(b.transpose(0, 2, 1))]
+    bv = rng.standard_normal(N).astype(npdt)
+    if bias:
+        ins.append(bv)
+    k = P.dot_kernel(M, N, K, dt, a_layout=al, b_layout=bl, batch=batch, bias=bias, relu=relu, swap=swap)
+    got = run_cuda(backend, k, ins).astype(np.float64).reshape(batch, M, N)
+    ref = np.matmul(a.astype(np.float64), b.astype(np.float64))
+    scale = np.abs(ref).max()
+    if bias:
+        ref = ref + bv.astype(np.float64)
+    if relu:
+        ref = np.maximum(ref, 0)
+    assert_close(got, ref, 2e-5 if dt == F32 else 3e-3, scale, backend.prepare_kernel(k).describe)
+
+
 @pytest.mark.parametrize("m,n,kk,dt,layout", [
     (2304, 2304, 192, F16, "mk-kn"),     # 9 x 9 tiles of 256 x 256 on 74 pairs: two waves, the second ragged
     (2200, 2120, 200, F16, "mk-kn"),     # M, N and K tails: the odd CTA of the last pair row holds 24 valid rows
