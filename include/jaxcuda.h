@@ -32,7 +32,8 @@ typedef enum {
   JAXCUDA_EINVAL = 3,       /* plain Error: size mismatch, bad image, bad range (src/backend/cpu.ts:21-24) */
   JAXCUDA_ECOMPILE = 4,     /* NVRTC rejected generated source */
   JAXCUDA_ECUDA = 5,        /* a CUDA or NCCL call failed */
-  JAXCUDA_ENOMEM = 6
+  JAXCUDA_ENOMEM = 6,
+  JAXCUDA_ETIMEOUT = 7      /* jaxcuda_comm_wait: the work is still running; nothing was cancelled */
 } jaxcuda_status;
 
 typedef struct jaxcuda_ctx jaxcuda_ctx;
@@ -220,6 +221,19 @@ int jaxcuda_allreduce_sum_f32(jaxcuda_ctx* ctx, const jaxcuda_slot* slots, int n
 int jaxcuda_allreduce_sum_f32_async(jaxcuda_ctx* ctx, const jaxcuda_slot* slots, int n);
 int jaxcuda_comm_join(jaxcuda_ctx* ctx);
 int jaxcuda_comm_destroy(jaxcuda_ctx* ctx);
+/* Failure detection for the sums.  A sum whose peer is late or gone never finishes, and a plain
+ * read or sync behind it would block for ever.  jaxcuda_comm_wait blocks the host until
+ * everything issued so far on the context's stream and on the sums' stream has finished, for at
+ * most timeout_ms, and polls the communicator's asynchronous error state (ncclCommGetAsyncError)
+ * meanwhile.  JAXCUDA_OK: all done.  JAXCUDA_ETIMEOUT: still running; nothing was cancelled, the
+ * call may be repeated, or the caller gives up with jaxcuda_comm_abort.  JAXCUDA_ECUDA: NCCL
+ * reported an error; the communicator has been aborted and later sums fail until
+ * jaxcuda_comm_init is called again.  Not allowed inside a capture.
+ * jaxcuda_comm_abort (ncclCommAbort) ends this rank's part of the communicator without waiting
+ * for the peers: NCCL kernels of this rank that still wait for a peer return, so the context's
+ * streams drain and the context stays usable. */
+int jaxcuda_comm_wait(jaxcuda_ctx* ctx, int timeout_ms);
+int jaxcuda_comm_abort(jaxcuda_ctx* ctx);
 
 /* Sort along the last axis of a contiguous [batch, n] device array without allocating anything.
  * No counterpart in the reference.  It is for embedders that cannot let the library call

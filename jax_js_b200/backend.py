@@ -23,7 +23,7 @@ _HERE = Path(__file__).resolve().parent
 _LIB_PATH = _HERE / "libjaxcuda.so"
 _lib = None
 
-OK, ESLOT, EUNSUPPORTED, EINVAL, ECOMPILE, ECUDA, ENOMEM = range(7)
+OK, ESLOT, EUNSUPPORTED, EINVAL, ECOMPILE, ECUDA, ENOMEM, ETIMEOUT = range(8)
 SIZE_MAX = ctypes.c_size_t(-1).value
 
 
@@ -94,6 +94,8 @@ SYMBOLS = {
     "jaxcuda_allreduce_sum_f32_async": (_I, [_P, ctypes.POINTER(_U32), _I]),
     "jaxcuda_comm_join": (_I, [_P]),
     "jaxcuda_comm_destroy": (_I, [_P]),
+    "jaxcuda_comm_wait": (_I, [_P, _I]),
+    "jaxcuda_comm_abort": (_I, [_P]),
     "jaxcuda_capture_begin": (_I, [_P]),
     "jaxcuda_capture_end": (_I, [_P, ctypes.POINTER(_P)]),
     "jaxcuda_graph_launch": (_I, [_P, _P]),
@@ -184,6 +186,8 @@ def _raise(status: int, message: str):
         raise CompileError(message)
     if status == ENOMEM:
         raise MemoryError(message)
+    if status == ETIMEOUT:
+        raise TimeoutError(message)
     raise CudaError(message)
 
 
@@ -412,6 +416,16 @@ class CudaBackend:
 
     def comm_join(self) -> None:
         self._check(self._lib.jaxcuda_comm_join(self._ctx))
+
+    def comm_wait(self, timeout_ms: int) -> None:
+        """Block until everything issued so far (sums included) has finished.  Raises TimeoutError
+        after `timeout_ms` (a peer is late or gone; nothing was cancelled) and CudaError when NCCL
+        reports an error, in which case the communicator has been aborted."""
+        self._check(self._lib.jaxcuda_comm_wait(self._ctx, int(timeout_ms)))
+
+    def comm_abort(self) -> None:
+        """Leave the communicator without waiting for the peers (ncclCommAbort)."""
+        self._check(self._lib.jaxcuda_comm_abort(self._ctx))
 
     # -- captured step lists ---------------------------------------------------------------
     def capture_begin(self) -> None:

@@ -10,6 +10,7 @@
 #include <dlfcn.h>
 #include <nvrtc.h>
 
+#include <chrono>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -19,6 +20,7 @@
 #include <mutex>
 #include <stdexcept>
 #include <string>
+#include <thread>
 #include <unordered_map>
 #include <vector>
 
@@ -258,6 +260,7 @@ struct jaxcuda_ctx {
   // second stream for sums that run under later kernels (jaxcuda_allreduce_sum_f32_async)
   cudaStream_t comm_stream = nullptr;
   cudaEvent_t comm_fork = nullptr, comm_done = nullptr;
+  cudaEvent_t wait_compute = nullptr, wait_comm = nullptr;   // jaxcuda_comm_wait's probes
   bool comm_pending = false;
   // copy streams of the asynchronous read / write calls, so that uploads, kernels and downloads of
   // consecutive steps overlap (the GPU has separate copy engines per direction)
@@ -522,6 +525,8 @@ int jaxcuda_destroy(jaxcuda_ctx* ctx) {
     for (cudaEvent_t ev : ctx->comm_events) cudaEventDestroy(ev);
     cudaStreamDestroy(ctx->comm_stream);
   }
+  if (ctx->wait_compute) cudaEventDestroy(ctx->wait_compute);
+  if (ctx->wait_comm) cudaEventDestroy(ctx->wait_comm);
   jaxcuda_comm_destroy(ctx);
   for (auto& kv : ctx->kernels) free_exe(ctx, kv.second.get());
   for (auto& ev : ctx->events) if (ev) cudaEventDestroy(ev);
@@ -1835,6 +1840,7 @@ typedef int (*nccl_allreduce_t)(const void*, void*, size_t, int, int, void*, cud
 typedef int (*nccl_destroy_t)(void*);
 typedef int (*nccl_group_t)(void);
 typedef const char* (*nccl_errstr_t)(int);
+typedef int (*nccl_async_err_t)(void*, int*);
 
 static void* nccl_handle(jaxcuda_ctx* ctx) {
   static void* h = nullptr;
@@ -1958,6 +1964,59 @@ static int allreduce_on(jaxcuda_ctx* ctx, const jaxcuda_slot* slots, int n, cuda
   if (r == 0) r = r2;
   if (r != 0) return fail(ctx, JAXCUDA_ECUDA, "ncclAllReduce: %s", errstr ? errstr(r) : "error");
   return JAXCUDA_OK;
+}
+
+// Asynchronous error state of the communicator (ncclCommGetAsyncError).  A communicator that reports
+// an error is aborted (ncclCommAbort returns without waiting for the peers, and ends the NCCL kernels
+// of this rank that still wait for them) and the context goes back to "no communicator".
+static int poll_comm(jaxcuda_ctx* ctx) {
+  if (!ctx->comm) return JAXCUDA_OK;
+  auto async_err = (nccl_async_err_t)dlsym(ctx->nccl_lib, "ncclCommGetAsyncError");
+  if (!async_err) return JAXCUDA_OK;
+  int state = 0;
+  int r = async_err(ctx->comm, &state);
+  if (r == 0 && (state == 0 || state == /*ncclInProgress*/ 7)) return JAXCUDA_OK;
+  auto errstr = (nccl_errstr_t)dlsym(ctx->nccl_lib, "ncclGetErrorString");
+  const int code = r != 0 ? r : state;
+  std::string what = errstr ? errstr(code) : "error";
+  jaxcuda_comm_abort(ctx);
+  return fail(ctx, JAXCUDA_ECUDA, "NCCL communicator failed (%s) and was aborted", what.c_str());
+}
+
+int jaxcuda_comm_abort(jaxcuda_ctx* ctx) {
+  if (!ctx) return JAXCUDA_EINVAL;
+  if (!ctx->comm) return JAXCUDA_OK;
+  auto abort_ = (nccl_destroy_t)dlsym(ctx->nccl_lib, "ncclCommAbort");
+  if (abort_) abort_(ctx->comm);
+  ctx->comm = nullptr;
+  ctx->nranks = 0;   // sums now fail with "communicator not initialised" instead of passing as one rank
+  return JAXCUDA_OK;
+}
+
+int jaxcuda_comm_wait(jaxcuda_ctx* ctx, int timeout_ms) {
+  if (!ctx || timeout_ms < 0) return JAXCUDA_EINVAL;
+  if (ctx->alloc.capturing) return fail(ctx, JAXCUDA_EINVAL, "comm_wait inside a capture");
+  cudaSetDevice(ctx->device);
+  if (int rc = flush_pending(ctx)) return rc;
+  if (!ctx->wait_compute) {
+    CUDA_TRY(ctx, cudaEventCreateWithFlags(&ctx->wait_compute, cudaEventDisableTiming));
+    CUDA_TRY(ctx, cudaEventCreateWithFlags(&ctx->wait_comm, cudaEventDisableTiming));
+  }
+  CUDA_TRY(ctx, cudaEventRecord(ctx->wait_compute, ctx->stream));
+  if (ctx->comm_stream) CUDA_TRY(ctx, cudaEventRecord(ctx->wait_comm, ctx->comm_stream));
+  const auto t0 = std::chrono::steady_clock::now();
+  for (int spins = 0;; spins++) {
+    cudaError_t a = cudaEventQuery(ctx->wait_compute);
+    cudaError_t b = ctx->comm_stream ? cudaEventQuery(ctx->wait_comm) : cudaSuccess;
+    if (a != cudaSuccess && a != cudaErrorNotReady) return fail(ctx, JAXCUDA_ECUDA, "comm_wait: %s", cudaGetErrorString(a));
+    if (b != cudaSuccess && b != cudaErrorNotReady) return fail(ctx, JAXCUDA_ECUDA, "comm_wait: %s", cudaGetErrorString(b));
+    if (int rc = poll_comm(ctx)) return rc;
+    if (a == cudaSuccess && b == cudaSuccess) return JAXCUDA_OK;
+    const auto waited = std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - t0).count();
+    if (waited >= (long long)timeout_ms * 1000)
+      return fail(ctx, JAXCUDA_ETIMEOUT, "work issued before comm_wait has not finished after %d ms", timeout_ms);
+    if (spins > 200) std::this_thread::sleep_for(std::chrono::microseconds(100));
+  }
 }
 
 int jaxcuda_comm_destroy(jaxcuda_ctx* ctx) {

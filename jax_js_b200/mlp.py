@@ -433,6 +433,14 @@ class MlpTrainer:
         self.params, self.mu, self.nu = list(new[1::3]), list(new[2::3]), list(new[3::3])
         return loss
 
+    def wait(self, timeout_ms: int) -> None:
+        """Watchdog for the steps issued so far.  A gradient sum whose peer is late or gone never
+        finishes, and reading the loss behind it would block for ever; this returns once the steps have
+        finished, raises TimeoutError after `timeout_ms` (the caller may wait again or leave the
+        communicator with `backend.comm_abort()`), and raises the backend's error when the
+        communication library reports a failure (the communicator is then already aborted)."""
+        self.be.comm_wait(timeout_ms)
+
     def close(self):
         if getattr(self, "graphs", None):
             for g, l in zip(self.graphs, self.graph_loss):

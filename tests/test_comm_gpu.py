@@ -100,3 +100,80 @@ def test_a_reader_waits_for_the_sum_of_its_operand_only(solo):
     solo.graph_destroy(graph)
     for s in (a, b, c, d, e):
         solo.dec_ref(s)
+
+
+def test_comm_wait_returns_when_the_sums_are_done_and_times_out_while_they_run(solo):
+    """The watchdog wait on a healthy communicator: with a zero limit it reports work still running
+    (and cancels nothing), with a generous one it returns once the queue has drained."""
+    n = 1 << 26
+    inc = _inc(solo, n)
+    a, b = solo.put(np.zeros(n, np.float32)), solo.malloc(n * 4)
+    solo.comm_wait(10000)
+    for _ in range(50):                         # some milliseconds of queued work, the sum in the middle
+        solo.dispatch(inc, [a], [b])
+    solo.allreduce_sum_f32_async([b])
+    for _ in range(50):
+        solo.dispatch(inc, [a], [b])
+    with pytest.raises(TimeoutError):
+        solo.comm_wait(0)
+    solo.comm_wait(10000)
+    assert (solo.get(b, F32) == 1).all()
+    solo.capture_begin()
+    with pytest.raises(ValueError):
+        solo.comm_wait(10)
+    solo.graph_destroy(solo.capture_end())
+    for s in (a, b):
+        solo.dec_ref(s)
+
+
+def test_an_error_reported_by_nccl_aborts_the_communicator(tmp_path):
+    """Failure made on the host: a stand-in NCCL library whose asynchronous error state the test
+    sets.  comm_wait reports it, the communicator is aborted, later sums are refused and the context
+    still runs Kernels."""
+    import os
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    lib = tmp_path / "libfakenccl.so"
+    subprocess.run(["gcc", "-shared", "-fPIC", "-O1", "-o", str(lib), os.path.join(here, "fake_nccl.c")], check=True)
+    script = r"""
+import os, sys
+import numpy as np
+sys.path.insert(0, os.environ["REPO_ROOT"])
+from jax_js_b200 import DType
+from jax_js_b200.alu import AluExp, AluVar, Kernel
+from jax_js_b200.backend import CudaBackend, CudaError
+be = CudaBackend(0)
+be.comm_init(1, 2, CudaBackend.comm_unique_id())
+n = 4096
+inc = be.prepare_kernel(Kernel(1, n, AluExp.add(AluExp.global_index(DType.Float32, 0, n, AluVar.gidx), AluExp.f32(1))))
+a, b = be.put(np.zeros(n, np.float32)), be.malloc(n * 4)
+be.dispatch(inc, [a], [b])
+be.allreduce_sum_f32_async([b])
+be.comm_wait(5000)
+print("healthy")
+open(os.environ["FAKE_NCCL_FLAG"], "w").write("6")
+try:
+    be.comm_wait(5000)
+    print("no error seen")
+except CudaError as e:
+    print("error:", e)
+try:
+    be.allreduce_sum_f32([b])
+    print("sum accepted")
+except ValueError as e:
+    print("refused:", e)
+be.dispatch(inc, [b], [a])
+print("value", float(be.get(a, DType.Float32)[0]))
+be.close()
+"""
+    env = dict(os.environ, JAXCUDA_NCCL_LIB=str(lib), FAKE_NCCL_FLAG=str(tmp_path / "flag"), FAKE_NCCL_ABORTED=str(tmp_path / "aborted"),
+               REPO_ROOT=os.path.dirname(here))
+    out = subprocess.run([sys.executable, "-c", script], env=env, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = out.stdout.strip().splitlines()
+    assert lines[0] == "healthy"
+    assert lines[1].startswith("error:") and "remote process exited" in lines[1] and "aborted" in lines[1], lines
+    assert lines[2].startswith("refused:") and "not initialised" in lines[2], lines
+    assert lines[3] == "value 2.0", lines
+    assert (tmp_path / "aborted").read_text() == "aborted"
