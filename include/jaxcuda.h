@@ -152,6 +152,22 @@ int jaxcuda_sync(jaxcuda_ctx* ctx);
  * WebGPU timestamp queries, src/backend/webgpu/tracing.ts:11-164): records an event now. */
 int jaxcuda_event_record(jaxcuda_ctx* ctx, int index); /* index in [0, 65536) */
 int jaxcuda_event_elapsed_ms(jaxcuda_ctx* ctx, int start_index, int stop_index, float* ms);
+
+/* Per-dispatch tracing: profiler.startTrace / stopTrace flip a flag (src/tracing.ts:15-33) and a
+ * backend that sees it times every dispatch and reports it through emitTrace (src/tracing.ts:89-106;
+ * the wasm backend around dispatch, src/backend/wasm.ts:172-173 and 266-269; the webgpu backend with
+ * a timestamp pair per pass, src/backend/webgpu/tracing.ts:11-164).  Here: between trace_start and
+ * trace_stop every eager jaxcuda_dispatch is bracketed by a pair of CUDA events on the context's
+ * stream (at most 2^20 dispatches per trace; dispatches inside a capture are not timed one by one,
+ * a replay is timed by its caller).  trace_stop waits for the last traced dispatch and returns
+ * the number of records; trace_record gives record `index`: the executable, its start relative
+ * to trace_start and its duration on the device, in milliseconds, and its plan (the text of
+ * jaxcuda_exe_describe, valid even if the executable has been released since).  The records
+ * stay until the next trace_start. */
+int jaxcuda_trace_start(jaxcuda_ctx* ctx);
+int jaxcuda_trace_stop(jaxcuda_ctx* ctx, int* n_records);
+int jaxcuda_trace_record(jaxcuda_ctx* ctx, int index, jaxcuda_exe** exe, double* start_ms, double* duration_ms,
+                         char* name, size_t name_len);
 /* Number of kernels this context has launched so far (its own kernels only). */
 uint64_t jaxcuda_launch_count(jaxcuda_ctx* ctx);
 

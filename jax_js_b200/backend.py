@@ -85,6 +85,10 @@ SYMBOLS = {
     "jaxcuda_sync": (_I, [_P]),
     "jaxcuda_event_record": (_I, [_P, _I]),
     "jaxcuda_event_elapsed_ms": (_I, [_P, _I, _I, ctypes.POINTER(ctypes.c_float)]),
+    "jaxcuda_trace_start": (_I, [_P]),
+    "jaxcuda_trace_stop": (_I, [_P, ctypes.POINTER(ctypes.c_int)]),
+    "jaxcuda_trace_record": (_I, [_P, _I, ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_double),
+                                  ctypes.POINTER(ctypes.c_double), ctypes.c_char_p, ctypes.c_size_t]),
     "jaxcuda_launch_count": (_U64, [_P]),
     "jaxcuda_slot_ptr": (_I, [_P, _U32, ctypes.POINTER(_U64)]),
     "jaxcuda_stream": (_U64, [_P]),
@@ -367,6 +371,25 @@ class CudaBackend:
 
     def launch_count(self) -> int:
         return int(self._lib.jaxcuda_launch_count(self._ctx))
+
+    # -- tracing (src/tracing.ts:15-33, :89-106) ---------------------------------------------
+    def start_trace(self) -> None:
+        """From here on every eager dispatch is timed on the device (a pair of CUDA events)."""
+        self._check(self._lib.jaxcuda_trace_start(self._ctx))
+
+    def stop_trace(self) -> list:
+        """Ends the trace and returns one record per dispatch, in dispatch order: the executable's
+        handle, its plan, its start relative to `start_trace` and its duration, in milliseconds (what
+        the reference passes to `emitTrace`)."""
+        n = ctypes.c_int()
+        self._check(self._lib.jaxcuda_trace_stop(self._ctx, ctypes.byref(n)))
+        out = []
+        name = ctypes.create_string_buffer(512)
+        for i in range(n.value):
+            exe, t0, dt = ctypes.c_void_p(), ctypes.c_double(), ctypes.c_double()
+            self._check(self._lib.jaxcuda_trace_record(self._ctx, i, ctypes.byref(exe), ctypes.byref(t0), ctypes.byref(dt), name, 512))
+            out.append({"exe": exe.value, "name": name.value.decode(), "start_ms": t0.value, "duration_ms": dt.value})
+        return out
 
     def host_alloc(self, nbytes: int) -> np.ndarray:
         """Pinned host memory as a uint8 array (freed with host_free)."""

@@ -261,6 +261,13 @@ struct jaxcuda_ctx {
   cudaStream_t comm_stream = nullptr;
   cudaEvent_t comm_fork = nullptr, comm_done = nullptr;
   cudaEvent_t wait_compute = nullptr, wait_comm = nullptr;   // jaxcuda_comm_wait's probes
+  // Tracing: while it is on, every eager dispatch is bracketed by a pair of timing events.
+  struct TraceRec { jaxcuda_exe* exe; std::string name; cudaEvent_t begin, end; };
+  bool tracing = false;
+  cudaEvent_t trace_origin = nullptr;
+  std::vector<TraceRec> trace;
+  std::vector<cudaEvent_t> trace_events;   // pool, reused by the next trace
+  size_t trace_events_used = 0;
   bool comm_pending = false;
   // copy streams of the asynchronous read / write calls, so that uploads, kernels and downloads of
   // consecutive steps overlap (the GPU has separate copy engines per direction)
@@ -525,6 +532,8 @@ int jaxcuda_destroy(jaxcuda_ctx* ctx) {
     for (cudaEvent_t ev : ctx->comm_events) cudaEventDestroy(ev);
     cudaStreamDestroy(ctx->comm_stream);
   }
+  for (cudaEvent_t ev : ctx->trace_events) cudaEventDestroy(ev);
+  if (ctx->trace_origin) cudaEventDestroy(ctx->trace_origin);
   if (ctx->wait_compute) cudaEventDestroy(ctx->wait_compute);
   if (ctx->wait_comm) cudaEventDestroy(ctx->wait_comm);
   jaxcuda_comm_destroy(ctx);
@@ -1035,9 +1044,40 @@ int jaxcuda_prepare_routine(jaxcuda_ctx* ctx, const char* name, const jaxcuda_ro
   return JAXCUDA_OK;
 }
 
+static int dispatch_untraced(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const jaxcuda_slot* inputs, int n_inputs,
+                             const jaxcuda_slot* outputs, int n_outputs);
+
+static const size_t kTraceLimit = 1 << 20;   // dispatches kept per trace; later ones run untimed
+
+static int trace_event(jaxcuda_ctx* ctx, cudaEvent_t* out) {
+  if (ctx->trace_events_used == ctx->trace_events.size()) {
+    cudaEvent_t ev;
+    CUDA_TRY(ctx, cudaEventCreate(&ev));
+    ctx->trace_events.push_back(ev);
+  }
+  *out = ctx->trace_events[ctx->trace_events_used++];
+  return JAXCUDA_OK;
+}
+
 int jaxcuda_dispatch(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const jaxcuda_slot* inputs, int n_inputs,
                      const jaxcuda_slot* outputs, int n_outputs) {
   if (!ctx || !exe || exe->ctx != ctx) return JAXCUDA_EINVAL;
+  // A captured list is timed as a whole by whoever replays it; its dispatches are deferred and fused.
+  if (!ctx->tracing || ctx->alloc.capturing || ctx->trace.size() >= kTraceLimit)
+    return dispatch_untraced(ctx, exe, inputs, n_inputs, outputs, n_outputs);
+  cudaSetDevice(ctx->device);
+  jaxcuda_ctx::TraceRec rec{exe, exe->describe, nullptr, nullptr};
+  if (int rc = trace_event(ctx, &rec.begin)) return rc;
+  if (int rc = trace_event(ctx, &rec.end)) return rc;
+  CUDA_TRY(ctx, cudaEventRecord(rec.begin, ctx->stream));
+  const int rc = dispatch_untraced(ctx, exe, inputs, n_inputs, outputs, n_outputs);
+  CUDA_TRY(ctx, cudaEventRecord(rec.end, ctx->stream));
+  if (rc == JAXCUDA_OK) ctx->trace.push_back(std::move(rec));
+  return rc;
+}
+
+static int dispatch_untraced(jaxcuda_ctx* ctx, jaxcuda_exe* exe, const jaxcuda_slot* inputs, int n_inputs,
+                             const jaxcuda_slot* outputs, int n_outputs) {
   cudaSetDevice(ctx->device);
   std::vector<SlotRec*> in(n_inputs), outv(n_outputs);
   for (int i = 0; i < n_inputs; i++) if (!(in[i] = find_slot(ctx, inputs[i]))) return slot_error(ctx, inputs[i]);
@@ -1725,6 +1765,43 @@ int jaxcuda_event_elapsed_ms(jaxcuda_ctx* ctx, int a, int b, float* ms) {
   return JAXCUDA_OK;
 }
 uint64_t jaxcuda_launch_count(jaxcuda_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+// ---- tracing ------------------------------------------------------------------------------
+int jaxcuda_trace_start(jaxcuda_ctx* ctx) {
+  if (!ctx) return JAXCUDA_EINVAL;
+  if (ctx->alloc.capturing) return fail(ctx, JAXCUDA_EINVAL, "trace_start inside a capture");
+  cudaSetDevice(ctx->device);
+  if (!ctx->trace_origin) CUDA_TRY(ctx, cudaEventCreate(&ctx->trace_origin));
+  ctx->trace.clear();
+  ctx->trace_events_used = 0;
+  CUDA_TRY(ctx, cudaEventRecord(ctx->trace_origin, ctx->stream));
+  ctx->tracing = true;
+  return JAXCUDA_OK;
+}
+int jaxcuda_trace_stop(jaxcuda_ctx* ctx, int* n_records) {
+  if (!ctx) return JAXCUDA_EINVAL;
+  if (ctx->alloc.capturing) return fail(ctx, JAXCUDA_EINVAL, "trace_stop inside a capture");
+  ctx->tracing = false;
+  cudaSetDevice(ctx->device);
+  if (!ctx->trace.empty()) CUDA_TRY(ctx, cudaEventSynchronize(ctx->trace.back().end));
+  if (n_records) *n_records = (int)ctx->trace.size();
+  return JAXCUDA_OK;
+}
+int jaxcuda_trace_record(jaxcuda_ctx* ctx, int index, jaxcuda_exe** exe, double* start_ms, double* duration_ms,
+                         char* name, size_t name_len) {
+  if (!ctx || index < 0 || (size_t)index >= ctx->trace.size() || ctx->tracing) return JAXCUDA_EINVAL;
+  const jaxcuda_ctx::TraceRec& r = ctx->trace[index];
+  cudaSetDevice(ctx->device);
+  float t0 = 0, dt = 0;
+  CUDA_TRY(ctx, cudaEventSynchronize(r.end));
+  CUDA_TRY(ctx, cudaEventElapsedTime(&t0, ctx->trace_origin, r.begin));
+  CUDA_TRY(ctx, cudaEventElapsedTime(&dt, r.begin, r.end));
+  if (exe) *exe = r.exe;
+  if (start_ms) *start_ms = t0;
+  if (duration_ms) *duration_ms = dt;
+  if (name && name_len) snprintf(name, name_len, "%s", r.name.c_str());
+  return JAXCUDA_OK;
+}
 
 // ---- captured step lists ------------------------------------------------------------------
 int jaxcuda_copy(jaxcuda_ctx* ctx, jaxcuda_slot dst, jaxcuda_slot src) {

@@ -233,6 +233,26 @@ Napi::Value GraphCost(const Napi::CallbackInfo& info) {   // what JitProgram.toS
   return out;
 }
 
+// Per-dispatch timing while the reference's profiler is on (src/tracing.ts:15-33).
+Napi::Value TraceStart(const Napi::CallbackInfo& info) {
+  if (jaxcuda_trace_start(Ctx(info[0])) != JAXCUDA_OK) Throw(info.Env(), Ctx(info[0]));
+  return info.Env().Undefined();
+}
+Napi::Value TraceStop(const Napi::CallbackInfo& info) {
+  int n = 0;
+  if (jaxcuda_trace_stop(Ctx(info[0]), &n) != JAXCUDA_OK) Throw(info.Env(), Ctx(info[0]));
+  auto out = Napi::Array::New(info.Env(), n);
+  for (int i = 0; i < n; i++) {
+    double start = 0, duration = 0;
+    if (jaxcuda_trace_record(Ctx(info[0]), i, nullptr, &start, &duration, nullptr, 0) != JAXCUDA_OK) Throw(info.Env(), Ctx(info[0]));
+    auto rec = Napi::Object::New(info.Env());
+    rec.Set("startMs", Napi::Number::New(info.Env(), start));
+    rec.Set("durationMs", Napi::Number::New(info.Env(), duration));
+    out.Set((uint32_t)i, rec);
+  }
+  return out;
+}
+
 Napi::Object Init(Napi::Env env, Napi::Object exports) {
   exports.Set("create", Napi::Function::New(env, Create));
   exports.Set("destroy", Napi::Function::New(env, Destroy));
@@ -250,6 +270,8 @@ Napi::Object Init(Napi::Env env, Napi::Object exports) {
   exports.Set("graphLaunch", Napi::Function::New(env, GraphLaunch));
   exports.Set("graphDestroy", Napi::Function::New(env, GraphDestroy));
   exports.Set("graphCost", Napi::Function::New(env, GraphCost));
+  exports.Set("traceStart", Napi::Function::New(env, TraceStart));
+  exports.Set("traceStop", Napi::Function::New(env, TraceStop));
   return exports;
 }
 

@@ -21,6 +21,7 @@
 import { AluExp, AluOp, DType, Kernel } from "../alu";
 import { Backend, Device, Executable, Slot, SlotError, UnsupportedOpError, UnsupportedRoutineError } from "../backend";
 import { Routine } from "../routine";
+import { emitTrace, isTracing, onFlushTrace, traceSourceInfo, type TraceInfo } from "../tracing";
 import { tuneNullopt } from "../tuner";
 import { FpHash } from "../utils";
 
@@ -41,6 +42,8 @@ interface Native {
   graphLaunch(ctx: bigint, graph: bigint): void;
   graphDestroy(ctx: bigint, graph: bigint): void;
   graphCost(graph: bigint): { launches: number; bytes: number; fusedRuns: number };
+  traceStart(ctx: bigint): void;                       // jaxcuda_trace_start
+  traceStop(ctx: bigint): { startMs: number; durationMs: number }[];   // jaxcuda_trace_stop + jaxcuda_trace_record
 }
 
 // Codes of include/jaxcuda_ir.h, in the declaration order of AluOp (src/alu.ts:1365-1407).
@@ -175,8 +178,40 @@ export class CudaBackend implements Backend {
     }
   }
 
+  // Tracing (src/tracing.ts:15-33): the library times every dispatch with a pair of CUDA events while
+  // a trace is on; the records are turned into `performance.measure` entries when the profiler
+  // flushes (the webgpu backend resolves its timestamp queries at the same point,
+  // src/backend/webgpu/tracing.ts:61-70), placed on the host clock from the moment the trace began.
+  #traceInfos: TraceInfo[] | null = null;
+  #traceAnchor = 0;
+  #recording = false;
+  #flushRegistered = false;
+
+  #flushTrace(): void {
+    const infos = this.#traceInfos;
+    if (!infos) return;
+    this.#traceInfos = null;
+    const records = this.native.traceStop(this.ctx);
+    for (let i = 0; i < records.length && i < infos.length; i++) {
+      const start = this.#traceAnchor + records[i].startMs;
+      emitTrace("cuda", infos[i], start, start + records[i].durationMs);
+    }
+  }
+
   dispatch(exe: Executable<bigint>, inputs: Slot[], outputs: Slot[]): void {
+    // dispatches inside a recording are fused and replayed as one graph: the library leaves no record of them
+    const traced = isTracing() && !this.#recording;
+    if (traced && !this.#traceInfos) {
+      this.native.traceStart(this.ctx);
+      this.#traceAnchor = performance.now();
+      this.#traceInfos = [];
+      if (!this.#flushRegistered) onFlushTrace(() => this.#flushTrace());   // stopTrace runs every callback ever registered
+      this.#flushRegistered = true;
+    } else if (!isTracing() && this.#traceInfos) {
+      this.#flushTrace();
+    }
     this.#check(this.native.dispatch(this.ctx, exe.data, Uint32Array.from(inputs), Uint32Array.from(outputs)));
+    if (traced) this.#traceInfos!.push(traceSourceInfo(exe.source));   // a dispatch that failed left no record either
   }
 
   /**
@@ -188,10 +223,12 @@ export class CudaBackend implements Backend {
    */
   record(steps: () => void): { replay: () => void; destroy: () => void; cost: { launches: number; bytes: number; fusedRuns: number } } {
     this.native.captureBegin(this.ctx);
+    this.#recording = true;
     let graph: bigint;
     try {
       steps();
     } finally {
+      this.#recording = false;
       graph = this.native.captureEnd(this.ctx);
     }
     return {

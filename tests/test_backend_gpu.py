@@ -307,3 +307,40 @@ def backend_scratch(backend, nbytes):
     if "buf" not in _SCRATCH:
         _SCRATCH["buf"] = backend.host_alloc(nbytes)
     return _SCRATCH["buf"]
+
+
+def test_trace_times_every_eager_dispatch(backend):
+    """startTrace / stopTrace (src/tracing.ts:15-33): between them every dispatch leaves a record with
+    its plan, its start and its duration on the device; records come in dispatch order, do not
+    overlap on the one stream, and a larger Kernel takes longer.  Dispatches inside a capture and
+    after stop_trace leave none."""
+    from jax_js_b200 import AluExp, AluVar, DType, Kernel
+    F32 = DType.Float32
+
+    def inc(n):
+        return backend.prepare_kernel(Kernel(1, n, AluExp.add(AluExp.global_index(F32, 0, n, AluVar.gidx), AluExp.f32(1))))
+
+    small, large = inc(1 << 12), inc(1 << 26)
+    a, b = backend.put(np.zeros(1 << 26, np.float32)), backend.malloc(4 << 26)
+    backend.dispatch(large, [a], [b])             # not traced
+    backend.start_trace()
+    for exe in (small, large, small, large):
+        backend.dispatch(exe, [a], [b])
+    backend.capture_begin()
+    backend.dispatch(small, [a], [b])
+    graph = backend.capture_end()
+    backend.graph_launch(graph)
+    records = backend.stop_trace()
+    backend.dispatch(small, [a], [b])             # not traced
+    assert [r["exe"] for r in records] == [small.data, large.data, small.data, large.data]
+    assert all(r["name"].startswith("elementwise") for r in records)
+    assert all(r["start_ms"] >= 0 and r["duration_ms"] > 0 for r in records)
+    for before, after in zip(records, records[1:]):
+        assert after["start_ms"] >= before["start_ms"] + before["duration_ms"] - 1e-3
+    assert records[1]["duration_ms"] > 4 * records[0]["duration_ms"]
+    assert 0.05 < records[1]["duration_ms"] < 5.0           # 512 MB through HBM
+    backend.start_trace()
+    assert backend.stop_trace() == []
+    backend.graph_destroy(graph)
+    for s in (a, b):
+        backend.dec_ref(s)
