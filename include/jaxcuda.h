@@ -153,6 +153,18 @@ int jaxcuda_sync(jaxcuda_ctx* ctx);
 int jaxcuda_event_record(jaxcuda_ctx* ctx, int index); /* index in [0, 65536) */
 int jaxcuda_event_elapsed_ms(jaxcuda_ctx* ctx, int start_index, int stop_index, float* ms);
 
+/* Checked build (the pool's memory checker cannot be run on these kernels, so the library checks
+ * itself).  With JAXCUDA_CHECKED=1 in the environment when the process first creates a context,
+ * every scalar load of the generated kernels tests its index, also where the planner has proven
+ * the range and the normal build tests nothing, and counts the indices outside the buffer.
+ * jaxcuda_checked_counts waits for the stream, returns and resets the two counters:
+ * allowed_outside, loads that the Kernel lets fall outside and that read element 0 as the
+ * reference's Wasm backend does (src/backend/wasm/translation.ts:221-228); proven_outside, loads
+ * that were proven in range and were not: any non-zero value is a bug of the planner.  Vector
+ * loads and TMA are not instrumented (the planner takes them only for proven, contiguous ranges).  JAXCUDA_EINVAL in a
+ * normal build. */
+int jaxcuda_checked_counts(jaxcuda_ctx* ctx, uint64_t* allowed_outside, uint64_t* proven_outside);
+
 /* Per-dispatch tracing: profiler.startTrace / stopTrace flip a flag (src/tracing.ts:15-33) and a
  * backend that sees it times every dispatch and reports it through emitTrace (src/tracing.ts:89-106;
  * the wasm backend around dispatch, src/backend/wasm.ts:172-173 and 266-269; the webgpu backend with

@@ -85,6 +85,7 @@ SYMBOLS = {
     "jaxcuda_sync": (_I, [_P]),
     "jaxcuda_event_record": (_I, [_P, _I]),
     "jaxcuda_event_elapsed_ms": (_I, [_P, _I, _I, ctypes.POINTER(ctypes.c_float)]),
+    "jaxcuda_checked_counts": (_I, [_P, ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64)]),
     "jaxcuda_trace_start": (_I, [_P]),
     "jaxcuda_trace_stop": (_I, [_P, ctypes.POINTER(ctypes.c_int)]),
     "jaxcuda_trace_record": (_I, [_P, _I, ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_double),
@@ -371,6 +372,13 @@ class CudaBackend:
 
     def launch_count(self) -> int:
         return int(self._lib.jaxcuda_launch_count(self._ctx))
+
+    def checked_counts(self) -> tuple:
+        """Checked build only (JAXCUDA_CHECKED=1 in the environment): (loads the Kernels let fall outside
+        their buffers, loads proven in range that were not) since the last call; the second must be 0."""
+        a, b = ctypes.c_uint64(), ctypes.c_uint64()
+        self._check(self._lib.jaxcuda_checked_counts(self._ctx, ctypes.byref(a), ctypes.byref(b)))
+        return a.value, b.value
 
     # -- tracing (src/tracing.ts:15-33, :89-106) ---------------------------------------------
     def start_trace(self) -> None:

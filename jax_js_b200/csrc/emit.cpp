@@ -71,6 +71,9 @@ std::string load_value(const Node& nd, const std::string& ix, bool proven) {
   if (len == 0) return nd.dtype == JAXCUDA_F64 ? "0.0" : (nd.dtype == JAXCUDA_F32 || nd.dtype == JAXCUDA_F16) ? "0.0f" : "0";
   // An index outside the buffer reads element 0, as the Wasm emitter does (translation.ts:221-228).
   std::string at = proven ? ix : "((u32)(" + ix + ") < " + S(len) + "u ? (" + ix + ") : 0)";
+  // Checked build: every scalar load tests its index, also those whose range the affine analysis
+  // has proven, and counts the misses by kind.
+  if (emit_checked()) at = "jx_ix((i64)(" + ix + "), " + S(len) + "u, " + (proven ? "1" : "0") + ")";
   std::string p = std::string("((const ") + ptype(nd.dtype) + "*)p" + S((int64_t)nd.arg0) + ")[" + at + "]";
   return nd.dtype == JAXCUDA_F16 ? "jx_h2f(" + p + ")" : p;
 }

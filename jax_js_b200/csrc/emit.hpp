@@ -6,6 +6,7 @@
 // src/backend/webgpu.ts:285-530) and of the Wasm tile planner
 // (src/backend/wasm/tilePlan.ts:278-334), re-derived for Blackwell.
 #pragma once
+#include <cstdlib>
 
 #include <string>
 #include <vector>
@@ -165,6 +166,13 @@ struct BatchStage {
 };
 // work (outputs x reduction length) up to which a Kernel counts as small
 inline double small_kernel_work() { return 16384; }
+
+// JAXCUDA_CHECKED=1 (read once per process): the emitter routes every scalar load through jx_ix,
+// which counts indices outside the buffer, and the runtime compiles with JX_CHECKED defined.
+inline bool emit_checked() {
+  static const bool on = [] { const char* v = getenv("JAXCUDA_CHECKED"); return v && *v && atoi(v) != 0; }();
+  return on;
+}
 bool plan_small_batch(const std::vector<BatchStage>& stages, int n_params, const Options& opt, Plan& plan, std::string& why);
 
 // Implemented in gemm_tc.cpp: rewrites `plan` to the tcgen05 skeleton when `g` qualifies.

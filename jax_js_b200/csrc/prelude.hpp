@@ -18,6 +18,16 @@ typedef unsigned long long u64;
 
 struct __align__(2) jx_half { u16 x; };
 
+#ifdef JX_CHECKED
+// Checked build: an index outside its buffer is counted at JX_OOB_ADDR, word 0 for a load that the
+// Kernel allows to fall outside (it reads element 0), word 1 for a load whose range had been proven.
+__device__ __forceinline__ int jx_ix(i64 ix, u32 len, int proven) {
+  if (ix >= 0 && ix < (i64)len) return (int)ix;
+  atomicAdd((u32*)JX_OOB_ADDR + proven, 1u);
+  return 0;
+}
+#endif
+
 #define JX_INF __int_as_float(0x7f800000)
 #define JX_NAN __int_as_float(0x7fc00000)
 

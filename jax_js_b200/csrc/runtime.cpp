@@ -252,6 +252,7 @@ struct jaxcuda_ctx {
   // polls it, which must not cross PCIe); it is copied to the pinned `status_host` before a sync.
   int* status_host = nullptr;
   int* status_dev = nullptr;
+  unsigned* oob_dev = nullptr;   // checked build: the two counters of jx_ix
   bool tc_dispatched = false;
   // NCCL (resolved with dlopen so that the library loads where NCCL is absent)
   void* nccl_lib = nullptr;
@@ -361,8 +362,14 @@ uint64_t fnv1a(const uint8_t* p, size_t n) {
 }
 
 // NVRTC: CUDA C -> sm_100a cubin.  Needs no GPU.
-bool nvrtc_compile(const std::string& src, std::vector<char>& cubin, std::string& err) {
+bool nvrtc_compile(const std::string& src_in, std::vector<char>& cubin, std::string& err, const void* oob_words = nullptr) {
   nvrtcProgram prog;
+  std::string src = src_in;
+  if (emit_checked()) {   // the checked build's counters live at a fixed device address of the context
+    char head[96];
+    snprintf(head, sizeof head, "#define JX_CHECKED 1\n#define JX_OOB_ADDR 0x%llxull\n", (unsigned long long)(uintptr_t)oob_words);
+    src = head + src;
+  }
   if (nvrtcCreateProgram(&prog, src.c_str(), "jaxcuda_kernel.cu", 0, nullptr, nullptr) != NVRTC_SUCCESS) {
     err = "nvrtcCreateProgram failed";
     return false;
@@ -388,7 +395,7 @@ bool nvrtc_compile(const std::string& src, std::vector<char>& cubin, std::string
 
 int compile_plan(jaxcuda_ctx* ctx, jaxcuda_exe* exe) {
   std::vector<char> cubin;
-  if (!nvrtc_compile(exe->plan.source, cubin, ctx->last_error)) return JAXCUDA_ECOMPILE;
+  if (!nvrtc_compile(exe->plan.source, cubin, ctx->last_error, ctx->oob_dev)) return JAXCUDA_ECOMPILE;
   CUresult cr = ctx->drv.ModuleLoadData(&exe->module, cubin.data());
   if (cr != CUDA_SUCCESS) return drv_fail(ctx, "cuModuleLoadData", cr);
   for (const Stage& st : exe->plan.stages) {
@@ -480,6 +487,9 @@ int jaxcuda_create(int device, jaxcuda_ctx** out) {
       (e = cudaMemset(ctx->status_dev, 0, sizeof(int))) != cudaSuccess)
     return fail(nullptr, JAXCUDA_ECUDA, "status word: %s", cudaGetErrorString(e));
   *ctx->status_host = 0;
+  if (emit_checked() && ((e = cudaMalloc((void**)&ctx->oob_dev, 2 * sizeof(unsigned))) != cudaSuccess ||
+                         (e = cudaMemset(ctx->oob_dev, 0, 2 * sizeof(unsigned))) != cudaSuccess))
+    return fail(nullptr, JAXCUDA_ECUDA, "checked build counters: %s", cudaGetErrorString(e));
   ctx->opt.sm_count = prop.multiProcessorCount;
   ctx->opt.ew_ilp = env_int("JAXCUDA_EW_ILP", ctx->opt.ew_ilp);
   ctx->opt.ew_blocks_per_sm = env_int("JAXCUDA_EW_BLOCKS_PER_SM", ctx->opt.ew_blocks_per_sm);
@@ -543,6 +553,7 @@ int jaxcuda_destroy(jaxcuda_ctx* ctx) {
   ctx->alloc.release_cached();
   if (ctx->status_host) cudaFreeHost(ctx->status_host);
   if (ctx->status_dev) cudaFree(ctx->status_dev);
+  if (ctx->oob_dev) cudaFree(ctx->oob_dev);
   cudaStreamDestroy(ctx->stream);
   delete ctx;
   return JAXCUDA_OK;
@@ -1765,6 +1776,21 @@ int jaxcuda_event_elapsed_ms(jaxcuda_ctx* ctx, int a, int b, float* ms) {
   return JAXCUDA_OK;
 }
 uint64_t jaxcuda_launch_count(jaxcuda_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+// ---- checked build --------------------------------------------------------------------------
+int jaxcuda_checked_counts(jaxcuda_ctx* ctx, uint64_t* allowed_outside, uint64_t* proven_outside) {
+  if (!ctx) return JAXCUDA_EINVAL;
+  if (!ctx->oob_dev) return fail(ctx, JAXCUDA_EINVAL, "not a checked build: create the context with JAXCUDA_CHECKED=1 in the environment");
+  if (ctx->alloc.capturing) return fail(ctx, JAXCUDA_EINVAL, "checked_counts inside a capture");
+  cudaSetDevice(ctx->device);
+  if (int rc = jaxcuda_sync(ctx)) return rc;
+  unsigned words[2] = {0, 0};
+  CUDA_TRY(ctx, cudaMemcpy(words, ctx->oob_dev, sizeof words, cudaMemcpyDeviceToHost));
+  CUDA_TRY(ctx, cudaMemset(ctx->oob_dev, 0, sizeof words));
+  if (allowed_outside) *allowed_outside = words[0];
+  if (proven_outside) *proven_outside = words[1];
+  return JAXCUDA_OK;
+}
 
 // ---- tracing ------------------------------------------------------------------------------
 int jaxcuda_trace_start(jaxcuda_ctx* ctx) {
