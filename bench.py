@@ -196,7 +196,8 @@ def mlp_train(be, rank, world, dist, steps=8, warmup=2):
     off = rank * local - (rank * local // chunk) * chunk
     sx = be.put(np.concatenate(xs)[off:off + local])
     sy = be.put(np.concatenate(ys)[off:off + local])
-    tr = mlp.MlpTrainer(be, dims, local, GB, overlap=os.environ.get("BENCH_MLP_OVERLAP", "1") != "0")
+    hoist = {"0": False, "1": True}.get(os.environ.get("BENCH_MLP_HOIST", ""))   # default: on several ranks
+    tr = mlp.MlpTrainer(be, dims, local, GB, overlap=os.environ.get("BENCH_MLP_OVERLAP", "1") != "0", hoist=hoist)
     losses = []
     for _ in range(warmup):
         be.dec_ref(tr.step(sx, sy, world))
@@ -237,7 +238,7 @@ def mlp_train(be, rank, world, dist, steps=8, warmup=2):
         # the same shard without the sums (a trainer of its own, world 1 on the local batch): what the
         # step costs in kernels alone; the rest of the step is sums that nothing hides and waiting
         # for the slowest rank
-        solo = mlp.MlpTrainer(be, dims, local, GB)
+        solo = mlp.MlpTrainer(be, dims, local, GB, hoist=hoist)
         for _ in range(2):
             be.dec_ref(solo.step(sx, sy, 1))
         solo.capture(sx, sy, 1)
@@ -260,6 +261,8 @@ def mlp_train(be, rank, world, dist, steps=8, warmup=2):
             "allreduce_bytes": 4 * sum(mlp.leaf_sizes(dims)), "loss_last": vals[-1],
             "replay": "one CUDA graph launch per step (gradient program + NCCL sum + Adam program; two graphs alternate between two state buffers)",
             "gradient_sum": "per layer on a second stream, under back-propagation" if tr.overlap and world > 1 else "after the gradient program",
+            "kernel_order": "the reference's list with the weight-gradient Kernels of layers 2.. moved to where their inputs exist (same Kernels, same bits)"
+                            if tr.hoist else "the reference's list",
             "eager_ms_per_step": eager_ms, "phases": phases,
             "gemm": "3xTF32 on tcgen05 (f32 accuracy), f32 accumulate"}
 

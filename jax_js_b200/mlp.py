@@ -298,15 +298,28 @@ class MlpTrainer:
     program -- identical on every rank, so parameters stay replicated."""
 
     def __init__(self, backend, dims: Sequence[int], local_batch: int, global_batch: int, lr: float = 1e-3,
-                 seed: int = 0, allreduce=None, overlap: bool = True):
+                 seed: int = 0, allreduce=None, overlap: bool = True, hoist: bool | None = None):
         self.be, self.dims = backend, list(dims)
         self.names = param_order(len(dims) - 1)
         self.sizes = leaf_sizes(dims)
         self.grad = mlp_grad_program(local_batch, dims, global_batch=global_batch)
-        # the last layer's weights last: their gradient is the last to arrive, and with overlapped
-        # sums it is still in flight while the other leaves are updated
-        n = len(self.names)
-        self.adam = adam_program(self.sizes, self.names, lr, order=[i for i in range(n) if i != n - 2] + [n - 2])
+        n, L = len(self.names), len(dims) - 1
+        # The reference's list yields every weight gradient at its end (dW1 .. dWL), where the sum of
+        # the largest has nothing left to run under.  On several ranks (hoist=None: when the shard
+        # is smaller than the global batch) dW2 .. dWL move to where their inputs exist, so each of
+        # their sums runs under the back-propagation of the layers below; dW1 stays last.  Same
+        # Kernels, same bits (JitProgram.hoisted).
+        self.hoist = (global_batch > local_batch if hoist is None else hoist) and L >= 2
+        if self.hoist:
+            self.grad = self.grad.hoisted([f"dW{l}" for l in range(2, L + 1)])
+            # the leaves whose gradients travel with the last sum are updated last
+            self.late = ["b2", "b1", "W1"]
+        else:
+            # the last layer's weights last: their gradient is the last to arrive, and with overlapped
+            # sums it is still in flight while the other leaves are updated
+            self.late = [f"W{L}"]
+        tail = [self.names.index(x) for x in self.late]
+        self.adam = adam_program(self.sizes, self.names, lr, order=[i for i in range(n) if i not in tail] + tail)
         self.grad.prepare(backend)
         self.adam.prepare(backend)
         self.allreduce = allreduce if allreduce is not None else backend.allreduce_sum_f32
@@ -330,12 +343,13 @@ class MlpTrainer:
             self.allreduce(list(outs[1:]) + [outs[0]])
         else:
             # The program yields the loss and the bias gradients first (last layer first), then the
-            # weight gradients from the first layer up.  Every weight gradient goes out as soon as it
+            # weight gradients from the first layer up (hoisted: dWL .. dW2 each right after the
+            # cotangent of its layer, dW1 last).  Every weight gradient goes out as soon as it
             # exists, under the kernels that follow it; the loss and the biases (a few KB) ride with the
-            # first of them.  The sums stay in flight into the Adam program: the backend makes every
+            # next of them.  The sums stay in flight into the Adam program: the backend makes every
             # Kernel that reads a gradient wait for that gradient's sum (and for no later one).
             ready = []
-            last = f"dW{len(self.dims) - 1}"
+            last = "dW1" if self.hoist else f"dW{len(self.dims) - 1}"   # the weight gradient the program yields last
 
             def on_output(name, slot):
                 ready.append(slot)
@@ -356,7 +370,7 @@ class MlpTrainer:
     def _adam(self, ins, out_slots=None):
         """The Adam program; joins the gradient sum still in flight just before its first reader."""
         be = self.be
-        late = {f"g_W{len(self.dims) - 1}"}
+        late = {f"g_{x}" for x in self.late}
 
         def before_step(step):
             if self._tail and late.intersection(step.inputs):

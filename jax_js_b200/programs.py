@@ -230,6 +230,60 @@ class JitProgram:
             raise
         return backend.capture_end(), outs
 
+    def hoisted(self, targets: Sequence[str]) -> "JitProgram":
+        """The same Kernels in another order: the Kernel that writes each of `targets`, together with
+        the chain of intermediates that only it reads, moves to the earliest point at which its inputs
+        exist; everything else keeps its order, and every intermediate is released after its last
+        reader in the new order.  Only independent steps change places, so every Kernel sees the
+        inputs it saw before and the outputs are the same bits.  (The reference's executor runs its
+        list front to back, src/frontend/jit.ts:111-162; a driver that overlaps communication with the
+        list wants an output that feeds a long transfer to exist early.)"""
+        ex = [s for s in self.steps if s.kind == "execute"]
+        nbytes = {s.name: s.nbytes for s in self.steps if s.kind == "malloc"}
+        pos = {s.name: i for i, s in enumerate(ex)}
+        uses: dict = {}
+        for s in ex:
+            for n in set(s.inputs):
+                uses[n] = uses.get(n, 0) + 1
+        after: dict = {}          # position -> chains to run right after it
+        moved = set()
+        for t in targets:
+            if t not in pos:
+                raise ValueError(f"{t} is not written by a Kernel of this program")
+            chain = [pos[t]]
+            while True:
+                private = [n for n in ex[chain[0]].inputs if n in pos and uses.get(n) == 1 and n not in self.outputs]
+                if len(private) != 1 or pos[private[0]] in moved:
+                    break
+                chain.insert(0, pos[private[0]])
+            ready = max([pos[n] for i in chain for n in ex[i].inputs if n in pos and pos[n] not in chain], default=-1)
+            if ready >= chain[0]:
+                continue          # already as early as it can be
+            moved.update(chain)
+            after.setdefault(ready, []).append(chain)
+        order = [i for chain in after.get(-1, []) for i in chain]
+        for i in range(len(ex)):
+            if i in moved:
+                continue
+            order.append(i)
+            for chain in after.get(i, []):
+                order.extend(chain)
+        last_use = {}
+        for rank, i in enumerate(order):
+            for n in ex[i].inputs:
+                last_use[n] = rank
+        out = JitProgram(list(self.inputs), list(self.outputs))
+        for rank, i in enumerate(order):
+            s = ex[i]
+            out.steps.append(Step("malloc", s.name, nbytes[s.name]))
+            out.steps.append(Step("execute", s.name, 0, s.kernel, tuple(s.inputs)))
+            for n in dict.fromkeys(s.inputs):
+                if n in pos and n not in self.outputs and last_use[n] == rank:
+                    out.steps.append(Step("free", n))
+            if s.name not in last_use and s.name not in self.outputs:
+                out.steps.append(Step("free", s.name))
+        return out
+
     def cost(self, backend):
         """Sum of algorithmic bytes, flops and launches over the execute steps."""
         self.prepare(backend)

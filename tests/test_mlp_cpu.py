@@ -123,8 +123,9 @@ def _rank_main(rank, world, port, out):
         s = tr.step(sx, sy, world=world)
         losses.append(float(be.get(s, "float32")[0]))
         be.dec_ref(s)
-    # each step summed loss and bias gradients as one group, then every weight gradient as it appeared
-    assert tr.overlap and be.joined and be.async_calls == [5, 1, 1] * 2, be.async_calls   # loss + biases ride with dW1
+    # on several ranks dW3 and dW2 are hoisted to where their inputs exist; whatever small outputs came before
+    # a weight gradient ride with its sum: (loss, dW3), (db3, dW2), (db2, db1, dW1)
+    assert tr.hoist and tr.overlap and be.joined and be.async_calls == [2, 2, 3] * 2, be.async_calls
     if rank == 0:
         np.savez(out, losses=np.array(losses), **{f"p{i}": be.get(s, "float32") for i, s in enumerate(tr.params)})
     dist.destroy_process_group()
@@ -169,3 +170,27 @@ def test_step_list_hooks_and_caller_owned_outputs():
     assert runs == ["m1", "u", "s", "softmax", "m2", "m2k", "s2", "lse", "m3", "argmax"]
     assert [n for kind, n in events if kind == "out"] == ["softmax", "lse", "argmax"]
     assert events.index(("out", "softmax")) == events.index(("run", "softmax")) + 1
+
+
+def test_hoisted_program_is_a_permutation_with_the_same_bits():
+    """JitProgram.hoisted moves the weight-gradient Kernels of layers 2.. to where their inputs exist:
+    the same Kernels, every intermediate released after its last reader, and on the oracle backend
+    the same outputs bit for bit; nothing is read after it was released (the backend would raise)."""
+    prog = mlp.mlp_grad_program(B, DIMS, global_batch=2 * B)
+    hoisted = prog.hoisted(["dW2", "dW3"])
+    names = [s.name for s in prog.steps if s.kind == "execute"]
+    moved = [s.name for s in hoisted.steps if s.kind == "execute"]
+    assert sorted(names) == sorted(moved) and names != moved
+    assert moved.index("dW3") < moved.index("dz2") < moved.index("dW2") < moved.index("dz1") < moved.index("dW1") == len(moved) - 1
+    assert {id(s.kernel) for s in prog.steps if s.kind == "execute"} == {id(s.kernel) for s in hoisted.steps if s.kind == "execute"}
+    frees = [s.name for s in hoisted.steps if s.kind == "free"]
+    assert sorted(frees) == sorted(s.name for s in prog.steps if s.kind == "free") and len(set(frees)) == len(frees)
+    assert prog.hoisted([]).steps and [s.name for s in prog.hoisted([]).steps if s.kind == "execute"] == names
+    x, y = _data()
+    be = OracleBackend()
+    params = [be.put(a) for a in mlp.init_params(DIMS, 0)]
+    ins = [be.put(x), be.put(y), be.put(np.eye(DIMS[-1], dtype=np.float32))] + params
+    a = [be.get(s, "float32").copy() for s in prog.execute(be, ins)]
+    b = [be.get(s, "float32").copy() for s in hoisted.execute(be, ins)]
+    for u, v in zip(a, b):
+        assert np.array_equal(u.view(np.uint32), v.view(np.uint32))
