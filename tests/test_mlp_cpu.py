@@ -123,9 +123,16 @@ def _rank_main(rank, world, port, out):
         s = tr.step(sx, sy, world=world)
         losses.append(float(be.get(s, "float32")[0]))
         be.dec_ref(s)
-    # on several ranks dW3 and dW2 are hoisted to where their inputs exist; whatever small outputs came before
-    # a weight gradient ride with its sum: (loss, dW3), (db3, dW2), (db2, db1, dW1)
-    assert tr.hoist and tr.overlap and be.joined and be.async_calls == [2, 2, 3] * 2, be.async_calls
+    # each step summed loss and bias gradients as one group, then every weight gradient as it appeared
+    assert tr.overlap and be.joined and be.async_calls == [5, 1, 1] * 2, be.async_calls   # loss + biases ride with dW1
+    # with dW3 and dW2 hoisted to where their inputs exist, whatever small outputs came before a weight
+    # gradient ride with its sum: (loss, dW3), (db3, dW2), (db2, db1, dW1); the step is the same step
+    be.async_calls.clear()
+    th = mlp.MlpTrainer(be, DIMS, hi - lo, B, hoist=True)
+    s = th.step(sx, sy, world=world)
+    assert th.hoist and be.async_calls == [2, 2, 3], be.async_calls
+    assert abs(float(be.get(s, "float32")[0]) - losses[0]) <= 1e-6 * abs(losses[0])
+    be.dec_ref(s)
     if rank == 0:
         np.savez(out, losses=np.array(losses), **{f"p{i}": be.get(s, "float32") for i, s in enumerate(tr.params)})
     dist.destroy_process_group()
