@@ -89,8 +89,13 @@ class ClockSampler:
         try:
             import pynvml
             pynvml.nvmlInit()
-            visible = [v for v in os.environ.get("CUDA_VISIBLE_DEVICES", "").split(",") if v.strip().isdigit()]
-            self.nvml, self.handle = pynvml, pynvml.nvmlDeviceGetHandleByIndex(int(visible[index]) if index < len(visible) else index)
+            self.nvml = pynvml
+            try:       # the CUDA device's own UUID: NVML may number the GPUs of the machine differently
+                import torch
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(f"GPU-{torch.cuda.get_device_properties(index).uuid}")
+            except Exception:
+                visible = [v for v in os.environ.get("CUDA_VISIBLE_DEVICES", "").split(",") if v.strip().isdigit()]
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(int(visible[index]) if index < len(visible) else index)
             self.sm_max = int(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
             self._read_nvml()
             self.source = "nvml, every 5 ms"
