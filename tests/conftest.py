@@ -28,4 +28,10 @@ def backend(lib):
     from jax_js_b200.backend import CudaBackend
     be = CudaBackend(int(os.environ.get("JAXCUDA_DEVICE", "0")))
     yield be
+    # A session run with JAXCUDA_CHECKED=1 is the memory check of the whole suite: no load whose range
+    # the planner had proven may have fallen outside its buffer in any test.
+    if os.environ.get("JAXCUDA_CHECKED", "0") not in ("", "0"):
+        allowed, proven = be.checked_counts()
+        print(f"\nchecked build: {allowed} loads outside their buffers by the Kernels' own indices, {proven} outside a proven range")
+        assert proven == 0
     be.close()
