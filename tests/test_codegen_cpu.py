@@ -242,3 +242,27 @@ def test_step_list_check_reports_epilogue_fusion_and_small_batches(lib):
     assert len(report) == 12                     # 27 Kernels in 12 launches
     body = source[source.index("jx_batch("):]
     assert body.count("__syncthreads();") == 11 and "__restrict__" not in body.split("{")[0]
+
+
+def test_checked_build_sources_compile_without_a_gpu():
+    """JAXCUDA_CHECKED=1 (read once per process, hence the child): every scalar load of the generated
+    source goes through jx_ix, and NVRTC accepts the result for each skeleton."""
+    import os
+    import subprocess
+    import sys
+    script = r"""
+import os, sys
+sys.path.insert(0, os.environ["REPO_ROOT"])
+from jax_js_b200 import AluOp, programs as P
+from jax_js_b200.backend import check_kernel
+kernels = [P.softmax_exp_kernel(64, 512), P.row_reduce_kernel(64, 512, AluOp.Max), P.dot_kernel(256, 256, 128, bias=True, relu=True),
+           P.dot_kernel(64, 10, 784), P.conv2d_kernel(2, 3, 17, 19, 5, 3, 3, 1, 1), P.conv2d_kernel(8, 64, 28, 28, 128, 3, 3, 1, 1),
+           P.matvec_kernel(512, 1024)]
+for k in kernels:
+    describe, source = check_kernel(k, compile=True)[:2]
+    assert "jx_ix(" in source, describe
+print("ok", len(kernels))
+"""
+    env = dict(os.environ, JAXCUDA_CHECKED="1", REPO_ROOT=str(ROOT))
+    out = subprocess.run([sys.executable, "-c", script], env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0 and out.stdout.strip() == "ok 7", out.stdout[-500:] + out.stderr[-1500:]
